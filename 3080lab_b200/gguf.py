@@ -1,0 +1,216 @@
+"""GGUF container reader and the Q4_0 block codec (host side, numpy).
+
+Call surface follows the reference's `lab/gguf.py`: `GGUF(path).meta / .tensors / .raw(name) / .f32(name)`
+(lab/gguf.py:27-85) and `q4_0_blocks(bytes) -> (d, q)` (lab/gguf.py:88-94).  Written from the GGUF v2/v3 file
+format and the ggml Q4_0 block definition; the device layout helpers restate `q4_rows` / `to_device_q4`
+(scripts/qwen_gguf.py:44-60).
+
+Q4_0 block = 18 bytes for 32 weights: an fp16 scale `d` followed by 16 bytes `qs`.  Weight i (i < 16) is the low
+nibble of qs[i], weight i + 16 the high nibble; the value is `d * (nibble - 8)`.
+
+Device layout ("canonical" in this package, the reference's): `W` int32 `[N, K/8]`, nibble i of word w is weight
+8w + i (natural weight order, not ggml's low-half/high-half order); `S` fp16 `[N, K/32]`.
+"""
+from __future__ import annotations
+
+import mmap
+import struct
+from dataclasses import dataclass
+from pathlib import Path
+
+import numpy as np
+
+# ggml type id -> (name, weights per block, bytes per block)
+GGML_TYPES = {0: ("F32", 1, 4), 1: ("F16", 1, 2), 2: ("Q4_0", 32, 18)}
+
+_FIXED = {0: "B", 1: "b", 2: "H", 3: "h", 4: "I", 5: "i", 6: "f", 7: "?", 10: "Q", 11: "q", 12: "d"}
+_T_STRING, _T_ARRAY = 8, 9
+
+
+@dataclass(frozen=True)
+class TensorInfo:
+    name: str
+    dims: tuple          # ggml order: dims[0] is the contiguous (K) axis, dims[1] the rows (N)
+    type: int
+    offset: int          # relative to the start of the data section
+
+
+class _Cursor:
+    """Little-endian reader over a bytes-like object."""
+
+    def __init__(self, buf):
+        self.buf, self.at = buf, 0
+
+    def take(self, fmt: str):
+        size = struct.calcsize("<" + fmt)
+        out = struct.unpack_from("<" + fmt, self.buf, self.at)
+        self.at += size
+        return out
+
+    def string(self) -> str:
+        n, = self.take("Q")
+        s = bytes(self.buf[self.at:self.at + n]).decode("utf-8", "replace")
+        self.at += n
+        return s
+
+    def value(self, t: int):
+        if t == _T_STRING:
+            return self.string()
+        if t == _T_ARRAY:
+            et, n = self.take("IQ")
+            return [self.value(et) for _ in range(n)]
+        if t not in _FIXED:
+            raise ValueError(f"unknown GGUF metadata type {t}")
+        return self.take(_FIXED[t])[0]
+
+
+class GGUF:
+    """Parsed GGUF file.  `meta` maps key -> value, `tensors` maps name -> TensorInfo; tensor bytes stay memory-mapped."""
+
+    def __init__(self, path):
+        self.path = Path(path)
+        self._fh = open(self.path, "rb")
+        self._map = mmap.mmap(self._fh.fileno(), 0, access=mmap.ACCESS_READ)
+        cur = _Cursor(self._map)
+        magic, = cur.take("4s")
+        if magic != b"GGUF":
+            raise ValueError(f"{self.path}: not a GGUF file (magic {magic!r})")
+        version, n_tensors, n_kv = cur.take("IQQ")
+        if version not in (2, 3):
+            raise ValueError(f"{self.path}: GGUF version {version} not supported")
+        self.version = version
+        self.meta: dict = {}
+        for _ in range(n_kv):
+            key = cur.string()
+            t, = cur.take("I")
+            self.meta[key] = cur.value(t)
+        self.tensors: dict[str, TensorInfo] = {}
+        for _ in range(n_tensors):
+            name = cur.string()
+            nd, = cur.take("I")
+            dims = cur.take(f"{nd}Q")
+            t, off = cur.take("IQ")
+            self.tensors[name] = TensorInfo(name, tuple(dims), t, off)
+        align = int(self.meta.get("general.alignment", 32))
+        self.data_start = -(-cur.at // align) * align
+        self.mm = np.frombuffer(self._map, dtype=np.uint8)
+
+    def raw(self, name: str):
+        """-> (uint8 view of the tensor's bytes, TensorInfo)."""
+        t = self.tensors[name]
+        if t.type not in GGML_TYPES:
+            raise NotImplementedError(f"ggml type {t.type} of {name}")
+        _, per, size = GGML_TYPES[t.type]
+        count = int(np.prod(t.dims))
+        begin = self.data_start + t.offset
+        return self.mm[begin:begin + count // per * size], t
+
+    def f32(self, name: str) -> np.ndarray:
+        """Dequantised fp32 array shaped rows-first (reversed ggml dims)."""
+        b, t = self.raw(name)
+        kind = GGML_TYPES[t.type][0]
+        if kind == "F32":
+            flat = b.view(np.float32)
+        elif kind == "F16":
+            flat = b.view(np.float16).astype(np.float32)
+        else:
+            d, q = q4_0_blocks(b)
+            flat = (d[:, None] * (q.astype(np.float32) - 8.0)).reshape(-1)
+        return flat.reshape(tuple(reversed(t.dims)))
+
+
+def q4_0_blocks(b: np.ndarray):
+    """Decode raw Q4_0 bytes -> (d float32 [nblk], q uint8 [nblk, 32]); q is in weight order and still carries the
+    +8 offset (value = d * (q - 8)).  Same contract as the reference's `q4_0_blocks` (lab/gguf.py:88-94)."""
+    rec = np.ascontiguousarray(b, dtype=np.uint8).reshape(-1, 18)
+    d = np.ascontiguousarray(rec[:, 0:2]).view(np.float16).reshape(-1).astype(np.float32)
+    packed = rec[:, 2:18]
+    q = np.empty((rec.shape[0], 32), np.uint8)
+    q[:, :16] = packed & 0x0F
+    q[:, 16:] = packed >> 4
+    return d, q
+
+
+def q4_0_encode(q: np.ndarray, d: np.ndarray) -> np.ndarray:
+    """Inverse of `q4_0_blocks`: q uint8 [..., 32] in weight order (0..15), d fp16 [...] -> uint8 bytes [nblk * 18]."""
+    q = np.asarray(q, np.uint8).reshape(-1, 32)
+    d = np.asarray(d, np.float16).reshape(-1)
+    rec = np.empty((q.shape[0], 18), np.uint8)
+    rec[:, 0:2] = d.view(np.uint8).reshape(-1, 2)
+    rec[:, 2:18] = (q[:, :16] & 0x0F) | (q[:, 16:] << 4)
+    return rec.reshape(-1)
+
+
+def q4_rows(g: GGUF, name: str):
+    """-> (q uint8 [N, K] with values 0..15, d fp16 [N, K/32]) for a Q4_0 tensor (scripts/qwen_gguf.py:44-51)."""
+    b, t = g.raw(name)
+    if GGML_TYPES[t.type][0] != "Q4_0":
+        raise ValueError(f"{name} is not Q4_0")
+    K, N = t.dims
+    _, q = q4_0_blocks(b)
+    d16 = np.ascontiguousarray(np.ascontiguousarray(b).reshape(-1, 18)[:, 0:2]).view(np.float16).reshape(N, K // 32)
+    return q.reshape(N, K), d16
+
+
+def pack_nibbles(q: np.ndarray) -> np.ndarray:
+    """q uint8 [N, K] (0..15) -> W int32 [N, K/8]: nibble i of word w = weight 8w + i (scripts/qwen_gguf.py:54-60)."""
+    N, K = q.shape
+    if K % 32:
+        raise ValueError("K must be a multiple of the 32-weight block")
+    lanes = q.reshape(N, K // 8, 8).astype(np.uint32)
+    words = np.zeros((N, K // 8), np.uint32)
+    for i in range(8):
+        words |= lanes[:, :, i] << np.uint32(4 * i)
+    return words.view(np.int32)
+
+
+def unpack_nibbles(W: np.ndarray) -> np.ndarray:
+    """W int32 [N, K/8] -> q uint8 [N, K] (0..15); inverse of `pack_nibbles`."""
+    words = np.ascontiguousarray(W).view(np.uint32)
+    N, KW = words.shape
+    q = np.empty((N, KW, 8), np.uint8)
+    for i in range(8):
+        q[:, :, i] = (words >> np.uint32(4 * i)) & np.uint32(15)
+    return q.reshape(N, KW * 8)
+
+
+def write_gguf(path, meta: dict, tensors: dict, alignment: int = 32) -> None:
+    """Write a minimal GGUF v3 file (used by the tests and by tools that export synthetic models).
+
+    `meta`: key -> int / float / str / bool / list of those.  `tensors`: name -> (ggml_type, dims_ggml_order, bytes)."""
+    def enc_str(s):
+        raw = s.encode("utf-8")
+        return struct.pack("<Q", len(raw)) + raw
+
+    def enc_val(v):
+        if isinstance(v, bool):
+            return 7, struct.pack("<?", v)
+        if isinstance(v, int):
+            return (4, struct.pack("<I", v)) if 0 <= v < 2 ** 32 else (11, struct.pack("<q", v))
+        if isinstance(v, float):
+            return 6, struct.pack("<f", v)
+        if isinstance(v, str):
+            return _T_STRING, enc_str(v)
+        if isinstance(v, (list, tuple)):
+            if not v:
+                return _T_ARRAY, struct.pack("<IQ", 4, 0)
+            et, _ = enc_val(v[0])
+            return _T_ARRAY, struct.pack("<IQ", et, len(v)) + b"".join(enc_val(x)[1] for x in v)
+        raise TypeError(type(v))
+
+    meta = dict(meta)
+    meta.setdefault("general.alignment", alignment)
+    head = struct.pack("<4sIQQ", b"GGUF", 3, len(tensors), len(meta))
+    for k, v in meta.items():
+        t, payload = enc_val(v)
+        head += enc_str(k) + struct.pack("<I", t) + payload
+    offset, blobs = 0, []
+    for name, (ttype, dims, data) in tensors.items():
+        data = bytes(data)
+        head += enc_str(name) + struct.pack("<I", len(dims)) + struct.pack(f"<{len(dims)}Q", *dims)
+        head += struct.pack("<IQ", ttype, offset)
+        pad = -len(data) % alignment
+        blobs.append(data + b"\0" * pad)
+        offset += len(data) + pad
+    head += b"\0" * (-len(head) % alignment)
+    Path(path).write_bytes(head + b"".join(blobs))

@@ -1,0 +1,100 @@
+"""Generate the golden fixtures in this folder by running the reference's own Python code.
+
+Run once in a container that has the reference checked out:
+
+    python tests/golden/make_golden.py /path/to/reference
+
+It imports the reference's `lab.gguf` (numpy only) and records what that code returns for seeded inputs.  The
+fixtures are small .npz files; the tests never need the reference at run time.
+
+Fixtures:
+  q4_0_codec.npz   random Q4_0 bytes -> reference q4_0_blocks(d, q) and the GGUF.f32 dequantisation
+  gguf_file.npz    a tiny GGUF file (bytes) -> what the reference's GGUF class parses out of it
+  gemv_small.npz   a 64 x 256 GEMV drawn like lab/experiments/gemv5.py:40-46, dequantise-and-dot by reference code
+  gemv_ffn_up.npz  the 8960 x 1536 ffn_up GEMV: y from the reference's fp32 dequantise-and-dot, and the float64 oracle
+"""
+from __future__ import annotations
+
+import importlib
+import sys
+import tempfile
+from pathlib import Path
+
+import numpy as np
+
+HERE = Path(__file__).resolve().parent
+ROOT = HERE.parents[1]
+
+
+def gemv_inputs(n: int, k: int, bf16_x: bool):
+    """Input recipe of lab/experiments/gemv5.py:40-46 (rng = default_rng(n + k); q, then d, then x)."""
+    rng = np.random.default_rng(n + k)
+    q = rng.integers(0, 16, size=(n, k), dtype=np.uint32)
+    d = rng.uniform(0.002, 0.02, size=(n, k // 32)).astype(np.float16)
+    x = rng.standard_normal(k).astype(np.float32)
+    if bf16_x:                                   # gemv5 truncates x to bf16; the ffn_up configuration keeps fp32
+        x = ((x.view(np.uint32) >> 16) << 16).view(np.float32)
+    return q.astype(np.uint8), d, x
+
+
+def to_q4_0_bytes(q: np.ndarray, d: np.ndarray) -> np.ndarray:
+    """Rows of natural-order nibbles -> ggml Q4_0 records (low nibbles = weights 0..15, high = 16..31)."""
+    qb = q.reshape(-1, 32)
+    rec = np.empty((qb.shape[0], 18), np.uint8)
+    rec[:, :2] = d.reshape(-1).view(np.uint8).reshape(-1, 2)
+    rec[:, 2:] = qb[:, :16] | (qb[:, 16:] << 4)
+    return rec.reshape(-1)
+
+
+def main(ref_root: str) -> None:
+    sys.path.insert(0, ref_root)
+    ref = importlib.import_module("lab.gguf")
+    sys.path.insert(0, str(ROOT))
+    ours = importlib.import_module("3080lab_b200.gguf")
+
+    # 1. codec
+    rng = np.random.default_rng(1)
+    raw = rng.integers(0, 256, size=96 * 18, dtype=np.uint8)
+    rec = raw.reshape(-1, 18)
+    rec[:, :2] = rng.uniform(-0.05, 0.05, size=96).astype(np.float16).view(np.uint8).reshape(-1, 2)
+    d, q = ref.q4_0_blocks(raw)
+    deq = (d[:, None] * (q.astype(np.float32) - 8)).reshape(-1)          # the GGUF.f32 Q4_0 branch
+    np.savez_compressed(HERE / "q4_0_codec.npz", raw=raw, d=d, q=q, f32=deq)
+
+    # 2. a GGUF file parsed by the reference reader
+    qs, ds, _ = gemv_inputs(16, 64, False)
+    f16t = rng.standard_normal((4, 8)).astype(np.float16)
+    f32t = rng.standard_normal(8).astype(np.float32)
+    with tempfile.TemporaryDirectory() as tmp:
+        path = Path(tmp) / "tiny.gguf"
+        ours.write_gguf(path, {"general.architecture": "qwen2", "qwen2.block_count": 2,
+                               "qwen2.rope.freq_base": 1e6, "tokens": ["a", "b", "c"]},
+                        {"blk.0.attn_q.weight": (2, (64, 16), to_q4_0_bytes(qs, ds).tobytes()),
+                         "token_embd.weight": (1, (8, 4), f16t.tobytes()),
+                         "output_norm.weight": (0, (8,), f32t.tobytes())})
+        blob = np.frombuffer(path.read_bytes(), np.uint8)
+        g = ref.GGUF(path)
+        np.savez_compressed(
+            HERE / "gguf_file.npz", blob=blob, data_start=g.data_start,
+            meta_keys=np.array(sorted(g.meta)), meta_block_count=g.meta["qwen2.block_count"],
+            meta_freq_base=g.meta["qwen2.rope.freq_base"], meta_tokens=np.array(g.meta["tokens"]),
+            names=np.array(list(g.tensors)), dims_q=np.array(g.tensors["blk.0.attn_q.weight"].dims),
+            q_f32=g.f32("blk.0.attn_q.weight"), e_f32=g.f32("token_embd.weight"), n_f32=g.f32("output_norm.weight"))
+        del g
+
+    # 3/4. GEMV: the reference's numpy dequantise-and-dot on gemv5's input recipe
+    for name, n, k, bf in (("gemv_small", 64, 256, True), ("gemv_ffn_up", 8960, 1536, False)):
+        q, d, x = gemv_inputs(n, k, bf)
+        dd, qq = ref.q4_0_blocks(to_q4_0_bytes(q, d))
+        w = (dd[:, None] * (qq.astype(np.float32) - 8)).reshape(n, k)     # lab/gguf.py:77-79
+        y32 = w @ x
+        y64 = ((q.astype(np.float64) - 8) * np.repeat(d.astype(np.float64), 32, axis=1)) @ x.astype(np.float64)
+        out = {"n": n, "k": k, "bf16_x": bf, "y_ref_f32": y32, "y_ref_f64": y64}
+        if n * k <= 1 << 16:
+            out.update(q=q, d=d, x=x)
+        np.savez_compressed(HERE / f"{name}.npz", **out)
+    print("fixtures written to", HERE)
+
+
+if __name__ == "__main__":
+    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")

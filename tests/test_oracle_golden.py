@@ -1,0 +1,120 @@
+"""The oracle and the host-side codec against fixtures produced by the reference's own Python code."""
+import numpy as np
+
+from conftest import gemv_inputs, oracle, pkg
+
+
+def test_q4_0_blocks_matches_reference(golden):
+    g = golden["q4_0_codec"]
+    for impl in (oracle().q4_0_blocks, pkg("gguf").q4_0_blocks):
+        d, q = impl(g["raw"])
+        assert d.dtype == np.float32 and q.dtype == np.uint8
+        np.testing.assert_array_equal(d, g["d"])
+        np.testing.assert_array_equal(q, g["q"])
+        deq = (d[:, None] * (q.astype(np.float32) - 8)).reshape(-1)
+        np.testing.assert_array_equal(deq, g["f32"])
+
+
+def test_q4_0_encode_round_trip(golden):
+    gg = pkg("gguf")
+    g = golden["q4_0_codec"]
+    d16 = g["raw"].reshape(-1, 18)[:, :2].copy().view(np.float16).reshape(-1)
+    np.testing.assert_array_equal(gg.q4_0_encode(g["q"], d16), g["raw"])
+
+
+def test_gguf_reader_matches_reference(golden, tmp_path):
+    gg = pkg("gguf")
+    g = golden["gguf_file"]
+    path = tmp_path / "tiny.gguf"
+    path.write_bytes(g["blob"].tobytes())
+    f = gg.GGUF(path)
+    assert f.data_start == int(g["data_start"])
+    assert sorted(f.meta) == list(g["meta_keys"])
+    assert f.meta["qwen2.block_count"] == int(g["meta_block_count"])
+    assert abs(f.meta["qwen2.rope.freq_base"] - float(g["meta_freq_base"])) == 0
+    assert f.meta["tokens"] == list(g["meta_tokens"])
+    assert list(f.tensors) == list(g["names"])
+    assert tuple(f.tensors["blk.0.attn_q.weight"].dims) == tuple(g["dims_q"])
+    np.testing.assert_array_equal(f.f32("blk.0.attn_q.weight"), g["q_f32"])
+    np.testing.assert_array_equal(f.f32("token_embd.weight"), g["e_f32"])
+    np.testing.assert_array_equal(f.f32("output_norm.weight"), g["n_f32"])
+    q, d = gg.q4_rows(f, "blk.0.attn_q.weight")
+    W = gg.pack_nibbles(q)
+    np.testing.assert_array_equal(gg.unpack_nibbles(W), q)
+    np.testing.assert_array_equal(oracle().dequant(W, d, np.float32), g["q_f32"])
+
+
+def test_gguf_rejects_bad_magic(tmp_path):
+    import pytest
+    p = tmp_path / "bad.gguf"
+    p.write_bytes(b"GGML" + b"\0" * 64)
+    with pytest.raises(ValueError):
+        pkg("gguf").GGUF(p)
+
+
+def test_gemv_oracle_small_matches_reference(golden):
+    g = golden["gemv_small"]
+    q, d, x = gemv_inputs(int(g["n"]), int(g["k"]), bool(g["bf16_x"]))
+    np.testing.assert_array_equal(q, g["q"])
+    np.testing.assert_array_equal(d, g["d"])
+    np.testing.assert_array_equal(x, g["x"])
+    W = pkg("gguf").pack_nibbles(q)
+    o = oracle()
+    np.testing.assert_array_equal(o.gemv_ref(W, d, x), g["y_ref_f64"])
+    y32 = o.gemv_numpy_f32(W, d, x)
+    assert np.max(np.abs(y32 - g["y_ref_f32"])) <= 1e-5 * np.max(np.abs(g["y_ref_f32"]))
+
+
+def test_gemv_oracle_ffn_up_matches_reference(golden):
+    """The 8960 x 1536 ffn_up GEMV of the first benchmark configuration."""
+    g = golden["gemv_ffn_up"]
+    q, d, x = gemv_inputs(8960, 1536, False)
+    W = pkg("gguf").pack_nibbles(q)
+    o = oracle()
+    y = o.gemv_ref(W, d, x)
+    np.testing.assert_allclose(y, g["y_ref_f64"], rtol=0, atol=1e-12)
+    scale = np.max(np.abs(g["y_ref_f64"]))
+    assert np.max(np.abs(g["y_ref_f32"] - y)) / scale < 1e-5          # the reference's fp32 numpy path vs float64
+
+
+def test_quant_q8_1_properties():
+    o = oracle()
+    rng = np.random.default_rng(3)
+    x = rng.standard_normal((5, 256)).astype(np.float16)
+    x[1, 32:64] = 0                                    # an all-zero block: d = 0, q = 0
+    x[2, 0] = 60000.0                                  # near the fp16 maximum
+    q, d, s = o.quant_q8_1(x)
+    assert q.dtype == np.int8 and d.dtype == np.float16 and s.dtype == np.int32
+    assert np.all(np.abs(q.astype(int)) <= 127)
+    assert np.all(q[1, 32:64] == 0) and d[1, 1] == 0
+    np.testing.assert_array_equal(s, q.reshape(5, 8, 32).astype(np.int32).sum(-1))
+    amax = np.abs(x.astype(np.float32)).reshape(5, 8, 32).max(-1)
+    # the block maximum quantises to +-127 exactly
+    hit = np.abs(q.reshape(5, 8, 32).astype(int)).max(-1)
+    assert np.all(hit[amax > 0] == 127)
+    recon = q.reshape(5, 8, 32) * (amax / np.float32(127))[..., None]
+    assert np.max(np.abs(recon - x.astype(np.float32).reshape(5, 8, 32))) <= 0.5 * np.max(amax / 127) * 1.0001
+
+
+def test_blockdot_and_mmq_consistent():
+    o = oracle()
+    rng = np.random.default_rng(4)
+    M, K, P = 24, 128, 5
+    W = rng.integers(0, 2 ** 32, size=(M, K // 8), dtype=np.uint32).view(np.int32)
+    S = rng.uniform(0.002, 0.02, size=(M, K // 32)).astype(np.float16)
+    x = rng.standard_normal((P, K)).astype(np.float16)
+    xq, xd, _ = o.quant_q8_1(x)
+    dots = o.blockdot(W, xq)
+    q4 = o.unpack_words(W) - 8
+    slow = np.zeros((P, M, K // 32), np.int64)
+    for p in range(P):
+        for m in range(M):
+            for b in range(K // 32):
+                slow[p, m, b] = int(np.dot(q4[m, 32 * b:32 * b + 32], xq[p, 32 * b:32 * b + 32].astype(np.int64)))
+    np.testing.assert_array_equal(dots, slow)
+    y = o.mmq(W, S, xq, xd)
+    y2 = np.einsum("pmb,mb,pb->pm", dots.astype(np.float64), S.astype(np.float64), xd.astype(np.float64))
+    np.testing.assert_allclose(y, y2, rtol=1e-12, atol=1e-12)
+    # int8 activations cost about half a percent against the fp16-activation GEMV
+    yf = x.astype(np.float64) @ o.dequant(W, S).T
+    assert np.max(np.abs(y - yf)) / np.max(np.abs(yf)) < 2e-2
