@@ -1,0 +1,318 @@
+// Decode attention: RoPE(q), RoPE(k_new), K/V append, GQA attention over an fp16 KV cache, split over the context.
+//
+// Reference arithmetic: ATTN4 (lab/qwen_kernels.py:517-605): NeoX pairs (d, d + HD/2) with fp32 cos/sin tables, q and
+// the new k rounded to 16 bits after rotation, one writer per KV head for the cache append while readers take the new
+// position from shared memory, s_j = (q . k_j) * scale, e_j = __expf(s_j - max), out = round16(sum e_j v_j / sum e_j).
+// The split over the context follows the flash-decoding ATTN2 (:358-442): per-chunk (max, sum, partial output) go to
+// a workspace and the last CTA to arrive combines them, here in chunk order so the result does not depend on timing.
+//
+// B200 shape: one CTA per (chunk of 128 positions, KV head, sequence) serves all NH/NKV query heads of that KV head,
+// so every K/V row is read once.  Scores: one thread per position, its whole K row (HD * 2 bytes) in flight as
+// 16-byte loads.  P.V: HD/8 lanes per row with 16-byte loads, 16 rows in flight per warp.
+#include "q4b_internal.h"
+
+namespace q4b {
+
+namespace {
+
+constexpr int CH = 128;        // positions per CTA
+constexpr int AT = 128;        // threads per CTA
+constexpr int NW = AT / 32;
+
+template <int HD, int GRP>
+__global__ void __launch_bounds__(AT) attn_decode_kernel(const __half* __restrict__ qkv, const float* __restrict__ cosT,
+                                                         const float* __restrict__ sinT, const int64_t* __restrict__ posp,
+                                                         __half* __restrict__ kc, __half* __restrict__ vc,
+                                                         __half* __restrict__ out, int NH, int NKV, int max_len,
+                                                         float scale, unsigned* cnt, float* part_ml, float* part_o, int NC) {
+  constexpr int HALF = HD / 2;
+  constexpr int LPR = HD / 8;          // lanes per K/V row in the P.V pass (16-byte loads)
+  constexpr int PPI = 32 / LPR;        // rows per warp iteration
+  __shared__ __align__(16) float qs[GRP][HD];
+  __shared__ __align__(16) float kn[HD];
+  __shared__ __align__(16) float vn[HD];
+  __shared__ float sc[GRP][CH];
+  __shared__ float redw[GRP][NW];
+  __shared__ __align__(16) float red_o[NW][GRP][HD];
+  __shared__ float stat[GRP][2];
+  __shared__ bool last;
+
+  pdl_wait();
+  const int b = blockIdx.z, kvh = blockIdx.y, chunk = blockIdx.x;
+  const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
+  int p = (int)posp[b];
+  p = p < 0 ? 0 : (p >= max_len ? max_len - 1 : p);
+  const int c0 = chunk * CH;
+  if (c0 > p) return;                                            // chunk entirely in the future: nothing to do
+  const int nact = p / CH + 1;                                   // active chunks of this sequence
+  const bool has_new = p < c0 + CH;                              // this chunk holds the position being appended
+  const int QKV = (NH + 2 * NKV) * HD;
+  const __half* row = qkv + (size_t)b * QKV;
+  const float* cs = cosT + (size_t)p * HALF;
+  const float* sn = sinT + (size_t)p * HALF;
+  __half* kbase = kc + ((size_t)b * NKV + kvh) * (size_t)max_len * HD;
+  __half* vbase = vc + ((size_t)b * NKV + kvh) * (size_t)max_len * HD;
+
+  for (int e = t; e < GRP * HD; e += AT) {
+    const int hl = e / HD, d = e - hl * HD, dd = d % HALF;
+    const __half* qh = row + (size_t)(kvh * GRP + hl) * HD;
+    const float a = __half2float(qh[d]), o = __half2float(qh[d < HALF ? d + HALF : d - HALF]);
+    const float r = d < HALF ? a * cs[dd] - o * sn[dd] : a * cs[dd] + o * sn[dd];
+    qs[hl][d] = __half2float(__float2half_rn(r));
+  }
+  if (has_new) {
+    for (int d = t; d < HD; d += AT) {
+      const int dd = d % HALF;
+      const __half* kh = row + (size_t)NH * HD + (size_t)kvh * HD;
+      const float a = __half2float(kh[d]), o = __half2float(kh[d < HALF ? d + HALF : d - HALF]);
+      const __half kr = __float2half_rn(d < HALF ? a * cs[dd] - o * sn[dd] : a * cs[dd] + o * sn[dd]);
+      const __half vr = row[(size_t)(NH + NKV) * HD + (size_t)kvh * HD + d];
+      kn[d] = __half2float(kr);
+      vn[d] = __half2float(vr);
+      kbase[(size_t)p * HD + d] = kr;                            // the only writer of (b, kvh, p)
+      vbase[(size_t)p * HD + d] = vr;
+    }
+  }
+  __syncthreads();
+
+  // ---- scores: thread t <-> position c0 + t
+  float s[GRP];
+  {
+    const int j = c0 + t;
+    const bool valid = j <= p;
+#pragma unroll
+    for (int h = 0; h < GRP; ++h) s[h] = 0.f;
+    if (valid) {
+      if (j == p) {
+#pragma unroll 4
+        for (int d = 0; d < HD; ++d) {
+          const float k = kn[d];
+#pragma unroll
+          for (int h = 0; h < GRP; ++h) s[h] = fmaf(qs[h][d], k, s[h]);
+        }
+      } else {
+        const uint4* kr = reinterpret_cast<const uint4*>(kbase + (size_t)j * HD);
+        uint4 kv[HD / 8];
+#pragma unroll
+        for (int i = 0; i < HD / 8; ++i) kv[i] = __ldg(kr + i);
+#pragma unroll
+        for (int i = 0; i < HD / 8; ++i) {
+          const uint32_t w[4] = {kv[i].x, kv[i].y, kv[i].z, kv[i].w};
+          float kf[8];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[u]));
+            kf[2 * u] = f.x;
+            kf[2 * u + 1] = f.y;
+          }
+#pragma unroll
+          for (int h = 0; h < GRP; ++h) {
+            const float4 q0 = *reinterpret_cast<const float4*>(&qs[h][8 * i]);
+            const float4 q1 = *reinterpret_cast<const float4*>(&qs[h][8 * i + 4]);
+            float a = s[h];
+            a = fmaf(q0.x, kf[0], a); a = fmaf(q0.y, kf[1], a); a = fmaf(q0.z, kf[2], a); a = fmaf(q0.w, kf[3], a);
+            a = fmaf(q1.x, kf[4], a); a = fmaf(q1.y, kf[5], a); a = fmaf(q1.z, kf[6], a); a = fmaf(q1.w, kf[7], a);
+            s[h] = a;
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int h = 0; h < GRP; ++h) s[h] = valid ? s[h] * scale : -INFINITY;
+  }
+  // chunk maximum per head
+#pragma unroll
+  for (int h = 0; h < GRP; ++h) {
+    const float m = warp_max(s[h]);
+    if (lane == 0) redw[h][warp] = m;
+  }
+  __syncthreads();
+  float mx[GRP];
+#pragma unroll
+  for (int h = 0; h < GRP; ++h) {
+    float m = redw[h][0];
+#pragma unroll
+    for (int w = 1; w < NW; ++w) m = fmaxf(m, redw[h][w]);
+    mx[h] = m;                                                   // finite: position c0 <= p is always valid
+  }
+  __syncthreads();
+#pragma unroll
+  for (int h = 0; h < GRP; ++h) {
+    const float e = __expf(s[h] - mx[h]);                        // 0 for masked positions
+    sc[h][t] = e;
+    const float l = warp_sum(e);
+    if (lane == 0) redw[h][warp] = l;
+  }
+  __syncthreads();
+  float ls[GRP];
+#pragma unroll
+  for (int h = 0; h < GRP; ++h) {
+    float l = 0.f;
+#pragma unroll
+    for (int w = 0; w < NW; ++w) l += redw[h][w];
+    ls[h] = l;
+  }
+
+  // ---- P.V: warp w <-> positions c0 + 32w .. +31; lane <-> (row in the iteration, 8 dims)
+  const int psub = lane / LPR, d0 = (lane % LPR) * 8;
+  float acc[GRP][8];
+#pragma unroll
+  for (int h = 0; h < GRP; ++h)
+#pragma unroll
+    for (int u = 0; u < 8; ++u) acc[h][u] = 0.f;
+  constexpr int ITERS = 32 / PPI, UNR = ITERS < 8 ? ITERS : 8;
+  for (int it0 = 0; it0 < ITERS; it0 += UNR) {
+    uint4 vv[UNR];
+#pragma unroll
+    for (int u = 0; u < UNR; ++u) {
+      const int jl = 32 * warp + (it0 + u) * PPI + psub, j = c0 + jl;
+      vv[u] = make_uint4(0u, 0u, 0u, 0u);
+      if (j < p) vv[u] = __ldg(reinterpret_cast<const uint4*>(vbase + (size_t)j * HD + d0));
+    }
+#pragma unroll
+    for (int u = 0; u < UNR; ++u) {
+      const int jl = 32 * warp + (it0 + u) * PPI + psub, j = c0 + jl;
+      if (j > p) continue;
+      float vf[8];
+      if (j == p) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) vf[k] = vn[d0 + k];
+      } else {
+        const uint32_t w[4] = {vv[u].x, vv[u].y, vv[u].z, vv[u].w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[k]));
+          vf[2 * k] = f.x;
+          vf[2 * k + 1] = f.y;
+        }
+      }
+#pragma unroll
+      for (int h = 0; h < GRP; ++h) {
+        const float e = sc[h][jl];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) acc[h][k] = fmaf(e, vf[k], acc[h][k]);
+      }
+    }
+  }
+#pragma unroll
+  for (int h = 0; h < GRP; ++h)
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      float a = acc[h][k];
+#pragma unroll
+      for (int o = 16; o >= LPR; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
+      acc[h][k] = a;
+    }
+  if (psub == 0) {
+#pragma unroll
+    for (int h = 0; h < GRP; ++h)
+#pragma unroll
+      for (int k = 0; k < 8; ++k) red_o[warp][h][d0 + k] = acc[h][k];
+  }
+  __syncthreads();
+
+  // ---- chunk result; a single active chunk writes the output directly
+  const size_t head0 = (size_t)b * NH + (size_t)kvh * GRP;
+  if (nact == 1) {
+    for (int e = t; e < GRP * HD; e += AT) {
+      const int hl = e / HD, d = e - hl * HD;
+      float o = 0.f;
+#pragma unroll
+      for (int w = 0; w < NW; ++w) o += red_o[w][hl][d];
+      float l = 0.f;
+#pragma unroll
+      for (int w = 0; w < NW; ++w) l += redw[hl][w];
+      out[(head0 + hl) * HD + d] = __float2half_rn(o / l);
+    }
+    return;
+  }
+  for (int e = t; e < GRP * HD; e += AT) {
+    const int hl = e / HD, d = e - hl * HD;
+    float o = 0.f;
+#pragma unroll
+    for (int w = 0; w < NW; ++w) o += red_o[w][hl][d];
+    part_o[((head0 + hl) * NC + chunk) * HD + d] = o;
+  }
+  if (t < GRP) {
+    part_ml[((head0 + t) * NC + chunk) * 2] = mx[t];
+    part_ml[((head0 + t) * NC + chunk) * 2 + 1] = ls[t];
+  }
+  __threadfence();
+  __syncthreads();
+  if (t == 0) last = atomicAdd(cnt + (size_t)b * NKV + kvh, 1u) == (unsigned)(nact - 1);
+  __syncthreads();
+  if (!last) return;
+  __threadfence();
+  if (t < GRP) {
+    float M = -INFINITY;
+    for (int c = 0; c < nact; ++c) M = fmaxf(M, __ldcg(part_ml + ((head0 + t) * NC + c) * 2));
+    float L = 0.f;
+    for (int c = 0; c < nact; ++c)
+      L += __ldcg(part_ml + ((head0 + t) * NC + c) * 2 + 1) * __expf(__ldcg(part_ml + ((head0 + t) * NC + c) * 2) - M);
+    stat[t][0] = M;
+    stat[t][1] = L;
+  }
+  __syncthreads();
+  for (int e = t; e < GRP * HD; e += AT) {
+    const int hl = e / HD, d = e - hl * HD;
+    const float M = stat[hl][0];
+    float o = 0.f;
+    for (int c = 0; c < nact; ++c)
+      o += __ldcg(part_o + ((head0 + hl) * NC + c) * HD + d) * __expf(__ldcg(part_ml + ((head0 + hl) * NC + c) * 2) - M);
+    out[(head0 + hl) * HD + d] = __float2half_rn(o / stat[hl][1]);
+  }
+  if (t == 0) cnt[(size_t)b * NKV + kvh] = 0u;
+}
+
+size_t align16(size_t v) { return (v + 15) & ~(size_t)15; }
+
+template <int HD>
+int dispatch_grp(int grp, dim3 grid, cudaStream_t st, const __half* qkv, const float* cosT, const float* sinT,
+                 const int64_t* pos, __half* kc, __half* vc, __half* out, int NH, int NKV, int max_len, float scale,
+                 unsigned* cnt, float* ml, float* po, int NC) {
+#define Q4B_ATTN_CASE(G)                                                                                         \
+  case G:                                                                                                        \
+    attn_decode_kernel<HD, G><<<grid, AT, 0, st>>>(qkv, cosT, sinT, pos, kc, vc, out, NH, NKV, max_len, scale, cnt, \
+                                                   ml, po, NC);                                                  \
+    return Q4B_OK;
+  switch (grp) {
+    Q4B_ATTN_CASE(1) Q4B_ATTN_CASE(2) Q4B_ATTN_CASE(3) Q4B_ATTN_CASE(4) Q4B_ATTN_CASE(5) Q4B_ATTN_CASE(6)
+    Q4B_ATTN_CASE(7) Q4B_ATTN_CASE(8)
+    default: return Q4B_E_SHAPE;
+  }
+#undef Q4B_ATTN_CASE
+}
+
+}  // namespace
+
+size_t attn_decode_workspace(int B, int NH, int HD, int max_len) {
+  if (B <= 0 || NH <= 0 || HD <= 0 || max_len <= 0) return 0;
+  const size_t NC = (size_t)(max_len + CH - 1) / CH;
+  return align16((size_t)B * NH * 4) + align16((size_t)B * NH * NC * 2 * 4) + (size_t)B * NH * NC * HD * 4;
+}
+
+int attn_decode(const void* qkv, const float* cosT, const float* sinT, const int64_t* pos, void* kc, void* vc, void* out,
+                int B, int NH, int NKV, int HD, int max_len, float scale, void* ws, size_t ws_bytes, cudaStream_t st) {
+  if (B <= 0 || NH <= 0 || NKV <= 0 || max_len <= 0 || (NH % NKV) || NH / NKV > 8 || (HD != 64 && HD != 128))
+    return fail(Q4B_E_SHAPE, "attn_decode: need HD in {64,128}, NH a multiple of NKV, NH/NKV <= 8");
+  if (!qkv || !cosT || !sinT || !pos || !kc || !vc || !out || !ws || !aligned16(kc) || !aligned16(vc) || !aligned16(ws))
+    return fail(Q4B_E_ALIGN, "attn_decode: null or misaligned pointer");
+  if (ws_bytes < attn_decode_workspace(B, NH, HD, max_len)) return fail(Q4B_E_WORKSPACE, "attn_decode: workspace too small");
+  const int NC = (max_len + CH - 1) / CH;
+  char* base = reinterpret_cast<char*>(ws);
+  unsigned* cnt = reinterpret_cast<unsigned*>(base);
+  float* ml = reinterpret_cast<float*>(base + align16((size_t)B * NH * 4));
+  float* po = reinterpret_cast<float*>(base + align16((size_t)B * NH * 4) + align16((size_t)B * NH * NC * 2 * 4));
+  dim3 grid(NC, NKV, B);
+  int rc;
+  if (HD == 128)
+    rc = dispatch_grp<128>(NH / NKV, grid, st, (const __half*)qkv, cosT, sinT, pos, (__half*)kc, (__half*)vc, (__half*)out,
+                           NH, NKV, max_len, scale, cnt, ml, po, NC);
+  else
+    rc = dispatch_grp<64>(NH / NKV, grid, st, (const __half*)qkv, cosT, sinT, pos, (__half*)kc, (__half*)vc, (__half*)out,
+                          NH, NKV, max_len, scale, cnt, ml, po, NC);
+  if (rc != Q4B_OK) return fail(rc, "attn_decode: unsupported head group");
+  return check_launch("attn_decode");
+}
+
+}  // namespace q4b

@@ -1,0 +1,142 @@
+// extern "C" surface of libq4b200: argument checks live in the per-op launchers, this file only forwards and keeps
+// the per-thread error text.
+#include <stdio.h>
+#include <string.h>
+
+#include "q4b_internal.h"
+
+namespace q4b {
+
+static thread_local char g_err[256] = "";
+static int g_sm_count = 0;
+
+void set_cuda_error(cudaError_t e, const char* where) {
+  snprintf(g_err, sizeof(g_err), "%s: CUDA error %d (%s)", where, (int)e, cudaGetErrorString(e));
+}
+
+int fail(int code, const char* msg) {
+  snprintf(g_err, sizeof(g_err), "%s", msg);
+  return code;
+}
+
+int sm_count() {
+  if (g_sm_count <= 0) {
+    int dev = 0, n = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess && cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && n > 0)
+      g_sm_count = n;
+    else
+      return 148;
+  }
+  return g_sm_count;
+}
+
+// per-op launchers (defined next to their kernels)
+int gemv_q4_0(const void*, const void*, const void*, void*, const void*, int, int, int, int, cudaStream_t);
+int embed(const void*, const int64_t*, float*, int, int, int, cudaStream_t);
+int rmsnorm(const float*, const float*, void*, int, int, float, cudaStream_t);
+size_t argmax_workspace(int, int);
+int argmax_advance(const float*, int, int, int64_t*, int64_t*, void*, size_t, cudaStream_t);
+size_t attn_decode_workspace(int, int, int, int);
+int attn_decode(const void*, const float*, const float*, const int64_t*, void*, void*, void*, int, int, int, int, int, float,
+                void*, size_t, cudaStream_t);
+size_t head_workspace(int);
+int head_f16_argmax(const void*, const void*, float*, int, int, int64_t*, int64_t*, void*, size_t, cudaStream_t);
+
+}  // namespace q4b
+
+using namespace q4b;
+
+static inline cudaStream_t S(q4b_stream_t s) { return reinterpret_cast<cudaStream_t>(s); }
+
+extern "C" {
+
+int q4b_version(void) { return 1000; }
+
+const char* q4b_last_error(void) { return g_err; }
+
+int q4b_init(int device) {
+  cudaError_t e = cudaSetDevice(device);
+  if (e != cudaSuccess) {
+    set_cuda_error(e, "q4b_init");
+    return Q4B_E_CUDA;
+  }
+  int n = 0;
+  e = cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, device);
+  if (e != cudaSuccess) {
+    set_cuda_error(e, "q4b_init");
+    return Q4B_E_CUDA;
+  }
+  g_sm_count = n;
+  g_err[0] = 0;
+  return Q4B_OK;
+}
+
+int q4b_gemv_q4_0(const void* W, const void* Sc, const void* X, void* Y, const void* AUX, int N, int K, int epilogue,
+                  int x_dtype, q4b_stream_t stream) {
+  return gemv_q4_0(W, Sc, X, Y, AUX, N, K, epilogue, x_dtype, S(stream));
+}
+
+int q4b_rmsnorm(const float* h, const float* w, void* out, int rows, int H, float eps, q4b_stream_t stream) {
+  return rmsnorm(h, w, out, rows, H, eps, S(stream));
+}
+
+int q4b_embed(const void* E, const int64_t* tok, float* h, int rows, int H, int V, q4b_stream_t stream) {
+  return embed(E, tok, h, rows, H, V, S(stream));
+}
+
+size_t q4b_attn_decode_workspace(int B, int NH, int HD, int max_len) { return attn_decode_workspace(B, NH, HD, max_len); }
+
+int q4b_attn_decode(const void* qkv, const float* cosT, const float* sinT, const int64_t* pos, void* kc, void* vc,
+                    void* out, int B, int NH, int NKV, int HD, int max_len, float scale, void* workspace,
+                    size_t workspace_bytes, q4b_stream_t stream) {
+  return attn_decode(qkv, cosT, sinT, pos, kc, vc, out, B, NH, NKV, HD, max_len, scale, workspace, workspace_bytes, S(stream));
+}
+
+size_t q4b_head_workspace(int V) { return head_workspace(V); }
+
+int q4b_head_f16_argmax(const void* E, const void* x, float* logits, int V, int H, int64_t* tok, int64_t* pos,
+                        void* workspace, size_t workspace_bytes, q4b_stream_t stream) {
+  return head_f16_argmax(E, x, logits, V, H, tok, pos, workspace, workspace_bytes, S(stream));
+}
+
+size_t q4b_argmax_workspace(int rows, int V) { return argmax_workspace(rows, V); }
+
+int q4b_argmax_advance(const float* logits, int rows, int V, int64_t* tok, int64_t* pos, void* workspace,
+                       size_t workspace_bytes, q4b_stream_t stream) {
+  return argmax_advance(logits, rows, V, tok, pos, workspace, workspace_bytes, S(stream));
+}
+
+int q4b_decode_step(const q4b_decode_desc* d, q4b_stream_t stream) {
+  if (!d || !d->layer) return fail(Q4B_E_ARG, "decode_step: null descriptor");
+  cudaStream_t st = S(stream);
+  const int H = d->hidden, QR = d->n_heads * d->head_dim;
+#define Q4B_TRY(call)            \
+  do {                           \
+    int rc_ = (call);            \
+    if (rc_ != Q4B_OK) return rc_; \
+  } while (0)
+  Q4B_TRY(embed(d->embed, d->tok, d->h, 1, H, d->vocab, st));
+  for (int i = 0; i < d->layers; ++i) {
+    const q4b_layer& L = d->layer[i];
+    Q4B_TRY(rmsnorm(d->h, L.ln1, d->x, 1, H, d->eps, st));
+    Q4B_TRY(gemv_q4_0(L.qkv.W, L.qkv.S, d->x, d->qkv, L.qkv_bias, L.qkv.N, L.qkv.K, Q4B_EPI_BIASF, Q4B_X_F16, st));
+    Q4B_TRY(attn_decode(d->qkv, d->cosT, d->sinT, d->pos, L.kc, L.vc, d->att, 1, d->n_heads, d->n_kv_heads, d->head_dim,
+                        d->max_len, d->scale, d->attn_ws, d->attn_ws_bytes, st));
+    Q4B_TRY(gemv_q4_0(L.o.W, L.o.S, d->att, d->h, nullptr, L.o.N, L.o.K, Q4B_EPI_RESID, Q4B_X_F16, st));
+    Q4B_TRY(rmsnorm(d->h, L.ln2, d->x, 1, H, d->eps, st));
+    Q4B_TRY(gemv_q4_0(L.gu.W, L.gu.S, d->x, d->act, nullptr, L.gu.N, L.gu.K, Q4B_EPI_SWIGLU, Q4B_X_F16, st));
+    Q4B_TRY(gemv_q4_0(L.down.W, L.down.S, d->act, d->h, nullptr, L.down.N, L.down.K, Q4B_EPI_RESID, Q4B_X_F16, st));
+  }
+  (void)QR;
+  Q4B_TRY(rmsnorm(d->h, d->norm, d->x, 1, H, d->eps, st));
+  if (d->head.W) {
+    Q4B_TRY(gemv_q4_0(d->head.W, d->head.S, d->x, d->logits, nullptr, d->head.N, d->head.K, Q4B_EPI_LOGITS, Q4B_X_F16, st));
+    Q4B_TRY(argmax_advance(d->logits, 1, d->vocab, d->tok, d->pos, d->head_ws, d->head_ws_bytes, st));
+  } else {
+    Q4B_TRY(head_f16_argmax(d->embed, d->x, d->logits, d->vocab, H, d->tok, d->pos, d->head_ws, d->head_ws_bytes, st));
+  }
+#undef Q4B_TRY
+  return Q4B_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,59 @@
+// Internal declarations shared by the .cu files of libq4b200.  Not installed; the public C-ABI is include/q4b200.h.
+#pragma once
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/q4b200.h"
+
+namespace q4b {
+
+// Last CUDA error text seen by a launcher on this thread (read through q4b_last_error()).
+void set_cuda_error(cudaError_t e, const char* where);
+int fail(int code, const char* msg);
+
+inline int check_launch(const char* where) {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    set_cuda_error(e, where);
+    return Q4B_E_CUDA;
+  }
+  return Q4B_OK;
+}
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+int sm_count();
+
+// ---- device helpers -------------------------------------------------------------------------------------------
+#ifdef __CUDACC__
+// Exact nibble -> fp32: bits (0x4B000000 | q) are the float 2^23 + q, so subtracting 2^23 + 8 leaves q - 8.
+__device__ __forceinline__ float nib_f32(uint32_t w, int i) {
+  return __int_as_float(((w >> (4 * i)) & 15u) | 0x4B000000u) - 8388616.0f;
+}
+
+__device__ __forceinline__ uint4 ldg_stream16(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Programmatic dependent launch: wait for the kernels this one depends on / let dependents start their prologue.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+#endif
+
+}  // namespace q4b

@@ -1,0 +1,170 @@
+"""Host engines: the batch-1 fused decode step and its greedy loop.
+
+`FusedQwen` mirrors the reference class of that name (scripts/qwen_fused.py:55-145; GGUF variant
+scripts/qwen_gguf.py:63-144): it owns the weights, the KV cache [L, NKV, max_len, HD], the fp32 residual stream and
+the 16-bit activation buffers as torch CUDA tensors, keeps `tok` / `pos` on the device, and `step()` runs one decode
+token.  `run_fused` mirrors the reference protocol (scripts/qwen_fused.py:148-180): the prompt goes through `step()`
+token by token, one step is captured in a CUDA graph, the graph is replayed once per generated token."""
+from __future__ import annotations
+
+import ctypes as C
+import math
+
+import numpy as np
+import torch
+
+from . import _ffi
+from . import qwen_kernels as K
+from .synth import ModelConfig, rope_tables
+
+
+def _dev(a: np.ndarray, device):
+    return torch.from_numpy(np.ascontiguousarray(a)).to(device)
+
+
+class FusedQwen:
+    def __init__(self, model: dict, max_len: int = 1024, device="cuda:0"):
+        if not torch.cuda.is_available():
+            raise RuntimeError("FusedQwen needs a CUDA device; there is no CPU path")
+        self.cfg: ModelConfig = model["cfg"]
+        c = self.cfg
+        self.device = torch.device(device)
+        self.max_len = max_len
+        torch.cuda.set_device(self.device)
+        K.init(self.device.index or 0)
+        self.embed = _dev(model["embed"], self.device)
+        self.L = []
+        for Lw in model["layers"]:
+            d = {k: _dev(Lw[k], self.device) for k in ("ln1", "ln2", "qkv_b")}
+            for k in ("qkv", "o", "gu", "down"):
+                d[k] = (_dev(Lw[k][0], self.device), _dev(Lw[k][1], self.device))
+            self.L.append(d)
+        self.norm = _dev(model["norm"], self.device)
+        self.head = None if model["head"] is None else tuple(_dev(a, self.device) for a in model["head"])
+        cos, sin = rope_tables(c, max_len)
+        self.cos, self.sin = _dev(cos, self.device), _dev(sin, self.device)
+        f16, f32, dv = torch.float16, torch.float32, self.device
+        self.kc = torch.zeros(c.layers, c.n_kv_heads, max_len, c.head_dim, dtype=f16, device=dv)
+        self.vc = torch.zeros_like(self.kc)
+        self.h = torch.zeros(c.hidden, dtype=f32, device=dv)
+        self.x = torch.zeros(c.hidden, dtype=f16, device=dv)
+        self.qkv = torch.zeros(c.qkv_rows, dtype=f16, device=dv)
+        self.att = torch.zeros(c.q_rows, dtype=f16, device=dv)
+        self.xm = torch.zeros(c.ffn, dtype=f16, device=dv)
+        self.logits = torch.zeros(c.vocab, dtype=f32, device=dv)
+        self.tok = torch.zeros(1, dtype=torch.long, device=dv)
+        self.pos = torch.zeros(1, dtype=torch.long, device=dv)
+        self.attn_ws = K.attn_workspace(1, c.n_heads, c.head_dim, max_len, dv)
+        self.head_ws = K.head_workspace(c.vocab, 1, dv)
+        self.scale = 1.0 / math.sqrt(c.head_dim)
+        self._desc = self._make_desc()
+        self.launches_per_step = 1 + 7 * c.layers + (2 if self.head is None else 3)
+
+    # ---- descriptor for the one-call step -------------------------------------------------------------------------
+    def _make_desc(self):
+        c = self.cfg
+
+        def lin(pair, n, k):
+            return _ffi.Linear(pair[0].data_ptr(), pair[1].data_ptr(), n, k)
+
+        self._layers = (_ffi.Layer * c.layers)()
+        for i, L in enumerate(self.L):
+            self._layers[i] = _ffi.Layer(
+                L["ln1"].data_ptr(), L["ln2"].data_ptr(), L["qkv_b"].data_ptr(),
+                lin(L["qkv"], c.qkv_rows, c.hidden), lin(L["o"], c.hidden, c.q_rows),
+                lin(L["gu"], 2 * c.ffn, c.hidden), lin(L["down"], c.hidden, c.ffn),
+                self.kc[i].data_ptr(), self.vc[i].data_ptr())
+        head = lin(self.head, c.vocab, c.hidden) if self.head is not None else _ffi.Linear(None, None, 0, 0)
+        return _ffi.DecodeDesc(
+            c.layers, c.hidden, c.ffn, c.n_heads, c.n_kv_heads, c.head_dim, c.vocab, self.max_len, c.eps, self.scale,
+            self.embed.data_ptr(), C.cast(self._layers, C.POINTER(_ffi.Layer)), self.norm.data_ptr(), head,
+            self.cos.data_ptr(), self.sin.data_ptr(), self.tok.data_ptr(), self.pos.data_ptr(), self.h.data_ptr(),
+            self.x.data_ptr(), self.qkv.data_ptr(), self.att.data_ptr(), self.xm.data_ptr(), self.logits.data_ptr(),
+            self.attn_ws.data_ptr(), self.attn_ws.numel(), self.head_ws.data_ptr(), self.head_ws.numel())
+
+    # ---- one decode token -------------------------------------------------------------------------------------------
+    def step(self) -> None:
+        """One decode token through q4b_decode_step (all launches issued from C, on the current stream)."""
+        _ffi.call("q4b_decode_step", C.byref(self._desc), torch.cuda.current_stream().cuda_stream)
+
+    def gemv(self, name, wsplit, X, Y, aux, N, Kdim, epi):
+        K.gemv(wsplit[0], wsplit[1], X, Y, aux, N, Kdim, epi)
+
+    def rms(self, w, out):
+        K.rms(self.h, w, out, self.cfg.eps)
+
+    def step_ops(self) -> None:
+        """The same token through the per-op entry points, in the reference's launch order
+        (scripts/qwen_fused.py:113-145)."""
+        c = self.cfg
+        H = c.hidden
+        K.embed(self.embed, self.tok, self.h)
+        for i, L in enumerate(self.L):
+            self.rms(L["ln1"], self.x)
+            self.gemv("qkv", L["qkv"], self.x, self.qkv, L["qkv_b"], c.qkv_rows, H, "biasf")
+            K.attn(self.qkv, self.cos, self.sin, self.pos, self.kc[i], self.vc[i], self.att, c.n_heads, c.n_kv_heads,
+                   c.head_dim, self.max_len, self.scale, self.attn_ws)
+            self.gemv("o", L["o"], self.att, self.h, None, H, c.q_rows, "resid")
+            self.rms(L["ln2"], self.x)
+            self.gemv("gu", L["gu"], self.x, self.xm, None, 2 * c.ffn, H, "swiglu")
+            self.gemv("down", L["down"], self.xm, self.h, None, H, c.ffn, "resid")
+        self.rms(self.norm, self.x)
+        if self.head is None:
+            K.head_argmax(self.embed, self.x, self.logits, self.tok, self.pos, self.head_ws)
+        else:
+            self.gemv("head", self.head, self.x, self.logits, None, c.vocab, H, "logits")
+            K.finish(self.logits, self.tok, self.pos, self.head_ws)
+
+    # ---- graph + greedy loop ------------------------------------------------------------------------------------------
+    def reset(self) -> None:
+        self.kc.zero_()
+        self.vc.zero_()
+        self.pos.zero_()
+        self.tok.zero_()
+
+    def feed(self, ids) -> None:
+        """Prompt through the decode path, token by token; leaves tok = first generated token, pos = len(ids)."""
+        for t in ids:
+            self.tok.fill_(int(t))
+            self.step()
+
+    def capture(self) -> torch.cuda.CUDAGraph:
+        """Capture one `step()` in a CUDA graph (warm-up on a side stream first, state restored afterwards)."""
+        torch.cuda.synchronize()
+        pos0, tok0 = self.pos.clone(), self.tok.clone()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            self.step()
+        torch.cuda.current_stream().wait_stream(side)
+        self.pos.copy_(pos0)
+        self.tok.copy_(tok0)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            self.step()
+        self.pos.copy_(pos0)
+        self.tok.copy_(tok0)
+        torch.cuda.synchronize()
+        return g
+
+
+def run_fused(m: FusedQwen, ids, gen: int):
+    """Greedy decode after a prompt, by graph replay.  -> (tokens [gen], ms per token of a second, timed pass)."""
+    m.reset()
+    m.feed(ids)
+    g = m.capture()
+    pos0, tok0 = m.pos.clone(), m.tok.clone()
+    toks = [int(tok0.item())]
+    for _ in range(gen - 1):
+        g.replay()
+        toks.append(int(m.tok.item()))
+    m.pos.copy_(pos0)
+    m.tok.copy_(tok0)
+    torch.cuda.synchronize()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    for _ in range(gen):
+        g.replay()
+    e.record()
+    torch.cuda.synchronize()
+    return toks, s.elapsed_time(e) / gen

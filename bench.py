@@ -1,0 +1,353 @@
+"""Benchmark of the Qwen2.5-1.5B-shaped Q4_0 decode step (batch 1, 512-token prompt, greedy decode).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One "step" is one greedy decode token of one sequence: the whole hot path (embed, 28 layers, LM head, argmax) replayed
+as one CUDA graph.  With N > 1 (launched under torchrun) every rank decodes its own sequence on its own GPU with a full
+weight copy and no collective on the data path (weak scaling); the value is total tokens per second, timed on the
+device, maximum over ranks.  Prints ONE JSON line on rank 0.
+
+`--impl reference` times the reference's CPU implementation of the same step (its numpy dequantise-and-dot, restated
+in oracle/q4ref.py) on the host cores; each of its steps is a bounded sample of the workload (see `cpu_baseline`).
+"""
+from __future__ import annotations
+
+import argparse
+import importlib
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+METRIC = "decode_tok_per_s_batch1"
+PROMPT, MAX_LEN = 512, 1024
+NOMINAL_HBM_GBS = 8000.0
+
+
+def measured_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        return json.loads(p.read_text()), "measured"
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks / throttle reasons every 200 ms while a timed region runs."""
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu, self.rows, self.proc, self.th = gpu_index, [], None, None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                                          "-lms", "200", "-i", str(self.gpu)], stdout=subprocess.PIPE, text=True)
+        except OSError:
+            self.proc = None
+            return
+        self.th = threading.Thread(target=self._read, daemon=True)
+        self.th.start()
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        for r in self.rows:
+            if len(r) < 9:
+                continue
+            try:
+                sm.append(float(r[1]))
+                mx.append(float(r[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def algorithmic_bytes_per_token(cfg, ctx_mean: float) -> float:
+    """Q4_0 layer weights + LM head + KV cache rows read, per decode token (activations < 0.1 %, left out)."""
+    return cfg.q4_bytes_per_layer() * cfg.layers + cfg.head_bytes() + cfg.kv_bytes_per_position() * ctx_mean
+
+
+# ------------------------------------------------------------------------------------------------------ CPU baseline
+def cpu_baseline(model, cfg, budget_s: float = 20.0):
+    """Reference numpy path on the host cores, bounded: a few layers + the LM head of one decode token at context 512,
+    scaled to the full layer count."""
+    ora = importlib.import_module("oracle.q4ref")
+    synth = importlib.import_module("3080lab_b200.synth")
+    cos, sin = synth.rope_tables(cfg, MAX_LEN)
+    n_layers = min(cfg.layers, 4)
+    dec = ora.CpuDecoder(model, MAX_LEN, cos, sin, layers=range(n_layers))
+    rng = np.random.default_rng(0)
+    dec.kc[:n_layers, :, :PROMPT] = rng.standard_normal((n_layers, cfg.n_kv_heads, PROMPT, cfg.head_dim)).astype(np.float16)
+    dec.vc[:n_layers, :, :PROMPT] = rng.standard_normal((n_layers, cfg.n_kv_heads, PROMPT, cfg.head_dim)).astype(np.float16)
+    h = model["embed"][17].astype(np.float32)
+    h = dec.layer(0, h, PROMPT)                                     # warm-up (BLAS threads, page faults)
+    t_layers, t0 = [], time.perf_counter()
+    while True:
+        for i in range(n_layers):
+            t = time.perf_counter()
+            h = dec.layer(i, h, PROMPT)
+            t_layers.append(time.perf_counter() - t)
+        if time.perf_counter() - t0 > budget_s * 0.6 or len(t_layers) >= 3 * n_layers:
+            break
+    t = time.perf_counter()
+    dec.head(h)
+    t_head = time.perf_counter() - t
+    t_tok = statistics.mean(t_layers) * cfg.layers + t_head
+    return {"value": 1.0 / t_tok, "unit": "tok/s", "cores": os.cpu_count(), "kind": "port",
+            "sample": f"1 decode token at context {PROMPT}: {len(t_layers)} layer passes over {n_layers} of {cfg.layers} "
+                      f"layers ({statistics.mean(t_layers):.3f} s each) + the full LM head ({t_head:.2f} s), layers scaled "
+                      f"to {cfg.layers}; numpy fp32 dequantise-and-dot per linear, nothing cached",
+            "s_per_token": t_tok}
+
+
+def run_reference(args, rank: int) -> None:
+    if rank != 0:
+        return
+    synth = importlib.import_module("3080lab_b200.synth")
+    ora = importlib.import_module("oracle.q4ref")
+    cfg = synth.QWEN25_1P5B
+    model = synth.synth_model(cfg, 0)
+    cos, sin = synth.rope_tables(cfg, MAX_LEN)
+    # each step = `per` layers of one decode token; sized so K + W steps fit in ~2.5 minutes
+    n_have = 4
+    dec = ora.CpuDecoder(model, MAX_LEN, cos, sin, layers=range(n_have))
+    rng = np.random.default_rng(0)
+    dec.kc[:n_have, :, :PROMPT] = rng.standard_normal((n_have, cfg.n_kv_heads, PROMPT, cfg.head_dim)).astype(np.float16)
+    dec.vc[:n_have, :, :PROMPT] = rng.standard_normal((n_have, cfg.n_kv_heads, PROMPT, cfg.head_dim)).astype(np.float16)
+    h = model["embed"][17].astype(np.float32)
+    t = time.perf_counter()
+    h = dec.layer(0, h, PROMPT)
+    t_est = time.perf_counter() - t
+    t = time.perf_counter()
+    dec.head(h)
+    t_head = time.perf_counter() - t
+    total = max(1, args.steps + args.warmup)
+    per = int(max(1, min(n_have, (150.0 / total) / max(t_est, 1e-3))))
+    for w in range(args.warmup):
+        for i in range(per):
+            h = dec.layer(i, h, PROMPT)
+    t0 = time.perf_counter()
+    for s in range(args.steps):
+        for i in range(per):
+            h = dec.layer(i, h, PROMPT)
+    dt = time.perf_counter() - t0
+    t_layer = dt / (args.steps * per)
+    t_tok = t_layer * cfg.layers + t_head
+    val = 1.0 / t_tok
+    sample = (f"each step = {per} of {cfg.layers} layers of one decode token at context {PROMPT} (numpy fp32 dequantise-"
+              f"and-dot per linear, {t_layer:.3f} s per layer); LM head timed once ({t_head:.2f} s); "
+              f"tok/s = 1 / ({cfg.layers} x layer + head)")
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": val, "unit": "tok/s", "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": 1e3 * dt / max(1, args.steps), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "qwen2.5-1.5b-shape Q4_0 decode, batch 1, 512-token context, CPU numpy path"},
+        "cpu_baseline": {"value": val, "unit": "tok/s", "cores": os.cpu_count(), "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }), flush=True)
+
+
+# ----------------------------------------------------------------------------------------------------------- GPU arm
+def time_kernel(fn, n: int, torch):
+    """Average device time of n back-to-back launches on the current stream, in microseconds."""
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    s.record()
+    for _ in range(n):
+        fn()
+    e.record()
+    torch.cuda.synchronize()
+    return 1e3 * s.elapsed_time(e) / n
+
+
+def run_ours(args, rank: int, world: int, local_rank: int) -> None:
+    import torch
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the product has no CPU path (use --impl reference for the CPU arm)")
+    torch.cuda.set_device(local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local_rank}"))
+    synth = importlib.import_module("3080lab_b200.synth")
+    engine = importlib.import_module("3080lab_b200.engine")
+    K = importlib.import_module("3080lab_b200.qwen_kernels")
+    cfg = synth.QWEN25_1P5B
+    model = synth.synth_model(cfg, 0)                       # same weights on every rank, a different prompt per rank
+    m = engine.FusedQwen(model, max_len=MAX_LEN, device=f"cuda:{local_rank}")
+    prompt = synth.synth_prompt(cfg, PROMPT, seed=rank)
+    if args.steps + args.warmup + PROMPT > MAX_LEN:
+        raise SystemExit(f"steps + warmup must stay below {MAX_LEN - PROMPT}")
+    m.reset()
+    m.feed(prompt)
+    g = m.capture()
+    pos0, tok0 = m.pos.clone(), m.tok.clone()
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-resident timing: W warm-up replays, then K timed replays between CUDA events
+    for _ in range(max(args.warmup, 3)):
+        g.replay()
+    m.pos.copy_(pos0 + args.warmup)
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    barrier()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    for _ in range(args.steps):
+        g.replay()
+    e.record()
+    barrier()
+    ms = s.elapsed_time(e)
+    clocks = sampler.stop() if rank == 0 else None
+    t = torch.tensor([ms], device="cuda")
+    if dist is not None:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_max = float(t.item())
+
+    # ---- end to end through the public API: token id in from pinned host memory, generated token back, every step
+    m.pos.copy_(pos0)
+    m.tok.copy_(tok0)
+    host_in = torch.zeros(1, dtype=torch.long).pin_memory()
+    host_out = torch.zeros(1, dtype=torch.long).pin_memory()
+    host_in[0] = int(tok0.item())
+    for _ in range(3):
+        m.tok.copy_(host_in, non_blocking=True)
+        g.replay()
+        host_out.copy_(m.tok, non_blocking=True)
+        torch.cuda.synchronize()
+    m.pos.copy_(pos0)
+    host_in[0] = int(tok0.item())
+    barrier()
+    s2, e2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s2.record()
+    for _ in range(args.steps):
+        m.tok.copy_(host_in, non_blocking=True)          # H2D: this step's input token
+        g.replay()
+        host_out.copy_(m.tok, non_blocking=True)         # D2H: this step's result
+        torch.cuda.current_stream().synchronize()
+        host_in[0] = host_out[0]                         # the host feeds the token it just read back
+    e2.record()
+    barrier()
+    t2 = torch.tensor([s2.elapsed_time(e2)], device="cuda")
+    if dist is not None:
+        dist.all_reduce(t2, op=dist.ReduceOp.MAX)
+    e2e_ms = float(t2.item())
+
+    if rank != 0:
+        if dist is not None:
+            dist.destroy_process_group()
+        return
+
+    # ---- roofline of the dominant kernels, timed alone on this stream (rank 0)
+    peaks, peak_kind = measured_peaks()
+    c = cfg
+    rep = 5
+    def gu_all():
+        for L in m.L:
+            K.gemv(L["gu"][0], L["gu"][1], m.x, m.xm, None, 2 * c.ffn, c.hidden, "swiglu")
+    def down_all():
+        for L in m.L:
+            K.gemv(L["down"][0], L["down"][1], m.xm, m.h, None, c.hidden, c.ffn, "resid")
+    def head_once():
+        K.head_argmax(m.embed, m.x, m.logits, None, None, m.head_ws)
+    for f in (gu_all, down_all, head_once):
+        f()
+    us_gu = time_kernel(gu_all, rep, torch) / c.layers
+    us_down = time_kernel(down_all, rep, torch) / c.layers
+    us_head = time_kernel(head_once, rep, torch)
+    b_gu = 2 * c.ffn * c.hidden // 32 * 18 + c.hidden * 2 + c.ffn * 2
+    b_down = c.hidden * c.ffn // 32 * 18 + c.ffn * 2 + c.hidden * 8
+    b_head = c.head_bytes() + c.hidden * 2 + c.vocab * 4
+    kern = {
+        "gemv_q4_0 gate_up 17920x1536 (+swiglu)": (b_gu, us_gu, c.layers),
+        "gemv_q4_0 down 1536x8960 (+resid)": (b_down, us_down, c.layers),
+        "head_f16_argmax 151936x1536": (b_head, us_head, 1),
+    }
+    dominant = max(kern, key=lambda k: kern[k][1] * kern[k][2])
+    b, us, _ = kern[dominant]
+    ach = b / us / 1e3
+    roofline = {"bound": "hbm", "kernel": dominant, "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                "frac": ach / peaks["hbm_gbs"], "peak_kind": f"of {peak_kind}", "traffic": None,
+                "bytes_per_launch": b, "us_per_launch": us,
+                "others": {k: {"achieved": v[0] / v[1] / 1e3, "frac": v[0] / v[1] / 1e3 / peaks["hbm_gbs"],
+                               "us_per_launch": v[1], "launches_per_step": v[2]} for k, v in kern.items() if k != dominant}}
+
+    ctx_mean = PROMPT + args.warmup + (args.steps - 1) / 2.0
+    step_bytes = algorithmic_bytes_per_token(cfg, ctx_mean)
+    ms_step = ms_max / args.steps
+    value = world * args.steps / (ms_max / 1e3)
+    out = {
+        "metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic",
+        "config": {"workload": "qwen2.5-1.5b-shape Q4_0 decode, batch 1 per GPU, 512-token prompt then greedy decode",
+                   "weights": "random-init Q4_0 from seed 0, tied fp16 LM head, fp16 KV cache", "context": f"{PROMPT}..{PROMPT + args.warmup + args.steps}",
+                   "l2": "inputs larger than L2: 1.2 GB of weights streamed per step, no flush needed",
+                   "parallelism": f"dp{world} (independent sequences, no collective)"},
+        "step_hbm": {"algorithmic_bytes": step_bytes, "achieved_gbs": step_bytes / (ms_step * 1e-3) / 1e9,
+                     "frac_of_measured_copy_peak": step_bytes / (ms_step * 1e-3) / 1e9 / peaks["hbm_gbs"],
+                     "frac_of_nominal_8tbs": step_bytes / (ms_step * 1e-3) / 1e9 / NOMINAL_HBM_GBS},
+        "roofline": roofline,
+        "e2e": {"value": world * args.steps / (e2e_ms / 1e3), "unit": "tok/s", "h2d_bytes_per_step": 8, "d2h_bytes_per_step": 8},
+        "gpu_launches": m.launches_per_step * args.steps,
+        "clocks": clocks,
+    }
+    if world == 1 and not args.no_cpu:
+        out["cpu_baseline"] = cpu_baseline(model, cfg)
+    print(json.dumps(out), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=256)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+    if world != args.gpus and world == 1 and args.gpus > 1:
+        raise SystemExit("bench.py --gpus N > 1 must be launched with torch.distributed.run --nproc-per-node N")
+    run_ours(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,150 @@
+/* libq4b200 — C-ABI of the B200 (sm_100a) Qwen2.5 Q4_0 inference hot path.
+ *
+ * The reference launches every kernel through `Kern(src).launch(grid, block, args)` (scripts/qwen_fused.py:30-42;
+ * 2-D grid + dynamic shared memory variant scripts/qwen_batched_decode.py:51-67): raw device pointers as 64-bit
+ * integers, int32/float scalars, the launch on torch's current stream, buffers owned by the caller, no allocation
+ * and no synchronisation inside.  Each function below replaces one such launch site (the kernel source it stands in
+ * for is cited per function); grid/block/shared-memory choices move inside the library.
+ *
+ * Conventions
+ *   - every pointer is a DEVICE pointer unless the comment says "host";
+ *   - `stream` is a cudaStream_t passed as void* (0 = legacy default stream); launches are capturable in CUDA graphs;
+ *   - return value: Q4B_OK or a negative Q4B_E_* code; shapes, alignment and workspace sizes are validated on the
+ *     host before anything is launched; q4b_last_error() returns a text for the last failure on the calling thread;
+ *   - nothing here allocates or frees device memory, and nothing synchronises;
+ *   - workspaces and counters are caller-allocated, must be zero-filled once before first use, and are left zeroed
+ *     again by each kernel that uses them (self-resetting, as the reference's `cnt` / `fin_cnt` words,
+ *     lab/qwen_batched.py:659-661, lab/qwen_kernels.py:280).
+ *
+ * Layouts
+ *   Q4_0 canonical: W int32 [N, K/8], nibble i of word w = weight 8w+i, value (nibble-8)*d; S fp16 [N, K/32]
+ *   (scripts/qwen_gguf.py:44-60).  K must be a multiple of 32; W and S 16-byte aligned.
+ *   Activations fp16, residual stream and logits fp32, KV cache fp16 [B, NKV, max_len, HD] per layer,
+ *   RoPE tables fp32 [max_len, HD/2], token ids and positions int64 on the device.
+ */
+#ifndef Q4B200_H
+#define Q4B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define Q4B_OK 0
+#define Q4B_E_SHAPE (-1)      /* a dimension is zero, negative, or not a multiple the kernel needs */
+#define Q4B_E_ALIGN (-2)      /* a pointer is null or not 16-byte aligned */
+#define Q4B_E_WORKSPACE (-3)  /* workspace_bytes is smaller than the matching *_workspace() query */
+#define Q4B_E_CUDA (-4)       /* the CUDA runtime reported an error; text in q4b_last_error() */
+#define Q4B_E_ARG (-5)        /* unknown epilogue / dtype / mode id */
+#define Q4B_E_TIMEOUT (-6)    /* a bounded device-side wait gave up (reported through a status word) */
+
+/* GEMV / MMQ epilogues, named as the reference's (lab/qwen_kernels.py:21-45). */
+#define Q4B_EPI_STORE 0   /* Y fp16 [N]        = acc */
+#define Q4B_EPI_BIASF 1   /* Y fp16 [N]        = acc + AUX fp32 [N] */
+#define Q4B_EPI_RESID 2   /* Y fp32 [N]       += acc */
+#define Q4B_EPI_SWIGLU 3  /* Y fp16 [N/2]      = silu(acc[2o]) * acc[2o+1]  (rows interleaved gate, up) */
+#define Q4B_EPI_LOGITS 4  /* Y fp32 [N]        = acc */
+
+#define Q4B_X_F16 0
+#define Q4B_X_F32 1
+
+typedef void* q4b_stream_t;
+
+/* Library version (major * 1000 + minor). */
+int q4b_version(void);
+/* Text of the last error on the calling thread ("" if none).  Host pointer, valid until the next call. */
+const char* q4b_last_error(void);
+/* One-time per-device set-up (function attributes, SM count).  Replaces the module load + cuFuncSetAttribute of
+ * Kern.__init__ (scripts/qwen_batched_decode.py:51-58).  Idempotent. */
+int q4b_init(int device);
+
+/* Q4_0 GEMV, one activation vector.  Replaces the launch of `gemv_source(S, epi, "g32f16", G)`
+ * (lab/qwen_kernels.py:14-113; host call FusedQwen.gemv scripts/qwen_fused.py:104-107).
+ * X: fp16 [K] (Q4B_X_F16) or fp32 [K] (Q4B_X_F32).  Y/AUX per epilogue (see Q4B_EPI_*). */
+int q4b_gemv_q4_0(const void* W, const void* S, const void* X, void* Y, const void* AUX, int N, int K, int epilogue,
+                  int x_dtype, q4b_stream_t stream);
+
+/* RMSNorm over `rows` rows: out fp16 [rows, H] = h fp32 [rows, H] * rsqrt(mean(h^2) + eps) * w fp32 [H].
+ * Replaces RMSNORM_F32W_1P (lab/qwen_kernels.py:683-705; host call FusedQwen.rms scripts/qwen_fused.py:109-111). */
+int q4b_rmsnorm(const float* h, const float* w, void* out, int rows, int H, float eps, q4b_stream_t stream);
+
+/* Embedding lookup: h fp32 [rows, H] = float(E fp16 [V, H][tok[row]]).  Replaces EMBED_F32
+ * (lab/qwen_kernels.py:284-290).  Token ids outside [0, V) are clamped into range. */
+int q4b_embed(const void* E, const int64_t* tok, float* h, int rows, int H, int V, q4b_stream_t stream);
+
+/* Decode attention for B sequences, one new token each: RoPE(q), RoPE(k_new), K/V append at pos[b], GQA attention
+ * over positions 0..pos[b], split over the context in fixed-size chunks with a deterministic combine.
+ * Replaces ATTN4 (lab/qwen_kernels.py:517-605) and the flash-decoding ATTN2 (:358-442).
+ * qkv fp16 [B, (NH + 2 NKV) HD]; cosT/sinT fp32 [max_len, HD/2]; pos int64 [B]; kc/vc fp16 [B, NKV, max_len, HD];
+ * out fp16 [B, NH HD].  HD must be 64 or 128, NH a multiple of NKV with NH/NKV <= 8, pos[b] < max_len.
+ * workspace: q4b_attn_decode_workspace(B, NH, HD, max_len) bytes, zero-filled once. */
+size_t q4b_attn_decode_workspace(int B, int NH, int HD, int max_len);
+int q4b_attn_decode(const void* qkv, const float* cosT, const float* sinT, const int64_t* pos, void* kc, void* vc,
+                    void* out, int B, int NH, int NKV, int HD, int max_len, float scale, void* workspace,
+                    size_t workspace_bytes, q4b_stream_t stream);
+
+/* LM head for a tied fp16 embedding table with the greedy pick fused: logits fp32 [V] = E fp16 [V, H] . x fp16 [H];
+ * tok[0] = lowest index among the maxima; pos[0] += 1.  Replaces gemv_source(..., "logits") + FINISH_MB
+ * (lab/qwen_kernels.py:14-113, 250-282; host scripts/qwen_fused.py:133-142).  tok/pos may be null (logits only).
+ * workspace: q4b_head_workspace(V) bytes, zero-filled once. */
+size_t q4b_head_workspace(int V);
+int q4b_head_f16_argmax(const void* E, const void* x, float* logits, int V, int H, int64_t* tok, int64_t* pos,
+                        void* workspace, size_t workspace_bytes, q4b_stream_t stream);
+
+/* Greedy pick over fp32 logits [rows, V]: tok[r] = lowest index among the maxima of row r; pos[r] += 1.
+ * Replaces FINISH / FINISH_MB (lab/qwen_kernels.py:222-282) and the torch.argmax of the batched engine
+ * (scripts/qwen_batched_decode.py:186-187).  workspace: q4b_argmax_workspace(rows, V) bytes, zero-filled once. */
+size_t q4b_argmax_workspace(int rows, int V);
+int q4b_argmax_advance(const float* logits, int rows, int V, int64_t* tok, int64_t* pos, void* workspace,
+                       size_t workspace_bytes, q4b_stream_t stream);
+
+/* ---- whole decode step, batch 1 -------------------------------------------------------------------------------
+ * One greedy decode token through every layer, launched back to back on `stream` (capturable as one CUDA graph).
+ * Replaces the launch sequence of FusedQwen.step (scripts/qwen_fused.py:113-145): embed, then per layer
+ * rmsnorm -> qkv GEMV(+bias) -> attention -> o GEMV(+residual) -> rmsnorm -> gate/up GEMV(+SwiGLU) -> down
+ * GEMV(+residual), then final rmsnorm -> LM head -> argmax, pos += 1.  The descriptor is a HOST struct of device
+ * pointers; the caller owns every buffer.  `layer` points to a host array of `layers` entries. */
+typedef struct {
+  const void* W;   /* int32 [N, K/8] */
+  const void* S;   /* fp16  [N, K/32] */
+  int N, K;
+} q4b_linear;
+
+typedef struct {
+  const float* ln1;       /* fp32 [hidden] */
+  const float* ln2;
+  const float* qkv_bias;  /* fp32 [qkv rows] */
+  q4b_linear qkv, o, gu, down;
+  void* kc;               /* fp16 [batch, n_kv_heads, max_len, head_dim] */
+  void* vc;
+} q4b_layer;
+
+typedef struct {
+  int layers, hidden, ffn, n_heads, n_kv_heads, head_dim, vocab, max_len;
+  float eps, scale;
+  const void* embed;      /* fp16 [vocab, hidden]; also the LM head when head.W is null */
+  const q4b_layer* layer; /* host array */
+  const float* norm;      /* fp32 [hidden] */
+  q4b_linear head;        /* Q4_0 head, or W = S = null for the tied fp16 head */
+  const float* cosT;      /* fp32 [max_len, head_dim/2] */
+  const float* sinT;
+  int64_t* tok;           /* [1] in: token to feed, out: greedy pick */
+  int64_t* pos;           /* [1] in: its position, out: +1 */
+  float* h;               /* fp32 [hidden] residual stream */
+  void* x;                /* fp16 [hidden] */
+  void* qkv;              /* fp16 [qkv rows] */
+  void* att;              /* fp16 [n_heads * head_dim] */
+  void* act;              /* fp16 [ffn] */
+  float* logits;          /* fp32 [vocab] */
+  void* attn_ws;  size_t attn_ws_bytes;   /* q4b_attn_decode_workspace(1, ...) */
+  void* head_ws;  size_t head_ws_bytes;   /* max(q4b_head_workspace, q4b_argmax_workspace(1, vocab)) */
+} q4b_decode_desc;
+
+int q4b_decode_step(const q4b_decode_desc* desc, q4b_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* Q4B200_H */

@@ -335,48 +335,84 @@ class Oracle:
 
 
 # --------------------------------------------------------------------------------------------- timed CPU baseline
-def cpu_decode_step_numpy(model, state, tok):
-    """The reference's numpy CPU path applied to one decode token: every linear is `gemv_numpy_f32` (dequantise from
-    the nibbles, then fp32 matvec; nothing cached), other ops in fp32 numpy.  `state` = dict(kc, vc, pos, cos, sin).
-    Used only for timing the CPU baseline; its arithmetic is the fp32 statement of `Oracle.step`."""
-    c = model["cfg"]
-    p = state["pos"]
-    h = model["embed"][tok].astype(F32)
-    half = c.head_dim // 2
-    cs, sn = state["cos"][p], state["sin"][p]
+def canonical_to_gguf_bytes(W, S):
+    """Canonical device layout -> raw ggml Q4_0 records (inverse of q4_rows + pack, scripts/qwen_gguf.py:44-60), so the
+    CPU baseline can start from the bytes the reference's numpy path starts from."""
+    q = unpack_words(W).astype(np.uint8).reshape(-1, 32)
+    rec = np.empty((q.shape[0], 18), np.uint8)
+    rec[:, :2] = np.ascontiguousarray(S).reshape(-1).view(np.uint8).reshape(-1, 2)
+    rec[:, 2:] = q[:, :16] | (q[:, 16:] << 4)
+    return rec.reshape(-1)
 
-    def rms(v, w):
-        return (v * (1.0 / np.sqrt(np.mean(v * v) + np.float32(c.eps))) * w).astype(F16).astype(F32)
 
-    def rot(x):
-        a, b = x[:, :half], x[:, half:]
-        return np.concatenate([a * cs - b * sn, b * cs + a * sn], axis=1).astype(F16)
+def gemv_numpy_bytes(raw, n, k, x):
+    """The reference's numpy CPU path for one linear, from raw GGUF bytes: q4_0_blocks, then the GGUF.f32 statement
+    d[:, None] * (q.astype(float32) - 8) reshaped [n, k] (lab/gguf.py:77-79, 88-94), then the fp32 matvec."""
+    d, q = q4_0_blocks(raw)
+    w = (d[:, None] * (q.astype(F32) - 8)).reshape(n, k)
+    return w @ np.asarray(x, F32)
 
-    for i, L in enumerate(model["layers"]):
-        x = rms(h, L["ln1"])
-        qkv = (gemv_numpy_f32(*L["qkv"], x) + L["qkv_b"]).astype(F16).astype(F32)
+
+class CpuDecoder:
+    """fp32 numpy decode of one sequence with every linear going through `gemv_numpy_bytes` (nothing dequantised ahead
+    of time).  Only the CPU-baseline timing uses it; `layer()` and `head()` can be timed separately so that a bounded
+    sample (a few layers) can be scaled to a whole token."""
+
+    def __init__(self, model, max_len, cos, sin, layers=None):
+        self.m, self.c = model, model["cfg"]
+        c = self.c
+        self.cos, self.sin = np.asarray(cos, F32), np.asarray(sin, F32)
+        self.kc = np.zeros((c.layers, c.n_kv_heads, max_len, c.head_dim), F16)
+        self.vc = np.zeros_like(self.kc)
+        self.raw = {}
+        for i in (range(c.layers) if layers is None else layers):
+            L = model["layers"][i]
+            self.raw[i] = {k: canonical_to_gguf_bytes(*L[k]) for k in ("qkv", "o", "gu", "down")}
+        self.head_raw = None if c.tied_fp16_head else canonical_to_gguf_bytes(*model["head"])
+
+    def _rms(self, v, w):
+        return (v * (1.0 / np.sqrt(np.mean(v * v) + np.float32(self.c.eps))) * w).astype(F16).astype(F32)
+
+    def layer(self, i, h, p):
+        c, L, raw = self.c, self.m["layers"][i], self.raw[i]
+        half = c.head_dim // 2
+        cs, sn = self.cos[p], self.sin[p]
+
+        def rot(x):
+            a, b = x[:, :half], x[:, half:]
+            return np.concatenate([a * cs - b * sn, b * cs + a * sn], axis=1).astype(F16)
+
+        x = self._rms(h, L["ln1"])
+        qkv = (gemv_numpy_bytes(raw["qkv"], c.qkv_rows, c.hidden, x) + L["qkv_b"]).astype(F16).astype(F32)
         q = rot(qkv[:c.q_rows].reshape(c.n_heads, c.head_dim)).astype(F32)
-        state["kc"][i, :, p] = rot(qkv[c.q_rows:c.q_rows + c.kv_rows].reshape(c.n_kv_heads, c.head_dim))
-        state["vc"][i, :, p] = qkv[c.q_rows + c.kv_rows:].reshape(c.n_kv_heads, c.head_dim).astype(F16)
+        self.kc[i, :, p] = rot(qkv[c.q_rows:c.q_rows + c.kv_rows].reshape(c.n_kv_heads, c.head_dim))
+        self.vc[i, :, p] = qkv[c.q_rows + c.kv_rows:].reshape(c.n_kv_heads, c.head_dim).astype(F16)
         att = np.empty((c.n_heads, c.head_dim), F32)
         grp = c.n_heads // c.n_kv_heads
         for hh in range(c.n_heads):
-            k = state["kc"][i, hh // grp, :p + 1].astype(F32)
-            v = state["vc"][i, hh // grp, :p + 1].astype(F32)
+            k = self.kc[i, hh // grp, :p + 1].astype(F32)
+            v = self.vc[i, hh // grp, :p + 1].astype(F32)
             s = (k @ q[hh]) * np.float32(1.0 / np.sqrt(c.head_dim))
             e = np.exp(s - s.max())
             att[hh] = (e @ v) / e.sum()
         att = att.reshape(-1).astype(F16).astype(F32)
-        h = h + gemv_numpy_f32(*L["o"], att)
-        x = rms(h, L["ln2"])
-        gu = gemv_numpy_f32(*L["gu"], x)
+        h = h + gemv_numpy_bytes(raw["o"], c.hidden, c.q_rows, att)
+        x = self._rms(h, L["ln2"])
+        gu = gemv_numpy_bytes(raw["gu"], 2 * c.ffn, c.hidden, x)
         g, u = gu[0::2], gu[1::2]
         act = (g / (1.0 + np.exp(-g)) * u).astype(F16).astype(F32)
-        h = h + gemv_numpy_f32(*L["down"], act)
-    x = rms(h, model["norm"])
-    if c.tied_fp16_head:
-        logits = model["embed"].astype(F32) @ x
-    else:
-        logits = gemv_numpy_f32(*model["head"], x)
-    state["pos"] = p + 1
-    return int(np.argmax(logits))
+        return h + gemv_numpy_bytes(raw["down"], c.hidden, c.ffn, act)
+
+    def head(self, h):
+        x = self._rms(h, self.m["norm"])
+        if self.c.tied_fp16_head:
+            logits = self.m["embed"].astype(F32) @ x
+        else:
+            logits = gemv_numpy_bytes(self.head_raw, self.c.vocab, self.c.hidden, x)
+        return int(np.argmax(logits)), logits
+
+    def step(self, tok, p):
+        h = self.m["embed"][tok].astype(F32)
+        for i in range(self.c.layers):
+            h = self.layer(i, h, p)
+        return self.head(h)
