@@ -41,6 +41,7 @@ int attn_decode(const void*, const float*, const float*, const int64_t*, void*, 
                 void*, size_t, cudaStream_t);
 size_t head_workspace(int);
 int head_f16_argmax(const void*, const void*, float*, int, int, int64_t*, int64_t*, void*, size_t, cudaStream_t);
+int blockdot(const void*, const void*, int32_t*, int, int, int, int, uint32_t*, cudaStream_t);
 
 }  // namespace q4b
 
@@ -104,6 +105,11 @@ size_t q4b_argmax_workspace(int rows, int V) { return argmax_workspace(rows, V);
 int q4b_argmax_advance(const float* logits, int rows, int V, int64_t* tok, int64_t* pos, void* workspace,
                        size_t workspace_bytes, q4b_stream_t stream) {
   return argmax_advance(logits, rows, V, tok, pos, workspace, workspace_bytes, S(stream));
+}
+
+int q4b_blockdot_q4_0_q8_1(const void* W, const void* xq, int32_t* out, int M, int K, int P, int mode, uint32_t* status,
+                           q4b_stream_t stream) {
+  return blockdot(W, xq, out, M, K, P, mode, status, S(stream));
 }
 
 int q4b_decode_step(const q4b_decode_desc* d, q4b_stream_t stream) {

@@ -201,9 +201,9 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
     cfg = synth.QWEN25_1P5B
     model = synth.synth_model(cfg, 0)                       # same weights on every rank, a different prompt per rank
     m = engine.FusedQwen(model, max_len=MAX_LEN, device=f"cuda:{local_rank}")
-    prompt = synth.synth_prompt(cfg, PROMPT, seed=rank)
-    if args.steps + args.warmup + PROMPT > MAX_LEN:
-        raise SystemExit(f"steps + warmup must stay below {MAX_LEN - PROMPT}")
+    prompt = synth.synth_prompt(cfg, args.prompt, seed=rank)
+    if args.steps + max(args.warmup, 3) + args.prompt > MAX_LEN:
+        raise SystemExit(f"prompt + steps + warmup must stay below {MAX_LEN}")
     m.reset()
     m.feed(prompt)
     g = m.capture()
@@ -234,6 +234,12 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
     if dist is not None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms_max = float(t.item())
+    if args.profile:
+        if rank == 0:
+            print(json.dumps({"profile_run": True, "ms_per_step": ms_max / args.steps, "steps": args.steps}), flush=True)
+        if dist is not None:
+            dist.destroy_process_group()
+        return
 
     # ---- end to end through the public API: token id in from pinned host memory, generated token back, every step
     m.pos.copy_(pos0)
@@ -303,7 +309,7 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
                 "others": {k: {"achieved": v[0] / v[1] / 1e3, "frac": v[0] / v[1] / 1e3 / peaks["hbm_gbs"],
                                "us_per_launch": v[1], "launches_per_step": v[2]} for k, v in kern.items() if k != dominant}}
 
-    ctx_mean = PROMPT + args.warmup + (args.steps - 1) / 2.0
+    ctx_mean = args.prompt + args.warmup + (args.steps - 1) / 2.0
     step_bytes = algorithmic_bytes_per_token(cfg, ctx_mean)
     ms_step = ms_max / args.steps
     value = world * args.steps / (ms_max / 1e3)
@@ -312,7 +318,7 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
         "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic",
         "config": {"workload": "qwen2.5-1.5b-shape Q4_0 decode, batch 1 per GPU, 512-token prompt then greedy decode",
-                   "weights": "random-init Q4_0 from seed 0, tied fp16 LM head, fp16 KV cache", "context": f"{PROMPT}..{PROMPT + args.warmup + args.steps}",
+                   "weights": "random-init Q4_0 from seed 0, tied fp16 LM head, fp16 KV cache", "context": f"{args.prompt}..{args.prompt + args.warmup + args.steps}",
                    "l2": "inputs larger than L2: 1.2 GB of weights streamed per step, no flush needed",
                    "parallelism": f"dp{world} (independent sequences, no collective)"},
         "step_hbm": {"algorithmic_bytes": step_bytes, "achieved_gbs": step_bytes / (ms_step * 1e-3) / 1e9,
@@ -337,6 +343,9 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
+    ap.add_argument("--prompt", type=int, default=PROMPT, help="prompt length (512 = the benchmark configuration)")
+    ap.add_argument("--profile", action="store_true",
+                    help="short run for a profiler: only the warm-up and timed graph replays, no e2e / roofline / CPU legs")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

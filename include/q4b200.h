@@ -100,6 +100,16 @@ size_t q4b_argmax_workspace(int rows, int V);
 int q4b_argmax_advance(const float* logits, int rows, int V, int64_t* tok, int64_t* pos, void* workspace,
                        size_t workspace_bytes, q4b_stream_t stream);
 
+/* ---- tensor-core block dots (verification entry) ----------------------------------------------------------------
+ * out int32 [P, M, K/32]: out[n, m, b] = sum_{i<32} (q4[m, 32b+i] - 8) * xq[n, 32b+i], exact, computed with
+ * tcgen05.mma.kind::i8.  The reference obtains the same integers from mma.m16n8k32.u8.s8 with the -8*sum(q8)
+ * correction in the C operand (lab/qwen_batched.py:1237-1243); its tensor-core known-answer check demands exact
+ * equality (lab/experiments/tensor.py:122-200).  W canonical Q4_0 words [M, K/8]; xq int8 [P, K].
+ * mode bit 0: 0 = A operand staged in shared memory, 1 = A operand written to tensor memory; mode >> 1: tile width
+ * (8, 16, 32; 0 = pick from P).  status: one uint32 the kernel sets to 1 if a bounded wait expired (zero it first). */
+int q4b_blockdot_q4_0_q8_1(const void* W, const void* xq, int32_t* out, int M, int K, int P, int mode,
+                           uint32_t* status, q4b_stream_t stream);
+
 /* ---- whole decode step, batch 1 -------------------------------------------------------------------------------
  * One greedy decode token through every layer, launched back to back on `stream` (capturable as one CUDA graph).
  * Replaces the launch sequence of FusedQwen.step (scripts/qwen_fused.py:113-145): embed, then per layer
