@@ -49,6 +49,10 @@ SIGNATURES = {
     "q4b_argmax_workspace": (_Z, [_I, _I]),
     "q4b_argmax_advance": (_I, [_P, _I, _I, _P, _P, _P, _Z, _P]),
     "q4b_blockdot_q4_0_q8_1": (_I, [_P, _P, _P, _I, _I, _I, _I, _P, _P]),
+    "q4b_gemv_q4_0_tc": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _P, _P]),
+    "q4b_mmq_q4_0_q8_1": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P]),
+    "q4b_quant_q8_1": (_I, [_P, _P, _P, _P, _I, _I, _P]),
+    "q4b_rmsnorm_q8_1": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _F, _P]),
     "q4b_decode_step": (_I, [C.POINTER(DecodeDesc), _P]),
 }
 

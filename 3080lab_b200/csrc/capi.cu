@@ -42,6 +42,10 @@ int attn_decode(const void*, const float*, const float*, const int64_t*, void*, 
 size_t head_workspace(int);
 int head_f16_argmax(const void*, const void*, float*, int, int, int64_t*, int64_t*, void*, size_t, cudaStream_t);
 int blockdot(const void*, const void*, int32_t*, int, int, int, int, uint32_t*, cudaStream_t);
+int mmq_stream(const void*, const void*, const void*, const void*, void*, const void*, int, int, int, int, int, int, uint32_t*,
+               cudaStream_t);
+int quant_q8_1(const void*, void*, void*, void*, int, int, cudaStream_t);
+int rmsnorm_q8_1(const float*, const float*, void*, void*, void*, void*, int, int, float, cudaStream_t);
 
 }  // namespace q4b
 
@@ -110,6 +114,28 @@ int q4b_argmax_advance(const float* logits, int rows, int V, int64_t* tok, int64
 int q4b_blockdot_q4_0_q8_1(const void* W, const void* xq, int32_t* out, int M, int K, int P, int mode, uint32_t* status,
                            q4b_stream_t stream) {
   return blockdot(W, xq, out, M, K, P, mode, status, S(stream));
+}
+
+int q4b_gemv_q4_0_tc(const void* W, const void* Sc, const void* X, void* Y, const void* AUX, int N, int K, int epilogue,
+                     int x_dtype, uint32_t* status, q4b_stream_t stream) {
+  if (x_dtype != Q4B_X_F16 && x_dtype != Q4B_X_F32) return fail(Q4B_E_ARG, "gemv_q4_0_tc: unknown x_dtype");
+  const int ldy = epilogue == Q4B_EPI_SWIGLU ? N / 2 : N;
+  return mmq_stream(W, Sc, X, nullptr, Y, AUX, N, K, 1, x_dtype == Q4B_X_F16 ? 0 : 1, epilogue, ldy, status, S(stream));
+}
+
+int q4b_mmq_q4_0_q8_1(const void* W, const void* Sc, const void* xq, const void* xd, void* Y, const void* AUX, int N, int K,
+                      int P, int epilogue, int ldy, uint32_t* status, q4b_stream_t stream) {
+  if (P < 1 || P > 32) return fail(Q4B_E_SHAPE, "mmq_q4_0_q8_1: 1..32 activation rows supported by the streaming kernel");
+  return mmq_stream(W, Sc, xq, xd, Y, AUX, N, K, P, 2, epilogue, ldy, status, S(stream));
+}
+
+int q4b_quant_q8_1(const void* x, void* xq, void* xd, void* xsum, int rows, int K, q4b_stream_t stream) {
+  return quant_q8_1(x, xq, xd, xsum, rows, K, S(stream));
+}
+
+int q4b_rmsnorm_q8_1(const float* h, const float* w, void* xq, void* xd, void* xsum, void* x16, int rows, int H, float eps,
+                     q4b_stream_t stream) {
+  return rmsnorm_q8_1(h, w, xq, xd, xsum, x16, rows, H, eps, S(stream));
 }
 
 int q4b_decode_step(const q4b_decode_desc* d, q4b_stream_t stream) {

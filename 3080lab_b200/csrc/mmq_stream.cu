@@ -1,0 +1,423 @@
+// Streaming Q4_0 x int8 matrix product for decode (1..32 activation columns) on the tcgen05 int8 tensor cores.
+//
+//   y[n, m] = sum_b dw[m, b] * sx[n, b] * dot_b[m, n],   dot_b = sum_{i<32} (q4[m, 32b+i] - 8) * x8[n, 32b+i]  (exact)
+//
+// Two uses of the same kernel:
+//   Q8_1 mode   columns are sequences: x8 = Q8_1 int8 values, sx = their fp16 block scales.  This is the reference's
+//               MMQ arithmetic (lab/qwen_batched.py:1237-1243: exact int32 block dots, fp32 dw*dx scaling in k-block
+//               order) applied to batched decode.
+//   exact mode  one activation vector: each 32-value block of x is written as a block-fixed-point integer
+//               X_i = x_i / 2^e (24 or 30 bits) split into signed base-256 digits; digit j is column j, so
+//               sum_i (q-8) x_i = 2^e * sum_j 256^j dot_b[., j] with every dot an exact integer.  For fp16 x this
+//               equals the reference's dequantise-and-dot (lab/qwen_kernels.py:14-113) with no rounding inside a
+//               block; the only roundings are the per-block fp32 scale-and-add, as in the reference.
+//
+// Data movement (per CTA = 128 weight rows x one K slice):
+//   * thread t owns row t.  Before the programmatic-dependency wait it issues two 1-D bulk (TMA) copies: its row's
+//     nibbles and fp16 scales for the whole K slice, into a padded shared-memory slab, completing on one mbarrier.
+//     Weights never depend on the previous kernel, so with programmatic dependent launch this prefetch overlaps the
+//     producer of x.
+//   * after the wait the activation slice is staged once into shared memory as the UMMA B operand (K-major 8x16-byte
+//     core matrices, bytes permuted to match the nibble expansion order).
+//   * per batch of G k-blocks: each thread expands 16 bytes of nibbles to 32 signed bytes 16*(q-8) (two logic ops per
+//     four weights) and stores them with tcgen05.st straight into tensor memory as the A operand; one thread issues G
+//     tcgen05.mma.kind::i8 (M = 128, N = columns, K = 32 = one Q4_0 block), each into its own TMEM accumulator; the
+//     previous batch's accumulators are read back (tcgen05.ld) and folded into fp32 registers with the block scales
+//     while the tensor core works on the current one.
+//   * split-K: the CTAs of a thread-block cluster share a row tile; partial sums cross through distributed shared
+//     memory and are added in rank order, so results are bit-repeatable.
+// All waits are bounded (status word + fall through).
+#include "q4b_internal.h"
+#include "tc05.cuh"
+
+namespace q4b {
+
+namespace {
+
+constexpr int MODE_X16 = 0, MODE_X32 = 1, MODE_Q8 = 2;
+constexpr int ROWS = 128;
+constexpr size_t MAX_DYN_SMEM = 226 * 1024;   // 227 KB per CTA on sm_100 minus the static barriers
+
+struct StreamArgs {
+  const uint8_t* W;     // canonical nibbles, row pitch K/2 bytes
+  const __half* S;      // [N, K/32]
+  const void* X;        // exact modes: fp16 / fp32 [K]; Q8 mode: int8 [cols, K]
+  const __half* XD;     // Q8 mode: fp16 [cols, K/32]
+  void* Y;
+  const void* AUX;
+  uint32_t* status;
+  int N, K, cols, epi, ldy;
+  int gps;              // groups (of 8 k-blocks) per K slice
+  int ksplit;
+};
+
+__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   tc::smem_u32(dst)),
+               "l"(src), "r"(bytes), "r"(tc::smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float ld_peer_f32(const float* local, uint32_t rank) {
+  uint32_t a;
+  float v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(a) : "r"(tc::smem_u32(local)), "r"(rank));
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(a) : "memory");
+  return v;
+}
+
+// position of element i (0..31) of a k-block inside the 32 operand bytes (see tc::expand_nibbles)
+__device__ __forceinline__ int perm_pos(int i) { return 4 * (2 * (i >> 3) + (i & 1)) + ((i & 7) >> 1); }
+
+template <int NT>
+__device__ __forceinline__ uint32_t b_offset(int kbl, int n, int pos) {
+  return (uint32_t)kbl * (NT * 32) + (uint32_t)(((n >> 3) * 2 + (pos >> 4)) * 128 + (n & 7) * 16 + (pos & 15));
+}
+
+template <int MODE, int NT>
+__global__ void __launch_bounds__(ROWS) mmq_stream_kernel(const StreamArgs a) {
+  constexpr int G = NT <= 16 ? 8 : 4;                  // k-blocks per MMA batch
+  constexpr int NL = MODE == MODE_X16 ? 3 : 4;         // digits in exact mode
+  constexpr int NACC = MODE == MODE_Q8 ? NT : 1;
+  constexpr uint32_t A_COLS = 2 * G * 8, D_COLS = 2 * G * NT;
+  constexpr uint32_t TCOLS = (A_COLS + D_COLS) <= 128 ? 128 : ((A_COLS + D_COLS) <= 256 ? 256 : 512);
+  constexpr uint32_t IDESC = tc::idesc_i8(128, NT);
+
+  extern __shared__ __align__(128) uint8_t smem[];
+  __shared__ __align__(8) uint64_t bar_load;
+  __shared__ __align__(8) uint64_t bar_mma[2];
+  __shared__ uint32_t tmem_base_s;
+
+  const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
+  const int row0 = blockIdx.x * ROWS, row = row0 + t;
+  const int ks = blockIdx.y;
+  const int KB = a.K >> 5, GT = a.K >> 8;
+  const int g0 = ks * a.gps, ng = min(a.gps, GT - g0);          // host guarantees ng >= 1
+  const int nkb = ng * 8, kb0 = g0 * 8;
+  const uint32_t pitchW = a.gps * 128 + 16, pitchS = a.gps * 16 + 16;
+  uint8_t* slabW = smem;
+  uint8_t* slabS = slabW + ROWS * pitchW;
+  uint8_t* sB = slabS + ((ROWS * pitchS + 127) & ~127u);
+  float* xs = reinterpret_cast<float*>(sB + (size_t)a.gps * 8 * NT * 32);     // block scales of the activations
+
+  if (warp == 0) {
+    tc::tmem_alloc(&tmem_base_s, TCOLS);
+    tc::tmem_relinquish();
+  }
+  if (t == 0) {
+    tc::mbar_init(&bar_load, ROWS);
+    tc::mbar_init(&bar_mma[0], 1);
+    tc::mbar_init(&bar_mma[1], 1);
+    tc::mbar_fence_init();
+  }
+  tc::fence_before_sync();
+  __syncthreads();
+  tc::fence_after_sync();
+
+  // ---- weights: one bulk copy of nibbles and one of scales per row, whole K slice
+  if (row < a.N) {
+    const uint32_t bw = (uint32_t)ng * 128, bs = (uint32_t)ng * 16;
+    tc::mbar_expect_tx(&bar_load, bw + bs);
+    bulk_g2s(slabW + t * pitchW, a.W + (size_t)row * (a.K >> 1) + (size_t)g0 * 128, bw, &bar_load);
+    bulk_g2s(slabS + t * pitchS, a.S + (size_t)row * KB + kb0, bs, &bar_load);
+  } else {
+    tc::mbar_arrive(&bar_load);
+  }
+  pdl_launch_dependents();
+  pdl_wait();                                           // the activations come from the previous kernel
+
+  // ---- activations -> UMMA B operand in shared memory
+  if (MODE == MODE_Q8) {
+    const int8_t* xq = reinterpret_cast<const int8_t*>(a.X);
+    const int per = nkb * 2;
+    for (int c = t; c < NT * per; c += ROWS) {
+      const int n = c / per, r = c - n * per, kbl = r >> 1, kc = r & 1;
+      uint4 v = make_uint4(0u, 0u, 0u, 0u);
+      if (n < a.cols) v = __ldg(reinterpret_cast<const uint4*>(xq + (size_t)n * a.K + (size_t)(kb0 + kbl) * 32 + kc * 16));
+      uint32_t e0, o0, e1, o1;
+      tc::permute_bytes(v.x, v.y, e0, o0);
+      tc::permute_bytes(v.z, v.w, e1, o1);
+      *reinterpret_cast<uint4*>(sB + b_offset<NT>(kbl, n, kc * 16)) = make_uint4(e0, o0, e1, o1);
+    }
+    for (int c = t; c < NT * nkb; c += ROWS) {
+      const int n = c / nkb, kbl = c - n * nkb;
+      xs[kbl * NT + n] = n < a.cols ? __half2float(a.XD[(size_t)n * KB + kb0 + kbl]) : 0.f;
+    }
+  } else {
+    // exact mode: warp <-> k-block, lane <-> element.  X_i = rint(x_i * 2^-e) with |X_i| < 2^(8 NL - 2), split into
+    // signed base-256 digits, digit j -> column j.
+    for (int c = t; c < nkb * 64; c += ROWS)            // columns NL..7 must read as zero
+      *reinterpret_cast<uint32_t*>(sB + (size_t)c * 4) = 0u;
+    __syncthreads();
+    for (int kbl = warp; kbl < nkb; kbl += ROWS / 32) {
+      const int k = (kb0 + kbl) * 32 + lane;
+      const float x = MODE == MODE_X16 ? __half2float(reinterpret_cast<const __half*>(a.X)[k])
+                                       : reinterpret_cast<const float*>(a.X)[k];
+      const float amax = warp_max(fabsf(x));
+      int e = (__float_as_int(amax) >> 23) & 0xFF;      // biased exponent of the block maximum
+      e = max(e, 8 * NL);                               // tiny blocks: keep the scale a normal float
+      // 2^(8 NL - 3) / 2^(e - 127): |x| < 2^(e - 126) maps below 2^(8 NL - 2)
+      const float inv = __int_as_float((127 + (8 * NL - 3) - (e - 127)) << 23);
+      const float scl = __int_as_float((127 - (8 * NL - 3) + (e - 127)) << 23);
+      int X = (amax > 0.f && amax < INFINITY) ? __float2int_rn(x * inv) : 0;
+      const int pos = perm_pos(lane);
+#pragma unroll
+      for (int j = 0; j < NL; ++j) {
+        const int dgt = (int)(int8_t)(X & 0xFF);
+        sB[b_offset<NT>(kbl, j, pos)] = (uint8_t)dgt;
+        X = (X - dgt) >> 8;
+      }
+      if (lane == 0) xs[kbl] = (amax > 0.f && amax < INFINITY) ? scl : 0.f;
+    }
+  }
+  tc::fence_async_smem();
+  __syncthreads();
+
+  bool ok = tc::mbar_wait(&bar_load, 0);                // slab landed (async-proxy writes made visible by the barrier)
+
+  const uint32_t tmem = tmem_base_s;
+  const uint32_t lane_off = (uint32_t)(32 * warp) << 16;
+  const uint32_t tmem_a = tmem, tmem_d = tmem + A_COLS;
+  float acc[NACC];
+#pragma unroll
+  for (int n = 0; n < NACC; ++n) acc[n] = 0.f;
+
+  const int nbatch = nkb / G;
+  const uint8_t* myW = slabW + t * pitchW;
+  const __half* myS = reinterpret_cast<const __half*>(slabS + t * pitchS);
+
+  auto fold = [&](int bi) {                             // accumulators of batch bi -> acc
+    const int slot = bi & 1;
+    ok = tc::mbar_wait(&bar_mma[slot], (uint32_t)(bi >> 1) & 1u) && ok;
+    tc::fence_after_sync();
+#pragma unroll 2
+    for (int j = 0; j < G; ++j) {
+      const int kbl = bi * G + j;
+      const float dw = __half2float(myS[kbl]) * 0.0625f;           // 1/16 undoes the 16*(q-8) operand scaling
+      const uint32_t dcol = tmem_d + lane_off + (uint32_t)((slot * G + j) * NT);
+      if (MODE == MODE_Q8) {
+#pragma unroll
+        for (int c0 = 0; c0 < NT; c0 += 8) {
+          uint32_t d[8];
+          tc::tmem_ld8(dcol + c0, d);
+          tc::tmem_wait_ld();
+          const float4 s0 = *reinterpret_cast<const float4*>(xs + kbl * NT + c0);
+          const float4 s1 = *reinterpret_cast<const float4*>(xs + kbl * NT + c0 + 4);
+          const float sx[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+#pragma unroll
+          for (int n = 0; n < 8; ++n) acc[(c0 + n) % NACC] = fmaf(dw * sx[n], (float)(int32_t)d[n], acc[(c0 + n) % NACC]);
+        }
+      } else {
+        uint32_t d[8];
+        tc::tmem_ld8(dcol, d);
+        tc::tmem_wait_ld();
+        float f = fmaf(256.f, (float)(int32_t)d[1], (float)(int32_t)d[0]);
+        f = fmaf(65536.f, (float)(int32_t)d[2], f);
+        if (NL == 4) f = fmaf(16777216.f, (float)(int32_t)d[3], f);
+        acc[0] = fmaf(dw * xs[kbl], f, acc[0]);
+      }
+    }
+    tc::fence_before_sync();
+  };
+
+  for (int bi = 0; bi < nbatch; ++bi) {
+    const int slot = bi & 1;
+#pragma unroll 2
+    for (int j = 0; j < G; ++j) {
+      const uint4 w = *reinterpret_cast<const uint4*>(myW + (size_t)(bi * G + j) * 16);
+      uint32_t ex[8];
+      tc::expand_nibbles(w.x, ex[0], ex[1]);
+      tc::expand_nibbles(w.y, ex[2], ex[3]);
+      tc::expand_nibbles(w.z, ex[4], ex[5]);
+      tc::expand_nibbles(w.w, ex[6], ex[7]);
+      tc::tmem_st8(tmem_a + lane_off + (uint32_t)((slot * G + j) * 8), ex);
+    }
+    tc::tmem_wait_st();
+    tc::fence_before_sync();
+    __syncthreads();
+    if (t == 0) {
+      tc::fence_after_sync();
+      const uint32_t b0 = tc::smem_u32(sB);
+      for (int j = 0; j < G; ++j) {
+        const uint64_t bdesc = tc::smem_desc_kmajor(b0 + (uint32_t)(bi * G + j) * (NT * 32), 128, 256);
+        tc::mma_i8_ts(tmem_d + (uint32_t)((slot * G + j) * NT), tmem_a + (uint32_t)((slot * G + j) * 8), bdesc, IDESC, 0u);
+      }
+      tc::mma_commit(&bar_mma[slot]);
+    }
+    if (bi > 0) fold(bi - 1);
+  }
+  if (nbatch > 0) fold(nbatch - 1);
+  __syncthreads();                                      // every thread is done with the slabs and with TMEM
+
+  // ---- split-K: partial sums through distributed shared memory, added in rank order
+  if (a.ksplit > 1) {
+    float* part = reinterpret_cast<float*>(slabW);      // [NACC][128]
+    if (ks != 0) {
+#pragma unroll
+      for (int n = 0; n < NACC; ++n) part[n * ROWS + t] = acc[n];
+    }
+    cluster_sync_all();
+    if (ks == 0) {
+      for (int r = 1; r < a.ksplit; ++r) {
+#pragma unroll
+        for (int n = 0; n < NACC; ++n) acc[n] += ld_peer_f32(part + n * ROWS + t, (uint32_t)r);
+      }
+    }
+    cluster_sync_all();                                 // peers stay alive until the leader has read them
+  }
+
+  if (ks == 0) {
+#pragma unroll
+    for (int n = 0; n < NACC; ++n) {
+      const float v = acc[n];
+      const float partner = __shfl_xor_sync(0xffffffffu, v, 1);
+      if (n < a.cols && row < a.N) {
+        const size_t base = (size_t)n * a.ldy;
+        switch (a.epi) {
+          case Q4B_EPI_STORE: reinterpret_cast<__half*>(a.Y)[base + row] = __float2half_rn(v); break;
+          case Q4B_EPI_BIASF:
+            reinterpret_cast<__half*>(a.Y)[base + row] = __float2half_rn(v + reinterpret_cast<const float*>(a.AUX)[row]);
+            break;
+          case Q4B_EPI_RESID: reinterpret_cast<float*>(a.Y)[base + row] += v; break;
+          case Q4B_EPI_LOGITS: reinterpret_cast<float*>(a.Y)[base + row] = v; break;
+          case Q4B_EPI_SWIGLU:
+            if ((t & 1) == 0) reinterpret_cast<__half*>(a.Y)[base + (row >> 1)] = __float2half_rn(v / (1.f + __expf(-v)) * partner);
+            break;
+          default: break;
+        }
+      }
+    }
+  }
+  if (!ok && t == 0) atomicExch(a.status, 1u);
+  tc::fence_before_sync();
+  __syncthreads();
+  if (warp == 0) tc::tmem_dealloc(tmem, TCOLS);
+}
+
+struct Geometry {
+  int ksplit, gps;
+  size_t smem;
+  uint32_t tcols;
+};
+
+size_t smem_bytes(int gps, int nt) {
+  const size_t pitchW = (size_t)gps * 128 + 16, pitchS = (size_t)gps * 16 + 16;
+  size_t s = ROWS * pitchW;
+  s += (ROWS * pitchS + 127) & ~(size_t)127;
+  s += (size_t)gps * 8 * nt * 32;          // B operand
+  s += (size_t)gps * 8 * nt * 4;           // activation block scales
+  return s + 128;
+}
+
+bool plan(int N, int K, int nt, Geometry& g) {
+  const int GT = K / 256, tiles = (N + ROWS - 1) / ROWS;
+  const int G = nt <= 16 ? 8 : 4;
+  const uint32_t need = 2 * G * 8 + 2 * G * nt;
+  g.tcols = need <= 128 ? 128 : (need <= 256 ? 256 : 512);
+  const int sms = sm_count();
+  int best = -1;
+  for (int ks = 1; ks <= 8 && ks <= GT; ++ks) {
+    const int gps = (GT + ks - 1) / ks;
+    if ((ks - 1) * gps >= GT) continue;                 // an empty slice
+    if (smem_bytes(gps, nt) > MAX_DYN_SMEM) continue;
+    best = ks;
+    if ((long)tiles * ks >= (sms * 3) / 5) break;       // enough CTAs to occupy the machine
+  }
+  if (best < 0) return false;
+  g.ksplit = best;
+  g.gps = (GT + best - 1) / best;
+  g.smem = smem_bytes(g.gps, nt);
+  // tcgen05.alloc blocks while an SM's 512 TMEM columns are taken; CTAs of one cluster wait for each other, so the
+  // number of co-resident CTAs times their columns must never exceed 512.  Shared memory is the limiter we control.
+  const size_t max_ctas = 512 / g.tcols;
+  const size_t floor_smem = (227 * 1024) / (max_ctas + 1) + 1024;
+  if (g.smem < floor_smem) g.smem = floor_smem;
+  return true;
+}
+
+template <int MODE, int NT>
+int launch(const StreamArgs& a, const Geometry& g, cudaStream_t st) {
+  static size_t configured = 0;
+  auto kern = mmq_stream_kernel<MODE, NT>;
+  if (g.smem > configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_DYN_SMEM);
+    if (e != cudaSuccess) {
+      set_cuda_error(e, "mmq_stream: cudaFuncSetAttribute");
+      return Q4B_E_CUDA;
+    }
+    configured = MAX_DYN_SMEM;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((a.N + ROWS - 1) / ROWS, g.ksplit, 1);
+  cfg.blockDim = dim3(ROWS, 1, 1);
+  cfg.dynamicSmemBytes = g.smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[2];
+  int na = 0;
+  attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[na].val.programmaticStreamSerializationAllowed = 1;
+  ++na;
+  if (g.ksplit > 1) {
+    attr[na].id = cudaLaunchAttributeClusterDimension;
+    attr[na].val.clusterDim.x = 1;
+    attr[na].val.clusterDim.y = g.ksplit;
+    attr[na].val.clusterDim.z = 1;
+    ++na;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = na;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, a);
+  if (e != cudaSuccess) {
+    set_cuda_error(e, "mmq_stream: launch");
+    return Q4B_E_CUDA;
+  }
+  return Q4B_OK;
+}
+
+template <int MODE>
+int launch_nt(int nt, const StreamArgs& a, const Geometry& g, cudaStream_t st) {
+  if (nt == 8) return launch<MODE, 8>(a, g, st);
+  if (nt == 16) return launch<MODE, 16>(a, g, st);
+  return launch<MODE, 32>(a, g, st);
+}
+
+}  // namespace
+
+// mode: 0 exact fp16 x, 1 exact fp32 x, 2 Q8_1.  cols: 1 for the exact modes, 1..32 sequences for Q8_1.
+int mmq_stream(const void* W, const void* S, const void* X, const void* XD, void* Y, const void* AUX, int N, int K,
+               int cols, int mode, int epilogue, int ldy, uint32_t* status, cudaStream_t st) {
+  if (N <= 0 || K <= 0 || (K % 256)) return fail(Q4B_E_SHAPE, "mmq_stream: N > 0 and K a positive multiple of 256 required");
+  if (mode < 0 || mode > 2) return fail(Q4B_E_ARG, "mmq_stream: unknown mode");
+  if (epilogue < Q4B_EPI_STORE || epilogue > Q4B_EPI_LOGITS) return fail(Q4B_E_ARG, "mmq_stream: unknown epilogue");
+  if (cols < 1 || cols > 32 || (mode != MODE_Q8 && cols != 1)) return fail(Q4B_E_SHAPE, "mmq_stream: 1..32 columns (1 in exact mode)");
+  if (epilogue == Q4B_EPI_SWIGLU && (N % 2)) return fail(Q4B_E_SHAPE, "mmq_stream: swiglu needs an even row count");
+  if (!W || !S || !X || !Y || !status || !aligned16(W) || !aligned16(S) || !aligned16(X))
+    return fail(Q4B_E_ALIGN, "mmq_stream: W, S, X must be non-null and 16-byte aligned");
+  if (mode == MODE_Q8 && !XD) return fail(Q4B_E_ALIGN, "mmq_stream: Q8_1 mode needs the block scales");
+  if (epilogue == Q4B_EPI_BIASF && !AUX) return fail(Q4B_E_ALIGN, "mmq_stream: biasf needs AUX");
+  const int nt = mode != MODE_Q8 ? 8 : (cols <= 8 ? 8 : (cols <= 16 ? 16 : 32));
+  Geometry g;
+  if (!plan(N, K, nt, g)) return fail(Q4B_E_SHAPE, "mmq_stream: no K split fits shared memory for this K");
+  StreamArgs a;
+  a.W = reinterpret_cast<const uint8_t*>(W);
+  a.S = reinterpret_cast<const __half*>(S);
+  a.X = X;
+  a.XD = reinterpret_cast<const __half*>(XD);
+  a.Y = Y;
+  a.AUX = AUX;
+  a.status = status;
+  a.N = N;
+  a.K = K;
+  a.cols = cols;
+  a.epi = epilogue;
+  a.ldy = ldy;
+  a.gps = g.gps;
+  a.ksplit = g.ksplit;
+  if (mode == MODE_X16) return launch_nt<MODE_X16>(nt, a, g, st);
+  if (mode == MODE_X32) return launch_nt<MODE_X32>(nt, a, g, st);
+  return launch_nt<MODE_Q8>(nt, a, g, st);
+}
+
+}  // namespace q4b

@@ -1,0 +1,108 @@
+// Q8_1 activation quantiser and the fused RMSNorm + quantise kernel.
+//
+// Per 32 values: amax = max|x|, d = amax / 127 (fp32 division), q = d > 0 ? rint(x / d) : 0 (fp32 division, round to
+// nearest even), exactly the arithmetic of the reference's QUANT_Q8 (lab/qwen_batched.py:1030-1039), so the int8
+// values equal the reference's.  Stored per block: the 32 int8 values, d rounded to fp16, and optionally the Q8_1 sum
+// term d * sum(q) as fp16.  Layout is planar: xq int8 [P, K], xd fp16 [P, K/32], xsum fp16 [P, K/32].
+// The fused form follows rmsnorm_q8_source (lab/qwen_batched.py:1044-1091): the normalised value is rounded to 16 bits
+// first, so the result is identical to RMSNorm followed by the quantiser.
+#include "q4b_internal.h"
+
+namespace q4b {
+
+namespace {
+
+// 8 lanes per block, 4 consecutive values per lane: each lane reads 8 bytes and writes 4.
+__device__ __forceinline__ void quant_block4(const float x[4], int8_t* q_out, __half* d_out, __half* s_out, int lane_in_blk,
+                                             bool live) {
+  float amax = fmaxf(fmaxf(fabsf(x[0]), fabsf(x[1])), fmaxf(fabsf(x[2]), fabsf(x[3])));
+#pragma unroll
+  for (int o = 4; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  const float d = amax / 127.f;
+  int q[4], sq = 0;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    q[i] = d > 0.f ? __float2int_rn(x[i] / d) : 0;
+    sq += q[i];
+  }
+  if (live) {
+    const uint32_t packed = (uint32_t)(q[0] & 0xFF) | ((uint32_t)(q[1] & 0xFF) << 8) | ((uint32_t)(q[2] & 0xFF) << 16) |
+                            ((uint32_t)(q[3] & 0xFF) << 24);
+    *reinterpret_cast<uint32_t*>(q_out) = packed;
+  }
+#pragma unroll
+  for (int o = 4; o; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+  if (live && lane_in_blk == 0) {
+    *d_out = __float2half_rn(d);
+    if (s_out) *s_out = __float2half_rn(d * (float)sq);
+  }
+}
+
+__global__ void __launch_bounds__(256) quant_q8_1_kernel(const __half* __restrict__ x, int8_t* __restrict__ xq,
+                                                         __half* __restrict__ xd, __half* __restrict__ xsum, size_t nblk) {
+  pdl_wait();
+  const size_t gid = (size_t)blockIdx.x * 256 + threadIdx.x;
+  const size_t blk = gid >> 3;
+  const int l = (int)(gid & 7);
+  const bool live = blk < nblk;                      // whole 8-lane groups are live or dead together
+  const size_t at = (live ? blk : 0) * 32 + l * 4;
+  const uint2 raw = *reinterpret_cast<const uint2*>(x + at);
+  const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&raw.x));
+  const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
+  const float v[4] = {a.x, a.y, b.x, b.y};
+  quant_block4(v, xq + at, xd + (live ? blk : 0), xsum ? xsum + (live ? blk : 0) : nullptr, l, live);
+}
+
+// One CTA of H/4 threads (<= 1024) per row: RMSNorm in registers, round to fp16, quantise.
+__global__ void __launch_bounds__(1024) rmsnorm_q8_1_kernel(const float* __restrict__ h, const float* __restrict__ w,
+                                                            int8_t* __restrict__ xq, __half* __restrict__ xd,
+                                                            __half* __restrict__ xsum, __half* __restrict__ x16, int H,
+                                                            float eps) {
+  __shared__ float part[32];
+  pdl_wait();
+  const int row = blockIdx.x, t = threadIdx.x, i0 = 4 * t;
+  const float4 hv = *reinterpret_cast<const float4*>(h + (size_t)row * H + i0);
+  const float4 wv = *reinterpret_cast<const float4*>(w + i0);
+  float ss = hv.x * hv.x + hv.y * hv.y + hv.z * hv.z + hv.w * hv.w;
+  ss = warp_sum(ss);
+  if ((t & 31) == 0) part[t >> 5] = ss;
+  __syncthreads();
+  float tot = 0.f;
+  for (int j = 0; j < (int)(blockDim.x >> 5); ++j) tot += part[j];
+  const float r = rsqrtf(tot / (float)H + eps);
+  const __half2 p0 = __floats2half2_rn(hv.x * r * wv.x, hv.y * r * wv.y);
+  const __half2 p1 = __floats2half2_rn(hv.z * r * wv.z, hv.w * r * wv.w);
+  if (x16) {
+    uint2 st;
+    st.x = *reinterpret_cast<const uint32_t*>(&p0);
+    st.y = *reinterpret_cast<const uint32_t*>(&p1);
+    *reinterpret_cast<uint2*>(x16 + (size_t)row * H + i0) = st;
+  }
+  const float2 a = __half22float2(p0), b = __half22float2(p1);
+  const float v[4] = {a.x, a.y, b.x, b.y};
+  const size_t blk = ((size_t)row * H + i0) >> 5;
+  quant_block4(v, xq + (size_t)row * H + i0, xd + blk, xsum ? xsum + blk : nullptr, t & 7, true);
+}
+
+}  // namespace
+
+int quant_q8_1(const void* x, void* xq, void* xd, void* xsum, int rows, int K, cudaStream_t st) {
+  if (rows <= 0 || K <= 0 || (K % 32)) return fail(Q4B_E_SHAPE, "quant_q8_1: rows > 0 and K a positive multiple of 32 required");
+  if (!x || !xq || !xd || (reinterpret_cast<uintptr_t>(x) & 7u) || (reinterpret_cast<uintptr_t>(xq) & 3u))
+    return fail(Q4B_E_ALIGN, "quant_q8_1: null or misaligned pointer");
+  const size_t nblk = (size_t)rows * (K / 32);
+  const size_t threads = nblk * 8;
+  quant_q8_1_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, st>>>((const __half*)x, (int8_t*)xq, (__half*)xd, (__half*)xsum, nblk);
+  return check_launch("quant_q8_1");
+}
+
+int rmsnorm_q8_1(const float* h, const float* w, void* xq, void* xd, void* xsum, void* x16, int rows, int H, float eps,
+                 cudaStream_t st) {
+  if (rows <= 0 || H <= 0 || (H % 128) || H > 4096) return fail(Q4B_E_SHAPE, "rmsnorm_q8_1: H must be a multiple of 128, at most 4096");
+  if (!h || !w || !xq || !xd || !aligned16(h) || !aligned16(w) || (reinterpret_cast<uintptr_t>(xq) & 3u))
+    return fail(Q4B_E_ALIGN, "rmsnorm_q8_1: null or misaligned pointer");
+  rmsnorm_q8_1_kernel<<<rows, H / 4, 0, st>>>(h, w, (int8_t*)xq, (__half*)xd, (__half*)xsum, (__half*)x16, H, eps);
+  return check_launch("rmsnorm_q8_1");
+}
+
+}  // namespace q4b

@@ -20,3 +20,42 @@ def blockdot(W, xq, M: int, K: int, mode: int = 0) -> torch.Tensor:
     if int(status.item()) != 0:
         raise _ffi.Q4BError(_ffi.E_TIMEOUT, "blockdot: a bounded wait on the tensor-core pipeline expired")
     return out
+
+
+class Status:
+    """The uint32 status word the tensor-core kernels set when a bounded device-side wait expires."""
+
+    def __init__(self, device):
+        self.word = torch.zeros(1, dtype=torch.int32, device=device)
+
+    def check(self, what: str = "tensor-core kernel") -> None:
+        if int(self.word.item()) != 0:
+            self.word.zero_()
+            raise _ffi.Q4BError(_ffi.E_TIMEOUT, f"{what}: a bounded wait on the tensor-core pipeline expired")
+
+
+def gemv_tc(W, S, X, Y, aux, N: int, K: int, epi: str, status: Status) -> None:
+    """Exact Q4_0 GEMV of one activation vector on the int8 tensor cores; same contract as qwen_kernels.gemv."""
+    xd = _ffi.X_F16 if X.dtype == torch.float16 else _ffi.X_F32
+    if X.dtype not in (torch.float16, torch.float32):
+        raise TypeError("X must be fp16 or fp32")
+    _ffi.call("q4b_gemv_q4_0_tc", _p(W), _p(S), _p(X), _p(Y), _p(aux), N, K, _ffi.EPI[epi], xd, _p(status.word), _stream())
+
+
+def quant_q8(x, xq, xd, xsum=None) -> None:
+    """x fp16 [rows, K] -> xq int8 [rows, K], xd fp16 [rows, K/32] (QUANT_Q8, lab/qwen_batched.py:1016-1041)."""
+    rows = 1 if x.dim() == 1 else x.shape[0]
+    _ffi.call("q4b_quant_q8_1", _p(x), _p(xq), _p(xd), _p(xsum), rows, x.shape[-1], _stream())
+
+
+def rmsnorm_q8(h, w, xq, xd, eps: float, xsum=None, x16=None) -> None:
+    """RMSNorm + Q8_1 quantiser in one pass (rmsnorm_q8_source, lab/qwen_batched.py:1044-1091)."""
+    rows = 1 if h.dim() == 1 else h.shape[0]
+    _ffi.call("q4b_rmsnorm_q8_1", _p(h), _p(w), _p(xq), _p(xd), _p(xsum), _p(x16), rows, h.shape[-1], float(eps), _stream())
+
+
+def gemm8(W, S, xq, xd, Y, aux, N: int, K: int, P: int, epi: str, ldy: int, status: Status) -> None:
+    """Y[P, :] = epilogue(Q8_1(xq, xd) x Q4_0(W, S)^T) with exact int32 block dots (gemm_q4i8_ms_source,
+    lab/qwen_batched.py:1271-1561)."""
+    _ffi.call("q4b_mmq_q4_0_q8_1", _p(W), _p(S), _p(xq), _p(xd), _p(Y), _p(aux), N, K, P, _ffi.EPI[epi], ldy,
+              _p(status.word), _stream())

@@ -110,6 +110,35 @@ int q4b_argmax_advance(const float* logits, int rows, int V, int64_t* tok, int64
 int q4b_blockdot_q4_0_q8_1(const void* W, const void* xq, int32_t* out, int M, int K, int P, int mode,
                            uint32_t* status, q4b_stream_t stream);
 
+/* ---- tensor-core path for decode --------------------------------------------------------------------------------
+ * Q4_0 GEMV for one activation vector on the tcgen05 int8 tensor cores, exact: each 32-value block of x is split
+ * into signed base-256 digits of a block-fixed-point integer, the digits are the columns of an int8 MMA, and the
+ * integer block dots are recombined and scaled in fp32.  Same contract and epilogues as q4b_gemv_q4_0 (it replaces
+ * the same launch site, lab/qwen_kernels.py:14-113); K must be a multiple of 256.  Launched with programmatic
+ * dependent launch: the weight prefetch overlaps the kernel that precedes it in the stream.
+ * status: one uint32, set to 1 if a bounded device-side wait expired (zero it once; check when convenient). */
+int q4b_gemv_q4_0_tc(const void* W, const void* S, const void* X, void* Y, const void* AUX, int N, int K, int epilogue,
+                     int x_dtype, uint32_t* status, q4b_stream_t stream);
+
+/* Q8_1 x Q4_0 matrix product ("MMQ") for P <= 32 activation rows (batched decode): Y[p, n] = epilogue(sum over
+ * k-blocks of dw[n, b] * dx[p, b] * dot(p, n, b)) with exact int32 block dots.  Replaces the launch of
+ * gemm_q4i8_ms_source (lab/qwen_batched.py:1271-1561; host Prefill.gemm8 scripts/qwen_prefill.py:176-190) and, for
+ * batched decode, of gemv_v2_source (lab/qwen_batched.py:467-641; host Batched.gemv
+ * scripts/qwen_batched_decode.py:138-154).  xq int8 [P, K], xd fp16 [P, K/32]; Y rows have pitch ldy elements:
+ * store/biasf fp16 [P, ldy], resid/logits fp32 [P, ldy], swiglu fp16 [P, ldy] with N/2 outputs per row. */
+int q4b_mmq_q4_0_q8_1(const void* W, const void* S, const void* xq, const void* xd, void* Y, const void* AUX, int N,
+                      int K, int P, int epilogue, int ldy, uint32_t* status, q4b_stream_t stream);
+
+/* Q8_1 quantiser: xq int8 [rows, K], xd fp16 [rows, K/32] (= amax/127 rounded to fp16), xsum fp16 [rows, K/32]
+ * (= d * sum(q), may be null) from x fp16 [rows, K].  Replaces QUANT_Q8 (lab/qwen_batched.py:1016-1041). */
+int q4b_quant_q8_1(const void* x, void* xq, void* xd, void* xsum, int rows, int K, q4b_stream_t stream);
+
+/* RMSNorm fused with the Q8_1 quantiser (rmsnorm_q8_source, lab/qwen_batched.py:1044-1091): the normalised row is
+ * rounded to fp16, then quantised.  x16 (fp16 [rows, H], may be null) also receives the rounded row.
+ * H a multiple of 128, at most 4096. */
+int q4b_rmsnorm_q8_1(const float* h, const float* w, void* xq, void* xd, void* xsum, void* x16, int rows, int H,
+                     float eps, q4b_stream_t stream);
+
 /* ---- whole decode step, batch 1 -------------------------------------------------------------------------------
  * One greedy decode token through every layer, launched back to back on `stream` (capturable as one CUDA graph).
  * Replaces the launch sequence of FusedQwen.step (scripts/qwen_fused.py:113-145): embed, then per layer

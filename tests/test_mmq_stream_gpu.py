@@ -1,0 +1,200 @@
+"""The tcgen05 streaming kernel: exact single-vector GEMV (digit columns) and Q8_1 x Q4_0 for 1..32 rows, against
+the oracle.  fp32 results within 1e-3 of the largest reference magnitude (observed ~1e-6); quantiser outputs exact."""
+import numpy as np
+import pytest
+
+from conftest import gemv_inputs, oracle, pkg
+
+torch = pytest.importorskip("torch")
+pytestmark = pytest.mark.gpu
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def nerr(got, ref):
+    ref = np.asarray(ref, np.float64)
+    return float(np.max(np.abs(np.asarray(got, np.float64) - ref)) / max(np.max(np.abs(ref)), 1e-30))
+
+
+def rand_q4(rng, n, k):
+    W = rng.integers(0, 2 ** 32, size=(n, k // 8), dtype=np.uint32).view(np.int32)
+    S = rng.uniform(0.002, 0.02, size=(n, k // 32)).astype(np.float16)
+    return W, S
+
+
+@pytest.fixture(scope="module")
+def QB():
+    pkg("qwen_kernels").init(0)
+    return pkg("qwen_batched")
+
+
+@pytest.mark.parametrize("n,k", [(128, 256), (5, 256), (200, 512), (2048, 1536), (1536, 1536), (17920, 1536), (1536, 8960),
+                                 (130, 3584), (260, 18944)])
+@pytest.mark.parametrize("xdt", ["f16", "f32"])
+def test_gemv_tc_matches_oracle(QB, n, k, xdt):
+    o = oracle()
+    rng = np.random.default_rng(n * 7 + k)
+    W, S = rand_q4(rng, n, k)
+    x = rng.standard_normal(k).astype(np.float16 if xdt == "f16" else np.float32)
+    x[::97] *= 1e-3                                           # wide dynamic range inside blocks
+    ref = o.gemv_ref(W, S, x)
+    st = QB.Status("cuda")
+    y = torch.full((n + 8,), float("nan"), device="cuda")
+    Wd, Sd, xd = dev(W), dev(S), dev(x)
+    QB.gemv_tc(Wd, Sd, xd, y, None, n, k, "logits", st)
+    st.check()
+    got = y.cpu().numpy()
+    assert np.all(np.isnan(got[n:]))
+    assert nerr(got[:n], ref) < 2e-6
+    y2 = torch.empty(n, device="cuda")
+    QB.gemv_tc(Wd, Sd, xd, y2, None, n, k, "logits", st)
+    st.check()
+    assert torch.equal(y2, y[:n]), "not bit-repeatable"
+
+
+def test_gemv_tc_ffn_up_golden(QB, golden):
+    g = golden["gemv_ffn_up"]
+    q, d, x = gemv_inputs(8960, 1536, False)
+    W = pkg("gguf").pack_nibbles(q)
+    st = QB.Status("cuda")
+    y = torch.empty(8960, device="cuda")
+    QB.gemv_tc(dev(W), dev(d), dev(x), y, None, 8960, 1536, "logits", st)
+    st.check()
+    got = y.cpu().numpy()
+    assert nerr(got, g["y_ref_f64"]) < 2e-6
+    assert nerr(got, g["y_ref_f32"]) < 1e-5
+
+
+@pytest.mark.parametrize("n,k", [(256, 256), (2048, 1536), (1536, 8960)])
+def test_gemv_tc_epilogues(QB, n, k):
+    o = oracle()
+    rng = np.random.default_rng(n + k + 1)
+    W, S = rand_q4(rng, n, k)
+    x = rng.standard_normal(k).astype(np.float16)
+    acc = o.gemv_ref(W, S, x)
+    Wd, Sd, xd = dev(W), dev(S), dev(x)
+    st = QB.Status("cuda")
+    y = torch.empty(n, dtype=torch.float16, device="cuda")
+    QB.gemv_tc(Wd, Sd, xd, y, None, n, k, "store", st)
+    assert nerr(y.float().cpu().numpy(), o.f16(acc)) < 1e-3
+    bias = (0.1 * rng.standard_normal(n)).astype(np.float32)
+    QB.gemv_tc(Wd, Sd, xd, y, dev(bias), n, k, "biasf", st)
+    assert nerr(y.float().cpu().numpy(), o.f16(acc + bias)) < 1e-3
+    h0 = rng.standard_normal(n).astype(np.float32)
+    h = dev(h0)
+    QB.gemv_tc(Wd, Sd, xd, h, None, n, k, "resid", st)
+    assert nerr(h.cpu().numpy(), h0 + acc) < 1e-5
+    ys = torch.empty(n // 2, dtype=torch.float16, device="cuda")
+    QB.gemv_tc(Wd, Sd, xd, ys, None, n, k, "swiglu", st)
+    assert nerr(ys.float().cpu().numpy(), o.silu_mul(acc[0::2], acc[1::2])) < 1e-3
+    st.check()
+
+
+def test_gemv_tc_matches_cuda_core_gemv(QB):
+    """Two independent implementations of the same dequantise-and-dot agree to fp32 rounding."""
+    K = pkg("qwen_kernels")
+    rng = np.random.default_rng(77)
+    n, k = 2048, 1536
+    W, S = rand_q4(rng, n, k)
+    x = rng.standard_normal(k).astype(np.float16)
+    Wd, Sd, xd = dev(W), dev(S), dev(x)
+    a, b = torch.empty(n, device="cuda"), torch.empty(n, device="cuda")
+    st = QB.Status("cuda")
+    K.gemv(Wd, Sd, xd, a, None, n, k, "logits")
+    QB.gemv_tc(Wd, Sd, xd, b, None, n, k, "logits", st)
+    st.check()
+    assert nerr(b.cpu().numpy(), a.cpu().numpy()) < 2e-6
+
+
+@pytest.mark.parametrize("rows,K", [(1, 1536), (8, 8960), (32, 256), (5, 64), (2048, 1536)])
+def test_quant_q8_1_exact(QB, rows, K):
+    o = oracle()
+    rng = np.random.default_rng(rows + K)
+    x = (rng.standard_normal((rows, K)) * rng.uniform(0.01, 30, size=(rows, 1))).astype(np.float16)
+    x[0, :32] = 0
+    xq = torch.empty(rows, K, dtype=torch.int8, device="cuda")
+    xd = torch.empty(rows, K // 32, dtype=torch.float16, device="cuda")
+    xs = torch.empty(rows, K // 32, dtype=torch.float16, device="cuda")
+    QB.quant_q8(dev(x), xq, xd, xs)
+    q, d, s = o.quant_q8_1(x)
+    assert np.array_equal(xq.cpu().numpy(), q)
+    assert np.array_equal(xd.cpu().numpy().view(np.uint16), d.view(np.uint16))
+    want_s = (d.astype(np.float32) * 0 + (np.abs(x.astype(np.float32)).reshape(rows, -1, 32).max(-1) / np.float32(127)) * s.astype(np.float32)).astype(np.float16)
+    assert np.array_equal(xs.cpu().numpy().view(np.uint16), want_s.view(np.uint16))
+
+
+@pytest.mark.parametrize("rows,H", [(1, 1536), (8, 1536), (3, 3584), (32, 512), (2, 128)])
+def test_rmsnorm_q8_1_equals_rmsnorm_then_quant(QB, rows, H):
+    K = pkg("qwen_kernels")
+    rng = np.random.default_rng(rows * H)
+    h = dev((3 * rng.standard_normal((rows, H))).astype(np.float32))
+    w = dev((1 + 0.1 * rng.standard_normal(H)).astype(np.float32))
+    x16 = torch.empty(rows, H, dtype=torch.float16, device="cuda")
+    xq = torch.empty(rows, H, dtype=torch.int8, device="cuda")
+    xd = torch.empty(rows, H // 32, dtype=torch.float16, device="cuda")
+    QB.rmsnorm_q8(h, w, xq, xd, 1e-6, x16=x16)
+    o = oracle()
+    ref16 = o.rmsnorm(h.cpu().numpy(), w.cpu().numpy(), 1e-6)
+    got16 = x16.float().cpu().numpy()
+    assert nerr(got16, ref16) < 1e-3
+    # quantising the fp16 row it wrote gives exactly its int8 output (fused == unfused)
+    q, d, _ = o.quant_q8_1(x16.cpu().numpy())
+    assert np.array_equal(xq.cpu().numpy(), q)
+    assert np.array_equal(xd.cpu().numpy().view(np.uint16), d.view(np.uint16))
+    xq2, xd2 = torch.empty_like(xq), torch.empty_like(xd)
+    QB.quant_q8(x16, xq2, xd2)
+    assert torch.equal(xq, xq2) and torch.equal(xd, xd2)
+
+
+@pytest.mark.parametrize("P", [1, 3, 8, 9, 16, 17, 32])
+@pytest.mark.parametrize("n,k", [(2048, 1536), (1536, 8960), (200, 512)])
+def test_mmq_stream_q8_matches_oracle(QB, P, n, k):
+    o = oracle()
+    rng = np.random.default_rng(P * 1000 + n + k)
+    W, S = rand_q4(rng, n, k)
+    x = rng.standard_normal((P, k)).astype(np.float16)
+    xq, xd, _ = o.quant_q8_1(x)
+    ref = o.mmq(W, S, xq, xd)
+    st = QB.Status("cuda")
+    y = torch.full((P, n), float("nan"), device="cuda")
+    QB.gemm8(dev(W), dev(S), dev(xq), dev(xd), y, None, n, k, P, "logits", n, st)
+    st.check()
+    assert nerr(y.cpu().numpy(), ref) < 2e-6
+
+
+def test_mmq_stream_q8_epilogues(QB):
+    o = oracle()
+    rng = np.random.default_rng(5)
+    P, n, k = 8, 512, 1536
+    W, S = rand_q4(rng, n, k)
+    x = rng.standard_normal((P, k)).astype(np.float16)
+    xq, xd, _ = o.quant_q8_1(x)
+    acc = o.mmq(W, S, xq, xd)
+    Wd, Sd, xqd, xdd = dev(W), dev(S), dev(xq), dev(xd)
+    st = QB.Status("cuda")
+    bias = (0.1 * rng.standard_normal(n)).astype(np.float32)
+    y = torch.empty(P, n, dtype=torch.float16, device="cuda")
+    QB.gemm8(Wd, Sd, xqd, xdd, y, dev(bias), n, k, P, "biasf", n, st)
+    assert nerr(y.float().cpu().numpy(), o.f16(acc + bias)) < 1e-3
+    h0 = rng.standard_normal((P, n)).astype(np.float32)
+    h = dev(h0)
+    QB.gemm8(Wd, Sd, xqd, xdd, h, None, n, k, P, "resid", n, st)
+    assert nerr(h.cpu().numpy(), h0 + acc) < 1e-5
+    ys = torch.empty(P, n // 2, dtype=torch.float16, device="cuda")
+    QB.gemm8(Wd, Sd, xqd, xdd, ys, None, n, k, P, "swiglu", n // 2, st)
+    assert nerr(ys.float().cpu().numpy(), o.silu_mul(acc[:, 0::2], acc[:, 1::2])) < 1e-3
+    st.check()
+
+
+def test_mmq_stream_rejects_bad_shapes(QB):
+    ffi = pkg("_ffi")
+    st = QB.Status("cuda")
+    z = torch.zeros(4096, dtype=torch.int32, device="cuda")
+    with pytest.raises(ffi.Q4BError) as e:
+        QB.gemv_tc(z, z, z.view(torch.float16), z, None, 4, 96, "logits", st)      # K not a multiple of 256
+    assert e.value.code == ffi.E_SHAPE
+    with pytest.raises(ffi.Q4BError) as e:
+        QB.gemm8(z, z, z, z, z, None, 128, 256, 33, "logits", 128, st)              # too many rows for this kernel
+    assert e.value.code == ffi.E_SHAPE
