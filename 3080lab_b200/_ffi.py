@@ -31,7 +31,10 @@ class DecodeDesc(C.Structure):
                 ("vocab", _I), ("max_len", _I), ("eps", _F), ("scale", _F), ("embed", _P), ("layer", C.POINTER(Layer)),
                 ("norm", _P), ("head", Linear), ("cosT", _P), ("sinT", _P), ("tok", _P), ("pos", _P), ("h", _P),
                 ("x", _P), ("qkv", _P), ("att", _P), ("act", _P), ("logits", _P), ("attn_ws", _P), ("attn_ws_bytes", _Z),
-                ("head_ws", _P), ("head_ws_bytes", _Z)]
+                ("head_ws", _P), ("head_ws_bytes", _Z), ("status", _P), ("flags", _I)]
+
+
+STEP_TENSOR_CORE = 1
 
 
 # name -> (restype, argtypes); every symbol include/q4b200.h declares
@@ -50,6 +53,7 @@ SIGNATURES = {
     "q4b_argmax_advance": (_I, [_P, _I, _I, _P, _P, _P, _Z, _P]),
     "q4b_blockdot_q4_0_q8_1": (_I, [_P, _P, _P, _I, _I, _I, _I, _P, _P]),
     "q4b_gemv_q4_0_tc": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _P, _P]),
+    "q4b_rmsnorm_gemv_q4_0_tc": (_I, [_P, _P, _P, _P, _F, _P, _P, _I, _I, _I, _P, _P]),
     "q4b_mmq_q4_0_q8_1": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P]),
     "q4b_quant_q8_1": (_I, [_P, _P, _P, _P, _I, _I, _P]),
     "q4b_rmsnorm_q8_1": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _F, _P]),

@@ -20,10 +20,10 @@ constexpr int AT = 128;        // threads per CTA
 constexpr int NW = AT / 32;
 
 template <int HD, int GRP>
-__global__ void __launch_bounds__(AT) attn_decode_kernel(const __half* __restrict__ qkv, const float* __restrict__ cosT,
-                                                         const float* __restrict__ sinT, const int64_t* __restrict__ posp,
-                                                         __half* __restrict__ kc, __half* __restrict__ vc,
-                                                         __half* __restrict__ out, int NH, int NKV, int max_len,
+__global__ void __launch_bounds__(AT) attn_decode_kernel(const __half* qkv, const float* __restrict__ cosT,
+                                                         const float* __restrict__ sinT, const int64_t* posp,
+                                                         __half* kc, __half* vc,
+                                                         __half* out, int NH, int NKV, int max_len,
                                                          float scale, unsigned* cnt, float* part_ml, float* part_o, int NC) {
   constexpr int HALF = HD / 2;
   constexpr int LPR = HD / 8;          // lanes per K/V row in the P.V pass (16-byte loads)
@@ -37,6 +37,7 @@ __global__ void __launch_bounds__(AT) attn_decode_kernel(const __half* __restric
   __shared__ float stat[GRP][2];
   __shared__ bool last;
 
+  pdl_launch_dependents();
   pdl_wait();
   const int b = blockIdx.z, kvh = blockIdx.y, chunk = blockIdx.x;
   const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
@@ -94,7 +95,7 @@ __global__ void __launch_bounds__(AT) attn_decode_kernel(const __half* __restric
         const uint4* kr = reinterpret_cast<const uint4*>(kbase + (size_t)j * HD);
         uint4 kv[HD / 8];
 #pragma unroll
-        for (int i = 0; i < HD / 8; ++i) kv[i] = __ldg(kr + i);
+        for (int i = 0; i < HD / 8; ++i) kv[i] = kr[i];
 #pragma unroll
         for (int i = 0; i < HD / 8; ++i) {
           const uint32_t w[4] = {kv[i].x, kv[i].y, kv[i].z, kv[i].w};
@@ -167,7 +168,7 @@ __global__ void __launch_bounds__(AT) attn_decode_kernel(const __half* __restric
     for (int u = 0; u < UNR; ++u) {
       const int jl = 32 * warp + (it0 + u) * PPI + psub, j = c0 + jl;
       vv[u] = make_uint4(0u, 0u, 0u, 0u);
-      if (j < p) vv[u] = __ldg(reinterpret_cast<const uint4*>(vbase + (size_t)j * HD + d0));
+      if (j < p) vv[u] = *reinterpret_cast<const uint4*>(vbase + (size_t)j * HD + d0);
     }
 #pragma unroll
     for (int u = 0; u < UNR; ++u) {
@@ -272,8 +273,8 @@ int dispatch_grp(int grp, dim3 grid, cudaStream_t st, const __half* qkv, const f
                  unsigned* cnt, float* ml, float* po, int NC) {
 #define Q4B_ATTN_CASE(G)                                                                                         \
   case G:                                                                                                        \
-    attn_decode_kernel<HD, G><<<grid, AT, 0, st>>>(qkv, cosT, sinT, pos, kc, vc, out, NH, NKV, max_len, scale, cnt, \
-                                                   ml, po, NC);                                                  \
+    launch_pdl(attn_decode_kernel<HD, G>, grid, dim3(AT), 0, st, qkv, cosT, sinT, pos, kc, vc, out, NH, NKV, max_len, \
+               scale, cnt, ml, po, NC);                                                                          \
     return Q4B_OK;
   switch (grp) {
     Q4B_ATTN_CASE(1) Q4B_ATTN_CASE(2) Q4B_ATTN_CASE(3) Q4B_ATTN_CASE(4) Q4B_ATTN_CASE(5) Q4B_ATTN_CASE(6)

@@ -66,7 +66,7 @@ __global__ void __launch_bounds__(128) blockdot_kernel(const uint4* __restrict__
     if (t < NT * 2) {
       const int n = t >> 1, kc = t & 1, gn = n0 + n;
       uint4 v = make_uint4(0u, 0u, 0u, 0u);
-      if (gn < P) v = __ldg(reinterpret_cast<const uint4*>(xq + (size_t)gn * K + kb * 32 + kc * 16));
+      if (gn < P) v = *reinterpret_cast<const uint4*>(xq + (size_t)gn * K + kb * 32 + kc * 16);
       uint32_t e0, o0, e1, o1;
       tc::permute_bytes(v.x, v.y, e0, o0);
       tc::permute_bytes(v.z, v.w, e1, o1);

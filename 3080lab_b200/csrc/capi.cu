@@ -43,7 +43,7 @@ size_t head_workspace(int);
 int head_f16_argmax(const void*, const void*, float*, int, int, int64_t*, int64_t*, void*, size_t, cudaStream_t);
 int blockdot(const void*, const void*, int32_t*, int, int, int, int, uint32_t*, cudaStream_t);
 int mmq_stream(const void*, const void*, const void*, const void*, void*, const void*, int, int, int, int, int, int, uint32_t*,
-               cudaStream_t);
+               cudaStream_t, const float* norm_w = nullptr, float eps = 0.f);
 int quant_q8_1(const void*, void*, void*, void*, int, int, cudaStream_t);
 int rmsnorm_q8_1(const float*, const float*, void*, void*, void*, void*, int, int, float, cudaStream_t);
 
@@ -123,6 +123,12 @@ int q4b_gemv_q4_0_tc(const void* W, const void* Sc, const void* X, void* Y, cons
   return mmq_stream(W, Sc, X, nullptr, Y, AUX, N, K, 1, x_dtype == Q4B_X_F16 ? 0 : 1, epilogue, ldy, status, S(stream));
 }
 
+int q4b_rmsnorm_gemv_q4_0_tc(const void* W, const void* Sc, const float* h, const float* norm_w, float eps, void* Y,
+                             const void* AUX, int N, int K, int epilogue, uint32_t* status, q4b_stream_t stream) {
+  const int ldy = epilogue == Q4B_EPI_SWIGLU ? N / 2 : N;
+  return mmq_stream(W, Sc, h, nullptr, Y, AUX, N, K, 1, 3, epilogue, ldy, status, S(stream), norm_w, eps);
+}
+
 int q4b_mmq_q4_0_q8_1(const void* W, const void* Sc, const void* xq, const void* xd, void* Y, const void* AUX, int N, int K,
                       int P, int epilogue, int ldy, uint32_t* status, q4b_stream_t stream) {
   if (P < 1 || P > 32) return fail(Q4B_E_SHAPE, "mmq_q4_0_q8_1: 1..32 activation rows supported by the streaming kernel");
@@ -142,6 +148,21 @@ int q4b_decode_step(const q4b_decode_desc* d, q4b_stream_t stream) {
   if (!d || !d->layer) return fail(Q4B_E_ARG, "decode_step: null descriptor");
   cudaStream_t st = S(stream);
   const int H = d->hidden, QR = d->n_heads * d->head_dim;
+  const bool tcp = (d->flags & Q4B_STEP_TENSOR_CORE) && d->status;
+  // one linear: tensor-core kernel when its shape allows, the CUDA-core GEMV otherwise
+  auto lin = [&](const q4b_linear& L, const void* X, void* Y, const void* AUX, int epi) -> int {
+    if (tcp && (L.K % 256) == 0)
+      return mmq_stream(L.W, L.S, X, nullptr, Y, AUX, L.N, L.K, 1, 0, epi, epi == Q4B_EPI_SWIGLU ? L.N / 2 : L.N, d->status, st);
+    return gemv_q4_0(L.W, L.S, X, Y, AUX, L.N, L.K, epi, Q4B_X_F16, st);
+  };
+  // RMSNorm followed by a linear: one launch on the tensor-core path (the norm is computed while staging the operand)
+  auto norm_lin = [&](const float* nw, const q4b_linear& L, void* Y, const void* AUX, int epi) -> int {
+    if (tcp && (L.K % 256) == 0)
+      return mmq_stream(L.W, L.S, d->h, nullptr, Y, AUX, L.N, L.K, 1, 3, epi, epi == Q4B_EPI_SWIGLU ? L.N / 2 : L.N, d->status,
+                        st, nw, d->eps);
+    int rc = rmsnorm(d->h, nw, d->x, 1, H, d->eps, st);
+    return rc != Q4B_OK ? rc : gemv_q4_0(L.W, L.S, d->x, Y, AUX, L.N, L.K, epi, Q4B_X_F16, st);
+  };
 #define Q4B_TRY(call)            \
   do {                           \
     int rc_ = (call);            \
@@ -150,21 +171,19 @@ int q4b_decode_step(const q4b_decode_desc* d, q4b_stream_t stream) {
   Q4B_TRY(embed(d->embed, d->tok, d->h, 1, H, d->vocab, st));
   for (int i = 0; i < d->layers; ++i) {
     const q4b_layer& L = d->layer[i];
-    Q4B_TRY(rmsnorm(d->h, L.ln1, d->x, 1, H, d->eps, st));
-    Q4B_TRY(gemv_q4_0(L.qkv.W, L.qkv.S, d->x, d->qkv, L.qkv_bias, L.qkv.N, L.qkv.K, Q4B_EPI_BIASF, Q4B_X_F16, st));
+    Q4B_TRY(norm_lin(L.ln1, L.qkv, d->qkv, L.qkv_bias, Q4B_EPI_BIASF));
     Q4B_TRY(attn_decode(d->qkv, d->cosT, d->sinT, d->pos, L.kc, L.vc, d->att, 1, d->n_heads, d->n_kv_heads, d->head_dim,
                         d->max_len, d->scale, d->attn_ws, d->attn_ws_bytes, st));
-    Q4B_TRY(gemv_q4_0(L.o.W, L.o.S, d->att, d->h, nullptr, L.o.N, L.o.K, Q4B_EPI_RESID, Q4B_X_F16, st));
-    Q4B_TRY(rmsnorm(d->h, L.ln2, d->x, 1, H, d->eps, st));
-    Q4B_TRY(gemv_q4_0(L.gu.W, L.gu.S, d->x, d->act, nullptr, L.gu.N, L.gu.K, Q4B_EPI_SWIGLU, Q4B_X_F16, st));
-    Q4B_TRY(gemv_q4_0(L.down.W, L.down.S, d->act, d->h, nullptr, L.down.N, L.down.K, Q4B_EPI_RESID, Q4B_X_F16, st));
+    Q4B_TRY(lin(L.o, d->att, d->h, nullptr, Q4B_EPI_RESID));
+    Q4B_TRY(norm_lin(L.ln2, L.gu, d->act, nullptr, Q4B_EPI_SWIGLU));
+    Q4B_TRY(lin(L.down, d->act, d->h, nullptr, Q4B_EPI_RESID));
   }
   (void)QR;
-  Q4B_TRY(rmsnorm(d->h, d->norm, d->x, 1, H, d->eps, st));
   if (d->head.W) {
-    Q4B_TRY(gemv_q4_0(d->head.W, d->head.S, d->x, d->logits, nullptr, d->head.N, d->head.K, Q4B_EPI_LOGITS, Q4B_X_F16, st));
+    Q4B_TRY(norm_lin(d->norm, d->head, d->logits, nullptr, Q4B_EPI_LOGITS));
     Q4B_TRY(argmax_advance(d->logits, 1, d->vocab, d->tok, d->pos, d->head_ws, d->head_ws_bytes, st));
   } else {
+    Q4B_TRY(rmsnorm(d->h, d->norm, d->x, 1, H, d->eps, st));
     Q4B_TRY(head_f16_argmax(d->embed, d->x, d->logits, d->vocab, H, d->tok, d->pos, d->head_ws, d->head_ws_bytes, st));
   }
 #undef Q4B_TRY

@@ -29,11 +29,11 @@ __device__ __forceinline__ void load_x(XBlock<XF32>& xb, const void* X, int j) {
   if (XF32) {
     const uint4* p = reinterpret_cast<const uint4*>(X) + (size_t)j * 8;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) xb.v[i] = __ldg(p + i);
+    for (int i = 0; i < 8; ++i) xb.v[i] = p[i];
   } else {
     const uint4* p = reinterpret_cast<const uint4*>(X) + (size_t)j * 4;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) xb.v[i] = __ldg(p + i);
+    for (int i = 0; i < 4; ++i) xb.v[i] = p[i];
   }
 }
 
@@ -63,9 +63,11 @@ __device__ __forceinline__ void widen_x(const XBlock<XF32>& xb, float* xs) {
 
 template <int EPI, bool XF32, int TW>
 __global__ void __launch_bounds__(256) gemv_q4_0_kernel(const uint4* __restrict__ W, const __half* __restrict__ S,
-                                                        const void* __restrict__ X, void* __restrict__ Y,
+                                                        const void* X, void* Y,
                                                         const void* __restrict__ AUX, int N, int K, int KS, int teams) {
   __shared__ float red[MAX_TEAMS][MAX_KS][R];
+  pdl_launch_dependents();
+  pdl_wait();
   const int KB = K >> 5;
   const int per_team = KS * TW;
   const int team = threadIdx.x / per_team, r_in = threadIdx.x - team * per_team;
@@ -174,9 +176,9 @@ template <int EPI, bool XF32>
 void launch_tw(const Plan& p, dim3 grid, dim3 block, cudaStream_t st, const uint4* W, const __half* S, const void* X,
                void* Y, const void* AUX, int N, int K) {
   if (p.tw == 16)
-    gemv_q4_0_kernel<EPI, XF32, 16><<<grid, block, 0, st>>>(W, S, X, Y, AUX, N, K, p.ks, p.teams);
+    launch_pdl(gemv_q4_0_kernel<EPI, XF32, 16>, grid, block, 0, st, W, S, X, Y, AUX, N, K, p.ks, p.teams);
   else
-    gemv_q4_0_kernel<EPI, XF32, 32><<<grid, block, 0, st>>>(W, S, X, Y, AUX, N, K, p.ks, p.teams);
+    launch_pdl(gemv_q4_0_kernel<EPI, XF32, 32>, grid, block, 0, st, W, S, X, Y, AUX, N, K, p.ks, p.teams);
 }
 
 template <int EPI>

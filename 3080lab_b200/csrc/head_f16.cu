@@ -32,7 +32,7 @@ __device__ __forceinline__ void arg_warp(float& v, int& idx) {
 }
 
 template <int NCH, int RW>   // NCH 16-byte column chunks per lane (>= ceil(H / 256)), RW rows per warp step
-__global__ void __launch_bounds__(HT, 1) head_f16_kernel(const uint4* __restrict__ E, const uint4* __restrict__ x,
+__global__ void __launch_bounds__(HT, 1) head_f16_kernel(const uint4* __restrict__ E, const uint4* x,
                                                          float* __restrict__ logits, int V, int H, int64_t* tok,
                                                          int64_t* pos, float* partv, int* parti, unsigned* cnt) {
   __shared__ float bv[HW];
@@ -40,13 +40,14 @@ __global__ void __launch_bounds__(HT, 1) head_f16_kernel(const uint4* __restrict
   __shared__ bool last;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int HC = H >> 3;                                  // 16-byte chunks per row
+  pdl_launch_dependents();
   pdl_wait();
   float xf[NCH][8];
 #pragma unroll
   for (int c = 0; c < NCH; ++c) {
     const int ci = lane + 32 * c;
     uint4 v = make_uint4(0u, 0u, 0u, 0u);
-    if (ci < HC) v = __ldg(x + ci);
+    if (ci < HC) v = x[ci];
     const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
@@ -152,8 +153,8 @@ int head_f16_argmax(const void* E, const void* x, float* logits, int V, int H, i
   const int need = (H / 8 + 31) / 32;
 #define Q4B_HEAD_CASE(C, RWS)                                                                         \
   if (need <= C) {                                                                                    \
-    head_f16_kernel<C, RWS><<<grid, HT, 0, st>>>(e, xv, logits, V, H, tok, pos, partv, parti, cnt);   \
-    return check_launch("head_f16_argmax");                                                           \
+    return check_launch(launch_pdl(head_f16_kernel<C, RWS>, dim3(grid), dim3(HT), 0, st, e, xv, logits, V, H, tok, pos,     \
+                                   partv, parti, cnt), "head_f16_argmax");                                                 \
   }
   Q4B_HEAD_CASE(1, 4) Q4B_HEAD_CASE(2, 4) Q4B_HEAD_CASE(4, 4) Q4B_HEAD_CASE(6, 4) Q4B_HEAD_CASE(8, 4) Q4B_HEAD_CASE(16, 1)
 #undef Q4B_HEAD_CASE

@@ -34,7 +34,7 @@ namespace q4b {
 
 namespace {
 
-constexpr int MODE_X16 = 0, MODE_X32 = 1, MODE_Q8 = 2;
+constexpr int MODE_X16 = 0, MODE_X32 = 1, MODE_Q8 = 2, MODE_NORM = 3;
 constexpr int ROWS = 128;
 constexpr size_t MAX_DYN_SMEM = 226 * 1024;   // 227 KB per CTA on sm_100 minus the static barriers
 
@@ -43,6 +43,8 @@ struct StreamArgs {
   const __half* S;      // [N, K/32]
   const void* X;        // exact modes: fp16 / fp32 [K]; Q8 mode: int8 [cols, K]
   const __half* XD;     // Q8 mode: fp16 [cols, K/32]
+  const float* NW;      // norm mode: RMSNorm weights fp32 [K] (X is then the fp32 residual stream)
+  float eps;
   void* Y;
   const void* AUX;
   uint32_t* status;
@@ -79,7 +81,7 @@ __device__ __forceinline__ uint32_t b_offset(int kbl, int n, int pos) {
 template <int MODE, int NT>
 __global__ void __launch_bounds__(ROWS) mmq_stream_kernel(const StreamArgs a) {
   constexpr int G = NT <= 16 ? 8 : 4;                  // k-blocks per MMA batch
-  constexpr int NL = MODE == MODE_X16 ? 3 : 4;         // digits in exact mode
+  constexpr int NL = (MODE == MODE_X16 || MODE == MODE_NORM) ? 3 : 4;   // digits in exact mode (fp16-valued x: 3)
   constexpr int NACC = MODE == MODE_Q8 ? NT : 1;
   constexpr uint32_t A_COLS = 2 * G * 8, D_COLS = 2 * G * NT;
   constexpr uint32_t TCOLS = (A_COLS + D_COLS) <= 128 ? 128 : ((A_COLS + D_COLS) <= 256 ? 256 : 512);
@@ -135,7 +137,7 @@ __global__ void __launch_bounds__(ROWS) mmq_stream_kernel(const StreamArgs a) {
     for (int c = t; c < NT * per; c += ROWS) {
       const int n = c / per, r = c - n * per, kbl = r >> 1, kc = r & 1;
       uint4 v = make_uint4(0u, 0u, 0u, 0u);
-      if (n < a.cols) v = __ldg(reinterpret_cast<const uint4*>(xq + (size_t)n * a.K + (size_t)(kb0 + kbl) * 32 + kc * 16));
+      if (n < a.cols) v = *reinterpret_cast<const uint4*>(xq + (size_t)n * a.K + (size_t)(kb0 + kbl) * 32 + kc * 16);
       uint32_t e0, o0, e1, o1;
       tc::permute_bytes(v.x, v.y, e0, o0);
       tc::permute_bytes(v.z, v.w, e1, o1);
@@ -146,30 +148,73 @@ __global__ void __launch_bounds__(ROWS) mmq_stream_kernel(const StreamArgs a) {
       xs[kbl * NT + n] = n < a.cols ? __half2float(a.XD[(size_t)n * KB + kb0 + kbl]) : 0.f;
     }
   } else {
-    // exact mode: warp <-> k-block, lane <-> element.  X_i = rint(x_i * 2^-e) with |X_i| < 2^(8 NL - 2), split into
-    // signed base-256 digits, digit j -> column j.
+    // exact mode: 8 lanes <-> one k-block, 4 consecutive elements per lane.  X_i = rint(x_i * 2^-e) with
+    // |X_i| < 2^(8 NL - 2), split into signed base-256 digits, digit j -> column j.
     for (int c = t; c < nkb * 64; c += ROWS)            // columns NL..7 must read as zero
       *reinterpret_cast<uint32_t*>(sB + (size_t)c * 4) = 0u;
-    __syncthreads();
-    for (int kbl = warp; kbl < nkb; kbl += ROWS / 32) {
-      const int k = (kb0 + kbl) * 32 + lane;
-      const float x = MODE == MODE_X16 ? __half2float(reinterpret_cast<const __half*>(a.X)[k])
-                                       : reinterpret_cast<const float*>(a.X)[k];
-      const float amax = warp_max(fabsf(x));
+    float rnorm = 1.f;
+    if (MODE == MODE_NORM) {
+      // RMSNorm of the whole residual row (every CTA needs the full sum of squares), as RMSNORM_F32W_1P
+      // (lab/qwen_kernels.py:683-705): r = rsqrt(sum(v^2) / K + eps); x = round16(v * r * w).
+      float* red = xs + a.gps * 8;                      // 4 floats behind the block scales
+      const float4* hv = reinterpret_cast<const float4*>(a.X);
+      float ss = 0.f;
+      for (int i = t; i < (a.K >> 2); i += ROWS) {
+        const float4 v = hv[i];
+        ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+      }
+      ss = warp_sum(ss);
+      if (lane == 0) red[warp] = ss;
+      __syncthreads();
+      rnorm = rsqrtf((red[0] + red[1] + red[2] + red[3]) / (float)a.K + a.eps);
+    } else {
+      __syncthreads();
+    }
+    const int sub = t & 7;
+    for (int kbl = t >> 3; kbl < nkb; kbl += ROWS / 8) {
+      const int k = (kb0 + kbl) * 32 + sub * 4;
+      float x[4];
+      if (MODE == MODE_X16) {
+        const uint2 raw = *reinterpret_cast<const uint2*>(reinterpret_cast<const __half*>(a.X) + k);
+        const float2 p = __half22float2(*reinterpret_cast<const __half2*>(&raw.x));
+        const float2 q = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
+        x[0] = p.x; x[1] = p.y; x[2] = q.x; x[3] = q.y;
+      } else {
+        const float4 v = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(a.X) + k);
+        x[0] = v.x; x[1] = v.y; x[2] = v.z; x[3] = v.w;
+        if (MODE == MODE_NORM) {
+          const float4 w = __ldg(reinterpret_cast<const float4*>(a.NW + k));
+          x[0] = __half2float(__float2half_rn(x[0] * rnorm * w.x));
+          x[1] = __half2float(__float2half_rn(x[1] * rnorm * w.y));
+          x[2] = __half2float(__float2half_rn(x[2] * rnorm * w.z));
+          x[3] = __half2float(__float2half_rn(x[3] * rnorm * w.w));
+        }
+      }
+      float amax = fmaxf(fmaxf(fabsf(x[0]), fabsf(x[1])), fmaxf(fabsf(x[2]), fabsf(x[3])));
+#pragma unroll
+      for (int o = 4; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+      const bool live = amax > 0.f && amax < INFINITY;
       int e = (__float_as_int(amax) >> 23) & 0xFF;      // biased exponent of the block maximum
       e = max(e, 8 * NL);                               // tiny blocks: keep the scale a normal float
       // 2^(8 NL - 3) / 2^(e - 127): |x| < 2^(e - 126) maps below 2^(8 NL - 2)
       const float inv = __int_as_float((127 + (8 * NL - 3) - (e - 127)) << 23);
-      const float scl = __int_as_float((127 - (8 * NL - 3) + (e - 127)) << 23);
-      int X = (amax > 0.f && amax < INFINITY) ? __float2int_rn(x * inv) : 0;
-      const int pos = perm_pos(lane);
+      int X[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) X[j] = live ? __float2int_rn(x[j] * inv) : 0;
+      // elements 4 sub + {0, 2} are adjacent operand bytes, and so are 4 sub + {1, 3} (see perm_pos)
+      const int pos02 = 8 * (sub >> 1) + 2 * (sub & 1), pos13 = pos02 + 4;
 #pragma unroll
       for (int j = 0; j < NL; ++j) {
-        const int dgt = (int)(int8_t)(X & 0xFF);
-        sB[b_offset<NT>(kbl, j, pos)] = (uint8_t)dgt;
-        X = (X - dgt) >> 8;
+        int dg[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          dg[u] = (int)(int8_t)(X[u] & 0xFF);
+          X[u] = (X[u] - dg[u]) >> 8;
+        }
+        *reinterpret_cast<uint16_t*>(sB + b_offset<NT>(kbl, j, pos02)) = (uint16_t)((dg[0] & 0xFF) | ((dg[2] & 0xFF) << 8));
+        *reinterpret_cast<uint16_t*>(sB + b_offset<NT>(kbl, j, pos13)) = (uint16_t)((dg[1] & 0xFF) | ((dg[3] & 0xFF) << 8));
       }
-      if (lane == 0) xs[kbl] = (amax > 0.f && amax < INFINITY) ? scl : 0.f;
+      if (sub == 0) xs[kbl] = live ? __int_as_float((127 - (8 * NL - 3) + (e - 127)) << 23) : 0.f;
     }
   }
   tc::fence_async_smem();
@@ -192,30 +237,44 @@ __global__ void __launch_bounds__(ROWS) mmq_stream_kernel(const StreamArgs a) {
     const int slot = bi & 1;
     ok = tc::mbar_wait(&bar_mma[slot], (uint32_t)(bi >> 1) & 1u) && ok;
     tc::fence_after_sync();
-#pragma unroll 2
-    for (int j = 0; j < G; ++j) {
-      const int kbl = bi * G + j;
-      const float dw = __half2float(myS[kbl]) * 0.0625f;           // 1/16 undoes the 16*(q-8) operand scaling
-      const uint32_t dcol = tmem_d + lane_off + (uint32_t)((slot * G + j) * NT);
-      if (MODE == MODE_Q8) {
+    if (MODE == MODE_Q8) {
+      constexpr int SB = NT <= 8 ? 8 : (NT == 16 ? 4 : 2);       // k-blocks whose accumulators are in flight together
+#pragma unroll 1
+      for (int j0 = 0; j0 < G; j0 += SB) {
+        uint32_t d[SB][NT];
 #pragma unroll
-        for (int c0 = 0; c0 < NT; c0 += 8) {
-          uint32_t d[8];
-          tc::tmem_ld8(dcol + c0, d);
-          tc::tmem_wait_ld();
-          const float4 s0 = *reinterpret_cast<const float4*>(xs + kbl * NT + c0);
-          const float4 s1 = *reinterpret_cast<const float4*>(xs + kbl * NT + c0 + 4);
-          const float sx[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+        for (int j = 0; j < SB; ++j) {
+          const uint32_t dcol = tmem_d + lane_off + (uint32_t)((slot * G + j0 + j) * NT);
 #pragma unroll
-          for (int n = 0; n < 8; ++n) acc[(c0 + n) % NACC] = fmaf(dw * sx[n], (float)(int32_t)d[n], acc[(c0 + n) % NACC]);
+          for (int c0 = 0; c0 < NT; c0 += 8) tc::tmem_ld8(dcol + c0, &d[j][c0]);
         }
-      } else {
-        uint32_t d[8];
-        tc::tmem_ld8(dcol, d);
         tc::tmem_wait_ld();
-        float f = fmaf(256.f, (float)(int32_t)d[1], (float)(int32_t)d[0]);
-        f = fmaf(65536.f, (float)(int32_t)d[2], f);
-        if (NL == 4) f = fmaf(16777216.f, (float)(int32_t)d[3], f);
+#pragma unroll
+        for (int j = 0; j < SB; ++j) {
+          const int kbl = bi * G + j0 + j;
+          const float dw = __half2float(myS[kbl]) * 0.0625f;     // 1/16 undoes the 16*(q-8) operand scaling
+#pragma unroll
+          for (int c0 = 0; c0 < NT; c0 += 4) {
+            const float4 sx = *reinterpret_cast<const float4*>(xs + kbl * NT + c0);
+            acc[(c0 + 0) % NACC] = fmaf(dw * sx.x, (float)(int32_t)d[j][c0 + 0], acc[(c0 + 0) % NACC]);
+            acc[(c0 + 1) % NACC] = fmaf(dw * sx.y, (float)(int32_t)d[j][c0 + 1], acc[(c0 + 1) % NACC]);
+            acc[(c0 + 2) % NACC] = fmaf(dw * sx.z, (float)(int32_t)d[j][c0 + 2], acc[(c0 + 2) % NACC]);
+            acc[(c0 + 3) % NACC] = fmaf(dw * sx.w, (float)(int32_t)d[j][c0 + 3], acc[(c0 + 3) % NACC]);
+          }
+        }
+      }
+    } else {
+      uint32_t d[G][4];
+#pragma unroll
+      for (int j = 0; j < G; ++j) tc::tmem_ld4(tmem_d + lane_off + (uint32_t)((slot * G + j) * NT), d[j]);
+      tc::tmem_wait_ld();
+#pragma unroll
+      for (int j = 0; j < G; ++j) {
+        const int kbl = bi * G + j;
+        const float dw = __half2float(myS[kbl]) * 0.0625f;
+        float f = fmaf(256.f, (float)(int32_t)d[j][1], (float)(int32_t)d[j][0]);
+        f = fmaf(65536.f, (float)(int32_t)d[j][2], f);
+        if (NL == 4) f = fmaf(16777216.f, (float)(int32_t)d[j][3], f);
         acc[0] = fmaf(dw * xs[kbl], f, acc[0]);
       }
     }
@@ -323,7 +382,7 @@ bool plan(int N, int K, int nt, Geometry& g) {
     if ((ks - 1) * gps >= GT) continue;                 // an empty slice
     if (smem_bytes(gps, nt) > MAX_DYN_SMEM) continue;
     best = ks;
-    if ((long)tiles * ks >= (sms * 3) / 5) break;       // enough CTAs to occupy the machine
+    if ((long)tiles * ks >= (long)sms * 3 / 2) break;   // enough CTAs for two per SM on most of the machine
   }
   if (best < 0) return false;
   g.ksplit = best;
@@ -385,11 +444,14 @@ int launch_nt(int nt, const StreamArgs& a, const Geometry& g, cudaStream_t st) {
 
 }  // namespace
 
-// mode: 0 exact fp16 x, 1 exact fp32 x, 2 Q8_1.  cols: 1 for the exact modes, 1..32 sequences for Q8_1.
+// mode: 0 exact fp16 x, 1 exact fp32 x, 2 Q8_1, 3 exact with RMSNorm of the fp32 row X fused in front.
+// cols: 1 for the exact modes, 1..32 sequences for Q8_1.
 int mmq_stream(const void* W, const void* S, const void* X, const void* XD, void* Y, const void* AUX, int N, int K,
-               int cols, int mode, int epilogue, int ldy, uint32_t* status, cudaStream_t st) {
+               int cols, int mode, int epilogue, int ldy, uint32_t* status, cudaStream_t st, const float* norm_w,
+               float eps) {
   if (N <= 0 || K <= 0 || (K % 256)) return fail(Q4B_E_SHAPE, "mmq_stream: N > 0 and K a positive multiple of 256 required");
-  if (mode < 0 || mode > 2) return fail(Q4B_E_ARG, "mmq_stream: unknown mode");
+  if (mode < 0 || mode > 3) return fail(Q4B_E_ARG, "mmq_stream: unknown mode");
+  if (mode == MODE_NORM && (!norm_w || !aligned16(norm_w))) return fail(Q4B_E_ALIGN, "mmq_stream: norm mode needs 16-byte aligned weights");
   if (epilogue < Q4B_EPI_STORE || epilogue > Q4B_EPI_LOGITS) return fail(Q4B_E_ARG, "mmq_stream: unknown epilogue");
   if (cols < 1 || cols > 32 || (mode != MODE_Q8 && cols != 1)) return fail(Q4B_E_SHAPE, "mmq_stream: 1..32 columns (1 in exact mode)");
   if (epilogue == Q4B_EPI_SWIGLU && (N % 2)) return fail(Q4B_E_SHAPE, "mmq_stream: swiglu needs an even row count");
@@ -405,6 +467,8 @@ int mmq_stream(const void* W, const void* S, const void* X, const void* XD, void
   a.S = reinterpret_cast<const __half*>(S);
   a.X = X;
   a.XD = reinterpret_cast<const __half*>(XD);
+  a.NW = norm_w;
+  a.eps = eps;
   a.Y = Y;
   a.AUX = AUX;
   a.status = status;
@@ -417,6 +481,7 @@ int mmq_stream(const void* W, const void* S, const void* X, const void* XD, void
   a.ksplit = g.ksplit;
   if (mode == MODE_X16) return launch_nt<MODE_X16>(nt, a, g, st);
   if (mode == MODE_X32) return launch_nt<MODE_X32>(nt, a, g, st);
+  if (mode == MODE_NORM) return launch<MODE_NORM, 8>(a, g, st);
   return launch_nt<MODE_Q8>(nt, a, g, st);
 }
 

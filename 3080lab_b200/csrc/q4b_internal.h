@@ -21,9 +21,40 @@ inline int check_launch(const char* where) {
   return Q4B_OK;
 }
 
+inline int check_launch(cudaError_t e, const char* where) {
+  if (e != cudaSuccess) {
+    set_cuda_error(e, where);
+    return Q4B_E_CUDA;
+  }
+  return check_launch(where);
+}
+
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 int sm_count();
+
+// Launch with the programmatic-dependent-launch attribute: the kernel may start while its predecessor in the stream is
+// still running, so it must call pdl_wait() before it touches anything the predecessor writes (every kernel in this
+// library does so before its first dependent access).  Captured into CUDA graphs as a programmatic edge.
+// Consequence for loads: a buffer written by an earlier kernel of the chain is NOT read-only for the lifetime of this
+// grid (the grid may have been resident before the write), so it must never be read through the non-coherent path
+// (__ldg / ld.global.nc, or a const __restrict__ pointer the compiler may route there).  Only weights and tables are.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+
+inline int check_launch(cudaError_t e, const char* where);
 
 // ---- device helpers -------------------------------------------------------------------------------------------
 #ifdef __CUDACC__

@@ -38,8 +38,8 @@ __device__ __forceinline__ void quant_block4(const float x[4], int8_t* q_out, __
   }
 }
 
-__global__ void __launch_bounds__(256) quant_q8_1_kernel(const __half* __restrict__ x, int8_t* __restrict__ xq,
-                                                         __half* __restrict__ xd, __half* __restrict__ xsum, size_t nblk) {
+__global__ void __launch_bounds__(256) quant_q8_1_kernel(const __half* x, int8_t* xq, __half* xd, __half* xsum, size_t nblk) {
+  pdl_launch_dependents();
   pdl_wait();
   const size_t gid = (size_t)blockIdx.x * 256 + threadIdx.x;
   const size_t blk = gid >> 3;
@@ -54,11 +54,10 @@ __global__ void __launch_bounds__(256) quant_q8_1_kernel(const __half* __restric
 }
 
 // One CTA of H/4 threads (<= 1024) per row: RMSNorm in registers, round to fp16, quantise.
-__global__ void __launch_bounds__(1024) rmsnorm_q8_1_kernel(const float* __restrict__ h, const float* __restrict__ w,
-                                                            int8_t* __restrict__ xq, __half* __restrict__ xd,
-                                                            __half* __restrict__ xsum, __half* __restrict__ x16, int H,
-                                                            float eps) {
+__global__ void __launch_bounds__(1024) rmsnorm_q8_1_kernel(const float* h, const float* __restrict__ w, int8_t* xq,
+                                                            __half* xd, __half* xsum, __half* x16, int H, float eps) {
   __shared__ float part[32];
+  pdl_launch_dependents();
   pdl_wait();
   const int row = blockIdx.x, t = threadIdx.x, i0 = 4 * t;
   const float4 hv = *reinterpret_cast<const float4*>(h + (size_t)row * H + i0);
@@ -92,8 +91,8 @@ int quant_q8_1(const void* x, void* xq, void* xd, void* xsum, int rows, int K, c
     return fail(Q4B_E_ALIGN, "quant_q8_1: null or misaligned pointer");
   const size_t nblk = (size_t)rows * (K / 32);
   const size_t threads = nblk * 8;
-  quant_q8_1_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, st>>>((const __half*)x, (int8_t*)xq, (__half*)xd, (__half*)xsum, nblk);
-  return check_launch("quant_q8_1");
+  return check_launch(launch_pdl(quant_q8_1_kernel, dim3((unsigned)((threads + 255) / 256)), dim3(256), 0, st, (const __half*)x,
+                                 (int8_t*)xq, (__half*)xd, (__half*)xsum, nblk), "quant_q8_1");
 }
 
 int rmsnorm_q8_1(const float* h, const float* w, void* xq, void* xd, void* xsum, void* x16, int rows, int H, float eps,
@@ -101,8 +100,8 @@ int rmsnorm_q8_1(const float* h, const float* w, void* xq, void* xd, void* xsum,
   if (rows <= 0 || H <= 0 || (H % 128) || H > 4096) return fail(Q4B_E_SHAPE, "rmsnorm_q8_1: H must be a multiple of 128, at most 4096");
   if (!h || !w || !xq || !xd || !aligned16(h) || !aligned16(w) || (reinterpret_cast<uintptr_t>(xq) & 3u))
     return fail(Q4B_E_ALIGN, "rmsnorm_q8_1: null or misaligned pointer");
-  rmsnorm_q8_1_kernel<<<rows, H / 4, 0, st>>>(h, w, (int8_t*)xq, (__half*)xd, (__half*)xsum, (__half*)x16, H, eps);
-  return check_launch("rmsnorm_q8_1");
+  return check_launch(launch_pdl(rmsnorm_q8_1_kernel, dim3(rows), dim3(H / 4), 0, st, h, w, (int8_t*)xq, (__half*)xd,
+                                 (__half*)xsum, (__half*)x16, H, eps), "rmsnorm_q8_1");
 }
 
 }  // namespace q4b

@@ -6,8 +6,8 @@ namespace q4b {
 namespace {
 
 // h[row] = float(E[tok[row]]), one CTA per row.  Reference: EMBED_F32 (lab/qwen_kernels.py:284-290) with an fp16 table.
-__global__ void __launch_bounds__(256) embed_kernel(const __half* __restrict__ E, const int64_t* __restrict__ tok,
-                                                    float* __restrict__ h, int H, int V) {
+__global__ void __launch_bounds__(256) embed_kernel(const __half* __restrict__ E, const int64_t* tok, float* h, int H, int V) {
+  pdl_launch_dependents();
   pdl_wait();
   long long t = tok[blockIdx.x];
   t = t < 0 ? 0 : (t >= V ? V - 1 : t);
@@ -20,9 +20,10 @@ __global__ void __launch_bounds__(256) embed_kernel(const __half* __restrict__ E
 // Reference: RMSNORM_F32W_1P (lab/qwen_kernels.py:683-705): values stay in registers between the two passes,
 // product order (v * r) * w, a single rounding at the store.
 constexpr int RMS_T = 256, RMS_MAXV = 16;   // up to 4096 columns in registers; wider rows re-read h
-__global__ void __launch_bounds__(RMS_T) rmsnorm_kernel(const float* __restrict__ h, const float* __restrict__ w,
-                                                        __half* __restrict__ out, int H, float eps) {
+__global__ void __launch_bounds__(RMS_T) rmsnorm_kernel(const float* h, const float* __restrict__ w, __half* out, int H,
+                                                        float eps) {
   __shared__ float part[RMS_T / 32];
+  pdl_launch_dependents();
   pdl_wait();
   const float* hr = h + (size_t)blockIdx.x * H;
   __half* o = out + (size_t)blockIdx.x * H;
@@ -71,11 +72,12 @@ __device__ __forceinline__ void arg_warp(float& v, int& idx) {
   }
 }
 
-__global__ void __launch_bounds__(ARG_T) argmax_kernel(const float* __restrict__ logits, int V, int64_t* tok,
+__global__ void __launch_bounds__(ARG_T) argmax_kernel(const float* logits, int V, int64_t* tok,
                                                        int64_t* pos, float* partv, int* parti, unsigned* cnt) {
   __shared__ float bv[ARG_T / 32];
   __shared__ int bi[ARG_T / 32];
   __shared__ bool last;
+  pdl_launch_dependents();
   pdl_wait();
   const int row = blockIdx.y;
   const float* lr = logits + (size_t)row * V;
@@ -128,15 +130,13 @@ int embed(const void* E, const int64_t* tok, float* h, int rows, int H, int V, c
   if (rows <= 0 || H <= 0 || (H % 2) || V <= 0) return fail(Q4B_E_SHAPE, "embed: rows, V > 0 and even H required");
   if (!E || !tok || !h || (reinterpret_cast<uintptr_t>(E) & 3u) || (reinterpret_cast<uintptr_t>(h) & 7u))
     return fail(Q4B_E_ALIGN, "embed: null or misaligned pointer");
-  embed_kernel<<<rows, 256, 0, st>>>(reinterpret_cast<const __half*>(E), tok, h, H, V);
-  return check_launch("embed");
+  return check_launch(launch_pdl(embed_kernel, dim3(rows), dim3(256), 0, st, reinterpret_cast<const __half*>(E), tok, h, H, V), "embed");
 }
 
 int rmsnorm(const float* h, const float* w, void* out, int rows, int H, float eps, cudaStream_t st) {
   if (rows <= 0 || H <= 0) return fail(Q4B_E_SHAPE, "rmsnorm: rows, H > 0 required");
   if (!h || !w || !out) return fail(Q4B_E_ALIGN, "rmsnorm: null pointer");
-  rmsnorm_kernel<<<rows, RMS_T, 0, st>>>(h, w, reinterpret_cast<__half*>(out), H, eps);
-  return check_launch("rmsnorm");
+  return check_launch(launch_pdl(rmsnorm_kernel, dim3(rows), dim3(RMS_T), 0, st, h, w, reinterpret_cast<__half*>(out), H, eps), "rmsnorm");
 }
 
 size_t argmax_workspace(int rows, int V) {
@@ -153,8 +153,8 @@ int argmax_advance(const float* logits, int rows, int V, int64_t* tok, int64_t* 
   unsigned* cnt = reinterpret_cast<unsigned*>(ws);
   float* partv = reinterpret_cast<float*>(reinterpret_cast<char*>(ws) + (((size_t)rows * 4 + 15) & ~(size_t)15));
   int* parti = reinterpret_cast<int*>(partv + (size_t)rows * ARG_SLICES);
-  argmax_kernel<<<dim3(ARG_SLICES, rows), ARG_T, 0, st>>>(logits, V, tok, pos, partv, parti, cnt);
-  return check_launch("argmax_advance");
+  return check_launch(launch_pdl(argmax_kernel, dim3(ARG_SLICES, rows), dim3(ARG_T), 0, st, logits, V, tok, pos, partv, parti, cnt),
+                      "argmax_advance");
 }
 
 }  // namespace q4b

@@ -23,7 +23,7 @@ def _dev(a: np.ndarray, device):
 
 
 class FusedQwen:
-    def __init__(self, model: dict, max_len: int = 1024, device="cuda:0"):
+    def __init__(self, model: dict, max_len: int = 1024, device="cuda:0", tensor_core: bool = True):
         if not torch.cuda.is_available():
             raise RuntimeError("FusedQwen needs a CUDA device; there is no CPU path")
         self.cfg: ModelConfig = model["cfg"]
@@ -57,8 +57,11 @@ class FusedQwen:
         self.attn_ws = K.attn_workspace(1, c.n_heads, c.head_dim, max_len, dv)
         self.head_ws = K.head_workspace(c.vocab, 1, dv)
         self.scale = 1.0 / math.sqrt(c.head_dim)
+        self.tensor_core = tensor_core
+        self.status = torch.zeros(1, dtype=torch.int32, device=dv)
         self._desc = self._make_desc()
-        self.launches_per_step = 1 + 7 * c.layers + (2 if self.head is None else 3)
+        fused = tensor_core and c.hidden % 256 == 0
+        self.launches_per_step = 1 + (5 if fused else 7) * c.layers + 2
 
     # ---- descriptor for the one-call step -------------------------------------------------------------------------
     def _make_desc(self):
@@ -80,18 +83,40 @@ class FusedQwen:
             self.embed.data_ptr(), C.cast(self._layers, C.POINTER(_ffi.Layer)), self.norm.data_ptr(), head,
             self.cos.data_ptr(), self.sin.data_ptr(), self.tok.data_ptr(), self.pos.data_ptr(), self.h.data_ptr(),
             self.x.data_ptr(), self.qkv.data_ptr(), self.att.data_ptr(), self.xm.data_ptr(), self.logits.data_ptr(),
-            self.attn_ws.data_ptr(), self.attn_ws.numel(), self.head_ws.data_ptr(), self.head_ws.numel())
+            self.attn_ws.data_ptr(), self.attn_ws.numel(), self.head_ws.data_ptr(), self.head_ws.numel(),
+            self.status.data_ptr(), _ffi.STEP_TENSOR_CORE if self.tensor_core else 0)
 
     # ---- one decode token -------------------------------------------------------------------------------------------
     def step(self) -> None:
         """One decode token through q4b_decode_step (all launches issued from C, on the current stream)."""
         _ffi.call("q4b_decode_step", C.byref(self._desc), torch.cuda.current_stream().cuda_stream)
 
+    def check_status(self) -> None:
+        """Raise if a bounded device-side wait of the tensor-core kernels expired since the last check (synchronises)."""
+        if int(self.status.item()) != 0:
+            self.status.zero_()
+            raise _ffi.Q4BError(_ffi.E_TIMEOUT, "decode step: a bounded wait on the tensor-core pipeline expired")
+
     def gemv(self, name, wsplit, X, Y, aux, N, Kdim, epi):
-        K.gemv(wsplit[0], wsplit[1], X, Y, aux, N, Kdim, epi)
+        if self.tensor_core and Kdim % 256 == 0:
+            _ffi.call("q4b_gemv_q4_0_tc", wsplit[0].data_ptr(), wsplit[1].data_ptr(), X.data_ptr(), Y.data_ptr(),
+                      0 if aux is None else aux.data_ptr(), N, Kdim, _ffi.EPI[epi], _ffi.X_F16, self.status.data_ptr(),
+                      torch.cuda.current_stream().cuda_stream)
+        else:
+            K.gemv(wsplit[0], wsplit[1], X, Y, aux, N, Kdim, epi)
 
     def rms(self, w, out):
         K.rms(self.h, w, out, self.cfg.eps)
+
+    def norm_gemv(self, nw, wsplit, Y, aux, N, Kdim, epi):
+        """RMSNorm(h) * nw followed by a linear; one launch on the tensor-core path."""
+        if self.tensor_core and Kdim % 256 == 0:
+            _ffi.call("q4b_rmsnorm_gemv_q4_0_tc", wsplit[0].data_ptr(), wsplit[1].data_ptr(), self.h.data_ptr(),
+                      nw.data_ptr(), float(self.cfg.eps), Y.data_ptr(), 0 if aux is None else aux.data_ptr(), N, Kdim,
+                      _ffi.EPI[epi], self.status.data_ptr(), torch.cuda.current_stream().cuda_stream)
+        else:
+            self.rms(nw, self.x)
+            K.gemv(wsplit[0], wsplit[1], self.x, Y, aux, N, Kdim, epi)
 
     def step_ops(self) -> None:
         """The same token through the per-op entry points, in the reference's launch order
@@ -100,19 +125,17 @@ class FusedQwen:
         H = c.hidden
         K.embed(self.embed, self.tok, self.h)
         for i, L in enumerate(self.L):
-            self.rms(L["ln1"], self.x)
-            self.gemv("qkv", L["qkv"], self.x, self.qkv, L["qkv_b"], c.qkv_rows, H, "biasf")
+            self.norm_gemv(L["ln1"], L["qkv"], self.qkv, L["qkv_b"], c.qkv_rows, H, "biasf")
             K.attn(self.qkv, self.cos, self.sin, self.pos, self.kc[i], self.vc[i], self.att, c.n_heads, c.n_kv_heads,
                    c.head_dim, self.max_len, self.scale, self.attn_ws)
             self.gemv("o", L["o"], self.att, self.h, None, H, c.q_rows, "resid")
-            self.rms(L["ln2"], self.x)
-            self.gemv("gu", L["gu"], self.x, self.xm, None, 2 * c.ffn, H, "swiglu")
+            self.norm_gemv(L["ln2"], L["gu"], self.xm, None, 2 * c.ffn, H, "swiglu")
             self.gemv("down", L["down"], self.xm, self.h, None, H, c.ffn, "resid")
-        self.rms(self.norm, self.x)
         if self.head is None:
+            self.rms(self.norm, self.x)
             K.head_argmax(self.embed, self.x, self.logits, self.tok, self.pos, self.head_ws)
         else:
-            self.gemv("head", self.head, self.x, self.logits, None, c.vocab, H, "logits")
+            self.norm_gemv(self.norm, self.head, self.logits, None, c.vocab, H, "logits")
             K.finish(self.logits, self.tok, self.pos, self.head_ws)
 
     # ---- graph + greedy loop ------------------------------------------------------------------------------------------
@@ -158,6 +181,7 @@ def run_fused(m: FusedQwen, ids, gen: int):
     for _ in range(gen - 1):
         g.replay()
         toks.append(int(m.tok.item()))
+    m.check_status()
     m.pos.copy_(pos0)
     m.tok.copy_(tok0)
     torch.cuda.synchronize()

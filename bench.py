@@ -200,7 +200,7 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
     K = importlib.import_module("3080lab_b200.qwen_kernels")
     cfg = synth.QWEN25_1P5B
     model = synth.synth_model(cfg, 0)                       # same weights on every rank, a different prompt per rank
-    m = engine.FusedQwen(model, max_len=MAX_LEN, device=f"cuda:{local_rank}")
+    m = engine.FusedQwen(model, max_len=MAX_LEN, device=f"cuda:{local_rank}", tensor_core=not args.cuda_core)
     prompt = synth.synth_prompt(cfg, args.prompt, seed=rank)
     if args.steps + max(args.warmup, 3) + args.prompt > MAX_LEN:
         raise SystemExit(f"prompt + steps + warmup must stay below {MAX_LEN}")
@@ -229,6 +229,7 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
     e.record()
     barrier()
     ms = s.elapsed_time(e)
+    m.check_status()
     clocks = sampler.stop() if rank == 0 else None
     t = torch.tensor([ms], device="cuda")
     if dist is not None:
@@ -281,10 +282,10 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
     rep = 5
     def gu_all():
         for L in m.L:
-            K.gemv(L["gu"][0], L["gu"][1], m.x, m.xm, None, 2 * c.ffn, c.hidden, "swiglu")
+            m.gemv("gu", L["gu"], m.x, m.xm, None, 2 * c.ffn, c.hidden, "swiglu")
     def down_all():
         for L in m.L:
-            K.gemv(L["down"][0], L["down"][1], m.xm, m.h, None, c.hidden, c.ffn, "resid")
+            m.gemv("down", L["down"], m.xm, m.h, None, c.hidden, c.ffn, "resid")
     def head_once():
         K.head_argmax(m.embed, m.x, m.logits, None, None, m.head_ws)
     for f in (gu_all, down_all, head_once):
@@ -295,9 +296,10 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
     b_gu = 2 * c.ffn * c.hidden // 32 * 18 + c.hidden * 2 + c.ffn * 2
     b_down = c.hidden * c.ffn // 32 * 18 + c.ffn * 2 + c.hidden * 8
     b_head = c.head_bytes() + c.hidden * 2 + c.vocab * 4
+    gname = "mmq_stream (tcgen05 exact GEMV)" if m.tensor_core else "gemv_q4_0 (CUDA cores)"
     kern = {
-        "gemv_q4_0 gate_up 17920x1536 (+swiglu)": (b_gu, us_gu, c.layers),
-        "gemv_q4_0 down 1536x8960 (+resid)": (b_down, us_down, c.layers),
+        f"{gname} gate_up 17920x1536 (+swiglu)": (b_gu, us_gu, c.layers),
+        f"{gname} down 1536x8960 (+resid)": (b_down, us_down, c.layers),
         "head_f16_argmax 151936x1536": (b_head, us_head, 1),
     }
     dominant = max(kern, key=lambda k: kern[k][1] * kern[k][2])
@@ -343,6 +345,7 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
+    ap.add_argument("--cuda-core", action="store_true", help="linears on the CUDA-core GEMV instead of the tensor-core kernel")
     ap.add_argument("--prompt", type=int, default=PROMPT, help="prompt length (512 = the benchmark configuration)")
     ap.add_argument("--profile", action="store_true",
                     help="short run for a profiler: only the warm-up and timed graph replays, no e2e / roofline / CPU legs")

@@ -120,6 +120,12 @@ int q4b_blockdot_q4_0_q8_1(const void* W, const void* xq, int32_t* out, int M, i
 int q4b_gemv_q4_0_tc(const void* W, const void* S, const void* X, void* Y, const void* AUX, int N, int K, int epilogue,
                      int x_dtype, uint32_t* status, q4b_stream_t stream);
 
+/* RMSNorm fused in front of q4b_gemv_q4_0_tc: x = round16(h * rsqrt(mean(h^2) + eps) * norm_w) is formed while the
+ * activation operand is staged, so the norm costs no launch (the reference tried the opposite fusion, norm in the
+ * tail of the producing GEMV, lab/qwen_kernels.py:54-85, and measured it slower).  h, norm_w fp32 [K]. */
+int q4b_rmsnorm_gemv_q4_0_tc(const void* W, const void* S, const float* h, const float* norm_w, float eps, void* Y,
+                             const void* AUX, int N, int K, int epilogue, uint32_t* status, q4b_stream_t stream);
+
 /* Q8_1 x Q4_0 matrix product ("MMQ") for P <= 32 activation rows (batched decode): Y[p, n] = epilogue(sum over
  * k-blocks of dw[n, b] * dx[p, b] * dot(p, n, b)) with exact int32 block dots.  Replaces the launch of
  * gemm_q4i8_ms_source (lab/qwen_batched.py:1271-1561; host Prefill.gemm8 scripts/qwen_prefill.py:176-190) and, for
@@ -179,7 +185,11 @@ typedef struct {
   float* logits;          /* fp32 [vocab] */
   void* attn_ws;  size_t attn_ws_bytes;   /* q4b_attn_decode_workspace(1, ...) */
   void* head_ws;  size_t head_ws_bytes;   /* max(q4b_head_workspace, q4b_argmax_workspace(1, vocab)) */
+  uint32_t* status;       /* [1] set to 1 when a bounded device-side wait expired (tensor-core path); zero it once */
+  int flags;              /* Q4B_STEP_* */
 } q4b_decode_desc;
+
+#define Q4B_STEP_TENSOR_CORE 1  /* linears through q4b_gemv_q4_0_tc where K is a multiple of 256 */
 
 int q4b_decode_step(const q4b_decode_desc* desc, q4b_stream_t stream);
 

@@ -9,26 +9,25 @@ torch = pytest.importorskip("torch")
 pytestmark = pytest.mark.gpu
 
 
-def build(cfg_name, seed, max_len):
+def build(cfg_name, seed, max_len, tensor_core=True):
     s = pkg("synth")
     cfg = s.CONFIGS[cfg_name]
     model = s.synth_model(cfg, seed)
-    eng = pkg("engine").FusedQwen(model, max_len=max_len)
+    eng = pkg("engine").FusedQwen(model, max_len=max_len, tensor_core=tensor_core)
     cos, sin = s.rope_tables(cfg, max_len)
     orc = oracle().Oracle(model, max_len, cos, sin)
     return s, cfg, model, eng, orc
 
 
+@pytest.mark.parametrize("tensor_core", [True, False])
 @pytest.mark.parametrize("cfg_name,seed", [("tiny", 0), ("small", 1)])
-def test_greedy_tokens_match_oracle_64_steps(cfg_name, seed):
-    s, cfg, model, eng, orc = build(cfg_name, seed, 128)
+def test_greedy_tokens_match_oracle_64_steps(cfg_name, seed, tensor_core):
+    s, cfg, model, eng, orc = build(cfg_name, seed, 128, tensor_core)
     prompt = s.synth_prompt(cfg, 24, seed)
     want = orc.greedy(prompt, 64)
     E = pkg("engine")
     got, _ = E.run_fused(eng, prompt, 64)
     assert got == want
-    # state after the run: same position, logits of the last step within tolerance
-    assert int(eng.pos.item()) == int(orc.pos[0]) + 0 or True
 
 
 def test_step_logits_and_cache_match_oracle():
@@ -57,6 +56,7 @@ def test_one_call_step_equals_per_op_step():
     """q4b_decode_step and the per-op entry points run the same kernels: bit-identical state."""
     s, cfg, model, eng, _ = build("tiny", 5, 64)
     eng2 = pkg("engine").FusedQwen(model, max_len=64)
+    assert eng.tensor_core and eng2.tensor_core
     for t in s.synth_prompt(cfg, 10, 5):
         eng.tok.fill_(int(t))
         eng2.tok.fill_(int(t))
@@ -64,6 +64,8 @@ def test_one_call_step_equals_per_op_step():
         eng2.step_ops()
     assert torch.equal(eng.logits, eng2.logits) and torch.equal(eng.kc, eng2.kc) and torch.equal(eng.h, eng2.h)
     assert torch.equal(eng.tok, eng2.tok) and torch.equal(eng.pos, eng2.pos)
+    eng.check_status()
+    eng2.check_status()
 
 
 def test_graph_replay_equals_eager():
