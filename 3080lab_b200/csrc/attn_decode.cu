@@ -265,6 +265,285 @@ __global__ void __launch_bounds__(AT) attn_decode_kernel(const __half* qkv, cons
   if (t == 0) cnt[(size_t)b * NKV + kvh] = 0u;
 }
 
+
+// ---- cluster variant ------------------------------------------------------------------------------------------------
+// The context is cut into 8 chunks, one CTA each, and the 8 CTAs of a (sequence, KV head, head subgroup) form a
+// thread-block cluster: partial (max, sum, output) stay in shared memory and the first CTA combines them through
+// distributed shared memory in chunk order.  No workspace, no atomics, no second trip through global memory.  A query
+// head group is split over CTAs (HSUB heads each) so that decode at batch 1 still spreads over several dozen SMs.
+constexpr int NCL = 8;         // chunks = cluster size
+
+template <int HD, int HSUB, int PASSES>
+__global__ void __launch_bounds__(AT) attn_decode_cluster_kernel(const __half* qkv, const float* __restrict__ cosT,
+                                                                 const float* __restrict__ sinT, const int64_t* posp,
+                                                                 __half* kc, __half* vc, __half* out, int NH, int NKV, int GRP,
+                                                                 int nsub, int max_len, float scale) {
+  constexpr int HALF = HD / 2;
+  constexpr int LPR = HD / 8;          // lanes per K/V row in the P.V pass (16-byte loads)
+  constexpr int PPI = 32 / LPR;        // rows per warp iteration
+  constexpr int CHK = 128 * PASSES;    // positions per CTA
+  __shared__ __align__(16) float qs[HSUB][HD];
+  __shared__ __align__(16) float kn[HD];
+  __shared__ __align__(16) float vn[HD];
+  __shared__ float sc[HSUB][CHK];
+  __shared__ float redw[HSUB][NW];
+  __shared__ __align__(16) float red_o[NW][HSUB][HD];
+  __shared__ __align__(16) float part_o[HSUB][HD];
+  __shared__ float part_ml[HSUB][2];
+  __shared__ float wgt[HSUB][NCL + 1];          // [h][c] = exp(m_c - M), [h][NCL] = L
+
+  pdl_launch_dependents();
+  pdl_wait();
+  const int b = blockIdx.z, chunk = blockIdx.x;
+  const int kvh = blockIdx.y / nsub, hs = blockIdx.y - kvh * nsub;
+  const int h0 = hs * HSUB, nh = min(HSUB, GRP - h0);
+  const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
+  int p = (int)posp[b];
+  p = p < 0 ? 0 : (p >= max_len ? max_len - 1 : p);
+  const int c0 = chunk * CHK;
+  const bool active = c0 <= p;
+  const int nact = p / CHK + 1;
+  const size_t head0 = (size_t)b * NH + (size_t)kvh * GRP + h0;
+
+  if (active) {
+    const bool has_new = p < c0 + CHK;
+    const int QKV = (NH + 2 * NKV) * HD;
+    const __half* row = qkv + (size_t)b * QKV;
+    const float* cs = cosT + (size_t)p * HALF;
+    const float* sn = sinT + (size_t)p * HALF;
+    __half* kbase = kc + ((size_t)b * NKV + kvh) * (size_t)max_len * HD;
+    __half* vbase = vc + ((size_t)b * NKV + kvh) * (size_t)max_len * HD;
+    for (int e = t; e < HSUB * HD; e += AT) {
+      const int hl = e / HD, d = e - hl * HD, dd = d % HALF;
+      float r = 0.f;
+      if (hl < nh) {
+        const __half* qh = row + (size_t)(kvh * GRP + h0 + hl) * HD;
+        const float a = __half2float(qh[d]), o = __half2float(qh[d < HALF ? d + HALF : d - HALF]);
+        r = d < HALF ? a * cs[dd] - o * sn[dd] : a * cs[dd] + o * sn[dd];
+      }
+      qs[hl][d] = __half2float(__float2half_rn(r));
+    }
+    if (has_new) {
+      for (int d = t; d < HD; d += AT) {
+        const int dd = d % HALF;
+        const __half* kh = row + (size_t)NH * HD + (size_t)kvh * HD;
+        const float a = __half2float(kh[d]), o = __half2float(kh[d < HALF ? d + HALF : d - HALF]);
+        const __half kr = __float2half_rn(d < HALF ? a * cs[dd] - o * sn[dd] : a * cs[dd] + o * sn[dd]);
+        const __half vr = row[(size_t)(NH + NKV) * HD + (size_t)kvh * HD + d];
+        kn[d] = __half2float(kr);
+        vn[d] = __half2float(vr);
+        if (hs == 0) {                                              // the only writer of (b, kvh, p)
+          kbase[(size_t)p * HD + d] = kr;
+          vbase[(size_t)p * HD + d] = vr;
+        }
+      }
+    }
+    __syncthreads();
+
+    // ---- scores: thread t <-> positions c0 + 128 pass + t
+    float s[PASSES][HSUB];
+#pragma unroll
+    for (int ps = 0; ps < PASSES; ++ps) {
+      const int j = c0 + 128 * ps + t;
+      const bool valid = j <= p;
+#pragma unroll
+      for (int h = 0; h < HSUB; ++h) s[ps][h] = 0.f;
+      if (valid) {
+        if (j == p) {
+#pragma unroll 4
+          for (int d = 0; d < HD; ++d) {
+            const float k = kn[d];
+#pragma unroll
+            for (int h = 0; h < HSUB; ++h) s[ps][h] = fmaf(qs[h][d], k, s[ps][h]);
+          }
+        } else {
+          const uint4* kr = reinterpret_cast<const uint4*>(kbase + (size_t)j * HD);
+          uint4 kv[HD / 8];
+#pragma unroll
+          for (int i = 0; i < HD / 8; ++i) kv[i] = kr[i];
+#pragma unroll
+          for (int i = 0; i < HD / 8; ++i) {
+            const uint32_t w[4] = {kv[i].x, kv[i].y, kv[i].z, kv[i].w};
+            float kf[8];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[u]));
+              kf[2 * u] = f.x;
+              kf[2 * u + 1] = f.y;
+            }
+#pragma unroll
+            for (int h = 0; h < HSUB; ++h) {
+              const float4 q0 = *reinterpret_cast<const float4*>(&qs[h][8 * i]);
+              const float4 q1 = *reinterpret_cast<const float4*>(&qs[h][8 * i + 4]);
+              float a = s[ps][h];
+              a = fmaf(q0.x, kf[0], a); a = fmaf(q0.y, kf[1], a); a = fmaf(q0.z, kf[2], a); a = fmaf(q0.w, kf[3], a);
+              a = fmaf(q1.x, kf[4], a); a = fmaf(q1.y, kf[5], a); a = fmaf(q1.z, kf[6], a); a = fmaf(q1.w, kf[7], a);
+              s[ps][h] = a;
+            }
+          }
+        }
+      }
+#pragma unroll
+      for (int h = 0; h < HSUB; ++h) s[ps][h] = valid ? s[ps][h] * scale : -INFINITY;
+    }
+#pragma unroll
+    for (int h = 0; h < HSUB; ++h) {
+      float m = s[0][h];
+#pragma unroll
+      for (int ps = 1; ps < PASSES; ++ps) m = fmaxf(m, s[ps][h]);
+      m = warp_max(m);
+      if (lane == 0) redw[h][warp] = m;
+    }
+    __syncthreads();
+    float mx[HSUB];
+#pragma unroll
+    for (int h = 0; h < HSUB; ++h) {
+      float m = redw[h][0];
+#pragma unroll
+      for (int w = 1; w < NW; ++w) m = fmaxf(m, redw[h][w]);
+      mx[h] = m;                                                   // finite: position c0 <= p is always valid
+    }
+    __syncthreads();
+#pragma unroll
+    for (int h = 0; h < HSUB; ++h) {
+      float l = 0.f;
+#pragma unroll
+      for (int ps = 0; ps < PASSES; ++ps) {
+        const float e = __expf(s[ps][h] - mx[h]);                  // 0 for masked positions
+        sc[h][128 * ps + t] = e;
+        l += e;
+      }
+      l = warp_sum(l);
+      if (lane == 0) redw[h][warp] = l;
+    }
+    __syncthreads();
+
+    // ---- P.V: warp w <-> positions c0 + w * 32 PASSES ...; lane <-> (row in the iteration, 8 dims)
+    const int psub = lane / LPR, d0 = (lane % LPR) * 8;
+    float acc[HSUB][8];
+#pragma unroll
+    for (int h = 0; h < HSUB; ++h)
+#pragma unroll
+      for (int u = 0; u < 8; ++u) acc[h][u] = 0.f;
+    constexpr int ITERS = 32 * PASSES / PPI, UNR = 8;
+    static_assert(ITERS % UNR == 0, "unroll must divide the iteration count");
+    for (int it0 = 0; it0 < ITERS; it0 += UNR) {
+      uint4 vv[UNR];
+#pragma unroll
+      for (int u = 0; u < UNR; ++u) {
+        const int j = c0 + 32 * PASSES * warp + (it0 + u) * PPI + psub;
+        vv[u] = make_uint4(0u, 0u, 0u, 0u);
+        if (j < p) vv[u] = *reinterpret_cast<const uint4*>(vbase + (size_t)j * HD + d0);
+      }
+#pragma unroll
+      for (int u = 0; u < UNR; ++u) {
+        const int jl = 32 * PASSES * warp + (it0 + u) * PPI + psub, j = c0 + jl;
+        if (j > p) continue;
+        float vf[8];
+        if (j == p) {
+#pragma unroll
+          for (int k = 0; k < 8; ++k) vf[k] = vn[d0 + k];
+        } else {
+          const uint32_t w[4] = {vv[u].x, vv[u].y, vv[u].z, vv[u].w};
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[k]));
+            vf[2 * k] = f.x;
+            vf[2 * k + 1] = f.y;
+          }
+        }
+#pragma unroll
+        for (int h = 0; h < HSUB; ++h) {
+          const float e = sc[h][jl];
+#pragma unroll
+          for (int k = 0; k < 8; ++k) acc[h][k] = fmaf(e, vf[k], acc[h][k]);
+        }
+      }
+    }
+#pragma unroll
+    for (int h = 0; h < HSUB; ++h)
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        float a = acc[h][k];
+#pragma unroll
+        for (int o = 16; o >= LPR; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
+        acc[h][k] = a;
+      }
+    if (psub == 0) {
+#pragma unroll
+      for (int h = 0; h < HSUB; ++h)
+#pragma unroll
+        for (int k = 0; k < 8; ++k) red_o[warp][h][d0 + k] = acc[h][k];
+    }
+    __syncthreads();
+    for (int e = t; e < HSUB * HD; e += AT) {
+      const int hl = e / HD, d = e - hl * HD;
+      float o = 0.f;
+#pragma unroll
+      for (int w = 0; w < NW; ++w) o += red_o[w][hl][d];
+      part_o[hl][d] = o;
+    }
+    if (t < HSUB) {
+      float l = 0.f;
+#pragma unroll
+      for (int w = 0; w < NW; ++w) l += redw[t][w];
+      part_ml[t][0] = mx[t];
+      part_ml[t][1] = l;
+    }
+  }
+  cluster_sync_all();                                               // every chunk's partials are in place
+  if (chunk == 0) {
+    if (t < nh) {
+      float M = -INFINITY;
+      for (int c = 0; c < nact; ++c) M = fmaxf(M, ld_peer_f32(&part_ml[t][0], (uint32_t)c));
+      float L = 0.f;
+      for (int c = 0; c < nact; ++c) {
+        const float w = __expf(ld_peer_f32(&part_ml[t][0], (uint32_t)c) - M);
+        wgt[t][c] = w;
+        L += ld_peer_f32(&part_ml[t][1], (uint32_t)c) * w;
+      }
+      wgt[t][NCL] = L;
+    }
+    __syncthreads();
+    for (int e = t; e < nh * HD; e += AT) {
+      const int hl = e / HD, d = e - hl * HD;
+      float o = 0.f;
+      for (int c = 0; c < nact; ++c) o += ld_peer_f32(&part_o[hl][d], (uint32_t)c) * wgt[hl][c];
+      out[(head0 + hl) * HD + d] = __float2half_rn(o / wgt[hl][NCL]);
+    }
+  }
+  cluster_sync_all();                                               // peers stay resident until their partials are read
+}
+
+template <int HD, int HSUB>
+int launch_cluster_passes(int passes, dim3 grid, cudaStream_t st, const __half* qkv, const float* cosT, const float* sinT,
+                          const int64_t* pos, __half* kc, __half* vc, __half* out, int NH, int NKV, int GRP, int nsub,
+                          int max_len, float scale) {
+  cudaError_t e;
+  if (passes == 1)
+    e = launch_pdl_cluster(attn_decode_cluster_kernel<HD, HSUB, 1>, grid, dim3(AT), 0, st, NCL, 1, qkv, cosT, sinT, pos, kc, vc,
+                           out, NH, NKV, GRP, nsub, max_len, scale);
+  else if (passes == 2)
+    e = launch_pdl_cluster(attn_decode_cluster_kernel<HD, HSUB, 2>, grid, dim3(AT), 0, st, NCL, 1, qkv, cosT, sinT, pos, kc, vc,
+                           out, NH, NKV, GRP, nsub, max_len, scale);
+  else
+    e = launch_pdl_cluster(attn_decode_cluster_kernel<HD, HSUB, 4>, grid, dim3(AT), 0, st, NCL, 1, qkv, cosT, sinT, pos, kc, vc,
+                           out, NH, NKV, GRP, nsub, max_len, scale);
+  return check_launch(e, "attn_decode");
+}
+
+template <int HD>
+int launch_cluster(int hsub, int passes, dim3 grid, cudaStream_t st, const __half* qkv, const float* cosT, const float* sinT,
+                   const int64_t* pos, __half* kc, __half* vc, __half* out, int NH, int NKV, int GRP, int nsub, int max_len,
+                   float scale) {
+  switch (hsub) {
+    case 1: return launch_cluster_passes<HD, 1>(passes, grid, st, qkv, cosT, sinT, pos, kc, vc, out, NH, NKV, GRP, nsub, max_len, scale);
+    case 2: return launch_cluster_passes<HD, 2>(passes, grid, st, qkv, cosT, sinT, pos, kc, vc, out, NH, NKV, GRP, nsub, max_len, scale);
+    case 3: return launch_cluster_passes<HD, 3>(passes, grid, st, qkv, cosT, sinT, pos, kc, vc, out, NH, NKV, GRP, nsub, max_len, scale);
+    default: return launch_cluster_passes<HD, 4>(passes, grid, st, qkv, cosT, sinT, pos, kc, vc, out, NH, NKV, GRP, nsub, max_len, scale);
+  }
+}
+
 size_t align16(size_t v) { return (v + 15) & ~(size_t)15; }
 
 template <int HD>
@@ -299,6 +578,18 @@ int attn_decode(const void* qkv, const float* cosT, const float* sinT, const int
   if (!qkv || !cosT || !sinT || !pos || !kc || !vc || !out || !ws || !aligned16(kc) || !aligned16(vc) || !aligned16(ws))
     return fail(Q4B_E_ALIGN, "attn_decode: null or misaligned pointer");
   if (ws_bytes < attn_decode_workspace(B, NH, HD, max_len)) return fail(Q4B_E_WORKSPACE, "attn_decode: workspace too small");
+  if (max_len <= NCL * 128 * 4) {
+    // cluster path: 8 chunks of 128 / 256 / 512 positions; a head group is served by 1..4 CTAs
+    static const int hsub_for[9] = {1, 1, 2, 3, 2, 3, 2, 4, 4};
+    const int GRP = NH / NKV, hsub = hsub_for[GRP], nsub = (GRP + hsub - 1) / hsub;
+    const int passes = max_len <= NCL * 128 ? 1 : (max_len <= NCL * 256 ? 2 : 4);
+    dim3 grid(NCL, NKV * nsub, B);
+    if (HD == 128)
+      return launch_cluster<128>(hsub, passes, grid, st, (const __half*)qkv, cosT, sinT, pos, (__half*)kc, (__half*)vc,
+                                 (__half*)out, NH, NKV, GRP, nsub, max_len, scale);
+    return launch_cluster<64>(hsub, passes, grid, st, (const __half*)qkv, cosT, sinT, pos, (__half*)kc, (__half*)vc,
+                              (__half*)out, NH, NKV, GRP, nsub, max_len, scale);
+  }
   const int NC = (max_len + CH - 1) / CH;
   char* base = reinterpret_cast<char*>(ws);
   unsigned* cnt = reinterpret_cast<unsigned*>(base);

@@ -59,17 +59,6 @@ __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t by
                "l"(src), "r"(bytes), "r"(tc::smem_u32(bar))
                : "memory");
 }
-__device__ __forceinline__ void cluster_sync_all() {
-  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-__device__ __forceinline__ float ld_peer_f32(const float* local, uint32_t rank) {
-  uint32_t a;
-  float v;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(a) : "r"(tc::smem_u32(local)), "r"(rank));
-  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(a) : "memory");
-  return v;
-}
-
 // position of element i (0..31) of a k-block inside the 32 operand bytes (see tc::expand_nibbles)
 __device__ __forceinline__ int perm_pos(int i) { return 4 * (2 * (i >> 3) + (i & 1)) + ((i & 7) >> 1); }
 
