@@ -18,7 +18,7 @@ _P, _I, _F, _Z = C.c_void_p, C.c_int, C.c_float, C.c_size_t
 
 
 class Linear(C.Structure):
-    _fields_ = [("W", _P), ("S", _P), ("N", _I), ("K", _I)]
+    _fields_ = [("W", _P), ("S", _P), ("N", _I), ("K", _I), ("Wt", _P), ("St", _P)]
 
 
 class Layer(C.Structure):
@@ -53,6 +53,8 @@ SIGNATURES = {
     "q4b_argmax_advance": (_I, [_P, _I, _I, _P, _P, _P, _Z, _P]),
     "q4b_blockdot_q4_0_q8_1": (_I, [_P, _P, _P, _I, _I, _I, _I, _P, _P]),
     "q4b_gemv_q4_0_tc": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _P, _P]),
+    "q4b_pack_q4_0": (_I, [_P, _P, _P, _P, _I, _I, _P]),
+    "q4b_trace_buffer": (_I, [_P, _Z]),
     "q4b_rmsnorm_gemv_q4_0_tc": (_I, [_P, _P, _P, _P, _F, _P, _P, _I, _I, _I, _P, _P]),
     "q4b_mmq_q4_0_q8_1": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P]),
     "q4b_quant_q8_1": (_I, [_P, _P, _P, _P, _I, _I, _P]),

@@ -44,6 +44,8 @@ int head_f16_argmax(const void*, const void*, float*, int, int, int64_t*, int64_
 int blockdot(const void*, const void*, int32_t*, int, int, int, int, uint32_t*, cudaStream_t);
 int mmq_stream(const void*, const void*, const void*, const void*, void*, const void*, int, int, int, int, int, int, uint32_t*,
                cudaStream_t, const float* norm_w = nullptr, float eps = 0.f);
+void mmq_stream_trace(unsigned long long*);
+int pack_q4_0(const void*, const void*, void*, void*, int, int, cudaStream_t);
 int quant_q8_1(const void*, void*, void*, void*, int, int, cudaStream_t);
 int rmsnorm_q8_1(const float*, const float*, void*, void*, void*, void*, int, int, float, cudaStream_t);
 
@@ -123,6 +125,16 @@ int q4b_gemv_q4_0_tc(const void* W, const void* Sc, const void* X, void* Y, cons
   return mmq_stream(W, Sc, X, nullptr, Y, AUX, N, K, 1, x_dtype == Q4B_X_F16 ? 0 : 1, epilogue, ldy, status, S(stream));
 }
 
+int q4b_pack_q4_0(const void* W, const void* Sc, void* Wt, void* St, int N, int K, q4b_stream_t stream) {
+  return pack_q4_0(W, Sc, Wt, St, N, K, S(stream));
+}
+
+int q4b_trace_buffer(uint64_t* device_buffer, size_t entries) {
+  if (device_buffer && entries < (size_t)4096 * 16) return fail(Q4B_E_WORKSPACE, "trace_buffer: need 4096 x 16 entries");
+  mmq_stream_trace(reinterpret_cast<unsigned long long*>(device_buffer));
+  return Q4B_OK;
+}
+
 int q4b_rmsnorm_gemv_q4_0_tc(const void* W, const void* Sc, const float* h, const float* norm_w, float eps, void* Y,
                              const void* AUX, int N, int K, int epilogue, uint32_t* status, q4b_stream_t stream) {
   const int ldy = epilogue == Q4B_EPI_SWIGLU ? N / 2 : N;
@@ -151,14 +163,14 @@ int q4b_decode_step(const q4b_decode_desc* d, q4b_stream_t stream) {
   const bool tcp = (d->flags & Q4B_STEP_TENSOR_CORE) && d->status;
   // one linear: tensor-core kernel when its shape allows, the CUDA-core GEMV otherwise
   auto lin = [&](const q4b_linear& L, const void* X, void* Y, const void* AUX, int epi) -> int {
-    if (tcp && (L.K % 256) == 0)
-      return mmq_stream(L.W, L.S, X, nullptr, Y, AUX, L.N, L.K, 1, 0, epi, epi == Q4B_EPI_SWIGLU ? L.N / 2 : L.N, d->status, st);
+    if (tcp && L.Wt && (L.K % 256) == 0)
+      return mmq_stream(L.Wt, L.St, X, nullptr, Y, AUX, L.N, L.K, 1, 0, epi, epi == Q4B_EPI_SWIGLU ? L.N / 2 : L.N, d->status, st);
     return gemv_q4_0(L.W, L.S, X, Y, AUX, L.N, L.K, epi, Q4B_X_F16, st);
   };
   // RMSNorm followed by a linear: one launch on the tensor-core path (the norm is computed while staging the operand)
   auto norm_lin = [&](const float* nw, const q4b_linear& L, void* Y, const void* AUX, int epi) -> int {
-    if (tcp && (L.K % 256) == 0)
-      return mmq_stream(L.W, L.S, d->h, nullptr, Y, AUX, L.N, L.K, 1, 3, epi, epi == Q4B_EPI_SWIGLU ? L.N / 2 : L.N, d->status,
+    if (tcp && L.Wt && (L.K % 256) == 0)
+      return mmq_stream(L.Wt, L.St, d->h, nullptr, Y, AUX, L.N, L.K, 1, 3, epi, epi == Q4B_EPI_SWIGLU ? L.N / 2 : L.N, d->status,
                         st, nw, d->eps);
     int rc = rmsnorm(d->h, nw, d->x, 1, H, d->eps, st);
     return rc != Q4B_OK ? rc : gemv_q4_0(L.W, L.S, d->x, Y, AUX, L.N, L.K, epi, Q4B_X_F16, st);

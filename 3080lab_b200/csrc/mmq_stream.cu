@@ -13,10 +13,11 @@
 //               block; the only roundings are the per-block fp32 scale-and-add, as in the reference.
 //
 // Data movement (per CTA = 128 weight rows x one K slice):
-//   * thread t owns row t.  Before the programmatic-dependency wait it issues two 1-D bulk (TMA) copies: its row's
-//     nibbles and fp16 scales for the whole K slice, into a padded shared-memory slab, completing on one mbarrier.
-//     Weights never depend on the previous kernel, so with programmatic dependent launch this prefetch overlaps the
-//     producer of x.
+//   * weights arrive tile-packed (pack.cu): a CTA's row tile x K slice is one contiguous range.  Before the
+//     programmatic-dependency wait one thread issues two 1-D bulk (TMA) copies per batch of k-blocks (nibbles, fp16
+//     scales) into shared memory, each batch completing on its own mbarrier.  Weights never depend on the previous
+//     kernel, so with programmatic dependent launch the whole prefetch overlaps the producer of x.  (Per-row copies
+//     from the canonical layout were measured first: issuing 256 small bulk copies per CTA cost 1.8 us.)
 //   * after the wait the activation slice is staged once into shared memory as the UMMA B operand (K-major 8x16-byte
 //     core matrices, bytes permuted to match the nibble expansion order).
 //   * per batch of G k-blocks: each thread expands 16 bytes of nibbles to 32 signed bytes 16*(q-8) (two logic ops per
@@ -36,15 +37,17 @@ namespace {
 
 constexpr int MODE_X16 = 0, MODE_X32 = 1, MODE_Q8 = 2, MODE_NORM = 3;
 constexpr int ROWS = 128;
+constexpr int MAX_BATCH = 20;                   // batches (mbarriers) per CTA
 constexpr size_t MAX_DYN_SMEM = 226 * 1024;   // 227 KB per CTA on sm_100 minus the static barriers
 
 struct StreamArgs {
-  const uint8_t* W;     // canonical nibbles, row pitch K/2 bytes
-  const __half* S;      // [N, K/32]
+  const uint8_t* W;     // tile-packed nibbles [T, K/32, 128, 16 bytes]
+  const __half* S;      // tile-packed scales [T, K/32, 128]
   const void* X;        // exact modes: fp16 / fp32 [K]; Q8 mode: int8 [cols, K]
   const __half* XD;     // Q8 mode: fp16 [cols, K/32]
   const float* NW;      // norm mode: RMSNorm weights fp32 [K] (X is then the fp32 residual stream)
   float eps;
+  unsigned long long* trace;   // optional: 16 %globaltimer stamps per CTA (thread 0), see q4b_trace_buffer
   void* Y;
   const void* AUX;
   uint32_t* status;
@@ -72,52 +75,68 @@ __global__ void __launch_bounds__(ROWS) mmq_stream_kernel(const StreamArgs a) {
   constexpr int G = NT <= 16 ? 8 : 4;                  // k-blocks per MMA batch
   constexpr int NL = (MODE == MODE_X16 || MODE == MODE_NORM) ? 3 : 4;   // digits in exact mode (fp16-valued x: 3)
   constexpr int NACC = MODE == MODE_Q8 ? NT : 1;
+  constexpr bool PUSH = NACC <= 8;                     // split-K partials pushed to the leader (else pulled)
   constexpr uint32_t A_COLS = 2 * G * 8, D_COLS = 2 * G * NT;
   constexpr uint32_t TCOLS = (A_COLS + D_COLS) <= 128 ? 128 : ((A_COLS + D_COLS) <= 256 ? 256 : 512);
   constexpr uint32_t IDESC = tc::idesc_i8(128, NT);
 
   extern __shared__ __align__(128) uint8_t smem[];
-  __shared__ __align__(8) uint64_t bar_load;
+  __shared__ __align__(8) uint64_t bar_load[MAX_BATCH];
   __shared__ __align__(8) uint64_t bar_mma[2];
   __shared__ uint32_t tmem_base_s;
 
   const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
   const int row0 = blockIdx.x * ROWS, row = row0 + t;
   const int ks = blockIdx.y;
+  unsigned long long* tr = (a.trace && t == 0) ? a.trace + (size_t)(blockIdx.y * gridDim.x + blockIdx.x) * 16 : nullptr;
+  int tri = 0;
+  auto stamp = [&]() {
+    if (tr && tri < 16) {
+      unsigned long long g;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g));
+      tr[tri++] = g;
+    }
+  };
+  stamp();                                              // 0: start
+  pdl_launch_dependents();                              // let the next kernel's CTAs begin their own prologue now
   const int KB = a.K >> 5, GT = a.K >> 8;
   const int g0 = ks * a.gps, ng = min(a.gps, GT - g0);          // host guarantees ng >= 1
   const int nkb = ng * 8, kb0 = g0 * 8;
-  const uint32_t pitchW = a.gps * 128 + 16, pitchS = a.gps * 16 + 16;
-  uint8_t* slabW = smem;
-  uint8_t* slabS = slabW + ROWS * pitchW;
-  uint8_t* sB = slabS + ((ROWS * pitchS + 127) & ~127u);
+  uint8_t* slabW = smem;                                         // [k-block][128 rows][16 bytes]
+  uint8_t* slabS = slabW + (size_t)a.gps * 8 * 2048;             // [k-block][128 rows] fp16
+  uint8_t* sB = slabS + (size_t)a.gps * 8 * 256;
   float* xs = reinterpret_cast<float*>(sB + (size_t)a.gps * 8 * NT * 32);     // block scales of the activations
+  float* red_buf = xs + (size_t)a.gps * 8 * NT;                  // split-K partials pushed by the peers: [rank-1][NACC][128]
+  const int nbatch = nkb / G;
 
   if (warp == 0) {
     tc::tmem_alloc(&tmem_base_s, TCOLS);
     tc::tmem_relinquish();
   }
   if (t == 0) {
-    tc::mbar_init(&bar_load, ROWS);
+    for (int b = 0; b < nbatch; ++b) tc::mbar_init(&bar_load[b], 1);
     tc::mbar_init(&bar_mma[0], 1);
     tc::mbar_init(&bar_mma[1], 1);
     tc::mbar_fence_init();
   }
+  stamp();                                              // TMEM allocated, barriers initialised
   tc::fence_before_sync();
   __syncthreads();
   tc::fence_after_sync();
+  stamp();
 
-  // ---- weights: one bulk copy of nibbles and one of scales per row, whole K slice
-  if (row < a.N) {
-    const uint32_t bw = (uint32_t)ng * 128, bs = (uint32_t)ng * 16;
-    tc::mbar_expect_tx(&bar_load, bw + bs);
-    bulk_g2s(slabW + t * pitchW, a.W + (size_t)row * (a.K >> 1) + (size_t)g0 * 128, bw, &bar_load);
-    bulk_g2s(slabS + t * pitchS, a.S + (size_t)row * KB + kb0, bs, &bar_load);
-  } else {
-    tc::mbar_arrive(&bar_load);
+  // ---- weights: per batch of G k-blocks one bulk copy of nibbles and one of scales, issued by one thread
+  if (t == 0) {
+    const size_t kbg = (size_t)blockIdx.x * KB + kb0;            // first k-block of this CTA in the packed arrays
+    for (int b = 0; b < nbatch; ++b) {
+      tc::mbar_expect_tx(&bar_load[b], (uint32_t)G * (2048 + 256));
+      bulk_g2s(slabW + (size_t)b * G * 2048, a.W + (kbg + (size_t)b * G) * 2048, (uint32_t)G * 2048, &bar_load[b]);
+      bulk_g2s(slabS + (size_t)b * G * 256, a.S + (kbg + (size_t)b * G) * 128, (uint32_t)G * 256, &bar_load[b]);
+    }
   }
-  pdl_launch_dependents();
+  stamp();                                              // bulk copies issued
   pdl_wait();                                           // the activations come from the previous kernel
+  stamp();                                              // 2: predecessor complete
 
   // ---- activations -> UMMA B operand in shared memory
   if (MODE == MODE_Q8) {
@@ -141,6 +160,30 @@ __global__ void __launch_bounds__(ROWS) mmq_stream_kernel(const StreamArgs a) {
     // |X_i| < 2^(8 NL - 2), split into signed base-256 digits, digit j -> column j.
     for (int c = t; c < nkb * 64; c += ROWS)            // columns NL..7 must read as zero
       *reinterpret_cast<uint32_t*>(sB + (size_t)c * 4) = 0u;
+    // all global loads of this thread's operand elements are issued before anything waits on them
+    constexpr int MAXIT = 5;                            // 16 k-blocks per pass over the CTA's threads, at most 80 per slice
+    float xin[MAXIT][4];
+#pragma unroll
+    for (int u = 0; u < MAXIT; ++u) {
+      const int kbl = (t >> 3) + u * (ROWS / 8);
+      xin[u][0] = xin[u][1] = xin[u][2] = xin[u][3] = 0.f;
+      if (kbl < nkb) {
+        const int k = (kb0 + kbl) * 32 + (t & 7) * 4;
+        if (MODE == MODE_X16) {
+          const uint2 raw = *reinterpret_cast<const uint2*>(reinterpret_cast<const __half*>(a.X) + k);
+          const float2 p = __half22float2(*reinterpret_cast<const __half2*>(&raw.x));
+          const float2 q = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
+          xin[u][0] = p.x; xin[u][1] = p.y; xin[u][2] = q.x; xin[u][3] = q.y;
+        } else {
+          const float4 v = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(a.X) + k);
+          xin[u][0] = v.x; xin[u][1] = v.y; xin[u][2] = v.z; xin[u][3] = v.w;
+          if (MODE == MODE_NORM) {                      // (v * r) * w is evaluated as (v * w) * r: r arrives last
+            const float4 w = __ldg(reinterpret_cast<const float4*>(a.NW + k));
+            xin[u][0] *= w.x; xin[u][1] *= w.y; xin[u][2] *= w.z; xin[u][3] *= w.w;
+          }
+        }
+      }
+    }
     float rnorm = 1.f;
     if (MODE == MODE_NORM) {
       // RMSNorm of the whole residual row (every CTA needs the full sum of squares), as RMSNORM_F32W_1P
@@ -160,24 +203,16 @@ __global__ void __launch_bounds__(ROWS) mmq_stream_kernel(const StreamArgs a) {
       __syncthreads();
     }
     const int sub = t & 7;
-    for (int kbl = t >> 3; kbl < nkb; kbl += ROWS / 8) {
-      const int k = (kb0 + kbl) * 32 + sub * 4;
+    for (int kbl = t >> 3, it = 0; kbl < nkb; kbl += ROWS / 8, ++it) {
       float x[4];
-      if (MODE == MODE_X16) {
-        const uint2 raw = *reinterpret_cast<const uint2*>(reinterpret_cast<const __half*>(a.X) + k);
-        const float2 p = __half22float2(*reinterpret_cast<const __half2*>(&raw.x));
-        const float2 q = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
-        x[0] = p.x; x[1] = p.y; x[2] = q.x; x[3] = q.y;
-      } else {
-        const float4 v = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(a.X) + k);
-        x[0] = v.x; x[1] = v.y; x[2] = v.z; x[3] = v.w;
-        if (MODE == MODE_NORM) {
-          const float4 w = __ldg(reinterpret_cast<const float4*>(a.NW + k));
-          x[0] = __half2float(__float2half_rn(x[0] * rnorm * w.x));
-          x[1] = __half2float(__float2half_rn(x[1] * rnorm * w.y));
-          x[2] = __half2float(__float2half_rn(x[2] * rnorm * w.z));
-          x[3] = __half2float(__float2half_rn(x[3] * rnorm * w.w));
+#pragma unroll
+      for (int u = 0; u < MAXIT; ++u)
+        if (u == it) {
+          x[0] = xin[u][0]; x[1] = xin[u][1]; x[2] = xin[u][2]; x[3] = xin[u][3];
         }
+      if (MODE == MODE_NORM) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) x[j] = __half2float(__float2half_rn(x[j] * rnorm));   // xin holds v * w
       }
       float amax = fmaxf(fmaxf(fabsf(x[0]), fabsf(x[1])), fmaxf(fabsf(x[2]), fabsf(x[3])));
 #pragma unroll
@@ -208,8 +243,9 @@ __global__ void __launch_bounds__(ROWS) mmq_stream_kernel(const StreamArgs a) {
   }
   tc::fence_async_smem();
   __syncthreads();
+  stamp();                                              // 3: activation operand staged
 
-  bool ok = tc::mbar_wait(&bar_load, 0);                // slab landed (async-proxy writes made visible by the barrier)
+  bool ok = true;                // slab landed (async-proxy writes made visible by the barrier)
 
   const uint32_t tmem = tmem_base_s;
   const uint32_t lane_off = (uint32_t)(32 * warp) << 16;
@@ -218,9 +254,8 @@ __global__ void __launch_bounds__(ROWS) mmq_stream_kernel(const StreamArgs a) {
 #pragma unroll
   for (int n = 0; n < NACC; ++n) acc[n] = 0.f;
 
-  const int nbatch = nkb / G;
-  const uint8_t* myW = slabW + t * pitchW;
-  const __half* myS = reinterpret_cast<const __half*>(slabS + t * pitchS);
+  const uint8_t* myW = slabW + t * 16;
+  const __half* myS = reinterpret_cast<const __half*>(slabS) + t;
 
   auto fold = [&](int bi) {                             // accumulators of batch bi -> acc
     const int slot = bi & 1;
@@ -241,7 +276,7 @@ __global__ void __launch_bounds__(ROWS) mmq_stream_kernel(const StreamArgs a) {
 #pragma unroll
         for (int j = 0; j < SB; ++j) {
           const int kbl = bi * G + j0 + j;
-          const float dw = __half2float(myS[kbl]) * 0.0625f;     // 1/16 undoes the 16*(q-8) operand scaling
+          const float dw = __half2float(myS[kbl * 128]) * 0.0625f;   // 1/16 undoes the 16*(q-8) operand scaling
 #pragma unroll
           for (int c0 = 0; c0 < NT; c0 += 4) {
             const float4 sx = *reinterpret_cast<const float4*>(xs + kbl * NT + c0);
@@ -260,7 +295,7 @@ __global__ void __launch_bounds__(ROWS) mmq_stream_kernel(const StreamArgs a) {
 #pragma unroll
       for (int j = 0; j < G; ++j) {
         const int kbl = bi * G + j;
-        const float dw = __half2float(myS[kbl]) * 0.0625f;
+        const float dw = __half2float(myS[kbl * 128]) * 0.0625f;
         float f = fmaf(256.f, (float)(int32_t)d[j][1], (float)(int32_t)d[j][0]);
         f = fmaf(65536.f, (float)(int32_t)d[j][2], f);
         if (NL == 4) f = fmaf(16777216.f, (float)(int32_t)d[j][3], f);
@@ -272,9 +307,10 @@ __global__ void __launch_bounds__(ROWS) mmq_stream_kernel(const StreamArgs a) {
 
   for (int bi = 0; bi < nbatch; ++bi) {
     const int slot = bi & 1;
+    ok = tc::mbar_wait(&bar_load[bi], 0) && ok;         // this batch's weights landed (async-proxy writes now visible)
 #pragma unroll 2
     for (int j = 0; j < G; ++j) {
-      const uint4 w = *reinterpret_cast<const uint4*>(myW + (size_t)(bi * G + j) * 16);
+      const uint4 w = *reinterpret_cast<const uint4*>(myW + (size_t)(bi * G + j) * 2048);
       uint32_t ex[8];
       tc::expand_nibbles(w.x, ex[0], ex[1]);
       tc::expand_nibbles(w.y, ex[2], ex[3]);
@@ -294,27 +330,52 @@ __global__ void __launch_bounds__(ROWS) mmq_stream_kernel(const StreamArgs a) {
       }
       tc::mma_commit(&bar_mma[slot]);
     }
+    stamp();                                            // 5, 6, ...: batch expanded and issued
     if (bi > 0) fold(bi - 1);
   }
   if (nbatch > 0) fold(nbatch - 1);
   __syncthreads();                                      // every thread is done with the slabs and with TMEM
+  stamp();                                              // all batches folded
 
-  // ---- split-K: partial sums through distributed shared memory, added in rank order
+  // ---- split-K.  Few accumulators per thread: every peer pushes its partial sums into the leader's shared memory
+  // (remote stores), one cluster barrier publishes them and the leader adds them in rank order.  Many accumulators
+  // (16 / 32 activation rows): the push buffer would not fit beside the slabs, so peers park their partials in their
+  // own dead weight slab and the leader pulls them between two barriers.
   if (a.ksplit > 1) {
-    float* part = reinterpret_cast<float*>(slabW);      // [NACC][128]
-    if (ks != 0) {
+    if (PUSH) {
+      if (ks != 0) {
+        uint32_t remote;
+        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(tc::smem_u32(red_buf)), "r"(0));
 #pragma unroll
-      for (int n = 0; n < NACC; ++n) part[n * ROWS + t] = acc[n];
-    }
-    cluster_sync_all();
-    if (ks == 0) {
-      for (int r = 1; r < a.ksplit; ++r) {
-#pragma unroll
-        for (int n = 0; n < NACC; ++n) acc[n] += ld_peer_f32(part + n * ROWS + t, (uint32_t)r);
+        for (int n = 0; n < NACC; ++n)
+          asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote + (uint32_t)((((ks - 1) * NACC + n) * ROWS + t) * 4)),
+                       "f"(acc[n])
+                       : "memory");
       }
+      cluster_sync_all();
+      if (ks == 0) {
+        for (int r = 1; r < a.ksplit; ++r) {
+#pragma unroll
+          for (int n = 0; n < NACC; ++n) acc[n] += red_buf[((r - 1) * NACC + n) * ROWS + t];
+        }
+      }
+    } else {
+      float* part = reinterpret_cast<float*>(slabW);    // [NACC][128], every thread is past its last slab read
+      if (ks != 0) {
+#pragma unroll
+        for (int n = 0; n < NACC; ++n) part[n * ROWS + t] = acc[n];
+      }
+      cluster_sync_all();
+      if (ks == 0) {
+        for (int r = 1; r < a.ksplit; ++r) {
+#pragma unroll
+          for (int n = 0; n < NACC; ++n) acc[n] += ld_peer_f32(part + n * ROWS + t, (uint32_t)r);
+        }
+      }
+      cluster_sync_all();                               // peers stay resident until the leader has read them
     }
-    cluster_sync_all();                                 // peers stay alive until the leader has read them
   }
+  stamp();                                              // split-K reduced
 
   if (ks == 0) {
 #pragma unroll
@@ -342,7 +403,11 @@ __global__ void __launch_bounds__(ROWS) mmq_stream_kernel(const StreamArgs a) {
   tc::fence_before_sync();
   __syncthreads();
   if (warp == 0) tc::tmem_dealloc(tmem, TCOLS);
+  stamp();                                              // end
+  if (tr) tr[15] = (unsigned long long)tri;
 }
+
+unsigned long long* g_trace = nullptr;
 
 struct Geometry {
   int ksplit, gps;
@@ -350,16 +415,15 @@ struct Geometry {
   uint32_t tcols;
 };
 
-size_t smem_bytes(int gps, int nt) {
-  const size_t pitchW = (size_t)gps * 128 + 16, pitchS = (size_t)gps * 16 + 16;
-  size_t s = ROWS * pitchW;
-  s += (ROWS * pitchS + 127) & ~(size_t)127;
-  s += (size_t)gps * 8 * nt * 32;          // B operand
-  s += (size_t)gps * 8 * nt * 4;           // activation block scales
+size_t smem_bytes(int gps, int nt, int nacc, int ksplit) {
+  size_t s = (size_t)gps * 8 * (2048 + 256);   // weight slabs
+  s += (size_t)gps * 8 * nt * 32;              // B operand
+  s += (size_t)gps * 8 * nt * 4;               // activation block scales (+ the norm reduction scratch)
+  if (nacc <= 8) s += (size_t)(ksplit - 1) * nacc * ROWS * 4;   // split-K partials pushed to the leader
   return s + 128;
 }
 
-bool plan(int N, int K, int nt, Geometry& g) {
+bool plan(int N, int K, int nt, int nacc, Geometry& g) {
   const int GT = K / 256, tiles = (N + ROWS - 1) / ROWS;
   const int G = nt <= 16 ? 8 : 4;
   const uint32_t need = 2 * G * 8 + 2 * G * nt;
@@ -369,14 +433,15 @@ bool plan(int N, int K, int nt, Geometry& g) {
   for (int ks = 1; ks <= 8 && ks <= GT; ++ks) {
     const int gps = (GT + ks - 1) / ks;
     if ((ks - 1) * gps >= GT) continue;                 // an empty slice
-    if (smem_bytes(gps, nt) > MAX_DYN_SMEM) continue;
+    if (gps * 8 / G > MAX_BATCH || gps > 10) continue;
+    if (smem_bytes(gps, nt, nacc, ks) > MAX_DYN_SMEM) continue;
     best = ks;
     if ((long)tiles * ks >= (long)sms * 3 / 2) break;   // enough CTAs for two per SM on most of the machine
   }
   if (best < 0) return false;
   g.ksplit = best;
   g.gps = (GT + best - 1) / best;
-  g.smem = smem_bytes(g.gps, nt);
+  g.smem = smem_bytes(g.gps, nt, nacc, best);
   // tcgen05.alloc blocks while an SM's 512 TMEM columns are taken; CTAs of one cluster wait for each other, so the
   // number of co-resident CTAs times their columns must never exceed 512.  Shared memory is the limiter we control.
   const size_t max_ctas = 512 / g.tcols;
@@ -433,6 +498,9 @@ int launch_nt(int nt, const StreamArgs& a, const Geometry& g, cudaStream_t st) {
 
 }  // namespace
 
+// Device buffer for the optional timeline stamps of the next launches (16 x uint64 per CTA, up to 4096 CTAs); null = off.
+void mmq_stream_trace(unsigned long long* buf) { g_trace = buf; }
+
 // mode: 0 exact fp16 x, 1 exact fp32 x, 2 Q8_1, 3 exact with RMSNorm of the fp32 row X fused in front.
 // cols: 1 for the exact modes, 1..32 sequences for Q8_1.
 int mmq_stream(const void* W, const void* S, const void* X, const void* XD, void* Y, const void* AUX, int N, int K,
@@ -450,7 +518,7 @@ int mmq_stream(const void* W, const void* S, const void* X, const void* XD, void
   if (epilogue == Q4B_EPI_BIASF && !AUX) return fail(Q4B_E_ALIGN, "mmq_stream: biasf needs AUX");
   const int nt = mode != MODE_Q8 ? 8 : (cols <= 8 ? 8 : (cols <= 16 ? 16 : 32));
   Geometry g;
-  if (!plan(N, K, nt, g)) return fail(Q4B_E_SHAPE, "mmq_stream: no K split fits shared memory for this K");
+  if (!plan(N, K, nt, mode == MODE_Q8 ? nt : 1, g)) return fail(Q4B_E_SHAPE, "mmq_stream: no K split fits shared memory for this K");
   StreamArgs a;
   a.W = reinterpret_cast<const uint8_t*>(W);
   a.S = reinterpret_cast<const __half*>(S);
@@ -458,6 +526,7 @@ int mmq_stream(const void* W, const void* S, const void* X, const void* XD, void
   a.XD = reinterpret_cast<const __half*>(XD);
   a.NW = norm_w;
   a.eps = eps;
+  a.trace = g_trace;
   a.Y = Y;
   a.AUX = AUX;
   a.status = status;

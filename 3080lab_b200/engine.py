@@ -14,6 +14,7 @@ import numpy as np
 import torch
 
 from . import _ffi
+from . import qwen_batched as QB
 from . import qwen_kernels as K
 from .synth import ModelConfig, rope_tables
 
@@ -41,6 +42,16 @@ class FusedQwen:
             self.L.append(d)
         self.norm = _dev(model["norm"], self.device)
         self.head = None if model["head"] is None else tuple(_dev(a, self.device) for a in model["head"])
+        # tile-packed copies for the tensor-core kernels (K a multiple of 256)
+        self.tensor_core = tensor_core
+        self.packed = {}
+        if tensor_core:
+            for i, d in enumerate(self.L):
+                for k in ("qkv", "o", "gu", "down"):
+                    if d[k][0].shape[1] * 8 % 256 == 0:
+                        self.packed[id(d[k][0])] = QB.pack_q4(*d[k])
+            if self.head is not None and c.hidden % 256 == 0:
+                self.packed[id(self.head[0])] = QB.pack_q4(*self.head)
         cos, sin = rope_tables(c, max_len)
         self.cos, self.sin = _dev(cos, self.device), _dev(sin, self.device)
         f16, f32, dv = torch.float16, torch.float32, self.device
@@ -57,7 +68,6 @@ class FusedQwen:
         self.attn_ws = K.attn_workspace(1, c.n_heads, c.head_dim, max_len, dv)
         self.head_ws = K.head_workspace(c.vocab, 1, dv)
         self.scale = 1.0 / math.sqrt(c.head_dim)
-        self.tensor_core = tensor_core
         self.status = torch.zeros(1, dtype=torch.int32, device=dv)
         self._desc = self._make_desc()
         fused = tensor_core and c.hidden % 256 == 0
@@ -68,7 +78,9 @@ class FusedQwen:
         c = self.cfg
 
         def lin(pair, n, k):
-            return _ffi.Linear(pair[0].data_ptr(), pair[1].data_ptr(), n, k)
+            pk = self.packed.get(id(pair[0]))
+            return _ffi.Linear(pair[0].data_ptr(), pair[1].data_ptr(), n, k, pk[0].data_ptr() if pk else None,
+                               pk[1].data_ptr() if pk else None)
 
         self._layers = (_ffi.Layer * c.layers)()
         for i, L in enumerate(self.L):
@@ -77,7 +89,7 @@ class FusedQwen:
                 lin(L["qkv"], c.qkv_rows, c.hidden), lin(L["o"], c.hidden, c.q_rows),
                 lin(L["gu"], 2 * c.ffn, c.hidden), lin(L["down"], c.hidden, c.ffn),
                 self.kc[i].data_ptr(), self.vc[i].data_ptr())
-        head = lin(self.head, c.vocab, c.hidden) if self.head is not None else _ffi.Linear(None, None, 0, 0)
+        head = lin(self.head, c.vocab, c.hidden) if self.head is not None else _ffi.Linear(None, None, 0, 0, None, None)
         return _ffi.DecodeDesc(
             c.layers, c.hidden, c.ffn, c.n_heads, c.n_kv_heads, c.head_dim, c.vocab, self.max_len, c.eps, self.scale,
             self.embed.data_ptr(), C.cast(self._layers, C.POINTER(_ffi.Layer)), self.norm.data_ptr(), head,
@@ -98,8 +110,9 @@ class FusedQwen:
             raise _ffi.Q4BError(_ffi.E_TIMEOUT, "decode step: a bounded wait on the tensor-core pipeline expired")
 
     def gemv(self, name, wsplit, X, Y, aux, N, Kdim, epi):
-        if self.tensor_core and Kdim % 256 == 0:
-            _ffi.call("q4b_gemv_q4_0_tc", wsplit[0].data_ptr(), wsplit[1].data_ptr(), X.data_ptr(), Y.data_ptr(),
+        pk = self.packed.get(id(wsplit[0]))
+        if pk is not None:
+            _ffi.call("q4b_gemv_q4_0_tc", pk[0].data_ptr(), pk[1].data_ptr(), X.data_ptr(), Y.data_ptr(),
                       0 if aux is None else aux.data_ptr(), N, Kdim, _ffi.EPI[epi], _ffi.X_F16, self.status.data_ptr(),
                       torch.cuda.current_stream().cuda_stream)
         else:
@@ -110,8 +123,9 @@ class FusedQwen:
 
     def norm_gemv(self, nw, wsplit, Y, aux, N, Kdim, epi):
         """RMSNorm(h) * nw followed by a linear; one launch on the tensor-core path."""
-        if self.tensor_core and Kdim % 256 == 0:
-            _ffi.call("q4b_rmsnorm_gemv_q4_0_tc", wsplit[0].data_ptr(), wsplit[1].data_ptr(), self.h.data_ptr(),
+        pk = self.packed.get(id(wsplit[0]))
+        if pk is not None:
+            _ffi.call("q4b_rmsnorm_gemv_q4_0_tc", pk[0].data_ptr(), pk[1].data_ptr(), self.h.data_ptr(),
                       nw.data_ptr(), float(self.cfg.eps), Y.data_ptr(), 0 if aux is None else aux.data_ptr(), N, Kdim,
                       _ffi.EPI[epi], self.status.data_ptr(), torch.cuda.current_stream().cuda_stream)
         else:

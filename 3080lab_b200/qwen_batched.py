@@ -22,6 +22,19 @@ def blockdot(W, xq, M: int, K: int, mode: int = 0) -> torch.Tensor:
     return out
 
 
+def pack_q4(W, S):
+    """Canonical Q4_0 (W int32 [N, K/8], S fp16 [N, K/32]) -> tile-packed (Wt int32 [T, K/32, 128, 4], St fp16
+    [T, K/32, 128]) for the tensor-core kernels; same bytes, last row tile zero-padded (the reference repacks for its
+    tensor-core kernels likewise: pack_q4_mma / pack_q4_i8, lab/qwen_batched.py:394-436, 987-1013)."""
+    N, KW = W.shape
+    K = KW * 8
+    T = (N + 127) // 128
+    Wt = torch.empty(T, K // 32, 128, 4, dtype=torch.int32, device=W.device)
+    St = torch.empty(T, K // 32, 128, dtype=torch.float16, device=W.device)
+    _ffi.call("q4b_pack_q4_0", _p(W), _p(S), _p(Wt), _p(St), N, K, _stream())
+    return Wt, St
+
+
 class Status:
     """The uint32 status word the tensor-core kernels set when a bounded device-side wait expires."""
 
@@ -35,7 +48,8 @@ class Status:
 
 
 def gemv_tc(W, S, X, Y, aux, N: int, K: int, epi: str, status: Status) -> None:
-    """Exact Q4_0 GEMV of one activation vector on the int8 tensor cores; same contract as qwen_kernels.gemv."""
+    """Exact Q4_0 GEMV of one activation vector on the int8 tensor cores; same contract as qwen_kernels.gemv, with
+    (W, S) tile-packed by `pack_q4`."""
     xd = _ffi.X_F16 if X.dtype == torch.float16 else _ffi.X_F32
     if X.dtype not in (torch.float16, torch.float32):
         raise TypeError("X must be fp16 or fp32")

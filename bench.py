@@ -174,16 +174,29 @@ def run_reference(args, rank: int) -> None:
 
 
 # ----------------------------------------------------------------------------------------------------------- GPU arm
-def time_kernel(fn, n: int, torch):
-    """Average device time of n back-to-back launches on the current stream, in microseconds."""
-    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+def time_kernel(fn, launches: int, reps: int, torch):
+    """Average device time per launch, in microseconds: `fn` (which issues `launches` launches on the current stream) is
+    captured in a CUDA graph so the host's launch rate does not limit it, replayed `reps` times between CUDA events."""
+    fn()
     torch.cuda.synchronize()
-    s.record()
-    for _ in range(n):
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
         fn()
+    torch.cuda.current_stream().wait_stream(side)
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        fn()
+    torch.cuda.synchronize()
+    for _ in range(3):
+        g.replay()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    for _ in range(reps):
+        g.replay()
     e.record()
     torch.cuda.synchronize()
-    return 1e3 * s.elapsed_time(e) / n
+    return 1e3 * s.elapsed_time(e) / (reps * launches)
 
 
 def run_ours(args, rank: int, world: int, local_rank: int) -> None:
@@ -279,26 +292,25 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
     # ---- roofline of the dominant kernels, timed alone on this stream (rank 0)
     peaks, peak_kind = measured_peaks()
     c = cfg
-    rep = 5
+    rep = 10
     def gu_all():
         for L in m.L:
-            m.gemv("gu", L["gu"], m.x, m.xm, None, 2 * c.ffn, c.hidden, "swiglu")
+            m.norm_gemv(L["ln2"], L["gu"], m.xm, None, 2 * c.ffn, c.hidden, "swiglu")
     def down_all():
         for L in m.L:
             m.gemv("down", L["down"], m.xm, m.h, None, c.hidden, c.ffn, "resid")
     def head_once():
         K.head_argmax(m.embed, m.x, m.logits, None, None, m.head_ws)
-    for f in (gu_all, down_all, head_once):
-        f()
-    us_gu = time_kernel(gu_all, rep, torch) / c.layers
-    us_down = time_kernel(down_all, rep, torch) / c.layers
-    us_head = time_kernel(head_once, rep, torch)
-    b_gu = 2 * c.ffn * c.hidden // 32 * 18 + c.hidden * 2 + c.ffn * 2
+    # each graph walks all 28 layers' matrices (433 MB / 218 MB / 467 MB per replay: larger than the 126 MB L2)
+    us_gu = time_kernel(gu_all, c.layers, rep, torch)
+    us_down = time_kernel(down_all, c.layers, rep, torch)
+    us_head = time_kernel(head_once, 1, rep, torch)
+    b_gu = 2 * c.ffn * c.hidden // 32 * 18 + c.hidden * 4 + c.ffn * 2
     b_down = c.hidden * c.ffn // 32 * 18 + c.ffn * 2 + c.hidden * 8
     b_head = c.head_bytes() + c.hidden * 2 + c.vocab * 4
     gname = "mmq_stream (tcgen05 exact GEMV)" if m.tensor_core else "gemv_q4_0 (CUDA cores)"
     kern = {
-        f"{gname} gate_up 17920x1536 (+swiglu)": (b_gu, us_gu, c.layers),
+        f"{gname} rmsnorm + gate_up 17920x1536 (+swiglu)": (b_gu, us_gu, c.layers),
         f"{gname} down 1536x8960 (+resid)": (b_down, us_down, c.layers),
         "head_f16_argmax 151936x1536": (b_head, us_head, 1),
     }

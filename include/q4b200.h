@@ -17,6 +17,8 @@
  *     lab/qwen_batched.py:659-661, lab/qwen_kernels.py:280).
  *
  * Layouts
+ *   Q4_0 tile-packed (tensor-core kernels): Wt int32 [T, K/32, 128, 4], St fp16 [T, K/32, 128] with T = ceil(N/128):
+ *   the 16 bytes of (row r of tile t, k-block b) sit at ((t * K/32 + b) * 128 + r) * 16; made by q4b_pack_q4_0.
  *   Q4_0 canonical: W int32 [N, K/8], nibble i of word w = weight 8w+i, value (nibble-8)*d; S fp16 [N, K/32]
  *   (scripts/qwen_gguf.py:44-60).  K must be a multiple of 32; W and S 16-byte aligned.
  *   Activations fp16, residual stream and logits fp32, KV cache fp16 [B, NKV, max_len, HD] per layer,
@@ -110,29 +112,42 @@ int q4b_argmax_advance(const float* logits, int rows, int V, int64_t* tok, int64
 int q4b_blockdot_q4_0_q8_1(const void* W, const void* xq, int32_t* out, int M, int K, int P, int mode,
                            uint32_t* status, q4b_stream_t stream);
 
+/* Repack canonical Q4_0 into the tile-packed layout (same bytes, last tile zero-padded).  Wt needs
+ * ceil(N/128) * 128 * K/2 bytes, St ceil(N/128) * 128 * K/32 * 2 bytes.  Counterpart of the reference's repackers
+ * pack_q4_mma / pack_q4_i8 (lab/qwen_batched.py:394-436, 987-1013). */
+int q4b_pack_q4_0(const void* W, const void* S, void* Wt, void* St, int N, int K, q4b_stream_t stream);
+
 /* ---- tensor-core path for decode --------------------------------------------------------------------------------
  * Q4_0 GEMV for one activation vector on the tcgen05 int8 tensor cores, exact: each 32-value block of x is split
  * into signed base-256 digits of a block-fixed-point integer, the digits are the columns of an int8 MMA, and the
  * integer block dots are recombined and scaled in fp32.  Same contract and epilogues as q4b_gemv_q4_0 (it replaces
- * the same launch site, lab/qwen_kernels.py:14-113); K must be a multiple of 256.  Launched with programmatic
+ * the same launch site, lab/qwen_kernels.py:14-113) except that the weights are passed TILE-PACKED (Wt, St from
+ * q4b_pack_q4_0); K must be a multiple of 256.  Launched with programmatic
  * dependent launch: the weight prefetch overlaps the kernel that precedes it in the stream.
  * status: one uint32, set to 1 if a bounded device-side wait expired (zero it once; check when convenient). */
-int q4b_gemv_q4_0_tc(const void* W, const void* S, const void* X, void* Y, const void* AUX, int N, int K, int epilogue,
+int q4b_gemv_q4_0_tc(const void* Wt, const void* St, const void* X, void* Y, const void* AUX, int N, int K, int epilogue,
                      int x_dtype, uint32_t* status, q4b_stream_t stream);
+
+/* Optional in-kernel timeline of the tensor-core kernels: while a buffer is set, thread 0 of every CTA writes up to 15
+ * %globaltimer stamps (ns) at its phase boundaries into buffer[cta * 16 ..], and the count into entry 15.  The
+ * reference has the same facility (`timed=True`, lab/qwen_kernels.py:46-53).  entries >= 4096 * 16; null switches it
+ * off.  Host-side global state: not thread-safe, meant for profiling runs. */
+int q4b_trace_buffer(uint64_t* device_buffer, size_t entries);
 
 /* RMSNorm fused in front of q4b_gemv_q4_0_tc: x = round16(h * rsqrt(mean(h^2) + eps) * norm_w) is formed while the
  * activation operand is staged, so the norm costs no launch (the reference tried the opposite fusion, norm in the
  * tail of the producing GEMV, lab/qwen_kernels.py:54-85, and measured it slower).  h, norm_w fp32 [K]. */
-int q4b_rmsnorm_gemv_q4_0_tc(const void* W, const void* S, const float* h, const float* norm_w, float eps, void* Y,
+int q4b_rmsnorm_gemv_q4_0_tc(const void* Wt, const void* St, const float* h, const float* norm_w, float eps, void* Y,
                              const void* AUX, int N, int K, int epilogue, uint32_t* status, q4b_stream_t stream);
 
 /* Q8_1 x Q4_0 matrix product ("MMQ") for P <= 32 activation rows (batched decode): Y[p, n] = epilogue(sum over
  * k-blocks of dw[n, b] * dx[p, b] * dot(p, n, b)) with exact int32 block dots.  Replaces the launch of
  * gemm_q4i8_ms_source (lab/qwen_batched.py:1271-1561; host Prefill.gemm8 scripts/qwen_prefill.py:176-190) and, for
  * batched decode, of gemv_v2_source (lab/qwen_batched.py:467-641; host Batched.gemv
- * scripts/qwen_batched_decode.py:138-154).  xq int8 [P, K], xd fp16 [P, K/32]; Y rows have pitch ldy elements:
+ * scripts/qwen_batched_decode.py:138-154).  Weights tile-packed; xq int8 [P, K], xd fp16 [P, K/32]; Y rows have pitch
+ * ldy elements:
  * store/biasf fp16 [P, ldy], resid/logits fp32 [P, ldy], swiglu fp16 [P, ldy] with N/2 outputs per row. */
-int q4b_mmq_q4_0_q8_1(const void* W, const void* S, const void* xq, const void* xd, void* Y, const void* AUX, int N,
+int q4b_mmq_q4_0_q8_1(const void* Wt, const void* St, const void* xq, const void* xd, void* Y, const void* AUX, int N,
                       int K, int P, int epilogue, int ldy, uint32_t* status, q4b_stream_t stream);
 
 /* Q8_1 quantiser: xq int8 [rows, K], xd fp16 [rows, K/32] (= amax/127 rounded to fp16), xsum fp16 [rows, K/32]
@@ -152,9 +167,11 @@ int q4b_rmsnorm_q8_1(const float* h, const float* w, void* xq, void* xd, void* x
  * GEMV(+residual), then final rmsnorm -> LM head -> argmax, pos += 1.  The descriptor is a HOST struct of device
  * pointers; the caller owns every buffer.  `layer` points to a host array of `layers` entries. */
 typedef struct {
-  const void* W;   /* int32 [N, K/8] */
-  const void* S;   /* fp16  [N, K/32] */
+  const void* W;   /* canonical: int32 [N, K/8] */
+  const void* S;   /* canonical: fp16  [N, K/32] */
   int N, K;
+  const void* Wt;  /* tile-packed copy for the tensor-core path, or null */
+  const void* St;
 } q4b_linear;
 
 typedef struct {

@@ -42,7 +42,8 @@ def test_gemv_tc_matches_oracle(QB, n, k, xdt):
     ref = o.gemv_ref(W, S, x)
     st = QB.Status("cuda")
     y = torch.full((n + 8,), float("nan"), device="cuda")
-    Wd, Sd, xd = dev(W), dev(S), dev(x)
+    Wd, Sd = QB.pack_q4(dev(W), dev(S))
+    xd = dev(x)
     QB.gemv_tc(Wd, Sd, xd, y, None, n, k, "logits", st)
     st.check()
     got = y.cpu().numpy()
@@ -60,7 +61,7 @@ def test_gemv_tc_ffn_up_golden(QB, golden):
     W = pkg("gguf").pack_nibbles(q)
     st = QB.Status("cuda")
     y = torch.empty(8960, device="cuda")
-    QB.gemv_tc(dev(W), dev(d), dev(x), y, None, 8960, 1536, "logits", st)
+    QB.gemv_tc(*QB.pack_q4(dev(W), dev(d)), dev(x), y, None, 8960, 1536, "logits", st)
     st.check()
     got = y.cpu().numpy()
     assert nerr(got, g["y_ref_f64"]) < 2e-6
@@ -74,7 +75,8 @@ def test_gemv_tc_epilogues(QB, n, k):
     W, S = rand_q4(rng, n, k)
     x = rng.standard_normal(k).astype(np.float16)
     acc = o.gemv_ref(W, S, x)
-    Wd, Sd, xd = dev(W), dev(S), dev(x)
+    Wd, Sd = QB.pack_q4(dev(W), dev(S))
+    xd = dev(x)
     st = QB.Status("cuda")
     y = torch.empty(n, dtype=torch.float16, device="cuda")
     QB.gemv_tc(Wd, Sd, xd, y, None, n, k, "store", st)
@@ -103,7 +105,7 @@ def test_gemv_tc_matches_cuda_core_gemv(QB):
     a, b = torch.empty(n, device="cuda"), torch.empty(n, device="cuda")
     st = QB.Status("cuda")
     K.gemv(Wd, Sd, xd, a, None, n, k, "logits")
-    QB.gemv_tc(Wd, Sd, xd, b, None, n, k, "logits", st)
+    QB.gemv_tc(*QB.pack_q4(Wd, Sd), xd, b, None, n, k, "logits", st)
     st.check()
     assert nerr(b.cpu().numpy(), a.cpu().numpy()) < 2e-6
 
@@ -159,7 +161,7 @@ def test_mmq_stream_q8_matches_oracle(QB, P, n, k):
     ref = o.mmq(W, S, xq, xd)
     st = QB.Status("cuda")
     y = torch.full((P, n), float("nan"), device="cuda")
-    QB.gemm8(dev(W), dev(S), dev(xq), dev(xd), y, None, n, k, P, "logits", n, st)
+    QB.gemm8(*QB.pack_q4(dev(W), dev(S)), dev(xq), dev(xd), y, None, n, k, P, "logits", n, st)
     st.check()
     assert nerr(y.cpu().numpy(), ref) < 2e-6
 
@@ -172,7 +174,8 @@ def test_mmq_stream_q8_epilogues(QB):
     x = rng.standard_normal((P, k)).astype(np.float16)
     xq, xd, _ = o.quant_q8_1(x)
     acc = o.mmq(W, S, xq, xd)
-    Wd, Sd, xqd, xdd = dev(W), dev(S), dev(xq), dev(xd)
+    Wd, Sd = QB.pack_q4(dev(W), dev(S))
+    xqd, xdd = dev(xq), dev(xd)
     st = QB.Status("cuda")
     bias = (0.1 * rng.standard_normal(n)).astype(np.float32)
     y = torch.empty(P, n, dtype=torch.float16, device="cuda")
@@ -186,6 +189,41 @@ def test_mmq_stream_q8_epilogues(QB):
     QB.gemm8(Wd, Sd, xqd, xdd, ys, None, n, k, P, "swiglu", n // 2, st)
     assert nerr(ys.float().cpu().numpy(), o.silu_mul(acc[:, 0::2], acc[:, 1::2])) < 1e-3
     st.check()
+
+
+def test_pack_q4_layout(QB):
+    rng = np.random.default_rng(8)
+    n, k = 200, 512
+    W, S = rand_q4(rng, n, k)
+    Wt, St = QB.pack_q4(dev(W), dev(S))
+    Wt, St = Wt.cpu().numpy(), St.cpu().numpy()
+    KB = k // 32
+    Wp = np.full((256, KB, 4), np.uint32(0x88888888).view(np.int32), np.int32)
+    Wp[:n] = W.reshape(n, KB, 4)
+    Sp = np.zeros((256, KB), np.float16)
+    Sp[:n] = S
+    assert np.array_equal(Wt, Wp.reshape(2, 128, KB, 4).transpose(0, 2, 1, 3))
+    assert np.array_equal(St, Sp.reshape(2, 128, KB).transpose(0, 2, 1))
+
+
+def test_rmsnorm_gemv_tc_fused(QB):
+    o = oracle()
+    ffi = pkg("_ffi")
+    rng = np.random.default_rng(21)
+    for n, k in ((2048, 1536), (17920, 1536), (768, 512)):
+        W, S = rand_q4(rng, n, k)
+        h = (3 * rng.standard_normal(k)).astype(np.float32)
+        nw = (1 + 0.1 * rng.standard_normal(k)).astype(np.float32)
+        x16 = o.rmsnorm(h, nw, 1e-6)
+        ref = o.gemv_ref(W, S, x16)
+        Wt, St = QB.pack_q4(dev(W), dev(S))
+        st = QB.Status("cuda")
+        y = torch.empty(n, device="cuda")
+        hd, nwd = dev(h), dev(nw)
+        ffi.call("q4b_rmsnorm_gemv_q4_0_tc", Wt.data_ptr(), St.data_ptr(), hd.data_ptr(), nwd.data_ptr(), 1e-6, y.data_ptr(),
+                 None, n, k, ffi.EPI["logits"], st.word.data_ptr(), torch.cuda.current_stream().cuda_stream)
+        st.check()
+        assert nerr(y.cpu().numpy(), ref) < 1e-3          # x may differ from the oracle's by one fp16 ulp in places
 
 
 def test_mmq_stream_rejects_bad_shapes(QB):
