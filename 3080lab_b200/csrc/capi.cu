@@ -41,6 +41,7 @@ int attn_decode(const void*, const float*, const float*, const int64_t*, void*, 
                 void*, size_t, cudaStream_t);
 size_t head_workspace(int);
 int head_f16_argmax(const void*, const void*, float*, int, int, int64_t*, int64_t*, void*, size_t, cudaStream_t);
+int head_f16_batched(const void*, const void*, float*, int, int, int, cudaStream_t);
 int blockdot(const void*, const void*, int32_t*, int, int, int, int, uint32_t*, cudaStream_t);
 int mmq_stream(const void*, const void*, const void*, const void*, void*, const void*, int, int, int, int, int, int, uint32_t*,
                cudaStream_t, const float* norm_w = nullptr, float eps = 0.f);
@@ -104,6 +105,10 @@ size_t q4b_head_workspace(int V) { return head_workspace(V); }
 int q4b_head_f16_argmax(const void* E, const void* x, float* logits, int V, int H, int64_t* tok, int64_t* pos,
                         void* workspace, size_t workspace_bytes, q4b_stream_t stream) {
   return head_f16_argmax(E, x, logits, V, H, tok, pos, workspace, workspace_bytes, S(stream));
+}
+
+int q4b_head_f16_batched(const void* E, const void* x, float* logits, int V, int H, int B, q4b_stream_t stream) {
+  return head_f16_batched(E, x, logits, V, H, B, S(stream));
 }
 
 size_t q4b_argmax_workspace(int rows, int V) { return argmax_workspace(rows, V); }

@@ -206,3 +206,120 @@ def run_fused(m: FusedQwen, ids, gen: int):
     e.record()
     torch.cuda.synchronize()
     return toks, s.elapsed_time(e) / gen
+
+
+class Batched:
+    """B concurrent sequences, one decode token each per `step()` — the reference's `Batched(m, B)`
+    (scripts/qwen_batched_decode.py:86-187) with the linears routed through Q8_1 activations and the int8
+    tensor-core MMQ, as the target configuration asks (the reference's batched path uses fp16 `mma` on dequantised
+    weights; its int8 MMQ serves prefill, scripts/qwen_prefill.py:176-246).  Shares the weights of a `FusedQwen`.
+    KV cache [L, B, NKV, max_len, HD] (scripts/qwen_batched_decode.py:99)."""
+
+    def __init__(self, m: FusedQwen, B: int):
+        if not 1 <= B <= 32:
+            raise ValueError("1 <= B <= 32 sequences")
+        if not m.tensor_core or m.cfg.hidden % 256 or m.cfg.q_rows % 256 or m.cfg.ffn % 256:
+            raise ValueError("the batched path needs tile-packed weights (K multiples of 256)")
+        self.m, self.B = m, B
+        c, dv = m.cfg, m.device
+        f16, f32 = torch.float16, torch.float32
+        self.h = torch.zeros(B, c.hidden, dtype=f32, device=dv)
+        self.x = torch.zeros(B, c.hidden, dtype=f16, device=dv)
+        self.qkv = torch.zeros(B, c.qkv_rows, dtype=f16, device=dv)
+        self.att = torch.zeros(B, c.q_rows, dtype=f16, device=dv)
+        self.xm = torch.zeros(B, c.ffn, dtype=f16, device=dv)
+        kmax = max(c.hidden, c.q_rows, c.ffn)
+        self.xq = torch.zeros(B * kmax, dtype=torch.int8, device=dv)
+        self.xd = torch.zeros(B * kmax // 32, dtype=f16, device=dv)
+        self.logits = torch.zeros(B, c.vocab, dtype=f32, device=dv)
+        self.tok = torch.zeros(B, dtype=torch.long, device=dv)
+        self.pos = torch.zeros(B, dtype=torch.long, device=dv)
+        self.kc = torch.zeros(c.layers, B, c.n_kv_heads, m.max_len, c.head_dim, dtype=f16, device=dv)
+        self.vc = torch.zeros_like(self.kc)
+        self.attn_ws = K.attn_workspace(B, c.n_heads, c.head_dim, m.max_len, dv)
+        self.head_ws = K.head_workspace(c.vocab, B, dv)
+        self.status = QB.Status(dv)
+        self.launches_per_step = 1 + 9 * c.layers + 3
+
+    def gemm8(self, pair, N, Kdim, Y, aux, epi, ldy):
+        Wt, St = self.m.packed[id(pair[0])]
+        QB.gemm8(Wt, St, self.xq, self.xd, Y, aux, N, Kdim, self.B, epi, ldy, self.status)
+
+    def step(self) -> None:
+        m, c, B = self.m, self.m.cfg, self.B
+        H = c.hidden
+        K.embed(m.embed, self.tok, self.h)
+        for i, L in enumerate(m.L):
+            QB.rmsnorm_q8(self.h, L["ln1"], self.xq, self.xd, c.eps)
+            self.gemm8(L["qkv"], c.qkv_rows, H, self.qkv, L["qkv_b"], "biasf", c.qkv_rows)
+            K.attn(self.qkv, m.cos, m.sin, self.pos, self.kc[i], self.vc[i], self.att, c.n_heads, c.n_kv_heads, c.head_dim,
+                   m.max_len, m.scale, self.attn_ws)
+            QB.quant_q8(self.att, self.xq, self.xd)
+            self.gemm8(L["o"], H, c.q_rows, self.h, None, "resid", H)
+            QB.rmsnorm_q8(self.h, L["ln2"], self.xq, self.xd, c.eps)
+            self.gemm8(L["gu"], 2 * c.ffn, H, self.xm, None, "swiglu", c.ffn)
+            QB.quant_q8(self.xm, self.xq, self.xd)
+            self.gemm8(L["down"], H, c.ffn, self.h, None, "resid", H)
+        if m.head is None:
+            K.rms(self.h, m.norm, self.x, c.eps)
+            QB.head_batched(m.embed, self.x, self.logits)
+        else:
+            QB.rmsnorm_q8(self.h, m.norm, self.xq, self.xd, c.eps)
+            self.gemm8(m.head, c.vocab, H, self.logits, None, "logits", c.vocab)
+        K.finish(self.logits, self.tok, self.pos, self.head_ws)
+
+    def reset(self) -> None:
+        self.kc.zero_()
+        self.vc.zero_()
+        self.pos.zero_()
+        self.tok.zero_()
+
+    def feed(self, prompts) -> None:
+        """prompts: int array [B, P]; every sequence advances one prompt token per step."""
+        prompts = np.asarray(prompts)
+        for j in range(prompts.shape[1]):
+            self.tok.copy_(torch.from_numpy(np.ascontiguousarray(prompts[:, j])).to(self.tok.device))
+            self.step()
+
+    def capture(self) -> torch.cuda.CUDAGraph:
+        torch.cuda.synchronize()
+        pos0, tok0 = self.pos.clone(), self.tok.clone()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            self.step()
+        torch.cuda.current_stream().wait_stream(side)
+        self.pos.copy_(pos0)
+        self.tok.copy_(tok0)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            self.step()
+        self.pos.copy_(pos0)
+        self.tok.copy_(tok0)
+        torch.cuda.synchronize()
+        return g
+
+
+def run_batched(bm: Batched, prompts, gen: int):
+    """Greedy decode of B sequences after their prompts, by graph replay (scripts/qwen_batched_decode.py:203-237).
+    -> (tokens [B, gen], ms per step of a second, timed pass)."""
+    bm.reset()
+    bm.feed(prompts)
+    g = bm.capture()
+    pos0, tok0 = bm.pos.clone(), bm.tok.clone()
+    seqs = [tok0.clone()]
+    for _ in range(gen - 1):
+        g.replay()
+        seqs.append(bm.tok.clone())
+    toks = torch.stack(seqs, 1).cpu().numpy()
+    bm.status.check("batched decode")
+    bm.pos.copy_(pos0)
+    bm.tok.copy_(tok0)
+    torch.cuda.synchronize()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    for _ in range(gen):
+        g.replay()
+    e.record()
+    torch.cuda.synchronize()
+    return toks, s.elapsed_time(e) / gen

@@ -95,6 +95,11 @@ size_t q4b_head_workspace(int V);
 int q4b_head_f16_argmax(const void* E, const void* x, float* logits, int V, int H, int64_t* tok, int64_t* pos,
                         void* workspace, size_t workspace_bytes, q4b_stream_t stream);
 
+/* LM head over the tied fp16 table for B = 1..32 sequences: logits fp32 [B, V] = x fp16 [B, H] . E fp16 [V, H]^T.
+ * Replaces head_v2_source / the cuBLAS fp16 head of the batched engine (lab/qwen_batched.py:681-833,
+ * scripts/qwen_batched_decode.py:172-185).  H a multiple of 32.  Follow with q4b_argmax_advance for the greedy pick. */
+int q4b_head_f16_batched(const void* E, const void* x, float* logits, int V, int H, int B, q4b_stream_t stream);
+
 /* Greedy pick over fp32 logits [rows, V]: tok[r] = lowest index among the maxima of row r; pos[r] += 1.
  * Replaces FINISH / FINISH_MB (lab/qwen_kernels.py:222-282) and the torch.argmax of the batched engine
  * (scripts/qwen_batched_decode.py:186-187).  workspace: q4b_argmax_workspace(rows, V) bytes, zero-filled once. */
