@@ -46,6 +46,10 @@ int blockdot(const void*, const void*, int32_t*, int, int, int, int, uint32_t*, 
 int mmq_stream(const void*, const void*, const void*, const void*, void*, const void*, int, int, int, int, int, int, uint32_t*,
                cudaStream_t, const float* norm_w = nullptr, float eps = 0.f);
 void mmq_stream_trace(unsigned long long*);
+size_t q8_tiled_bytes(int, int);
+int mmq_prefill(const void*, const void*, const void*, void*, const void*, int, int, int, int, int, uint32_t*, cudaStream_t);
+int quant_q8_1_tiled(const void*, void*, int, int, cudaStream_t);
+int rmsnorm_q8_1_tiled(const float*, const float*, void*, int, int, float, cudaStream_t);
 int pack_q4_0(const void*, const void*, void*, void*, int, int, cudaStream_t);
 int quant_q8_1(const void*, void*, void*, void*, int, int, cudaStream_t);
 int rmsnorm_q8_1(const float*, const float*, void*, void*, void*, void*, int, int, float, cudaStream_t);
@@ -132,6 +136,21 @@ int q4b_gemv_q4_0_tc(const void* W, const void* Sc, const void* X, void* Y, cons
 
 int q4b_pack_q4_0(const void* W, const void* Sc, void* Wt, void* St, int N, int K, q4b_stream_t stream) {
   return pack_q4_0(W, Sc, Wt, St, N, K, S(stream));
+}
+
+size_t q4b_q8_tiled_bytes(int rows, int K) { return (rows > 0 && K > 0) ? q8_tiled_bytes(rows, K) : 0; }
+
+int q4b_quant_q8_1_tiled(const void* x, void* xt, int rows, int K, q4b_stream_t stream) {
+  return quant_q8_1_tiled(x, xt, rows, K, S(stream));
+}
+
+int q4b_rmsnorm_q8_1_tiled(const float* h, const float* w, void* xt, int rows, int H, float eps, q4b_stream_t stream) {
+  return rmsnorm_q8_1_tiled(h, w, xt, rows, H, eps, S(stream));
+}
+
+int q4b_mmq_prefill_q4_0_q8_1(const void* Wt, const void* St, const void* xt, void* Y, const void* AUX, int N, int K, int P,
+                              int epilogue, int ldy, uint32_t* status, q4b_stream_t stream) {
+  return mmq_prefill(Wt, St, xt, Y, AUX, N, K, P, epilogue, ldy, status, S(stream));
 }
 
 int q4b_trace_buffer(uint64_t* device_buffer, size_t entries) {

@@ -1,0 +1,272 @@
+// Q8_1 x Q4_0 matrix product for prefill (hundreds to thousands of activation rows) on the tcgen05 int8 tensor cores.
+//
+//   Y[p, m] = epilogue( sum_b dw[m, b] * dx[p, b] * dot_b[m, p] ),  dot_b exact int32 over one 32-weight block
+//
+// the arithmetic of the reference's MMQ (gemm_q4i8_ms_source, lab/qwen_batched.py:1271-1561; block arithmetic
+// :1237-1243): one int8 MMA per k-block because every block has its own pair of scales, fp32 rescale-and-add per block
+// in ascending k order.  What changes is where things live on Blackwell:
+//   * CTA tile = 128 weight rows (UMMA M) x 128 activation rows (UMMA N); one tcgen05.mma.kind::i8 (K = 32) per k-block
+//     into one of two TMEM accumulator slots (128 columns each);
+//   * weights arrive tile-packed through bulk (TMA) copies in batches of 8 k-blocks (ring of 4); thread r of the first
+//     warpgroup expands row r's nibbles to signed bytes and writes them into TMEM as the A operand (tcgen05.st);
+//   * activations arrive pre-tiled from the quantiser (quant_q8_1.cu, "tiled" outputs): per (128-row tile, k-block)
+//     4096 bytes already in the UMMA K-major core-matrix order + 128 fp32 block scales, one bulk copy per stage
+//     (ring of 8), used directly as the B operand;
+//   * warp 8 (one thread) issues copies and MMAs; warpgroup 0 expands A and rescales accumulator columns 0..63,
+//     warpgroup 1 rescales columns 64..127; the rescale of k-block b overlaps the MMA of b+1 and the expansion of b+2.
+// The per-block rescale (one int->float, two multiplies/FMAs per output per k-block) is CUDA-core work of the same
+// order as the tensor-core time at full rate; it is the structural cost of Q4_0 x Q8_1 and bounds this kernel.
+// All waits are bounded; after the first expired wait a thread stops waiting (status word, garbage out, no hang).
+#include "q4b_internal.h"
+#include "tc05.cuh"
+
+namespace q4b {
+
+namespace {
+
+constexpr int PF_WG = 128, PF_THREADS = 2 * PF_WG + 32;
+constexpr int NTOK = 128;                 // activation rows per CTA tile (UMMA N)
+constexpr int SB = 8;                     // activation stages (one k-block each)
+constexpr int WB = 4;                     // weight batches in flight (8 k-blocks each)
+constexpr uint32_t STAGE_BYTES = 4096 + 512;
+constexpr uint32_t WBATCH_W = 8 * 2048, WBATCH_S = 8 * 256;
+constexpr size_t PF_SMEM = (size_t)WB * (WBATCH_W + WBATCH_S) + (size_t)SB * STAGE_BYTES + 128;
+
+struct PrefillArgs {
+  const uint8_t* Wt;   // tile-packed nibbles
+  const __half* St;    // tile-packed scales
+  const uint8_t* Xt;   // tiled Q8_1 activations [P/128][K/32][4608]
+  void* Y;
+  const void* AUX;
+  uint32_t* status;
+  int N, K, P, epi, ldy;
+};
+
+__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   tc::smem_u32(dst)),
+               "l"(src), "r"(bytes), "r"(tc::smem_u32(bar))
+               : "memory");
+}
+
+// wait unless an earlier wait of this thread already expired
+__device__ __forceinline__ void waitb(uint64_t* bar, uint32_t parity, bool& ok) {
+  if (ok) ok = tc::mbar_wait(bar, parity);
+}
+
+__global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const PrefillArgs a) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  __shared__ __align__(8) uint64_t w_full[WB], w_empty[WB], b_full[SB], b_empty[SB], a_full[2], d_full[2], d_empty[2];
+  __shared__ uint32_t tmem_base_s;
+
+  uint8_t* slabW = smem;                                   // [WB][8][128 rows][16]
+  uint8_t* slabS = slabW + (size_t)WB * WBATCH_W;          // [WB][8][128] fp16
+  uint8_t* stage = slabS + (size_t)WB * WBATCH_S;          // [SB][4608]
+
+  const int t = threadIdx.x, warp = t >> 5;
+  const int KB = a.K >> 5, NBATCH = KB >> 3;
+  const int row_tile = blockIdx.x, tok_tile = blockIdx.y;
+  const size_t wbase = (size_t)row_tile * KB;              // k-block index of this row tile in the packed arrays
+  const uint8_t* xbase = a.Xt + (size_t)tok_tile * KB * STAGE_BYTES;
+
+  if (warp == 0) {
+    tc::tmem_alloc(&tmem_base_s, 512);
+    tc::tmem_relinquish();
+  }
+  if (t == 0) {
+    for (int i = 0; i < WB; ++i) {
+      tc::mbar_init(&w_full[i], 1);
+      tc::mbar_init(&w_empty[i], 2 * PF_WG);
+    }
+    for (int i = 0; i < SB; ++i) {
+      tc::mbar_init(&b_full[i], 1);
+      tc::mbar_init(&b_empty[i], 1 + 2 * PF_WG);
+    }
+    for (int i = 0; i < 2; ++i) {
+      tc::mbar_init(&a_full[i], PF_WG);
+      tc::mbar_init(&d_full[i], 1);
+      tc::mbar_init(&d_empty[i], 2 * PF_WG);
+    }
+    tc::mbar_fence_init();
+  }
+  tc::fence_before_sync();
+  __syncthreads();
+  tc::fence_after_sync();
+  pdl_launch_dependents();
+  const uint32_t tmem = tmem_base_s;
+  const uint32_t tmem_a = tmem, tmem_d = tmem + 128;       // A: 2 x 8 columns; D: 2 x 128 columns
+  constexpr uint32_t IDESC = tc::idesc_i8(128, NTOK);
+  bool ok = true;
+
+  if (warp == 8) {
+    // ===================== producer + MMA issuer (one thread) =====================
+    if ((t & 31) == 0) {
+      auto load_w = [&](int j) {                           // weight batch j -> slot j % WB
+        const int s = j % WB;
+        tc::mbar_expect_tx(&w_full[s], WBATCH_W + WBATCH_S);
+        bulk_g2s(slabW + (size_t)s * WBATCH_W, a.Wt + (wbase + (size_t)j * 8) * 2048, WBATCH_W, &w_full[s]);
+        bulk_g2s(slabS + (size_t)s * WBATCH_S, a.St + (wbase + (size_t)j * 8) * 128, WBATCH_S, &w_full[s]);
+      };
+      auto load_b = [&](int b) {                           // activation k-block b -> stage b % SB
+        const int s = b % SB;
+        tc::mbar_expect_tx(&b_full[s], STAGE_BYTES);
+        bulk_g2s(stage + (size_t)s * STAGE_BYTES, xbase + (size_t)b * STAGE_BYTES, STAGE_BYTES, &b_full[s]);
+      };
+      for (int j = 0; j < WB && j < NBATCH; ++j) load_w(j);   // weights do not depend on the previous kernel
+      pdl_wait();                                             // activations do
+      for (int b = 0; b < SB && b < KB; ++b) load_b(b);
+      const uint32_t stage0 = tc::smem_u32(stage);
+      for (int b = 0; b < KB; ++b) {
+        const int slot = b & 1, s = b % SB;
+        waitb(&a_full[slot], (uint32_t)(b >> 1) & 1u, ok);
+        waitb(&b_full[s], (uint32_t)(b / SB) & 1u, ok);
+        if (b >= 2) waitb(&d_empty[slot], (uint32_t)((b - 2) >> 1) & 1u, ok);
+        tc::fence_after_sync();
+        const uint64_t bdesc = tc::smem_desc_kmajor(stage0 + (uint32_t)s * STAGE_BYTES, 128, 256);
+        tc::mma_i8_ts(tmem_d + (uint32_t)slot * 128, tmem_a + (uint32_t)slot * 8, bdesc, IDESC, 0u);
+        tc::mma_commit(&d_full[slot]);
+        tc::mma_commit(&b_empty[s]);
+        // refill with a lag of three k-blocks, so that this thread never waits on a rescale that has only just begun
+        if (b >= 3) {
+          const int ob = b - 3;
+          if (ob + SB < KB) {
+            waitb(&b_empty[ob % SB], (uint32_t)(ob / SB) & 1u, ok);
+            load_b(ob + SB);
+          }
+          if ((ob & 7) == 7) {                             // the last k-block of weight batch ob / 8 has been rescaled
+            const int oj = ob >> 3;
+            if (oj + WB < NBATCH) {
+              waitb(&w_empty[oj % WB], (uint32_t)(oj / WB) & 1u, ok);
+              load_w(oj + WB);
+            }
+          }
+        }
+      }
+    }
+  } else {
+    // ===================== warpgroup 0: expand A + rescale columns 0..63; warpgroup 1: rescale columns 64..127 ======
+    const int wg = t >> 7, r = t & 127;                    // r: row of the tile = TMEM lane
+    const uint32_t lane_off = (uint32_t)(32 * (warp & 3)) << 16;
+    float acc[64];
+#pragma unroll
+    for (int n = 0; n < 64; ++n) acc[n] = 0.f;
+
+    auto rescale = [&](int b) {
+      const int slot = b & 1, s = b % SB, ws = (b >> 3) % WB;
+      waitb(&d_full[slot], (uint32_t)(b >> 1) & 1u, ok);
+      tc::fence_after_sync();
+      uint32_t d[64];
+      const uint32_t dcol = tmem_d + lane_off + (uint32_t)slot * 128 + (uint32_t)wg * 64;
+      tc::tmem_ld16(dcol, d);
+      tc::tmem_ld16(dcol + 16, d + 16);
+      tc::tmem_ld16(dcol + 32, d + 32);
+      tc::tmem_ld16(dcol + 48, d + 48);
+      tc::tmem_wait_ld();
+      tc::fence_before_sync();
+      tc::mbar_arrive(&d_empty[slot]);                     // the accumulator slot may be overwritten
+      const float dw = __half2float(reinterpret_cast<const __half*>(slabS + (size_t)ws * WBATCH_S)[(b & 7) * 128 + r]) * 0.0625f;
+      const float4* sx = reinterpret_cast<const float4*>(stage + (size_t)s * STAGE_BYTES + 4096) + wg * 16;
+#pragma unroll
+      for (int q = 0; q < 16; ++q) {
+        const float4 x4 = sx[q];
+        acc[4 * q + 0] = fmaf(dw * x4.x, (float)(int32_t)d[4 * q + 0], acc[4 * q + 0]);
+        acc[4 * q + 1] = fmaf(dw * x4.y, (float)(int32_t)d[4 * q + 1], acc[4 * q + 1]);
+        acc[4 * q + 2] = fmaf(dw * x4.z, (float)(int32_t)d[4 * q + 2], acc[4 * q + 2]);
+        acc[4 * q + 3] = fmaf(dw * x4.w, (float)(int32_t)d[4 * q + 3], acc[4 * q + 3]);
+      }
+      tc::mbar_arrive(&b_empty[s]);                        // done with this stage's block scales
+      if ((b & 7) == 7) tc::mbar_arrive(&w_empty[ws]);     // done with this weight batch's scales (and nibbles)
+    };
+
+    for (int b = 0; b < KB; ++b) {
+      if ((b & 7) == 0) waitb(&w_full[(b >> 3) % WB], (uint32_t)((b >> 3) / WB) & 1u, ok);
+      if (wg == 0) {
+        const int ws = (b >> 3) % WB, slot = b & 1;
+        const uint4 w = *reinterpret_cast<const uint4*>(slabW + (size_t)ws * WBATCH_W + (size_t)(b & 7) * 2048 + r * 16);
+        uint32_t ex[8];
+        tc::expand_nibbles(w.x, ex[0], ex[1]);
+        tc::expand_nibbles(w.y, ex[2], ex[3]);
+        tc::expand_nibbles(w.z, ex[4], ex[5]);
+        tc::expand_nibbles(w.w, ex[6], ex[7]);
+        // A slot b & 1 was last read by the MMA of k-block b - 2, whose completion this thread saw in rescale(b - 2)
+        tc::tmem_st8(tmem_a + lane_off + (uint32_t)slot * 8, ex);
+        tc::tmem_wait_st();
+        tc::fence_before_sync();
+        tc::mbar_arrive(&a_full[slot]);
+        if (b >= 1) rescale(b - 1);
+      } else {
+        rescale(b);
+      }
+    }
+    if (wg == 0) rescale(KB - 1);
+
+    // ---- epilogue: thread (row r, 64 activation rows)
+    pdl_wait();                                            // Y / AUX may be written by the previous kernel
+    const int row = row_tile * 128 + r;
+    const int tok0 = tok_tile * NTOK + wg * 64;
+#pragma unroll
+    for (int n = 0; n < 64; ++n) {                         // fully unrolled: acc[] must stay in registers
+      const float v = acc[n];
+      const float partner = __shfl_xor_sync(0xffffffffu, v, 1);
+      const int p = tok0 + n;
+      if (p < a.P && row < a.N) {
+        const size_t base = (size_t)p * a.ldy;
+        switch (a.epi) {
+          case Q4B_EPI_STORE: reinterpret_cast<__half*>(a.Y)[base + row] = __float2half_rn(v); break;
+          case Q4B_EPI_BIASF:
+            reinterpret_cast<__half*>(a.Y)[base + row] = __float2half_rn(v + reinterpret_cast<const float*>(a.AUX)[row]);
+            break;
+          case Q4B_EPI_RESID: reinterpret_cast<float*>(a.Y)[base + row] += v; break;
+          case Q4B_EPI_LOGITS: reinterpret_cast<float*>(a.Y)[base + row] = v; break;
+          case Q4B_EPI_SWIGLU:
+            if ((r & 1) == 0) reinterpret_cast<__half*>(a.Y)[base + (row >> 1)] = __float2half_rn(v / (1.f + __expf(-v)) * partner);
+            break;
+          default: break;
+        }
+      }
+    }
+  }
+  if (!ok) atomicExch(a.status, 1u);
+  tc::fence_before_sync();
+  __syncthreads();
+  if (warp == 0) tc::tmem_dealloc(tmem, 512);
+}
+
+}  // namespace
+
+size_t q8_tiled_bytes(int P, int K) { return (size_t)((P + NTOK - 1) / NTOK) * (size_t)(K / 32) * STAGE_BYTES; }
+
+int mmq_prefill(const void* Wt, const void* St, const void* Xt, void* Y, const void* AUX, int N, int K, int P, int epilogue,
+                int ldy, uint32_t* status, cudaStream_t st) {
+  if (N <= 0 || P <= 0 || K <= 0 || (K % 256)) return fail(Q4B_E_SHAPE, "mmq_prefill: N, P > 0 and K a positive multiple of 256 required");
+  if (epilogue < Q4B_EPI_STORE || epilogue > Q4B_EPI_LOGITS) return fail(Q4B_E_ARG, "mmq_prefill: unknown epilogue");
+  if (epilogue == Q4B_EPI_SWIGLU && (N % 2)) return fail(Q4B_E_SHAPE, "mmq_prefill: swiglu needs an even row count");
+  if (!Wt || !St || !Xt || !Y || !status || !aligned16(Wt) || !aligned16(St) || !aligned16(Xt))
+    return fail(Q4B_E_ALIGN, "mmq_prefill: null or misaligned pointer");
+  if (epilogue == Q4B_EPI_BIASF && !AUX) return fail(Q4B_E_ALIGN, "mmq_prefill: biasf needs AUX");
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(mmq_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PF_SMEM);
+    if (e != cudaSuccess) {
+      set_cuda_error(e, "mmq_prefill: cudaFuncSetAttribute");
+      return Q4B_E_CUDA;
+    }
+    configured = true;
+  }
+  PrefillArgs a;
+  a.Wt = reinterpret_cast<const uint8_t*>(Wt);
+  a.St = reinterpret_cast<const __half*>(St);
+  a.Xt = reinterpret_cast<const uint8_t*>(Xt);
+  a.Y = Y;
+  a.AUX = AUX;
+  a.status = status;
+  a.N = N;
+  a.K = K;
+  a.P = P;
+  a.epi = epilogue;
+  a.ldy = ldy;
+  dim3 grid((N + 127) / 128, (P + NTOK - 1) / NTOK);
+  return check_launch(launch_pdl(mmq_prefill_kernel, grid, dim3(PF_THREADS), PF_SMEM, st, a), "mmq_prefill");
+}
+
+}  // namespace q4b

@@ -38,6 +38,61 @@ __device__ __forceinline__ void quant_block4(const float x[4], int8_t* q_out, __
   }
 }
 
+// Tiled output for the prefill MMQ: per (tile of 128 rows, k-block) 4096 bytes in the UMMA K-major core-matrix order
+// (8-row x 16-byte core matrices, the 32 bytes of a block permuted as the nibble expansion permutes the weights:
+// position 4 (2 (i / 8) + (i & 1)) + (i & 7) / 2 for element i) followed by the 128 block scales as fp32.  Lane `sub`
+// holds elements 4 sub .. 4 sub + 3: elements {0, 2} and {1, 3} land on adjacent bytes, two 16-bit stores.
+__device__ __forceinline__ void quant_block4_tiled(const float x[4], uint8_t* tile, int n, int sub) {
+  float amax = fmaxf(fmaxf(fabsf(x[0]), fabsf(x[1])), fmaxf(fabsf(x[2]), fabsf(x[3])));
+#pragma unroll
+  for (int o = 4; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  const float d = amax / 127.f;
+  int q[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) q[i] = d > 0.f ? __float2int_rn(x[i] / d) : 0;
+  const int pos02 = 8 * (sub >> 1) + 2 * (sub & 1), pos13 = pos02 + 4;
+  uint8_t* rowp = tile + (n >> 3) * 256 + (n & 7) * 16;
+  *reinterpret_cast<uint16_t*>(rowp + (pos02 >> 4) * 128 + (pos02 & 15)) = (uint16_t)((q[0] & 0xFF) | ((q[2] & 0xFF) << 8));
+  *reinterpret_cast<uint16_t*>(rowp + (pos13 >> 4) * 128 + (pos13 & 15)) = (uint16_t)((q[1] & 0xFF) | ((q[3] & 0xFF) << 8));
+  if (sub == 0) reinterpret_cast<float*>(tile + 4096)[n] = __half2float(__float2half_rn(d));
+}
+
+__global__ void __launch_bounds__(256) quant_q8_1_tiled_kernel(const __half* x, uint8_t* xt, int P, int KB) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const size_t gid = (size_t)blockIdx.x * 256 + threadIdx.x;
+  const size_t blk = gid >> 3;
+  const int sub = (int)(gid & 7);
+  if (blk >= (size_t)P * KB) return;                 // whole 8-lane groups leave together
+  const int p = (int)(blk / KB), kb = (int)(blk - (size_t)p * KB);
+  const uint2 raw = *reinterpret_cast<const uint2*>(x + blk * 32 + sub * 4);
+  const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&raw.x));
+  const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
+  const float v[4] = {a.x, a.y, b.x, b.y};
+  quant_block4_tiled(v, xt + ((size_t)(p >> 7) * KB + kb) * 4608, p & 127, sub);
+}
+
+__global__ void __launch_bounds__(1024) rmsnorm_q8_1_tiled_kernel(const float* h, const float* __restrict__ w, uint8_t* xt,
+                                                                  int H, float eps) {
+  __shared__ float part[32];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int row = blockIdx.x, t = threadIdx.x, i0 = 4 * t;
+  const float4 hv = *reinterpret_cast<const float4*>(h + (size_t)row * H + i0);
+  const float4 wv = *reinterpret_cast<const float4*>(w + i0);
+  float ss = hv.x * hv.x + hv.y * hv.y + hv.z * hv.z + hv.w * hv.w;
+  ss = warp_sum(ss);
+  if ((t & 31) == 0) part[t >> 5] = ss;
+  __syncthreads();
+  float tot = 0.f;
+  for (int j = 0; j < (int)(blockDim.x >> 5); ++j) tot += part[j];
+  const float r = rsqrtf(tot / (float)H + eps);
+  const float v[4] = {__half2float(__float2half_rn(hv.x * r * wv.x)), __half2float(__float2half_rn(hv.y * r * wv.y)),
+                      __half2float(__float2half_rn(hv.z * r * wv.z)), __half2float(__float2half_rn(hv.w * r * wv.w))};
+  const int KB = H >> 5;
+  quant_block4_tiled(v, xt + ((size_t)(row >> 7) * KB + (i0 >> 5)) * 4608, row & 127, t & 7);
+}
+
 __global__ void __launch_bounds__(256) quant_q8_1_kernel(const __half* x, int8_t* xq, __half* xd, __half* xsum, size_t nblk) {
   pdl_launch_dependents();
   pdl_wait();
@@ -93,6 +148,21 @@ int quant_q8_1(const void* x, void* xq, void* xd, void* xsum, int rows, int K, c
   const size_t threads = nblk * 8;
   return check_launch(launch_pdl(quant_q8_1_kernel, dim3((unsigned)((threads + 255) / 256)), dim3(256), 0, st, (const __half*)x,
                                  (int8_t*)xq, (__half*)xd, (__half*)xsum, nblk), "quant_q8_1");
+}
+
+int quant_q8_1_tiled(const void* x, void* xt, int rows, int K, cudaStream_t st) {
+  if (rows <= 0 || K <= 0 || (K % 32)) return fail(Q4B_E_SHAPE, "quant_q8_1_tiled: rows > 0 and K a positive multiple of 32 required");
+  if (!x || !xt || (reinterpret_cast<uintptr_t>(x) & 7u) || !aligned16(xt)) return fail(Q4B_E_ALIGN, "quant_q8_1_tiled: null or misaligned pointer");
+  const size_t threads = (size_t)rows * (K / 32) * 8;
+  return check_launch(launch_pdl(quant_q8_1_tiled_kernel, dim3((unsigned)((threads + 255) / 256)), dim3(256), 0, st,
+                                 (const __half*)x, (uint8_t*)xt, rows, K / 32), "quant_q8_1_tiled");
+}
+
+int rmsnorm_q8_1_tiled(const float* h, const float* w, void* xt, int rows, int H, float eps, cudaStream_t st) {
+  if (rows <= 0 || H <= 0 || (H % 128) || H > 4096) return fail(Q4B_E_SHAPE, "rmsnorm_q8_1_tiled: H must be a multiple of 128, at most 4096");
+  if (!h || !w || !xt || !aligned16(h) || !aligned16(w) || !aligned16(xt)) return fail(Q4B_E_ALIGN, "rmsnorm_q8_1_tiled: null or misaligned pointer");
+  return check_launch(launch_pdl(rmsnorm_q8_1_tiled_kernel, dim3(rows), dim3(H / 4), 0, st, h, w, (uint8_t*)xt, H, eps),
+                      "rmsnorm_q8_1_tiled");
 }
 
 int rmsnorm_q8_1(const float* h, const float* w, void* xq, void* xd, void* xsum, void* x16, int rows, int H, float eps,

@@ -78,3 +78,24 @@ def gemm8(W, S, xq, xd, Y, aux, N: int, K: int, P: int, epi: str, ldy: int, stat
 def head_batched(E, x, logits) -> None:
     """logits fp32 [B, V] = x fp16 [B, H] . E^T for the tied fp16 table (head_v2_source, lab/qwen_batched.py:681-833)."""
     _ffi.call("q4b_head_f16_batched", _p(E), _p(x), _p(logits), E.shape[0], E.shape[1], x.shape[0], _stream())
+
+
+def q8_tiled_buffer(rows: int, K: int, device) -> torch.Tensor:
+    """Zero-filled buffer for tiled Q8_1 activations of up to `rows` rows of K values."""
+    return torch.zeros(_ffi.lib().q4b_q8_tiled_bytes(rows, K), dtype=torch.uint8, device=device)
+
+
+def quant_q8_tiled(x, xt) -> None:
+    """x fp16 [rows, K] -> tiled Q8_1 (the prefill MMQ's activation operand)."""
+    _ffi.call("q4b_quant_q8_1_tiled", _p(x), _p(xt), x.shape[0], x.shape[1], _stream())
+
+
+def rmsnorm_q8_tiled(h, w, xt, eps: float) -> None:
+    _ffi.call("q4b_rmsnorm_q8_1_tiled", _p(h), _p(w), _p(xt), h.shape[0], h.shape[1], float(eps), _stream())
+
+
+def gemm8_prefill(Wt, St, xt, Y, aux, N: int, K: int, P: int, epi: str, ldy: int, status: Status) -> None:
+    """The prefill GEMM: Y[P, :] = epilogue(tiled Q8_1 x tile-packed Q4_0^T) on tcgen05 (gemm_q4i8_ms_source,
+    lab/qwen_batched.py:1271-1561)."""
+    _ffi.call("q4b_mmq_prefill_q4_0_q8_1", _p(Wt), _p(St), _p(xt), _p(Y), _p(aux), N, K, P, _ffi.EPI[epi], ldy,
+              _p(status.word), _stream())

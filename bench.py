@@ -212,6 +212,11 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
     engine = importlib.import_module("3080lab_b200.engine")
     K = importlib.import_module("3080lab_b200.qwen_kernels")
     cfg = synth.QWEN25_1P5B
+    if args.layers:
+        if not args.profile:
+            raise SystemExit("--layers is for --profile runs; the benchmark always runs the full model")
+        cfg = synth.ModelConfig(f"qwen2.5-1.5b-{args.layers}layers", args.layers, cfg.hidden, cfg.ffn, cfg.n_heads, cfg.n_kv_heads,
+                                cfg.head_dim, cfg.vocab)
     model = synth.synth_model(cfg, 0)                       # same weights on every rank, a different prompt per rank
     m = engine.FusedQwen(model, max_len=MAX_LEN, device=f"cuda:{local_rank}", tensor_core=not args.cuda_core)
     prompt = synth.synth_prompt(cfg, args.prompt, seed=rank)
@@ -359,6 +364,7 @@ def main() -> None:
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
     ap.add_argument("--cuda-core", action="store_true", help="linears on the CUDA-core GEMV instead of the tensor-core kernel")
     ap.add_argument("--prompt", type=int, default=PROMPT, help="prompt length (512 = the benchmark configuration)")
+    ap.add_argument("--layers", type=int, default=0, help="profile runs only: cut the model to this many layers")
     ap.add_argument("--profile", action="store_true",
                     help="short run for a profiler: only the warm-up and timed graph replays, no e2e / roofline / CPU legs")
     args = ap.parse_args()

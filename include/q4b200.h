@@ -133,6 +133,22 @@ int q4b_pack_q4_0(const void* W, const void* S, void* Wt, void* St, int N, int K
 int q4b_gemv_q4_0_tc(const void* Wt, const void* St, const void* X, void* Y, const void* AUX, int N, int K, int epilogue,
                      int x_dtype, uint32_t* status, q4b_stream_t stream);
 
+/* ---- prefill: Q8_1 x Q4_0 for many activation rows ------------------------------------------------------------------
+ * Tiled Q8_1 activations for the prefill MMQ: for each (tile of 128 rows, 32-value block) 4096 bytes of int8 values
+ * already in the tensor-core operand order, then the 128 block scales as fp32 (fp16-rounded values).  The quantisers
+ * below write this format directly; rows beyond `rows` inside the last tile must be zero (zero-fill the buffer once).
+ * q4b_q8_tiled_bytes(rows, K) = ceil(rows/128) * K/32 * 4608. */
+size_t q4b_q8_tiled_bytes(int rows, int K);
+/* QUANT_Q8 (lab/qwen_batched.py:1016-1041) / rmsnorm_q8_source (:1044-1091) with tiled output. */
+int q4b_quant_q8_1_tiled(const void* x, void* xt, int rows, int K, q4b_stream_t stream);
+int q4b_rmsnorm_q8_1_tiled(const float* h, const float* w, void* xt, int rows, int H, float eps, q4b_stream_t stream);
+/* Y[P, :] = epilogue(Xt x Q4_0(Wt, St)^T): the prefill GEMM (gemm_q4i8_ms_source, lab/qwen_batched.py:1271-1561;
+ * host Prefill.gemm8, scripts/qwen_prefill.py:176-190) on tcgen05 int8 tensor cores with TMEM accumulators, 128 x 128
+ * tiles, exact int32 block dots rescaled per k-block in fp32.  Weights tile-packed, activations tiled Q8_1, any P;
+ * K a multiple of 256; Y pitch ldy elements as in q4b_mmq_q4_0_q8_1. */
+int q4b_mmq_prefill_q4_0_q8_1(const void* Wt, const void* St, const void* xt, void* Y, const void* AUX, int N, int K,
+                              int P, int epilogue, int ldy, uint32_t* status, q4b_stream_t stream);
+
 /* Optional in-kernel timeline of the tensor-core kernels: while a buffer is set, thread 0 of every CTA writes up to 15
  * %globaltimer stamps (ns) at its phase boundaries into buffer[cta * 16 ..], and the count into entry 15.  The
  * reference has the same facility (`timed=True`, lab/qwen_kernels.py:46-53).  entries >= 4096 * 16; null switches it
