@@ -12,8 +12,10 @@
 //   * activations arrive pre-tiled from the quantiser (quant_q8_1.cu, "tiled" outputs): per (128-row tile, k-block)
 //     4096 bytes already in the UMMA K-major core-matrix order + 128 fp32 block scales, one bulk copy per stage
 //     (ring of 8), used directly as the B operand;
-//   * warp 8 (one thread) issues copies and MMAs; warpgroup 0 expands A and rescales accumulator columns 0..63,
-//     warpgroup 1 rescales columns 64..127; the rescale of k-block b overlaps the MMA of b+1 and the expansion of b+2.
+//   * warp 8 (one thread) issues the MMAs, warp 9 (one thread) the bulk copies; warpgroup 0 expands A and rescales
+//     accumulator columns 0..63, warpgroup 1 rescales columns 64..127; the rescale of k-block b overlaps the MMA of b+1
+//     and the expansion of b+2.  Barrier arrivals are one per warp (an elected lane after the warp-wide TMEM wait):
+//     with one arrival per thread the 640 shared-memory barrier updates per k-block were the bottleneck.
 // The per-block rescale (one int->float, two multiplies/FMAs per output per k-block) is CUDA-core work of the same
 // order as the tensor-core time at full rate; it is the structural cost of Q4_0 x Q8_1 and bounds this kernel.
 // All waits are bounded; after the first expired wait a thread stops waiting (status word, garbage out, no hang).
@@ -24,7 +26,7 @@ namespace q4b {
 
 namespace {
 
-constexpr int PF_WG = 128, PF_THREADS = 2 * PF_WG + 32;
+constexpr int PF_WG = 128, PF_THREADS = 2 * PF_WG + 64;   // two warpgroups + MMA warp + copy warp
 constexpr int NTOK = 128;                 // activation rows per CTA tile (UMMA N)
 constexpr int SB = 8;                     // activation stages (one k-block each)
 constexpr int WB = 4;                     // weight batches in flight (8 k-blocks each)
@@ -76,16 +78,16 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const Prefil
   if (t == 0) {
     for (int i = 0; i < WB; ++i) {
       tc::mbar_init(&w_full[i], 1);
-      tc::mbar_init(&w_empty[i], 2 * PF_WG);
+      tc::mbar_init(&w_empty[i], 8);
     }
     for (int i = 0; i < SB; ++i) {
       tc::mbar_init(&b_full[i], 1);
-      tc::mbar_init(&b_empty[i], 1 + 2 * PF_WG);
+      tc::mbar_init(&b_empty[i], 1 + 8);
     }
     for (int i = 0; i < 2; ++i) {
-      tc::mbar_init(&a_full[i], PF_WG);
+      tc::mbar_init(&a_full[i], 4);
       tc::mbar_init(&d_full[i], 1);
-      tc::mbar_init(&d_empty[i], 2 * PF_WG);
+      tc::mbar_init(&d_empty[i], 8);
     }
     tc::mbar_fence_init();
   }
@@ -98,8 +100,8 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const Prefil
   constexpr uint32_t IDESC = tc::idesc_i8(128, NTOK);
   bool ok = true;
 
-  if (warp == 8) {
-    // ===================== producer + MMA issuer (one thread) =====================
+  if (warp == 9) {
+    // ===================== bulk-copy producer (one thread) =====================
     if ((t & 31) == 0) {
       auto load_w = [&](int j) {                           // weight batch j -> slot j % WB
         const int s = j % WB;
@@ -115,6 +117,23 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const Prefil
       for (int j = 0; j < WB && j < NBATCH; ++j) load_w(j);   // weights do not depend on the previous kernel
       pdl_wait();                                             // activations do
       for (int b = 0; b < SB && b < KB; ++b) load_b(b);
+      for (int ob = 0; ob < KB; ++ob) {                       // refill each ring slot as soon as its k-block is done with
+        if (ob + SB < KB) {
+          waitb(&b_empty[ob % SB], (uint32_t)(ob / SB) & 1u, ok);
+          load_b(ob + SB);
+        }
+        if ((ob & 7) == 7) {
+          const int oj = ob >> 3;
+          if (oj + WB < NBATCH) {
+            waitb(&w_empty[oj % WB], (uint32_t)(oj / WB) & 1u, ok);
+            load_w(oj + WB);
+          }
+        }
+      }
+    }
+  } else if (warp == 8) {
+    // ===================== MMA issuer (one thread) =====================
+    if ((t & 31) == 0) {
       const uint32_t stage0 = tc::smem_u32(stage);
       for (int b = 0; b < KB; ++b) {
         const int slot = b & 1, s = b % SB;
@@ -126,26 +145,11 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const Prefil
         tc::mma_i8_ts(tmem_d + (uint32_t)slot * 128, tmem_a + (uint32_t)slot * 8, bdesc, IDESC, 0u);
         tc::mma_commit(&d_full[slot]);
         tc::mma_commit(&b_empty[s]);
-        // refill with a lag of three k-blocks, so that this thread never waits on a rescale that has only just begun
-        if (b >= 3) {
-          const int ob = b - 3;
-          if (ob + SB < KB) {
-            waitb(&b_empty[ob % SB], (uint32_t)(ob / SB) & 1u, ok);
-            load_b(ob + SB);
-          }
-          if ((ob & 7) == 7) {                             // the last k-block of weight batch ob / 8 has been rescaled
-            const int oj = ob >> 3;
-            if (oj + WB < NBATCH) {
-              waitb(&w_empty[oj % WB], (uint32_t)(oj / WB) & 1u, ok);
-              load_w(oj + WB);
-            }
-          }
-        }
       }
     }
   } else {
     // ===================== warpgroup 0: expand A + rescale columns 0..63; warpgroup 1: rescale columns 64..127 ======
-    const int wg = t >> 7, r = t & 127;                    // r: row of the tile = TMEM lane
+    const int wg = t >> 7, r = t & 127, lane = t & 31;     // r: row of the tile = TMEM lane
     const uint32_t lane_off = (uint32_t)(32 * (warp & 3)) << 16;
     float acc[64];
 #pragma unroll
@@ -161,9 +165,9 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const Prefil
       tc::tmem_ld16(dcol + 16, d + 16);
       tc::tmem_ld16(dcol + 32, d + 32);
       tc::tmem_ld16(dcol + 48, d + 48);
-      tc::tmem_wait_ld();
+      tc::tmem_wait_ld();                                  // warp-wide: every lane's accumulator values are in registers
       tc::fence_before_sync();
-      tc::mbar_arrive(&d_empty[slot]);                     // the accumulator slot may be overwritten
+      if (lane == 0) tc::mbar_arrive(&d_empty[slot]);      // one arrival per warp: the slot may be overwritten
       const float dw = __half2float(reinterpret_cast<const __half*>(slabS + (size_t)ws * WBATCH_S)[(b & 7) * 128 + r]) * 0.0625f;
       const float4* sx = reinterpret_cast<const float4*>(stage + (size_t)s * STAGE_BYTES + 4096) + wg * 16;
 #pragma unroll
@@ -174,8 +178,11 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const Prefil
         acc[4 * q + 2] = fmaf(dw * x4.z, (float)(int32_t)d[4 * q + 2], acc[4 * q + 2]);
         acc[4 * q + 3] = fmaf(dw * x4.w, (float)(int32_t)d[4 * q + 3], acc[4 * q + 3]);
       }
-      tc::mbar_arrive(&b_empty[s]);                        // done with this stage's block scales
-      if ((b & 7) == 7) tc::mbar_arrive(&w_empty[ws]);     // done with this weight batch's scales (and nibbles)
+      __syncwarp();
+      if (lane == 0) {
+        tc::mbar_arrive(&b_empty[s]);                      // this warp is done with the stage's block scales
+        if ((b & 7) == 7) tc::mbar_arrive(&w_empty[ws]);   // ... and with the weight batch's scales and nibbles
+      }
     };
 
     for (int b = 0; b < KB; ++b) {
@@ -190,9 +197,9 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const Prefil
         tc::expand_nibbles(w.w, ex[6], ex[7]);
         // A slot b & 1 was last read by the MMA of k-block b - 2, whose completion this thread saw in rescale(b - 2)
         tc::tmem_st8(tmem_a + lane_off + (uint32_t)slot * 8, ex);
-        tc::tmem_wait_st();
+        tc::tmem_wait_st();                                // warp-wide
         tc::fence_before_sync();
-        tc::mbar_arrive(&a_full[slot]);
+        if (lane == 0) tc::mbar_arrive(&a_full[slot]);
         if (b >= 1) rescale(b - 1);
       } else {
         rescale(b);
