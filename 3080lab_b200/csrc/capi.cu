@@ -46,6 +46,7 @@ int blockdot(const void*, const void*, int32_t*, int, int, int, int, uint32_t*, 
 int mmq_stream(const void*, const void*, const void*, const void*, void*, const void*, int, int, int, int, int, int, uint32_t*,
                cudaStream_t, const float* norm_w = nullptr, float eps = 0.f);
 void mmq_stream_trace(unsigned long long*);
+int attn_prefill(const void*, const float*, const float*, void*, void*, void*, int, int, int, int, int, int, float, cudaStream_t);
 size_t q8_tiled_bytes(int, int);
 int mmq_prefill(const void*, const void*, const void*, void*, const void*, int, int, int, int, int, uint32_t*, cudaStream_t);
 int quant_q8_1_tiled(const void*, void*, int, int, cudaStream_t);
@@ -151,6 +152,11 @@ int q4b_rmsnorm_q8_1_tiled(const float* h, const float* w, void* xt, int rows, i
 int q4b_mmq_prefill_q4_0_q8_1(const void* Wt, const void* St, const void* xt, void* Y, const void* AUX, int N, int K, int P,
                               int epilogue, int ldy, uint32_t* status, q4b_stream_t stream) {
   return mmq_prefill(Wt, St, xt, Y, AUX, N, K, P, epilogue, ldy, status, S(stream));
+}
+
+int q4b_attn_prefill(const void* qkv, const float* cosT, const float* sinT, void* kc, void* vc, void* out, int P, int NH,
+                     int NKV, int HD, int max_len, int pos0, float scale, q4b_stream_t stream) {
+  return attn_prefill(qkv, cosT, sinT, kc, vc, out, P, NH, NKV, HD, max_len, pos0, scale, S(stream));
 }
 
 int q4b_trace_buffer(uint64_t* device_buffer, size_t entries) {

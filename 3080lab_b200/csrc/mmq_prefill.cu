@@ -151,9 +151,10 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const Prefil
     // ===================== warpgroup 0: expand A + rescale columns 0..63; warpgroup 1: rescale columns 64..127 ======
     const int wg = t >> 7, r = t & 127, lane = t & 31;     // r: row of the tile = TMEM lane
     const uint32_t lane_off = (uint32_t)(32 * (warp & 3)) << 16;
-    float acc[64];
+    uint64_t acc2[32];                                     // 64 fp32 accumulators as packed pairs
 #pragma unroll
-    for (int n = 0; n < 64; ++n) acc[n] = 0.f;
+    for (int n = 0; n < 32; ++n) acc2[n] = 0ull;
+    const uint64_t neg_bias = tc::pack2(-tc::I2F_BIAS, -tc::I2F_BIAS);
 
     auto rescale = [&](int b) {
       const int slot = b & 1, s = b % SB, ws = (b >> 3) % WB;
@@ -169,14 +170,17 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const Prefil
       tc::fence_before_sync();
       if (lane == 0) tc::mbar_arrive(&d_empty[slot]);      // one arrival per warp: the slot may be overwritten
       const float dw = __half2float(reinterpret_cast<const __half*>(slabS + (size_t)ws * WBATCH_S)[(b & 7) * 128 + r]) * 0.0625f;
-      const float4* sx = reinterpret_cast<const float4*>(stage + (size_t)s * STAGE_BYTES + 4096) + wg * 16;
+      // per pair of outputs: two integer adds (exact int -> float through the magic constant), then three two-wide
+      // fp32 ops: subtract the bias, scale dw * dx, fused multiply-add into the accumulators
+      const ulonglong2* sx = reinterpret_cast<const ulonglong2*>(stage + (size_t)s * STAGE_BYTES + 4096) + wg * 16;
+      const uint64_t dw2 = tc::pack2(dw, dw);
 #pragma unroll
       for (int q = 0; q < 16; ++q) {
-        const float4 x4 = sx[q];
-        acc[4 * q + 0] = fmaf(dw * x4.x, (float)(int32_t)d[4 * q + 0], acc[4 * q + 0]);
-        acc[4 * q + 1] = fmaf(dw * x4.y, (float)(int32_t)d[4 * q + 1], acc[4 * q + 1]);
-        acc[4 * q + 2] = fmaf(dw * x4.z, (float)(int32_t)d[4 * q + 2], acc[4 * q + 2]);
-        acc[4 * q + 3] = fmaf(dw * x4.w, (float)(int32_t)d[4 * q + 3], acc[4 * q + 3]);
+        const ulonglong2 x4 = sx[q];                       // four block scales = two packed pairs
+        const uint64_t f0 = tc::add2(tc::pack2u(d[4 * q + 0] + tc::I2F_MAGIC, d[4 * q + 1] + tc::I2F_MAGIC), neg_bias);
+        const uint64_t f1 = tc::add2(tc::pack2u(d[4 * q + 2] + tc::I2F_MAGIC, d[4 * q + 3] + tc::I2F_MAGIC), neg_bias);
+        acc2[2 * q + 0] = tc::fma2(tc::mul2(dw2, x4.x), f0, acc2[2 * q + 0]);
+        acc2[2 * q + 1] = tc::fma2(tc::mul2(dw2, x4.y), f1, acc2[2 * q + 1]);
       }
       __syncwarp();
       if (lane == 0) {
@@ -212,8 +216,8 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const Prefil
     const int row = row_tile * 128 + r;
     const int tok0 = tok_tile * NTOK + wg * 64;
 #pragma unroll
-    for (int n = 0; n < 64; ++n) {                         // fully unrolled: acc[] must stay in registers
-      const float v = acc[n];
+    for (int n = 0; n < 64; ++n) {                         // fully unrolled: the accumulators must stay in registers
+      const float v = (n & 1) ? tc::hi2(acc2[n >> 1]) : tc::lo2(acc2[n >> 1]);
       const float partner = __shfl_xor_sync(0xffffffffu, v, 1);
       const int p = tok0 + n;
       if (p < a.P && row < a.N) {

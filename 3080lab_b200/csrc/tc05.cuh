@@ -134,6 +134,35 @@ __device__ __forceinline__ void mma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
+// ---- packed fp32 pairs (sm_100 has two-wide fp32 add / mul / fma on 64-bit registers) ---------------------------------
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+  return (uint64_t)__float_as_uint(lo) | ((uint64_t)__float_as_uint(hi) << 32);
+}
+__device__ __forceinline__ uint64_t pack2u(uint32_t lo, uint32_t hi) { return (uint64_t)lo | ((uint64_t)hi << 32); }
+__device__ __forceinline__ float lo2(uint64_t v) { return __uint_as_float((uint32_t)v); }
+__device__ __forceinline__ float hi2(uint64_t v) { return __uint_as_float((uint32_t)(v >> 32)); }
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t mul2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+// int32 -> fp32 without the (slow) conversion unit, for |v| < 2^22: the bits of v + 0x4B400000 are the float
+// 2^23 + 2^22 + v, so one integer add and one float subtract give float(v) exactly.  The reference plants the same
+// constant in the MMA's C operand (lab/qwen_batched.py:1016-1041, 1237-1243); tcgen05 accumulators start from zero, so
+// here it is added after the fact.
+constexpr uint32_t I2F_MAGIC = 0x4B400000u;
+constexpr float I2F_BIAS = 12582912.f;
+
 // ---- nibble expansion ---------------------------------------------------------------------------------------------
 // One 32-bit word = 8 nibbles q (weights 8w..8w+7).  ((q ^ 8) << 4) as a signed byte equals 16 * (q - 8), so two
 // logic ops per four weights give signed int8 operands with the Q4_0 offset already applied; the factor 16 is

@@ -323,3 +323,75 @@ def run_batched(bm: Batched, prompts, gen: int):
     e.record()
     torch.cuda.synchronize()
     return toks, s.elapsed_time(e) / gen
+
+
+class Prefill:
+    """P prompt tokens of one sequence per `chunk()` — the reference's `Prefill(m, P, "i8")`
+    (scripts/qwen_prefill.py:82-246): RMSNorm+Q8_1 -> int8 MMQ QKV (+bias) -> K/V append + causal flash attention ->
+    Q8_1 -> MMQ o (+residual) -> RMSNorm+Q8_1 -> MMQ gate/up (+SwiGLU) -> Q8_1 -> MMQ down (+residual).  Writes the KV
+    cache of the `FusedQwen` it wraps, so decode continues from the prefilled state."""
+
+    def __init__(self, m: FusedQwen, P: int):
+        c = m.cfg
+        if not m.tensor_core or c.hidden % 256 or c.q_rows % 256 or c.ffn % 256 or c.head_dim != 128:
+            raise ValueError("the prefill path needs tile-packed weights (K multiples of 256) and head_dim 128")
+        self.m, self.P = m, P
+        dv, f16, f32 = m.device, torch.float16, torch.float32
+        self.h = torch.zeros(P, c.hidden, dtype=f32, device=dv)
+        self.qkv = torch.zeros(P, c.qkv_rows, dtype=f16, device=dv)
+        self.att = torch.zeros(P, c.q_rows, dtype=f16, device=dv)
+        self.xm = torch.zeros(P, c.ffn, dtype=f16, device=dv)
+        self.tok = torch.zeros(P, dtype=torch.long, device=dv)
+        self.xt = QB.q8_tiled_buffer(P, max(c.hidden, c.q_rows), dv)
+        self.xt2 = QB.q8_tiled_buffer(P, c.ffn, dv)          # the down GEMM's input, written while gate/up reads xt
+        self.status = QB.Status(dv)
+        self.launches_per_chunk = 1 + 10 * c.layers
+
+    def gemm8(self, pair, xt, N, Kdim, Y, aux, epi, ldy):
+        Wt, St = self.m.packed[id(pair[0])]
+        QB.gemm8_prefill(Wt, St, xt, Y, aux, N, Kdim, self.P, epi, ldy, self.status)
+
+    def chunk(self, pos0: int = 0) -> None:
+        """One pass over the P tokens in self.tok at positions pos0 .. pos0 + P - 1."""
+        m, c, H = self.m, self.m.cfg, self.m.cfg.hidden
+        K.embed(m.embed, self.tok, self.h)
+        for i, L in enumerate(m.L):
+            QB.rmsnorm_q8_tiled(self.h, L["ln1"], self.xt, c.eps)
+            self.gemm8(L["qkv"], self.xt, c.qkv_rows, H, self.qkv, L["qkv_b"], "biasf", c.qkv_rows)
+            QB.attn_prefill(self.qkv, m.cos, m.sin, m.kc[i], m.vc[i], self.att, c.n_heads, c.n_kv_heads, c.head_dim,
+                            m.max_len, pos0, m.scale)
+            QB.quant_q8_tiled(self.att, self.xt)
+            self.gemm8(L["o"], self.xt, H, c.q_rows, self.h, None, "resid", H)
+            QB.rmsnorm_q8_tiled(self.h, L["ln2"], self.xt, c.eps)
+            self.gemm8(L["gu"], self.xt, 2 * c.ffn, H, self.xm, None, "swiglu", c.ffn)
+            QB.quant_q8_tiled(self.xm, self.xt2)
+            self.gemm8(L["down"], self.xt2, H, c.ffn, self.h, None, "resid", H)
+
+    def finish(self, pos0: int = 0) -> None:
+        """Greedy token after the last prompt token: final norm + LM head on the last row; leaves the wrapped engine
+        with tok = first generated token and pos = pos0 + P (ready for `step()`)."""
+        m = self.m
+        m.h.copy_(self.h[self.P - 1])
+        m.pos.fill_(pos0 + self.P - 1)
+        if m.head is None:
+            m.rms(m.norm, m.x)
+            K.head_argmax(m.embed, m.x, m.logits, m.tok, m.pos, m.head_ws)
+        else:
+            m.norm_gemv(m.norm, m.head, m.logits, None, m.cfg.vocab, m.cfg.hidden, "logits")
+            K.finish(m.logits, m.tok, m.pos, m.head_ws)
+
+
+def prefill(m: FusedQwen, ids, chunk: int = 0):
+    """Prefill `ids` (one sequence) in chunks against m's cache (scripts/qwen_prefill.py:262-301).  -> Prefill object."""
+    ids = np.asarray(ids, np.int64)
+    n = len(ids)
+    chunk = chunk or n
+    if n % chunk:
+        raise ValueError("the prompt length must be a multiple of the chunk")
+    pf = Prefill(m, chunk)
+    for s0 in range(0, n, chunk):
+        pf.tok.copy_(torch.from_numpy(ids[s0:s0 + chunk]).to(pf.tok.device))
+        pf.chunk(s0)
+    pf.finish(n - chunk)
+    pf.status.check("prefill")
+    return pf

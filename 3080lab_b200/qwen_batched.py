@@ -99,3 +99,10 @@ def gemm8_prefill(Wt, St, xt, Y, aux, N: int, K: int, P: int, epi: str, ldy: int
     lab/qwen_batched.py:1271-1561)."""
     _ffi.call("q4b_mmq_prefill_q4_0_q8_1", _p(Wt), _p(St), _p(xt), _p(Y), _p(aux), N, K, P, _ffi.EPI[epi], ldy,
               _p(status.word), _stream())
+
+
+def attn_prefill(qkv, cosT, sinT, kc, vc, out, NH: int, NKV: int, HD: int, max_len: int, pos0: int, scale: float) -> None:
+    """RoPE + K/V append + causal GQA flash attention for a chunk of prompt tokens of one sequence
+    (flash_prefill_v3_source, lab/qwen_batched.py:1795-2037; K/V write of `biasf_kv`, :1316-1362)."""
+    _ffi.call("q4b_attn_prefill", _p(qkv), _p(cosT), _p(sinT), _p(kc), _p(vc), _p(out), qkv.shape[0], NH, NKV, HD, max_len,
+              pos0, float(scale), _stream())

@@ -149,6 +149,14 @@ int q4b_rmsnorm_q8_1_tiled(const float* h, const float* w, void* xt, int rows, i
 int q4b_mmq_prefill_q4_0_q8_1(const void* Wt, const void* St, const void* xt, void* Y, const void* AUX, int N, int K,
                               int P, int epilogue, int ldy, uint32_t* status, q4b_stream_t stream);
 
+/* Prefill attention for one sequence: rotate K (NeoX pairs) and append K/V of P prompt tokens at positions
+ * pos0 .. pos0+P-1, then causal GQA flash attention of the P queries (rotated inside) over positions 0 .. pos0+P-1.
+ * Replaces the K/V write of the `biasf_kv` epilogue (lab/qwen_batched.py:1316-1362) and flash_prefill_v3_source
+ * (:1795-2037; host Prefill.chunk scripts/qwen_prefill.py:196-246).  qkv fp16 [P, (NH + 2 NKV) HD] (bias added,
+ * un-rotated); kc/vc fp16 [NKV, max_len, HD]; out fp16 [P, NH HD].  HD = 128. */
+int q4b_attn_prefill(const void* qkv, const float* cosT, const float* sinT, void* kc, void* vc, void* out, int P, int NH,
+                     int NKV, int HD, int max_len, int pos0, float scale, q4b_stream_t stream);
+
 /* Optional in-kernel timeline of the tensor-core kernels: while a buffer is set, thread 0 of every CTA writes up to 15
  * %globaltimer stamps (ns) at its phase boundaries into buffer[cta * 16 ..], and the count into entry 15.  The
  * reference has the same facility (`timed=True`, lab/qwen_kernels.py:46-53).  entries >= 4096 * 16; null switches it
