@@ -36,6 +36,7 @@ int embed(const void*, const int64_t*, float*, int, int, int, cudaStream_t);
 int rmsnorm(const float*, const float*, void*, int, int, float, cudaStream_t);
 size_t argmax_workspace(int, int);
 int argmax_advance(const float*, int, int, int64_t*, int64_t*, void*, size_t, cudaStream_t);
+int argmax_advance_static(const float*, int, int, int64_t*, int64_t*, cudaStream_t);
 size_t attn_decode_workspace(int, int, int, int);
 int attn_decode(const void*, const float*, const float*, const int64_t*, void*, void*, void*, int, int, int, int, int, float,
                 void*, size_t, cudaStream_t);
@@ -110,6 +111,10 @@ size_t q4b_head_workspace(int V) { return head_workspace(V); }
 int q4b_head_f16_argmax(const void* E, const void* x, float* logits, int V, int H, int64_t* tok, int64_t* pos,
                         void* workspace, size_t workspace_bytes, q4b_stream_t stream) {
   return head_f16_argmax(E, x, logits, V, H, tok, pos, workspace, workspace_bytes, S(stream));
+}
+
+int q4b_argmax_advance_static(const float* logits, int rows, int V, int64_t* tok, int64_t* pos, q4b_stream_t stream) {
+  return argmax_advance_static(logits, rows, V, tok, pos, S(stream));
 }
 
 int q4b_head_f16_batched(const void* E, const void* x, float* logits, int V, int H, int B, q4b_stream_t stream) {

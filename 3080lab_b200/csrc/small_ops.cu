@@ -124,6 +124,13 @@ __global__ void __launch_bounds__(ARG_T) argmax_kernel(const float* logits, int 
   }
 }
 
+// Scratch of the allocation-free greedy pick: counters first, then per-slice maxima and indices, for up to
+// STATIC_MAX_ROWS rows.  It lives in the library image: every GPU that loads the library carries these bytes until the
+// process exits.
+constexpr int STATIC_MAX_ROWS = 64;
+constexpr size_t STATIC_SCRATCH_BYTES = 256 + (size_t)STATIC_MAX_ROWS * ARG_SLICES * 8;
+static __device__ __align__(256) unsigned char g_argmax_scratch[STATIC_SCRATCH_BYTES];
+
 }  // namespace
 
 int embed(const void* E, const int64_t* tok, float* h, int rows, int H, int V, cudaStream_t st) {
@@ -155,6 +162,44 @@ int argmax_advance(const float* logits, int rows, int V, int64_t* tok, int64_t* 
   int* parti = reinterpret_cast<int*>(partv + (size_t)rows * ARG_SLICES);
   return check_launch(launch_pdl(argmax_kernel, dim3(ARG_SLICES, rows), dim3(ARG_T), 0, st, logits, V, tok, pos, partv, parti, cnt),
                       "argmax_advance");
+}
+
+// Greedy pick without caller-provided scratch.  In host code `g_argmax_scratch` is only a handle for the runtime, not a
+// device address, so the address is looked up with cudaGetSymbolAddress: once per device, with that device current, and
+// remembered.  No allocation of any kind happens here.
+int argmax_advance_static(const float* logits, int rows, int V, int64_t* tok, int64_t* pos, cudaStream_t st) {
+  if (rows <= 0 || V <= 0) return fail(Q4B_E_SHAPE, "argmax_advance_static: rows, V > 0 required");
+  if (rows > STATIC_MAX_ROWS)
+    return fail(Q4B_E_SHAPE, "argmax_advance_static: at most 64 rows fit the built-in scratch; use q4b_argmax_advance with a workspace");
+  if (!logits) return fail(Q4B_E_ALIGN, "argmax_advance_static: null pointer");
+  constexpr int MAX_DEV = 64;
+  static unsigned char* base[MAX_DEV] = {nullptr};
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= MAX_DEV) {
+    set_cuda_error(e != cudaSuccess ? e : cudaErrorInvalidDevice, "argmax_advance_static: cudaGetDevice");
+    return Q4B_E_CUDA;
+  }
+  if (!base[dev]) {                                   // first call on this device: resolve the symbol's device address
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_argmax_scratch);
+    if (e != cudaSuccess || !p) {
+      set_cuda_error(e != cudaSuccess ? e : cudaErrorInvalidSymbol, "argmax_advance_static: cudaGetSymbolAddress");
+      return Q4B_E_CUDA;
+    }
+    base[dev] = static_cast<unsigned char*>(p);
+  }
+  unsigned* cnt = reinterpret_cast<unsigned*>(base[dev]);
+  float* partv = reinterpret_cast<float*>(base[dev] + 256);
+  int* parti = reinterpret_cast<int*>(partv + (size_t)STATIC_MAX_ROWS * ARG_SLICES);
+  // the array keeps whatever the previous call (or an interrupted one) left: the arrival counters must start at zero
+  e = cudaMemsetAsync(cnt, 0, 256, st);
+  if (e != cudaSuccess) {
+    set_cuda_error(e, "argmax_advance_static: cudaMemsetAsync");
+    return Q4B_E_CUDA;
+  }
+  argmax_kernel<<<dim3(ARG_SLICES, rows), ARG_T, 0, st>>>(logits, V, tok, pos, partv, parti, cnt);
+  return check_launch("argmax_advance_static");
 }
 
 }  // namespace q4b

@@ -95,6 +95,21 @@ size_t q4b_head_workspace(int V);
 int q4b_head_f16_argmax(const void* E, const void* x, float* logits, int V, int H, int64_t* tok, int64_t* pos,
                         void* workspace, size_t workspace_bytes, q4b_stream_t stream);
 
+/* The same greedy pick for callers that may not allocate device memory.  (No counterpart in the reference: there the
+ * caller always owns a torch-allocated workspace.)  Some hosts give a library nothing but the input and output
+ * buffers and keep every allocation to themselves: a serving runtime whose device-memory budget is fixed at start-up,
+ * or a binding from a language whose foreign-function layer can pass pointers but cannot create device buffers.  For
+ * them the scratch (arrival counters and per-slice maxima) lives in a fixed array inside the library image, about
+ * 33 KB per GPU for as long as the library is loaded.
+ *   - at most 64 rows; more is rejected with Q4B_E_SHAPE (use q4b_argmax_advance with a workspace instead);
+ *   - nothing is allocated or freed, by this function or by anything it calls;
+ *   - the first call on each device looks up the array's device address (that device must be current); make that
+ *     first call before any stream capture begins;
+ *   - all calls on a device share the one array: two calls whose kernels can overlap on the GPU (different streams,
+ *     no ordering between them) race on it and give wrong results.  Calls ordered on one stream are fine; the counters
+ *     are cleared at the start of every call. */
+int q4b_argmax_advance_static(const float* logits, int rows, int V, int64_t* tok, int64_t* pos, q4b_stream_t stream);
+
 /* LM head over the tied fp16 table for B = 1..32 sequences: logits fp32 [B, V] = x fp16 [B, H] . E fp16 [V, H]^T.
  * Replaces head_v2_source / the cuBLAS fp16 head of the batched engine (lab/qwen_batched.py:681-833,
  * scripts/qwen_batched_decode.py:172-185).  H a multiple of 32.  Follow with q4b_argmax_advance for the greedy pick. */
