@@ -355,6 +355,130 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
         dist.destroy_process_group()
 
 
+def run_other_workload(args, local_rank: int) -> None:
+    """The other single-GPU configurations of the benchmark set, on request (`--workload`): batched decode at 8 / 32
+    sequences with a 1024-token KV context (128 steps), and the 2048-token prefill.  One JSON line each; the default
+    benchmark line stays the batch-1 decode."""
+    import torch
+    torch.cuda.set_device(local_rank)
+    synth = importlib.import_module("3080lab_b200.synth")
+    engine = importlib.import_module("3080lab_b200.engine")
+    cfg = synth.QWEN25_1P5B
+    model = synth.synth_model(cfg, 0)
+    peaks, peak_kind = measured_peaks()
+    sampler = ClockSampler(local_rank)
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if args.workload == "prefill2048":
+        P = 2048
+        m = engine.FusedQwen(model, max_len=P, device=f"cuda:{local_rank}")
+        pf = engine.Prefill(m, P)
+        ids = synth.synth_prompt(cfg, P, 0)
+        host_ids = torch.from_numpy(ids).pin_memory()
+        pf.tok.copy_(host_ids)
+
+        def one():
+            pf.chunk(0)
+        one()
+        torch.cuda.synchronize()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            one()
+        torch.cuda.current_stream().wait_stream(side)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            one()
+        torch.cuda.synchronize()
+        for _ in range(max(args.warmup, 3)):
+            g.replay()
+        steps = min(args.steps, 20)
+        sampler.start()
+        torch.cuda.synchronize()
+        s.record()
+        for _ in range(steps):
+            g.replay()
+        e.record()
+        torch.cuda.synchronize()
+        ms = s.elapsed_time(e) / steps
+        clocks = sampler.stop()
+        pf.status.check("prefill")
+        # end to end: token ids from pinned host memory in, first generated token back out
+        host_out = torch.zeros(1, dtype=torch.long).pin_memory()
+        s.record()
+        for _ in range(steps):
+            pf.tok.copy_(host_ids, non_blocking=True)
+            g.replay()
+            pf.finish(0)
+            host_out.copy_(m.tok, non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+        e.record()
+        torch.cuda.synchronize()
+        e2e_ms = s.elapsed_time(e) / steps
+        ops = 2.0 * P * 46792704 * cfg.layers
+        nominal_int8 = 4500.0
+        print(json.dumps({
+            "metric": "prefill_tok_per_s", "value": P / ms * 1e3, "unit": "tok/s", "n_gpus": 1, "steps": steps,
+            "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "int8 x int4 -> int32, fp32 scaling", "data": "synthetic",
+            "config": {"workload": "qwen2.5-1.5b-shape prefill, one 2048-token prompt, Q8_1 x Q4_0 MMQ + causal flash attention",
+                       "l2": "3.3 GB of activations and weights touched per pass, larger than L2"},
+            "roofline": {"bound": "tensor", "kernel": "mmq_prefill_kernel (whole pass incl. attention and quantisers)",
+                         "achieved": ops / (ms * 1e-3) / 1e12, "peak": nominal_int8, "unit": "TOP/s (int8)",
+                         "frac": ops / (ms * 1e-3) / 1e12 / nominal_int8, "peak_kind": "of nominal dense int8 (no measured int8 peak)",
+                         "traffic": None},
+            "e2e": {"value": P / e2e_ms * 1e3, "unit": "tok/s", "h2d_bytes_per_step": P * 8, "d2h_bytes_per_step": 8},
+            "gpu_launches": pf.launches_per_chunk * steps, "clocks": clocks}), flush=True)
+        return
+    B = 8 if args.workload == "batched8" else 32
+    ctx, gen = 1024, min(args.steps, 128)
+    m = engine.FusedQwen(model, max_len=ctx + 256, device=f"cuda:{local_rank}")
+    bm = engine.Batched(m, B)
+    bm.kc.normal_()                                   # a 1024-token KV context per sequence (N(0,1) fp16, as the
+    bm.vc.normal_()                                   # reference's decode A/B harness fills it, scripts/decode_ab.py:56-58)
+    bm.pos.fill_(ctx)
+    bm.tok.copy_(torch.from_numpy(synth.synth_prompt(cfg, B, 5)).cuda())
+    g = bm.capture()
+    for _ in range(max(args.warmup, 3)):
+        g.replay()
+    bm.pos.fill_(ctx)
+    sampler.start()
+    torch.cuda.synchronize()
+    s.record()
+    for _ in range(gen):
+        g.replay()
+    e.record()
+    torch.cuda.synchronize()
+    ms = s.elapsed_time(e) / gen
+    clocks = sampler.stop()
+    bm.status.check("batched decode")
+    host_in = torch.zeros(B, dtype=torch.long).pin_memory()
+    host_out = torch.zeros(B, dtype=torch.long).pin_memory()
+    host_in.copy_(bm.tok)
+    bm.pos.fill_(ctx)
+    s.record()
+    for _ in range(gen):
+        bm.tok.copy_(host_in, non_blocking=True)
+        g.replay()
+        host_out.copy_(bm.tok, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        host_in.copy_(host_out)
+    e.record()
+    torch.cuda.synchronize()
+    e2e_ms = s.elapsed_time(e) / gen
+    step_bytes = cfg.q4_bytes_per_layer() * cfg.layers + cfg.head_bytes() + B * cfg.kv_bytes_per_position() * (ctx + gen / 2.0)
+    ach = step_bytes / (ms * 1e-3) / 1e9
+    print(json.dumps({
+        "metric": f"decode_tok_per_s_batch{B}", "value": B / ms * 1e3, "unit": "tok/s", "n_gpus": 1, "steps": gen,
+        "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "int8 x int4 -> int32, fp32 scaling", "data": "synthetic",
+        "config": {"workload": f"qwen2.5-1.5b-shape batched decode, {B} sequences, 1024-token KV context, Q8_1 x Q4_0 MMQ",
+                   "l2": "1.2 GB of weights + KV streamed per step, larger than L2"},
+        "roofline": {"bound": "hbm", "kernel": "whole step", "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": ach / peaks["hbm_gbs"], "peak_kind": f"of {peak_kind}", "traffic": None},
+        "e2e": {"value": B / e2e_ms * 1e3, "unit": "tok/s", "h2d_bytes_per_step": 8 * B, "d2h_bytes_per_step": 8 * B},
+        "gpu_launches": bm.launches_per_step * gen, "clocks": clocks}), flush=True)
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -362,6 +486,8 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
+    ap.add_argument("--workload", default="decode_b1", choices=["decode_b1", "batched8", "batched32", "prefill2048"],
+                    help="decode_b1 is the benchmark; the others are the further single-GPU configurations")
     ap.add_argument("--cuda-core", action="store_true", help="linears on the CUDA-core GEMV instead of the tensor-core kernel")
     ap.add_argument("--prompt", type=int, default=PROMPT, help="prompt length (512 = the benchmark configuration)")
     ap.add_argument("--layers", type=int, default=0, help="profile runs only: cut the model to this many layers")
@@ -373,6 +499,11 @@ def main() -> None:
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
         run_reference(args, rank)
+        return
+    if args.workload != "decode_b1":
+        if world > 1:
+            raise SystemExit("--workload other than decode_b1 runs on one GPU")
+        run_other_workload(args, local_rank)
         return
     if world != args.gpus and world == 1 and args.gpus > 1:
         raise SystemExit("bench.py --gpus N > 1 must be launched with torch.distributed.run --nproc-per-node N")
