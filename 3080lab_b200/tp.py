@@ -1,0 +1,152 @@
+"""Tensor-parallel batched decode: one process per GPU, NCCL all-reduce over NVLink after o_proj and down_proj.
+
+The reference is single-GPU (no NCCL anywhere); the target configuration adds this for the 7B shape.  Split:
+  * QKV by heads (query heads and KV heads divided evenly; a rank keeps the K/V cache of its own KV heads),
+  * gate/up by interleaved (gate, up) row pairs,
+  * o_proj and down_proj along K (row-parallel): every rank produces a partial [B, hidden] that is summed across ranks
+    (`all_reduce`, sum) before it is added to the residual stream.
+K slices of the row-parallel matrices stay multiples of the 32-weight block, so no Q4_0 block or Q8_1 block straddles
+a rank and the per-block int8 quantisation of a slice equals that of the full vector.  Where a slice is not a multiple
+of the tensor-core kernels' 256-wide K group (7B: 3584/4 = 896, 18944/4 = 4736) it is padded with zero-weight blocks.
+RMSNorm, residual stream, embedding and LM head are replicated (every rank computes the same greedy token).
+"""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from . import qwen_batched as QB
+from . import qwen_kernels as K
+from .engine import FusedQwen
+from .synth import ModelConfig
+
+
+def _pad_k(W: np.ndarray, S: np.ndarray, mult: int = 256):
+    """Pad the K axis of a canonical Q4_0 matrix with zero-weight blocks (nibble 8, scale 0) up to a multiple of `mult`."""
+    n, kw = W.shape
+    k = kw * 8
+    kp = -(-k // mult) * mult
+    if kp == k:
+        return W, S
+    Wp = np.full((n, kp // 8), np.uint32(0x88888888).view(np.int32), np.int32)
+    Sp = np.zeros((n, kp // 32), np.float16)
+    Wp[:, :kw] = W
+    Sp[:, :k // 32] = S
+    return Wp, Sp
+
+
+def shard_config(cfg: ModelConfig, tp: int) -> ModelConfig:
+    if cfg.n_heads % tp or cfg.n_kv_heads % tp or cfg.ffn % tp or (cfg.ffn // tp) % 32:
+        raise ValueError(f"tp={tp} does not divide {cfg.n_heads} query heads / {cfg.n_kv_heads} KV heads / ffn {cfg.ffn}")
+    return ModelConfig(f"{cfg.name}-tp{tp}", cfg.layers, cfg.hidden, cfg.ffn // tp, cfg.n_heads // tp, cfg.n_kv_heads // tp,
+                       cfg.head_dim, cfg.vocab, cfg.eps, cfg.rope_theta, cfg.tied_fp16_head)
+
+
+def shard_model(model: dict, rank: int, tp: int) -> dict:
+    """The weights rank `rank` of `tp` holds, as a model dict with the local head / ffn counts.  `o` and `down` are the
+    K slices (padded to a multiple of 256); everything else is a row slice."""
+    cfg: ModelConfig = model["cfg"]
+    lc = shard_config(cfg, tp)
+    hd = cfg.head_dim
+    q0, q1 = rank * lc.n_heads * hd, (rank + 1) * lc.n_heads * hd
+    k0, k1 = cfg.q_rows + rank * lc.n_kv_heads * hd, cfg.q_rows + (rank + 1) * lc.n_kv_heads * hd
+    v0, v1 = k0 + cfg.kv_rows, k1 + cfg.kv_rows
+    rows = np.r_[q0:q1, k0:k1, v0:v1]
+    f0, f1 = rank * lc.ffn, (rank + 1) * lc.ffn
+    layers = []
+    for L in model["layers"]:
+        Wq, Sq = L["qkv"]
+        Wo, So = L["o"]
+        Wg, Sg = L["gu"]
+        Wd, Sd = L["down"]
+        layers.append({
+            "ln1": L["ln1"], "ln2": L["ln2"],
+            "qkv": (np.ascontiguousarray(Wq[rows]), np.ascontiguousarray(Sq[rows])),
+            "qkv_b": np.ascontiguousarray(L["qkv_b"][rows]),
+            "o": _pad_k(np.ascontiguousarray(Wo[:, q0 // 8:q1 // 8]), np.ascontiguousarray(So[:, q0 // 32:q1 // 32])),
+            "gu": (np.ascontiguousarray(Wg[2 * f0:2 * f1]), np.ascontiguousarray(Sg[2 * f0:2 * f1])),
+            "down": _pad_k(np.ascontiguousarray(Wd[:, f0 // 8:f1 // 8]), np.ascontiguousarray(Sd[:, f0 // 32:f1 // 32])),
+        })
+    return {"cfg": lc, "full_cfg": cfg, "embed": model["embed"], "layers": layers, "norm": model["norm"], "head": model["head"],
+            "rank": rank, "tp": tp}
+
+
+class TPBatched:
+    """B sequences, one decode token each per `step()`, on one rank of a tensor-parallel group.  Same op order as
+    `engine.Batched`; the o_proj / down_proj partials are all-reduced (sum) before the residual add.  `group` is a
+    torch.distributed process group (NCCL on GPUs); with group=None (tp = 1) it degenerates to the single-GPU path."""
+
+    def __init__(self, shard: dict, B: int, max_len: int, device, group=None):
+        import torch.distributed as dist
+        self.dist, self.group = dist, group
+        self.B = B
+        self.full: ModelConfig = shard.get("full_cfg", shard["cfg"])
+        self.m = FusedQwen(shard, max_len=max_len, device=device)        # local weights, RoPE tables, packing
+        m, c = self.m, self.m.cfg
+        self.ko = m.L[0]["o"][0].shape[1] * 8                             # padded K of the row-parallel slices
+        self.kd = m.L[0]["down"][0].shape[1] * 8
+        dv, f16, f32 = m.device, torch.float16, torch.float32
+        self.h = torch.zeros(B, c.hidden, dtype=f32, device=dv)
+        self.x = torch.zeros(B, c.hidden, dtype=f16, device=dv)
+        self.qkv = torch.zeros(B, c.qkv_rows, dtype=f16, device=dv)
+        self.att = torch.zeros(B, self.ko, dtype=f16, device=dv)         # zero beyond the local q rows (K padding)
+        self.xm = torch.zeros(B, self.kd, dtype=f16, device=dv)
+        self.part = torch.zeros(B, c.hidden, dtype=f32, device=dv)
+        kmax = max(c.hidden, self.ko, self.kd)
+        self.xq = torch.zeros(B * kmax, dtype=torch.int8, device=dv)
+        self.xd = torch.zeros(B * kmax // 32, dtype=f16, device=dv)
+        self.logits = torch.zeros(B, c.vocab, dtype=f32, device=dv)
+        self.tok = torch.zeros(B, dtype=torch.long, device=dv)
+        self.pos = torch.zeros(B, dtype=torch.long, device=dv)
+        self.kc = torch.zeros(c.layers, B, c.n_kv_heads, max_len, c.head_dim, dtype=f16, device=dv)
+        self.vc = torch.zeros_like(self.kc)
+        self.attn_ws = K.attn_workspace(B, c.n_heads, c.head_dim, max_len, dv)
+        self.head_ws = K.head_workspace(c.vocab, B, dv)
+        self.status = QB.Status(dv)
+        self.att_view = self.att[:, :c.q_rows] if self.ko == c.q_rows else None
+        self.allreduces_per_step = 2 * c.layers
+
+    def _gemm8(self, pair, N, Kdim, Y, aux, epi, ldy):
+        Wt, St = self.m.packed[id(pair[0])]
+        QB.gemm8(Wt, St, self.xq, self.xd, Y, aux, N, Kdim, self.B, epi, ldy, self.status)
+
+    def _reduce_add(self):
+        """h += sum over ranks of the partial [B, hidden]."""
+        if self.group is not None:
+            self.dist.all_reduce(self.part, op=self.dist.ReduceOp.SUM, group=self.group)
+        self.h.add_(self.part)
+
+    def step(self) -> None:
+        m, c, H = self.m, self.m.cfg, self.m.cfg.hidden
+        K.embed(m.embed, self.tok, self.h)
+        for i, L in enumerate(m.L):
+            QB.rmsnorm_q8(self.h, L["ln1"], self.xq, self.xd, c.eps)
+            self._gemm8(L["qkv"], c.qkv_rows, H, self.qkv, L["qkv_b"], "biasf", c.qkv_rows)
+            if self.att_view is None:
+                # the attention kernel writes rows of c.q_rows values; with K padding they land in a staging buffer first
+                if not hasattr(self, "_att_tmp"):
+                    self._att_tmp = torch.zeros(self.B, c.q_rows, dtype=torch.float16, device=self.att.device)
+                K.attn(self.qkv, m.cos, m.sin, self.pos, self.kc[i], self.vc[i], self._att_tmp, c.n_heads, c.n_kv_heads,
+                       c.head_dim, m.max_len, m.scale, self.attn_ws)
+                self.att[:, :c.q_rows].copy_(self._att_tmp)
+            else:
+                K.attn(self.qkv, m.cos, m.sin, self.pos, self.kc[i], self.vc[i], self.att, c.n_heads, c.n_kv_heads,
+                       c.head_dim, m.max_len, m.scale, self.attn_ws)
+            QB.quant_q8(self.att, self.xq, self.xd)
+            self._gemm8(L["o"], H, self.ko, self.part, None, "logits", H)
+            self._reduce_add()
+            QB.rmsnorm_q8(self.h, L["ln2"], self.xq, self.xd, c.eps)
+            if self.kd == c.ffn:
+                self._gemm8(L["gu"], 2 * c.ffn, H, self.xm, None, "swiglu", c.ffn)
+            else:
+                self._gemm8(L["gu"], 2 * c.ffn, H, self.xm, None, "swiglu", self.kd)   # pitch = padded K, tail stays zero
+            QB.quant_q8(self.xm, self.xq, self.xd)
+            self._gemm8(L["down"], H, self.kd, self.part, None, "logits", H)
+            self._reduce_add()
+        if m.head is None:
+            K.rms(self.h, m.norm, self.x, c.eps)
+            QB.head_batched(m.embed, self.x, self.logits)
+        else:
+            QB.rmsnorm_q8(self.h, m.norm, self.xq, self.xd, c.eps)
+            self._gemm8(m.head, c.vocab, H, self.logits, None, "logits", c.vocab)
+        K.finish(self.logits, self.tok, self.pos, self.head_ws)
