@@ -16,6 +16,12 @@ import argparse
 import importlib
 import json
 import os
+import sys as _sys
+
+if "reference" in _sys.argv:
+    # The CPU arm uses every host core: torchrun exports OMP_NUM_THREADS=1, which BLAS reads when numpy is imported.
+    for _v in ("OMP_NUM_THREADS", "OPENBLAS_NUM_THREADS", "MKL_NUM_THREADS"):
+        os.environ[_v] = str(os.cpu_count() or 1)
 import statistics
 import subprocess
 import sys
@@ -88,6 +94,18 @@ class ClockSampler:
                 "samples": len(sm), "reasons": sorted(reasons)}
 
 
+def blas_threads() -> int:
+    """Threads numpy's BLAS actually uses (the `cores` of the CPU baseline)."""
+    try:
+        from threadpoolctl import threadpool_info
+        n = [p.get("num_threads", 0) for p in threadpool_info() if p.get("user_api") == "blas"]
+        if n:
+            return int(max(n))
+    except Exception:
+        pass
+    return int(os.environ.get("OMP_NUM_THREADS", os.cpu_count() or 1))
+
+
 def algorithmic_bytes_per_token(cfg, ctx_mean: float) -> float:
     """Q4_0 layer weights + LM head + KV cache rows read, per decode token (activations < 0.1 %, left out)."""
     return cfg.q4_bytes_per_layer() * cfg.layers + cfg.head_bytes() + cfg.kv_bytes_per_position() * ctx_mean
@@ -119,7 +137,7 @@ def cpu_baseline(model, cfg, budget_s: float = 20.0):
     dec.head(h)
     t_head = time.perf_counter() - t
     t_tok = statistics.mean(t_layers) * cfg.layers + t_head
-    return {"value": 1.0 / t_tok, "unit": "tok/s", "cores": os.cpu_count(), "kind": "port",
+    return {"value": 1.0 / t_tok, "unit": "tok/s", "cores": blas_threads(), "kind": "port",
             "sample": f"1 decode token at context {PROMPT}: {len(t_layers)} layer passes over {n_layers} of {cfg.layers} "
                       f"layers ({statistics.mean(t_layers):.3f} s each) + the full LM head ({t_head:.2f} s), layers scaled "
                       f"to {cfg.layers}; numpy fp32 dequantise-and-dot per linear, nothing cached",
@@ -168,7 +186,7 @@ def run_reference(args, rank: int) -> None:
         "warmup": args.warmup, "ms_per_step": 1e3 * dt / max(1, args.steps), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": "qwen2.5-1.5b-shape Q4_0 decode, batch 1, 512-token context, CPU numpy path"},
-        "cpu_baseline": {"value": val, "unit": "tok/s", "cores": os.cpu_count(), "kind": "port", "sample": sample},
+        "cpu_baseline": {"value": val, "unit": "tok/s", "cores": blas_threads(), "kind": "port", "sample": sample},
         "e2e": {"value": val, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }), flush=True)
 
