@@ -285,12 +285,13 @@ __global__ void __launch_bounds__(AT) attn_decode_cluster_kernel(const __half* q
   __shared__ __align__(16) float qs[HSUB][HD];
   __shared__ __align__(16) float kn[HD];
   __shared__ __align__(16) float vn[HD];
-  __shared__ float sc[HSUB][CHK];
-  __shared__ float redw[HSUB][NW];
+  __shared__ float sc[HSUB][CHK];                // exp(score - warp maximum), read back only by the warp that wrote it
+  __shared__ float wml[NW][HSUB][2];             // per warp: maximum, sum
   __shared__ __align__(16) float red_o[NW][HSUB][HD];
   __shared__ __align__(16) float part_o[HSUB][HD];
   __shared__ float part_ml[HSUB][2];
-  __shared__ float wgt[HSUB][NCL + 1];          // [h][c] = exp(m_c - M), [h][NCL] = L
+  __shared__ float pml[HSUB][NCL][2];            // combiner: every chunk's (max, sum)
+  __shared__ float wgt[HSUB][NCL + 1];           // [h][c] = exp(m_c - M), [h][NCL] = L
 
   pdl_launch_dependents();
   pdl_wait();
@@ -313,6 +314,22 @@ __global__ void __launch_bounds__(AT) attn_decode_cluster_kernel(const __half* q
     const float* sn = sinT + (size_t)p * HALF;
     __half* kbase = kc + ((size_t)b * NKV + kvh) * (size_t)max_len * HD;
     __half* vbase = vc + ((size_t)b * NKV + kvh) * (size_t)max_len * HD;
+
+    // ---- this thread's K rows first (positions c0 + 128 pass + t): they do not depend on the query preparation
+    constexpr int PRE = PASSES * HD <= 256 ? PASSES : 256 / HD;       // passes whose K row is held in registers
+    uint4 kv[PRE][HD / 8];
+#pragma unroll
+    for (int ps = 0; ps < PRE; ++ps) {
+      const int j = c0 + 128 * ps + t;
+      if (j < p) {
+        const uint4* kr = reinterpret_cast<const uint4*>(kbase + (size_t)j * HD);
+#pragma unroll
+        for (int i = 0; i < HD / 8; ++i) kv[ps][i] = kr[i];
+      } else {
+#pragma unroll
+        for (int i = 0; i < HD / 8; ++i) kv[ps][i] = make_uint4(0u, 0u, 0u, 0u);
+      }
+    }
     for (int e = t; e < HSUB * HD; e += AT) {
       const int hl = e / HD, d = e - hl * HD, dd = d % HALF;
       float r = 0.f;
@@ -340,7 +357,7 @@ __global__ void __launch_bounds__(AT) attn_decode_cluster_kernel(const __half* q
     }
     __syncthreads();
 
-    // ---- scores: thread t <-> positions c0 + 128 pass + t
+    // ---- scores; softmax statistics per WARP (shuffles only), so no block-wide barrier until the partial outputs
     float s[PASSES][HSUB];
 #pragma unroll
     for (int ps = 0; ps < PASSES; ++ps) {
@@ -348,115 +365,105 @@ __global__ void __launch_bounds__(AT) attn_decode_cluster_kernel(const __half* q
       const bool valid = j <= p;
 #pragma unroll
       for (int h = 0; h < HSUB; ++h) s[ps][h] = 0.f;
-      if (valid) {
-        if (j == p) {
+      if (j == p) {
 #pragma unroll 4
-          for (int d = 0; d < HD; ++d) {
-            const float k = kn[d];
+        for (int d = 0; d < HD; ++d) {
+          const float k = kn[d];
 #pragma unroll
-            for (int h = 0; h < HSUB; ++h) s[ps][h] = fmaf(qs[h][d], k, s[ps][h]);
+          for (int h = 0; h < HSUB; ++h) s[ps][h] = fmaf(qs[h][d], k, s[ps][h]);
+        }
+      } else if (valid) {
+        const uint4* kr = reinterpret_cast<const uint4*>(kbase + (size_t)j * HD);
+#pragma unroll
+        for (int i = 0; i < HD / 8; ++i) {
+          const uint4 kq = ps < PRE ? kv[ps < PRE ? ps : 0][i] : kr[i];
+          const uint32_t w[4] = {kq.x, kq.y, kq.z, kq.w};
+          float kf[8];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[u]));
+            kf[2 * u] = f.x;
+            kf[2 * u + 1] = f.y;
           }
-        } else {
-          const uint4* kr = reinterpret_cast<const uint4*>(kbase + (size_t)j * HD);
-          uint4 kv[HD / 8];
 #pragma unroll
-          for (int i = 0; i < HD / 8; ++i) kv[i] = kr[i];
-#pragma unroll
-          for (int i = 0; i < HD / 8; ++i) {
-            const uint32_t w[4] = {kv[i].x, kv[i].y, kv[i].z, kv[i].w};
-            float kf[8];
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-              const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[u]));
-              kf[2 * u] = f.x;
-              kf[2 * u + 1] = f.y;
-            }
-#pragma unroll
-            for (int h = 0; h < HSUB; ++h) {
-              const float4 q0 = *reinterpret_cast<const float4*>(&qs[h][8 * i]);
-              const float4 q1 = *reinterpret_cast<const float4*>(&qs[h][8 * i + 4]);
-              float a = s[ps][h];
-              a = fmaf(q0.x, kf[0], a); a = fmaf(q0.y, kf[1], a); a = fmaf(q0.z, kf[2], a); a = fmaf(q0.w, kf[3], a);
-              a = fmaf(q1.x, kf[4], a); a = fmaf(q1.y, kf[5], a); a = fmaf(q1.z, kf[6], a); a = fmaf(q1.w, kf[7], a);
-              s[ps][h] = a;
-            }
+          for (int h = 0; h < HSUB; ++h) {
+            const float4 q0 = *reinterpret_cast<const float4*>(&qs[h][8 * i]);
+            const float4 q1 = *reinterpret_cast<const float4*>(&qs[h][8 * i + 4]);
+            float a = s[ps][h];
+            a = fmaf(q0.x, kf[0], a); a = fmaf(q0.y, kf[1], a); a = fmaf(q0.z, kf[2], a); a = fmaf(q0.w, kf[3], a);
+            a = fmaf(q1.x, kf[4], a); a = fmaf(q1.y, kf[5], a); a = fmaf(q1.z, kf[6], a); a = fmaf(q1.w, kf[7], a);
+            s[ps][h] = a;
           }
         }
       }
 #pragma unroll
       for (int h = 0; h < HSUB; ++h) s[ps][h] = valid ? s[ps][h] * scale : -INFINITY;
     }
+    float wm[HSUB];                                                 // this warp's maximum (may be -inf: nothing valid)
 #pragma unroll
     for (int h = 0; h < HSUB; ++h) {
       float m = s[0][h];
 #pragma unroll
       for (int ps = 1; ps < PASSES; ++ps) m = fmaxf(m, s[ps][h]);
-      m = warp_max(m);
-      if (lane == 0) redw[h][warp] = m;
-    }
-    __syncthreads();
-    float mx[HSUB];
-#pragma unroll
-    for (int h = 0; h < HSUB; ++h) {
-      float m = redw[h][0];
-#pragma unroll
-      for (int w = 1; w < NW; ++w) m = fmaxf(m, redw[h][w]);
-      mx[h] = m;                                                   // finite: position c0 <= p is always valid
-    }
-    __syncthreads();
-#pragma unroll
-    for (int h = 0; h < HSUB; ++h) {
+      wm[h] = warp_max(m);
+      const float ref = wm[h] == -INFINITY ? 0.f : wm[h];
       float l = 0.f;
 #pragma unroll
       for (int ps = 0; ps < PASSES; ++ps) {
-        const float e = __expf(s[ps][h] - mx[h]);                  // 0 for masked positions
+        const float e = __expf(s[ps][h] - ref);                    // 0 for masked positions
         sc[h][128 * ps + t] = e;
         l += e;
       }
       l = warp_sum(l);
-      if (lane == 0) redw[h][warp] = l;
+      if (lane == 0) {
+        wml[warp][h][0] = wm[h];
+        wml[warp][h][1] = l;
+      }
     }
-    __syncthreads();
+    __syncwarp();
 
-    // ---- P.V: warp w <-> positions c0 + w * 32 PASSES ...; lane <-> (row in the iteration, 8 dims)
+    // ---- P.V over the positions this warp scored: c0 + 128 pass + 32 warp + (0..31); lane <-> (row of the step, 8 dims)
     const int psub = lane / LPR, d0 = (lane % LPR) * 8;
     float acc[HSUB][8];
 #pragma unroll
     for (int h = 0; h < HSUB; ++h)
 #pragma unroll
       for (int u = 0; u < 8; ++u) acc[h][u] = 0.f;
-    constexpr int ITERS = 32 * PASSES / PPI, UNR = 8;
-    static_assert(ITERS % UNR == 0, "unroll must divide the iteration count");
-    for (int it0 = 0; it0 < ITERS; it0 += UNR) {
-      uint4 vv[UNR];
+    constexpr int IPP = 32 / PPI;                                    // warp steps per pass
+    constexpr int UNR = IPP < 8 ? IPP : 8;
 #pragma unroll
-      for (int u = 0; u < UNR; ++u) {
-        const int j = c0 + 32 * PASSES * warp + (it0 + u) * PPI + psub;
-        vv[u] = make_uint4(0u, 0u, 0u, 0u);
-        if (j < p) vv[u] = *reinterpret_cast<const uint4*>(vbase + (size_t)j * HD + d0);
-      }
+    for (int ps = 0; ps < PASSES; ++ps) {
+      for (int it0 = 0; it0 < IPP; it0 += UNR) {
+        uint4 vv[UNR];
 #pragma unroll
-      for (int u = 0; u < UNR; ++u) {
-        const int jl = 32 * PASSES * warp + (it0 + u) * PPI + psub, j = c0 + jl;
-        if (j > p) continue;
-        float vf[8];
-        if (j == p) {
-#pragma unroll
-          for (int k = 0; k < 8; ++k) vf[k] = vn[d0 + k];
-        } else {
-          const uint32_t w[4] = {vv[u].x, vv[u].y, vv[u].z, vv[u].w};
-#pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[k]));
-            vf[2 * k] = f.x;
-            vf[2 * k + 1] = f.y;
-          }
+        for (int u = 0; u < UNR; ++u) {
+          const int j = c0 + 128 * ps + 32 * warp + (it0 + u) * PPI + psub;
+          vv[u] = make_uint4(0u, 0u, 0u, 0u);
+          if (j < p) vv[u] = *reinterpret_cast<const uint4*>(vbase + (size_t)j * HD + d0);
         }
 #pragma unroll
-        for (int h = 0; h < HSUB; ++h) {
-          const float e = sc[h][jl];
+        for (int u = 0; u < UNR; ++u) {
+          const int jl = 128 * ps + 32 * warp + (it0 + u) * PPI + psub, j = c0 + jl;
+          if (j > p) continue;
+          float vf[8];
+          if (j == p) {
 #pragma unroll
-          for (int k = 0; k < 8; ++k) acc[h][k] = fmaf(e, vf[k], acc[h][k]);
+            for (int k = 0; k < 8; ++k) vf[k] = vn[d0 + k];
+          } else {
+            const uint32_t w[4] = {vv[u].x, vv[u].y, vv[u].z, vv[u].w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[k]));
+              vf[2 * k] = f.x;
+              vf[2 * k + 1] = f.y;
+            }
+          }
+#pragma unroll
+          for (int h = 0; h < HSUB; ++h) {
+            const float e = sc[h][jl];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) acc[h][k] = fmaf(e, vf[k], acc[h][k]);
+          }
         }
       }
     }
@@ -476,39 +483,56 @@ __global__ void __launch_bounds__(AT) attn_decode_cluster_kernel(const __half* q
         for (int k = 0; k < 8; ++k) red_o[warp][h][d0 + k] = acc[h][k];
     }
     __syncthreads();
+    // ---- the four warps' partials -> this chunk's partial (fixed warp order)
     for (int e = t; e < HSUB * HD; e += AT) {
       const int hl = e / HD, d = e - hl * HD;
-      float o = 0.f;
+      float M = wml[0][hl][0];
 #pragma unroll
-      for (int w = 0; w < NW; ++w) o += red_o[w][hl][d];
+      for (int w = 1; w < NW; ++w) M = fmaxf(M, wml[w][hl][0]);     // finite: position c0 <= p is valid
+      float o = 0.f, l = 0.f;
+#pragma unroll
+      for (int w = 0; w < NW; ++w) {
+        const float f = __expf(wml[w][hl][0] - M);                  // -inf -> 0
+        o += red_o[w][hl][d] * f;
+        l += wml[w][hl][1] * f;
+      }
       part_o[hl][d] = o;
-    }
-    if (t < HSUB) {
-      float l = 0.f;
-#pragma unroll
-      for (int w = 0; w < NW; ++w) l += redw[t][w];
-      part_ml[t][0] = mx[t];
-      part_ml[t][1] = l;
+      if (d == 0) {
+        part_ml[hl][0] = M;
+        part_ml[hl][1] = l;
+      }
     }
   }
   cluster_sync_all();                                               // every chunk's partials are in place
   if (chunk == 0) {
+    if (t < HSUB * NCL) {                                           // one thread per (head, chunk): both loads in flight
+      const int hl = t / NCL, c = t - hl * NCL;
+      if (c < nact) {
+        pml[hl][c][0] = ld_peer_f32(&part_ml[hl][0], (uint32_t)c);
+        pml[hl][c][1] = ld_peer_f32(&part_ml[hl][1], (uint32_t)c);
+      }
+    }
+    __syncthreads();
     if (t < nh) {
       float M = -INFINITY;
-      for (int c = 0; c < nact; ++c) M = fmaxf(M, ld_peer_f32(&part_ml[t][0], (uint32_t)c));
+      for (int c = 0; c < nact; ++c) M = fmaxf(M, pml[t][c][0]);
       float L = 0.f;
       for (int c = 0; c < nact; ++c) {
-        const float w = __expf(ld_peer_f32(&part_ml[t][0], (uint32_t)c) - M);
+        const float w = __expf(pml[t][c][0] - M);
         wgt[t][c] = w;
-        L += ld_peer_f32(&part_ml[t][1], (uint32_t)c) * w;
+        L += pml[t][c][1] * w;
       }
       wgt[t][NCL] = L;
     }
     __syncthreads();
     for (int e = t; e < nh * HD; e += AT) {
       const int hl = e / HD, d = e - hl * HD;
+      float pv[NCL];
+#pragma unroll
+      for (int c = 0; c < NCL; ++c) pv[c] = c < nact ? ld_peer_f32(&part_o[hl][d], (uint32_t)c) : 0.f;
       float o = 0.f;
-      for (int c = 0; c < nact; ++c) o += ld_peer_f32(&part_o[hl][d], (uint32_t)c) * wgt[hl][c];
+#pragma unroll
+      for (int c = 0; c < NCL; ++c) o += c < nact ? pv[c] * wgt[hl][c] : 0.f;
       out[(head0 + hl) * HD + d] = __float2half_rn(o / wgt[hl][NCL]);
     }
   }
