@@ -31,10 +31,12 @@ class DecodeDesc(C.Structure):
                 ("vocab", _I), ("max_len", _I), ("eps", _F), ("scale", _F), ("embed", _P), ("layer", C.POINTER(Layer)),
                 ("norm", _P), ("head", Linear), ("cosT", _P), ("sinT", _P), ("tok", _P), ("pos", _P), ("h", _P),
                 ("x", _P), ("qkv", _P), ("att", _P), ("act", _P), ("logits", _P), ("attn_ws", _P), ("attn_ws_bytes", _Z),
-                ("head_ws", _P), ("head_ws_bytes", _Z), ("status", _P), ("flags", _I)]
+                ("head_ws", _P), ("head_ws_bytes", _Z), ("status", _P), ("flags", _I), ("persistent_ws", _P),
+                ("persistent_ws_bytes", _Z)]
 
 
 STEP_TENSOR_CORE = 1
+STEP_PERSISTENT = 2
 
 
 # name -> (restype, argtypes); every symbol include/q4b200.h declares
@@ -67,6 +69,10 @@ SIGNATURES = {
     "q4b_quant_q8_1": (_I, [_P, _P, _P, _P, _I, _I, _P]),
     "q4b_rmsnorm_q8_1": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _F, _P]),
     "q4b_decode_step": (_I, [C.POINTER(DecodeDesc), _P]),
+    "q4b_decode_persistent_workspace": (_Z, [C.POINTER(DecodeDesc)]),
+    "q4b_decode_persistent_prepare": (_I, [C.POINTER(DecodeDesc), _P, _Z]),
+    "q4b_decode_persistent_layers": (_I, [C.POINTER(DecodeDesc), _P, _Z, _P]),
+    "q4b_decode_persistent_trace": (_I, [_P, _I]),
 }
 
 

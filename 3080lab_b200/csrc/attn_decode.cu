@@ -299,9 +299,36 @@ __global__ void __launch_bounds__(AT) attn_decode_cluster_kernel(const __half* q
   const int kvh = blockIdx.y / nsub, hs = blockIdx.y - kvh * nsub;
   const int h0 = hs * HSUB, nh = min(HSUB, GRP - h0);
   const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
-  int p = (int)posp[b];
-  p = p < 0 ? 0 : (p >= max_len ? max_len - 1 : p);
   const int c0 = chunk * CHK;
+  const int64_t praw = posp[b];
+  __half* kbase = kc + ((size_t)b * NKV + kvh) * (size_t)max_len * HD;
+  __half* vbase = vc + ((size_t)b * NKV + kvh) * (size_t)max_len * HD;
+  const int psub = lane / LPR, d0 = (lane % LPR) * 8;     // P.V pass: lane <-> (row of the warp step, 8 dims)
+  constexpr int IPP = 32 / PPI;                          // warp steps per pass
+  constexpr bool VPRE = PASSES == 1;                     // V rows of the chunk held in registers from the start
+
+  // ---- K (and, for one-pass chunks, V) rows are requested before the position is known, so that the position, the
+  // cache rows and the new q/k/v row are one round trip to memory instead of two.  Rows at or beyond the current
+  // position hold stale or concurrently appended data; they are loaded but never used.
+  constexpr int PRE = PASSES * HD <= 256 ? PASSES : 256 / HD;       // passes whose K row is held in registers
+  uint4 kv[PRE][HD / 8];
+#pragma unroll
+  for (int ps = 0; ps < PRE; ++ps) {
+    const int j = min(c0 + 128 * ps + t, max_len - 1);
+    const uint4* kr = reinterpret_cast<const uint4*>(kbase + (size_t)j * HD);
+#pragma unroll
+    for (int i = 0; i < HD / 8; ++i) kv[ps][i] = kr[i];
+  }
+  uint4 vpre[VPRE ? IPP : 1];
+  if (VPRE) {
+#pragma unroll
+    for (int it = 0; it < IPP; ++it) {
+      const int j = min(c0 + 32 * warp + it * PPI + psub, max_len - 1);
+      vpre[it] = *reinterpret_cast<const uint4*>(vbase + (size_t)j * HD + d0);
+    }
+  }
+  int p = (int)praw;
+  p = p < 0 ? 0 : (p >= max_len ? max_len - 1 : p);
   const bool active = c0 <= p;
   const int nact = p / CHK + 1;
   const size_t head0 = (size_t)b * NH + (size_t)kvh * GRP + h0;
@@ -312,24 +339,6 @@ __global__ void __launch_bounds__(AT) attn_decode_cluster_kernel(const __half* q
     const __half* row = qkv + (size_t)b * QKV;
     const float* cs = cosT + (size_t)p * HALF;
     const float* sn = sinT + (size_t)p * HALF;
-    __half* kbase = kc + ((size_t)b * NKV + kvh) * (size_t)max_len * HD;
-    __half* vbase = vc + ((size_t)b * NKV + kvh) * (size_t)max_len * HD;
-
-    // ---- this thread's K rows first (positions c0 + 128 pass + t): they do not depend on the query preparation
-    constexpr int PRE = PASSES * HD <= 256 ? PASSES : 256 / HD;       // passes whose K row is held in registers
-    uint4 kv[PRE][HD / 8];
-#pragma unroll
-    for (int ps = 0; ps < PRE; ++ps) {
-      const int j = c0 + 128 * ps + t;
-      if (j < p) {
-        const uint4* kr = reinterpret_cast<const uint4*>(kbase + (size_t)j * HD);
-#pragma unroll
-        for (int i = 0; i < HD / 8; ++i) kv[ps][i] = kr[i];
-      } else {
-#pragma unroll
-        for (int i = 0; i < HD / 8; ++i) kv[ps][i] = make_uint4(0u, 0u, 0u, 0u);
-      }
-    }
     for (int e = t; e < HSUB * HD; e += AT) {
       const int hl = e / HD, d = e - hl * HD, dd = d % HALF;
       float r = 0.f;
@@ -376,7 +385,7 @@ __global__ void __launch_bounds__(AT) attn_decode_cluster_kernel(const __half* q
         const uint4* kr = reinterpret_cast<const uint4*>(kbase + (size_t)j * HD);
 #pragma unroll
         for (int i = 0; i < HD / 8; ++i) {
-          const uint4 kq = ps < PRE ? kv[ps < PRE ? ps : 0][i] : kr[i];
+          const uint4 kq = ps < PRE ? kv[ps < PRE ? ps : 0][i] : kr[i];   // (registers hold rows below p exactly)
           const uint32_t w[4] = {kq.x, kq.y, kq.z, kq.w};
           float kf[8];
 #pragma unroll
@@ -422,24 +431,27 @@ __global__ void __launch_bounds__(AT) attn_decode_cluster_kernel(const __half* q
     }
     __syncwarp();
 
-    // ---- P.V over the positions this warp scored: c0 + 128 pass + 32 warp + (0..31); lane <-> (row of the step, 8 dims)
-    const int psub = lane / LPR, d0 = (lane % LPR) * 8;
+    // ---- P.V over the positions this warp scored: c0 + 128 pass + 32 warp + (0..31)
     float acc[HSUB][8];
 #pragma unroll
     for (int h = 0; h < HSUB; ++h)
 #pragma unroll
       for (int u = 0; u < 8; ++u) acc[h][u] = 0.f;
-    constexpr int IPP = 32 / PPI;                                    // warp steps per pass
     constexpr int UNR = IPP < 8 ? IPP : 8;
 #pragma unroll
     for (int ps = 0; ps < PASSES; ++ps) {
+#pragma unroll
       for (int it0 = 0; it0 < IPP; it0 += UNR) {
         uint4 vv[UNR];
 #pragma unroll
         for (int u = 0; u < UNR; ++u) {
           const int j = c0 + 128 * ps + 32 * warp + (it0 + u) * PPI + psub;
-          vv[u] = make_uint4(0u, 0u, 0u, 0u);
-          if (j < p) vv[u] = *reinterpret_cast<const uint4*>(vbase + (size_t)j * HD + d0);
+          if (VPRE) {
+            vv[u] = vpre[it0 + u];
+          } else {
+            vv[u] = make_uint4(0u, 0u, 0u, 0u);
+            if (j < p) vv[u] = *reinterpret_cast<const uint4*>(vbase + (size_t)j * HD + d0);
+          }
         }
 #pragma unroll
         for (int u = 0; u < UNR; ++u) {
@@ -595,6 +607,9 @@ size_t attn_decode_workspace(int B, int NH, int HD, int max_len) {
   return align16((size_t)B * NH * 4) + align16((size_t)B * NH * NC * 2 * 4) + (size_t)B * NH * NC * HD * 4;
 }
 
+int attn_decode_mma(const void*, const float*, const float*, const int64_t*, void*, void*, void*, int, int, int, int, float,
+                    cudaStream_t);
+
 int attn_decode(const void* qkv, const float* cosT, const float* sinT, const int64_t* pos, void* kc, void* vc, void* out,
                 int B, int NH, int NKV, int HD, int max_len, float scale, void* ws, size_t ws_bytes, cudaStream_t st) {
   if (B <= 0 || NH <= 0 || NKV <= 0 || max_len <= 0 || (NH % NKV) || NH / NKV > 8 || (HD != 64 && HD != 128))
@@ -602,6 +617,10 @@ int attn_decode(const void* qkv, const float* cosT, const float* sinT, const int
   if (!qkv || !cosT || !sinT || !pos || !kc || !vc || !out || !ws || !aligned16(kc) || !aligned16(vc) || !aligned16(ws))
     return fail(Q4B_E_ALIGN, "attn_decode: null or misaligned pointer");
   if (ws_bytes < attn_decode_workspace(B, NH, HD, max_len)) return fail(Q4B_E_WORKSPACE, "attn_decode: workspace too small");
+  // Several sequences: the tensor-core kernel that reads K/V once per KV group (throughput); one sequence keeps the
+  // latency-oriented kernels below.
+  if (B >= 2 && HD == 128 && aligned16(qkv))
+    return attn_decode_mma(qkv, cosT, sinT, pos, kc, vc, out, B, NH, NKV, max_len, scale, st);
   if (max_len <= NCL * 128 * 4) {
     // cluster path: 8 chunks of 128 / 256 / 512 positions; a head group is served by 1..4 CTAs
     static const int hsub_for[9] = {1, 1, 2, 3, 2, 3, 2, 4, 4};

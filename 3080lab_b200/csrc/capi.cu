@@ -47,6 +47,10 @@ int blockdot(const void*, const void*, int32_t*, int, int, int, int, uint32_t*, 
 int mmq_stream(const void*, const void*, const void*, const void*, void*, const void*, int, int, int, int, int, int, uint32_t*,
                cudaStream_t, const float* norm_w = nullptr, float eps = 0.f);
 void mmq_stream_trace(unsigned long long*);
+size_t decode_persistent_workspace(const q4b_decode_desc*);
+int decode_persistent_prepare(const q4b_decode_desc*, void*, size_t);
+int decode_persistent_layers(const q4b_decode_desc*, void*, size_t, cudaStream_t);
+void decode_persistent_trace(unsigned long long*, int);
 int attn_prefill(const void*, const float*, const float*, void*, void*, void*, int, int, int, int, int, int, float, cudaStream_t);
 size_t q8_tiled_bytes(int, int);
 int mmq_prefill(const void*, const void*, const void*, void*, const void*, int, int, int, int, int, uint32_t*, cudaStream_t);
@@ -216,7 +220,9 @@ int q4b_decode_step(const q4b_decode_desc* d, q4b_stream_t stream) {
     if (rc_ != Q4B_OK) return rc_; \
   } while (0)
   Q4B_TRY(embed(d->embed, d->tok, d->h, 1, H, d->vocab, st));
-  for (int i = 0; i < d->layers; ++i) {
+  const bool persistent = (d->flags & Q4B_STEP_PERSISTENT) && d->persistent_ws && d->status;
+  if (persistent) Q4B_TRY(decode_persistent_layers(d, d->persistent_ws, d->persistent_ws_bytes, st));
+  for (int i = 0; i < d->layers && !persistent; ++i) {
     const q4b_layer& L = d->layer[i];
     Q4B_TRY(norm_lin(L.ln1, L.qkv, d->qkv, L.qkv_bias, Q4B_EPI_BIASF));
     Q4B_TRY(attn_decode(d->qkv, d->cosT, d->sinT, d->pos, L.kc, L.vc, d->att, 1, d->n_heads, d->n_kv_heads, d->head_dim,
@@ -234,6 +240,18 @@ int q4b_decode_step(const q4b_decode_desc* d, q4b_stream_t stream) {
     Q4B_TRY(head_f16_argmax(d->embed, d->x, d->logits, d->vocab, H, d->tok, d->pos, d->head_ws, d->head_ws_bytes, st));
   }
 #undef Q4B_TRY
+  return Q4B_OK;
+}
+
+size_t q4b_decode_persistent_workspace(const q4b_decode_desc* desc) { return decode_persistent_workspace(desc); }
+int q4b_decode_persistent_prepare(const q4b_decode_desc* desc, void* ws, size_t ws_bytes) {
+  return decode_persistent_prepare(desc, ws, ws_bytes);
+}
+int q4b_decode_persistent_layers(const q4b_decode_desc* desc, void* ws, size_t ws_bytes, q4b_stream_t stream) {
+  return decode_persistent_layers(desc, ws, ws_bytes, S(stream));
+}
+int q4b_decode_persistent_trace(uint64_t* device_buffer, int stride) {
+  decode_persistent_trace(reinterpret_cast<unsigned long long*>(device_buffer), device_buffer ? stride : 0);   // stride < 0: |stride| stamps per CTA, stages subdivided
   return Q4B_OK;
 }
 

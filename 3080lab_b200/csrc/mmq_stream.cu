@@ -337,12 +337,51 @@ __global__ void __launch_bounds__(ROWS) mmq_stream_kernel(const StreamArgs a) {
   __syncthreads();                                      // every thread is done with the slabs and with TMEM
   stamp();                                              // all batches folded
 
+  // one output value: column (sequence) n of this thread's row
+  auto emit = [&](int n, float v) {
+    const float partner = __shfl_xor_sync(0xffffffffu, v, 1);
+    if (n < a.cols && row < a.N) {
+      const size_t base = (size_t)n * a.ldy;
+      switch (a.epi) {
+        case Q4B_EPI_STORE: reinterpret_cast<__half*>(a.Y)[base + row] = __float2half_rn(v); break;
+        case Q4B_EPI_BIASF:
+          reinterpret_cast<__half*>(a.Y)[base + row] = __float2half_rn(v + reinterpret_cast<const float*>(a.AUX)[row]);
+          break;
+        case Q4B_EPI_RESID: reinterpret_cast<float*>(a.Y)[base + row] += v; break;
+        case Q4B_EPI_LOGITS: reinterpret_cast<float*>(a.Y)[base + row] = v; break;
+        case Q4B_EPI_SWIGLU:
+          if ((t & 1) == 0) reinterpret_cast<__half*>(a.Y)[base + (row >> 1)] = __float2half_rn(v / (1.f + __expf(-v)) * partner);
+          break;
+        default: break;
+      }
+    }
+  };
+
   // ---- split-K.  Few accumulators per thread: every peer pushes its partial sums into the leader's shared memory
-  // (remote stores), one cluster barrier publishes them and the leader adds them in rank order.  Many accumulators
-  // (16 / 32 activation rows): the push buffer would not fit beside the slabs, so peers park their partials in their
-  // own dead weight slab and the leader pulls them between two barriers.
-  if (a.ksplit > 1) {
-    if (PUSH) {
+  // (remote stores), one cluster barrier publishes them and the leader adds them in rank order and writes the output.
+  // Many accumulators (16 / 32 activation rows): a reduce-scatter.  Every CTA parks its partials in its own dead
+  // weight slab; after one cluster barrier rank r sums columns r, r + ksplit, ... over all ranks (in rank order, so
+  // the result does not depend on which CTA does it) and writes those columns itself.  Per thread that is NACC remote
+  // loads spread over the cluster instead of (ksplit - 1) NACC on the leader.
+  if (a.ksplit > 1 && !PUSH) {
+    float* part = reinterpret_cast<float*>(slabW);      // [NACC][128], every thread is past its last slab read
+#pragma unroll
+    for (int n = 0; n < NACC; ++n) part[n * ROWS + t] = acc[n];
+    cluster_sync_all();
+    for (int n = ks; n < NACC; n += a.ksplit) {
+      float pv[8];
+#pragma unroll
+      for (int r = 0; r < 8; ++r) pv[r] = r < a.ksplit ? ld_peer_f32(part + n * ROWS + t, (uint32_t)r) : 0.f;
+      float v = 0.f;
+#pragma unroll
+      for (int r = 0; r < 8; ++r)
+        if (r < a.ksplit) v += pv[r];
+      emit(n, v);
+    }
+    cluster_sync_all();                                 // peers stay resident until everyone has read them
+    stamp();                                            // split-K reduced
+  } else {
+    if (a.ksplit > 1) {
       if (ks != 0) {
         uint32_t remote;
         asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(tc::smem_u32(red_buf)), "r"(0));
@@ -359,44 +398,11 @@ __global__ void __launch_bounds__(ROWS) mmq_stream_kernel(const StreamArgs a) {
           for (int n = 0; n < NACC; ++n) acc[n] += red_buf[((r - 1) * NACC + n) * ROWS + t];
         }
       }
-    } else {
-      float* part = reinterpret_cast<float*>(slabW);    // [NACC][128], every thread is past its last slab read
-      if (ks != 0) {
-#pragma unroll
-        for (int n = 0; n < NACC; ++n) part[n * ROWS + t] = acc[n];
-      }
-      cluster_sync_all();
-      if (ks == 0) {
-        for (int r = 1; r < a.ksplit; ++r) {
-#pragma unroll
-          for (int n = 0; n < NACC; ++n) acc[n] += ld_peer_f32(part + n * ROWS + t, (uint32_t)r);
-        }
-      }
-      cluster_sync_all();                               // peers stay resident until the leader has read them
     }
-  }
-  stamp();                                              // split-K reduced
-
-  if (ks == 0) {
+    stamp();                                            // split-K reduced
+    if (ks == 0) {
 #pragma unroll
-    for (int n = 0; n < NACC; ++n) {
-      const float v = acc[n];
-      const float partner = __shfl_xor_sync(0xffffffffu, v, 1);
-      if (n < a.cols && row < a.N) {
-        const size_t base = (size_t)n * a.ldy;
-        switch (a.epi) {
-          case Q4B_EPI_STORE: reinterpret_cast<__half*>(a.Y)[base + row] = __float2half_rn(v); break;
-          case Q4B_EPI_BIASF:
-            reinterpret_cast<__half*>(a.Y)[base + row] = __float2half_rn(v + reinterpret_cast<const float*>(a.AUX)[row]);
-            break;
-          case Q4B_EPI_RESID: reinterpret_cast<float*>(a.Y)[base + row] += v; break;
-          case Q4B_EPI_LOGITS: reinterpret_cast<float*>(a.Y)[base + row] = v; break;
-          case Q4B_EPI_SWIGLU:
-            if ((t & 1) == 0) reinterpret_cast<__half*>(a.Y)[base + (row >> 1)] = __float2half_rn(v / (1.f + __expf(-v)) * partner);
-            break;
-          default: break;
-        }
-      }
+      for (int n = 0; n < NACC; ++n) emit(n, acc[n]);
     }
   }
   if (!ok && t == 0) atomicExch(a.status, 1u);

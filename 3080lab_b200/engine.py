@@ -24,7 +24,8 @@ def _dev(a: np.ndarray, device):
 
 
 class FusedQwen:
-    def __init__(self, model: dict, max_len: int = 1024, device="cuda:0", tensor_core: bool = True):
+    def __init__(self, model: dict, max_len: int = 1024, device="cuda:0", tensor_core: bool = True,
+                 persistent: bool = False):
         if not torch.cuda.is_available():
             raise RuntimeError("FusedQwen needs a CUDA device; there is no CPU path")
         self.cfg: ModelConfig = model["cfg"]
@@ -72,6 +73,24 @@ class FusedQwen:
         self._desc = self._make_desc()
         fused = tensor_core and c.hidden % 256 == 0
         self.launches_per_step = 1 + (5 if fused else 7) * c.layers + 2
+        self.persistent = False
+        if persistent:
+            self.enable_persistent()
+
+    def enable_persistent(self) -> None:
+        """Route `step()` through the one-kernel-for-all-layers path.  Raises if the model shape is not supported."""
+        c = self.cfg
+        need = _ffi.lib().q4b_decode_persistent_workspace(C.byref(self._desc))
+        if need == 0 or not self.tensor_core:
+            raise _ffi.Q4BError(_ffi.E_SHAPE, "persistent decode: model shape not supported (needs tile-packed weights, "
+                                "hidden % 256 == 0, head_dim 64 or 128, at most 8 query heads per KV head)")
+        self.persistent_ws = torch.zeros(need, dtype=torch.uint8, device=self.device)
+        self._desc.persistent_ws = self.persistent_ws.data_ptr()
+        self._desc.persistent_ws_bytes = need
+        _ffi.call("q4b_decode_persistent_prepare", C.byref(self._desc), self.persistent_ws.data_ptr(), need)
+        self._desc.flags |= _ffi.STEP_PERSISTENT
+        self.persistent = True
+        self.launches_per_step = 1 + 1 + 2
 
     # ---- descriptor for the one-call step -------------------------------------------------------------------------
     def _make_desc(self):
@@ -96,7 +115,7 @@ class FusedQwen:
             self.cos.data_ptr(), self.sin.data_ptr(), self.tok.data_ptr(), self.pos.data_ptr(), self.h.data_ptr(),
             self.x.data_ptr(), self.qkv.data_ptr(), self.att.data_ptr(), self.xm.data_ptr(), self.logits.data_ptr(),
             self.attn_ws.data_ptr(), self.attn_ws.numel(), self.head_ws.data_ptr(), self.head_ws.numel(),
-            self.status.data_ptr(), _ffi.STEP_TENSOR_CORE if self.tensor_core else 0)
+            self.status.data_ptr(), _ffi.STEP_TENSOR_CORE if self.tensor_core else 0, None, 0)
 
     # ---- one decode token -------------------------------------------------------------------------------------------
     def step(self) -> None:

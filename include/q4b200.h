@@ -246,13 +246,34 @@ typedef struct {
   float* logits;          /* fp32 [vocab] */
   void* attn_ws;  size_t attn_ws_bytes;   /* q4b_attn_decode_workspace(1, ...) */
   void* head_ws;  size_t head_ws_bytes;   /* max(q4b_head_workspace, q4b_argmax_workspace(1, vocab)) */
-  uint32_t* status;       /* [1] set to 1 when a bounded device-side wait expired (tensor-core path); zero it once */
+  uint32_t* status;       /* [1] set non-zero when a bounded device-side wait expired (tensor-core paths); zero it once */
   int flags;              /* Q4B_STEP_* */
+  void* persistent_ws;    /* Q4B_STEP_PERSISTENT: q4b_decode_persistent_workspace bytes, prepared once */
+  size_t persistent_ws_bytes;
 } q4b_decode_desc;
 
 #define Q4B_STEP_TENSOR_CORE 1  /* linears through q4b_gemv_q4_0_tc where K is a multiple of 256 */
+#define Q4B_STEP_PERSISTENT 2   /* all layers in one cooperative kernel (q4b_decode_persistent_layers) */
 
 int q4b_decode_step(const q4b_decode_desc* desc, q4b_stream_t stream);
+
+/* ---- persistent decode: every layer of one batch-1 token in ONE cooperative kernel, one CTA per SM -------------
+ * Same arithmetic and rounding points as the launch sequence above (scripts/qwen_fused.py:113-145: rmsnorm, qkv
+ * GEMV + bias, RoPE / KV append / attention, o GEMV + residual, rmsnorm, gate/up GEMV + SwiGLU, down GEMV +
+ * residual, per layer), but the ops are separated by grid barriers instead of kernel boundaries and the Q4_0 weights
+ * stream through a shared-memory ring that never waits for activations.  Every layer matrix needs its tile-packed
+ * copy (q4b_pack_q4_0); hidden a multiple of 256, head_dim 64 or 128, at most 8 query heads per KV head.
+ *   workspace: bytes of device scratch for this model shape (0 if the shape is not supported).
+ *   prepare:   one-time, synchronous: writes the device-side layer table into the workspace and zeroes its counters.
+ *   layers:    in: desc->h = embedding row of the token, desc->pos = its position; out: desc->h = residual stream
+ *              after the last layer, K/V rows appended.  desc->act is used as scratch.  Launches must not overlap
+ *              on one workspace.  A bounded wait that expires sets *desc->status (2: grid barrier, 1: pipeline). */
+size_t q4b_decode_persistent_workspace(const q4b_decode_desc* desc);
+int q4b_decode_persistent_prepare(const q4b_decode_desc* desc, void* ws, size_t ws_bytes);
+int q4b_decode_persistent_layers(const q4b_decode_desc* desc, void* ws, size_t ws_bytes, q4b_stream_t stream);
+/* Optional timeline of the next persistent launches: `stride` %globaltimer stamps per CTA (start, after each grid
+ * barrier, end) into a device buffer of (SM count) x stride uint64; null switches it off.  No reference counterpart. */
+int q4b_decode_persistent_trace(uint64_t* device_buffer, int stride);
 
 #ifdef __cplusplus
 }
