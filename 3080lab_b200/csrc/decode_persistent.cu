@@ -56,7 +56,7 @@ constexpr int MAX_KSPLIT = 16;             // K slices of one linear
 constexpr int MAX_WHEADS = 8;              // heads one K slice of o_proj may touch
 constexpr uint32_t IDESC = tc::idesc_i8(128, 8);
 constexpr uint32_t GRID_WAIT_LIMIT = 1u << 20;   // acquire polls of a grid barrier (well under a second)
-constexpr uint32_t PIPE_WAIT_LIMIT = 1u << 20;   // try_waits of a pipeline mbarrier
+constexpr uint32_t PIPE_WAIT_LIMIT = 1u << 16;   // try_waits (each may sleep up to 20 us) of a pipeline mbarrier
 constexpr size_t MAX_DYN_SMEM = 226 * 1024;
 
 struct PLinear {
@@ -196,8 +196,8 @@ __global__ void __launch_bounds__(PT, 1) decode_persistent_kernel(const __grid_c
   auto wait = [&](uint64_t* bar, uint32_t parity) {
     if (!ok) return;
     for (uint32_t i = 0; i < PIPE_WAIT_LIMIT; ++i) {
-      if (tc::mbar_try(bar, parity)) return;
-      if ((i & 255u) == 255u && abort_s) break;
+      if (tc::mbar_try_hint(bar, parity, 20000u)) return;
+      if ((i & 15u) == 15u && abort_s) break;
     }
     ok = false;
     abort_s = 1u;

@@ -28,6 +28,8 @@
 //   * split-K: the CTAs of a thread-block cluster share a row tile; partial sums cross through distributed shared
 //     memory and are added in rank order, so results are bit-repeatable.
 // All waits are bounded (status word + fall through).
+#include <algorithm>
+
 #include "q4b_internal.h"
 #include "tc05.cuh"
 
@@ -54,6 +56,8 @@ struct StreamArgs {
   int N, K, cols, epi, ldy;
   int gps;              // groups (of 8 k-blocks) per K slice
   int ksplit;
+  int KBT;              // k-blocks per row of W / S / X in memory (K/32 unless this launch covers a window of K)
+  int kbw;              // first k-block of the window
 };
 
 __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
@@ -127,7 +131,7 @@ __global__ void __launch_bounds__(ROWS) mmq_stream_kernel(const StreamArgs a) {
 
   // ---- weights: per batch of G k-blocks one bulk copy of nibbles and one of scales, issued by one thread
   if (t == 0) {
-    const size_t kbg = (size_t)blockIdx.x * KB + kb0;            // first k-block of this CTA in the packed arrays
+    const size_t kbg = (size_t)blockIdx.x * a.KBT + a.kbw + kb0;  // first k-block of this CTA in the packed arrays
     for (int b = 0; b < nbatch; ++b) {
       tc::mbar_expect_tx(&bar_load[b], (uint32_t)G * (2048 + 256));
       bulk_g2s(slabW + (size_t)b * G * 2048, a.W + (kbg + (size_t)b * G) * 2048, (uint32_t)G * 2048, &bar_load[b]);
@@ -142,18 +146,30 @@ __global__ void __launch_bounds__(ROWS) mmq_stream_kernel(const StreamArgs a) {
   if (MODE == MODE_Q8) {
     const int8_t* xq = reinterpret_cast<const int8_t*>(a.X);
     const int per = nkb * 2;
-    for (int c = t; c < NT * per; c += ROWS) {
-      const int n = c / per, r = c - n * per, kbl = r >> 1, kc = r & 1;
-      uint4 v = make_uint4(0u, 0u, 0u, 0u);
-      if (n < a.cols) v = *reinterpret_cast<const uint4*>(xq + (size_t)n * a.K + (size_t)(kb0 + kbl) * 32 + kc * 16);
-      uint32_t e0, o0, e1, o1;
-      tc::permute_bytes(v.x, v.y, e0, o0);
-      tc::permute_bytes(v.z, v.w, e1, o1);
-      *reinterpret_cast<uint4*>(sB + b_offset<NT>(kbl, n, kc * 16)) = make_uint4(e0, o0, e1, o1);
+    for (int c0 = 0; c0 < NT * per; c0 += 4 * ROWS) {
+      uint4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int c = c0 + u * ROWS + t;
+        const int n = c / per, r = c - n * per, kbl = r >> 1, kc = r & 1;
+        v[u] = make_uint4(0u, 0u, 0u, 0u);
+        if (c < NT * per && n < a.cols) v[u] = *reinterpret_cast<const uint4*>(xq + ((size_t)n * a.KBT + a.kbw + kb0 + kbl) * 32 + kc * 16);
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int c = c0 + u * ROWS + t;
+        if (c < NT * per) {
+          const int n = c / per, r = c - n * per, kbl = r >> 1, kc = r & 1;
+          uint32_t e0, o0, e1, o1;
+          tc::permute_bytes(v[u].x, v[u].y, e0, o0);
+          tc::permute_bytes(v[u].z, v[u].w, e1, o1);
+          *reinterpret_cast<uint4*>(sB + b_offset<NT>(kbl, n, kc * 16)) = make_uint4(e0, o0, e1, o1);
+        }
+      }
     }
     for (int c = t; c < NT * nkb; c += ROWS) {
       const int n = c / nkb, kbl = c - n * nkb;
-      xs[kbl * NT + n] = n < a.cols ? __half2float(a.XD[(size_t)n * KB + kb0 + kbl]) : 0.f;
+      xs[kbl * NT + n] = n < a.cols ? __half2float(a.XD[(size_t)n * a.KBT + a.kbw + kb0 + kbl]) : 0.f;
     }
   } else {
     // exact mode: 8 lanes <-> one k-block, 4 consecutive elements per lane.  X_i = rint(x_i * 2^-e) with
@@ -368,16 +384,28 @@ __global__ void __launch_bounds__(ROWS) mmq_stream_kernel(const StreamArgs a) {
 #pragma unroll
     for (int n = 0; n < NACC; ++n) part[n * ROWS + t] = acc[n];
     cluster_sync_all();
-    for (int n = ks; n < NACC; n += a.ksplit) {
-      float pv[8];
+    // all remote loads of this thread are issued before the first add: own column i (= ks + i ksplit), rank r -> pv[i ksplit + r]
+    constexpr int NPV = NACC + 8;
+    float pv[NPV];
 #pragma unroll
-      for (int r = 0; r < 8; ++r) pv[r] = r < a.ksplit ? ld_peer_f32(part + n * ROWS + t, (uint32_t)r) : 0.f;
+    for (int q = 0; q < NPV; ++q) {
+      const int i = q / a.ksplit, r = q - i * a.ksplit, n = ks + i * a.ksplit;
+      pv[q] = n < NACC ? ld_peer_f32(part + n * ROWS + t, (uint32_t)r) : 0.f;
+    }
+    float* fin = reinterpret_cast<float*>(sB);          // [own column][128]: the B operand is dead (all MMAs retired)
+    {
       float v = 0.f;
 #pragma unroll
-      for (int r = 0; r < 8; ++r)
-        if (r < a.ksplit) v += pv[r];
-      emit(n, v);
+      for (int q = 0; q < NPV; ++q) {
+        const int i = q / a.ksplit, r = q - i * a.ksplit;
+        v += pv[q];                                     // rank order 0, 1, ... within a column
+        if (r == a.ksplit - 1) {
+          fin[i * ROWS + t] = v;
+          v = 0.f;
+        }
+      }
     }
+    for (int n = ks, i = 0; n < NACC; n += a.ksplit, ++i) emit(n, fin[i * ROWS + t]);
     cluster_sync_all();                                 // peers stay resident until everyone has read them
     stamp();                                            // split-K reduced
   } else {
@@ -441,6 +469,7 @@ bool plan(int N, int K, int nt, int nacc, Geometry& g) {
     if ((ks - 1) * gps >= GT) continue;                 // an empty slice
     if (gps * 8 / G > MAX_BATCH || gps > 10) continue;
     if (smem_bytes(gps, nt, nacc, ks) > MAX_DYN_SMEM) continue;
+    if (g.tcols == 512 && best > 0 && (long)tiles * ks > (long)sms) break;   // one CTA per SM: stay within one wave
     best = ks;
     if ((long)tiles * ks >= (long)sms * 3 / 2) break;   // enough CTAs for two per SM on most of the machine
   }
@@ -507,6 +536,35 @@ int launch_nt(int nt, const StreamArgs& a, const Geometry& g, cudaStream_t st) {
 // Device buffer for the optional timeline stamps of the next launches (16 x uint64 per CTA, up to 4096 CTAs); null = off.
 void mmq_stream_trace(unsigned long long* buf) { g_trace = buf; }
 
+// Q8_1 mode over the K window [32 kbw, 32 kbw + Kwin) of matrices whose rows hold Ktot values.
+static int mmq_stream_window(const void* W, const void* S, const void* X, const void* XD, void* Y, const void* AUX, int N, int Ktot,
+                             int kbw, int Kwin, int cols, int epilogue, int ldy, uint32_t* status, cudaStream_t st) {
+  const int nt = cols <= 8 ? 8 : (cols <= 16 ? 16 : 32);
+  Geometry g;
+  if (!plan(N, Kwin, nt, nt, g)) return fail(Q4B_E_SHAPE, "mmq_stream: K window does not fit");
+  StreamArgs a;
+  a.W = reinterpret_cast<const uint8_t*>(W);
+  a.S = reinterpret_cast<const __half*>(S);
+  a.X = X;
+  a.XD = reinterpret_cast<const __half*>(XD);
+  a.NW = nullptr;
+  a.eps = 0.f;
+  a.trace = g_trace;
+  a.Y = Y;
+  a.AUX = AUX;
+  a.status = status;
+  a.N = N;
+  a.K = Kwin;
+  a.cols = cols;
+  a.epi = epilogue;
+  a.ldy = ldy;
+  a.gps = g.gps;
+  a.ksplit = g.ksplit;
+  a.KBT = Ktot / 32;
+  a.kbw = kbw;
+  return launch_nt<MODE_Q8>(nt, a, g, st);
+}
+
 // mode: 0 exact fp16 x, 1 exact fp32 x, 2 Q8_1, 3 exact with RMSNorm of the fp32 row X fused in front.
 // cols: 1 for the exact modes, 1..32 sequences for Q8_1.
 int mmq_stream(const void* W, const void* S, const void* X, const void* XD, void* Y, const void* AUX, int N, int K,
@@ -524,7 +582,24 @@ int mmq_stream(const void* W, const void* S, const void* X, const void* XD, void
   if (epilogue == Q4B_EPI_BIASF && !AUX) return fail(Q4B_E_ALIGN, "mmq_stream: biasf needs AUX");
   const int nt = mode != MODE_Q8 ? 8 : (cols <= 8 ? 8 : (cols <= 16 ? 16 : 32));
   Geometry g;
-  if (!plan(N, K, nt, mode == MODE_Q8 ? nt : 1, g)) return fail(Q4B_E_SHAPE, "mmq_stream: no K split fits shared memory for this K");
+  if (!plan(N, K, nt, mode == MODE_Q8 ? nt : 1, g)) {
+    // K too long for one CTA's shared memory even at the largest split: cover it in windows, accumulating into the
+    // fp32 output (epilogues that are linear in K only: the first window stores or adds, the others add).
+    if (mode != MODE_Q8 || (epilogue != Q4B_EPI_RESID && epilogue != Q4B_EPI_LOGITS))
+      return fail(Q4B_E_SHAPE, "mmq_stream: no K split fits shared memory for this K");
+    for (int nwin = 2; nwin <= 8; ++nwin) {
+      const int gw = (K / 256 + nwin - 1) / nwin;         // 256-groups per window
+      Geometry gt;
+      if (!plan(N, gw * 256, nt, nt, gt)) continue;
+      for (int w = 0; w * gw < K / 256; ++w) {
+        const int kw = std::min(gw, K / 256 - w * gw) * 256;
+        int rc = mmq_stream_window(W, S, X, XD, Y, AUX, N, K, w * gw * 8, kw, cols, w == 0 ? epilogue : Q4B_EPI_RESID, ldy, status, st);
+        if (rc != Q4B_OK) return rc;
+      }
+      return Q4B_OK;
+    }
+    return fail(Q4B_E_SHAPE, "mmq_stream: no K split fits shared memory for this K");
+  }
   StreamArgs a;
   a.W = reinterpret_cast<const uint8_t*>(W);
   a.S = reinterpret_cast<const __half*>(S);
@@ -543,6 +618,8 @@ int mmq_stream(const void* W, const void* S, const void* X, const void* XD, void
   a.ldy = ldy;
   a.gps = g.gps;
   a.ksplit = g.ksplit;
+  a.KBT = K / 32;
+  a.kbw = 0;
   if (mode == MODE_X16) return launch_nt<MODE_X16>(nt, a, g, st);
   if (mode == MODE_X32) return launch_nt<MODE_X32>(nt, a, g, st);
   if (mode == MODE_NORM) return launch<MODE_NORM, 8>(a, g, st);

@@ -39,6 +39,17 @@ __device__ __forceinline__ bool mbar_try(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// try_wait with a suspend-time hint: the thread may sleep up to `ns` nanoseconds and is woken when the phase completes.
+// Waiting warps then stay out of the issue slots of the working warps on their scheduler.
+__device__ __forceinline__ bool mbar_try_hint(uint64_t* bar, uint32_t parity, uint32_t ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred P;\n\tmbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2, %3;\n\tselp.b32 %0, 1, 0, P;\n\t}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(ns)
+      : "memory");
+  return ok != 0;
+}
 // Bounded wait: about a second at most (each failed try_wait suspends for a hardware-chosen slice first).
 constexpr uint32_t WAIT_LIMIT = 1u << 22;
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {

@@ -18,7 +18,7 @@ import torch
 from . import qwen_batched as QB
 from . import qwen_kernels as K
 from .engine import FusedQwen
-from .synth import ModelConfig
+from .synth import ModelConfig, synth_q4
 
 
 def _pad_k(W: np.ndarray, S: np.ndarray, mult: int = 256):
@@ -71,6 +71,33 @@ def shard_model(model: dict, rank: int, tp: int) -> dict:
             "rank": rank, "tp": tp}
 
 
+def synth_shard(cfg: ModelConfig, rank: int, tp: int, seed: int = 0) -> dict:
+    """Random-init weights of ONE rank, drawn directly in the local shapes (1/tp of the work of drawing the whole model
+    and slicing it).  The global model these shards belong to is their concatenation: row slices for QKV and gate/up,
+    K slices for o_proj and down_proj; embedding, norms, biases of the local rows and the LM head come from
+    rank-independent streams, so every rank holds identical replicated parts."""
+    from .synth import synth_model
+    lc = shard_config(cfg, tp)
+    rep = synth_model(ModelConfig(cfg.name, 0, cfg.hidden, cfg.ffn, cfg.n_heads, cfg.n_kv_heads, cfg.head_dim, cfg.vocab,
+                                  cfg.eps, cfg.rope_theta, cfg.tied_fp16_head), seed)          # embed, norm, head only
+    layers = []
+    for i in range(cfg.layers):
+        shared = np.random.default_rng([seed, i, 1 << 16])
+        rng = np.random.default_rng([seed, i, rank])
+        ln1 = (1.0 + 0.1 * shared.standard_normal(cfg.hidden)).astype(np.float32)
+        ln2 = (1.0 + 0.1 * shared.standard_normal(cfg.hidden)).astype(np.float32)
+        layers.append({
+            "ln1": ln1, "ln2": ln2,
+            "qkv": synth_q4(rng, lc.qkv_rows, cfg.hidden),
+            "qkv_b": (0.1 * rng.standard_normal(lc.qkv_rows)).astype(np.float32),
+            "o": _pad_k(*synth_q4(rng, cfg.hidden, lc.q_rows)),
+            "gu": synth_q4(rng, 2 * lc.ffn, cfg.hidden),
+            "down": _pad_k(*synth_q4(rng, cfg.hidden, lc.ffn)),
+        })
+    return {"cfg": lc, "full_cfg": cfg, "embed": rep["embed"], "layers": layers, "norm": rep["norm"], "head": rep["head"],
+            "rank": rank, "tp": tp}
+
+
 class TPBatched:
     """B sequences, one decode token each per `step()`, on one rank of a tensor-parallel group.  Same op order as
     `engine.Batched`; the o_proj / down_proj partials are all-reduced (sum) before the residual add.  `group` is a
@@ -107,8 +134,13 @@ class TPBatched:
         self.allreduces_per_step = 2 * c.layers
 
     def _gemm8(self, pair, N, Kdim, Y, aux, epi, ldy):
+        """One linear over all B sequences; the tensor-core kernel takes up to 32 activation rows per launch."""
         Wt, St = self.m.packed[id(pair[0])]
-        QB.gemm8(Wt, St, self.xq, self.xd, Y, aux, N, Kdim, self.B, epi, ldy, self.status)
+        Yf = Y.view(-1)
+        for c0 in range(0, self.B, 32):
+            n = min(32, self.B - c0)
+            QB.gemm8(Wt, St, self.xq[c0 * Kdim:], self.xd[c0 * (Kdim // 32):], Yf[c0 * ldy:], aux, N, Kdim, n, epi, ldy,
+                     self.status)
 
     def _reduce_add(self):
         """h += sum over ranks of the partial [B, hidden]."""
@@ -150,3 +182,23 @@ class TPBatched:
             QB.rmsnorm_q8(self.h, m.norm, self.xq, self.xd, c.eps)
             self._gemm8(m.head, c.vocab, H, self.logits, None, "logits", c.vocab)
         K.finish(self.logits, self.tok, self.pos, self.head_ws)
+
+    def capture(self) -> torch.cuda.CUDAGraph:
+        """One `step()` (all-reduces included) as a CUDA graph; tok and pos are restored afterwards."""
+        torch.cuda.synchronize()
+        pos0, tok0 = self.pos.clone(), self.tok.clone()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            self.step()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        self.pos.copy_(pos0)
+        self.tok.copy_(tok0)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            self.step()
+        self.pos.copy_(pos0)
+        self.tok.copy_(tok0)
+        torch.cuda.synchronize()
+        return g

@@ -497,6 +497,104 @@ def run_other_workload(args, local_rank: int) -> None:
         "gpu_launches": bm.launches_per_step * gen, "clocks": clocks}), flush=True)
 
 
+def run_tp7b(args, rank: int, world: int, local_rank: int) -> None:
+    """Qwen2.5-7B shape, 64 sequences at a 2048-token context, tensor-parallel with NCCL all-reduce after o_proj and
+    down_proj.  The tensor-parallel degree is min(world, KV heads) = at most 4; further GPUs are data-parallel replicas
+    of the whole batch (8 GPUs = 2 replicas x TP4, each replica its own NCCL group)."""
+    import torch
+    import torch.distributed as dist
+    synth = importlib.import_module("3080lab_b200.synth")
+    tpm = importlib.import_module("3080lab_b200.tp")
+    cfg = synth.QWEN25_7B
+    torch.cuda.set_device(local_rank)
+    tp = min(world, cfg.n_kv_heads)
+    if world % tp:
+        raise SystemExit(f"tp7b: {world} GPUs is not a multiple of the tensor-parallel degree {tp}")
+    dp = world // tp
+    group = None
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local_rank}"))
+        for r in range(dp):                                  # every rank creates every group, in the same order
+            gr = dist.new_group(list(range(r * tp, (r + 1) * tp)))
+            if rank // tp == r:
+                group = gr
+        if tp == 1:
+            group = None
+    B, ctx, gen = 64, 2048, min(args.steps, 64)
+    if args.layers:
+        cfg = synth.ModelConfig(cfg.name, args.layers, cfg.hidden, cfg.ffn, cfg.n_heads, cfg.n_kv_heads, cfg.head_dim, cfg.vocab,
+                                cfg.eps, cfg.rope_theta, cfg.tied_fp16_head)
+    shard = tpm.synth_shard(cfg, rank % tp, tp, seed=0)
+    eng = tpm.TPBatched(shard, B, ctx + 128, f"cuda:{local_rank}", group)
+    eng.kc.normal_()
+    eng.vc.normal_()
+    eng.pos.fill_(ctx)
+    eng.tok.copy_(torch.from_numpy(synth.synth_prompt(cfg, B, 5 + rank // tp)).cuda())
+    sampler = ClockSampler(local_rank)
+    g = eng.capture()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        g.replay()
+    eng.pos.fill_(ctx)
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    sampler.start()
+    s.record()
+    for _ in range(gen):
+        g.replay()
+    e.record()
+    barrier()
+    ms = s.elapsed_time(e) / gen
+    clocks = sampler.stop()
+    eng.status.check("tensor-parallel decode")
+    host_in = torch.zeros(B, dtype=torch.long).pin_memory()
+    host_out = torch.zeros(B, dtype=torch.long).pin_memory()
+    host_in.copy_(eng.tok)
+    eng.pos.fill_(ctx)
+    barrier()
+    s.record()
+    for _ in range(gen):
+        eng.tok.copy_(host_in, non_blocking=True)
+        g.replay()
+        host_out.copy_(eng.tok, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        host_in.copy_(host_out)
+    e.record()
+    barrier()
+    e2e_ms = s.elapsed_time(e) / gen
+    if world > 1:
+        tms = torch.tensor([ms, e2e_ms], device="cuda")
+        dist.all_reduce(tms, op=dist.ReduceOp.MAX)
+        ms, e2e_ms = float(tms[0]), float(tms[1])
+    if rank == 0:
+        peaks, peak_kind = measured_peaks()
+        # bytes one GPU streams per step: its weight shard, the replicated head, its share of the KV cache
+        lc = shard["cfg"]
+        step_bytes = lc.q4_bytes_per_layer() * lc.layers + cfg.head_bytes() + B * lc.kv_bytes_per_position() * (ctx + gen / 2.0)
+        ach = step_bytes / (ms * 1e-3) / 1e9
+        print(json.dumps({
+            "metric": "decode_tok_per_s_7b_batch64", "value": dp * B / ms * 1e3, "unit": "tok/s", "n_gpus": world, "steps": gen,
+            "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "strong" if dp == 1 else "strong within a replica (tp), weak across replicas (dp)", "vs_baseline": None,
+            "dtype": "int8 x int4 -> int32, fp32 scaling", "data": "synthetic",
+            "config": {"workload": f"qwen2.5-7b-shape batched decode, 64 sequences per replica, 2048-token KV context, "
+                                   f"{cfg.layers} layers", "parallelism": f"tp{tp} x dp{dp}",
+                       "collective": f"NCCL all-reduce of [64, {cfg.hidden}] fp32 after o_proj and down_proj "
+                                     f"({2 * cfg.layers} per step)" if tp > 1 else "none",
+                       "l2": "weights + KV streamed per step are larger than L2"},
+            "roofline": {"bound": "hbm", "kernel": "whole step, per GPU", "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                         "frac": ach / peaks["hbm_gbs"], "peak_kind": f"of {peak_kind}", "traffic": None},
+            "e2e": {"value": dp * B / e2e_ms * 1e3, "unit": "tok/s", "h2d_bytes_per_step": 8 * B, "d2h_bytes_per_step": 8 * B},
+            "gpu_launches": gen * (4 + lc.layers * (7 + 4 * ((B + 31) // 32))), "clocks": clocks}), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -504,8 +602,9 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
-    ap.add_argument("--workload", default="decode_b1", choices=["decode_b1", "batched8", "batched32", "prefill2048"],
-                    help="decode_b1 is the benchmark; the others are the further single-GPU configurations")
+    ap.add_argument("--workload", default="decode_b1", choices=["decode_b1", "batched8", "batched32", "prefill2048", "tp7b"],
+                    help="decode_b1 is the benchmark; batched*/prefill2048 are the further single-GPU configurations; "
+                         "tp7b is the tensor-parallel 7B configuration (any --gpus, under torch.distributed.run)")
     ap.add_argument("--cuda-core", action="store_true", help="linears on the CUDA-core GEMV instead of the tensor-core kernel")
     ap.add_argument("--prompt", type=int, default=PROMPT, help="prompt length (512 = the benchmark configuration)")
     ap.add_argument("--layers", type=int, default=0, help="profile runs only: cut the model to this many layers")
@@ -517,6 +616,9 @@ def main() -> None:
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
         run_reference(args, rank)
+        return
+    if args.workload == "tp7b":
+        run_tp7b(args, rank, world, local_rank)
         return
     if args.workload != "decode_b1":
         if world > 1:

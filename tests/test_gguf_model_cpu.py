@@ -1,0 +1,76 @@
+"""GGUF model files: export -> load round trip of a synthetic Qwen2-architecture model (no GPU needed).
+
+Mirrors what the reference's GGUFQwen constructor does with a file (scripts/qwen_gguf.py:63-91): QKV concatenation,
+gate/up row interleave, canonical nibble packing."""
+import dataclasses
+import importlib
+
+import numpy as np
+import pytest
+
+from conftest import pkg
+
+
+def _same_cfg(a, b):
+    da, db = dataclasses.asdict(a), dataclasses.asdict(b)
+    for k in da:
+        if isinstance(da[k], float):
+            assert da[k] == pytest.approx(db[k], rel=1e-6), k      # GGUF stores eps and theta as float32
+        elif k != "name":
+            assert da[k] == db[k], k
+
+
+@pytest.mark.parametrize("tied", [True, False])
+def test_export_load_round_trip(tmp_path, tied):
+    synth, qg = pkg("synth"), pkg("qwen_gguf")
+    cfg = synth.ModelConfig("tiny-rt", 2, 256, 512, 4, 2, 64, 1024, tied_fp16_head=tied)
+    model = synth.synth_model(cfg, 11)
+    path = tmp_path / "model.gguf"
+    qg.export_model(model, path)
+    back = qg.load_model(path)
+    _same_cfg(cfg, back["cfg"])
+    assert np.array_equal(model["embed"], back["embed"]) and np.array_equal(model["norm"], back["norm"])
+    for a, b in zip(model["layers"], back["layers"]):
+        for k in ("ln1", "ln2", "qkv_b"):
+            assert np.array_equal(a[k], b[k]), k
+        for k in ("qkv", "o", "gu", "down"):
+            assert np.array_equal(a[k][0], b[k][0]) and np.array_equal(a[k][1], b[k][1]), k
+    if tied:
+        assert back["head"] is None
+    else:
+        assert np.array_equal(model["head"][0], back["head"][0]) and np.array_equal(model["head"][1], back["head"][1])
+
+
+def test_file_uses_llama_cpp_names_and_row_order(tmp_path):
+    synth, qg, G = pkg("synth"), pkg("qwen_gguf"), pkg("gguf")
+    cfg = synth.TINY
+    model = synth.synth_model(cfg, 2)
+    path = tmp_path / "model.gguf"
+    qg.export_model(model, path)
+    g = G.GGUF(path)
+    assert g.meta["general.architecture"] == "qwen2" and g.meta["qwen2.block_count"] == cfg.layers
+    for name in ("token_embd.weight", "output_norm.weight", "blk.0.attn_q.weight", "blk.0.attn_k.bias", "blk.1.ffn_gate.weight",
+                 "blk.1.ffn_up.weight", "blk.1.ffn_down.weight", "blk.0.attn_output.weight", "blk.0.attn_norm.weight"):
+        assert name in g.tensors, name
+    assert g.tensors["blk.0.attn_q.weight"].dims == (cfg.hidden, cfg.q_rows)        # ggml order: K first
+    assert g.tensors["blk.0.ffn_down.weight"].dims == (cfg.ffn, cfg.hidden)
+    # gate rows are the even rows of the interleaved gate/up matrix, k rows follow the q rows of QKV
+    q_gate, d_gate = G.q4_rows(g, "blk.0.ffn_gate.weight")
+    W, S = model["layers"][0]["gu"]
+    assert np.array_equal(G.pack_nibbles(q_gate), W[0::2]) and np.array_equal(d_gate, S[0::2])
+    q_k, _ = G.q4_rows(g, "blk.0.attn_k.weight")
+    assert np.array_equal(G.pack_nibbles(q_k), model["layers"][0]["qkv"][0][cfg.q_rows:cfg.q_rows + cfg.kv_rows])
+
+
+def test_q6_k_head_is_refused_by_name(tmp_path):
+    synth, qg, G = pkg("synth"), pkg("qwen_gguf"), pkg("gguf")
+    cfg = synth.TINY
+    model = synth.synth_model(cfg, 2)
+    path = tmp_path / "model.gguf"
+    qg.export_model(model, path)
+    g = G.GGUF(path)
+    tensors = {n: (t.type, t.dims, bytes(g.raw(n)[0])) for n, t in g.tensors.items()}
+    tensors["output.weight"] = (14, (cfg.hidden, cfg.vocab), bytes(cfg.vocab * cfg.hidden // 256 * 210))   # Q6_K record size
+    G.write_gguf(tmp_path / "q6.gguf", dict(g.meta), tensors)
+    with pytest.raises(NotImplementedError, match="Q6_K|ggml type 14"):
+        qg.load_model(tmp_path / "q6.gguf")

@@ -166,6 +166,28 @@ def test_mmq_stream_q8_matches_oracle(QB, P, n, k):
     assert nerr(y.cpu().numpy(), ref) < 2e-6
 
 
+@pytest.mark.parametrize("epi", ["logits", "resid"])
+def test_mmq_stream_q8_long_k_runs_in_windows(QB, epi):
+    """K = 18944 with 32 activation rows does not fit one CTA's shared memory at any split: the entry point covers K in
+    windows that accumulate into the fp32 output (the 7B down projection on one GPU)."""
+    o = oracle()
+    rng = np.random.default_rng(77)
+    P, n, k = 32, 256, 18944
+    W, S = rand_q4(rng, n, k)
+    x = rng.standard_normal((P, k)).astype(np.float16)
+    xq, xd, _ = o.quant_q8_1(x)
+    ref = o.mmq(W, S, xq, xd)
+    st = QB.Status("cuda")
+    y0 = rng.standard_normal((P, n)).astype(np.float32)
+    y = dev(y0.copy())
+    QB.gemm8(*QB.pack_q4(dev(W), dev(S)), dev(xq), dev(xd), y, None, n, k, P, epi, n, st)
+    st.check()
+    assert nerr(y.cpu().numpy(), ref + (y0 if epi == "resid" else 0.0)) < 5e-6
+    with pytest.raises(Exception):           # an epilogue that is not linear in K cannot be windowed
+        QB.gemm8(*QB.pack_q4(dev(W), dev(S)), dev(xq), dev(xd), torch.empty(P, n // 2, dtype=torch.float16, device="cuda"),
+                 None, n, k, P, "swiglu", n // 2, st)
+
+
 def test_mmq_stream_q8_epilogues(QB):
     o = oracle()
     rng = np.random.default_rng(5)

@@ -84,3 +84,23 @@ def test_shard_config_rejects_uneven_splits():
         tp.shard_config(s.QWEN25_7B, 8)          # 28 query heads / 4 KV heads do not divide by 8
     c = tp.shard_config(s.QWEN25_7B, 4)
     assert (c.n_heads, c.n_kv_heads, c.ffn) == (7, 1, 4736)
+
+
+def test_synth_shard_replicated_parts_and_shapes():
+    """Shards drawn directly in the local shapes: replicated tensors identical on every rank, K slices padded to 256."""
+    synth, tp = pkg("synth"), pkg("tp")
+    cfg = synth.ModelConfig("tp-shape", 2, 512, 1536, 8, 4, 64, 2048, tied_fp16_head=False)
+    shards = [tp.synth_shard(cfg, r, 4, seed=3) for r in range(4)]
+    lc = shards[0]["cfg"]
+    assert (lc.n_heads, lc.n_kv_heads, lc.ffn) == (2, 1, 384)
+    for s in shards[1:]:
+        assert np.array_equal(s["embed"], shards[0]["embed"]) and np.array_equal(s["norm"], shards[0]["norm"])
+        assert np.array_equal(s["head"][0], shards[0]["head"][0])
+        for a, b in zip(s["layers"], shards[0]["layers"]):
+            assert np.array_equal(a["ln1"], b["ln1"]) and np.array_equal(a["ln2"], b["ln2"])
+            assert not np.array_equal(a["qkv"][0], b["qkv"][0])
+    L = shards[2]["layers"][1]
+    assert L["qkv"][0].shape == (lc.qkv_rows, cfg.hidden // 8) and L["gu"][0].shape == (2 * lc.ffn, cfg.hidden // 8)
+    assert L["o"][0].shape == (cfg.hidden, 256 // 8)             # 128 local q columns padded to one 256-wide group
+    assert L["down"][0].shape == (cfg.hidden, 512 // 8)          # 384 -> 512
+    assert np.all(L["o"][1][:, 128 // 32:] == 0)                 # padding blocks carry a zero scale
