@@ -531,7 +531,18 @@ def run_tp7b(args, rank: int, world: int, local_rank: int) -> None:
     eng.pos.fill_(ctx)
     eng.tok.copy_(torch.from_numpy(synth.synth_prompt(cfg, B, 5 + rank // tp)).cuda())
     sampler = ClockSampler(local_rank)
-    g = eng.capture()
+    # One GPU: the step is replayed as a CUDA graph.  With tensor parallelism the step is launched op by op: a graph
+    # holding NCCL all-reduces did not complete on this pool (the 2-GPU run was killed at its time limit), and the host
+    # launch cost (~0.4 k launches per step) stays below the device time of a 7B step.
+    if tp == 1:
+        graph = eng.capture()
+        run_step = graph.replay
+    else:
+        run_step = eng.step
+
+    class _G:
+        replay = staticmethod(run_step)
+    g = _G
 
     def barrier():
         if world > 1:
