@@ -119,8 +119,8 @@ __global__ void __launch_bounds__(ROWS) mmq_stream_kernel(const StreamArgs a) {
   }
   if (t == 0) {
     for (int b = 0; b < nbatch; ++b) tc::mbar_init(&bar_load[b], 1);
-    tc::mbar_init(&bar_mma[0], 1);
-    tc::mbar_init(&bar_mma[1], 1);
+    tc::mbar_init(&bar_mma[0], 4);                       // one commit per issuing warp
+    tc::mbar_init(&bar_mma[1], 4);
     tc::mbar_fence_init();
   }
   stamp();                                              // TMEM allocated, barriers initialised
@@ -324,28 +324,37 @@ __global__ void __launch_bounds__(ROWS) mmq_stream_kernel(const StreamArgs a) {
   for (int bi = 0; bi < nbatch; ++bi) {
     const int slot = bi & 1;
     ok = tc::mbar_wait(&bar_load[bi], 0) && ok;         // this batch's weights landed (async-proxy writes now visible)
-#pragma unroll 2
+    // all nibble words of the batch are read before the first tensor-memory store (the stores are ordered asm
+    // statements; interleaved with the loads they would expose one shared-memory latency per k-block)
+    uint4 wv[G];
+#pragma unroll
+    for (int j = 0; j < G; ++j) wv[j] = *reinterpret_cast<const uint4*>(myW + (size_t)(bi * G + j) * 2048);
+#pragma unroll
     for (int j = 0; j < G; ++j) {
-      const uint4 w = *reinterpret_cast<const uint4*>(myW + (size_t)(bi * G + j) * 2048);
       uint32_t ex[8];
-      tc::expand_nibbles(w.x, ex[0], ex[1]);
-      tc::expand_nibbles(w.y, ex[2], ex[3]);
-      tc::expand_nibbles(w.z, ex[4], ex[5]);
-      tc::expand_nibbles(w.w, ex[6], ex[7]);
+      tc::expand_nibbles(wv[j].x, ex[0], ex[1]);
+      tc::expand_nibbles(wv[j].y, ex[2], ex[3]);
+      tc::expand_nibbles(wv[j].z, ex[4], ex[5]);
+      tc::expand_nibbles(wv[j].w, ex[6], ex[7]);
       tc::tmem_st8(tmem_a + lane_off + (uint32_t)((slot * G + j) * 8), ex);
     }
     tc::tmem_wait_st();
     tc::fence_before_sync();
     __syncthreads();
-    if (t == 0) {
+    // MMA issue is spread over the four warps (one lane each, G / 4 MMAs): a single thread needs ~90 clocks per
+    // tcgen05.mma, which at 8 per batch was 0.4 us on the critical path.  Every issuer commits to the batch's barrier.
+    if (lane == 0) {
       tc::fence_after_sync();
       const uint32_t b0 = tc::smem_u32(sB);
-      for (int j = 0; j < G; ++j) {
+#pragma unroll
+      for (int jj = 0; jj < G / 4; ++jj) {
+        const int j = warp * (G / 4) + jj;
         const uint64_t bdesc = tc::smem_desc_kmajor(b0 + (uint32_t)(bi * G + j) * (NT * 32), 128, 256);
         tc::mma_i8_ts(tmem_d + (uint32_t)((slot * G + j) * NT), tmem_a + (uint32_t)((slot * G + j) * 8), bdesc, IDESC, 0u);
       }
       tc::mma_commit(&bar_mma[slot]);
     }
+    __syncwarp();
     stamp();                                            // 5, 6, ...: batch expanded and issued
     if (bi > 0) fold(bi - 1);
   }
