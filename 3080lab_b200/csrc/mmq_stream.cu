@@ -142,6 +142,24 @@ __global__ void __launch_bounds__(ROWS) mmq_stream_kernel(const StreamArgs a) {
   pdl_wait();                                           // the activations come from the previous kernel
   stamp();                                              // 2: predecessor complete
 
+  // What the epilogue adds to this thread's outputs (residual rows, bias) is requested now, so that its latency hides
+  // behind the whole main loop instead of costing one round trip per column at the end.  addend[i] belongs to the
+  // i-th column this CTA writes: column i for the leader of a pushed reduction, column ks + i ksplit in a reduce-scatter.
+  constexpr int NOWN = PUSH ? NACC : (NACC + 1) / 2;
+  float addend[NOWN];
+  auto load_addends = [&]() {
+    const bool writer = PUSH ? ks == 0 : true;
+    const int cstep = PUSH ? 1 : a.ksplit, cfirst = PUSH ? 0 : (a.ksplit > 1 ? ks : 0);
+    const float bias = (a.epi == Q4B_EPI_BIASF && row < a.N) ? reinterpret_cast<const float*>(a.AUX)[row] : 0.f;
+#pragma unroll
+    for (int i = 0; i < NOWN; ++i) {
+      const int n = cfirst + i * cstep;
+      addend[i] = bias;
+      if (a.epi == Q4B_EPI_RESID && writer && n < a.cols && row < a.N) addend[i] = reinterpret_cast<const float*>(a.Y)[(size_t)n * a.ldy + row];
+    }
+  };
+  if (PUSH) load_addends();                             // few columns: now; many columns: next to the reduce-scatter loads
+
   // ---- activations -> UMMA B operand in shared memory
   if (MODE == MODE_Q8) {
     const int8_t* xq = reinterpret_cast<const int8_t*>(a.X);
@@ -167,9 +185,19 @@ __global__ void __launch_bounds__(ROWS) mmq_stream_kernel(const StreamArgs a) {
         }
       }
     }
-    for (int c = t; c < NT * nkb; c += ROWS) {
-      const int n = c / nkb, kbl = c - n * nkb;
-      xs[kbl * NT + n] = n < a.cols ? __half2float(a.XD[(size_t)n * a.KBT + a.kbw + kb0 + kbl]) : 0.f;
+    for (int c0 = 0; c0 < NT * nkb; c0 += 4 * ROWS) {
+      __half sv[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int c = c0 + u * ROWS + t, n = c / nkb, kbl = c - n * nkb;
+        sv[u] = __float2half_rn(0.f);
+        if (c < NT * nkb && n < a.cols) sv[u] = a.XD[(size_t)n * a.KBT + a.kbw + kb0 + kbl];
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int c = c0 + u * ROWS + t, n = c / nkb, kbl = c - n * nkb;
+        if (c < NT * nkb) xs[kbl * NT + n] = __half2float(sv[u]);
+      }
     }
   } else {
     // exact mode: 8 lanes <-> one k-block, 4 consecutive elements per lane.  X_i = rint(x_i * 2^-e) with
@@ -363,16 +391,16 @@ __global__ void __launch_bounds__(ROWS) mmq_stream_kernel(const StreamArgs a) {
   stamp();                                              // all batches folded
 
   // one output value: column (sequence) n of this thread's row
-  auto emit = [&](int n, float v) {
+  auto emit = [&](int n, float v, float add) {
     const float partner = __shfl_xor_sync(0xffffffffu, v, 1);
     if (n < a.cols && row < a.N) {
       const size_t base = (size_t)n * a.ldy;
       switch (a.epi) {
         case Q4B_EPI_STORE: reinterpret_cast<__half*>(a.Y)[base + row] = __float2half_rn(v); break;
         case Q4B_EPI_BIASF:
-          reinterpret_cast<__half*>(a.Y)[base + row] = __float2half_rn(v + reinterpret_cast<const float*>(a.AUX)[row]);
+          reinterpret_cast<__half*>(a.Y)[base + row] = __float2half_rn(v + add);
           break;
-        case Q4B_EPI_RESID: reinterpret_cast<float*>(a.Y)[base + row] += v; break;
+        case Q4B_EPI_RESID: reinterpret_cast<float*>(a.Y)[base + row] = add + v; break;
         case Q4B_EPI_LOGITS: reinterpret_cast<float*>(a.Y)[base + row] = v; break;
         case Q4B_EPI_SWIGLU:
           if ((t & 1) == 0) reinterpret_cast<__half*>(a.Y)[base + (row >> 1)] = __float2half_rn(v / (1.f + __expf(-v)) * partner);
@@ -393,6 +421,7 @@ __global__ void __launch_bounds__(ROWS) mmq_stream_kernel(const StreamArgs a) {
 #pragma unroll
     for (int n = 0; n < NACC; ++n) part[n * ROWS + t] = acc[n];
     cluster_sync_all();
+    load_addends();                                     // in flight together with the remote loads below
     // all remote loads of this thread are issued before the first add: own column i (= ks + i ksplit), rank r -> pv[i ksplit + r]
     constexpr int NPV = NACC + 8;
     float pv[NPV];
@@ -414,7 +443,11 @@ __global__ void __launch_bounds__(ROWS) mmq_stream_kernel(const StreamArgs a) {
         }
       }
     }
-    for (int n = ks, i = 0; n < NACC; n += a.ksplit, ++i) emit(n, fin[i * ROWS + t]);
+#pragma unroll
+    for (int i = 0; i < NOWN; ++i) {
+      const int n = ks + i * a.ksplit;
+      if (n < NACC) emit(n, fin[i * ROWS + t], addend[i]);
+    }
     cluster_sync_all();                                 // peers stay resident until everyone has read them
     stamp();                                            // split-K reduced
   } else {
@@ -439,7 +472,17 @@ __global__ void __launch_bounds__(ROWS) mmq_stream_kernel(const StreamArgs a) {
     stamp();                                            // split-K reduced
     if (ks == 0) {
 #pragma unroll
-      for (int n = 0; n < NACC; ++n) emit(n, acc[n]);
+      for (int n = 0; n < NACC; ++n) {
+        float add = PUSH ? addend[n < NOWN ? n : 0] : 0.f;
+        if (!PUSH) {                                     // unsplit launch with many columns: fetched here
+          add = 0.f;
+          if (row < a.N && n < a.cols) {
+            if (a.epi == Q4B_EPI_BIASF) add = reinterpret_cast<const float*>(a.AUX)[row];
+            if (a.epi == Q4B_EPI_RESID) add = reinterpret_cast<const float*>(a.Y)[(size_t)n * a.ldy + row];
+          }
+        }
+        emit(n, acc[n], add);
+      }
     }
   }
   if (!ok && t == 0) atomicExch(a.status, 1u);
