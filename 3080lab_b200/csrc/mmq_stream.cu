@@ -75,11 +75,17 @@ __device__ __forceinline__ uint32_t b_offset(int kbl, int n, int pos) {
 }
 
 template <int MODE, int NT>
-__global__ void __launch_bounds__(ROWS) mmq_stream_kernel(const StreamArgs a) {
+__global__ void __launch_bounds__(ROWS * ((MODE == MODE_Q8 && NT >= 16) ? 2 : 1)) mmq_stream_kernel(const StreamArgs a) {
   constexpr int G = NT <= 16 ? 8 : 4;                  // k-blocks per MMA batch
   constexpr int NL = (MODE == MODE_X16 || MODE == MODE_NORM) ? 3 : 4;   // digits in exact mode (fp16-valued x: 3)
-  constexpr int NACC = MODE == MODE_Q8 ? NT : 1;
-  constexpr bool PUSH = NACC <= 8;                     // split-K partials pushed to the leader (else pulled)
+  // With 16 or 32 activation rows the read-back of the accumulators (columns x k-blocks conversions and FMAs per
+  // thread) is the longest stage, so a second warpgroup takes half of the columns.  Warpgroup 0 expands the weights,
+  // issues the MMAs and folds columns [0, NT/2); warpgroup 1 only folds columns [NT/2, NT).
+  constexpr int FW = (MODE == MODE_Q8 && NT >= 16) ? 2 : 1;
+  constexpr int NTHR = ROWS * FW;
+  constexpr int NTOT = MODE == MODE_Q8 ? NT : 1;       // accumulator columns of the tile
+  constexpr int NACC = NTOT / FW;                      // ... of one thread
+  constexpr bool PUSH = NTOT <= 8;                     // split-K partials pushed to the leader (else a reduce-scatter)
   constexpr uint32_t A_COLS = 2 * G * 8, D_COLS = 2 * G * NT;
   constexpr uint32_t TCOLS = (A_COLS + D_COLS) <= 128 ? 128 : ((A_COLS + D_COLS) <= 256 ? 256 : 512);
   constexpr uint32_t IDESC = tc::idesc_i8(128, NT);
@@ -87,10 +93,13 @@ __global__ void __launch_bounds__(ROWS) mmq_stream_kernel(const StreamArgs a) {
   extern __shared__ __align__(128) uint8_t smem[];
   __shared__ __align__(8) uint64_t bar_load[MAX_BATCH];
   __shared__ __align__(8) uint64_t bar_mma[2];
+  __shared__ __align__(8) uint64_t bar_free[2];          // warpgroup 1 has read an accumulator slot
   __shared__ uint32_t tmem_base_s;
 
   const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
-  const int row0 = blockIdx.x * ROWS, row = row0 + t;
+  const int wg = t >> 7, r = t & (ROWS - 1), wq = warp & 3;   // warpgroup, row of the tile, TMEM lane quarter
+  const int cbase = wg * NACC;                           // first accumulator column of this thread
+  const int row0 = blockIdx.x * ROWS, row = row0 + r;
   const int ks = blockIdx.y;
   unsigned long long* tr = (a.trace && t == 0) ? a.trace + (size_t)(blockIdx.y * gridDim.x + blockIdx.x) * 16 : nullptr;
   int tri = 0;
@@ -103,7 +112,7 @@ __global__ void __launch_bounds__(ROWS) mmq_stream_kernel(const StreamArgs a) {
   };
   stamp();                                              // 0: start
   pdl_launch_dependents();                              // let the next kernel's CTAs begin their own prologue now
-  const int KB = a.K >> 5, GT = a.K >> 8;
+  const int GT = a.K >> 8;
   const int g0 = ks * a.gps, ng = min(a.gps, GT - g0);          // host guarantees ng >= 1
   const int nkb = ng * 8, kb0 = g0 * 8;
   uint8_t* slabW = smem;                                         // [k-block][128 rows][16 bytes]
@@ -121,6 +130,8 @@ __global__ void __launch_bounds__(ROWS) mmq_stream_kernel(const StreamArgs a) {
     for (int b = 0; b < nbatch; ++b) tc::mbar_init(&bar_load[b], 1);
     tc::mbar_init(&bar_mma[0], 4);                       // one commit per issuing warp
     tc::mbar_init(&bar_mma[1], 4);
+    tc::mbar_init(&bar_free[0], 4);
+    tc::mbar_init(&bar_free[1], 4);
     tc::mbar_fence_init();
   }
   stamp();                                              // TMEM allocated, barriers initialised
@@ -145,15 +156,14 @@ __global__ void __launch_bounds__(ROWS) mmq_stream_kernel(const StreamArgs a) {
   // What the epilogue adds to this thread's outputs (residual rows, bias) is requested now, so that its latency hides
   // behind the whole main loop instead of costing one round trip per column at the end.  addend[i] belongs to the
   // i-th column this CTA writes: column i for the leader of a pushed reduction, column ks + i ksplit in a reduce-scatter.
-  constexpr int NOWN = PUSH ? NACC : (NACC + 1) / 2;
+  constexpr int NOWN = PUSH ? NACC : (NTOT / 2 + FW - 1) / FW;   // reduce-scatter: this thread's share of the CTA's columns
   float addend[NOWN];
   auto load_addends = [&]() {
     const bool writer = PUSH ? ks == 0 : true;
-    const int cstep = PUSH ? 1 : a.ksplit, cfirst = PUSH ? 0 : (a.ksplit > 1 ? ks : 0);
     const float bias = (a.epi == Q4B_EPI_BIASF && row < a.N) ? reinterpret_cast<const float*>(a.AUX)[row] : 0.f;
 #pragma unroll
     for (int i = 0; i < NOWN; ++i) {
-      const int n = cfirst + i * cstep;
+      const int n = PUSH ? i : ks + (wg + FW * i) * a.ksplit;
       addend[i] = bias;
       if (a.epi == Q4B_EPI_RESID && writer && n < a.cols && row < a.N) addend[i] = reinterpret_cast<const float*>(a.Y)[(size_t)n * a.ldy + row];
     }
@@ -164,18 +174,18 @@ __global__ void __launch_bounds__(ROWS) mmq_stream_kernel(const StreamArgs a) {
   if (MODE == MODE_Q8) {
     const int8_t* xq = reinterpret_cast<const int8_t*>(a.X);
     const int per = nkb * 2;
-    for (int c0 = 0; c0 < NT * per; c0 += 4 * ROWS) {
+    for (int c0 = 0; c0 < NT * per; c0 += 4 * NTHR) {
       uint4 v[4];
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
-        const int c = c0 + u * ROWS + t;
+        const int c = c0 + u * NTHR + t;
         const int n = c / per, r = c - n * per, kbl = r >> 1, kc = r & 1;
         v[u] = make_uint4(0u, 0u, 0u, 0u);
         if (c < NT * per && n < a.cols) v[u] = *reinterpret_cast<const uint4*>(xq + ((size_t)n * a.KBT + a.kbw + kb0 + kbl) * 32 + kc * 16);
       }
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
-        const int c = c0 + u * ROWS + t;
+        const int c = c0 + u * NTHR + t;
         if (c < NT * per) {
           const int n = c / per, r = c - n * per, kbl = r >> 1, kc = r & 1;
           uint32_t e0, o0, e1, o1;
@@ -185,17 +195,17 @@ __global__ void __launch_bounds__(ROWS) mmq_stream_kernel(const StreamArgs a) {
         }
       }
     }
-    for (int c0 = 0; c0 < NT * nkb; c0 += 4 * ROWS) {
+    for (int c0 = 0; c0 < NT * nkb; c0 += 4 * NTHR) {
       __half sv[4];
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
-        const int c = c0 + u * ROWS + t, n = c / nkb, kbl = c - n * nkb;
+        const int c = c0 + u * NTHR + t, n = c / nkb, kbl = c - n * nkb;
         sv[u] = __float2half_rn(0.f);
         if (c < NT * nkb && n < a.cols) sv[u] = a.XD[(size_t)n * a.KBT + a.kbw + kb0 + kbl];
       }
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
-        const int c = c0 + u * ROWS + t, n = c / nkb, kbl = c - n * nkb;
+        const int c = c0 + u * NTHR + t, n = c / nkb, kbl = c - n * nkb;
         if (c < NT * nkb) xs[kbl * NT + n] = __half2float(sv[u]);
       }
     }
@@ -292,42 +302,49 @@ __global__ void __launch_bounds__(ROWS) mmq_stream_kernel(const StreamArgs a) {
   bool ok = true;                // slab landed (async-proxy writes made visible by the barrier)
 
   const uint32_t tmem = tmem_base_s;
-  const uint32_t lane_off = (uint32_t)(32 * warp) << 16;
+  const uint32_t lane_off = (uint32_t)(32 * wq) << 16;
   const uint32_t tmem_a = tmem, tmem_d = tmem + A_COLS;
   float acc[NACC];
 #pragma unroll
   for (int n = 0; n < NACC; ++n) acc[n] = 0.f;
 
-  const uint8_t* myW = slabW + t * 16;
-  const __half* myS = reinterpret_cast<const __half*>(slabS) + t;
+  const uint8_t* myW = slabW + r * 16;
+  const __half* myS = reinterpret_cast<const __half*>(slabS) + r;
 
   auto fold = [&](int bi) {                             // accumulators of batch bi -> acc
     const int slot = bi & 1;
     ok = tc::mbar_wait(&bar_mma[slot], (uint32_t)(bi >> 1) & 1u) && ok;
     tc::fence_after_sync();
     if (MODE == MODE_Q8) {
-      constexpr int SB = NT <= 8 ? 8 : (NT == 16 ? 4 : 2);       // k-blocks whose accumulators are in flight together
+      constexpr int SB = NACC <= 8 ? 8 : 4;                      // k-blocks whose accumulators are in flight together
+      static_assert(G % (SB < G ? SB : G) == 0, "batch size");
+      constexpr int SBE = SB < G ? SB : G;
 #pragma unroll 1
-      for (int j0 = 0; j0 < G; j0 += SB) {
-        uint32_t d[SB][NT];
+      for (int j0 = 0; j0 < G; j0 += SBE) {
+        uint32_t d[SBE][NACC];
 #pragma unroll
-        for (int j = 0; j < SB; ++j) {
-          const uint32_t dcol = tmem_d + lane_off + (uint32_t)((slot * G + j0 + j) * NT);
+        for (int j = 0; j < SBE; ++j) {
+          const uint32_t dcol = tmem_d + lane_off + (uint32_t)((slot * G + j0 + j) * NT + cbase);
 #pragma unroll
-          for (int c0 = 0; c0 < NT; c0 += 8) tc::tmem_ld8(dcol + c0, &d[j][c0]);
+          for (int c0 = 0; c0 < NACC; c0 += 8) tc::tmem_ld8(dcol + c0, &d[j][c0]);
         }
         tc::tmem_wait_ld();
+        if (FW == 2 && wg == 1 && j0 + SBE >= G) {               // slot read: warpgroup 0 may overwrite it
+          tc::fence_before_sync();
+          __syncwarp();
+          if (lane == 0) tc::mbar_arrive(&bar_free[slot]);
+        }
 #pragma unroll
-        for (int j = 0; j < SB; ++j) {
+        for (int j = 0; j < SBE; ++j) {
           const int kbl = bi * G + j0 + j;
           const float dw = __half2float(myS[kbl * 128]) * 0.0625f;   // 1/16 undoes the 16*(q-8) operand scaling
 #pragma unroll
-          for (int c0 = 0; c0 < NT; c0 += 4) {
-            const float4 sx = *reinterpret_cast<const float4*>(xs + kbl * NT + c0);
-            acc[(c0 + 0) % NACC] = fmaf(dw * sx.x, (float)(int32_t)d[j][c0 + 0], acc[(c0 + 0) % NACC]);
-            acc[(c0 + 1) % NACC] = fmaf(dw * sx.y, (float)(int32_t)d[j][c0 + 1], acc[(c0 + 1) % NACC]);
-            acc[(c0 + 2) % NACC] = fmaf(dw * sx.z, (float)(int32_t)d[j][c0 + 2], acc[(c0 + 2) % NACC]);
-            acc[(c0 + 3) % NACC] = fmaf(dw * sx.w, (float)(int32_t)d[j][c0 + 3], acc[(c0 + 3) % NACC]);
+          for (int c0 = 0; c0 < NACC; c0 += 4) {
+            const float4 sx = *reinterpret_cast<const float4*>(xs + kbl * NT + cbase + c0);
+            acc[c0 + 0] = fmaf(dw * sx.x, (float)(int32_t)d[j][c0 + 0], acc[c0 + 0]);
+            acc[c0 + 1] = fmaf(dw * sx.y, (float)(int32_t)d[j][c0 + 1], acc[c0 + 1]);
+            acc[c0 + 2] = fmaf(dw * sx.z, (float)(int32_t)d[j][c0 + 2], acc[c0 + 2]);
+            acc[c0 + 3] = fmaf(dw * sx.w, (float)(int32_t)d[j][c0 + 3], acc[c0 + 3]);
           }
         }
       }
@@ -352,6 +369,10 @@ __global__ void __launch_bounds__(ROWS) mmq_stream_kernel(const StreamArgs a) {
   for (int bi = 0; bi < nbatch; ++bi) {
     const int slot = bi & 1;
     ok = tc::mbar_wait(&bar_load[bi], 0) && ok;         // this batch's weights landed (async-proxy writes now visible)
+    if (FW == 2 && wg == 1) {                           // fold-only warpgroup: needs the batch's scales, then its accumulators
+      fold(bi);
+      continue;
+    }
     // all nibble words of the batch are read before the first tensor-memory store (the stores are ordered asm
     // statements; interleaved with the loads they would expose one shared-memory latency per k-block)
     uint4 wv[G];
@@ -368,7 +389,10 @@ __global__ void __launch_bounds__(ROWS) mmq_stream_kernel(const StreamArgs a) {
     }
     tc::tmem_wait_st();
     tc::fence_before_sync();
-    __syncthreads();
+    if (FW == 1) __syncthreads();
+    else asm volatile("bar.sync 1, 128;" ::: "memory");  // warpgroup 0 only
+    // the accumulator slot is overwritten: warpgroup 1 must have read batch bi - 2 out of it (this warpgroup has)
+    if (FW == 2 && bi >= 2) ok = tc::mbar_wait(&bar_free[slot], (uint32_t)((bi >> 1) - 1) & 1u) && ok;
     // MMA issue is spread over the four warps (one lane each, G / 4 MMAs): a single thread needs ~90 clocks per
     // tcgen05.mma, which at 8 per batch was 0.4 us on the critical path.  Every issuer commits to the batch's barrier.
     if (lane == 0) {
@@ -376,7 +400,7 @@ __global__ void __launch_bounds__(ROWS) mmq_stream_kernel(const StreamArgs a) {
       const uint32_t b0 = tc::smem_u32(sB);
 #pragma unroll
       for (int jj = 0; jj < G / 4; ++jj) {
-        const int j = warp * (G / 4) + jj;
+        const int j = wq * (G / 4) + jj;
         const uint64_t bdesc = tc::smem_desc_kmajor(b0 + (uint32_t)(bi * G + j) * (NT * 32), 128, 256);
         tc::mma_i8_ts(tmem_d + (uint32_t)((slot * G + j) * NT), tmem_a + (uint32_t)((slot * G + j) * 8), bdesc, IDESC, 0u);
       }
@@ -386,7 +410,7 @@ __global__ void __launch_bounds__(ROWS) mmq_stream_kernel(const StreamArgs a) {
     stamp();                                            // 5, 6, ...: batch expanded and issued
     if (bi > 0) fold(bi - 1);
   }
-  if (nbatch > 0) fold(nbatch - 1);
+  if (nbatch > 0 && wg == 0) fold(nbatch - 1);
   __syncthreads();                                      // every thread is done with the slabs and with TMEM
   stamp();                                              // all batches folded
 
@@ -403,7 +427,7 @@ __global__ void __launch_bounds__(ROWS) mmq_stream_kernel(const StreamArgs a) {
         case Q4B_EPI_RESID: reinterpret_cast<float*>(a.Y)[base + row] = add + v; break;
         case Q4B_EPI_LOGITS: reinterpret_cast<float*>(a.Y)[base + row] = v; break;
         case Q4B_EPI_SWIGLU:
-          if ((t & 1) == 0) reinterpret_cast<__half*>(a.Y)[base + (row >> 1)] = __float2half_rn(v / (1.f + __expf(-v)) * partner);
+          if ((r & 1) == 0) reinterpret_cast<__half*>(a.Y)[base + (row >> 1)] = __float2half_rn(v / (1.f + __expf(-v)) * partner);
           break;
         default: break;
       }
@@ -417,36 +441,37 @@ __global__ void __launch_bounds__(ROWS) mmq_stream_kernel(const StreamArgs a) {
   // the result does not depend on which CTA does it) and writes those columns itself.  Per thread that is NACC remote
   // loads spread over the cluster instead of (ksplit - 1) NACC on the leader.
   if (a.ksplit > 1 && !PUSH) {
-    float* part = reinterpret_cast<float*>(slabW);      // [NACC][128], every thread is past its last slab read
+    float* part = reinterpret_cast<float*>(slabW);      // [NTOT][128], every thread is past its last slab read
 #pragma unroll
-    for (int n = 0; n < NACC; ++n) part[n * ROWS + t] = acc[n];
+    for (int n = 0; n < NACC; ++n) part[(cbase + n) * ROWS + r] = acc[n];
     cluster_sync_all();
     load_addends();                                     // in flight together with the remote loads below
-    // all remote loads of this thread are issued before the first add: own column i (= ks + i ksplit), rank r -> pv[i ksplit + r]
-    constexpr int NPV = NACC + 8;
+    // This CTA sums columns ks, ks + ksplit, ...; its warpgroups take them alternately.  All remote loads of a thread
+    // are issued before the first add: own column ii (= ks + (wg + FW ii) ksplit), rank rr -> pv[ii ksplit + rr].
+    constexpr int NPV = NTOT / FW + 8;
     float pv[NPV];
 #pragma unroll
     for (int q = 0; q < NPV; ++q) {
-      const int i = q / a.ksplit, r = q - i * a.ksplit, n = ks + i * a.ksplit;
-      pv[q] = n < NACC ? ld_peer_f32(part + n * ROWS + t, (uint32_t)r) : 0.f;
+      const int ii = q / a.ksplit, rr = q - ii * a.ksplit, n = ks + (wg + FW * ii) * a.ksplit;
+      pv[q] = n < NTOT ? ld_peer_f32(part + n * ROWS + r, (uint32_t)rr) : 0.f;
     }
-    float* fin = reinterpret_cast<float*>(sB);          // [own column][128]: the B operand is dead (all MMAs retired)
+    float* fin = reinterpret_cast<float*>(sB);          // [own column][256]: the B operand is dead (all MMAs retired)
     {
       float v = 0.f;
 #pragma unroll
       for (int q = 0; q < NPV; ++q) {
-        const int i = q / a.ksplit, r = q - i * a.ksplit;
+        const int ii = q / a.ksplit, rr = q - ii * a.ksplit;
         v += pv[q];                                     // rank order 0, 1, ... within a column
-        if (r == a.ksplit - 1) {
-          fin[i * ROWS + t] = v;
+        if (rr == a.ksplit - 1) {
+          if (ii < NOWN) fin[ii * NTHR + t] = v;
           v = 0.f;
         }
       }
     }
 #pragma unroll
-    for (int i = 0; i < NOWN; ++i) {
-      const int n = ks + i * a.ksplit;
-      if (n < NACC) emit(n, fin[i * ROWS + t], addend[i]);
+    for (int ii = 0; ii < NOWN; ++ii) {
+      const int n = ks + (wg + FW * ii) * a.ksplit;
+      if (n < NTOT) emit(n, fin[ii * NTHR + t], addend[ii]);
     }
     cluster_sync_all();                                 // peers stay resident until everyone has read them
     stamp();                                            // split-K reduced
@@ -476,12 +501,12 @@ __global__ void __launch_bounds__(ROWS) mmq_stream_kernel(const StreamArgs a) {
         float add = PUSH ? addend[n < NOWN ? n : 0] : 0.f;
         if (!PUSH) {                                     // unsplit launch with many columns: fetched here
           add = 0.f;
-          if (row < a.N && n < a.cols) {
+          if (row < a.N && cbase + n < a.cols) {
             if (a.epi == Q4B_EPI_BIASF) add = reinterpret_cast<const float*>(a.AUX)[row];
-            if (a.epi == Q4B_EPI_RESID) add = reinterpret_cast<const float*>(a.Y)[(size_t)n * a.ldy + row];
+            if (a.epi == Q4B_EPI_RESID) add = reinterpret_cast<const float*>(a.Y)[(size_t)(cbase + n) * a.ldy + row];
           }
         }
-        emit(n, acc[n], add);
+        emit(cbase + n, acc[n], add);
       }
     }
   }
@@ -551,7 +576,7 @@ int launch(const StreamArgs& a, const Geometry& g, cudaStream_t st) {
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((a.N + ROWS - 1) / ROWS, g.ksplit, 1);
-  cfg.blockDim = dim3(ROWS, 1, 1);
+  cfg.blockDim = dim3(ROWS * ((MODE == MODE_Q8 && NT >= 16) ? 2 : 1), 1, 1);
   cfg.dynamicSmemBytes = g.smem;
   cfg.stream = st;
   cudaLaunchAttribute attr[2];
