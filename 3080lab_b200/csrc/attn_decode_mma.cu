@@ -11,9 +11,10 @@
 // rows padded to 272 bytes so that fragment reads are conflict-free).  All query heads of the KV group form ONE
 // 16-row MMA operand (rows beyond the group are zero), so K and V are read once per group, not once per head:
 //   S = Q K^T    mma.sync.m16n8k16, fp16 x fp16 -> fp32 (exact products of the fp16 inputs)
-//   O += P V     P split as P_hi + P_lo (two fp16 terms, so the probabilities keep ~22 bits) x V via ldmatrix.trans
+//   O += P V     P split as P_hi + P_lo (two fp16 terms, so the probabilities keep ~22 bits; with one term the output
+//                moved by ~1e-4, enough to flip fp16 roundings downstream) x V via ldmatrix.trans
 // with an fp32 online soft-max in base 2 per warp (a warp owns 16 positions of every tile).  Warps are merged in shared
-// memory, chunks through distributed shared memory by cluster rank 0 in chunk order.
+// memory, chunks through distributed shared memory in chunk order, each CTA of the cluster writing an eighth of the outputs.
 #include "q4b_internal.h"
 
 namespace q4b {
@@ -46,16 +47,17 @@ __device__ __forceinline__ void cp_async_wait() {
 }
 
 constexpr size_t STAGE = (size_t)TILE * PITCH;                 // one K or V tile
-constexpr size_t DYN_SMEM = 16 * PITCH + 4 * STAGE;            // Q rows, K[2], V[2]
+constexpr int NSTG = 1;                                        // tile buffers per CTA (other CTAs of the SM cover the load latency)
+constexpr size_t DYN_SMEM = 16 * PITCH + 2 * NSTG * STAGE;     // Q rows, K tiles, V tiles
 
-__global__ void __launch_bounds__(AT) attn_decode_mma_kernel(const __half* qkv, const float* __restrict__ cosT,
+__global__ void __launch_bounds__(AT, 4) attn_decode_mma_kernel(const __half* qkv, const float* __restrict__ cosT,
                                                              const float* __restrict__ sinT, const int64_t* posp, __half* kc,
                                                              __half* vc, __half* out, int NH, int NKV, int max_len, int chunk,
-                                                             float scale_log2e) {
+                                                             float scale_log2e, unsigned long long* trace) {
   extern __shared__ __align__(16) uint8_t sm[];
   uint8_t* sQ = sm;                           // [16][PITCH]
   uint8_t* sK = sQ + 16 * PITCH;              // [2][TILE][PITCH]
-  uint8_t* sV = sK + 2 * STAGE;               // [2][TILE][PITCH]
+  uint8_t* sV = sK + NSTG * STAGE;            // [NSTG][TILE][PITCH]
   __shared__ __align__(16) __half knew[HD], vnew[HD];
   __shared__ __align__(16) float part_o[MAXG][HD];   // this chunk: unnormalised output per head
   __shared__ float part_ml[MAXG][2];                 // (max, sum) in base-2 units
@@ -63,10 +65,22 @@ __global__ void __launch_bounds__(AT) attn_decode_mma_kernel(const __half* qkv, 
   __shared__ float pml[MAXG][NCL][2];
   __shared__ float wgt[MAXG][NCL + 1];
 
-  pdl_launch_dependents();
-  pdl_wait();
   const int t = threadIdx.x, warp = t >> 5, lane = t & 31, g = lane >> 2, tq = lane & 3;
   const int c = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+  // optional timeline: 16 %globaltimer stamps per CTA (thread 0), last entry = number of stamps
+  unsigned long long* tr = (trace && t == 0) ? trace + (size_t)((blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * 16 : nullptr;
+  int tri = 0;
+  auto stamp = [&]() {
+    if (tr && tri < 15) {
+      unsigned long long gt;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt));
+      tr[tri++] = gt;
+    }
+  };
+  stamp();                                     // 0: start
+  pdl_launch_dependents();
+  pdl_wait();
+  stamp();                                     // 1: predecessor complete
   const int GRP = NH / NKV;
   int p = (int)posp[b];
   p = p < 0 ? 0 : (p >= max_len ? max_len - 1 : p);
@@ -78,8 +92,8 @@ __global__ void __launch_bounds__(AT) attn_decode_mma_kernel(const __half* qkv, 
   const int ntile = active ? (min(p, c0 + chunk - 1) - c0) / TILE + 1 : 0;
 
   auto issue_tile = [&](int i) {               // tile i of this chunk -> stage i & 1
-    uint8_t* dk = sK + (size_t)(i & 1) * STAGE;
-    uint8_t* dv = sV + (size_t)(i & 1) * STAGE;
+    uint8_t* dk = sK + (size_t)(i % NSTG) * STAGE;
+    uint8_t* dv = sV + (size_t)(i % NSTG) * STAGE;
     const int t0 = c0 + i * TILE;
     for (int e = t; e < TILE * (HD / 8); e += AT) {
       const int r = e >> 4, cc = e & 15;
@@ -131,6 +145,7 @@ __global__ void __launch_bounds__(AT) attn_decode_mma_kernel(const __half* qkv, 
       vbase[(size_t)p * HD + t + HALF] = v1;
     }
     __syncthreads();
+    stamp();                                                     // 2: q / new row prepared
     uint32_t qa[8][2];                                           // rows g (rows g + 8 of the operand are zero)
     {
       const uint8_t* r0 = sQ + g * PITCH;
@@ -142,7 +157,7 @@ __global__ void __launch_bounds__(AT) attn_decode_mma_kernel(const __half* qkv, 
     }
 
     for (int i = 0; i < ntile; ++i) {
-      if (i + 1 < ntile) {
+      if (NSTG == 2 && i + 1 < ntile) {
         issue_tile(i + 1);
         cp_async_wait<1>();
       } else {
@@ -150,8 +165,8 @@ __global__ void __launch_bounds__(AT) attn_decode_mma_kernel(const __half* qkv, 
       }
       __syncthreads();
       const int t0 = c0 + i * TILE;
-      uint8_t* tk = sK + (size_t)(i & 1) * STAGE;
-      uint8_t* tv = sV + (size_t)(i & 1) * STAGE;
+      uint8_t* tk = sK + (size_t)(i % NSTG) * STAGE;
+      uint8_t* tv = sV + (size_t)(i % NSTG) * STAGE;
       if (p >= t0 && p < t0 + TILE) {                            // the new row goes into the staged tile directly
         if (t < 16) reinterpret_cast<uint4*>(tk + (p - t0) * PITCH)[t] = reinterpret_cast<const uint4*>(knew)[t];
         else if (t < 32) reinterpret_cast<uint4*>(tv + (p - t0) * PITCH)[t - 16] = reinterpret_cast<const uint4*>(vnew)[t - 16];
@@ -193,7 +208,7 @@ __global__ void __launch_bounds__(AT) attn_decode_mma_kernel(const __half* qkv, 
         const __half2 h = __floats2half2_rn(p0, p1);
         const float2 hf = __half22float2(h);
         ph[j] = *reinterpret_cast<const uint32_t*>(&h);
-        pl[j] = pack_h2(p0 - hf.x, p1 - hf.y);
+        pl[j] = pack_h2(p0 - hf.x, p1 - hf.y);                   // second fp16 term: P keeps ~22 bits through the MMA
       }
       l_run = l_run * cor + ps;                                  // per-lane partial; reduced over the quad at the end
 #pragma unroll
@@ -220,7 +235,9 @@ __global__ void __launch_bounds__(AT) attn_decode_mma_kernel(const __half* qkv, 
         o[j + 1][0] = a1[0];
         o[j + 1][1] = a1[1];
       }
-      __syncthreads();                                           // stage i & 1 is free for tile i + 2
+      __syncthreads();                                           // the tile buffer is free again
+      if (NSTG == 1 && i + 1 < ntile) issue_tile(i + 1);
+      stamp();                                                   // 3..: tile done
     }
     // ---- merge the four warps (each saw a quarter of every tile)
     l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
@@ -255,9 +272,12 @@ __global__ void __launch_bounds__(AT) attn_decode_mma_kernel(const __half* qkv, 
         part_ml[hl][1] = lv;
       }
     }
+    stamp();                                                     // warps merged
   }
   cluster_sync_all();                                            // every chunk's partials are in place
-  if (c == 0) {
+  stamp();                                                       // cluster barrier passed
+  // ---- merge of the chunks, spread over the cluster: every CTA reads all (max, sum) pairs and writes 1/8 of the outputs
+  {
     if (t < MAXG * NCL) {
       const int hl = t / NCL, cc = t - hl * NCL;
       if (hl < GRP && cc < nact) {
@@ -279,7 +299,8 @@ __global__ void __launch_bounds__(AT) attn_decode_mma_kernel(const __half* qkv, 
     }
     __syncthreads();
     const size_t head0 = (size_t)b * NH + (size_t)kvh * GRP;
-    for (int e = t; e < GRP * HD; e += AT) {
+    const int per = (GRP * HD + NCL - 1) / NCL;                  // outputs per CTA
+    for (int e = c * per + t; e < min((c + 1) * per, GRP * HD); e += AT) {
       const int hl = e / HD, d = e - hl * HD;
       float pv[NCL];
 #pragma unroll
@@ -291,9 +312,16 @@ __global__ void __launch_bounds__(AT) attn_decode_mma_kernel(const __half* qkv, 
     }
   }
   cluster_sync_all();                                            // peers stay resident until their partials are read
+  stamp();                                                       // end
+  if (tr) tr[15] = (unsigned long long)tri;
 }
 
+unsigned long long* g_attn_trace = nullptr;
+
 }  // namespace
+
+// Device buffer for the optional timeline of the next launches (16 x uint64 per CTA, up to 4096 CTAs); null = off.
+void attn_decode_mma_trace(unsigned long long* buf) { g_attn_trace = buf; }
 
 // Same contract as attn_decode (head_dim 128 only); needs no workspace.
 int attn_decode_mma(const void* qkv, const float* cosT, const float* sinT, const int64_t* pos, void* kc, void* vc, void* out, int B,
@@ -311,7 +339,7 @@ int attn_decode_mma(const void* qkv, const float* cosT, const float* sinT, const
   const float scale_log2e = scale * 1.4426950408889634f;
   return check_launch(launch_pdl_cluster(attn_decode_mma_kernel, dim3(NCL, NKV, B), dim3(AT), DYN_SMEM, st, NCL, 1,
                                          (const __half*)qkv, cosT, sinT, pos, (__half*)kc, (__half*)vc, (__half*)out, NH, NKV,
-                                         max_len, chunk, scale_log2e),
+                                         max_len, chunk, scale_log2e, g_attn_trace),
                       "attn_decode_mma");
 }
 

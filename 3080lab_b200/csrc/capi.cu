@@ -47,6 +47,7 @@ int blockdot(const void*, const void*, int32_t*, int, int, int, int, uint32_t*, 
 int mmq_stream(const void*, const void*, const void*, const void*, void*, const void*, int, int, int, int, int, int, uint32_t*,
                cudaStream_t, const float* norm_w = nullptr, float eps = 0.f);
 void mmq_stream_trace(unsigned long long*);
+void attn_decode_mma_trace(unsigned long long*);
 size_t decode_persistent_workspace(const q4b_decode_desc*);
 int decode_persistent_prepare(const q4b_decode_desc*, void*, size_t);
 int decode_persistent_layers(const q4b_decode_desc*, void*, size_t, cudaStream_t);
@@ -171,6 +172,7 @@ int q4b_attn_prefill(const void* qkv, const float* cosT, const float* sinT, void
 int q4b_trace_buffer(uint64_t* device_buffer, size_t entries) {
   if (device_buffer && entries < (size_t)4096 * 16) return fail(Q4B_E_WORKSPACE, "trace_buffer: need 4096 x 16 entries");
   mmq_stream_trace(reinterpret_cast<unsigned long long*>(device_buffer));
+  attn_decode_mma_trace(reinterpret_cast<unsigned long long*>(device_buffer));
   return Q4B_OK;
 }
 

@@ -27,8 +27,15 @@
 //     while the tensor core works on the current one.
 //   * split-K: the CTAs of a thread-block cluster share a row tile; partial sums cross through distributed shared
 //     memory and are added in rank order, so results are bit-repeatable.
+// Measured limits of this formulation on B200: tcgen05.mma instructions that write DIFFERENT accumulator tiles retire
+// one every ~177 clocks whatever N (8 or 32; 43 clocks when the same tile is overwritten), so a row tile consumes one
+// 2304-byte k-block per 177 clocks: 25 GB/s per SM, 3.8 TB/s per GPU.  A register-accumulator variant of the Q8_1 mode
+// (mma.sync.m16n8k32.s8, no tensor memory) was built and measured: faster per kernel when the weights sit in L2, but
+// slower inside the real decode step (4.73 K against 5.09 K tok/s at 8 sequences, 12.56 K against 12.73 K at 32), and
+// was dropped.
 // All waits are bounded (status word + fall through).
 #include <algorithm>
+#include <cstdlib>
 
 #include "q4b_internal.h"
 #include "tc05.cuh"
