@@ -1,0 +1,140 @@
+"""In-kernel timelines (%globaltimer stamps written by thread 0 of every CTA) of the decode kernels.
+
+The tensor-core kernels can stamp their phases into a caller-provided device buffer (`q4b_trace_buffer`,
+`q4b_decode_persistent_trace`; off by default, a few predicated instructions when off).  This tool runs one isolated
+launch of a kernel with stamping on and prints, per phase, the median and the maximum over the CTAs of the time since
+the first CTA started.  The numbers explain where a kernel's microseconds go; they are not benchmark values (an isolated
+launch has no programmatic overlap with its neighbours and its weights sit in L2 after the warm-up launches).
+
+    python 3080lab_b200/timeline.py gemv              # the four linears of a layer at batch 1 (exact tensor-core GEMV)
+    python 3080lab_b200/timeline.py mmq --batch 32    # the same four as Q8_1 x Q4_0 MMQ for 32 sequences
+    python 3080lab_b200/timeline.py attn --batch 32   # batched decode attention, 1024-token context
+    python 3080lab_b200/timeline.py persistent        # one token through the persistent all-layers kernel (8 layers)
+
+Stamp order of `mmq_stream_kernel`: start, TMEM allocated, barriers ready, bulk copies issued, predecessor complete,
+activation operand staged, one stamp per batch of k-blocks (expanded and issued), all batches folded, split-K reduced,
+end.  Of `attn_decode_mma_kernel`: start, predecessor complete, q / new row prepared, one per 64-position tile, warps
+merged, cluster barrier passed, end.  The persistent kernel labels its stamps (see `decode_persistent.cu`).
+"""
+from __future__ import annotations
+
+import argparse
+import importlib
+import sys
+from pathlib import Path
+
+import numpy as np
+
+sys.path.insert(0, str(Path(__file__).resolve().parent.parent))
+
+
+def _mods():
+    names = ("synth", "engine", "_ffi", "qwen_kernels")
+    return [importlib.import_module("3080lab_b200." + n) for n in names]
+
+
+def _report(name: str, buf) -> None:
+    t = buf.cpu().numpy().reshape(-1, 16)
+    t = t[t[:, 15] > 0]
+    t0 = t[:, 0].min()
+    for n in sorted({int(x) for x in t[:, 15]}):
+        rows = t[t[:, 15] == n]
+        rel = (rows[:, :n] - t0) / 1e3
+        print(f"{name}: {len(rows)} CTAs with {n} stamps")
+        print("   median us:", np.round(np.median(rel, axis=0), 2).tolist())
+        print("   max    us:", np.round(rel.max(axis=0), 2).tolist())
+
+
+def _traced(ffi, torch, fn, name: str) -> None:
+    buf = torch.zeros(4096 * 16, dtype=torch.int64, device="cuda")
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    ffi.call("q4b_trace_buffer", buf.data_ptr(), buf.numel())
+    fn()
+    torch.cuda.synchronize()
+    ffi.call("q4b_trace_buffer", None, 0)
+    _report(name, buf)
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("what", choices=["gemv", "mmq", "attn", "persistent"])
+    ap.add_argument("--batch", type=int, default=32)
+    args = ap.parse_args()
+    import torch
+    synth, engine, ffi, K = _mods()
+    layers = 8 if args.what == "persistent" else 2
+    cfg = synth.ModelConfig("qwen2.5-1.5b-cut", layers, 1536, 8960, 12, 2, 128, 8192)
+    model = synth.synth_model(cfg, 0)
+    c, H = cfg, cfg.hidden
+    if args.what == "gemv":
+        m = engine.FusedQwen(model, max_len=1024)
+        m.pos.fill_(600)
+        L = m.L[0]
+        ops = {
+            "qkv  (rmsnorm + 2048x1536 + bias)": lambda: m.norm_gemv(L["ln1"], L["qkv"], m.qkv, L["qkv_b"], c.qkv_rows, H, "biasf"),
+            "o    (1536x1536 + residual)": lambda: m.gemv("o", L["o"], m.att, m.h, None, H, c.q_rows, "resid"),
+            "gu   (rmsnorm + 17920x1536 + swiglu)": lambda: m.norm_gemv(L["ln2"], L["gu"], m.xm, None, 2 * c.ffn, H, "swiglu"),
+            "down (1536x8960 + residual)": lambda: m.gemv("down", L["down"], m.xm, m.h, None, H, c.ffn, "resid"),
+        }
+        for name, f in ops.items():
+            _traced(ffi, torch, f, name)
+    elif args.what in ("mmq", "attn"):
+        m = engine.FusedQwen(model, max_len=1280)
+        bm = engine.Batched(m, args.batch)
+        bm.kc.normal_()
+        bm.vc.normal_()
+        bm.qkv.normal_()
+        bm.pos.fill_(1024)
+        L = m.L[0]
+        if args.what == "mmq":
+            ops = {
+                "qkv": lambda: bm.gemm8(L["qkv"], c.qkv_rows, H, bm.qkv, L["qkv_b"], "biasf", c.qkv_rows),
+                "o": lambda: bm.gemm8(L["o"], H, c.q_rows, bm.h, None, "resid", H),
+                "gu": lambda: bm.gemm8(L["gu"], 2 * c.ffn, H, bm.xm, None, "swiglu", c.ffn),
+                "down": lambda: bm.gemm8(L["down"], H, c.ffn, bm.h, None, "resid", H),
+            }
+            for name, f in ops.items():
+                _traced(ffi, torch, f, f"{name} ({args.batch} sequences)")
+        else:
+            _traced(ffi, torch, lambda: K.attn(bm.qkv, m.cos, m.sin, bm.pos, bm.kc[0], bm.vc[0], bm.att, c.n_heads,
+                                               c.n_kv_heads, c.head_dim, m.max_len, m.scale, bm.attn_ws),
+                    f"attention ({args.batch} sequences, context 1024)")
+    else:
+        m = engine.FusedQwen(model, max_len=1024, persistent=True)
+        m.feed(synth.synth_prompt(cfg, 64, 1))
+        torch.cuda.synchronize()
+        m.check_status()
+        cap = 48 * layers + 8
+        nsm = torch.cuda.get_device_properties(0).multi_processor_count
+        buf = torch.zeros(nsm * cap, dtype=torch.int64, device="cuda")
+        ffi.call("q4b_decode_persistent_trace", buf.data_ptr(), -cap)      # negative: stages subdivided
+        m.step()
+        torch.cuda.synchronize()
+        ffi.call("q4b_decode_persistent_trace", None, 0)
+        raw = buf.cpu().numpy().view(np.uint64).reshape(nsm, cap)
+        lab = (raw >> np.uint64(56)).astype(int)
+        tm = (raw & np.uint64((1 << 56) - 1)).astype(np.float64)
+        names = {0: "start", 1: "barrier left", 2: "end", 10: "operand staged", 11: "staging: loads + partial sums",
+                 12: "staging: values", 13: "staging: digits", 14: "batches done", 20: "barrier entered",
+                 21: "barrier: CTA arrived", 30: "attention: q/k/v rows", 31: "attention: RoPE", 32: "attention: chunks"}
+        stages = ["qkv", "attention", "o", "gate_up", "down"]
+        layer = layers // 2
+        for si, sn in enumerate(stages):
+            rows: dict = {}
+            for cta in range(nsm):
+                n = int((raw[cta] != 0).sum())
+                outs = [i for i in range(n) if lab[cta, i] == 1]
+                lo, hi = outs[5 * layer + si - 1], outs[5 * layer + si]
+                for i in range(lo + 1, hi + 1):
+                    rows.setdefault(names.get(lab[cta, i], str(lab[cta, i])), []).append((tm[cta, i] - tm[cta, i - 1]) / 1e3)
+            print(f"layer {layer}, {sn}: us since the previous stamp (min / median / max over CTAs, count)")
+            for k, v in rows.items():
+                print(f"   {k:32s} {np.min(v):6.2f} {np.median(v):6.2f} {np.max(v):6.2f}  {len(v)}")
+        ends = [tm[cta, int((raw[cta] != 0).sum()) - 1] for cta in range(nsm)]
+        print(f"kernel: {(max(ends) - tm[:, 0].min()) / 1e3:.1f} us for {layers} layers")
+
+
+if __name__ == "__main__":
+    main()
