@@ -32,7 +32,7 @@ class DecodeDesc(C.Structure):
                 ("norm", _P), ("head", Linear), ("cosT", _P), ("sinT", _P), ("tok", _P), ("pos", _P), ("h", _P),
                 ("x", _P), ("qkv", _P), ("att", _P), ("act", _P), ("logits", _P), ("attn_ws", _P), ("attn_ws_bytes", _Z),
                 ("head_ws", _P), ("head_ws_bytes", _Z), ("status", _P), ("flags", _I), ("persistent_ws", _P),
-                ("persistent_ws_bytes", _Z)]
+                ("persistent_ws_bytes", _Z), ("head16", _P)]
 
 
 STEP_TENSOR_CORE = 1

@@ -239,7 +239,8 @@ int q4b_decode_step(const q4b_decode_desc* d, q4b_stream_t stream) {
     Q4B_TRY(argmax_advance(d->logits, 1, d->vocab, d->tok, d->pos, d->head_ws, d->head_ws_bytes, st));
   } else {
     Q4B_TRY(rmsnorm(d->h, d->norm, d->x, 1, H, d->eps, st));
-    Q4B_TRY(head_f16_argmax(d->embed, d->x, d->logits, d->vocab, H, d->tok, d->pos, d->head_ws, d->head_ws_bytes, st));
+    Q4B_TRY(head_f16_argmax(d->head16 ? d->head16 : d->embed, d->x, d->logits, d->vocab, H, d->tok, d->pos, d->head_ws,
+                            d->head_ws_bytes, st));
   }
 #undef Q4B_TRY
   return Q4B_OK;

@@ -43,6 +43,8 @@ class FusedQwen:
             self.L.append(d)
         self.norm = _dev(model["norm"], self.device)
         self.head = None if model["head"] is None else tuple(_dev(a, self.device) for a in model["head"])
+        # fp16 LM head table: the embedding (tied) unless the model brings its own (a GGUF `output.weight` kept in fp16)
+        self.head16 = self.embed if model.get("head16") is None else _dev(model["head16"], self.device)
         # tile-packed copies for the tensor-core kernels (K a multiple of 256)
         self.tensor_core = tensor_core
         self.packed = {}
@@ -115,7 +117,8 @@ class FusedQwen:
             self.cos.data_ptr(), self.sin.data_ptr(), self.tok.data_ptr(), self.pos.data_ptr(), self.h.data_ptr(),
             self.x.data_ptr(), self.qkv.data_ptr(), self.att.data_ptr(), self.xm.data_ptr(), self.logits.data_ptr(),
             self.attn_ws.data_ptr(), self.attn_ws.numel(), self.head_ws.data_ptr(), self.head_ws.numel(),
-            self.status.data_ptr(), _ffi.STEP_TENSOR_CORE if self.tensor_core else 0, None, 0)
+            self.status.data_ptr(), _ffi.STEP_TENSOR_CORE if self.tensor_core else 0, None, 0,
+            None if self.head16 is self.embed else self.head16.data_ptr())
 
     # ---- one decode token -------------------------------------------------------------------------------------------
     def step(self) -> None:
@@ -166,7 +169,7 @@ class FusedQwen:
             self.gemv("down", L["down"], self.xm, self.h, None, H, c.ffn, "resid")
         if self.head is None:
             self.rms(self.norm, self.x)
-            K.head_argmax(self.embed, self.x, self.logits, self.tok, self.pos, self.head_ws)
+            K.head_argmax(self.head16, self.x, self.logits, self.tok, self.pos, self.head_ws)
         else:
             self.norm_gemv(self.norm, self.head, self.logits, None, c.vocab, H, "logits")
             K.finish(self.logits, self.tok, self.pos, self.head_ws)
@@ -281,7 +284,7 @@ class Batched:
             self.gemm8(L["down"], H, c.ffn, self.h, None, "resid", H)
         if m.head is None:
             K.rms(self.h, m.norm, self.x, c.eps)
-            QB.head_batched(m.embed, self.x, self.logits)
+            QB.head_batched(m.head16, self.x, self.logits)
         else:
             QB.rmsnorm_q8(self.h, m.norm, self.xq, self.xd, c.eps)
             self.gemm8(m.head, c.vocab, H, self.logits, None, "logits", c.vocab)
@@ -394,7 +397,7 @@ class Prefill:
         m.pos.fill_(pos0 + self.P - 1)
         if m.head is None:
             m.rms(m.norm, m.x)
-            K.head_argmax(m.embed, m.x, m.logits, m.tok, m.pos, m.head_ws)
+            K.head_argmax(m.head16, m.x, m.logits, m.tok, m.pos, m.head_ws)
         else:
             m.norm_gemv(m.norm, m.head, m.logits, None, m.cfg.vocab, m.cfg.hidden, "logits")
             K.finish(m.logits, m.tok, m.pos, m.head_ws)

@@ -21,7 +21,7 @@ from pathlib import Path
 import numpy as np
 
 # ggml type id -> (name, weights per block, bytes per block)
-GGML_TYPES = {0: ("F32", 1, 4), 1: ("F16", 1, 2), 2: ("Q4_0", 32, 18)}
+GGML_TYPES = {0: ("F32", 1, 4), 1: ("F16", 1, 2), 2: ("Q4_0", 32, 18), 14: ("Q6_K", 256, 210)}
 
 _FIXED = {0: "B", 1: "b", 2: "H", 3: "h", 4: "I", 5: "i", 6: "f", 7: "?", 10: "Q", 11: "q", 12: "d"}
 _T_STRING, _T_ARRAY = 8, 9
@@ -113,6 +113,8 @@ class GGUF:
             flat = b.view(np.float32)
         elif kind == "F16":
             flat = b.view(np.float16).astype(np.float32)
+        elif kind == "Q6_K":
+            flat = q6_k_dequant(b)
         else:
             d, q = q4_0_blocks(b)
             flat = (d[:, None] * (q.astype(np.float32) - 8.0)).reshape(-1)
@@ -129,6 +131,35 @@ def q4_0_blocks(b: np.ndarray):
     q[:, :16] = packed & 0x0F
     q[:, 16:] = packed >> 4
     return d, q
+
+
+def q6_k_values(b: np.ndarray):
+    """Decode raw Q6_K bytes -> (q int8 [nblk, 256] in -32..31, sc int8 [nblk, 16], d fp16 [nblk]).
+
+    ggml's block_q6_K is 210 bytes for 256 weights: 128 bytes of low nibbles, 64 bytes of 2-bit high parts, 16 signed
+    sub-block scales, one fp16 super-scale.  Inside each half of 128 weights, weight 32 j + l (j = 0..3, l = 0..31) takes
+    its low nibble from byte 32 (j & 1) + l of the half's 64 nibble bytes (low nibble for j < 2, high nibble otherwise)
+    and its two high bits from bits 2j, 2j + 1 of byte l of the half's 32 high bytes; value = 6-bit code - 32, and weight
+    w of the block is scaled by d * sc[w // 16].  Same contract as the reference's `q6_k_parts` (lab/gguf.py:95-123)."""
+    rec = np.ascontiguousarray(b, dtype=np.uint8).reshape(-1, 210)
+    n = rec.shape[0]
+    nib = rec[:, 0:128].reshape(n, 2, 2, 32)                 # [block, half, byte group (j & 1), l]
+    high = rec[:, 128:192].reshape(n, 2, 1, 32)              # [block, half, -, l]
+    code = np.empty((n, 2, 4, 32), np.uint8)                 # [block, half, j, l]
+    for j in range(4):
+        low = (nib[:, :, j & 1, :] & 0x0F) if j < 2 else (nib[:, :, j & 1, :] >> 4)
+        code[:, :, j, :] = low | (((high[:, :, 0, :] >> (2 * j)) & 3) << 4)
+    q = (code.reshape(n, 256).astype(np.int16) - 32).astype(np.int8)
+    sc = np.ascontiguousarray(rec[:, 192:208]).view(np.int8)
+    d = np.ascontiguousarray(rec[:, 208:210]).view(np.float16).reshape(-1)
+    return q, sc, d
+
+
+def q6_k_dequant(b: np.ndarray) -> np.ndarray:
+    """Raw Q6_K bytes -> float32 weights [nblk * 256]: d * sc[w // 16] * q[w], evaluated in float32 as (d * sc) * q."""
+    q, sc, d = q6_k_values(b)
+    scale = d.astype(np.float32)[:, None] * sc.astype(np.float32)            # [nblk, 16]
+    return (np.repeat(scale, 16, axis=1) * q.astype(np.float32)).reshape(-1)
 
 
 def q4_0_encode(q: np.ndarray, d: np.ndarray) -> np.ndarray:

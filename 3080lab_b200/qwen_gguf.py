@@ -8,9 +8,12 @@ tensors `token_embd`, `blk.N.attn_{q,k,v,output}`, `blk.N.ffn_{gate,up,down}`, `
 by row (row 2i = gate i, row 2i + 1 = up i) so the SwiGLU epilogue sees both halves of a pair in one thread pair, all
 in the canonical device layout (`gguf.pack_nibbles`).  `GGUFQwen(path)` is `FusedQwen(load_model(path))`.
 
-Supported tensor types: Q4_0 for the layer matrices; Q4_0, F16 or F32 for `token_embd` (kept as an fp16 table: F32 and
-Q4_0 tables are rounded to fp16, the reference keeps fp32); `output.weight` absent (tied head) or Q4_0.  The reference
-reads a Q6_K head (scripts/qwen_gguf.py:92-113); that format is not built here and is refused by name.
+Supported tensor types: Q4_0 for the layer matrices; Q4_0, Q6_K, F16 or F32 for `token_embd` (kept as an fp16 table:
+everything but F16 is rounded to fp16, the reference keeps fp32); `output.weight` absent (tied head), Q4_0 (the Q4_0
+head path), or Q6_K / F16 / F32 (dequantised on the host into an untied fp16 head table, `model["head16"]`).  The
+reference runs a Q6_K head with its own GEMV kernel at 6.5625 bits per weight (scripts/qwen_gguf.py:92-113); here such a
+head costs 16 bits per weight and its values carry one fp16 rounding (relative 2^-11), which is the documented
+difference of this loader.
 
 `export_model(model, path)` writes the same layout back (used for synthetic models and by the tests).
 """
@@ -21,7 +24,7 @@ import numpy as np
 from . import gguf as G
 from .synth import ModelConfig
 
-_Q4_0, _F16, _F32 = 2, 1, 0      # ggml type ids
+_Q4_0, _F16, _F32, _Q6_K = 2, 1, 0, 14      # ggml type ids
 
 
 def _type_name(t: int) -> str:
@@ -48,18 +51,22 @@ def load_model(path) -> dict:
     vocab = int(emb_t.dims[1])
     if emb_t.type == _F16:
         embed = np.ascontiguousarray(g.raw("token_embd.weight")[0]).view(np.float16).reshape(vocab, H).copy()
-    elif emb_t.type in (_F32, _Q4_0):
+    elif emb_t.type in (_F32, _Q4_0, _Q6_K):
         embed = g.f32("token_embd.weight").astype(np.float16)
     else:
-        raise NotImplementedError(f"token_embd.weight is {_type_name(emb_t.type)}; Q4_0, F16 and F32 are supported")
-    head = None
+        raise NotImplementedError(f"token_embd.weight is {_type_name(emb_t.type)}; Q4_0, Q6_K, F16 and F32 are supported")
+    head, head16 = None, None
     if "output.weight" in g.tensors:
         t = g.tensors["output.weight"]
-        if t.type != _Q4_0:
-            raise NotImplementedError(f"output.weight is {_type_name(t.type)}: only a Q4_0 head (or a tied head) is built; "
-                                      "the Q6_K head of the reference (scripts/qwen_gguf.py:92-113) is not")
-        q, d = _q4(g, "output.weight")
-        head = (G.pack_nibbles(q), d)
+        if t.type == _Q4_0:
+            q, d = _q4(g, "output.weight")
+            head = (G.pack_nibbles(q), d)
+        elif t.type == _F16:
+            head16 = np.ascontiguousarray(g.raw("output.weight")[0]).view(np.float16).reshape(vocab, H).copy()
+        elif t.type in (_F32, _Q6_K):
+            head16 = g.f32("output.weight").astype(np.float16)
+        else:
+            raise NotImplementedError(f"output.weight is {_type_name(t.type)}; Q4_0, Q6_K, F16 and F32 are supported")
     layers = []
     for i in range(nL):
         p = f"blk.{i}."
@@ -84,9 +91,9 @@ def load_model(path) -> dict:
             "down": (G.pack_nibbles(dq), np.ascontiguousarray(dd)),
         })
     cfg = ModelConfig(str(m.get("general.name", arch)), nL, H, ffn, nh, nkv, hd, vocab, eps, theta,
-                      tied_fp16_head=head is None)
+                      tied_fp16_head=head is None)            # True also for an untied fp16 table (model["head16"])
     return {"cfg": cfg, "embed": embed, "layers": layers, "norm": g.f32("output_norm.weight").astype(np.float32).copy(),
-            "head": head}
+            "head": head, "head16": head16}
 
 
 def _q4_tensor(W: np.ndarray, S: np.ndarray):
@@ -113,6 +120,8 @@ def export_model(model: dict, path, arch: str = "qwen2") -> None:
                "output_norm.weight": _f32_tensor(model["norm"])}
     if model["head"] is not None:
         tensors["output.weight"] = _q4_tensor(*model["head"])
+    elif model.get("head16") is not None:
+        tensors["output.weight"] = (_F16, (c.hidden, c.vocab), np.ascontiguousarray(model["head16"], np.float16).tobytes())
     qr, kr = c.q_rows, c.kv_rows
     for i, L in enumerate(model["layers"]):
         p = f"blk.{i}."

@@ -177,7 +177,7 @@ class TPBatched:
             self._reduce_add()
         if m.head is None:
             K.rms(self.h, m.norm, self.x, c.eps)
-            QB.head_batched(m.embed, self.x, self.logits)
+            QB.head_batched(m.head16, self.x, self.logits)
         else:
             QB.rmsnorm_q8(self.h, m.norm, self.xq, self.xd, c.eps)
             self._gemm8(m.head, c.vocab, H, self.logits, None, "logits", c.vocab)

@@ -250,6 +250,8 @@ typedef struct {
   int flags;              /* Q4B_STEP_* */
   void* persistent_ws;    /* Q4B_STEP_PERSISTENT: q4b_decode_persistent_workspace bytes, prepared once */
   size_t persistent_ws_bytes;
+  const void* head16;     /* untied fp16 LM head [vocab, hidden] (a GGUF `output.weight` kept in fp16), or null: with
+                             head.W null the head is then `embed` (tied) */
 } q4b_decode_desc;
 
 #define Q4B_STEP_TENSOR_CORE 1  /* linears through q4b_gemv_q4_0_tc where K is a multiple of 256 */

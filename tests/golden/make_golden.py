@@ -61,6 +61,16 @@ def main(ref_root: str) -> None:
     deq = (d[:, None] * (q.astype(np.float32) - 8)).reshape(-1)          # the GGUF.f32 Q4_0 branch
     np.savez_compressed(HERE / "q4_0_codec.npz", raw=raw, d=d, q=q, f32=deq)
 
+    # 1b. Q6_K codec: random blocks (every bit pattern of ql / qh / scales is a valid block) with sane fp16 super-scales
+    rng6 = np.random.default_rng(6)
+    raw6 = rng6.integers(0, 256, size=(40, 210), dtype=np.uint8)
+    raw6[:, 208:210] = rng6.uniform(-0.02, 0.02, size=40).astype(np.float16).view(np.uint8).reshape(-1, 2)
+    raw6 = raw6.reshape(-1)
+    q6, sc6, d6 = ref.q6_k_parts(raw6)
+    q6b, s6 = ref.q6_k_blocks(raw6)
+    deq6 = (np.repeat(s6, 16, axis=1) * q6b.astype(np.float32)).reshape(-1)   # the GGUF.f32 Q6_K branch (lab/gguf.py:80-82)
+    np.savez_compressed(HERE / "q6_k_codec.npz", raw=raw6, q=q6, sc=sc6, d=d6, f32=deq6)
+
     # 2. a GGUF file parsed by the reference reader
     qs, ds, _ = gemv_inputs(16, 64, False)
     f16t = rng.standard_normal((4, 8)).astype(np.float16)

@@ -62,7 +62,9 @@ def test_file_uses_llama_cpp_names_and_row_order(tmp_path):
     assert np.array_equal(G.pack_nibbles(q_k), model["layers"][0]["qkv"][0][cfg.q_rows:cfg.q_rows + cfg.kv_rows])
 
 
-def test_q6_k_head_is_refused_by_name(tmp_path):
+def test_q6_k_tensors_load_as_fp16_tables(tmp_path):
+    """A file whose embedding and head are Q6_K (the layout of llama.cpp's Q4_0 exports) loads: both become fp16 tables,
+    the head an untied one; an unsupported type is refused by name."""
     synth, qg, G = pkg("synth"), pkg("qwen_gguf"), pkg("gguf")
     cfg = synth.TINY
     model = synth.synth_model(cfg, 2)
@@ -70,7 +72,23 @@ def test_q6_k_head_is_refused_by_name(tmp_path):
     qg.export_model(model, path)
     g = G.GGUF(path)
     tensors = {n: (t.type, t.dims, bytes(g.raw(n)[0])) for n, t in g.tensors.items()}
-    tensors["output.weight"] = (14, (cfg.hidden, cfg.vocab), bytes(cfg.vocab * cfg.hidden // 256 * 210))   # Q6_K record size
+    rng = np.random.default_rng(9)
+    nblk = cfg.vocab * cfg.hidden // 256
+
+    def q6(seed):
+        raw = np.random.default_rng(seed).integers(0, 256, size=(nblk, 210), dtype=np.uint8)
+        raw[:, 208:210] = rng.uniform(1e-4, 1e-3, nblk).astype(np.float16).view(np.uint8).reshape(-1, 2)
+        return raw.reshape(-1)
+
+    emb_raw, head_raw = q6(1), q6(2)
+    tensors["token_embd.weight"] = (14, (cfg.hidden, cfg.vocab), emb_raw.tobytes())
+    tensors["output.weight"] = (14, (cfg.hidden, cfg.vocab), head_raw.tobytes())
     G.write_gguf(tmp_path / "q6.gguf", dict(g.meta), tensors)
-    with pytest.raises(NotImplementedError, match="Q6_K|ggml type 14"):
-        qg.load_model(tmp_path / "q6.gguf")
+    back = qg.load_model(tmp_path / "q6.gguf")
+    assert back["head"] is None and back["head16"].dtype == np.float16 and back["head16"].shape == (cfg.vocab, cfg.hidden)
+    assert np.array_equal(back["embed"], G.q6_k_dequant(emb_raw).reshape(cfg.vocab, cfg.hidden).astype(np.float16))
+    assert np.array_equal(back["head16"], G.q6_k_dequant(head_raw).reshape(cfg.vocab, cfg.hidden).astype(np.float16))
+    tensors["output.weight"] = (8, (cfg.hidden, cfg.vocab), bytes(cfg.vocab * cfg.hidden // 32 * 34))     # Q8_0: not supported
+    G.write_gguf(tmp_path / "q8.gguf", dict(g.meta), tensors)
+    with pytest.raises(NotImplementedError, match="ggml type 8"):
+        qg.load_model(tmp_path / "q8.gguf")

@@ -118,3 +118,14 @@ def test_blockdot_and_mmq_consistent():
     # int8 activations cost about half a percent against the fp16-activation GEMV
     yf = x.astype(np.float64) @ o.dequant(W, S).T
     assert np.max(np.abs(y - yf)) / np.max(np.abs(yf)) < 2e-2
+
+
+def test_q6_k_codec_matches_reference_vectors(golden):
+    """Q6_K block decode against vectors made with the reference's q6_k_parts / GGUF.f32 (lab/gguf.py:80-82, 95-123)."""
+    G = pkg("gguf")
+    z = golden["q6_k_codec"]
+    q, sc, d = G.q6_k_values(z["raw"])
+    assert np.array_equal(q, z["q"]) and np.array_equal(sc, z["sc"])
+    assert np.array_equal(d.view(np.uint16), z["d"].view(np.uint16))
+    assert np.array_equal(G.q6_k_dequant(z["raw"]), z["f32"])
+    assert q.min() >= -32 and q.max() <= 31
