@@ -6,16 +6,21 @@
 // :1237-1243): one int8 MMA per k-block because every block has its own pair of scales, fp32 rescale-and-add per block
 // in ascending k order.  What changes is where things live on Blackwell:
 //   * CTA tile = 128 weight rows (UMMA M) x 128 activation rows (UMMA N); one tcgen05.mma.kind::i8 (K = 32) per k-block
-//     into one of two TMEM accumulator slots (128 columns each);
+//     into one of three TMEM accumulator slots (128 columns each);
 //   * weights arrive tile-packed through bulk (TMA) copies in batches of 8 k-blocks (ring of 4); thread r of the first
 //     warpgroup expands row r's nibbles to signed bytes and writes them into TMEM as the A operand (tcgen05.st);
 //   * activations arrive pre-tiled from the quantiser (quant_q8_1.cu, "tiled" outputs): per (128-row tile, k-block)
 //     4096 bytes already in the UMMA K-major core-matrix order + 128 fp32 block scales, one bulk copy per stage
 //     (ring of 8), used directly as the B operand;
-//   * warp 8 (one thread) issues the MMAs, warp 9 (one thread) the bulk copies; warpgroup 0 expands A and rescales
-//     accumulator columns 0..63, warpgroup 1 rescales columns 64..127; the rescale of k-block b overlaps the MMA of b+1
-//     and the expansion of b+2.  Barrier arrivals are one per warp (an elected lane after the warp-wide TMEM wait):
-//     with one arrival per thread the 640 shared-memory barrier updates per k-block were the bottleneck.
+//   * warps 8 and 10 (one thread each, even / odd k-blocks) issue the MMAs, warp 9 (one thread) the bulk copies;
+//     warpgroup 0 expands A and rescales accumulator columns 0..63, warpgroup 1 rescales columns 64..127; warpgroup 0
+//     rescales k-block b - 2 after expanding k-block b.  Barrier arrivals are one per warp (an elected lane after the
+//     warp-wide TMEM wait): with one arrival per thread the 640 shared-memory barrier updates per k-block were the
+//     bottleneck.
+// Measured per k-block on B200 (stamps of one CTA): ~770 ns, of which warpgroup 0 spends ~130-190 expanding, ~30 on
+// the accumulator read, ~270 on the rescale arithmetic and ~160 on barrier arrivals and loop overhead; an MMA to a fresh
+// accumulator tile retires in 278 clocks (146 ns); every mbarrier wait of an issuing thread costs ~160 ns even when the
+// barrier is already complete, which is why the "A ready" and "slot free" conditions share one barrier.
 // The per-block rescale (one int->float, two multiplies/FMAs per output per k-block) is CUDA-core work of the same
 // order as the tensor-core time at full rate; it is the structural cost of Q4_0 x Q8_1 and bounds this kernel.
 // All waits are bounded; after the first expired wait a thread stops waiting (status word, garbage out, no hang).
@@ -26,7 +31,11 @@ namespace q4b {
 
 namespace {
 
-constexpr int PF_WG = 128, PF_THREADS = 2 * PF_WG + 64;   // two warpgroups + MMA warp + copy warp
+// Accumulator slots in tensor memory (128 columns each; 3 x 128 + the A operands fill the 512 columns).  With three,
+// warpgroup 0 rescales k-block b - 2 after expanding k-block b, so the expand -> go -> MMA -> commit -> wake chain of one
+// k-block (~800 ns measured) spans two iterations instead of one.
+constexpr int NSLOT = 3;
+constexpr int PF_WG = 128, PF_THREADS = 2 * PF_WG + 96;   // two warpgroups + MMA warp (even k-blocks) + copy warp + MMA warp (odd)
 constexpr int NTOK = 128;                 // activation rows per CTA tile (UMMA N)
 constexpr int SB = 8;                     // activation stages (one k-block each)
 constexpr int WB = 4;                     // weight batches in flight (8 k-blocks each)
@@ -58,7 +67,7 @@ __device__ __forceinline__ void waitb(uint64_t* bar, uint32_t parity, bool& ok) 
 
 __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const PrefillArgs a) {
   extern __shared__ __align__(128) uint8_t smem[];
-  __shared__ __align__(8) uint64_t w_full[WB], w_empty[WB], b_full[SB], b_empty[SB], a_full[2], d_full[2], d_empty[2];
+  __shared__ __align__(8) uint64_t w_full[WB], w_empty[WB], b_full[SB], b_empty[SB], go[NSLOT], d_full[NSLOT];
   __shared__ uint32_t tmem_base_s;
 
   uint8_t* slabW = smem;                                   // [WB][8][128 rows][16]
@@ -84,19 +93,23 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const Prefil
       tc::mbar_init(&b_full[i], 1);
       tc::mbar_init(&b_empty[i], 1 + 8);
     }
-    for (int i = 0; i < 2; ++i) {
-      tc::mbar_init(&a_full[i], 4);
+    for (int i = 0; i < NSLOT; ++i) {
+      // go[slot]: the A operand of k-block b is in tensor memory (4 expanding warps) AND the accumulator slot has been
+      // read out for k-block b - 2 (8 rescaling warps).  One barrier instead of two: every wait of the issuing thread
+      // costs ~160 ns even when the barrier is already complete.
+      tc::mbar_init(&go[i], 4 + 8);
       tc::mbar_init(&d_full[i], 1);
-      tc::mbar_init(&d_empty[i], 8);
     }
     tc::mbar_fence_init();
+    for (int i = 0; i < NSLOT; ++i)
+      for (int k = 0; k < 8; ++k) tc::mbar_arrive(&go[i]);   // the first k-block of a slot has no predecessor to wait for
   }
   tc::fence_before_sync();
   __syncthreads();
   tc::fence_after_sync();
   pdl_launch_dependents();
   const uint32_t tmem = tmem_base_s;
-  const uint32_t tmem_a = tmem, tmem_d = tmem + 128;       // A: 2 x 8 columns; D: 2 x 128 columns
+  const uint32_t tmem_a = tmem, tmem_d = tmem + 128;       // A: NSLOT x 8 columns; D: NSLOT x 128 columns
   constexpr uint32_t IDESC = tc::idesc_i8(128, NTOK);
   bool ok = true;
 
@@ -131,15 +144,16 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const Prefil
         }
       }
     }
-  } else if (warp == 8) {
-    // ===================== MMA issuer (one thread) =====================
+  } else if (warp == 8 || warp == 10) {
+    // ===================== MMA issuers: one thread for the even k-blocks, one (in another warp) for the odd ones ==========
+    // Measured: one issuing thread spent ~700 ns per k-block on its three waits, the MMA and the two commits, which set
+    // the pace of the whole pipeline; the two slots are independent, so each gets its own issuer.
     if ((t & 31) == 0) {
       const uint32_t stage0 = tc::smem_u32(stage);
-      for (int b = 0; b < KB; ++b) {
-        const int slot = b & 1, s = b % SB;
-        waitb(&a_full[slot], (uint32_t)(b >> 1) & 1u, ok);
+      for (int b = warp == 8 ? 0 : 1; b < KB; b += 2) {
+        const int slot = b % NSLOT, s = b % SB;
+        waitb(&go[slot], (uint32_t)(b / NSLOT) & 1u, ok);
         waitb(&b_full[s], (uint32_t)(b / SB) & 1u, ok);
-        if (b >= 2) waitb(&d_empty[slot], (uint32_t)((b - 2) >> 1) & 1u, ok);
         tc::fence_after_sync();
         const uint64_t bdesc = tc::smem_desc_kmajor(stage0 + (uint32_t)s * STAGE_BYTES, 128, 256);
         tc::mma_i8_ts(tmem_d + (uint32_t)slot * 128, tmem_a + (uint32_t)slot * 8, bdesc, IDESC, 0u);
@@ -157,8 +171,8 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const Prefil
     const uint64_t neg_bias = tc::pack2(-tc::I2F_BIAS, -tc::I2F_BIAS);
 
     auto rescale = [&](int b) {
-      const int slot = b & 1, s = b % SB, ws = (b >> 3) % WB;
-      waitb(&d_full[slot], (uint32_t)(b >> 1) & 1u, ok);
+      const int slot = b % NSLOT, s = b % SB, ws = (b >> 3) % WB;
+      waitb(&d_full[slot], (uint32_t)(b / NSLOT) & 1u, ok);
       tc::fence_after_sync();
       uint32_t d[64];
       const uint32_t dcol = tmem_d + lane_off + (uint32_t)slot * 128 + (uint32_t)wg * 64;
@@ -168,7 +182,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const Prefil
       tc::tmem_ld16(dcol + 48, d + 48);
       tc::tmem_wait_ld();                                  // warp-wide: every lane's accumulator values are in registers
       tc::fence_before_sync();
-      if (lane == 0) tc::mbar_arrive(&d_empty[slot]);      // one arrival per warp: the slot may be overwritten
+      if (lane == 0) tc::mbar_arrive(&go[slot]);           // one arrival per warp: the slot may be overwritten (k-block b + NSLOT)
       const float dw = __half2float(reinterpret_cast<const __half*>(slabS + (size_t)ws * WBATCH_S)[(b & 7) * 128 + r]) * 0.0625f;
       // per pair of outputs: two integer adds (exact int -> float through the magic constant), then three two-wide
       // fp32 ops: subtract the bias, scale dw * dx, fused multiply-add into the accumulators
@@ -192,24 +206,25 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const Prefil
     for (int b = 0; b < KB; ++b) {
       if ((b & 7) == 0) waitb(&w_full[(b >> 3) % WB], (uint32_t)((b >> 3) / WB) & 1u, ok);
       if (wg == 0) {
-        const int ws = (b >> 3) % WB, slot = b & 1;
+        const int ws = (b >> 3) % WB, slot = b % NSLOT;
         const uint4 w = *reinterpret_cast<const uint4*>(slabW + (size_t)ws * WBATCH_W + (size_t)(b & 7) * 2048 + r * 16);
         uint32_t ex[8];
         tc::expand_nibbles(w.x, ex[0], ex[1]);
         tc::expand_nibbles(w.y, ex[2], ex[3]);
         tc::expand_nibbles(w.z, ex[4], ex[5]);
         tc::expand_nibbles(w.w, ex[6], ex[7]);
-        // A slot b & 1 was last read by the MMA of k-block b - 2, whose completion this thread saw in rescale(b - 2)
+        // the A slot was last read by the MMA of k-block b - NSLOT, whose completion this thread saw in rescale(b - NSLOT)
         tc::tmem_st8(tmem_a + lane_off + (uint32_t)slot * 8, ex);
         tc::tmem_wait_st();                                // warp-wide
         tc::fence_before_sync();
-        if (lane == 0) tc::mbar_arrive(&a_full[slot]);
-        if (b >= 1) rescale(b - 1);
+        if (lane == 0) tc::mbar_arrive(&go[slot]);
+        if (b >= NSLOT - 1) rescale(b - (NSLOT - 1));
       } else {
         rescale(b);
       }
     }
-    if (wg == 0) rescale(KB - 1);
+    if (wg == 0)
+      for (int b = max(KB - (NSLOT - 1), 0); b < KB; ++b) rescale(b);
 
     // ---- epilogue: thread (row r, 64 activation rows)
     pdl_wait();                                            // Y / AUX may be written by the previous kernel
