@@ -12,6 +12,7 @@ Fixtures:
   gguf_file.npz    a tiny GGUF file (bytes) -> what the reference's GGUF class parses out of it
   gemv_small.npz   a 64 x 256 GEMV drawn like lab/experiments/gemv5.py:40-46, dequantise-and-dot by reference code
   gemv_ffn_up.npz  the 8960 x 1536 ffn_up GEMV: y from the reference's fp32 dequantise-and-dot, and the float64 oracle
+  q6_k_codec.npz   random Q6_K blocks -> reference q6_k_parts (q, scales, d) and the GGUF.f32 dequantisation
 """
 from __future__ import annotations
 
@@ -107,4 +108,6 @@ def main(ref_root: str) -> None:
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        raise SystemExit("usage: python tests/golden/make_golden.py /path/to/reference")
+    main(sys.argv[1])
