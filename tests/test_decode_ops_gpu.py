@@ -223,3 +223,16 @@ def test_attn_decode_repeatable(K):
     a = _attn_case(K, 2, 12, 2, 128, 2048, [2047, 1000], 11)
     b = _attn_case(K, 2, 12, 2, 128, 2048, [2047, 1000], 11)
     assert np.array_equal(a, b)
+
+
+def test_attn_decode_batched_ragged_positions(K):
+    """32 sequences at different positions (tile and chunk boundaries of the tensor-core kernel: 64-position tiles,
+    chunks of max_len / 8 rounded to tiles), Qwen2.5-1.5B head shape."""
+    positions = [0, 1, 62, 63, 64, 65, 127, 128, 159, 160, 161, 191, 192, 319, 320, 321, 479, 480, 639, 640, 641, 799, 800, 959,
+                 960, 1000, 1023, 1024, 1119, 1120, 1278, 1279]
+    _attn_case(K, 32, 12, 2, 128, 1280, positions, 5)
+
+
+def test_attn_decode_batched_long_context(K):
+    """Chunks of several tiles (max_len 4100 -> 576-position chunks) and a 7-head group."""
+    _attn_case(K, 4, 14, 2, 128, 4100, [4099, 2048, 5, 3000], 9)
