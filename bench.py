@@ -332,16 +332,21 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
     b_down = c.hidden * c.ffn // 32 * 18 + c.ffn * 2 + c.hidden * 8
     b_head = c.head_bytes() + c.hidden * 2 + c.vocab * 4
     gname = "mmq_stream (tcgen05 exact GEMV)" if m.tensor_core else "gemv_q4_0 (CUDA cores)"
+    # last element: dram__bytes_read.sum + dram__bytes_write.sum per launch from the committed ncu capture of these
+    # kernels (profiles/decode_kernels_ncu_full_4layer.md; same shapes, so the traffic per launch is the same)
+    ncu_traffic = {"gu": 15_533_824, "down": 7_800_832, "head": 470_548_224} if m.tensor_core else {}
     kern = {
-        f"{gname} rmsnorm + gate_up 17920x1536 (+swiglu)": (b_gu, us_gu, c.layers),
-        f"{gname} down 1536x8960 (+resid)": (b_down, us_down, c.layers),
-        "head_f16_argmax 151936x1536": (b_head, us_head, 1),
+        f"{gname} rmsnorm + gate_up 17920x1536 (+swiglu)": (b_gu, us_gu, c.layers, ncu_traffic.get("gu")),
+        f"{gname} down 1536x8960 (+resid)": (b_down, us_down, c.layers, ncu_traffic.get("down")),
+        "head_f16_argmax 151936x1536": (b_head, us_head, 1, ncu_traffic.get("head")),
     }
     dominant = max(kern, key=lambda k: kern[k][1] * kern[k][2])
-    b, us, _ = kern[dominant]
+    b, us, _, traffic = kern[dominant]
     ach = b / us / 1e3
     roofline = {"bound": "hbm", "kernel": dominant, "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                "frac": ach / peaks["hbm_gbs"], "peak_kind": f"of {peak_kind}", "traffic": None,
+                "frac": ach / peaks["hbm_gbs"], "peak_kind": f"of {peak_kind}", "traffic": traffic,
+                "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum, one captured launch "
+                                  "(profiles/decode_kernels_ncu_full_4layer.md)" if traffic else None,
                 "bytes_per_launch": b, "us_per_launch": us,
                 "others": {k: {"achieved": v[0] / v[1] / 1e3, "frac": v[0] / v[1] / 1e3 / peaks["hbm_gbs"],
                                "us_per_launch": v[1], "launches_per_step": v[2]} for k, v in kern.items() if k != dominant}}
