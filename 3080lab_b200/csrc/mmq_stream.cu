@@ -443,41 +443,44 @@ __global__ void __launch_bounds__(ROWS * ((MODE == MODE_Q8 && NT >= 16) ? 2 : 1)
 
   // ---- split-K.  Few accumulators per thread: every peer pushes its partial sums into the leader's shared memory
   // (remote stores), one cluster barrier publishes them and the leader adds them in rank order and writes the output.
-  // Many accumulators (16 / 32 activation rows): a reduce-scatter, rank r sums columns r, r + ksplit, ... over all ranks
-  // (in rank order, so the result does not depend on which CTA does it) and writes those columns itself.
+  // Many accumulators (16 / 32 activation rows): a reduce-scatter.  Every CTA parks its partials in its own dead
+  // weight slab; after one cluster barrier rank r sums columns r, r + ksplit, ... over all ranks (in rank order, so
+  // the result does not depend on which CTA does it) and writes those columns itself.  Per thread that is NACC remote
+  // loads spread over the cluster instead of (ksplit - 1) NACC on the leader.
   if (a.ksplit > 1 && !PUSH) {
-    // Column n belongs to rank n % ksplit, as its column number n / ksplit.  Every CTA stores each of its partial sums
-    // straight into the owner's buffer [source rank][own column][row] (remote shared-memory stores, fire and forget),
-    // ONE cluster barrier publishes them, and the owner adds the ranks in order.  Nothing remote is touched after the
-    // barrier, so the CTAs leave independently.  (The earlier pull version needed a second barrier and exposed the
-    // latency of the remote loads: ~3 us per kernel against ~1.5.)
-    const int nownc = (NTOT + a.ksplit - 1) / a.ksplit;   // columns per owner (at most)
-    const uint32_t rb = tc::smem_u32(red_buf);
+    float* part = reinterpret_cast<float*>(slabW);      // [NTOT][128], every thread is past its last slab read
 #pragma unroll
-    for (int n = 0; n < NACC; ++n) {
-      const int col = cbase + n, owner = col % a.ksplit, i = col / a.ksplit;
-      uint32_t remote;
-      asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(rb), "r"(owner));
-      asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote + (uint32_t)(((ks * nownc + i) * ROWS + r) * 4)), "f"(acc[n])
-                   : "memory");
-    }
-    load_addends();                                     // in flight across the barrier
+    for (int n = 0; n < NACC; ++n) part[(cbase + n) * ROWS + r] = acc[n];
     cluster_sync_all();
-    // This CTA owns columns ks, ks + ksplit, ...; its warpgroups take them alternately (own column i = wg + FW ii).
+    load_addends();                                     // in flight together with the remote loads below
+    // This CTA sums columns ks, ks + ksplit, ...; its warpgroups take them alternately.  All remote loads of a thread
+    // are issued before the first add: own column ii (= ks + (wg + FW ii) ksplit), rank rr -> pv[ii ksplit + rr].
+    constexpr int NPV = NTOT / FW + 8;
+    float pv[NPV];
 #pragma unroll
-    for (int ii = 0; ii < NOWN; ++ii) {
-      const int i = wg + FW * ii, n = ks + i * a.ksplit;
-      if (n < NTOT) {                                   // uniform over the warp
-        float pv[8];
+    for (int q = 0; q < NPV; ++q) {
+      const int ii = q / a.ksplit, rr = q - ii * a.ksplit, n = ks + (wg + FW * ii) * a.ksplit;
+      pv[q] = n < NTOT ? ld_peer_f32(part + n * ROWS + r, (uint32_t)rr) : 0.f;
+    }
+    float* fin = reinterpret_cast<float*>(sB);          // [own column][256]: the B operand is dead (all MMAs retired)
+    {
+      float v = 0.f;
 #pragma unroll
-        for (int s2 = 0; s2 < 8; ++s2) pv[s2] = s2 < a.ksplit ? red_buf[(s2 * nownc + i) * ROWS + r] : 0.f;
-        float v = 0.f;
-#pragma unroll
-        for (int s2 = 0; s2 < 8; ++s2)
-          if (s2 < a.ksplit) v += pv[s2];               // rank order 0, 1, ...
-        emit(n, v, addend[ii]);
+      for (int q = 0; q < NPV; ++q) {
+        const int ii = q / a.ksplit, rr = q - ii * a.ksplit;
+        v += pv[q];                                     // rank order 0, 1, ... within a column
+        if (rr == a.ksplit - 1) {
+          if (ii < NOWN) fin[ii * NTHR + t] = v;
+          v = 0.f;
+        }
       }
     }
+#pragma unroll
+    for (int ii = 0; ii < NOWN; ++ii) {
+      const int n = ks + (wg + FW * ii) * a.ksplit;
+      if (n < NTOT) emit(n, fin[ii * NTHR + t], addend[ii]);
+    }
+    cluster_sync_all();                                 // peers stay resident until everyone has read them
     stamp();                                            // split-K reduced
   } else {
     if (a.ksplit > 1) {
@@ -535,7 +538,6 @@ size_t smem_bytes(int gps, int nt, int nacc, int ksplit) {
   s += (size_t)gps * 8 * nt * 32;              // B operand
   s += (size_t)gps * 8 * nt * 4;               // activation block scales (+ the norm reduction scratch)
   if (nacc <= 8) s += (size_t)(ksplit - 1) * nacc * ROWS * 4;   // split-K partials pushed to the leader
-  else if (ksplit > 1) s += (size_t)ksplit * ((nacc + ksplit - 1) / ksplit) * ROWS * 4;   // ... pushed to the column owners
   return s + 128;
 }
 
