@@ -49,6 +49,7 @@ SIGNATURES = {
     "q4b_embed": (_I, [_P, _P, _P, _I, _I, _I, _P]),
     "q4b_attn_decode_workspace": (_Z, [_I, _I, _I, _I]),
     "q4b_attn_decode": (_I, [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _P, _Z, _P]),
+    "q4b_attn_decode_q8_1": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _P]),
     "q4b_head_workspace": (_Z, [_I]),
     "q4b_head_f16_argmax": (_I, [_P, _P, _P, _I, _I, _P, _P, _P, _Z, _P]),
     "q4b_argmax_advance_static": (_I, [_P, _I, _I, _P, _P, _P]),

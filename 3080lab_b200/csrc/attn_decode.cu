@@ -608,7 +608,7 @@ size_t attn_decode_workspace(int B, int NH, int HD, int max_len) {
 }
 
 int attn_decode_mma(const void*, const float*, const float*, const int64_t*, void*, void*, void*, int, int, int, int, float,
-                    cudaStream_t);
+                    cudaStream_t, void* xq = nullptr, void* xd = nullptr);
 
 int attn_decode(const void* qkv, const float* cosT, const float* sinT, const int64_t* pos, void* kc, void* vc, void* out,
                 int B, int NH, int NKV, int HD, int max_len, float scale, void* ws, size_t ws_bytes, cudaStream_t st) {
@@ -648,6 +648,16 @@ int attn_decode(const void* qkv, const float* cosT, const float* sinT, const int
                           NH, NKV, max_len, scale, cnt, ml, po, NC);
   if (rc != Q4B_OK) return fail(rc, "attn_decode: unsupported head group");
   return check_launch("attn_decode");
+}
+
+// Decode attention whose output is also written as planar Q8_1.  Only the multi-sequence tensor-core kernel has the
+// fused quantiser; other cases report Q4B_E_SHAPE and the caller quantises separately.
+int attn_decode_q8(const void* qkv, const float* cosT, const float* sinT, const int64_t* pos, void* kc, void* vc, void* out,
+                   void* xq, void* xd, int B, int NH, int NKV, int HD, int max_len, float scale, cudaStream_t st) {
+  if (B < 2 || HD != 128 || NKV <= 0 || (NH % NKV) || NH / NKV > 8 || max_len <= 0) return Q4B_E_SHAPE;
+  if (!qkv || !cosT || !sinT || !pos || !kc || !vc || !out || !xq || !xd || !aligned16(kc) || !aligned16(vc) || !aligned16(qkv))
+    return fail(Q4B_E_ALIGN, "attn_decode_q8: null or misaligned pointer");
+  return attn_decode_mma(qkv, cosT, sinT, pos, kc, vc, out, B, NH, NKV, max_len, scale, st, xq, xd);
 }
 
 }  // namespace q4b

@@ -53,7 +53,7 @@ constexpr size_t DYN_SMEM = 16 * PITCH + 2 * NSTG * STAGE;     // Q rows, K tile
 __global__ void __launch_bounds__(AT, 4) attn_decode_mma_kernel(const __half* qkv, const float* __restrict__ cosT,
                                                              const float* __restrict__ sinT, const int64_t* posp, __half* kc,
                                                              __half* vc, __half* out, int NH, int NKV, int max_len, int chunk,
-                                                             float scale_log2e, unsigned long long* trace) {
+                                                             float scale_log2e, unsigned long long* trace, int8_t* xq, __half* xd) {
   extern __shared__ __align__(16) uint8_t sm[];
   uint8_t* sQ = sm;                           // [16][PITCH]
   uint8_t* sK = sQ + 16 * PITCH;              // [2][TILE][PITCH]
@@ -308,7 +308,20 @@ __global__ void __launch_bounds__(AT, 4) attn_decode_mma_kernel(const __half* qk
       float ov = 0.f;
 #pragma unroll
       for (int cc = 0; cc < NCL; ++cc) ov += cc < nact ? pv[cc] * wgt[hl][cc] : 0.f;
-      out[(head0 + hl) * HD + d] = __float2half_rn(ov / wgt[hl][NCL]);
+      const __half hv = __float2half_rn(ov / wgt[hl][NCL]);
+      out[(head0 + hl) * HD + d] = hv;
+      if (xq) {
+        // Fused Q8_1 quantiser of the rounded output (arithmetic of quant_q8_1.cu / the reference's QUANT_Q8,
+        // lab/qwen_batched.py:1030-1039).  The host passes xq only when a CTA's share is a whole number of 32-blocks
+        // and at most one per thread, so a warp holds exactly one block of one head here.
+        const float v = __half2float(hv);
+        const float amax = warp_max(fabsf(v));
+        const float dq = amax / 127.f;
+        const int q = dq > 0.f ? __float2int_rn(v / dq) : 0;
+        const size_t col = (head0 + hl) * HD + d;
+        xq[col] = (int8_t)q;
+        if (lane == 0) xd[col >> 5] = __float2half_rn(dq);
+      }
     }
   }
   cluster_sync_all();                                            // peers stay resident until their partials are read
@@ -324,8 +337,12 @@ unsigned long long* g_attn_trace = nullptr;
 void attn_decode_mma_trace(unsigned long long* buf) { g_attn_trace = buf; }
 
 // Same contract as attn_decode (head_dim 128 only); needs no workspace.
+// xq / xd (optional): also write the output as planar Q8_1 (int8 [B, NH*128], fp16 [B, NH*128/32]), saving the separate
+// quantiser launch in front of o_proj; needs (NH / NKV) * 128 to be a multiple of 256 (a CTA's eighth of a KV group is
+// then whole 32-blocks).  Returns Q4B_E_SHAPE without launching when that does not hold.
 int attn_decode_mma(const void* qkv, const float* cosT, const float* sinT, const int64_t* pos, void* kc, void* vc, void* out, int B,
-                    int NH, int NKV, int max_len, float scale, cudaStream_t st) {
+                    int NH, int NKV, int max_len, float scale, cudaStream_t st, void* xq, void* xd) {
+  if (xq && (!xd || ((NH / NKV) * HD) % (NCL * 32) != 0)) return Q4B_E_SHAPE;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(attn_decode_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)DYN_SMEM);
@@ -339,7 +356,7 @@ int attn_decode_mma(const void* qkv, const float* cosT, const float* sinT, const
   const float scale_log2e = scale * 1.4426950408889634f;
   return check_launch(launch_pdl_cluster(attn_decode_mma_kernel, dim3(NCL, NKV, B), dim3(AT), DYN_SMEM, st, NCL, 1,
                                          (const __half*)qkv, cosT, sinT, pos, (__half*)kc, (__half*)vc, (__half*)out, NH, NKV,
-                                         max_len, chunk, scale_log2e, g_attn_trace),
+                                         max_len, chunk, scale_log2e, g_attn_trace, (int8_t*)xq, (__half*)xd),
                       "attn_decode_mma");
 }
 

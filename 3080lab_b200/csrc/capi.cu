@@ -48,6 +48,8 @@ int mmq_stream(const void*, const void*, const void*, const void*, void*, const 
                cudaStream_t, const float* norm_w = nullptr, float eps = 0.f);
 void mmq_stream_trace(unsigned long long*);
 void attn_decode_mma_trace(unsigned long long*);
+int attn_decode_q8(const void*, const float*, const float*, const int64_t*, void*, void*, void*, void*, void*, int, int, int, int, int,
+                   float, cudaStream_t);
 size_t decode_persistent_workspace(const q4b_decode_desc*);
 int decode_persistent_prepare(const q4b_decode_desc*, void*, size_t);
 int decode_persistent_layers(const q4b_decode_desc*, void*, size_t, cudaStream_t);
@@ -104,6 +106,12 @@ int q4b_embed(const void* E, const int64_t* tok, float* h, int rows, int H, int 
 }
 
 size_t q4b_attn_decode_workspace(int B, int NH, int HD, int max_len) { return attn_decode_workspace(B, NH, HD, max_len); }
+
+int q4b_attn_decode_q8_1(const void* qkv, const float* cosT, const float* sinT, const int64_t* pos, void* kc, void* vc,
+                         void* out, void* xq, void* xd, int B, int NH, int NKV, int HD, int max_len, float scale,
+                         q4b_stream_t stream) {
+  return attn_decode_q8(qkv, cosT, sinT, pos, kc, vc, out, xq, xd, B, NH, NKV, HD, max_len, scale, S(stream));
+}
 
 int q4b_attn_decode(const void* qkv, const float* cosT, const float* sinT, const int64_t* pos, void* kc, void* vc,
                     void* out, int B, int NH, int NKV, int HD, int max_len, float scale, void* workspace,

@@ -274,9 +274,11 @@ class Batched:
         for i, L in enumerate(m.L):
             QB.rmsnorm_q8(self.h, L["ln1"], self.xq, self.xd, c.eps)
             self.gemm8(L["qkv"], c.qkv_rows, H, self.qkv, L["qkv_b"], "biasf", c.qkv_rows)
-            K.attn(self.qkv, m.cos, m.sin, self.pos, self.kc[i], self.vc[i], self.att, c.n_heads, c.n_kv_heads, c.head_dim,
-                   m.max_len, m.scale, self.attn_ws)
-            QB.quant_q8(self.att, self.xq, self.xd)
+            if not K.attn_q8(self.qkv, m.cos, m.sin, self.pos, self.kc[i], self.vc[i], self.att, self.xq, self.xd, c.n_heads,
+                             c.n_kv_heads, c.head_dim, m.max_len, m.scale):
+                K.attn(self.qkv, m.cos, m.sin, self.pos, self.kc[i], self.vc[i], self.att, c.n_heads, c.n_kv_heads,
+                       c.head_dim, m.max_len, m.scale, self.attn_ws)
+                QB.quant_q8(self.att, self.xq, self.xd)
             self.gemm8(L["o"], H, c.q_rows, self.h, None, "resid", H)
             QB.rmsnorm_q8(self.h, L["ln2"], self.xq, self.xd, c.eps)
             self.gemm8(L["gu"], 2 * c.ffn, H, self.xm, None, "swiglu", c.ffn)

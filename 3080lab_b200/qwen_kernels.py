@@ -62,6 +62,18 @@ def attn(qkv, cosT, sinT, pos, kc, vc, out, NH: int, NKV: int, HD: int, max_len:
               max_len, float(scale), _p(ws), ws.numel(), _stream())
 
 
+def attn_q8(qkv, cosT, sinT, pos, kc, vc, out, xq, xd, NH: int, NKV: int, HD: int, max_len: int, scale: float) -> bool:
+    """The same attention with the Q8_1 quantiser of its output fused in (xq int8, xd fp16 as `quant_q8` would write
+    them).  Returns False without launching when the shape has no fused kernel; the caller then uses `attn` and the
+    quantiser."""
+    rc = _ffi.lib().q4b_attn_decode_q8_1(_p(qkv), _p(cosT), _p(sinT), _p(pos), _p(kc), _p(vc), _p(out), _p(xq), _p(xd),
+                                         pos.numel(), NH, NKV, HD, max_len, float(scale), _stream())
+    if rc == _ffi.E_SHAPE:
+        return False
+    _ffi.check(rc)
+    return True
+
+
 def head_workspace(V: int, rows: int, device) -> torch.Tensor:
     L = _ffi.lib()
     n = max(L.q4b_head_workspace(V), L.q4b_argmax_workspace(rows, V))

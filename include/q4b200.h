@@ -87,6 +87,14 @@ int q4b_attn_decode(const void* qkv, const float* cosT, const float* sinT, const
                     void* out, int B, int NH, int NKV, int HD, int max_len, float scale, void* workspace,
                     size_t workspace_bytes, q4b_stream_t stream);
 
+/* The same attention with the Q8_1 quantiser of its output fused in: besides `out` it writes xq int8 [B, NH*HD] and
+ * xd fp16 [B, NH*HD/32], exactly what q4b_quant_q8_1(out, ...) would produce, so the quantiser launch in front of
+ * o_proj (QUANT_Q8, lab/qwen_batched.py:1016-1041) disappears.  Only for B >= 2, head_dim 128 and (NH / NKV) * 128 a
+ * multiple of 256; otherwise it returns Q4B_E_SHAPE without launching and the caller uses the two separate calls. */
+int q4b_attn_decode_q8_1(const void* qkv, const float* cosT, const float* sinT, const int64_t* pos, void* kc, void* vc,
+                         void* out, void* xq, void* xd, int B, int NH, int NKV, int HD, int max_len, float scale,
+                         q4b_stream_t stream);
+
 /* LM head for a tied fp16 embedding table with the greedy pick fused: logits fp32 [V] = E fp16 [V, H] . x fp16 [H];
  * tok[0] = lowest index among the maxima; pos[0] += 1.  Replaces gemv_source(..., "logits") + FINISH_MB
  * (lab/qwen_kernels.py:14-113, 250-282; host scripts/qwen_fused.py:133-142).  tok/pos may be null (logits only).
