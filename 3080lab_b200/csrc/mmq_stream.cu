@@ -504,7 +504,33 @@ __global__ void __launch_bounds__(ROWS * ((MODE == MODE_Q8 && NT >= 16) ? 2 : 1)
       }
     }
     stamp();                                            // split-K reduced
-    if (ks == 0) {
+    if (ks == 0 && a.epi == Q4B_EPI_SWIGLU_Q8) {
+      // SwiGLU product rounded to fp16, then the Q8_1 quantiser of quant_q8_1.cu on it (reference QUANT_Q8,
+      // lab/qwen_batched.py:1030-1039): a 32-block of the product is 64 weight rows = two warps of this tile.
+      float* wmax = xs;                                 // [column][TMEM lane quarter]; the activation scales are dead
+      float act[NACC];
+#pragma unroll
+      for (int n = 0; n < NACC; ++n) {
+        const float v = acc[n];
+        const float partner = __shfl_xor_sync(0xffffffffu, v, 1);
+        const bool live = (r & 1) == 0 && row < a.N && cbase + n < a.cols;
+        act[n] = live ? __half2float(__float2half_rn(v / (1.f + __expf(-v)) * partner)) : 0.f;
+        const float m = warp_max(fabsf(act[n]));
+        if (lane == 0) wmax[(cbase + n) * 4 + wq] = m;
+      }
+      __syncthreads();
+      int8_t* qo = reinterpret_cast<int8_t*>(a.Y);
+      __half* dout = reinterpret_cast<__half*>(const_cast<void*>(a.AUX));
+#pragma unroll
+      for (int n = 0; n < NACC; ++n) {
+        const int col = cbase + n;
+        const float amax = fmaxf(wmax[col * 4 + wq], wmax[col * 4 + (wq ^ 1)]);
+        const float dq = amax / 127.f;
+        const int q = dq > 0.f ? __float2int_rn(act[n] / dq) : 0;
+        if ((r & 1) == 0 && row < a.N && col < a.cols) qo[(size_t)col * a.ldy + (row >> 1)] = (int8_t)q;
+        if ((wq & 1) == 0 && lane == 0 && row < a.N && col < a.cols) dout[(size_t)col * (a.ldy >> 5) + (row >> 6)] = __float2half_rn(dq);
+      }
+    } else if (ks == 0) {
 #pragma unroll
       for (int n = 0; n < NACC; ++n) {
         float add = PUSH ? addend[n < NOWN ? n : 0] : 0.f;
@@ -659,7 +685,9 @@ int mmq_stream(const void* W, const void* S, const void* X, const void* XD, void
   if (N <= 0 || K <= 0 || (K % 256)) return fail(Q4B_E_SHAPE, "mmq_stream: N > 0 and K a positive multiple of 256 required");
   if (mode < 0 || mode > 3) return fail(Q4B_E_ARG, "mmq_stream: unknown mode");
   if (mode == MODE_NORM && (!norm_w || !aligned16(norm_w))) return fail(Q4B_E_ALIGN, "mmq_stream: norm mode needs 16-byte aligned weights");
-  if (epilogue < Q4B_EPI_STORE || epilogue > Q4B_EPI_LOGITS) return fail(Q4B_E_ARG, "mmq_stream: unknown epilogue");
+  if (epilogue < Q4B_EPI_STORE || epilogue > Q4B_EPI_SWIGLU_Q8) return fail(Q4B_E_ARG, "mmq_stream: unknown epilogue");
+  if (epilogue == Q4B_EPI_SWIGLU_Q8 && (mode != MODE_Q8 || (N % 64) || !AUX))
+    return fail(Q4B_E_SHAPE, "mmq_stream: swiglu_q8 needs Q8_1 mode, N a multiple of 64 and the scale output");
   if (cols < 1 || cols > 32 || (mode != MODE_Q8 && cols != 1)) return fail(Q4B_E_SHAPE, "mmq_stream: 1..32 columns (1 in exact mode)");
   if (epilogue == Q4B_EPI_SWIGLU && (N % 2)) return fail(Q4B_E_SHAPE, "mmq_stream: swiglu needs an even row count");
   if (!W || !S || !X || !Y || !status || !aligned16(W) || !aligned16(S) || !aligned16(X))
@@ -686,6 +714,8 @@ int mmq_stream(const void* W, const void* S, const void* X, const void* XD, void
     }
     return fail(Q4B_E_SHAPE, "mmq_stream: no K split fits shared memory for this K");
   }
+  if (epilogue == Q4B_EPI_SWIGLU_Q8 && g.ksplit > 1 && nt > 8)
+    return fail(Q4B_E_SHAPE, "mmq_stream: swiglu_q8 has no split-K form for more than 8 activation rows");
   StreamArgs a;
   a.W = reinterpret_cast<const uint8_t*>(W);
   a.S = reinterpret_cast<const __half*>(S);

@@ -253,6 +253,11 @@ class Batched:
         kmax = max(c.hidden, c.q_rows, c.ffn)
         self.xq = torch.zeros(B * kmax, dtype=torch.int8, device=dv)
         self.xd = torch.zeros(B * kmax // 32, dtype=f16, device=dv)
+        self.xq2 = torch.zeros(B * c.ffn, dtype=torch.int8, device=dv)       # Q8_1 SwiGLU product written by gate/up
+        self.xd2 = torch.zeros(B * c.ffn // 32, dtype=f16, device=dv)
+        # fused SwiGLU + quantiser epilogue: measured +0.7 % at 8 sequences and -5 % at 32 (16 columns per thread to reduce
+        # and quantise), so it is tried only for up to 8 sequences; None = decided by the first step
+        self._fuse_gu = None if B <= 8 else False
         self.logits = torch.zeros(B, c.vocab, dtype=f32, device=dv)
         self.tok = torch.zeros(B, dtype=torch.long, device=dv)
         self.pos = torch.zeros(B, dtype=torch.long, device=dv)
@@ -263,9 +268,10 @@ class Batched:
         self.status = QB.Status(dv)
         self.launches_per_step = 1 + 9 * c.layers + 3
 
-    def gemm8(self, pair, N, Kdim, Y, aux, epi, ldy):
+    def gemm8(self, pair, N, Kdim, Y, aux, epi, ldy, xq=None, xd=None):
         Wt, St = self.m.packed[id(pair[0])]
-        QB.gemm8(Wt, St, self.xq, self.xd, Y, aux, N, Kdim, self.B, epi, ldy, self.status)
+        QB.gemm8(Wt, St, self.xq if xq is None else xq, self.xd if xd is None else xd, Y, aux, N, Kdim, self.B, epi, ldy,
+                 self.status)
 
     def step(self) -> None:
         m, c, B = self.m, self.m.cfg, self.B
@@ -281,9 +287,21 @@ class Batched:
                 QB.quant_q8(self.att, self.xq, self.xd)
             self.gemm8(L["o"], H, c.q_rows, self.h, None, "resid", H)
             QB.rmsnorm_q8(self.h, L["ln2"], self.xq, self.xd, c.eps)
-            self.gemm8(L["gu"], 2 * c.ffn, H, self.xm, None, "swiglu", c.ffn)
-            QB.quant_q8(self.xm, self.xq, self.xd)
-            self.gemm8(L["down"], H, c.ffn, self.h, None, "resid", H)
+            if self._fuse_gu is not False:
+                # SwiGLU product quantised in the gate/up epilogue (second buffer pair: xq / xd are this GEMM's input)
+                try:
+                    self.gemm8(L["gu"], 2 * c.ffn, H, self.xq2, self.xd2, "swiglu_q8", c.ffn)
+                    self._fuse_gu = True
+                except _ffi.Q4BError as e:
+                    if e.code != _ffi.E_SHAPE or self._fuse_gu:
+                        raise
+                    self._fuse_gu = False                  # no fused form for this shape: separate quantiser from now on
+            if self._fuse_gu:
+                self.gemm8(L["down"], H, c.ffn, self.h, None, "resid", H, self.xq2, self.xd2)
+            else:
+                self.gemm8(L["gu"], 2 * c.ffn, H, self.xm, None, "swiglu", c.ffn)
+                QB.quant_q8(self.xm, self.xq, self.xd)
+                self.gemm8(L["down"], H, c.ffn, self.h, None, "resid", H)
         if m.head is None:
             K.rms(self.h, m.norm, self.x, c.eps)
             QB.head_batched(m.head16, self.x, self.logits)

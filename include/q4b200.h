@@ -48,6 +48,8 @@ extern "C" {
 #define Q4B_EPI_RESID 2   /* Y fp32 [N]       += acc */
 #define Q4B_EPI_SWIGLU 3  /* Y fp16 [N/2]      = silu(acc[2o]) * acc[2o+1]  (rows interleaved gate, up) */
 #define Q4B_EPI_LOGITS 4  /* Y fp32 [N]        = acc */
+#define Q4B_EPI_SWIGLU_Q8 5 /* Q8_1 MMQ only: the SwiGLU product rounded to fp16 and quantised in the epilogue:
+                               Y int8 [cols, N/2], AUX (written) fp16 [cols, N/64]; N a multiple of 64 */
 
 #define Q4B_X_F16 0
 #define Q4B_X_F32 1
