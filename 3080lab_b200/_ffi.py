@@ -11,7 +11,7 @@ from pathlib import Path
 LIB_PATH = Path(__file__).resolve().parent / "libq4b200.so"
 
 OK, E_SHAPE, E_ALIGN, E_WORKSPACE, E_CUDA, E_ARG, E_TIMEOUT = 0, -1, -2, -3, -4, -5, -6
-EPI = {"store": 0, "biasf": 1, "resid": 2, "swiglu": 3, "logits": 4, "swiglu_q8": 5}
+EPI = {"store": 0, "biasf": 1, "resid": 2, "swiglu": 3, "logits": 4, "swiglu_q8": 5, "biasf_rope_kv": 6}
 X_F16, X_F32 = 0, 1
 
 _P, _I, _F, _Z = C.c_void_p, C.c_int, C.c_float, C.c_size_t
@@ -37,6 +37,7 @@ class DecodeDesc(C.Structure):
 
 STEP_TENSOR_CORE = 1
 STEP_PERSISTENT = 2
+STEP_MMA_GEMV = 4
 
 
 # name -> (restype, argtypes); every symbol include/q4b200.h declares
@@ -58,6 +59,11 @@ SIGNATURES = {
     "q4b_argmax_advance": (_I, [_P, _I, _I, _P, _P, _P, _Z, _P]),
     "q4b_blockdot_q4_0_q8_1": (_I, [_P, _P, _P, _I, _I, _I, _I, _P, _P]),
     "q4b_gemv_q4_0_tc": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _P, _P]),
+    "q4b_gemv_q4_0_mma": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _P, _P]),
+    "q4b_rmsnorm_gemv_q4_0_mma": (_I, [_P, _P, _P, _P, _F, _P, _P, _I, _I, _I, _P, _P]),
+    "q4b_rmsnorm_qkv_rope_kv": (_I, [_P, _P, _P, _P, _F, _P, _P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P, _P]),
+    "q4b_debug_gemv_mma_expired_wait": (_I, [_P, _P, _P, _P, _I, _I, _P, _P]),
+    "q4b_attn_decode_cached": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _F, _P]),
     "q4b_pack_q4_0": (_I, [_P, _P, _P, _P, _I, _I, _P]),
     "q4b_q8_tiled_bytes": (_Z, [_I, _I]),
     "q4b_quant_q8_1_tiled": (_I, [_P, _P, _I, _I, _P]),

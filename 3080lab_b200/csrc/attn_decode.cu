@@ -277,7 +277,9 @@ template <int HD, int HSUB, int PASSES>
 __global__ void __launch_bounds__(AT) attn_decode_cluster_kernel(const __half* qkv, const float* __restrict__ cosT,
                                                                  const float* __restrict__ sinT, const int64_t* posp,
                                                                  __half* kc, __half* vc, __half* out, int NH, int NKV, int GRP,
-                                                                 int nsub, int max_len, float scale) {
+                                                                 int nsub, int max_len, float scale, int pre) {
+  // pre != 0: the producer of `qkv` already rotated q and appended the rotated k / raw v at pos (the fused epilogue of
+  // the QKV projection), so this kernel only reads: no tables, no writer, position pos comes from the cache like the rest
   constexpr int HALF = HD / 2;
   constexpr int LPR = HD / 8;          // lanes per K/V row in the P.V pass (16-byte loads)
   constexpr int PPI = 32 / LPR;        // rows per warp iteration
@@ -334,7 +336,7 @@ __global__ void __launch_bounds__(AT) attn_decode_cluster_kernel(const __half* q
   const size_t head0 = (size_t)b * NH + (size_t)kvh * GRP + h0;
 
   if (active) {
-    const bool has_new = p < c0 + CHK;
+    const bool has_new = !pre && p < c0 + CHK;
     const int QKV = (NH + 2 * NKV) * HD;
     const __half* row = qkv + (size_t)b * QKV;
     const float* cs = cosT + (size_t)p * HALF;
@@ -344,8 +346,13 @@ __global__ void __launch_bounds__(AT) attn_decode_cluster_kernel(const __half* q
       float r = 0.f;
       if (hl < nh) {
         const __half* qh = row + (size_t)(kvh * GRP + h0 + hl) * HD;
-        const float a = __half2float(qh[d]), o = __half2float(qh[d < HALF ? d + HALF : d - HALF]);
-        r = d < HALF ? a * cs[dd] - o * sn[dd] : a * cs[dd] + o * sn[dd];
+        const float a = __half2float(qh[d]);
+        if (pre) {
+          r = a;
+        } else {
+          const float o = __half2float(qh[d < HALF ? d + HALF : d - HALF]);
+          r = d < HALF ? a * cs[dd] - o * sn[dd] : a * cs[dd] + o * sn[dd];
+        }
       }
       qs[hl][d] = __half2float(__float2half_rn(r));
     }
@@ -374,7 +381,7 @@ __global__ void __launch_bounds__(AT) attn_decode_cluster_kernel(const __half* q
       const bool valid = j <= p;
 #pragma unroll
       for (int h = 0; h < HSUB; ++h) s[ps][h] = 0.f;
-      if (j == p) {
+      if (!pre && j == p) {
 #pragma unroll 4
         for (int d = 0; d < HD; ++d) {
           const float k = kn[d];
@@ -450,7 +457,7 @@ __global__ void __launch_bounds__(AT) attn_decode_cluster_kernel(const __half* q
             vv[u] = vpre[it0 + u];
           } else {
             vv[u] = make_uint4(0u, 0u, 0u, 0u);
-            if (j < p) vv[u] = *reinterpret_cast<const uint4*>(vbase + (size_t)j * HD + d0);
+            if (j < p || (pre && j == p)) vv[u] = *reinterpret_cast<const uint4*>(vbase + (size_t)j * HD + d0);
           }
         }
 #pragma unroll
@@ -458,7 +465,7 @@ __global__ void __launch_bounds__(AT) attn_decode_cluster_kernel(const __half* q
           const int jl = 128 * ps + 32 * warp + (it0 + u) * PPI + psub, j = c0 + jl;
           if (j > p) continue;
           float vf[8];
-          if (j == p) {
+          if (!pre && j == p) {
 #pragma unroll
             for (int k = 0; k < 8; ++k) vf[k] = vn[d0 + k];
           } else {
@@ -554,29 +561,29 @@ __global__ void __launch_bounds__(AT) attn_decode_cluster_kernel(const __half* q
 template <int HD, int HSUB>
 int launch_cluster_passes(int passes, dim3 grid, cudaStream_t st, const __half* qkv, const float* cosT, const float* sinT,
                           const int64_t* pos, __half* kc, __half* vc, __half* out, int NH, int NKV, int GRP, int nsub,
-                          int max_len, float scale) {
+                          int max_len, float scale, int pre) {
   cudaError_t e;
   if (passes == 1)
     e = launch_pdl_cluster(attn_decode_cluster_kernel<HD, HSUB, 1>, grid, dim3(AT), 0, st, NCL, 1, qkv, cosT, sinT, pos, kc, vc,
-                           out, NH, NKV, GRP, nsub, max_len, scale);
+                           out, NH, NKV, GRP, nsub, max_len, scale, pre);
   else if (passes == 2)
     e = launch_pdl_cluster(attn_decode_cluster_kernel<HD, HSUB, 2>, grid, dim3(AT), 0, st, NCL, 1, qkv, cosT, sinT, pos, kc, vc,
-                           out, NH, NKV, GRP, nsub, max_len, scale);
+                           out, NH, NKV, GRP, nsub, max_len, scale, pre);
   else
     e = launch_pdl_cluster(attn_decode_cluster_kernel<HD, HSUB, 4>, grid, dim3(AT), 0, st, NCL, 1, qkv, cosT, sinT, pos, kc, vc,
-                           out, NH, NKV, GRP, nsub, max_len, scale);
+                           out, NH, NKV, GRP, nsub, max_len, scale, pre);
   return check_launch(e, "attn_decode");
 }
 
 template <int HD>
 int launch_cluster(int hsub, int passes, dim3 grid, cudaStream_t st, const __half* qkv, const float* cosT, const float* sinT,
                    const int64_t* pos, __half* kc, __half* vc, __half* out, int NH, int NKV, int GRP, int nsub, int max_len,
-                   float scale) {
+                   float scale, int pre) {
   switch (hsub) {
-    case 1: return launch_cluster_passes<HD, 1>(passes, grid, st, qkv, cosT, sinT, pos, kc, vc, out, NH, NKV, GRP, nsub, max_len, scale);
-    case 2: return launch_cluster_passes<HD, 2>(passes, grid, st, qkv, cosT, sinT, pos, kc, vc, out, NH, NKV, GRP, nsub, max_len, scale);
-    case 3: return launch_cluster_passes<HD, 3>(passes, grid, st, qkv, cosT, sinT, pos, kc, vc, out, NH, NKV, GRP, nsub, max_len, scale);
-    default: return launch_cluster_passes<HD, 4>(passes, grid, st, qkv, cosT, sinT, pos, kc, vc, out, NH, NKV, GRP, nsub, max_len, scale);
+    case 1: return launch_cluster_passes<HD, 1>(passes, grid, st, qkv, cosT, sinT, pos, kc, vc, out, NH, NKV, GRP, nsub, max_len, scale, pre);
+    case 2: return launch_cluster_passes<HD, 2>(passes, grid, st, qkv, cosT, sinT, pos, kc, vc, out, NH, NKV, GRP, nsub, max_len, scale, pre);
+    case 3: return launch_cluster_passes<HD, 3>(passes, grid, st, qkv, cosT, sinT, pos, kc, vc, out, NH, NKV, GRP, nsub, max_len, scale, pre);
+    default: return launch_cluster_passes<HD, 4>(passes, grid, st, qkv, cosT, sinT, pos, kc, vc, out, NH, NKV, GRP, nsub, max_len, scale, pre);
   }
 }
 
@@ -610,8 +617,25 @@ size_t attn_decode_workspace(int B, int NH, int HD, int max_len) {
 int attn_decode_mma(const void*, const float*, const float*, const int64_t*, void*, void*, void*, int, int, int, int, float,
                     cudaStream_t, void* xq = nullptr, void* xd = nullptr);
 
+// pre != 0 (one sequence, max_len <= 4096 only): q arrives rotated and position pos is already in the cache (the fused
+// epilogue of the QKV projection did both); cosT / sinT / ws may then be null.
 int attn_decode(const void* qkv, const float* cosT, const float* sinT, const int64_t* pos, void* kc, void* vc, void* out,
-                int B, int NH, int NKV, int HD, int max_len, float scale, void* ws, size_t ws_bytes, cudaStream_t st) {
+                int B, int NH, int NKV, int HD, int max_len, float scale, void* ws, size_t ws_bytes, cudaStream_t st, int pre) {
+  if (pre) {
+    if (B != 1 || max_len > NCL * 128 * 4) return fail(Q4B_E_SHAPE, "attn_decode: the cached form serves one sequence with max_len <= 4096");
+    if (NH <= 0 || NKV <= 0 || max_len <= 0 || (NH % NKV) || NH / NKV > 8 || (HD != 64 && HD != 128))
+      return fail(Q4B_E_SHAPE, "attn_decode: need HD in {64,128}, NH a multiple of NKV, NH/NKV <= 8");
+    if (!qkv || !pos || !kc || !vc || !out || !aligned16(kc) || !aligned16(vc)) return fail(Q4B_E_ALIGN, "attn_decode: null or misaligned pointer");
+    static const int hsub_for[9] = {1, 1, 2, 3, 2, 3, 2, 4, 4};
+    const int GRP = NH / NKV, hsub = hsub_for[GRP], nsub = (GRP + hsub - 1) / hsub;
+    const int passes = max_len <= NCL * 128 ? 1 : (max_len <= NCL * 256 ? 2 : 4);
+    dim3 grid(NCL, NKV * nsub, 1);
+    if (HD == 128)
+      return launch_cluster<128>(hsub, passes, grid, st, (const __half*)qkv, cosT, sinT, pos, (__half*)kc, (__half*)vc,
+                                 (__half*)out, NH, NKV, GRP, nsub, max_len, scale, 1);
+    return launch_cluster<64>(hsub, passes, grid, st, (const __half*)qkv, cosT, sinT, pos, (__half*)kc, (__half*)vc,
+                              (__half*)out, NH, NKV, GRP, nsub, max_len, scale, 1);
+  }
   if (B <= 0 || NH <= 0 || NKV <= 0 || max_len <= 0 || (NH % NKV) || NH / NKV > 8 || (HD != 64 && HD != 128))
     return fail(Q4B_E_SHAPE, "attn_decode: need HD in {64,128}, NH a multiple of NKV, NH/NKV <= 8");
   if (!qkv || !cosT || !sinT || !pos || !kc || !vc || !out || !ws || !aligned16(kc) || !aligned16(vc) || !aligned16(ws))
@@ -629,9 +653,9 @@ int attn_decode(const void* qkv, const float* cosT, const float* sinT, const int
     dim3 grid(NCL, NKV * nsub, B);
     if (HD == 128)
       return launch_cluster<128>(hsub, passes, grid, st, (const __half*)qkv, cosT, sinT, pos, (__half*)kc, (__half*)vc,
-                                 (__half*)out, NH, NKV, GRP, nsub, max_len, scale);
+                                 (__half*)out, NH, NKV, GRP, nsub, max_len, scale, 0);
     return launch_cluster<64>(hsub, passes, grid, st, (const __half*)qkv, cosT, sinT, pos, (__half*)kc, (__half*)vc,
-                              (__half*)out, NH, NKV, GRP, nsub, max_len, scale);
+                              (__half*)out, NH, NKV, GRP, nsub, max_len, scale, 0);
   }
   const int NC = (max_len + CH - 1) / CH;
   char* base = reinterpret_cast<char*>(ws);

@@ -39,7 +39,13 @@ int argmax_advance(const float*, int, int, int64_t*, int64_t*, void*, size_t, cu
 int argmax_advance_static(const float*, int, int, int64_t*, int64_t*, cudaStream_t);
 size_t attn_decode_workspace(int, int, int, int);
 int attn_decode(const void*, const float*, const float*, const int64_t*, void*, void*, void*, int, int, int, int, int, float,
-                void*, size_t, cudaStream_t);
+                void*, size_t, cudaStream_t, int pre = 0);
+int gemv_mma(const void*, const void*, const void*, void*, const void*, int, int, int, int, uint32_t*, cudaStream_t,
+             const float* norm_w = nullptr, float eps = 0.f, const float* cosT = nullptr, const float* sinT = nullptr,
+             const int64_t* pos = nullptr, void* kc = nullptr, void* vc = nullptr, int NH = 0, int NKV = 0, int HD = 0,
+             int max_len = 0, int withhold_chunk = -1);
+int gemv_mma_ksplit(int, int);
+void gemv_mma_trace(unsigned long long*);
 size_t head_workspace(int);
 int head_f16_argmax(const void*, const void*, float*, int, int, int64_t*, int64_t*, void*, size_t, cudaStream_t);
 int head_f16_batched(const void*, const void*, float*, int, int, int, cudaStream_t);
@@ -153,6 +159,38 @@ int q4b_gemv_q4_0_tc(const void* W, const void* Sc, const void* X, void* Y, cons
   return mmq_stream(W, Sc, X, nullptr, Y, AUX, N, K, 1, x_dtype == Q4B_X_F16 ? 0 : 1, epilogue, ldy, status, S(stream));
 }
 
+int q4b_gemv_q4_0_mma(const void* W, const void* Sc, const void* X, void* Y, const void* AUX, int N, int K, int epilogue,
+                      int x_dtype, uint32_t* status, q4b_stream_t stream) {
+  if (x_dtype != Q4B_X_F16 && x_dtype != Q4B_X_F32) return fail(Q4B_E_ARG, "gemv_q4_0_mma: unknown x_dtype");
+  if (epilogue == Q4B_EPI_BIASF_ROPE_KV) return fail(Q4B_E_ARG, "gemv_q4_0_mma: use q4b_rmsnorm_qkv_rope_kv for the fused RoPE epilogue");
+  return gemv_mma(W, Sc, X, Y, AUX, N, K, x_dtype == Q4B_X_F16 ? 0 : 1, epilogue, status, S(stream));
+}
+
+int q4b_rmsnorm_gemv_q4_0_mma(const void* W, const void* Sc, const float* h, const float* norm_w, float eps, void* Y,
+                              const void* AUX, int N, int K, int epilogue, uint32_t* status, q4b_stream_t stream) {
+  if (epilogue == Q4B_EPI_BIASF_ROPE_KV) return fail(Q4B_E_ARG, "rmsnorm_gemv_q4_0_mma: use q4b_rmsnorm_qkv_rope_kv for the fused RoPE epilogue");
+  return gemv_mma(W, Sc, h, Y, AUX, N, K, 3, epilogue, status, S(stream), norm_w, eps);
+}
+
+int q4b_rmsnorm_qkv_rope_kv(const void* W, const void* Sc, const float* h, const float* norm_w, float eps, void* qkv,
+                            const float* bias, int K, const float* cosT, const float* sinT, const int64_t* pos, void* kc,
+                            void* vc, int NH, int NKV, int HD, int max_len, uint32_t* status, q4b_stream_t stream) {
+  return gemv_mma(W, Sc, h, qkv, bias, (NH + 2 * NKV) * HD, K, 3, Q4B_EPI_BIASF_ROPE_KV, status, S(stream), norm_w, eps, cosT,
+                  sinT, pos, kc, vc, NH, NKV, HD, max_len);
+}
+
+int q4b_debug_gemv_mma_expired_wait(const void* W, const void* Sc, const void* X, void* Y, int N, int K, uint32_t* status,
+                                    q4b_stream_t stream) {
+  return gemv_mma(W, Sc, X, Y, nullptr, N, K, 0, Q4B_EPI_LOGITS, status, S(stream), nullptr, 0.f, nullptr, nullptr, nullptr,
+                  nullptr, nullptr, 0, 0, 0, 0, 0);
+}
+
+int q4b_attn_decode_cached(const void* qkv, const int64_t* pos, const void* kc, const void* vc, void* out, int NH, int NKV,
+                           int HD, int max_len, float scale, q4b_stream_t stream) {
+  return attn_decode(qkv, nullptr, nullptr, pos, const_cast<void*>(kc), const_cast<void*>(vc), out, 1, NH, NKV, HD, max_len,
+                     scale, nullptr, 0, S(stream), 1);
+}
+
 int q4b_pack_q4_0(const void* W, const void* Sc, void* Wt, void* St, int N, int K, q4b_stream_t stream) {
   return pack_q4_0(W, Sc, Wt, St, N, K, S(stream));
 }
@@ -180,6 +218,7 @@ int q4b_attn_prefill(const void* qkv, const float* cosT, const float* sinT, void
 int q4b_trace_buffer(uint64_t* device_buffer, size_t entries) {
   if (device_buffer && entries < (size_t)4096 * 16) return fail(Q4B_E_WORKSPACE, "trace_buffer: need 4096 x 16 entries");
   mmq_stream_trace(reinterpret_cast<unsigned long long*>(device_buffer));
+  gemv_mma_trace(reinterpret_cast<unsigned long long*>(device_buffer));
   attn_decode_mma_trace(reinterpret_cast<unsigned long long*>(device_buffer));
   return Q4B_OK;
 }
@@ -210,14 +249,21 @@ int q4b_decode_step(const q4b_decode_desc* d, q4b_stream_t stream) {
   cudaStream_t st = S(stream);
   const int H = d->hidden, QR = d->n_heads * d->head_dim;
   const bool tcp = (d->flags & Q4B_STEP_TENSOR_CORE) && d->status;
-  // one linear: tensor-core kernel when its shape allows, the CUDA-core GEMV otherwise
+  const bool mmap = (d->flags & Q4B_STEP_MMA_GEMV) && d->status;
+  auto mma_ok = [&](const q4b_linear& L) { return mmap && L.Wt && (L.K % 32) == 0 && gemv_mma_ksplit(L.N, L.K) > 0; };
+  // the QKV projection can rotate q / k and append k, v itself when one 128-row tile holds whole heads
+  const bool fused_kv = mmap && d->head_dim > 0 && (128 % d->head_dim) == 0 && d->max_len <= 4096 &&
+                        d->n_heads % d->n_kv_heads == 0 && d->n_heads / d->n_kv_heads <= 8 && (d->head_dim == 64 || d->head_dim == 128);
+  // one linear: the mma.sync streaming GEMV or the tcgen05 kernel when its shape allows, the CUDA-core GEMV otherwise
   auto lin = [&](const q4b_linear& L, const void* X, void* Y, const void* AUX, int epi) -> int {
+    if (mma_ok(L)) return gemv_mma(L.Wt, L.St, X, Y, AUX, L.N, L.K, 0, epi, d->status, st);
     if (tcp && L.Wt && (L.K % 256) == 0)
       return mmq_stream(L.Wt, L.St, X, nullptr, Y, AUX, L.N, L.K, 1, 0, epi, epi == Q4B_EPI_SWIGLU ? L.N / 2 : L.N, d->status, st);
     return gemv_q4_0(L.W, L.S, X, Y, AUX, L.N, L.K, epi, Q4B_X_F16, st);
   };
   // RMSNorm followed by a linear: one launch on the tensor-core path (the norm is computed while staging the operand)
   auto norm_lin = [&](const float* nw, const q4b_linear& L, void* Y, const void* AUX, int epi) -> int {
+    if (mma_ok(L)) return gemv_mma(L.Wt, L.St, d->h, Y, AUX, L.N, L.K, 3, epi, d->status, st, nw, d->eps);
     if (tcp && L.Wt && (L.K % 256) == 0)
       return mmq_stream(L.Wt, L.St, d->h, nullptr, Y, AUX, L.N, L.K, 1, 3, epi, epi == Q4B_EPI_SWIGLU ? L.N / 2 : L.N, d->status,
                         st, nw, d->eps);
@@ -234,9 +280,16 @@ int q4b_decode_step(const q4b_decode_desc* d, q4b_stream_t stream) {
   if (persistent) Q4B_TRY(decode_persistent_layers(d, d->persistent_ws, d->persistent_ws_bytes, st));
   for (int i = 0; i < d->layers && !persistent; ++i) {
     const q4b_layer& L = d->layer[i];
-    Q4B_TRY(norm_lin(L.ln1, L.qkv, d->qkv, L.qkv_bias, Q4B_EPI_BIASF));
-    Q4B_TRY(attn_decode(d->qkv, d->cosT, d->sinT, d->pos, L.kc, L.vc, d->att, 1, d->n_heads, d->n_kv_heads, d->head_dim,
-                        d->max_len, d->scale, d->attn_ws, d->attn_ws_bytes, st));
+    if (fused_kv && mma_ok(L.qkv)) {
+      Q4B_TRY(gemv_mma(L.qkv.Wt, L.qkv.St, d->h, d->qkv, L.qkv_bias, L.qkv.N, L.qkv.K, 3, Q4B_EPI_BIASF_ROPE_KV, d->status, st, L.ln1,
+                       d->eps, d->cosT, d->sinT, d->pos, L.kc, L.vc, d->n_heads, d->n_kv_heads, d->head_dim, d->max_len));
+      Q4B_TRY(attn_decode(d->qkv, nullptr, nullptr, d->pos, L.kc, L.vc, d->att, 1, d->n_heads, d->n_kv_heads, d->head_dim,
+                          d->max_len, d->scale, nullptr, 0, st, 1));
+    } else {
+      Q4B_TRY(norm_lin(L.ln1, L.qkv, d->qkv, L.qkv_bias, Q4B_EPI_BIASF));
+      Q4B_TRY(attn_decode(d->qkv, d->cosT, d->sinT, d->pos, L.kc, L.vc, d->att, 1, d->n_heads, d->n_kv_heads, d->head_dim,
+                          d->max_len, d->scale, d->attn_ws, d->attn_ws_bytes, st));
+    }
     Q4B_TRY(lin(L.o, d->att, d->h, nullptr, Q4B_EPI_RESID));
     Q4B_TRY(norm_lin(L.ln2, L.gu, d->act, nullptr, Q4B_EPI_SWIGLU));
     Q4B_TRY(lin(L.down, d->act, d->h, nullptr, Q4B_EPI_RESID));

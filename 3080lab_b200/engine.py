@@ -25,7 +25,10 @@ def _dev(a: np.ndarray, device):
 
 class FusedQwen:
     def __init__(self, model: dict, max_len: int = 1024, device="cuda:0", tensor_core: bool = True,
-                 persistent: bool = False):
+                 persistent: bool = False, mma: bool = True):
+        """tensor_core: keep tile-packed weights and use the tensor-core kernels.  mma (needs tensor_core): the batch-1
+        linears go through the mma.sync streaming GEMV with RoPE / K-V append fused into the QKV projection; False
+        routes them through the tcgen05 exact-digit GEMV instead (kept as the second arm of A/B runs)."""
         if not torch.cuda.is_available():
             raise RuntimeError("FusedQwen needs a CUDA device; there is no CPU path")
         self.cfg: ModelConfig = model["cfg"]
@@ -47,13 +50,14 @@ class FusedQwen:
         self.head16 = self.embed if model.get("head16") is None else _dev(model["head16"], self.device)
         # tile-packed copies for the tensor-core kernels (K a multiple of 256)
         self.tensor_core = tensor_core
+        self.mma = bool(mma and tensor_core)
         self.packed = {}
         if tensor_core:
             for i, d in enumerate(self.L):
                 for k in ("qkv", "o", "gu", "down"):
-                    if d[k][0].shape[1] * 8 % 256 == 0:
+                    if self.mma or d[k][0].shape[1] * 8 % 256 == 0:
                         self.packed[id(d[k][0])] = QB.pack_q4(*d[k])
-            if self.head is not None and c.hidden % 256 == 0:
+            if self.head is not None and (self.mma or c.hidden % 256 == 0):
                 self.packed[id(self.head[0])] = QB.pack_q4(*self.head)
         cos, sin = rope_tables(c, max_len)
         self.cos, self.sin = _dev(cos, self.device), _dev(sin, self.device)
@@ -73,7 +77,7 @@ class FusedQwen:
         self.scale = 1.0 / math.sqrt(c.head_dim)
         self.status = torch.zeros(1, dtype=torch.int32, device=dv)
         self._desc = self._make_desc()
-        fused = tensor_core and c.hidden % 256 == 0
+        fused = tensor_core and (self.mma or c.hidden % 256 == 0)
         self.launches_per_step = 1 + (5 if fused else 7) * c.layers + 2
         self.persistent = False
         if persistent:
@@ -117,7 +121,8 @@ class FusedQwen:
             self.cos.data_ptr(), self.sin.data_ptr(), self.tok.data_ptr(), self.pos.data_ptr(), self.h.data_ptr(),
             self.x.data_ptr(), self.qkv.data_ptr(), self.att.data_ptr(), self.xm.data_ptr(), self.logits.data_ptr(),
             self.attn_ws.data_ptr(), self.attn_ws.numel(), self.head_ws.data_ptr(), self.head_ws.numel(),
-            self.status.data_ptr(), _ffi.STEP_TENSOR_CORE if self.tensor_core else 0, None, 0,
+            self.status.data_ptr(),
+            (_ffi.STEP_TENSOR_CORE if self.tensor_core else 0) | (_ffi.STEP_MMA_GEMV if self.mma else 0), None, 0,
             None if self.head16 is self.embed else self.head16.data_ptr())
 
     # ---- one decode token -------------------------------------------------------------------------------------------
@@ -133,7 +138,11 @@ class FusedQwen:
 
     def gemv(self, name, wsplit, X, Y, aux, N, Kdim, epi):
         pk = self.packed.get(id(wsplit[0]))
-        if pk is not None:
+        if pk is not None and self.mma:
+            _ffi.call("q4b_gemv_q4_0_mma", pk[0].data_ptr(), pk[1].data_ptr(), X.data_ptr(), Y.data_ptr(),
+                      0 if aux is None else aux.data_ptr(), N, Kdim, _ffi.EPI[epi], _ffi.X_F16, self.status.data_ptr(),
+                      torch.cuda.current_stream().cuda_stream)
+        elif pk is not None and Kdim % 256 == 0:
             _ffi.call("q4b_gemv_q4_0_tc", pk[0].data_ptr(), pk[1].data_ptr(), X.data_ptr(), Y.data_ptr(),
                       0 if aux is None else aux.data_ptr(), N, Kdim, _ffi.EPI[epi], _ffi.X_F16, self.status.data_ptr(),
                       torch.cuda.current_stream().cuda_stream)
@@ -146,7 +155,11 @@ class FusedQwen:
     def norm_gemv(self, nw, wsplit, Y, aux, N, Kdim, epi):
         """RMSNorm(h) * nw followed by a linear; one launch on the tensor-core path."""
         pk = self.packed.get(id(wsplit[0]))
-        if pk is not None:
+        if pk is not None and self.mma:
+            _ffi.call("q4b_rmsnorm_gemv_q4_0_mma", pk[0].data_ptr(), pk[1].data_ptr(), self.h.data_ptr(),
+                      nw.data_ptr(), float(self.cfg.eps), Y.data_ptr(), 0 if aux is None else aux.data_ptr(), N, Kdim,
+                      _ffi.EPI[epi], self.status.data_ptr(), torch.cuda.current_stream().cuda_stream)
+        elif pk is not None and Kdim % 256 == 0:
             _ffi.call("q4b_rmsnorm_gemv_q4_0_tc", pk[0].data_ptr(), pk[1].data_ptr(), self.h.data_ptr(),
                       nw.data_ptr(), float(self.cfg.eps), Y.data_ptr(), 0 if aux is None else aux.data_ptr(), N, Kdim,
                       _ffi.EPI[epi], self.status.data_ptr(), torch.cuda.current_stream().cuda_stream)
@@ -160,7 +173,23 @@ class FusedQwen:
         c = self.cfg
         H = c.hidden
         K.embed(self.embed, self.tok, self.h)
+        fused_kv = self.mma and 128 % c.head_dim == 0 and self.max_len <= 4096
+        st = torch.cuda.current_stream().cuda_stream
         for i, L in enumerate(self.L):
+            if fused_kv:
+                pk = self.packed[id(L["qkv"][0])]
+                _ffi.call("q4b_rmsnorm_qkv_rope_kv", pk[0].data_ptr(), pk[1].data_ptr(), self.h.data_ptr(),
+                          L["ln1"].data_ptr(), float(c.eps), self.qkv.data_ptr(), L["qkv_b"].data_ptr(), H,
+                          self.cos.data_ptr(), self.sin.data_ptr(), self.pos.data_ptr(), self.kc[i].data_ptr(),
+                          self.vc[i].data_ptr(), c.n_heads, c.n_kv_heads, c.head_dim, self.max_len,
+                          self.status.data_ptr(), st)
+                _ffi.call("q4b_attn_decode_cached", self.qkv.data_ptr(), self.pos.data_ptr(), self.kc[i].data_ptr(),
+                          self.vc[i].data_ptr(), self.att.data_ptr(), c.n_heads, c.n_kv_heads, c.head_dim, self.max_len,
+                          float(self.scale), st)
+                self.gemv("o", L["o"], self.att, self.h, None, H, c.q_rows, "resid")
+                self.norm_gemv(L["ln2"], L["gu"], self.xm, None, 2 * c.ffn, H, "swiglu")
+                self.gemv("down", L["down"], self.xm, self.h, None, H, c.ffn, "resid")
+                continue
             self.norm_gemv(L["ln1"], L["qkv"], self.qkv, L["qkv_b"], c.qkv_rows, H, "biasf")
             K.attn(self.qkv, self.cos, self.sin, self.pos, self.kc[i], self.vc[i], self.att, c.n_heads, c.n_kv_heads,
                    c.head_dim, self.max_len, self.scale, self.attn_ws)

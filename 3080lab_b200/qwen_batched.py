@@ -56,6 +56,34 @@ def gemv_tc(W, S, X, Y, aux, N: int, K: int, epi: str, status: Status) -> None:
     _ffi.call("q4b_gemv_q4_0_tc", _p(W), _p(S), _p(X), _p(Y), _p(aux), N, K, _ffi.EPI[epi], xd, _p(status.word), _stream())
 
 
+def gemv_mma(W, S, X, Y, aux, N: int, K: int, epi: str, status: Status) -> None:
+    """Exact Q4_0 GEMV of one activation vector by the streaming mma.sync kernel (bulk-copied weight slab, register
+    accumulators); same contract as `gemv_tc`, K a multiple of 32."""
+    if X.dtype not in (torch.float16, torch.float32):
+        raise TypeError("X must be fp16 or fp32")
+    xd = _ffi.X_F16 if X.dtype == torch.float16 else _ffi.X_F32
+    _ffi.call("q4b_gemv_q4_0_mma", _p(W), _p(S), _p(X), _p(Y), _p(aux), N, K, _ffi.EPI[epi], xd, _p(status.word), _stream())
+
+
+def rmsnorm_gemv_mma(W, S, h, norm_w, eps: float, Y, aux, N: int, K: int, epi: str, status: Status) -> None:
+    """RMSNorm(h) * norm_w -> fp16 -> `gemv_mma`, one launch."""
+    _ffi.call("q4b_rmsnorm_gemv_q4_0_mma", _p(W), _p(S), _p(h), _p(norm_w), float(eps), _p(Y), _p(aux), N, K, _ffi.EPI[epi],
+              _p(status.word), _stream())
+
+
+def rmsnorm_qkv_rope_kv(W, S, h, norm_w, eps: float, qkv, bias, K: int, cosT, sinT, pos, kc, vc, NH: int, NKV: int, HD: int,
+                        max_len: int, status: Status) -> None:
+    """The decode QKV projection with bias, rounding, RoPE of q / k and the K/V cache append fused in (the `biasf_kv`
+    epilogue, lab/qwen_batched.py:1316-1362, applied to one token).  Follow with `attn_cached`."""
+    _ffi.call("q4b_rmsnorm_qkv_rope_kv", _p(W), _p(S), _p(h), _p(norm_w), float(eps), _p(qkv), _p(bias), K, _p(cosT), _p(sinT),
+              _p(pos), _p(kc), _p(vc), NH, NKV, HD, max_len, _p(status.word), _stream())
+
+
+def attn_cached(qkv, pos, kc, vc, out, NH: int, NKV: int, HD: int, max_len: int, scale: float) -> None:
+    """Decode attention of one sequence over cache rows 0 .. pos (q already rotated, position pos already appended)."""
+    _ffi.call("q4b_attn_decode_cached", _p(qkv), _p(pos), _p(kc), _p(vc), _p(out), NH, NKV, HD, max_len, float(scale), _stream())
+
+
 def quant_q8(x, xq, xd, xsum=None) -> None:
     """x fp16 [rows, K] -> xq int8 [rows, K], xd fp16 [rows, K/32] (QUANT_Q8, lab/qwen_batched.py:1016-1041)."""
     rows = 1 if x.dim() == 1 else x.shape[0]

@@ -6,12 +6,14 @@ launch of a kernel with stamping on and prints, per phase, the median and the ma
 the first CTA started.  The numbers explain where a kernel's microseconds go; they are not benchmark values (an isolated
 launch has no programmatic overlap with its neighbours and its weights sit in L2 after the warm-up launches).
 
-    python 3080lab_b200/timeline.py gemv              # the four linears of a layer at batch 1 (exact tensor-core GEMV)
+    python 3080lab_b200/timeline.py gemv              # the four linears of a layer at batch 1 (streaming mma.sync GEMV)
+    python 3080lab_b200/timeline.py gemv --tcgen05    # the same four through the tcgen05 exact-digit GEMV
     python 3080lab_b200/timeline.py mmq --batch 32    # the same four as Q8_1 x Q4_0 MMQ for 32 sequences
     python 3080lab_b200/timeline.py attn --batch 32   # batched decode attention, 1024-token context
     python 3080lab_b200/timeline.py persistent        # one token through the persistent all-layers kernel (8 layers)
 
-Stamp order of `mmq_stream_kernel`: start, TMEM allocated, barriers ready, bulk copies issued, predecessor complete,
+Stamp order of `gemv_mma_kernel`: start, bulk copies issued, predecessor complete, activation operand staged, main loop
+done, split-K reduced.  Of `mmq_stream_kernel`: start, TMEM allocated, barriers ready, bulk copies issued, predecessor complete,
 activation operand staged, one stamp per batch of k-blocks (expanded and issued), all batches folded, split-K reduced,
 end.  Of `attn_decode_mma_kernel`: start, predecessor complete, q / new row prepared, one per 64-position tile, warps
 merged, cluster barrier passed, end.  The persistent kernel labels its stamps (see `decode_persistent.cu`).
@@ -61,6 +63,7 @@ def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("what", choices=["gemv", "mmq", "attn", "persistent"])
     ap.add_argument("--batch", type=int, default=32)
+    ap.add_argument("--tcgen05", action="store_true", help="gemv: the tcgen05 exact-digit kernel instead of the mma.sync one")
     args = ap.parse_args()
     import torch
     synth, engine, ffi, K = _mods()
@@ -69,7 +72,7 @@ def main() -> None:
     model = synth.synth_model(cfg, 0)
     c, H = cfg, cfg.hidden
     if args.what == "gemv":
-        m = engine.FusedQwen(model, max_len=1024)
+        m = engine.FusedQwen(model, max_len=1024, mma=not args.tcgen05)
         m.pos.fill_(600)
         L = m.L[0]
         ops = {

@@ -51,6 +51,8 @@ extern "C" {
 #define Q4B_EPI_SWIGLU_Q8 5 /* Q8_1 MMQ only: the SwiGLU product rounded to fp16 and quantised in the epilogue:
                                Y int8 [cols, N/2], AUX (written) fp16 [cols, N/64]; N a multiple of 64 */
 
+#define Q4B_EPI_BIASF_ROPE_KV 6 /* q4b_rmsnorm_qkv_rope_kv only: bias, round, RoPE of q and k, K/V append (see there) */
+
 #define Q4B_X_F16 0
 #define Q4B_X_F32 1
 
@@ -157,6 +159,46 @@ int q4b_pack_q4_0(const void* W, const void* S, void* Wt, void* St, int N, int K
  * status: one uint32, set to 1 if a bounded device-side wait expired (zero it once; check when convenient). */
 int q4b_gemv_q4_0_tc(const void* Wt, const void* St, const void* X, void* Y, const void* AUX, int N, int K, int epilogue,
                      int x_dtype, uint32_t* status, q4b_stream_t stream);
+
+/* ---- streaming GEMV for decode at batch 1 ----------------------------------------------------------------------------
+ * Q4_0 GEMV for one activation vector, exact (four signed base-256 digit planes of a 30-bit block-fixed-point x, int32
+ * block dots by mma.sync.m16n8k32.s8 with register accumulators, fp32 scale-and-add per block).  Same contract,
+ * epilogues and tile-packed weights as q4b_gemv_q4_0_tc; it replaces the same launch site (gemv_source,
+ * lab/qwen_kernels.py:14-113; host FusedQwen.gemv scripts/qwen_fused.py:104-107).  K a multiple of 32.  The CTA's whole
+ * weight slab is bulk-copied into shared memory ahead of the programmatic-dependency wait, so in a chain of launches
+ * the HBM stream of one kernel overlaps the computation of the one before it.
+ * status: one uint32, set non-zero if a bounded device-side wait expired (zero it once; check when convenient). */
+int q4b_gemv_q4_0_mma(const void* Wt, const void* St, const void* X, void* Y, const void* AUX, int N, int K, int epilogue,
+                      int x_dtype, uint32_t* status, q4b_stream_t stream);
+
+/* RMSNorm fused in front of q4b_gemv_q4_0_mma (see q4b_rmsnorm_gemv_q4_0_tc).  h, norm_w fp32 [K]. */
+int q4b_rmsnorm_gemv_q4_0_mma(const void* Wt, const void* St, const float* h, const float* norm_w, float eps, void* Y,
+                              const void* AUX, int N, int K, int epilogue, uint32_t* status, q4b_stream_t stream);
+
+/* The QKV projection of one decode token with everything up to the cache write fused in: RMSNorm(h) -> Q4_0 GEMV ->
+ * + bias, round to fp16 -> NeoX rotation of the q and k heads at position pos[0] from the ROUNDED values, rounded
+ * again -> rotated k and raw v stored into the cache row pos[0].  This is the `biasf_kv` epilogue of the reference's
+ * prefill GEMM (lab/qwen_batched.py:1316-1362) applied to the decode step, where the reference rotates inside the
+ * attention kernel instead (ATTN4, lab/qwen_kernels.py:533-547); the values are the same.
+ * qkv fp16 [(NH + 2 NKV) HD] receives rotated q, rotated k, v.  bias fp32 [(NH + 2 NKV) HD].  kc / vc fp16
+ * [NKV, max_len, HD] (one sequence).  HD must divide 128 (a row tile holds whole heads).  Follow with
+ * q4b_attn_decode_cached. */
+int q4b_rmsnorm_qkv_rope_kv(const void* Wt, const void* St, const float* h, const float* norm_w, float eps, void* qkv,
+                            const float* bias, int K, const float* cosT, const float* sinT, const int64_t* pos, void* kc,
+                            void* vc, int NH, int NKV, int HD, int max_len, uint32_t* status, q4b_stream_t stream);
+
+/* Exercise of the failure path of the bounded device-side waits, in a form that always returns: q4b_gemv_q4_0_mma
+ * (fp16 x, logits epilogue) with the bulk copies of its first weight chunk withheld and the wait cut to a few thousand
+ * polls.  The wait gives up, the kernel sets *status non-zero and finishes normally; Y is meaningless.  The reference's
+ * persistent kernel reports expired waits the same way (capped waits + err word, lab/qwen_mega.py:75-83, 153-161). */
+int q4b_debug_gemv_mma_expired_wait(const void* Wt, const void* St, const void* X, void* Y, int N, int K, uint32_t* status,
+                                    q4b_stream_t stream);
+
+/* Decode attention of one sequence when q is already rotated and position pos[0] is already in the cache
+ * (q4b_rmsnorm_qkv_rope_kv did both): attention over positions 0 .. pos[0] only, no tables, no cache write.  Same
+ * arithmetic as q4b_attn_decode (ATTN4, lab/qwen_kernels.py:548-603).  max_len <= 4096. */
+int q4b_attn_decode_cached(const void* qkv, const int64_t* pos, const void* kc, const void* vc, void* out, int NH, int NKV,
+                           int HD, int max_len, float scale, q4b_stream_t stream);
 
 /* ---- prefill: Q8_1 x Q4_0 for many activation rows ------------------------------------------------------------------
  * Tiled Q8_1 activations for the prefill MMQ: for each (tile of 128 rows, 32-value block) 4096 bytes of int8 values
@@ -266,6 +308,7 @@ typedef struct {
 
 #define Q4B_STEP_TENSOR_CORE 1  /* linears through q4b_gemv_q4_0_tc where K is a multiple of 256 */
 #define Q4B_STEP_PERSISTENT 2   /* all layers in one cooperative kernel (q4b_decode_persistent_layers) */
+#define Q4B_STEP_MMA_GEMV 4     /* linears through q4b_gemv_q4_0_mma, QKV through q4b_rmsnorm_qkv_rope_kv + q4b_attn_decode_cached */
 
 int q4b_decode_step(const q4b_decode_desc* desc, q4b_stream_t stream);
 
