@@ -277,7 +277,7 @@ template <int HD, int HSUB, int PASSES>
 __global__ void __launch_bounds__(AT) attn_decode_cluster_kernel(const __half* qkv, const float* __restrict__ cosT,
                                                                  const float* __restrict__ sinT, const int64_t* posp,
                                                                  __half* kc, __half* vc, __half* out, int NH, int NKV, int GRP,
-                                                                 int nsub, int max_len, float scale, int pre) {
+                                                                 int nsub, int max_len, float scale, int pre, unsigned long long* trace) {
   // pre != 0: the producer of `qkv` already rotated q and appended the rotated k / raw v at pos (the fused epilogue of
   // the QKV projection), so this kernel only reads: no tables, no writer, position pos comes from the cache like the rest
   constexpr int HALF = HD / 2;
@@ -290,24 +290,48 @@ __global__ void __launch_bounds__(AT) attn_decode_cluster_kernel(const __half* q
   __shared__ float sc[HSUB][CHK];                // exp(score - warp maximum), read back only by the warp that wrote it
   __shared__ float wml[NW][HSUB][2];             // per warp: maximum, sum
   __shared__ __align__(16) float red_o[NW][HSUB][HD];
-  __shared__ __align__(16) float part_o[HSUB][HD];
-  __shared__ float part_ml[HSUB][2];
-  __shared__ float pml[HSUB][NCL][2];            // combiner: every chunk's (max, sum)
-  __shared__ float wgt[HSUB][NCL + 1];           // [h][c] = exp(m_c - M), [h][NCL] = L
+  // combiner (meaningful in the cluster's first CTA): every chunk PUSHES its partial output and (max, sum) here through
+  // distributed shared memory, so after one cluster barrier the combine runs on local data only
+  __shared__ __align__(16) float comb_o[NCL][HSUB][HD];
+  __shared__ float comb_ml[NCL][HSUB][2];
 
+  unsigned long long* tr = (trace && threadIdx.x == 0)
+                               ? trace + (size_t)((blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * 16 : nullptr;
+  int tri = 0;
+  auto stamp = [&]() {
+    if (tr && tri < 15) {
+      unsigned long long gt;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt));
+      tr[tri++] = gt;
+      tr[15] = (unsigned long long)tri;
+    }
+  };
+  stamp();                                                          // 0: start
   pdl_launch_dependents();
-  pdl_wait();
+  asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");      // "this CTA exists" (paired with the wait before the push)
   const int b = blockIdx.z, chunk = blockIdx.x;
   const int kvh = blockIdx.y / nsub, hs = blockIdx.y - kvh * nsub;
   const int h0 = hs * HSUB, nh = min(HSUB, GRP - h0);
   const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
   const int c0 = chunk * CHK;
-  const int64_t praw = posp[b];
   __half* kbase = kc + ((size_t)b * NKV + kvh) * (size_t)max_len * HD;
   __half* vbase = vc + ((size_t)b * NKV + kvh) * (size_t)max_len * HD;
   const int psub = lane / LPR, d0 = (lane % LPR) * 8;     // P.V pass: lane <-> (row of the warp step, 8 dims)
   constexpr int IPP = 32 / PPI;                          // warp steps per pass
   constexpr bool VPRE = PASSES == 1;                     // V rows of the chunk held in registers from the start
+  // Ahead of the dependency wait: ask for this chunk's K and V rows to be brought into L2.  Rows below the current
+  // position were written by earlier tokens; a prefetch binds nothing, so a row that is still being appended by the
+  // predecessor is simply read again after the wait.
+  if (t < 2) {
+    const int rows = min(CHK, max_len - c0);
+    if (rows > 0) {
+      const __half* src = (t == 0 ? kbase : vbase) + (size_t)c0 * HD;
+      asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"((uint32_t)(rows * HD * 2)) : "memory");
+    }
+  }
+  pdl_wait();
+  stamp();                                                          // 1: predecessor complete
+  const int64_t praw = posp[b];
 
   // ---- K (and, for one-pass chunks, V) rows are requested before the position is known, so that the position, the
   // cache rows and the new q/k/v row are one round trip to memory instead of two.  Rows at or beyond the current
@@ -502,7 +526,12 @@ __global__ void __launch_bounds__(AT) attn_decode_cluster_kernel(const __half* q
         for (int k = 0; k < 8; ++k) red_o[warp][h][d0 + k] = acc[h][k];
     }
     __syncthreads();
-    // ---- the four warps' partials -> this chunk's partial (fixed warp order)
+    stamp();                                                        // 2: scores and P.V of the chunk done
+    // ---- the four warps' partials -> this chunk's partial (fixed warp order), pushed into the combiner CTA
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");   // pairs with the arrive at the top
+    uint32_t r_o, r_ml;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r_o) : "r"((uint32_t)__cvta_generic_to_shared(&comb_o[chunk][0][0])), "r"(0));
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r_ml) : "r"((uint32_t)__cvta_generic_to_shared(&comb_ml[chunk][0][0])), "r"(0));
     for (int e = t; e < HSUB * HD; e += AT) {
       const int hl = e / HD, d = e - hl * HD;
       float M = wml[0][hl][0];
@@ -515,47 +544,33 @@ __global__ void __launch_bounds__(AT) attn_decode_cluster_kernel(const __half* q
         o += red_o[w][hl][d] * f;
         l += wml[w][hl][1] * f;
       }
-      part_o[hl][d] = o;
+      asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(r_o + (uint32_t)(e * 4)), "f"(o) : "memory");
       if (d == 0) {
-        part_ml[hl][0] = M;
-        part_ml[hl][1] = l;
+        asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(r_ml + (uint32_t)(hl * 8)), "f"(M) : "memory");
+        asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(r_ml + (uint32_t)(hl * 8 + 4)), "f"(l) : "memory");
       }
     }
+  } else {
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
   }
-  cluster_sync_all();                                               // every chunk's partials are in place
-  if (chunk == 0) {
-    if (t < HSUB * NCL) {                                           // one thread per (head, chunk): both loads in flight
-      const int hl = t / NCL, c = t - hl * NCL;
-      if (c < nact) {
-        pml[hl][c][0] = ld_peer_f32(&part_ml[hl][0], (uint32_t)c);
-        pml[hl][c][1] = ld_peer_f32(&part_ml[hl][1], (uint32_t)c);
-      }
+  cluster_sync_all();                                               // every active chunk's partials are in the combiner
+  stamp();                                                          // 3: cluster barrier passed
+  if (chunk != 0) return;
+  // chunk order, so the result does not depend on timing; every thread derives the weights itself (a few exps) instead
+  // of a second block-wide exchange
+  for (int e = t; e < nh * HD; e += AT) {
+    const int hl = e / HD, d = e - hl * HD;
+    float M = -INFINITY;
+    for (int c = 0; c < nact; ++c) M = fmaxf(M, comb_ml[c][hl][0]);
+    float o = 0.f, L = 0.f;
+    for (int c = 0; c < nact; ++c) {
+      const float w = __expf(comb_ml[c][hl][0] - M);
+      L += comb_ml[c][hl][1] * w;
+      o += comb_o[c][hl][d] * w;
     }
-    __syncthreads();
-    if (t < nh) {
-      float M = -INFINITY;
-      for (int c = 0; c < nact; ++c) M = fmaxf(M, pml[t][c][0]);
-      float L = 0.f;
-      for (int c = 0; c < nact; ++c) {
-        const float w = __expf(pml[t][c][0] - M);
-        wgt[t][c] = w;
-        L += pml[t][c][1] * w;
-      }
-      wgt[t][NCL] = L;
-    }
-    __syncthreads();
-    for (int e = t; e < nh * HD; e += AT) {
-      const int hl = e / HD, d = e - hl * HD;
-      float pv[NCL];
-#pragma unroll
-      for (int c = 0; c < NCL; ++c) pv[c] = c < nact ? ld_peer_f32(&part_o[hl][d], (uint32_t)c) : 0.f;
-      float o = 0.f;
-#pragma unroll
-      for (int c = 0; c < NCL; ++c) o += c < nact ? pv[c] * wgt[hl][c] : 0.f;
-      out[(head0 + hl) * HD + d] = __float2half_rn(o / wgt[hl][NCL]);
-    }
+    out[(head0 + hl) * HD + d] = __float2half_rn(o / L);
   }
-  cluster_sync_all();                                               // peers stay resident until their partials are read
+  stamp();                                                          // 4: combined (first CTA of the cluster only)
 }
 
 template <int HD, int HSUB>
@@ -563,15 +578,16 @@ int launch_cluster_passes(int passes, dim3 grid, cudaStream_t st, const __half* 
                           const int64_t* pos, __half* kc, __half* vc, __half* out, int NH, int NKV, int GRP, int nsub,
                           int max_len, float scale, int pre) {
   cudaError_t e;
+  unsigned long long* trace = trace_slot(2, (int)(grid.x * grid.y * grid.z));
   if (passes == 1)
     e = launch_pdl_cluster(attn_decode_cluster_kernel<HD, HSUB, 1>, grid, dim3(AT), 0, st, NCL, 1, qkv, cosT, sinT, pos, kc, vc,
-                           out, NH, NKV, GRP, nsub, max_len, scale, pre);
+                           out, NH, NKV, GRP, nsub, max_len, scale, pre, trace);
   else if (passes == 2)
     e = launch_pdl_cluster(attn_decode_cluster_kernel<HD, HSUB, 2>, grid, dim3(AT), 0, st, NCL, 1, qkv, cosT, sinT, pos, kc, vc,
-                           out, NH, NKV, GRP, nsub, max_len, scale, pre);
+                           out, NH, NKV, GRP, nsub, max_len, scale, pre, trace);
   else
     e = launch_pdl_cluster(attn_decode_cluster_kernel<HD, HSUB, 4>, grid, dim3(AT), 0, st, NCL, 1, qkv, cosT, sinT, pos, kc, vc,
-                           out, NH, NKV, GRP, nsub, max_len, scale, pre);
+                           out, NH, NKV, GRP, nsub, max_len, scale, pre, trace);
   return check_launch(e, "attn_decode");
 }
 
@@ -616,6 +632,8 @@ size_t attn_decode_workspace(int B, int NH, int HD, int max_len) {
 
 int attn_decode_mma(const void*, const float*, const float*, const int64_t*, void*, void*, void*, int, int, int, int, float,
                     cudaStream_t, void* xq = nullptr, void* xd = nullptr);
+bool attn_cached_fits(int NH, int NKV, int HD, int max_len);
+int attn_cached(const void*, const int64_t*, const void*, const void*, void*, int, int, int, float, cudaStream_t);
 
 // pre != 0 (one sequence, max_len <= 4096 only): q arrives rotated and position pos is already in the cache (the fused
 // epilogue of the QKV projection did both); cosT / sinT / ws may then be null.
@@ -626,6 +644,8 @@ int attn_decode(const void* qkv, const float* cosT, const float* sinT, const int
     if (NH <= 0 || NKV <= 0 || max_len <= 0 || (NH % NKV) || NH / NKV > 8 || (HD != 64 && HD != 128))
       return fail(Q4B_E_SHAPE, "attn_decode: need HD in {64,128}, NH a multiple of NKV, NH/NKV <= 8");
     if (!qkv || !pos || !kc || !vc || !out || !aligned16(kc) || !aligned16(vc)) return fail(Q4B_E_ALIGN, "attn_decode: null or misaligned pointer");
+    // contexts up to 2048 with head_dim 128: the shared-memory-resident tensor-core kernel (attn_decode_cached.cu)
+    if (attn_cached_fits(NH, NKV, HD, max_len) && aligned16(qkv)) return attn_cached(qkv, pos, kc, vc, out, NH, NKV, max_len, scale, st);
     static const int hsub_for[9] = {1, 1, 2, 3, 2, 3, 2, 4, 4};
     const int GRP = NH / NKV, hsub = hsub_for[GRP], nsub = (GRP + hsub - 1) / hsub;
     const int passes = max_len <= NCL * 128 ? 1 : (max_len <= NCL * 256 ? 2 : 4);

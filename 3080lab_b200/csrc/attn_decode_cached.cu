@@ -1,0 +1,323 @@
+// Decode attention of ONE sequence over an fp16 K/V cache that already holds the current position, with q already
+// rotated: the attention half of ATTN4 (lab/qwen_kernels.py:548-603: s_j = (q . k_j) * scale, soft-max over j <= pos,
+// out = round16(sum e_j v_j / sum e_j)); rotation and the cache append were done by the QKV projection's epilogue
+// (gemv_mma.cu), as the reference's prefill path does it (lab/qwen_batched.py:1316-1362).
+//
+// Built for latency.  At batch 1 a layer's attention touches well under 1 MB; what costs is the chain of dependent
+// round trips, so the kernel removes them one by one:
+//   * the position and every cache row BELOW it were written by earlier decode steps, and the first launch of a decode
+//     step (the embedding lookup) triggers its dependents only after its own dependency wait, so all work of earlier
+//     steps is complete before any later launch of the step starts.  This kernel therefore reads the position and
+//     copies its whole chunk of K and V rows into shared memory (cp.async, rows padded to 272 bytes) BEFORE its
+//     dependency wait, while the QKV projection is still running;
+//   * the context is cut into 8 equal chunks of the ACTUAL length (not of max_len), one CTA each, a thread-block
+//     cluster per KV head; all query heads of the KV group form one 16-row MMA operand, so K and V are read once;
+//   * after the wait only q (1.5 KB) and the row of the current position are fetched; S = Q K^T and O = P V run on
+//     mma.sync.m16n8k16 (fp16 inputs, fp32 accumulation; P as two fp16 terms so the probabilities keep ~22 bits), a
+//     warp owns 16 positions at a time, no block-wide barrier inside the loop;
+//   * warps are merged through shared memory, chunks are PUSHED into the first CTA's shared memory (st.shared::cluster)
+//     and combined there in chunk order after one cluster barrier: no workspace, no atomics, no remote loads.
+#include "q4b_internal.h"
+
+namespace q4b {
+
+namespace {
+
+constexpr int HD = 128;
+constexpr int PITCH = HD * 2 + 16;             // bytes per staged row (conflict-free fragment reads)
+constexpr int NCL = 8;                         // chunks = cluster size
+constexpr int AT = 256, NW = AT / 32;
+constexpr int MAXG = 8;                        // query heads per KV head
+constexpr int MAX_CTX = 2048;                  // 8 chunks x 256 positions x 2 x 272 bytes of shared memory
+
+__device__ __forceinline__ void mma16816(float* c, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
+  const __half2 h = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+// 16 bytes global -> shared; `bytes` = 0 fills the destination with zeros instead (rows beyond the valid range)
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, int bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src), "r"(bytes)
+               : "memory");
+}
+
+__global__ void __launch_bounds__(AT, 2) attn_cached_kernel(const __half* qkv, const int64_t* posp, const __half* kc, const __half* vc,
+                                                            __half* out, int NH, int NKV, int max_len, int cap, float scale_log2e,
+                                                            unsigned long long* trace) {
+  extern __shared__ __align__(16) uint8_t sm[];
+  uint8_t* sQ = sm;                                  // [16][PITCH]   q heads of the group (rows >= GRP zero)
+  uint8_t* sK = sQ + 16 * PITCH;                     // [cap][PITCH]
+  uint8_t* sV = sK + (size_t)cap * PITCH;            // [cap][PITCH]
+  __shared__ float wml[NW][MAXG][2];                 // per warp: (max, sum) in base-2 units
+  // combiner (meaningful in the cluster's first CTA): every chunk pushes its partial output and (max, sum) here
+  __shared__ __align__(16) float comb_o[NCL][MAXG][HD];
+  __shared__ float comb_ml[NCL][MAXG][2];
+
+  const int t = threadIdx.x, warp = t >> 5, lane = t & 31, g = lane >> 2, tq = lane & 3;
+  const int c = blockIdx.x, kvh = blockIdx.y;
+  unsigned long long* tr = (trace && t == 0) ? trace + (size_t)(blockIdx.y * gridDim.x + blockIdx.x) * 16 : nullptr;
+  int tri = 0;
+  auto stamp = [&]() {
+    if (tr && tri < 15) {
+      unsigned long long gt;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt));
+      tr[tri++] = gt;
+      tr[15] = (unsigned long long)tri;
+    }
+  };
+  stamp();                                           // 0: start
+  pdl_launch_dependents();
+  asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");   // "this CTA exists" (paired with the wait before the push)
+  const int GRP = NH / NKV;
+  // the position belongs to the state of earlier steps (see the header): readable ahead of the wait
+  int p = (int)posp[0];
+  p = p < 0 ? 0 : (p >= max_len ? max_len - 1 : p);
+  const int n = p + 1;                               // positions 0 .. p
+  int chunk = ((n + NCL - 1) / NCL + 15) & ~15;      // equal chunks of the actual context, whole 16-position warp tiles
+  if (chunk > cap) chunk = cap;                      // (cannot happen while max_len <= 8 cap; keeps the copies in bounds)
+  const int c0 = c * chunk, c1 = min(c0 + chunk, n); // this CTA: positions c0 .. c1 - 1
+  const bool active = c0 < n;
+  const int nact = (n + chunk - 1) / chunk;
+  const int rows = active ? c1 - c0 : 0;
+  const int rows16 = (rows + 15) & ~15;
+  const __half* kbase = kc + (size_t)kvh * max_len * HD;
+  const __half* vbase = vc + (size_t)kvh * max_len * HD;
+  // ---- ahead of the wait: rows below the current position -> shared memory; the tail of the last warp tile is zeroed
+  // (a masked probability times a stale NaN would still be a NaN)
+  for (int e = t; e < rows16 * (HD / 8); e += AT) {
+    const int r = e >> 4, cc = e & 15;
+    const int j = c0 + r;
+    const bool ld = j < p;                           // row p itself arrives after the wait
+    const size_t off = (size_t)(ld ? j : 0) * HD + cc * 8;
+    cp_async16(sK + (size_t)r * PITCH + cc * 16, kbase + off, ld ? 16 : 0);
+    cp_async16(sV + (size_t)r * PITCH + cc * 16, vbase + off, ld ? 16 : 0);
+  }
+  asm volatile("cp.async.commit_group;" ::: "memory");
+  stamp();                                           // 1: cache rows requested
+  pdl_wait();
+  stamp();                                           // 2: predecessor complete
+  if (active) {
+    // ---- q heads of the group (already rotated) and the row of the current position: both requested at once
+    const bool mine = p >= c0 && p < c1 && t < 32;            // 16 threads carry the K row of position p, 16 its V row
+    uint4 qv = make_uint4(0u, 0u, 0u, 0u), pv = make_uint4(0u, 0u, 0u, 0u);
+    {
+      const int hl = t >> 4, cc = t & 15;
+      if (hl < GRP) qv = *reinterpret_cast<const uint4*>(qkv + (size_t)(kvh * GRP + hl) * HD + cc * 8);
+      if (mine) pv = *reinterpret_cast<const uint4*>((t < 16 ? kbase : vbase) + (size_t)p * HD + cc * 8);
+      *reinterpret_cast<uint4*>(sQ + hl * PITCH + cc * 16) = qv;
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");      // this thread's copies have landed (zero-filled slot of row p too)
+    __syncthreads();                                          // ... and everyone's; the plain stores below come after them
+    if (mine) *reinterpret_cast<uint4*>((t < 16 ? sK : sV) + (size_t)(p - c0) * PITCH + (t & 15) * 16) = pv;
+    __syncthreads();
+    stamp();                                         // 3: operands staged
+    uint32_t qa[8][2];                               // rows g of the A operand (rows g + 8 are zero)
+    {
+      const uint8_t* r0 = sQ + g * PITCH;
+#pragma unroll
+      for (int s = 0; s < 8; ++s) {
+        qa[s][0] = *reinterpret_cast<const uint32_t*>(r0 + (16 * s + 2 * tq) * 2);
+        qa[s][1] = *reinterpret_cast<const uint32_t*>(r0 + (16 * s + 2 * tq + 8) * 2);
+      }
+    }
+    float o[16][2];                                  // head g: 16 dim tiles x 2 columns
+#pragma unroll
+    for (int j = 0; j < 16; ++j) o[j][0] = o[j][1] = 0.f;
+    float m_run = -INFINITY, l_run = 0.f;
+    for (int w0 = 16 * warp; w0 < rows; w0 += 16 * NW) {      // this warp's 16-position tiles (one for contexts <= 1024)
+      // ---- S = Q K^T
+      float sacc[2][4];
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        sacc[j][0] = sacc[j][1] = sacc[j][2] = sacc[j][3] = 0.f;
+        const uint8_t* kr = sK + (size_t)(w0 + 8 * j + g) * PITCH;
+#pragma unroll
+        for (int s = 0; s < 8; ++s) {
+          const uint32_t b0 = *reinterpret_cast<const uint32_t*>(kr + (16 * s + 2 * tq) * 2);
+          const uint32_t b1 = *reinterpret_cast<const uint32_t*>(kr + (16 * s + 2 * tq + 8) * 2);
+          mma16816(sacc[j], qa[s][0], 0u, qa[s][1], 0u, b0, b1);
+        }
+      }
+      stamp();   // T: QK done
+      // ---- mask, online soft-max (base 2) for head g
+      float mx = m_run;
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const int key = w0 + 8 * j + 2 * tq;
+        sacc[j][0] = key < rows ? sacc[j][0] * scale_log2e : -INFINITY;
+        sacc[j][1] = key + 1 < rows ? sacc[j][1] * scale_log2e : -INFINITY;
+        mx = fmaxf(mx, fmaxf(sacc[j][0], sacc[j][1]));
+      }
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));    // finite: position w0 < rows is valid
+      const float cor = exp2f(m_run - mx);
+      m_run = mx;
+      float ps = 0.f;
+      uint32_t ph[2], pl[2];                         // A fragments (row g): k 2tq.. and k 2tq + 8..
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const float p0 = exp2f(sacc[j][0] - mx), p1 = exp2f(sacc[j][1] - mx);
+        ps += p0 + p1;
+        const __half2 h = __floats2half2_rn(p0, p1);
+        const float2 hf = __half22float2(h);
+        ph[j] = *reinterpret_cast<const uint32_t*>(&h);
+        pl[j] = pack_h2(p0 - hf.x, p1 - hf.y);       // second fp16 term: P keeps ~22 bits through the MMA
+      }
+      l_run = l_run * cor + ps;                      // per-lane partial; reduced over the quad at the end
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        o[j][0] *= cor;
+        o[j][1] *= cor;
+      }
+      stamp();   // T: softmax done
+      // ---- O += (P_hi + P_lo) V
+#pragma unroll
+      for (int j = 0; j < 16; j += 2) {
+        const int mtx = lane >> 3, r = lane & 7;
+        const uint8_t* addr = sV + (size_t)(w0 + (mtx & 1) * 8 + r) * PITCH + (8 * (j + (mtx >> 1))) * 2;
+        uint32_t b0, b1, b2, b3;
+        asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(b0), "=r"(b1), "=r"(b2), "=r"(b3)
+                     : "r"((uint32_t)__cvta_generic_to_shared(addr)));
+        float a0[4] = {o[j][0], o[j][1], 0.f, 0.f}, a1[4] = {o[j + 1][0], o[j + 1][1], 0.f, 0.f};
+        mma16816(a0, ph[0], 0u, ph[1], 0u, b0, b1);
+        mma16816(a0, pl[0], 0u, pl[1], 0u, b0, b1);
+        mma16816(a1, ph[0], 0u, ph[1], 0u, b2, b3);
+        mma16816(a1, pl[0], 0u, pl[1], 0u, b2, b3);
+        o[j][0] = a0[0];
+        o[j][1] = a0[1];
+        o[j + 1][0] = a1[0];
+        o[j + 1][1] = a1[1];
+      }
+    }
+    stamp();   // T: PV done
+    // ---- merge the warps (each saw different positions of the chunk); warps without a tile contribute (-inf, 0)
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
+    __syncthreads();
+    stamp();   // T: sync1                                 // every warp is done with the K tile: its space takes the partials
+    float* wo = reinterpret_cast<float*>(sK);        // [NW][MAXG][HD] = 32 KB <= cap x PITCH for cap >= 128
+    if (g < GRP) {
+#pragma unroll
+      for (int j = 0; j < 16; ++j)
+        *reinterpret_cast<float2*>(wo + ((size_t)warp * MAXG + g) * HD + 8 * j + 2 * tq) = make_float2(o[j][0], o[j][1]);
+      if (tq == 0) {
+        wml[warp][g][0] = m_run;
+        wml[warp][g][1] = l_run;
+      }
+    }
+    __syncthreads();
+    stamp();                                         // 4: chunk scored
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");   // pairs with the arrive at the top
+    uint32_t r_o, r_ml;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r_o) : "r"((uint32_t)__cvta_generic_to_shared(&comb_o[c][0][0])), "r"(0));
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r_ml) : "r"((uint32_t)__cvta_generic_to_shared(&comb_ml[c][0][0])), "r"(0));
+    // every load of the (at most four) outputs of a thread is issued before the first use: with eight warps per CTA the
+    // merge is a latency chain, not a throughput problem
+    constexpr int EPT = MAXG * HD / AT;              // outputs per thread
+#pragma unroll
+    for (int i = 0; i < EPT; ++i) {
+      const int e = t + i * AT;
+      if (e < GRP * HD) {
+        const int hl = e / HD, d = e - hl * HD;
+        float mw[NW], lw[NW], ow[NW];
+#pragma unroll
+        for (int w = 0; w < NW; ++w) {
+          mw[w] = wml[w][hl][0];
+          lw[w] = wml[w][hl][1];
+          ow[w] = wo[((size_t)w * MAXG + hl) * HD + d];
+        }
+        float M = mw[0];
+#pragma unroll
+        for (int w = 1; w < NW; ++w) M = fmaxf(M, mw[w]);            // finite: warp 0 always has a valid position
+        float ov = 0.f, lv = 0.f;
+#pragma unroll
+        for (int w = 0; w < NW; ++w) {
+          const float f = exp2f(mw[w] - M);                          // -inf -> 0
+          ov += ow[w] * f;
+          lv += lw[w] * f;
+        }
+        asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(r_o + (uint32_t)(e * 4)), "f"(ov) : "memory");
+        if (d == 0) {
+          asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(r_ml + (uint32_t)(hl * 8)), "f"(M) : "memory");
+          asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(r_ml + (uint32_t)(hl * 8 + 4)), "f"(lv) : "memory");
+        }
+      }
+    }
+    stamp();   // T: pushed
+  } else {
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+  }
+  cluster_sync_all();                                // every active chunk's partials are in the combiner
+  stamp();                                           // 5: cluster barrier passed
+  if (c != 0) return;
+  // chunk order, so the result does not depend on timing; every thread derives the weights itself (a few exp2)
+  constexpr int EPT2 = MAXG * HD / AT;
+#pragma unroll
+  for (int i = 0; i < EPT2; ++i) {
+    const int e = t + i * AT;
+    if (e < GRP * HD) {
+      const int hl = e / HD, d = e - hl * HD;
+      float mc[NCL], lc[NCL], oc[NCL];
+#pragma unroll
+      for (int cc = 0; cc < NCL; ++cc) {
+        const bool on = cc < nact;
+        mc[cc] = on ? comb_ml[cc][hl][0] : -INFINITY;
+        lc[cc] = on ? comb_ml[cc][hl][1] : 0.f;
+        oc[cc] = on ? comb_o[cc][hl][d] : 0.f;
+      }
+      float M = mc[0];
+#pragma unroll
+      for (int cc = 1; cc < NCL; ++cc) M = fmaxf(M, mc[cc]);
+      float ov = 0.f, L = 0.f;
+#pragma unroll
+      for (int cc = 0; cc < NCL; ++cc) {
+        const float w = exp2f(mc[cc] - M);
+        L += lc[cc] * w;
+        ov += oc[cc] * w;
+      }
+      out[(size_t)(kvh * GRP + hl) * HD + d] = __float2half_rn(ov / L);
+    }
+  }
+  stamp();                                           // 6: combined (first CTA of the cluster only)
+}
+
+}  // namespace
+
+// Largest context the shared-memory-resident form covers; longer caches use the chunked cluster kernel of attn_decode.cu.
+bool attn_cached_fits(int NH, int NKV, int HD, int max_len) {
+  return HD == 128 && NKV > 0 && NH % NKV == 0 && NH / NKV <= MAXG && max_len > 0 && max_len <= MAX_CTX;
+}
+
+int attn_cached(const void* qkv, const int64_t* pos, const void* kc, const void* vc, void* out, int NH, int NKV, int max_len,
+                float scale, cudaStream_t st) {
+  if (!attn_cached_fits(NH, NKV, HD, max_len)) return fail(Q4B_E_SHAPE, "attn_decode_cached: needs head_dim 128, NH/NKV <= 8, max_len <= 2048");
+  if (!qkv || !pos || !kc || !vc || !out || !aligned16(qkv) || !aligned16(kc) || !aligned16(vc))
+    return fail(Q4B_E_ALIGN, "attn_decode_cached: null or misaligned pointer");
+  int cap = ((max_len + NCL - 1) / NCL + 15) & ~15;  // positions per CTA at the longest context
+  if (cap < 128) cap = 128;                          // the K tile's space later holds the per-warp partials (32 KB)
+  const size_t smem = (size_t)(16 + 2 * cap) * PITCH;
+  static size_t configured[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return fail(Q4B_E_CUDA, "attn_decode_cached: no current device");
+  if (smem > configured[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(attn_cached_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) {
+      set_cuda_error(e, "attn_decode_cached");
+      return Q4B_E_CUDA;
+    }
+    configured[dev] = smem;
+  }
+  unsigned long long* trace = trace_slot(2, NCL * NKV);
+  const float scale_log2e = scale * 1.4426950408889634f;
+  return check_launch(launch_pdl_cluster(attn_cached_kernel, dim3(NCL, NKV), dim3(AT), smem, st, NCL, 1, (const __half*)qkv, pos,
+                                         (const __half*)kc, (const __half*)vc, (__half*)out, NH, NKV, max_len, cap, scale_log2e, trace),
+                      "attn_decode_cached");
+}
+
+}  // namespace q4b

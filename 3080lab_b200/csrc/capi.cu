@@ -19,6 +19,26 @@ int fail(int code, const char* msg) {
   return code;
 }
 
+// ---- chain timeline state (host side; profiling runs only, not thread-safe)
+static unsigned long long* g_chain_buf = nullptr;
+static size_t g_chain_entries = 0, g_chain_next = 0;
+static constexpr int MAX_CHAIN_RECORDS = 4096;
+static long long g_chain_log[MAX_CHAIN_RECORDS][3];
+static int g_chain_records = 0;
+
+unsigned long long* trace_slot(int kernel_id, int ctas) {
+  if (!g_chain_buf || ctas <= 0 || g_chain_records >= MAX_CHAIN_RECORDS) return nullptr;
+  const size_t need = (size_t)ctas * 16;
+  if (g_chain_next + need > g_chain_entries) return nullptr;
+  unsigned long long* p = g_chain_buf + g_chain_next;
+  g_chain_log[g_chain_records][0] = kernel_id;
+  g_chain_log[g_chain_records][1] = ctas;
+  g_chain_log[g_chain_records][2] = (long long)g_chain_next;
+  ++g_chain_records;
+  g_chain_next += need;
+  return p;
+}
+
 int sm_count() {
   if (g_sm_count <= 0) {
     int dev = 0, n = 0;
@@ -43,7 +63,7 @@ int attn_decode(const void*, const float*, const float*, const int64_t*, void*, 
 int gemv_mma(const void*, const void*, const void*, void*, const void*, int, int, int, int, uint32_t*, cudaStream_t,
              const float* norm_w = nullptr, float eps = 0.f, const float* cosT = nullptr, const float* sinT = nullptr,
              const int64_t* pos = nullptr, void* kc = nullptr, void* vc = nullptr, int NH = 0, int NKV = 0, int HD = 0,
-             int max_len = 0, int withhold_chunk = -1);
+             int max_len = 0, int withhold_chunk = -1, const GemvLookahead* look = nullptr);
 int gemv_mma_ksplit(int, int);
 void gemv_mma_trace(unsigned long long*);
 size_t head_workspace(int);
@@ -223,6 +243,21 @@ int q4b_trace_buffer(uint64_t* device_buffer, size_t entries) {
   return Q4B_OK;
 }
 
+int q4b_trace_chain(uint64_t* device_buffer, size_t entries) {
+  g_chain_buf = reinterpret_cast<unsigned long long*>(device_buffer);
+  g_chain_entries = device_buffer ? entries : 0;
+  g_chain_next = 0;
+  if (device_buffer) g_chain_records = 0;
+  return Q4B_OK;
+}
+
+int q4b_trace_chain_log(int64_t* records, int max_records) {
+  const int n = g_chain_records < max_records ? g_chain_records : max_records;
+  for (int i = 0; i < n && records; ++i)
+    for (int j = 0; j < 3; ++j) records[3 * i + j] = g_chain_log[i][j];
+  return g_chain_records;
+}
+
 int q4b_rmsnorm_gemv_q4_0_tc(const void* W, const void* Sc, const float* h, const float* norm_w, float eps, void* Y,
                              const void* AUX, int N, int K, int epilogue, uint32_t* status, q4b_stream_t stream) {
   const int ldy = epilogue == Q4B_EPI_SWIGLU ? N / 2 : N;
@@ -255,15 +290,39 @@ int q4b_decode_step(const q4b_decode_desc* d, q4b_stream_t stream) {
   const bool fused_kv = mmap && d->head_dim > 0 && (128 % d->head_dim) == 0 && d->max_len <= 4096 &&
                         d->n_heads % d->n_kv_heads == 0 && d->n_heads / d->n_kv_heads <= 8 && (d->head_dim == 64 || d->head_dim == 128);
   // one linear: the mma.sync streaming GEMV or the tcgen05 kernel when its shape allows, the CUDA-core GEMV otherwise
-  auto lin = [&](const q4b_linear& L, const void* X, void* Y, const void* AUX, int epi) -> int {
-    if (mma_ok(L)) return gemv_mma(L.Wt, L.St, X, Y, AUX, L.N, L.K, 0, epi, d->status, st);
+  // L2 look-ahead: a launch asks for the packed weights of launches two to three places down the chain, so that their
+  // own bulk copies (issued one launch ahead, when their CTAs move in) find the lines in L2 instead of waiting on HBM
+  auto look_at = [&](GemvLookahead& g, int slot, const q4b_linear* L) {
+    if (!L || !L->Wt || !mma_ok(*L)) return;
+    const size_t tiles = (size_t)(L->N + 127) / 128, kb = (size_t)L->K / 32;
+    g.ptr[2 * slot] = L->Wt;
+    g.bytes[2 * slot] = tiles * kb * 2048;
+    g.ptr[2 * slot + 1] = L->St;
+    g.bytes[2 * slot + 1] = tiles * kb * 256;
+  };
+  auto lin = [&](const q4b_linear& L, const void* X, void* Y, const void* AUX, int epi, const q4b_linear* ahead0 = nullptr,
+                 const q4b_linear* ahead1 = nullptr) -> int {
+    if (mma_ok(L)) {
+      GemvLookahead g{};
+      look_at(g, 0, ahead0);
+      look_at(g, 1, ahead1);
+      return gemv_mma(L.Wt, L.St, X, Y, AUX, L.N, L.K, 0, epi, d->status, st, nullptr, 0.f, nullptr, nullptr, nullptr, nullptr, nullptr,
+                      0, 0, 0, 0, -1, &g);
+    }
     if (tcp && L.Wt && (L.K % 256) == 0)
       return mmq_stream(L.Wt, L.St, X, nullptr, Y, AUX, L.N, L.K, 1, 0, epi, epi == Q4B_EPI_SWIGLU ? L.N / 2 : L.N, d->status, st);
     return gemv_q4_0(L.W, L.S, X, Y, AUX, L.N, L.K, epi, Q4B_X_F16, st);
   };
   // RMSNorm followed by a linear: one launch on the tensor-core path (the norm is computed while staging the operand)
-  auto norm_lin = [&](const float* nw, const q4b_linear& L, void* Y, const void* AUX, int epi) -> int {
-    if (mma_ok(L)) return gemv_mma(L.Wt, L.St, d->h, Y, AUX, L.N, L.K, 3, epi, d->status, st, nw, d->eps);
+  auto norm_lin = [&](const float* nw, const q4b_linear& L, void* Y, const void* AUX, int epi, const q4b_linear* ahead0 = nullptr,
+                      const q4b_linear* ahead1 = nullptr) -> int {
+    if (mma_ok(L)) {
+      GemvLookahead g{};
+      look_at(g, 0, ahead0);
+      look_at(g, 1, ahead1);
+      return gemv_mma(L.Wt, L.St, d->h, Y, AUX, L.N, L.K, 3, epi, d->status, st, nw, d->eps, nullptr, nullptr, nullptr, nullptr, nullptr,
+                      0, 0, 0, 0, -1, &g);
+    }
     if (tcp && L.Wt && (L.K % 256) == 0)
       return mmq_stream(L.Wt, L.St, d->h, nullptr, Y, AUX, L.N, L.K, 1, 3, epi, epi == Q4B_EPI_SWIGLU ? L.N / 2 : L.N, d->status,
                         st, nw, d->eps);
@@ -280,18 +339,22 @@ int q4b_decode_step(const q4b_decode_desc* d, q4b_stream_t stream) {
   if (persistent) Q4B_TRY(decode_persistent_layers(d, d->persistent_ws, d->persistent_ws_bytes, st));
   for (int i = 0; i < d->layers && !persistent; ++i) {
     const q4b_layer& L = d->layer[i];
+    const q4b_layer* Ln = i + 1 < d->layers ? &d->layer[i + 1] : nullptr;
+    // look-ahead plan: qkv asks for gate/up, o for down, gate/up for the next layer's qkv and o
     if (fused_kv && mma_ok(L.qkv)) {
+      GemvLookahead g{};
+      look_at(g, 0, &L.gu);
       Q4B_TRY(gemv_mma(L.qkv.Wt, L.qkv.St, d->h, d->qkv, L.qkv_bias, L.qkv.N, L.qkv.K, 3, Q4B_EPI_BIASF_ROPE_KV, d->status, st, L.ln1,
-                       d->eps, d->cosT, d->sinT, d->pos, L.kc, L.vc, d->n_heads, d->n_kv_heads, d->head_dim, d->max_len));
+                       d->eps, d->cosT, d->sinT, d->pos, L.kc, L.vc, d->n_heads, d->n_kv_heads, d->head_dim, d->max_len, -1, &g));
       Q4B_TRY(attn_decode(d->qkv, nullptr, nullptr, d->pos, L.kc, L.vc, d->att, 1, d->n_heads, d->n_kv_heads, d->head_dim,
                           d->max_len, d->scale, nullptr, 0, st, 1));
     } else {
-      Q4B_TRY(norm_lin(L.ln1, L.qkv, d->qkv, L.qkv_bias, Q4B_EPI_BIASF));
+      Q4B_TRY(norm_lin(L.ln1, L.qkv, d->qkv, L.qkv_bias, Q4B_EPI_BIASF, &L.gu));
       Q4B_TRY(attn_decode(d->qkv, d->cosT, d->sinT, d->pos, L.kc, L.vc, d->att, 1, d->n_heads, d->n_kv_heads, d->head_dim,
                           d->max_len, d->scale, d->attn_ws, d->attn_ws_bytes, st));
     }
-    Q4B_TRY(lin(L.o, d->att, d->h, nullptr, Q4B_EPI_RESID));
-    Q4B_TRY(norm_lin(L.ln2, L.gu, d->act, nullptr, Q4B_EPI_SWIGLU));
+    Q4B_TRY(lin(L.o, d->att, d->h, nullptr, Q4B_EPI_RESID, &L.down));
+    Q4B_TRY(norm_lin(L.ln2, L.gu, d->act, nullptr, Q4B_EPI_SWIGLU, Ln ? &Ln->qkv : nullptr, Ln ? &Ln->o : nullptr));
     Q4B_TRY(lin(L.down, d->act, d->h, nullptr, Q4B_EPI_RESID));
   }
   (void)QR;

@@ -26,6 +26,8 @@
 //   * Split-K over the CTAs of a thread-block cluster; partial sums are pushed into the leader's shared memory and added
 //     in rank order, so results are bit-repeatable.
 // Every wait is bounded (status word + fall through).
+#include <cstdlib>
+
 #include "q4b_internal.h"
 #include "tc05.cuh"
 
@@ -59,9 +61,13 @@ struct GemvArgs {
   __half* kc;
   __half* vc;
   int NH, NKV, HD, max_len;
+  // look-ahead: up to four ranges (weights of launches further down the chain) that this grid asks to be brought into L2
+  const uint8_t* pf[4];
+  unsigned long long pf_bytes[4];
   // failure-path exercise (q4b_debug_gemv_mma_expired_wait): polls per wait, and a chunk whose copies are withheld
   uint32_t wait_limit;
   int withhold_chunk;
+  int wait_in_loop;      // 1: each warp waits for a chunk when it first needs it (streaming overlaps compute); 0: all up front
 };
 
 __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
@@ -76,6 +82,14 @@ __device__ __forceinline__ void mma_s8(int (&c)[4], uint32_t a0, uint32_t a1, ui
       "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
       : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// first MMA of a block: the C operand is the zero register, no accumulator initialisation
+__device__ __forceinline__ void mma_s8_zero(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%10, %10, %10, %10};"
+      : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
 }
 
 __device__ __forceinline__ bool mbar_wait_n(uint64_t* bar, uint32_t parity, uint32_t limit) {
@@ -119,16 +133,31 @@ __global__ void __launch_bounds__(GT, 2) gemv_mma_kernel(const GemvArgs a) {
   float* red_buf = red + 4 * ROWS;                        // split-K partials pushed by the peers: [rank - 1][128]
   const int nch = (nkb + CHK - 1) / CHK;
 
-  if (t == 0) {
-    for (int c = 0; c < nch; ++c) tc::mbar_init(&bar_load[c], 1);
+  if (t < nch) {                                          // lane c of warp 0 owns chunk c: barrier, then its two copies
+    const int c = t;
+    tc::mbar_init(&bar_load[c], 1);
     tc::mbar_fence_init();
     const size_t kbg = (size_t)tile * a.KB + kb0;         // first k-block of this CTA in the packed arrays
-    for (int c = 0; c < nch; ++c) {
-      const int n = min(CHK, nkb - c * CHK);
-      tc::mbar_expect_tx(&bar_load[c], (uint32_t)n * (2048 + 256));
-      if (c == a.withhold_chunk) continue;                // debug: this barrier never completes, its wait must give up
+    const int n = min(CHK, nkb - c * CHK);
+    tc::mbar_expect_tx(&bar_load[c], (uint32_t)n * (2048 + 256));
+    if (c != a.withhold_chunk) {                          // (debug: a withheld chunk never completes, its wait must give up)
       bulk_g2s(slabW + (size_t)c * CHK * 2048, a.W + (kbg + (size_t)c * CHK) * 2048, (uint32_t)n * 2048, &bar_load[c]);
       bulk_g2s(slabS + (size_t)c * CHK * 256, a.S + (kbg + (size_t)c * CHK) * 128, (uint32_t)n * 256, &bar_load[c]);
+    }
+  }
+  if (warp == 1) {
+    // L2 look-ahead for launches further down the chain: this CTA's share of each range, 16 KB per lane and trip.  A
+    // prefetch binds nothing and needs no completion; the later kernels' own bulk copies then find the lines in L2.
+    const unsigned long long ncta = (unsigned long long)gridDim.x * gridDim.y, cta = (unsigned long long)blockIdx.y * gridDim.x + blockIdx.x;
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      if (!a.pf[r]) continue;
+      const unsigned long long share = ((a.pf_bytes[r] + ncta - 1) / ncta + 127) & ~127ull;
+      const unsigned long long lo = cta * share, hi = min(a.pf_bytes[r], lo + share);
+      for (unsigned long long o = lo + (unsigned long long)lane * 16384; o < hi; o += 32ull * 16384) {
+        const uint32_t n = (uint32_t)min(16384ull, hi - o) & ~15u;
+        if (n) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(a.pf[r] + o), "r"(n) : "memory");
+      }
     }
   }
   __syncwarp();
@@ -167,6 +196,19 @@ __global__ void __launch_bounds__(GT, 2) gemv_mma_kernel(const GemvArgs a) {
   }
 
   // ---- activations -> four int8 digit planes in shared memory
+  // norm mode: this thread's share of the whole residual row (for the sum of squares) is requested first, so that it
+  // and the operand elements below are one round trip to memory, not two
+  constexpr int HSQ = 2;                                  // float4 per thread held in registers (K <= 4096); the rest loops
+  float4 hq[HSQ];
+  if (MODE == MODE_NORM) {
+    const float4* hv = reinterpret_cast<const float4*>(a.X);
+#pragma unroll
+    for (int u = 0; u < HSQ; ++u) {
+      const int i = t + u * GT;
+      hq[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (i < (a.K >> 2)) hq[u] = hv[i];
+    }
+  }
   float xin[MAXIT][4];
 #pragma unroll
   for (int u = 0; u < MAXIT; ++u) {
@@ -182,21 +224,29 @@ __global__ void __launch_bounds__(GT, 2) gemv_mma_kernel(const GemvArgs a) {
       } else {
         const float4 v = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(a.X) + k);
         xin[u][0] = v.x; xin[u][1] = v.y; xin[u][2] = v.z; xin[u][3] = v.w;
-        if (MODE == MODE_NORM) {                          // (v * r) * w is evaluated as (v * w) * r: r arrives last
-          xin[u][0] *= nw[u].x; xin[u][1] *= nw[u].y; xin[u][2] *= nw[u].z; xin[u][3] *= nw[u].w;
-        }
       }
     }
   }
+  // all of this CTA's weight chunks: warp w polls chunk w (one poll chain per warp, in parallel), the block barrier
+  // below publishes the async-proxy writes to everyone; the main loop then runs without touching a barrier
+  bool ok = true;
+  if (!a.wait_in_loop && lane == 0)
+    for (int c = warp; c < nch; c += GT / 32) ok = mbar_wait_n(&bar_load[c], 0, a.wait_limit) && ok;
   float rnorm = 1.f;
   if (MODE == MODE_NORM) {
     // RMSNorm of the whole residual row (RMSNORM_F32W_1P, lab/qwen_kernels.py:683-705): every CTA needs the full sum
-    // of squares; r = rsqrt(sum(v^2) / K + eps); x = round16(v * r * w).
+    // of squares; r = rsqrt(sum(v^2) / K + eps); x = round16(v * r * w), evaluated as (v * w) * r: r arrives last.
     const float4* hv = reinterpret_cast<const float4*>(a.X);
     float ss = 0.f;
-    for (int i = t; i < (a.K >> 2); i += GT) {
+#pragma unroll
+    for (int u = 0; u < HSQ; ++u) ss += hq[u].x * hq[u].x + hq[u].y * hq[u].y + hq[u].z * hq[u].z + hq[u].w * hq[u].w;
+    for (int i = t + HSQ * GT; i < (a.K >> 2); i += GT) {
       const float4 v = hv[i];
       ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    }
+#pragma unroll
+    for (int u = 0; u < MAXIT; ++u) {
+      xin[u][0] *= nw[u].x; xin[u][1] *= nw[u].y; xin[u][2] *= nw[u].z; xin[u][3] *= nw[u].w;
     }
     ss = warp_sum(ss);
     if (lane == 0) red_ss[warp] = ss;
@@ -252,8 +302,8 @@ __global__ void __launch_bounds__(GT, 2) gemv_mma_kernel(const GemvArgs a) {
   __syncthreads();
   stamp();                                                // 3: activation operand staged
 
-  // ---- main loop: this warp owns rows rg * 32 .. + 31 and k-blocks kg, kg + 4, ...
-  bool ok = true;
+  // ---- main loop: this warp owns rows rg * 32 .. + 31 and k-blocks kg, kg + 4, ...; two k-blocks per trip so that the
+  // shared-memory loads and the MMA chain of one overlap the other's
   float acc0 = 0.f, acc1 = 0.f;                           // rows rA, rA + 8, digit pair (tq & 1)
   const int rA = rg * 32 + g + 16 * (tq >> 1);
   const uint32_t m0 = g < 4 ? 0xFFFFFFFFu : 0u, m1 = ~m0;
@@ -261,13 +311,7 @@ __global__ void __launch_bounds__(GT, 2) gemv_mma_kernel(const GemvArgs a) {
   const uint8_t* xp0 = xdig + ((g & 3) * 4 + tq) * 8;
   const __half* sp0 = reinterpret_cast<const __half*>(slabS) + rA;
   const float* xs0 = reinterpret_cast<const float*>(xsc) + (tq & 1);
-  int cur = -1;
-  for (int kb = kg; kb < nkb; kb += 4) {
-    const int ch = kb / CHK;
-    if (ch != cur) {
-      ok = mbar_wait_n(&bar_load[ch], 0, a.wait_limit) && ok;   // this chunk's weights landed (async-proxy writes now visible)
-      cur = ch;
-    }
+  auto block_dot = [&](int kb, float& sA, float& fA, float& sB, float& fB) {   // -> scale and integer dot of rows rA, rA + 8
     const uint8_t* wp = wp0 + (size_t)kb * 2048;
     const uint32_t w0 = *reinterpret_cast<const uint32_t*>(wp);
     const uint32_t w1 = *reinterpret_cast<const uint32_t*>(wp + 8 * 16);
@@ -276,17 +320,38 @@ __global__ void __launch_bounds__(GT, 2) gemv_mma_kernel(const GemvArgs a) {
     const uint2 xw = *reinterpret_cast<const uint2*>(xp0 + (size_t)kb * 128);
     const float xs = xs0[2 * kb];
     const float dA = __half2float(sp0[kb * 128]), dB = __half2float(sp0[kb * 128 + 8]);
-    int c[4] = {0, 0, 0, 0};
+    int c[4];
     uint32_t e0, o0, e1, o1, e2, o2, e3, o3;
     tc::expand_nibbles(w0, e0, o0);
     tc::expand_nibbles(w1, e1, o1);
     tc::expand_nibbles(w2, e2, o2);
     tc::expand_nibbles(w3, e3, o3);
-    mma_s8(c, e0, e1, e2, e3, xw.x & m0, xw.x & m1);      // even weights of the four words
+    mma_s8_zero(c, e0, e1, e2, e3, xw.x & m0, xw.x & m1); // even weights of the four words
     mma_s8(c, o0, o1, o2, o3, xw.y & m0, xw.y & m1);      // odd weights
-    const float f0 = (float)(c[0] + (c[1] << 8)), f1 = (float)(c[2] + (c[3] << 8));
-    acc0 = fmaf(dA * xs, f0, acc0);
-    acc1 = fmaf(dB * xs, f1, acc1);
+    sA = dA * xs;
+    sB = dB * xs;
+    fA = (float)(c[0] + (c[1] << 8));
+    fB = (float)(c[2] + (c[3] << 8));
+  };
+  int kb = kg, landed = a.wait_in_loop ? -1 : nch;
+  for (; kb + 4 < nkb; kb += 8) {
+    if ((kb >> 3) > landed) {                             // both k-blocks of a trip lie in one chunk (kg < 4, CHK = 8)
+      landed = kb >> 3;
+      ok = mbar_wait_n(&bar_load[landed], 0, a.wait_limit) && ok;
+    }
+    float sa0, fa0, sb0, fb0, sa1, fa1, sb1, fb1;
+    block_dot(kb, sa0, fa0, sb0, fb0);
+    block_dot(kb + 4, sa1, fa1, sb1, fb1);
+    stamp();                                              // (thread 0 only) one per trip, while the trace has room
+    acc0 = fmaf(sa1, fa1, fmaf(sa0, fa0, acc0));          // k-blocks in ascending order
+    acc1 = fmaf(sb1, fb1, fmaf(sb0, fb0, acc1));
+  }
+  if (kb < nkb) {
+    if ((kb >> 3) > landed) ok = mbar_wait_n(&bar_load[kb >> 3], 0, a.wait_limit) && ok;
+    float sa0, fa0, sb0, fb0;
+    block_dot(kb, sa0, fa0, sb0, fb0);
+    acc0 = fmaf(sa0, fa0, acc0);
+    acc1 = fmaf(sb0, fb0, acc1);
   }
   acc0 += __shfl_xor_sync(0xffffffffu, acc0, 1);          // low digit pair + high digit pair
   acc1 += __shfl_xor_sync(0xffffffffu, acc1, 1);
@@ -312,7 +377,7 @@ __global__ void __launch_bounds__(GT, 2) gemv_mma_kernel(const GemvArgs a) {
       for (int r = 1; r < a.ksplit; ++r) v += red_buf[(r - 1) * ROWS + t];
   }
   stamp();                                                // 5: split-K reduced
-  if (!ok && t == 0) atomicOr(a.status, 1u);
+  if (!ok) atomicOr(a.status, 1u);
   if (ks != 0) return;
 
   if (a.epi == EPI_ROPE_KV) {
@@ -392,7 +457,8 @@ int gemv_mma_ksplit(int N, int K) {
 
 int gemv_mma(const void* W, const void* S, const void* X, void* Y, const void* AUX, int N, int K, int mode, int epi,
              uint32_t* status, cudaStream_t st, const float* norm_w, float eps, const float* cosT, const float* sinT,
-             const int64_t* pos, void* kc, void* vc, int NH, int NKV, int HD, int max_len, int withhold_chunk) {
+             const int64_t* pos, void* kc, void* vc, int NH, int NKV, int HD, int max_len, int withhold_chunk,
+             const GemvLookahead* look) {
   if (N <= 0 || K <= 0 || (K % 32)) return fail(Q4B_E_SHAPE, "gemv_q4_0_mma: N > 0 and K a positive multiple of 32 required");
   if (!W || !S || !X || !Y || !status || !aligned16(W) || !aligned16(S) || !aligned16(X))
     return fail(Q4B_E_ALIGN, "gemv_q4_0_mma: null or misaligned pointer");
@@ -419,12 +485,20 @@ int gemv_mma(const void* W, const void* S, const void* X, void* Y, const void* A
   a.AUX = AUX;
   a.status = status;
   a.trace = g_trace;
+  if (unsigned long long* slot = trace_slot(1, T * ks)) a.trace = slot;
   a.N = N; a.K = K; a.KB = KB; a.epi = epi; a.ksplit = ks;
   a.cosT = cosT; a.sinT = sinT; a.pos = pos;
   a.kc = reinterpret_cast<__half*>(kc); a.vc = reinterpret_cast<__half*>(vc);
   a.NH = NH; a.NKV = NKV; a.HD = HD; a.max_len = max_len;
   a.withhold_chunk = withhold_chunk;
+  for (int r = 0; r < 4; ++r) {
+    const bool on = look && look->ptr[r] && look->bytes[r] >= 16 && aligned16(look->ptr[r]);
+    a.pf[r] = on ? reinterpret_cast<const uint8_t*>(look->ptr[r]) : nullptr;
+    a.pf_bytes[r] = on ? (unsigned long long)look->bytes[r] : 0ull;
+  }
   a.wait_limit = withhold_chunk >= 0 ? 4096u : tc::WAIT_LIMIT;
+  static const int in_loop = [] { const char* e = getenv("Q4B_GEMV_WAIT_IN_LOOP"); return e ? atoi(e) : 0; }();
+  a.wait_in_loop = in_loop;
   dim3 grid(T, ks), block(GT);
   int rc;
   cudaError_t e;

@@ -4,6 +4,10 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <mutex>
+#include <set>
+#include <utility>
+
 #include "../../include/q4b200.h"
 
 namespace q4b {
@@ -33,6 +37,30 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 
 int sm_count();
 
+// Every kernel of the library asks for the largest shared-memory carve-out.  An SM can change its L1 / shared-memory
+// split only while it is idle, so a kernel that wants a different split than the one running cannot place a CTA beside
+// it; with one split everywhere the CTAs of a programmatically dependent launch can move in while their predecessor is
+// still running, which is what lets their weight prefetch overlap it.  Once per (kernel, device).
+inline void prefer_max_shared(const void* kern) {
+  static std::mutex mu;
+  static std::set<std::pair<const void*, int>> done;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return;
+  std::lock_guard<std::mutex> lock(mu);
+  if (done.insert({kern, dev}).second)
+    cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared);
+}
+
+// Ranges a batch-1 GEMV launch asks to be brought into L2 for launches further down the chain (see gemv_mma.cu).
+struct GemvLookahead {
+  const void* ptr[4];
+  size_t bytes[4];
+};
+
+// Chain timeline (q4b_trace_chain): while a buffer is set, every traced launch gets its own region of 16 stamps per CTA
+// and a host-side record (kernel id, CTAs, offset), so a captured graph keeps writing the same regions on every replay.
+unsigned long long* trace_slot(int kernel_id, int ctas);
+
 // Launch with the programmatic-dependent-launch attribute: the kernel may start while its predecessor in the stream is
 // still running, so it must call pdl_wait() before it touches anything the predecessor writes (every kernel in this
 // library does so before its first dependent access).  Captured into CUDA graphs as a programmatic edge.
@@ -41,6 +69,7 @@ int sm_count();
 // (__ldg / ld.global.nc, or a const __restrict__ pointer the compiler may route there).  Only weights and tables are.
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
+  prefer_max_shared(reinterpret_cast<const void*>(kern));
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = block;
@@ -58,6 +87,7 @@ inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, siz
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_pdl_cluster(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, unsigned cx,
                                       unsigned cy, Args&&... args) {
+  prefer_max_shared(reinterpret_cast<const void*>(kern));
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = block;

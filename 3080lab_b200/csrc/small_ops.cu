@@ -6,9 +6,12 @@ namespace q4b {
 namespace {
 
 // h[row] = float(E[tok[row]]), one CTA per row.  Reference: EMBED_F32 (lab/qwen_kernels.py:284-290) with an fp16 table.
+// The lookup opens every decode step, and it is the step's fence: it lets its dependents start only AFTER its own
+// dependency wait, i.e. after everything of the previous step has completed.  Later launches of the step may therefore
+// read state that only earlier steps wrote (the position, cache rows below it) ahead of their own waits.
 __global__ void __launch_bounds__(256) embed_kernel(const __half* __restrict__ E, const int64_t* tok, float* h, int H, int V) {
-  pdl_launch_dependents();
   pdl_wait();
+  pdl_launch_dependents();
   long long t = tok[blockIdx.x];
   t = t < 0 ? 0 : (t >= V ? V - 1 : t);
   const __half2* src = reinterpret_cast<const __half2*>(E + (size_t)t * H);

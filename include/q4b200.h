@@ -196,7 +196,11 @@ int q4b_debug_gemv_mma_expired_wait(const void* Wt, const void* St, const void* 
 
 /* Decode attention of one sequence when q is already rotated and position pos[0] is already in the cache
  * (q4b_rmsnorm_qkv_rope_kv did both): attention over positions 0 .. pos[0] only, no tables, no cache write.  Same
- * arithmetic as q4b_attn_decode (ATTN4, lab/qwen_kernels.py:548-603).  max_len <= 4096. */
+ * arithmetic as q4b_attn_decode (ATTN4, lab/qwen_kernels.py:548-603).  max_len <= 4096.
+ * The kernel reads pos[0] and the cache rows BELOW it ahead of its programmatic-dependency wait, so those must come from
+ * work that completed before the chain of programmatically dependent launches it sits in began: earlier decode steps
+ * (q4b_embed, which opens a step, releases its dependents only after everything before it has completed), a prefill, or
+ * a copy.  Only qkv and cache row pos[0] may come from the launch directly in front of it. */
 int q4b_attn_decode_cached(const void* qkv, const int64_t* pos, const void* kc, const void* vc, void* out, int NH, int NKV,
                            int HD, int max_len, float scale, q4b_stream_t stream);
 
@@ -229,6 +233,17 @@ int q4b_attn_prefill(const void* qkv, const float* cosT, const float* sinT, void
  * reference has the same facility (`timed=True`, lab/qwen_kernels.py:46-53).  entries >= 4096 * 16; null switches it
  * off.  Host-side global state: not thread-safe, meant for profiling runs. */
 int q4b_trace_buffer(uint64_t* device_buffer, size_t entries);
+
+/* Timeline of a whole chain of launches (for example one captured decode step): while a buffer is set, every launch of
+ * the batch-1 GEMV (kernel id 1) and of the one-sequence attention (id 2) takes the next free region of the buffer,
+ * 16 stamps per CTA as above, and the library keeps a host-side record per launch.  Because the region is fixed at
+ * launch (capture) time, replays of a captured graph rewrite the same regions.  q4b_trace_chain(null, 0) stops handing
+ * out regions (already captured launches keep theirs: keep the buffer alive while such a graph can run).
+ * q4b_trace_chain_log copies up to max_records records of three int64 (kernel id, CTAs, offset of the region in
+ * entries) to HOST memory and returns how many launches were recorded.  No reference counterpart beyond `timed=True`
+ * (lab/qwen_kernels.py:46-53).  Host-side global state: not thread-safe, meant for profiling runs. */
+int q4b_trace_chain(uint64_t* device_buffer, size_t entries);
+int q4b_trace_chain_log(int64_t* records, int max_records);
 
 /* RMSNorm fused in front of q4b_gemv_q4_0_tc: x = round16(h * rsqrt(mean(h^2) + eps) * norm_w) is formed while the
  * activation operand is staged, so the norm costs no launch (the reference tried the opposite fusion, norm in the
