@@ -142,7 +142,6 @@ __global__ void __launch_bounds__(AT, 2) attn_cached_kernel(const __half* qkv, c
           mma16816(sacc[j], qa[s][0], 0u, qa[s][1], 0u, b0, b1);
         }
       }
-      stamp();   // T: QK done
       // ---- mask, online soft-max (base 2) for head g
       float mx = m_run;
 #pragma unroll
@@ -173,7 +172,6 @@ __global__ void __launch_bounds__(AT, 2) attn_cached_kernel(const __half* qkv, c
         o[j][0] *= cor;
         o[j][1] *= cor;
       }
-      stamp();   // T: softmax done
       // ---- O += (P_hi + P_lo) V
 #pragma unroll
       for (int j = 0; j < 16; j += 2) {
@@ -194,12 +192,10 @@ __global__ void __launch_bounds__(AT, 2) attn_cached_kernel(const __half* qkv, c
         o[j + 1][1] = a1[1];
       }
     }
-    stamp();   // T: PV done
     // ---- merge the warps (each saw different positions of the chunk); warps without a tile contribute (-inf, 0)
     l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
     l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
-    __syncthreads();
-    stamp();   // T: sync1                                 // every warp is done with the K tile: its space takes the partials
+    __syncthreads();                                 // every warp is done with the K tile: its space takes the partials
     float* wo = reinterpret_cast<float*>(sK);        // [NW][MAXG][HD] = 32 KB <= cap x PITCH for cap >= 128
     if (g < GRP) {
 #pragma unroll
@@ -248,7 +244,6 @@ __global__ void __launch_bounds__(AT, 2) attn_cached_kernel(const __half* qkv, c
         }
       }
     }
-    stamp();   // T: pushed
   } else {
     asm volatile("cp.async.wait_group 0;" ::: "memory");
     asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");

@@ -67,7 +67,6 @@ struct GemvArgs {
   // failure-path exercise (q4b_debug_gemv_mma_expired_wait): polls per wait, and a chunk whose copies are withheld
   uint32_t wait_limit;
   int withhold_chunk;
-  int wait_in_loop;      // 1: each warp waits for a chunk when it first needs it (streaming overlaps compute); 0: all up front
 };
 
 __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
@@ -228,9 +227,10 @@ __global__ void __launch_bounds__(GT, 2) gemv_mma_kernel(const GemvArgs a) {
     }
   }
   // all of this CTA's weight chunks: warp w polls chunk w (one poll chain per warp, in parallel), the block barrier
-  // below publishes the async-proxy writes to everyone; the main loop then runs without touching a barrier
+  // below publishes the async-proxy writes to everyone; the main loop then runs without touching a barrier (a poll
+  // inside the loop, once per trip, was measured: each costs ~0.12 us even on a completed barrier, +40 % loop time)
   bool ok = true;
-  if (!a.wait_in_loop && lane == 0)
+  if (lane == 0)
     for (int c = warp; c < nch; c += GT / 32) ok = mbar_wait_n(&bar_load[c], 0, a.wait_limit) && ok;
   float rnorm = 1.f;
   if (MODE == MODE_NORM) {
@@ -333,12 +333,8 @@ __global__ void __launch_bounds__(GT, 2) gemv_mma_kernel(const GemvArgs a) {
     fA = (float)(c[0] + (c[1] << 8));
     fB = (float)(c[2] + (c[3] << 8));
   };
-  int kb = kg, landed = a.wait_in_loop ? -1 : nch;
+  int kb = kg;
   for (; kb + 4 < nkb; kb += 8) {
-    if ((kb >> 3) > landed) {                             // both k-blocks of a trip lie in one chunk (kg < 4, CHK = 8)
-      landed = kb >> 3;
-      ok = mbar_wait_n(&bar_load[landed], 0, a.wait_limit) && ok;
-    }
     float sa0, fa0, sb0, fb0, sa1, fa1, sb1, fb1;
     block_dot(kb, sa0, fa0, sb0, fb0);
     block_dot(kb + 4, sa1, fa1, sb1, fb1);
@@ -347,7 +343,6 @@ __global__ void __launch_bounds__(GT, 2) gemv_mma_kernel(const GemvArgs a) {
     acc1 = fmaf(sb1, fb1, fmaf(sb0, fb0, acc1));
   }
   if (kb < nkb) {
-    if ((kb >> 3) > landed) ok = mbar_wait_n(&bar_load[kb >> 3], 0, a.wait_limit) && ok;
     float sa0, fa0, sb0, fb0;
     block_dot(kb, sa0, fa0, sb0, fb0);
     acc0 = fmaf(sa0, fa0, acc0);
@@ -497,8 +492,6 @@ int gemv_mma(const void* W, const void* S, const void* X, void* Y, const void* A
     a.pf_bytes[r] = on ? (unsigned long long)look->bytes[r] : 0ull;
   }
   a.wait_limit = withhold_chunk >= 0 ? 4096u : tc::WAIT_LIMIT;
-  static const int in_loop = [] { const char* e = getenv("Q4B_GEMV_WAIT_IN_LOOP"); return e ? atoi(e) : 0; }();
-  a.wait_in_loop = in_loop;
   dim3 grid(T, ks), block(GT);
   int rc;
   cudaError_t e;

@@ -13,6 +13,10 @@ Fixtures:
   gemv_small.npz   a 64 x 256 GEMV drawn like lab/experiments/gemv5.py:40-46, dequantise-and-dot by reference code
   gemv_ffn_up.npz  the 8960 x 1536 ffn_up GEMV: y from the reference's fp32 dequantise-and-dot, and the float64 oracle
   q6_k_codec.npz   random Q6_K blocks -> reference q6_k_parts (q, scales, d) and the GGUF.f32 dequantisation
+  tensor_s8_known_answer.npz  the seeded int8 operands of the reference's tensor-core known-answer check
+                   (lab/experiments/tensor.py:171-179, which demands exact equality) and its expected A8 @ B8 + C8
+  rope_tables.npz  cos / sin rows computed by the reference's own statement (scripts/qwen_gguf.py:111-113, torch double
+                   -> float) for head_dim 128, theta 1e6, at a spread of positions
 """
 from __future__ import annotations
 
@@ -104,6 +108,26 @@ def main(ref_root: str) -> None:
         if n * k <= 1 << 16:
             out.update(q=q, d=d, x=x)
         np.savez_compressed(HERE / f"{name}.npz", **out)
+    # 5. the s8 known-answer inputs: the draw order of lab/experiments/tensor.py:171-179 (fp16 A, B, fp32 C first, then
+    # the int8 operands), expected result as computed there (:178)
+    rng = np.random.default_rng(7)
+    rng.standard_normal((16, 16)).astype(np.float16)
+    rng.standard_normal((16, 8)).astype(np.float16)
+    rng.standard_normal((16, 8)).astype(np.float32)
+    A8 = rng.integers(-128, 128, (16, 32)).astype(np.int8)
+    B8 = rng.integers(-128, 128, (32, 8)).astype(np.int8)
+    C8 = rng.integers(-1000, 1000, (16, 8)).astype(np.int32)
+    np.savez_compressed(HERE / "tensor_s8_known_answer.npz", A8=A8, B8=B8, C8=C8,
+                        ref8=A8.astype(np.int32) @ B8.astype(np.int32) + C8)
+
+    # 6. RoPE tables by the reference's statement, executed with torch on the CPU (scripts/qwen_gguf.py:111-113)
+    import torch
+    hd, theta = 128, 1e6
+    positions = list(range(0, 48)) + [63, 64, 127, 128, 511, 512, 513, 600, 767, 1023, 1024, 2047, 4095]
+    inv = 1.0 / (theta ** (torch.arange(0, hd, 2).double() / hd))
+    ang = torch.tensor(positions).double()[:, None] * inv[None]
+    np.savez_compressed(HERE / "rope_tables.npz", positions=np.array(positions), head_dim=hd, theta=theta,
+                        cos=torch.cos(ang).float().numpy(), sin=torch.sin(ang).float().numpy())
     print("fixtures written to", HERE)
 
 

@@ -43,3 +43,17 @@ def test_blockdot_exact_ragged(a_tmem, M, K, P):
 @pytest.mark.parametrize("a_tmem", [0, 1])
 def test_blockdot_extreme_values(a_tmem):
     case(256, 128, 16, a_tmem, extreme=True)
+
+
+@pytest.mark.parametrize("a_tmem", [0, 1])
+def test_blockdot_reference_known_answer_inputs(golden, a_tmem):
+    """The seeded int8 operands of the reference's own tensor-core known-answer check
+    (lab/experiments/tensor.py:171-179; exact equality required there) through the tcgen05 block-dot entry: the low
+    nibble of A8 is the Q4_0 weight (nibble - 8), B8 the int8 activations, one 32-wide block."""
+    g = golden["tensor_s8_known_answer"]
+    A8, B8 = g["A8"].astype(np.int32), g["B8"]
+    nib = (A8 & 15).astype(np.uint8)
+    W = pkg("gguf").pack_nibbles(nib)
+    xq = np.ascontiguousarray(B8.T)                                 # [8 columns, 32]
+    got = pkg("qwen_batched").blockdot(torch.from_numpy(W).cuda(), torch.from_numpy(xq).cuda(), 16, 32, a_tmem).cpu().numpy()
+    assert np.array_equal(got[:, :, 0].T, (nib.astype(np.int32) - 8) @ B8.astype(np.int32))

@@ -249,3 +249,31 @@ def test_gemv_mma_rejects_bad_arguments(QB):
     with pytest.raises(ffi.Q4BError) as e:                        # K beyond what one cluster of 8 CTAs can hold in shared memory
         QB.gemv_mma(W, S, x, y, None, 300, 24576, "logits", st)
     assert e.value.code == ffi.E_SHAPE
+
+
+@pytest.mark.parametrize("max_len", [256, 1024, 2048])
+def test_attn_cached_every_chunk_geometry(QB, max_len):
+    """The shared-memory-resident attention cuts the ACTUAL context into 8 chunks of whole 16-position warp tiles, so the
+    geometry changes with the position: first position, one short of / exactly / one past tile and chunk boundaries,
+    the last row of the cache.  Against the oracle's decode attention on the same cache."""
+    o = oracle()
+    NH, NKV, HD = 12, 2, 128
+    rng = np.random.default_rng(max_len)
+    kc = rng.standard_normal((NKV, max_len, HD)).astype(np.float16)
+    vc = rng.standard_normal((NKV, max_len, HD)).astype(np.float16)
+    kcd, vcd = dev(kc), dev(vc)
+    scale = 1.0 / np.sqrt(HD)
+    qkv = torch.zeros((NH + 2 * NKV) * HD, dtype=torch.float16, device="cuda")
+    att = torch.empty(NH * HD, dtype=torch.float16, device="cuda")
+    for p in sorted({0, 1, 14, 15, 16, 17, 126, 127, 128, 129, 130, 255, max_len // 2, max_len - 2, max_len - 1}):
+        if p >= max_len:
+            continue
+        q = rng.standard_normal((NH, HD)).astype(np.float16)
+        qkv[:NH * HD] = dev(q.reshape(-1))
+        att.fill_(float("nan"))
+        QB.attn_cached(qkv, dev(np.array([p], np.int64)), kcd, vcd, att, NH, NKV, HD, max_len, scale)
+        ref = o.attn_decode(q, kc, vc, p + 1, scale)
+        got = att.float().cpu().numpy().reshape(NH, HD)
+        assert np.isfinite(got).all(), f"p={p}"
+        assert nerr(got, ref) < 2e-3, f"p={p}"
+    assert torch.equal(kcd, dev(kc)) and torch.equal(vcd, dev(vc)), "the cached form must not write the cache"

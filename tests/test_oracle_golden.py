@@ -129,3 +129,32 @@ def test_q6_k_codec_matches_reference_vectors(golden):
     assert np.array_equal(d.view(np.uint16), z["d"].view(np.uint16))
     assert np.array_equal(G.q6_k_dequant(z["raw"]), z["f32"])
     assert q.min() >= -32 and q.max() <= 31
+
+
+def test_rope_tables_match_the_reference_statement(golden):
+    """cos / sin rows against the reference's own table statement (scripts/qwen_gguf.py:111-113) executed with torch:
+    float64 angles, rounded to fp32.  numpy's and torch's double cos / sin may differ in the last double bit, which can
+    move the fp32 rounding by one unit on rare entries, never more."""
+    g = golden["rope_tables"]
+    s = pkg("synth")
+    cfg = s.ModelConfig("t", 1, 128, 64, 1, 1, int(g["head_dim"]), 16, rope_theta=float(g["theta"]))
+    cos, sin = s.rope_tables(cfg, 4096)
+    pos = g["positions"]
+    for got, want in ((cos[pos], g["cos"]), (sin[pos], g["sin"])):
+        ulp = np.abs(got.view(np.int32).astype(np.int64) - want.view(np.int32).astype(np.int64))
+        assert ulp.max() <= 1 and (ulp > 0).mean() < 1e-3
+    assert np.array_equal(cos[0], np.ones(64, np.float32)) and np.array_equal(sin[0], np.zeros(64, np.float32))
+
+
+def test_blockdot_oracle_on_the_reference_known_answer_inputs(golden):
+    """The seeded int8 operands of the reference's tensor-core known-answer check (lab/experiments/tensor.py:171-179,
+    exact equality demanded there).  The fixture's expected product pins the operands; the Q4_0 block dot takes the low
+    nibble of A8 as the weight (value nibble - 8), one 32-wide block per row."""
+    o = oracle()
+    g = golden["tensor_s8_known_answer"]
+    A8, B8, C8 = g["A8"].astype(np.int32), g["B8"].astype(np.int32), g["C8"]
+    assert np.array_equal(g["ref8"], A8 @ B8 + C8)
+    nib = (A8 & 15).astype(np.uint8)                                # [16 rows, 32]
+    W = pkg("gguf").pack_nibbles(nib)                               # canonical words [16, 4]
+    got = o.blockdot(W, np.ascontiguousarray(g["B8"].T))            # xq [8 columns, 32] -> [8, 16, 1]
+    assert np.array_equal(got[:, :, 0].T, (nib.astype(np.int32) - 8) @ B8)
