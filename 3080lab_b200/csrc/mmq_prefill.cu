@@ -7,22 +7,25 @@
 // in ascending k order.  What changes is where things live on Blackwell:
 //   * CTA tile = 128 weight rows (UMMA M) x 128 activation rows (UMMA N); one tcgen05.mma.kind::i8 (K = 32) per k-block
 //     into one of three TMEM accumulator slots (128 columns each);
-//   * weights arrive tile-packed through bulk (TMA) copies in batches of 8 k-blocks (ring of 4); thread r of the first
-//     warpgroup expands row r's nibbles to signed bytes and writes them into TMEM as the A operand (tcgen05.st);
+//   * weights arrive tile-packed through bulk (TMA) copies in batches of 8 k-blocks (ring of 4); four EXPANDER warps
+//     (thread = row) turn nibbles into signed bytes 16 (q - 8) and write them into a ring of eight A operands in tensor
+//     memory (tcgen05.st), running ahead of the MMAs by up to eight k-blocks;
 //   * activations arrive pre-tiled from the quantiser (quant_q8_1.cu, "tiled" outputs): per (128-row tile, k-block)
 //     4096 bytes already in the UMMA K-major core-matrix order + 128 fp32 block scales, one bulk copy per stage
 //     (ring of 8), used directly as the B operand;
-//   * warps 8 and 10 (one thread each, even / odd k-blocks) issue the MMAs, warp 9 (one thread) the bulk copies;
-//     warpgroup 0 expands A and rescales accumulator columns 0..63, warpgroup 1 rescales columns 64..127; warpgroup 0
-//     rescales k-block b - 2 after expanding k-block b.  Barrier arrivals are one per warp (an elected lane after the
-//     warp-wide TMEM wait): with one arrival per thread the 640 shared-memory barrier updates per k-block were the
-//     bottleneck.
-// Measured per k-block on B200 (stamps of one CTA): ~770 ns, of which warpgroup 0 spends ~130-190 expanding, ~30 on
-// the accumulator read, ~270 on the rescale arithmetic and ~160 on barrier arrivals and loop overhead; an MMA to a fresh
-// accumulator tile retires in 278 clocks (146 ns); every mbarrier wait of an issuing thread costs ~160 ns even when the
-// barrier is already complete, which is why the "A ready" and "slot free" conditions share one barrier.
-// The per-block rescale (one int->float, two multiplies/FMAs per output per k-block) is CUDA-core work of the same
-// order as the tensor-core time at full rate; it is the structural cost of Q4_0 x Q8_1 and bounds this kernel.
+//   * one thread issues the MMAs, one the bulk copies;
+//   * SIXTEEN rescale warps (four per TMEM lane quarter, 32 accumulator columns each) read an accumulator slot back in
+//     two halves of 16 columns, scale by dw * dx and add into fp32 registers, on a rolling schedule: the read of the
+//     next half is always in flight while the previous one is folded.
+// The rescale is CUDA-core work: per output and k-block one integer add (exact int -> float through a magic constant,
+// as the reference plants it in the C operand of its mma.sync, lab/qwen_batched.py:1016-1041, 1237-1243) and three fp32
+// operations (subtract the constant, scale product, fused multiply-add).  Measured on B200: two-wide fp32 instructions
+// (f32x2) retire 128 lane-operations per clock and SM, the same as scalar ones, and integer adds share that rate, so a
+// 128 x 128 x 32 k-block costs >= 384 fp32 + integer clocks against 64 tensor-core clocks: this formulation of
+// Q4_0 x Q8_1 tops out near a sixth of the int8 peak whatever the pipeline does; the pipeline's job is to keep the
+// fp32 pipe busy.  (A variant that pre-loaded the accumulator slot with the magic constant through tcgen05.st, so
+// that the words came back as floats, was measured: the extra 64 KB of tensor-memory writes per k-block cost more than
+// the integer adds they saved.)
 // All waits are bounded; after the first expired wait a thread stops waiting (status word, garbage out, no hang).
 #include "q4b_internal.h"
 #include "tc05.cuh"
@@ -31,11 +34,12 @@ namespace q4b {
 
 namespace {
 
-// Accumulator slots in tensor memory (128 columns each; 3 x 128 + the A operands fill the 512 columns).  With three,
-// warpgroup 0 rescales k-block b - 2 after expanding k-block b, so the expand -> go -> MMA -> commit -> wake chain of one
-// k-block (~800 ns measured) spans two iterations instead of one.
-constexpr int NSLOT = 3;
-constexpr int PF_WG = 128, PF_THREADS = 2 * PF_WG + 96;   // two warpgroups + MMA warp (even k-blocks) + copy warp + MMA warp (odd)
+constexpr int NSLOT = 3;                  // accumulator slots in tensor memory (128 columns each)
+constexpr int NA = 8;                     // A operands in tensor memory (8 columns each)
+constexpr int NRW = 16;                   // rescale warps: (TMEM lane quarter) x (column quarter)
+constexpr int NEW = 4;                    // expander warps: one per TMEM lane quarter
+constexpr int PF_THREADS = (NRW + NEW + 2) * 32;   // + MMA warp + copy warp
+constexpr int W_MMA = NRW + NEW, W_COPY = NRW + NEW + 1;
 constexpr int NTOK = 128;                 // activation rows per CTA tile (UMMA N)
 constexpr int SB = 8;                     // activation stages (one k-block each)
 constexpr int WB = 4;                     // weight batches in flight (8 k-blocks each)
@@ -64,17 +68,22 @@ __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t by
 __device__ __forceinline__ void waitb(uint64_t* bar, uint32_t parity, bool& ok) {
   if (ok) ok = tc::mbar_wait(bar, parity);
 }
-
 __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const PrefillArgs a) {
   extern __shared__ __align__(128) uint8_t smem[];
-  __shared__ __align__(8) uint64_t w_full[WB], w_empty[WB], b_full[SB], b_empty[SB], go[NSLOT], d_full[NSLOT];
+  // "empty" barriers are waited on with the inverted parity the first time round (a fresh barrier reads as having
+  // completed the phase before its first), so no pre-arrivals are needed
+  // "empty" barriers are waited on with the inverted parity the first time round (a fresh barrier reads as having
+  // completed the phase before its first), so no pre-arrivals are needed.  (One combined barrier per k-block for the MMA
+  // issuer - operand written, stage landed, slot free - was measured: 8 % slower than these separate ones.)
+  __shared__ __align__(8) uint64_t w_full[WB], w_empty[WB], b_full[SB], b_empty[SB], a_full[NA], a_empty[NA], d_full[NSLOT],
+      d_empty[NSLOT];
   __shared__ uint32_t tmem_base_s;
 
   uint8_t* slabW = smem;                                   // [WB][8][128 rows][16]
   uint8_t* slabS = slabW + (size_t)WB * WBATCH_W;          // [WB][8][128] fp16
   uint8_t* stage = slabS + (size_t)WB * WBATCH_S;          // [SB][4608]
 
-  const int t = threadIdx.x, warp = t >> 5;
+  const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
   const int KB = a.K >> 5, NBATCH = KB >> 3;
   const int row_tile = blockIdx.x, tok_tile = blockIdx.y;
   const size_t wbase = (size_t)row_tile * KB;              // k-block index of this row tile in the packed arrays
@@ -84,38 +93,37 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const Prefil
     tc::tmem_alloc(&tmem_base_s, 512);
     tc::tmem_relinquish();
   }
-  if (t == 0) {
+  if (t == 32) {
     for (int i = 0; i < WB; ++i) {
       tc::mbar_init(&w_full[i], 1);
-      tc::mbar_init(&w_empty[i], 8);
+      tc::mbar_init(&w_empty[i], NEW + NRW);               // nibbles read by the expanders, scales by the rescale warps
     }
     for (int i = 0; i < SB; ++i) {
       tc::mbar_init(&b_full[i], 1);
-      tc::mbar_init(&b_empty[i], 1 + 8);
+      tc::mbar_init(&b_empty[i], 1 + NRW);                 // operand read by the MMA (commit), block scales by the rescale warps
+    }
+    for (int i = 0; i < NA; ++i) {
+      tc::mbar_init(&a_full[i], NEW);
+      tc::mbar_init(&a_empty[i], 1);                       // commit of the MMA that read it
     }
     for (int i = 0; i < NSLOT; ++i) {
-      // go[slot]: the A operand of k-block b is in tensor memory (4 expanding warps) AND the accumulator slot has been
-      // read out for k-block b - 2 (8 rescaling warps).  One barrier instead of two: every wait of the issuing thread
-      // costs ~160 ns even when the barrier is already complete.
-      tc::mbar_init(&go[i], 4 + 8);
-      tc::mbar_init(&d_full[i], 1);
+      tc::mbar_init(&d_full[i], 1);                        // commit of the MMA that wrote it
+      tc::mbar_init(&d_empty[i], NRW);                     // read out by every rescale warp
     }
     tc::mbar_fence_init();
-    for (int i = 0; i < NSLOT; ++i)
-      for (int k = 0; k < 8; ++k) tc::mbar_arrive(&go[i]);   // the first k-block of a slot has no predecessor to wait for
   }
   tc::fence_before_sync();
   __syncthreads();
   tc::fence_after_sync();
   pdl_launch_dependents();
   const uint32_t tmem = tmem_base_s;
-  const uint32_t tmem_a = tmem, tmem_d = tmem + 128;       // A: NSLOT x 8 columns; D: NSLOT x 128 columns
+  const uint32_t tmem_a = tmem, tmem_d = tmem + NA * 8;    // A: NA x 8 columns; D: NSLOT x 128 columns
   constexpr uint32_t IDESC = tc::idesc_i8(128, NTOK);
   bool ok = true;
 
-  if (warp == 9) {
+  if (warp == W_COPY) {
     // ===================== bulk-copy producer (one thread) =====================
-    if ((t & 31) == 0) {
+    if (lane == 0) {
       auto load_w = [&](int j) {                           // weight batch j -> slot j % WB
         const int s = j % WB;
         tc::mbar_expect_tx(&w_full[s], WBATCH_W + WBATCH_S);
@@ -144,94 +152,125 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const Prefil
         }
       }
     }
-  } else if (warp == 8 || warp == 10) {
-    // ===================== MMA issuers: one thread for the even k-blocks, one (in another warp) for the odd ones ==========
-    // Measured: one issuing thread spent ~700 ns per k-block on its three waits, the MMA and the two commits, which set
-    // the pace of the whole pipeline; the two slots are independent, so each gets its own issuer.
-    if ((t & 31) == 0) {
+  } else if (warp == W_MMA) {
+    // ===================== MMA issuer (one thread) =====================
+    if (lane == 0) {
       const uint32_t stage0 = tc::smem_u32(stage);
-      for (int b = warp == 8 ? 0 : 1; b < KB; b += 2) {
-        const int slot = b % NSLOT, s = b % SB;
-        waitb(&go[slot], (uint32_t)(b / NSLOT) & 1u, ok);
+      for (int b = 0; b < KB; ++b) {
+        const int slot = b % NSLOT, s = b % SB, as = b % NA;
+        waitb(&a_full[as], (uint32_t)(b / NA) & 1u, ok);
         waitb(&b_full[s], (uint32_t)(b / SB) & 1u, ok);
+        waitb(&d_empty[slot], ((uint32_t)(b / NSLOT) & 1u) ^ 1u, ok);   // the slot has been read out (k-block b - NSLOT)
         tc::fence_after_sync();
         const uint64_t bdesc = tc::smem_desc_kmajor(stage0 + (uint32_t)s * STAGE_BYTES, 128, 256);
-        tc::mma_i8_ts(tmem_d + (uint32_t)slot * 128, tmem_a + (uint32_t)slot * 8, bdesc, IDESC, 0u);
+        tc::mma_i8_ts(tmem_d + (uint32_t)slot * 128, tmem_a + (uint32_t)as * 8, bdesc, IDESC, 0u);
         tc::mma_commit(&d_full[slot]);
+        tc::mma_commit(&a_empty[as]);
         tc::mma_commit(&b_empty[s]);
       }
     }
-  } else {
-    // ===================== warpgroup 0: expand A + rescale columns 0..63; warpgroup 1: rescale columns 64..127 ======
-    const int wg = t >> 7, r = t & 127, lane = t & 31;     // r: row of the tile = TMEM lane
+  } else if (warp >= NRW) {
+    // ===================== expanders: thread = weight row, nibbles -> signed bytes -> A operand in tensor memory ==========
+    const int r = (warp - NRW) * 32 + lane;                // row of the tile = TMEM lane
     const uint32_t lane_off = (uint32_t)(32 * (warp & 3)) << 16;
-    uint64_t acc2[32];                                     // 64 fp32 accumulators as packed pairs
-#pragma unroll
-    for (int n = 0; n < 32; ++n) acc2[n] = 0ull;
-    const uint64_t neg_bias = tc::pack2(-tc::I2F_BIAS, -tc::I2F_BIAS);
-
-    auto rescale = [&](int b) {
-      const int slot = b % NSLOT, s = b % SB, ws = (b >> 3) % WB;
-      waitb(&d_full[slot], (uint32_t)(b / NSLOT) & 1u, ok);
+    for (int b = 0; b < KB; ++b) {
+      const int ws = (b >> 3) % WB, as = b % NA;
+      if ((b & 7) == 0) waitb(&w_full[ws], (uint32_t)((b >> 3) / WB) & 1u, ok);
+      const uint4 w = *reinterpret_cast<const uint4*>(slabW + (size_t)ws * WBATCH_W + (size_t)(b & 7) * 2048 + r * 16);
+      uint32_t ex[8];
+      tc::expand_nibbles(w.x, ex[0], ex[1]);
+      tc::expand_nibbles(w.y, ex[2], ex[3]);
+      tc::expand_nibbles(w.z, ex[4], ex[5]);
+      tc::expand_nibbles(w.w, ex[6], ex[7]);
+      waitb(&a_empty[as], ((uint32_t)(b / NA) & 1u) ^ 1u, ok);   // the MMA of k-block b - NA has read this operand
       tc::fence_after_sync();
-      uint32_t d[64];
-      const uint32_t dcol = tmem_d + lane_off + (uint32_t)slot * 128 + (uint32_t)wg * 64;
-      tc::tmem_ld16(dcol, d);
-      tc::tmem_ld16(dcol + 16, d + 16);
-      tc::tmem_ld16(dcol + 32, d + 32);
-      tc::tmem_ld16(dcol + 48, d + 48);
-      tc::tmem_wait_ld();                                  // warp-wide: every lane's accumulator values are in registers
+      tc::tmem_st8(tmem_a + lane_off + (uint32_t)as * 8, ex);
+      tc::tmem_wait_st();                                  // warp-wide
       tc::fence_before_sync();
-      if (lane == 0) tc::mbar_arrive(&go[slot]);           // one arrival per warp: the slot may be overwritten (k-block b + NSLOT)
-      const float dw = __half2float(reinterpret_cast<const __half*>(slabS + (size_t)ws * WBATCH_S)[(b & 7) * 128 + r]) * 0.0625f;
-      // per pair of outputs: two integer adds (exact int -> float through the magic constant), then three two-wide
-      // fp32 ops: subtract the bias, scale dw * dx, fused multiply-add into the accumulators
-      const ulonglong2* sx = reinterpret_cast<const ulonglong2*>(stage + (size_t)s * STAGE_BYTES + 4096) + wg * 16;
-      const uint64_t dw2 = tc::pack2(dw, dw);
+      if (lane == 0) {
+        tc::mbar_arrive(&a_full[as]);
+        if ((b & 7) == 7) tc::mbar_arrive(&w_empty[ws]);   // this warp is done with the batch's nibbles
+      }
+    }
+
+  } else {
+    // ===================== rescale warps: TMEM lane quarter lq (rows), column quarter cq (32 activation rows) ==========
+    const int lq = warp & 3, cq = warp >> 2;
+    const int r = lq * 32 + lane;
+    const uint32_t lane_off = (uint32_t)(32 * lq) << 16;
+    const uint32_t dbase = tmem_d + lane_off + (uint32_t)cq * 32;
+    uint64_t acc2[16];                                     // 32 fp32 accumulators as packed pairs
 #pragma unroll
-      for (int q = 0; q < 16; ++q) {
-        const ulonglong2 x4 = sx[q];                       // four block scales = two packed pairs
+    for (int n = 0; n < 16; ++n) acc2[n] = 0ull;
+    const uint64_t neg_bias = tc::pack2(-tc::I2F_BIAS, -tc::I2F_BIAS);
+    // 16 columns of one k-block: exact int -> float through the magic constant (two integer adds per pair), then three
+    // two-wide fp32 ops per pair: subtract the bias, scale product dw * dx, fused multiply-add
+    auto fold16 = [&](const uint32_t* d, const ulonglong2* sx, uint64_t dw2, int half) {
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const ulonglong2 x4 = sx[4 * half + q];            // four block scales = two packed pairs
         const uint64_t f0 = tc::add2(tc::pack2u(d[4 * q + 0] + tc::I2F_MAGIC, d[4 * q + 1] + tc::I2F_MAGIC), neg_bias);
         const uint64_t f1 = tc::add2(tc::pack2u(d[4 * q + 2] + tc::I2F_MAGIC, d[4 * q + 3] + tc::I2F_MAGIC), neg_bias);
-        acc2[2 * q + 0] = tc::fma2(tc::mul2(dw2, x4.x), f0, acc2[2 * q + 0]);
-        acc2[2 * q + 1] = tc::fma2(tc::mul2(dw2, x4.y), f1, acc2[2 * q + 1]);
+        acc2[8 * half + 2 * q + 0] = tc::fma2(tc::mul2(dw2, x4.x), f0, acc2[8 * half + 2 * q + 0]);
+        acc2[8 * half + 2 * q + 1] = tc::fma2(tc::mul2(dw2, x4.y), f1, acc2[8 * half + 2 * q + 1]);
       }
+    };
+    // Rolling schedule: the read-back of the next 16 columns is always in flight while the previous 16 are folded, so a
+    // warp does not sit idle on tensor-memory latency.  (Handing the slot back before folding anything was measured:
+    // slower, the exposed read latency costs more than the earlier release gains.)
+    uint32_t dA[16], dB[16];
+    if (KB > 0) {
+      waitb(&w_full[0], 0u, ok);
+      waitb(&d_full[0], 0u, ok);
+      tc::fence_after_sync();
+      tc::tmem_ld16(dbase, dA);
+      tc::tmem_wait_ld();
+    }
+    int slot = 0, s = 0;                                   // b % NSLOT, b % SB, kept incrementally
+    for (int b = 0; b < KB; ++b) {
+      const int ws = (b >> 3) & (WB - 1);
+      tc::tmem_ld16(dbase + (uint32_t)slot * 128 + 16, dB);      // second half of k-block b
+      const float dw = __half2float(reinterpret_cast<const __half*>(slabS + (size_t)ws * WBATCH_S)[(b & 7) * 128 + r]) * 0.0625f;
+      const ulonglong2* sx = reinterpret_cast<const ulonglong2*>(stage + (size_t)s * STAGE_BYTES + 4096) + cq * 8;
+      const uint64_t dw2 = tc::pack2(dw, dw);
+      fold16(dA, sx, dw2, 0);
+      tc::tmem_wait_ld();                                  // warp-wide: the slot is now entirely in registers
+      tc::fence_before_sync();
+      if (lane == 0) tc::mbar_arrive(&d_empty[slot]);      // one arrival per warp: the MMA of k-block b + NSLOT may overwrite it
+      const int nb = b + 1, nslot = slot + 1 == NSLOT ? 0 : slot + 1;
+      const uint32_t npar = (uint32_t)(nb / NSLOT) & 1u;
+      bool requested = false;
+      if (nb < KB) {
+        if ((nb & 7) == 0) waitb(&w_full[(nb >> 3) & (WB - 1)], (uint32_t)((nb >> 3) / WB) & 1u, ok);   // next batch's weight scales
+        if (tc::mbar_try(&d_full[nslot], npar)) {
+          tc::fence_after_sync();
+          tc::tmem_ld16(dbase + (uint32_t)nslot * 128, dA);
+          requested = true;
+        }
+      }
+      fold16(dB, sx, dw2, 1);
       __syncwarp();
       if (lane == 0) {
         tc::mbar_arrive(&b_empty[s]);                      // this warp is done with the stage's block scales
-        if ((b & 7) == 7) tc::mbar_arrive(&w_empty[ws]);   // ... and with the weight batch's scales and nibbles
+        if ((b & 7) == 7) tc::mbar_arrive(&w_empty[ws]);   // ... and with the weight batch's scales
       }
-    };
-
-    for (int b = 0; b < KB; ++b) {
-      if ((b & 7) == 0) waitb(&w_full[(b >> 3) % WB], (uint32_t)((b >> 3) / WB) & 1u, ok);
-      if (wg == 0) {
-        const int ws = (b >> 3) % WB, slot = b % NSLOT;
-        const uint4 w = *reinterpret_cast<const uint4*>(slabW + (size_t)ws * WBATCH_W + (size_t)(b & 7) * 2048 + r * 16);
-        uint32_t ex[8];
-        tc::expand_nibbles(w.x, ex[0], ex[1]);
-        tc::expand_nibbles(w.y, ex[2], ex[3]);
-        tc::expand_nibbles(w.z, ex[4], ex[5]);
-        tc::expand_nibbles(w.w, ex[6], ex[7]);
-        // the A slot was last read by the MMA of k-block b - NSLOT, whose completion this thread saw in rescale(b - NSLOT)
-        tc::tmem_st8(tmem_a + lane_off + (uint32_t)slot * 8, ex);
-        tc::tmem_wait_st();                                // warp-wide
-        tc::fence_before_sync();
-        if (lane == 0) tc::mbar_arrive(&go[slot]);
-        if (b >= NSLOT - 1) rescale(b - (NSLOT - 1));
-      } else {
-        rescale(b);
+      if (nb < KB && !requested) {
+        waitb(&d_full[nslot], npar, ok);
+        tc::fence_after_sync();
+        tc::tmem_ld16(dbase + (uint32_t)nslot * 128, dA);
       }
+      tc::tmem_wait_ld();
+      slot = nslot;
+      s = s + 1 == SB ? 0 : s + 1;
     }
-    if (wg == 0)
-      for (int b = max(KB - (NSLOT - 1), 0); b < KB; ++b) rescale(b);
 
-    // ---- epilogue: thread (row r, 64 activation rows)
+    // ---- epilogue: thread (row r, 32 activation rows)
     pdl_wait();                                            // Y / AUX may be written by the previous kernel
     const int row = row_tile * 128 + r;
-    const int tok0 = tok_tile * NTOK + wg * 64;
+    const int tok0 = tok_tile * NTOK + cq * 32;
+    const float bias = (a.epi == Q4B_EPI_BIASF && row < a.N) ? reinterpret_cast<const float*>(a.AUX)[row] : 0.f;
 #pragma unroll
-    for (int n = 0; n < 64; ++n) {                         // fully unrolled: the accumulators must stay in registers
+    for (int n = 0; n < 32; ++n) {                         // fully unrolled: the accumulators must stay in registers
       const float v = (n & 1) ? tc::hi2(acc2[n >> 1]) : tc::lo2(acc2[n >> 1]);
       const float partner = __shfl_xor_sync(0xffffffffu, v, 1);
       const int p = tok0 + n;
@@ -239,9 +278,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const Prefil
         const size_t base = (size_t)p * a.ldy;
         switch (a.epi) {
           case Q4B_EPI_STORE: reinterpret_cast<__half*>(a.Y)[base + row] = __float2half_rn(v); break;
-          case Q4B_EPI_BIASF:
-            reinterpret_cast<__half*>(a.Y)[base + row] = __float2half_rn(v + reinterpret_cast<const float*>(a.AUX)[row]);
-            break;
+          case Q4B_EPI_BIASF: reinterpret_cast<__half*>(a.Y)[base + row] = __float2half_rn(v + bias); break;
           case Q4B_EPI_RESID: reinterpret_cast<float*>(a.Y)[base + row] += v; break;
           case Q4B_EPI_LOGITS: reinterpret_cast<float*>(a.Y)[base + row] = v; break;
           case Q4B_EPI_SWIGLU:
