@@ -71,6 +71,7 @@ SIGNATURES = {
     "q4b_mmq_prefill_q4_0_q8_1": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P]),
     "q4b_attn_prefill": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P]),
     "q4b_trace_buffer": (_I, [_P, _Z]),
+    "q4b_peak_i8_launch": (C.c_double, [_I, _P, _P]),
     "q4b_trace_chain": (_I, [_P, _Z]),
     "q4b_trace_chain_log": (_I, [_P, _I]),
     "q4b_rmsnorm_gemv_q4_0_tc": (_I, [_P, _P, _P, _P, _F, _P, _P, _I, _I, _I, _P, _P]),

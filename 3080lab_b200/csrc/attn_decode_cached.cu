@@ -300,6 +300,7 @@ int attn_cached(const void* qkv, const int64_t* pos, const void* kc, const void*
   static size_t configured[64] = {};
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return fail(Q4B_E_CUDA, "attn_decode_cached: no current device");
+  prefer_max_shared(reinterpret_cast<const void*>(&attn_cached_kernel));
   if (smem > configured[dev]) {
     cudaError_t e = cudaFuncSetAttribute(attn_cached_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) {

@@ -65,6 +65,7 @@ int gemv_mma(const void*, const void*, const void*, void*, const void*, int, int
              const int64_t* pos = nullptr, void* kc = nullptr, void* vc = nullptr, int NH = 0, int NKV = 0, int HD = 0,
              int max_len = 0, int withhold_chunk = -1, const GemvLookahead* look = nullptr);
 int gemv_mma_ksplit(int, int);
+double peak_i8_launch(int, uint32_t*, cudaStream_t);
 void gemv_mma_trace(unsigned long long*);
 size_t head_workspace(int);
 int head_f16_argmax(const void*, const void*, float*, int, int, int64_t*, int64_t*, void*, size_t, cudaStream_t);
@@ -242,6 +243,8 @@ int q4b_trace_buffer(uint64_t* device_buffer, size_t entries) {
   attn_decode_mma_trace(reinterpret_cast<unsigned long long*>(device_buffer));
   return Q4B_OK;
 }
+
+double q4b_peak_i8_launch(int iters, uint32_t* status, q4b_stream_t stream) { return peak_i8_launch(iters, status, S(stream)); }
 
 int q4b_trace_chain(uint64_t* device_buffer, size_t entries) {
   g_chain_buf = reinterpret_cast<unsigned long long*>(device_buffer);

@@ -424,6 +424,7 @@ int configure(size_t bytes) {
   static size_t configured[64] = {};
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return fail(Q4B_E_CUDA, "gemv_q4_0_mma: no current device");
+  prefer_max_shared(reinterpret_cast<const void*>(&gemv_mma_kernel<MODE>));
   if (bytes > configured[dev]) {
     cudaError_t e = cudaFuncSetAttribute(gemv_mma_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_DYN_SMEM);
     if (e != cudaSuccess) {

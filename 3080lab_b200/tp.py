@@ -131,7 +131,11 @@ class TPBatched:
         self.head_ws = K.head_workspace(c.vocab, B, dv)
         self.status = QB.Status(dv)
         self.att_view = self.att[:, :c.q_rows] if self.ko == c.q_rows else None
+        # with K padding the attention output lands in a staging buffer first (allocated here, not inside step())
+        self._att_tmp = None if self.att_view is not None else torch.zeros(B, c.q_rows, dtype=f16, device=dv)
         self.allreduces_per_step = 2 * c.layers
+        groups = (B + 31) // 32                                          # column groups per linear (<= 32 rows per launch)
+        self.launches_per_step = 1 + c.layers * (4 + 4 * groups + 2 + (0 if self.att_view is not None else 1)) + 2 + groups
 
     def _gemm8(self, pair, N, Kdim, Y, aux, epi, ldy):
         """One linear over all B sequences; the tensor-core kernel takes up to 32 activation rows per launch."""
@@ -156,8 +160,6 @@ class TPBatched:
             self._gemm8(L["qkv"], c.qkv_rows, H, self.qkv, L["qkv_b"], "biasf", c.qkv_rows)
             if self.att_view is None:
                 # the attention kernel writes rows of c.q_rows values; with K padding they land in a staging buffer first
-                if not hasattr(self, "_att_tmp"):
-                    self._att_tmp = torch.zeros(self.B, c.q_rows, dtype=torch.float16, device=self.att.device)
                 K.attn(self.qkv, m.cos, m.sin, self.pos, self.kc[i], self.vc[i], self._att_tmp, c.n_heads, c.n_kv_heads,
                        c.head_dim, m.max_len, m.scale, self.attn_ws)
                 self.att[:, :c.q_rows].copy_(self._att_tmp)
@@ -184,7 +186,17 @@ class TPBatched:
         K.finish(self.logits, self.tok, self.pos, self.head_ws)
 
     def capture(self) -> torch.cuda.CUDAGraph:
-        """One `step()` (all-reduces included) as a CUDA graph; tok and pos are restored afterwards."""
+        """One `step()` as a CUDA graph (tok and pos are restored afterwards).  Only without a process group (tensor-parallel
+        degree 1): a graph that held the NCCL all-reduces of a 2-rank step never completed its first replay on B200
+        (driver 580, NCCL 2.28; no GPU fault, the run was ended by its time limit), and the cause has not been established.
+        Candidates that reading the capture path leaves open: programmatic-dependent-launch edges on the kernels directly
+        in front of and behind a captured NCCL kernel node; NCCL's internal stream joined into the capture through event
+        waits after a warm-up that ran on a side stream; two communicators (the world group for barriers, the tensor-
+        parallel group inside the graph) in flight on one GPU.  Until one of them is confirmed the multi-rank step is
+        launched op by op, and this method refuses to record the known-hanging form."""
+        if self.group is not None:
+            raise RuntimeError("TPBatched.capture: a CUDA graph holding the NCCL all-reduces did not complete on this "
+                               "platform; run step() op by op when a process group is set")
         torch.cuda.synchronize()
         pos0, tok0 = self.pos.clone(), self.tok.clone()
         side = torch.cuda.Stream()

@@ -234,6 +234,13 @@ int q4b_attn_prefill(const void* qkv, const float* cosT, const float* sinT, void
  * off.  Host-side global state: not thread-safe, meant for profiling runs. */
 int q4b_trace_buffer(uint64_t* device_buffer, size_t entries);
 
+/* Peak of the int8 tensor-core path on this device, for roofline denominators: one launch of `iters` back-to-back
+ * tcgen05.mma.kind::i8 (M 128, N 256, K 32) per SM onto one accumulator tile.  Returns the number of int8 operations the
+ * launch executes (0.0 on error); the caller times the launch with events and divides.  status: one uint32, set
+ * non-zero if the bounded completion wait expired.  (The reference measures its tensor peaks with a microbenchmark of
+ * the same kind, lab/experiments/tensor.py.) */
+double q4b_peak_i8_launch(int iters, uint32_t* status, q4b_stream_t stream);
+
 /* Timeline of a whole chain of launches (for example one captured decode step): while a buffer is set, every launch of
  * the batch-1 GEMV (kernel id 1) and of the one-sequence attention (id 2) takes the next free region of the buffer,
  * 16 stamps per CTA as above, and the library keeps a host-side record per launch.  Because the region is fixed at
