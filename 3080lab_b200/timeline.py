@@ -11,6 +11,12 @@ launch has no programmatic overlap with its neighbours and its weights sit in L2
     python 3080lab_b200/timeline.py mmq --batch 32    # the same four as Q8_1 x Q4_0 MMQ for 32 sequences
     python 3080lab_b200/timeline.py attn --batch 32   # batched decode attention, 1024-token context
     python 3080lab_b200/timeline.py persistent        # one token through the persistent all-layers kernel (8 layers)
+    python 3080lab_b200/timeline.py chain             # one captured batch-1 decode step of the full 1.5B shape, launch by launch
+
+`chain` uses `q4b_trace_chain`: every GEMV / attention launch of the captured step keeps its own stamp region, so the
+replayed graph shows when each launch's CTAs start (how far ahead of their dependency wait they move in), when the wait
+returns, and when the launch ends, all on one clock.  Stamp order of `attn_cached_kernel`: start, cache rows requested,
+predecessor complete, operands staged, chunk scored, cluster barrier passed, combined (first CTA of a cluster only).
 
 Stamp order of `gemv_mma_kernel`: start, bulk copies issued, predecessor complete, activation operand staged, main loop
 done, split-K reduced.  Of `mmq_stream_kernel`: start, TMEM allocated, barriers ready, bulk copies issued, predecessor complete,
@@ -59,14 +65,73 @@ def _traced(ffi, torch, fn, name: str) -> None:
     _report(name, buf)
 
 
+def _chain(torch, synth, engine, ffi) -> None:
+    import ctypes as C
+    cfg = synth.QWEN25_1P5B
+    m = engine.FusedQwen(synth.synth_model(cfg, 0), max_len=1024)
+    m.kc.normal_()
+    m.vc.normal_()
+    m.pos.fill_(600)
+    for _ in range(3):
+        m.step()
+    torch.cuda.synchronize()
+    buf = torch.zeros(8 << 20, dtype=torch.int64, device="cuda")
+    m.pos.fill_(600)
+    ffi.call("q4b_trace_chain", buf.data_ptr(), buf.numel())
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        m.step()
+    ffi.call("q4b_trace_chain", None, 0)
+    rec = (C.c_int64 * (3 * 4096))()
+    n = ffi.lib().q4b_trace_chain_log(rec, 4096)
+    recs = np.frombuffer(rec, dtype=np.int64)[:3 * n].reshape(n, 3)
+    for _ in range(5):
+        m.pos.fill_(600)
+        g.replay()
+    torch.cuda.synchronize()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    for _ in range(20):
+        g.replay()
+    e.record()
+    torch.cuda.synchronize()
+    print(f"step: {1e3 * s.elapsed_time(e) / 20:.1f} us per token while stamping (context 600..620)")
+    m.pos.fill_(600)
+    g.replay()
+    torch.cuda.synchronize()
+    m.check_status()
+    raw = buf.cpu().numpy()
+    names = {1: "gemv", 2: "attn"}
+    t00 = None
+    lo = 5 * (cfg.layers // 2)
+    print("launches of one layer in the middle of the step; us since the first stamp of the step")
+    print("kernel  CTAs   first start   last start   wait returns (median)   last stamp   all stamps (median over CTAs)")
+    for i, (kid, ctas, off) in enumerate(recs):
+        t = raw[off:off + ctas * 16].reshape(ctas, 16)
+        t = t[t[:, 15] > 0]
+        if t00 is None:
+            t00 = t[:, 0].min()
+        if not lo <= i < lo + 6:
+            continue
+        ns = int(np.median(t[:, 15]))
+        rel = (t[:, :ns] - t00) / 1e3
+        wi = 2 if kid == 1 else 2                       # both kernels stamp: start, requests issued, wait returned, ...
+        last = max(t[j, int(t[j, 15]) - 1] for j in range(len(t)))
+        print(f"{names[int(kid)]:6s} {int(ctas):5d} {rel[:, 0].min():12.2f} {rel[:, 0].max():12.2f} {np.median(rel[:, wi]):14.2f}"
+              f" {(last - t00) / 1e3:20.2f}   {np.round(np.median(rel, axis=0), 2).tolist()}")
+
+
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("what", choices=["gemv", "mmq", "attn", "persistent"])
+    ap.add_argument("what", choices=["gemv", "mmq", "attn", "persistent", "chain"])
     ap.add_argument("--batch", type=int, default=32)
     ap.add_argument("--tcgen05", action="store_true", help="gemv: the tcgen05 exact-digit kernel instead of the mma.sync one")
     args = ap.parse_args()
     import torch
     synth, engine, ffi, K = _mods()
+    if args.what == "chain":
+        _chain(torch, synth, engine, ffi)
+        return
     layers = 8 if args.what == "persistent" else 2
     cfg = synth.ModelConfig("qwen2.5-1.5b-cut", layers, 1536, 8960, 12, 2, 128, 8192)
     model = synth.synth_model(cfg, 0)
