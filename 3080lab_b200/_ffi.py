@@ -38,6 +38,7 @@ class DecodeDesc(C.Structure):
 STEP_TENSOR_CORE = 1
 STEP_PERSISTENT = 2
 STEP_MMA_GEMV = 4
+STEP_LOOKAHEAD = 8
 
 
 # name -> (restype, argtypes); every symbol include/q4b200.h declares

@@ -13,10 +13,13 @@
 //   * the context is cut into 8 equal chunks of the ACTUAL length (not of max_len), one CTA each, a thread-block
 //     cluster per KV head; all query heads of the KV group form one 16-row MMA operand, so K and V are read once;
 //   * after the wait only q (1.5 KB) and the row of the current position are fetched; S = Q K^T and O = P V run on
-//     mma.sync.m16n8k16 (fp16 inputs, fp32 accumulation; P as two fp16 terms so the probabilities keep ~22 bits), a
-//     warp owns 16 positions at a time, no block-wide barrier inside the loop;
-//   * warps are merged through shared memory, chunks are PUSHED into the first CTA's shared memory (st.shared::cluster)
-//     and combined there in chunk order after one cluster barrier: no workspace, no atomics, no remote loads.
+//     mma.sync.m16n8k16 (fp16 inputs, fp32 accumulation; P as two fp16 terms so the probabilities keep ~22 bits).
+//     For S a warp owns 16 POSITIONS; the probabilities go through shared memory, and for O a warp owns 16 output
+//     DIMENSIONS over all positions of the chunk, so the warps' outputs are disjoint and need no merge;
+//   * chunks are combined by all eight CTAs at once: warp w PUSHES its 16 dimensions into CTA w's shared memory
+//     (st.shared::cluster), every CTA pushes its (max, sum) pairs to all, and after ONE cluster barrier CTA j combines
+//     dimensions 16 j .. 16 j + 15 of every head in chunk order: no workspace, no atomics, no remote loads, a sixteenth of
+//     an output per thread.
 #include "q4b_internal.h"
 
 namespace q4b {
@@ -29,6 +32,7 @@ constexpr int NCL = 8;                         // chunks = cluster size
 constexpr int AT = 256, NW = AT / 32;
 constexpr int MAXG = 8;                        // query heads per KV head
 constexpr int MAX_CTX = 2048;                  // 8 chunks x 256 positions x 2 x 272 bytes of shared memory
+constexpr int PPITCH = (256 + 8) * 2;          // bytes per row of the staged probabilities (conflict-free fragment reads)
 
 __device__ __forceinline__ void mma16816(float* c, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
   asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
@@ -52,9 +56,9 @@ __global__ void __launch_bounds__(AT, 2) attn_cached_kernel(const __half* qkv, c
   uint8_t* sQ = sm;                                  // [16][PITCH]   q heads of the group (rows >= GRP zero)
   uint8_t* sK = sQ + 16 * PITCH;                     // [cap][PITCH]
   uint8_t* sV = sK + (size_t)cap * PITCH;            // [cap][PITCH]
-  __shared__ float wml[NW][MAXG][2];                 // per warp: (max, sum) in base-2 units
-  // combiner (meaningful in the cluster's first CTA): every chunk pushes its partial output and (max, sum) here
-  __shared__ __align__(16) float comb_o[NCL][MAXG][HD];
+  __shared__ float wmax[NW][MAXG], wsum[NW][MAXG];   // per warp and head: maximum score, sum of probabilities (base 2)
+  // combiner: this CTA owns output dimensions 16 c .. 16 c + 15; every chunk pushes its share and its (max, sum) here
+  __shared__ __align__(16) float comb_o[NCL][MAXG][16];
   __shared__ float comb_ml[NCL][MAXG][2];
 
   const int t = threadIdx.x, warp = t >> 5, lane = t & 31, g = lane >> 2, tq = lane & 3;
@@ -124,162 +128,138 @@ __global__ void __launch_bounds__(AT, 2) attn_cached_kernel(const __half* qkv, c
         qa[s][1] = *reinterpret_cast<const uint32_t*>(r0 + (16 * s + 2 * tq + 8) * 2);
       }
     }
-    float o[16][2];                                  // head g: 16 dim tiles x 2 columns
+    // ---- S = Q K^T: warp w scores positions 16 w .. 16 w + 15 (and + 128 k for chunks beyond 128 rows)
+    constexpr int MAXT = 2;                          // 16-position tiles per warp: chunks of up to 256 rows
+    float sacc[MAXT][2][4];
+    float mx = -INFINITY;                            // running maximum of head g over this warp's positions
 #pragma unroll
-    for (int j = 0; j < 16; ++j) o[j][0] = o[j][1] = 0.f;
-    float m_run = -INFINITY, l_run = 0.f;
-    for (int w0 = 16 * warp; w0 < rows; w0 += 16 * NW) {      // this warp's 16-position tiles (one for contexts <= 1024)
-      // ---- S = Q K^T
-      float sacc[2][4];
+    for (int it = 0; it < MAXT; ++it) {
+      const int w0 = 16 * warp + 128 * it;
 #pragma unroll
       for (int j = 0; j < 2; ++j) {
-        sacc[j][0] = sacc[j][1] = sacc[j][2] = sacc[j][3] = 0.f;
-        const uint8_t* kr = sK + (size_t)(w0 + 8 * j + g) * PITCH;
+        sacc[it][j][0] = sacc[it][j][1] = sacc[it][j][2] = sacc[it][j][3] = 0.f;
+        if (w0 < rows) {
+          const uint8_t* kr = sK + (size_t)(w0 + 8 * j + g) * PITCH;
 #pragma unroll
-        for (int s = 0; s < 8; ++s) {
-          const uint32_t b0 = *reinterpret_cast<const uint32_t*>(kr + (16 * s + 2 * tq) * 2);
-          const uint32_t b1 = *reinterpret_cast<const uint32_t*>(kr + (16 * s + 2 * tq + 8) * 2);
-          mma16816(sacc[j], qa[s][0], 0u, qa[s][1], 0u, b0, b1);
+          for (int s = 0; s < 8; ++s) {
+            const uint32_t b0 = *reinterpret_cast<const uint32_t*>(kr + (16 * s + 2 * tq) * 2);
+            const uint32_t b1 = *reinterpret_cast<const uint32_t*>(kr + (16 * s + 2 * tq + 8) * 2);
+            mma16816(sacc[it][j], qa[s][0], 0u, qa[s][1], 0u, b0, b1);
+          }
+        }
+        const int key = w0 + 8 * j + 2 * tq;
+        sacc[it][j][0] = key < rows ? sacc[it][j][0] * scale_log2e : -INFINITY;
+        sacc[it][j][1] = key + 1 < rows ? sacc[it][j][1] * scale_log2e : -INFINITY;
+        mx = fmaxf(mx, fmaxf(sacc[it][j][0], sacc[it][j][1]));
+      }
+    }
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+    if (tq == 0) wmax[warp][g] = mx;                 // -inf for a warp without a valid position
+    __syncthreads();
+    // ---- chunk maximum of head g, probabilities as two fp16 terms into shared memory (the A operand of P V)
+    float M = wmax[0][g];                            // finite: position 0 of the chunk is valid
+#pragma unroll
+    for (int w = 1; w < NW; ++w) M = fmaxf(M, wmax[w][g]);
+    uint8_t* sPh = sK;                               // [8 heads][PPITCH] fp16, over the K tile (every warp is done with it)
+    uint8_t* sPl = sK + 8 * PPITCH;
+    float ps = 0.f;
+#pragma unroll
+    for (int it = 0; it < MAXT; ++it) {
+      const int w0 = 16 * warp + 128 * it;
+      if (w0 < rows16) {
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          const float p0 = exp2f(sacc[it][j][0] - M), p1 = exp2f(sacc[it][j][1] - M);   // masked -> 0
+          ps += p0 + p1;
+          const __half2 h = __floats2half2_rn(p0, p1);
+          const float2 hf = __half22float2(h);
+          const int col = w0 + 8 * j + 2 * tq;
+          *reinterpret_cast<uint32_t*>(sPh + g * PPITCH + col * 2) = *reinterpret_cast<const uint32_t*>(&h);
+          *reinterpret_cast<uint32_t*>(sPl + g * PPITCH + col * 2) = pack_h2(p0 - hf.x, p1 - hf.y);   // P keeps ~22 bits
         }
       }
-      // ---- mask, online soft-max (base 2) for head g
-      float mx = m_run;
-#pragma unroll
-      for (int j = 0; j < 2; ++j) {
-        const int key = w0 + 8 * j + 2 * tq;
-        sacc[j][0] = key < rows ? sacc[j][0] * scale_log2e : -INFINITY;
-        sacc[j][1] = key + 1 < rows ? sacc[j][1] * scale_log2e : -INFINITY;
-        mx = fmaxf(mx, fmaxf(sacc[j][0], sacc[j][1]));
-      }
-      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));    // finite: position w0 < rows is valid
-      const float cor = exp2f(m_run - mx);
-      m_run = mx;
-      float ps = 0.f;
-      uint32_t ph[2], pl[2];                         // A fragments (row g): k 2tq.. and k 2tq + 8..
-#pragma unroll
-      for (int j = 0; j < 2; ++j) {
-        const float p0 = exp2f(sacc[j][0] - mx), p1 = exp2f(sacc[j][1] - mx);
-        ps += p0 + p1;
-        const __half2 h = __floats2half2_rn(p0, p1);
-        const float2 hf = __half22float2(h);
-        ph[j] = *reinterpret_cast<const uint32_t*>(&h);
-        pl[j] = pack_h2(p0 - hf.x, p1 - hf.y);       // second fp16 term: P keeps ~22 bits through the MMA
-      }
-      l_run = l_run * cor + ps;                      // per-lane partial; reduced over the quad at the end
-#pragma unroll
-      for (int j = 0; j < 16; ++j) {
-        o[j][0] *= cor;
-        o[j][1] *= cor;
-      }
-      // ---- O += (P_hi + P_lo) V
-#pragma unroll
-      for (int j = 0; j < 16; j += 2) {
-        const int mtx = lane >> 3, r = lane & 7;
-        const uint8_t* addr = sV + (size_t)(w0 + (mtx & 1) * 8 + r) * PITCH + (8 * (j + (mtx >> 1))) * 2;
-        uint32_t b0, b1, b2, b3;
-        asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
-                     : "=r"(b0), "=r"(b1), "=r"(b2), "=r"(b3)
-                     : "r"((uint32_t)__cvta_generic_to_shared(addr)));
-        float a0[4] = {o[j][0], o[j][1], 0.f, 0.f}, a1[4] = {o[j + 1][0], o[j + 1][1], 0.f, 0.f};
-        mma16816(a0, ph[0], 0u, ph[1], 0u, b0, b1);
-        mma16816(a0, pl[0], 0u, pl[1], 0u, b0, b1);
-        mma16816(a1, ph[0], 0u, ph[1], 0u, b2, b3);
-        mma16816(a1, pl[0], 0u, pl[1], 0u, b2, b3);
-        o[j][0] = a0[0];
-        o[j][1] = a0[1];
-        o[j + 1][0] = a1[0];
-        o[j + 1][1] = a1[1];
-      }
     }
-    // ---- merge the warps (each saw different positions of the chunk); warps without a tile contribute (-inf, 0)
-    l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
-    l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
-    __syncthreads();                                 // every warp is done with the K tile: its space takes the partials
-    float* wo = reinterpret_cast<float*>(sK);        // [NW][MAXG][HD] = 32 KB <= cap x PITCH for cap >= 128
-    if (g < GRP) {
-#pragma unroll
-      for (int j = 0; j < 16; ++j)
-        *reinterpret_cast<float2*>(wo + ((size_t)warp * MAXG + g) * HD + 8 * j + 2 * tq) = make_float2(o[j][0], o[j][1]);
-      if (tq == 0) {
-        wml[warp][g][0] = m_run;
-        wml[warp][g][1] = l_run;
-      }
-    }
+    ps += __shfl_xor_sync(0xffffffffu, ps, 1);
+    ps += __shfl_xor_sync(0xffffffffu, ps, 2);
+    if (tq == 0) wsum[warp][g] = ps;
     __syncthreads();
     stamp();                                         // 4: chunk scored
+    // ---- O = (P_hi + P_lo) V: warp w owns output dimensions 16 w .. 16 w + 15 of every head, over all positions
+    float o[2][4];
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt) o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.f;
+    for (int k0 = 0; k0 < rows16; k0 += 16) {
+      const int mtx = lane >> 3, r = lane & 7;       // matrices: (positions 0-7 | 8-15) x (dims +0 | +8)
+      const uint8_t* addr = sV + (size_t)(k0 + (mtx & 1) * 8 + r) * PITCH + (16 * warp + 8 * (mtx >> 1)) * 2;
+      uint32_t b0, b1, b2, b3;
+      asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                   : "=r"(b0), "=r"(b1), "=r"(b2), "=r"(b3)
+                   : "r"((uint32_t)__cvta_generic_to_shared(addr)));
+      const uint32_t ph0 = *reinterpret_cast<const uint32_t*>(sPh + g * PPITCH + (k0 + 2 * tq) * 2);
+      const uint32_t ph1 = *reinterpret_cast<const uint32_t*>(sPh + g * PPITCH + (k0 + 2 * tq + 8) * 2);
+      const uint32_t pl0 = *reinterpret_cast<const uint32_t*>(sPl + g * PPITCH + (k0 + 2 * tq) * 2);
+      const uint32_t pl1 = *reinterpret_cast<const uint32_t*>(sPl + g * PPITCH + (k0 + 2 * tq + 8) * 2);
+      mma16816(o[0], ph0, 0u, ph1, 0u, b0, b1);
+      mma16816(o[1], ph0, 0u, ph1, 0u, b2, b3);
+      mma16816(o[0], pl0, 0u, pl1, 0u, b0, b1);
+      mma16816(o[1], pl0, 0u, pl1, 0u, b2, b3);
+    }
+    // ---- push: this warp's 16 dimensions to CTA `warp`, the chunk's (max, sum) of every head to every CTA
     asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");   // pairs with the arrive at the top
-    uint32_t r_o, r_ml;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r_o) : "r"((uint32_t)__cvta_generic_to_shared(&comb_o[c][0][0])), "r"(0));
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r_ml) : "r"((uint32_t)__cvta_generic_to_shared(&comb_ml[c][0][0])), "r"(0));
-    // every load of the (at most four) outputs of a thread is issued before the first use: with eight warps per CTA the
-    // merge is a latency chain, not a throughput problem
-    constexpr int EPT = MAXG * HD / AT;              // outputs per thread
+    if (g < GRP) {
+      uint32_t r_o;
+      asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r_o) : "r"((uint32_t)__cvta_generic_to_shared(&comb_o[c][g][0])), "r"(warp));
 #pragma unroll
-    for (int i = 0; i < EPT; ++i) {
-      const int e = t + i * AT;
-      if (e < GRP * HD) {
-        const int hl = e / HD, d = e - hl * HD;
-        float mw[NW], lw[NW], ow[NW];
-#pragma unroll
-        for (int w = 0; w < NW; ++w) {
-          mw[w] = wml[w][hl][0];
-          lw[w] = wml[w][hl][1];
-          ow[w] = wo[((size_t)w * MAXG + hl) * HD + d];
-        }
-        float M = mw[0];
-#pragma unroll
-        for (int w = 1; w < NW; ++w) M = fmaxf(M, mw[w]);            // finite: warp 0 always has a valid position
-        float ov = 0.f, lv = 0.f;
-#pragma unroll
-        for (int w = 0; w < NW; ++w) {
-          const float f = exp2f(mw[w] - M);                          // -inf -> 0
-          ov += ow[w] * f;
-          lv += lw[w] * f;
-        }
-        asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(r_o + (uint32_t)(e * 4)), "f"(ov) : "memory");
-        if (d == 0) {
-          asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(r_ml + (uint32_t)(hl * 8)), "f"(M) : "memory");
-          asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(r_ml + (uint32_t)(hl * 8 + 4)), "f"(lv) : "memory");
-        }
+      for (int nt = 0; nt < 2; ++nt) {
+        asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(r_o + (uint32_t)((8 * nt + 2 * tq) * 4)), "f"(o[nt][0]) : "memory");
+        asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(r_o + (uint32_t)((8 * nt + 2 * tq + 1) * 4)), "f"(o[nt][1]) : "memory");
       }
+    }
+    if (t < NCL * MAXG) {                            // thread (target CTA, head)
+      const int tgt = t >> 3, hl = t & 7;
+      float Mh = wmax[0][hl], lh = 0.f;
+#pragma unroll
+      for (int w = 1; w < NW; ++w) Mh = fmaxf(Mh, wmax[w][hl]);
+#pragma unroll
+      for (int w = 0; w < NW; ++w) lh += wsum[w][hl];
+      uint32_t r_ml;
+      asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r_ml) : "r"((uint32_t)__cvta_generic_to_shared(&comb_ml[c][hl][0])), "r"(tgt));
+      asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(r_ml), "f"(Mh) : "memory");
+      asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(r_ml + 4u), "f"(lh) : "memory");
     }
   } else {
     asm volatile("cp.async.wait_group 0;" ::: "memory");
     asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
   }
-  cluster_sync_all();                                // every active chunk's partials are in the combiner
+  cluster_sync_all();                                // every active chunk's partials are in the combiners
   stamp();                                           // 5: cluster barrier passed
-  if (c != 0) return;
-  // chunk order, so the result does not depend on timing; every thread derives the weights itself (a few exp2)
-  constexpr int EPT2 = MAXG * HD / AT;
-#pragma unroll
-  for (int i = 0; i < EPT2; ++i) {
-    const int e = t + i * AT;
-    if (e < GRP * HD) {
-      const int hl = e / HD, d = e - hl * HD;
+  // chunk order, so the result does not depend on timing; thread (head, dimension) of this CTA's 16 dimensions
+  if (t < MAXG * 16) {
+    const int hl = t >> 4, dd = t & 15;
+    if (hl < GRP) {
       float mc[NCL], lc[NCL], oc[NCL];
 #pragma unroll
       for (int cc = 0; cc < NCL; ++cc) {
         const bool on = cc < nact;
         mc[cc] = on ? comb_ml[cc][hl][0] : -INFINITY;
         lc[cc] = on ? comb_ml[cc][hl][1] : 0.f;
-        oc[cc] = on ? comb_o[cc][hl][d] : 0.f;
+        oc[cc] = on ? comb_o[cc][hl][dd] : 0.f;
       }
-      float M = mc[0];
+      float Mx = mc[0];
 #pragma unroll
-      for (int cc = 1; cc < NCL; ++cc) M = fmaxf(M, mc[cc]);
+      for (int cc = 1; cc < NCL; ++cc) Mx = fmaxf(Mx, mc[cc]);
       float ov = 0.f, L = 0.f;
 #pragma unroll
       for (int cc = 0; cc < NCL; ++cc) {
-        const float w = exp2f(mc[cc] - M);
+        const float w = exp2f(mc[cc] - Mx);
         L += lc[cc] * w;
         ov += oc[cc] * w;
       }
-      out[(size_t)(kvh * GRP + hl) * HD + d] = __float2half_rn(ov / L);
+      out[(size_t)(kvh * GRP + hl) * HD + 16 * c + dd] = __float2half_rn(ov / L);
     }
   }
-  stamp();                                           // 6: combined (first CTA of the cluster only)
+  stamp();                                           // 6: combined
 }
 
 }  // namespace

@@ -331,6 +331,8 @@ typedef struct {
 #define Q4B_STEP_TENSOR_CORE 1  /* linears through q4b_gemv_q4_0_tc where K is a multiple of 256 */
 #define Q4B_STEP_PERSISTENT 2   /* all layers in one cooperative kernel (q4b_decode_persistent_layers) */
 #define Q4B_STEP_MMA_GEMV 4     /* linears through q4b_gemv_q4_0_mma, QKV through q4b_rmsnorm_qkv_rope_kv + q4b_attn_decode_cached */
+#define Q4B_STEP_LOOKAHEAD 8    /* with Q4B_STEP_MMA_GEMV: each GEMV launch also asks for the weights of launches two to three
+                                   places down the chain to be brought into L2 (cp.async.bulk.prefetch.L2); off by default */
 
 int q4b_decode_step(const q4b_decode_desc* desc, q4b_stream_t stream);
 
