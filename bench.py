@@ -422,6 +422,9 @@ def bench_prefill(model, cfg, steps: int, warmup: int, local_rank: int, torch, i
     ops = 2.0 * P * 46792704 * cfg.layers
     nominal_int8 = 4500.0
     ach_gu = ops_gu / us_gu / 1e6
+    # quality of int8 activations: mean next-token NLL of the first 512 prompt tokens under the prefill path and under
+    # the fp16-activation decode path (the reference's perplexity check, scripts/qwen_prefill.py:315-333)
+    nll = engine.perplexity(m, ids[:512], chunk=512)
     out = {
         "metric": "prefill_tok_per_s", "value": P / ms * 1e3, "unit": "tok/s", "n_gpus": 1, "steps": steps,
         "warmup": warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
@@ -436,6 +439,8 @@ def bench_prefill(model, cfg, steps: int, warmup: int, local_rank: int, torch, i
                      "peak_kind": "of measured (tcgen05.mma.kind::i8 micro-benchmark in this run)" if i8_peak.get("tops") else "of nominal dense int8",
                      "frac_of_nominal_4500": ach_gu / nominal_int8, "measured_i8_peak": i8_peak, "us_per_launch": us_gu, "traffic": None},
         "e2e": {"value": P / e2e_ms * 1e3, "unit": "tok/s", "h2d_bytes_per_step": P * 8, "d2h_bytes_per_step": 8},
+        "nll": {"int8_activations": nll["i8"], "fp16_activations": nll["f16"], "tokens": nll["tokens"],
+                "what": "mean next-token NLL over the first 512 prompt tokens (uniform random tokens), prefill path vs decode path"},
         "gpu_launches": pf.launches_per_chunk * steps, "clocks": clocks}
     del pf, m, g
     torch.cuda.empty_cache()

@@ -122,3 +122,19 @@ def test_chunked_prefill_equals_single_chunk():
     assert torch.equal(m1.vc[0], m2.vc[0])                               # layer 0 sees identical inputs
     rel = (m1.logits - m2.logits).abs().max() / m1.logits.abs().max()
     assert float(rel) < 2e-2
+
+
+def test_nll_of_int8_and_fp16_activation_paths_agree():
+    """The reference's quality check of int8 activations (scripts/qwen_prefill.py:315-333): mean next-token NLL over all
+    positions, prefill path (Q8_1 activations) against the token-by-token decode path (fp16 activations).  On a small
+    random-weight model the two must agree to well under one percent of the NLL itself."""
+    s, E = pkg("synth"), pkg("engine")
+    cfg = s.CONFIGS["small"]
+    model = s.synth_model(cfg, 7)
+    m = E.FusedQwen(model, max_len=128)
+    ids = s.synth_prompt(cfg, 128, 7)
+    r = E.perplexity(m, ids, chunk=64)
+    assert r["tokens"] == 127
+    assert np.isfinite(r["i8"]) and np.isfinite(r["f16"])
+    assert 0.5 * np.log(cfg.vocab) < r["f16"] < 2.0 * np.log(cfg.vocab)      # random weights: near the uniform level
+    assert abs(r["i8"] - r["f16"]) < 5e-3 * r["f16"]
