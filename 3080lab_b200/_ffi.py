@@ -32,7 +32,7 @@ class DecodeDesc(C.Structure):
                 ("norm", _P), ("head", Linear), ("cosT", _P), ("sinT", _P), ("tok", _P), ("pos", _P), ("h", _P),
                 ("x", _P), ("qkv", _P), ("att", _P), ("act", _P), ("logits", _P), ("attn_ws", _P), ("attn_ws_bytes", _Z),
                 ("head_ws", _P), ("head_ws_bytes", _Z), ("status", _P), ("flags", _I), ("persistent_ws", _P),
-                ("persistent_ws_bytes", _Z), ("head16", _P)]
+                ("persistent_ws_bytes", _Z), ("head16", _P), ("head_q6_L", _P), ("head_q6_H", _P), ("head_q6_SC", _P), ("head_q6_D", _P)]
 
 
 STEP_TENSOR_CORE = 1
@@ -54,6 +54,7 @@ SIGNATURES = {
     "q4b_attn_decode_q8_1": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _P]),
     "q4b_head_workspace": (_Z, [_I]),
     "q4b_head_f16_argmax": (_I, [_P, _P, _P, _I, _I, _P, _P, _P, _Z, _P]),
+    "q4b_head_q6_k_argmax": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _P, _P, _P, _Z, _P]),
     "q4b_argmax_advance_static": (_I, [_P, _I, _I, _P, _P, _P]),
     "q4b_head_f16_batched": (_I, [_P, _P, _P, _I, _I, _I, _P]),
     "q4b_argmax_workspace": (_Z, [_I, _I]),

@@ -66,6 +66,8 @@ int gemv_mma(const void*, const void*, const void*, void*, const void*, int, int
              int max_len = 0, int withhold_chunk = -1, const GemvLookahead* look = nullptr);
 int gemv_mma_ksplit(int, int);
 double peak_i8_launch(int, uint32_t*, cudaStream_t);
+int head_q6_k_argmax(const void*, const void*, const void*, const void*, const void*, float*, int, int, int64_t*, int64_t*, void*, size_t,
+                     cudaStream_t);
 void gemv_mma_trace(unsigned long long*);
 size_t head_workspace(int);
 int head_f16_argmax(const void*, const void*, float*, int, int, int64_t*, int64_t*, void*, size_t, cudaStream_t);
@@ -151,6 +153,11 @@ size_t q4b_head_workspace(int V) { return head_workspace(V); }
 int q4b_head_f16_argmax(const void* E, const void* x, float* logits, int V, int H, int64_t* tok, int64_t* pos,
                         void* workspace, size_t workspace_bytes, q4b_stream_t stream) {
   return head_f16_argmax(E, x, logits, V, H, tok, pos, workspace, workspace_bytes, S(stream));
+}
+
+int q4b_head_q6_k_argmax(const void* L, const void* Hb, const void* SC, const void* D, const void* x, float* logits, int V, int K,
+                         int64_t* tok, int64_t* pos, void* workspace, size_t workspace_bytes, q4b_stream_t stream) {
+  return head_q6_k_argmax(L, Hb, SC, D, x, logits, V, K, tok, pos, workspace, workspace_bytes, S(stream));
 }
 
 int q4b_argmax_advance_static(const float* logits, int rows, int V, int64_t* tok, int64_t* pos, q4b_stream_t stream) {
@@ -368,6 +375,10 @@ int q4b_decode_step(const q4b_decode_desc* d, q4b_stream_t stream) {
   if (d->head.W) {
     Q4B_TRY(norm_lin(d->norm, d->head, d->logits, nullptr, Q4B_EPI_LOGITS));
     Q4B_TRY(argmax_advance(d->logits, 1, d->vocab, d->tok, d->pos, d->head_ws, d->head_ws_bytes, st));
+  } else if (d->head_q6_L && d->head_q6_H && d->head_q6_SC && d->head_q6_D && (H % 512) == 0 && H <= 2048) {
+    Q4B_TRY(rmsnorm(d->h, d->norm, d->x, 1, H, d->eps, st));
+    Q4B_TRY(head_q6_k_argmax(d->head_q6_L, d->head_q6_H, d->head_q6_SC, d->head_q6_D, d->x, d->logits, d->vocab, H, d->tok, d->pos,
+                             d->head_ws, d->head_ws_bytes, st));
   } else {
     Q4B_TRY(rmsnorm(d->h, d->norm, d->x, 1, H, d->eps, st));
     Q4B_TRY(head_f16_argmax(d->head16 ? d->head16 : d->embed, d->x, d->logits, d->vocab, H, d->tok, d->pos, d->head_ws,

@@ -48,6 +48,11 @@ class FusedQwen:
         self.head = None if model["head"] is None else tuple(_dev(a, self.device) for a in model["head"])
         # fp16 LM head table: the embedding (tied) unless the model brings its own (a GGUF `output.weight` kept in fp16)
         self.head16 = self.embed if model.get("head16") is None else _dev(model["head16"], self.device)
+        # a Q6_K head kept at 6.5625 bits per weight (planes of gguf.q6_k_planes): used by the batch-1 step
+        q6 = model.get("head_q6")
+        self.head_q6 = None
+        if q6 is not None and self.head is None and c.hidden % 512 == 0 and c.hidden <= 2048:
+            self.head_q6 = tuple(_dev(a, self.device) for a in q6)
         # tile-packed copies for the tensor-core kernels (K a multiple of 256)
         self.tensor_core = tensor_core
         self.mma = bool(mma and tensor_core)
@@ -123,7 +128,8 @@ class FusedQwen:
             self.attn_ws.data_ptr(), self.attn_ws.numel(), self.head_ws.data_ptr(), self.head_ws.numel(),
             self.status.data_ptr(),
             (_ffi.STEP_TENSOR_CORE if self.tensor_core else 0) | (_ffi.STEP_MMA_GEMV if self.mma else 0), None, 0,
-            None if self.head16 is self.embed else self.head16.data_ptr())
+            None if self.head16 is self.embed else self.head16.data_ptr(),
+            *(tuple(a.data_ptr() for a in self.head_q6) if self.head_q6 is not None else (None, None, None, None)))
 
     # ---- one decode token -------------------------------------------------------------------------------------------
     def step(self) -> None:
@@ -196,7 +202,10 @@ class FusedQwen:
             self.gemv("o", L["o"], self.att, self.h, None, H, c.q_rows, "resid")
             self.norm_gemv(L["ln2"], L["gu"], self.xm, None, 2 * c.ffn, H, "swiglu")
             self.gemv("down", L["down"], self.xm, self.h, None, H, c.ffn, "resid")
-        if self.head is None:
+        if self.head is None and self.head_q6 is not None:
+            self.rms(self.norm, self.x)
+            K.head_q6_argmax(self.head_q6, self.x, self.logits, self.tok, self.pos, self.head_ws)
+        elif self.head is None:
             self.rms(self.norm, self.x)
             K.head_argmax(self.head16, self.x, self.logits, self.tok, self.pos, self.head_ws)
         else:

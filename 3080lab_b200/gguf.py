@@ -162,6 +162,47 @@ def q6_k_dequant(b: np.ndarray) -> np.ndarray:
     return (np.repeat(scale, 16, axis=1) * q.astype(np.float32)).reshape(-1)
 
 
+def _q6_hi_shift(i: int) -> int:
+    """Bit position of the two high bits of weight i (0..15) inside its word of the Hb plane: byte (i % 8) // 2, slot
+    (i % 2) + 2 * (i // 8).  With that order ((Hb << 4) & 0x30303030), ((Hb << 2) & ...), (Hb & ...), ((Hb >> 2) & ...)
+    are the high bits of weights (0,2,4,6), (1,3,5,7), (8,10,12,14), (9,11,13,15) already sitting at bits 4-5 of the
+    bytes that the low-nibble words give for the same weights, so four 6-bit codes cost three instructions."""
+    return 8 * ((i % 8) // 2) + 2 * ((i % 2) + 2 * (i // 8))
+
+
+def q6_k_planes(b: np.ndarray, n_rows: int, k: int):
+    """Raw Q6_K bytes of an [n_rows, k] matrix -> the device planes of the Q6_K head kernel: L int32 [N, K/8] (low
+    nibbles of q + 32, nibble i of word w = weight 8w+i, as the reference's plane, scripts/qwen_gguf.py:92-104), Hb int32
+    [N, K/16] (high two bits of the 16 weights of a sub-block, at the bit positions of `_q6_hi_shift`; the reference uses
+    field i = weight i), SC int8 [N, K/16], D fp16 [N, K/256].  Same 6.5625 bits per weight as the file."""
+    if k % 256:
+        raise ValueError("K must be a multiple of the 256-weight Q6_K block")
+    q, sc, d = q6_k_values(b)
+    code = (q.astype(np.int16) + 32).reshape(n_rows, k).astype(np.uint32)            # 0..63
+    lo = np.zeros((n_rows, k // 8), np.uint32)
+    for i in range(8):
+        lo |= (code[:, i::8] & 15) << np.uint32(4 * i)
+    hi = np.zeros((n_rows, k // 16), np.uint32)
+    for i in range(16):
+        hi |= (code[:, i::16] >> 4) << np.uint32(_q6_hi_shift(i))
+    return (lo.view(np.int32), hi.view(np.int32), np.ascontiguousarray(sc.reshape(n_rows, k // 16)),
+            np.ascontiguousarray(d.reshape(n_rows, k // 256)))
+
+
+def q6_k_planes_dense(L, Hb, SC, D, dtype=np.float64) -> np.ndarray:
+    """The planes back to dense weights (d * sc) * (q - 32), the fp32 scale product formed first as in the kernel and in
+    the reference's `q6_k_blocks` (lab/gguf.py:95-113).  -> [N, K]."""
+    L, Hb = np.asarray(L).view(np.uint32), np.asarray(Hb).view(np.uint32)
+    n, k = L.shape[0], L.shape[1] * 8
+    code = np.zeros((n, k), np.int32)
+    for i in range(8):
+        code[:, i::8] = (L >> np.uint32(4 * i)) & 15
+    for i in range(16):
+        code[:, i::16] |= ((Hb >> np.uint32(_q6_hi_shift(i))) & 3).astype(np.int32) << 4
+    scale = np.repeat(np.asarray(D, np.float32), 16, axis=1) * np.asarray(SC, np.float32)   # [N, K/16], fp32 product
+    return (np.repeat(scale, 16, axis=1).astype(dtype) * (code - 32).astype(dtype))
+
+
 def q4_0_encode(q: np.ndarray, d: np.ndarray) -> np.ndarray:
     """Inverse of `q4_0_blocks`: q uint8 [..., 32] in weight order (0..15), d fp16 [...] -> uint8 bytes [nblk * 18]."""
     q = np.asarray(q, np.uint8).reshape(-1, 32)

@@ -11,7 +11,8 @@ in the canonical device layout (`gguf.pack_nibbles`).  `GGUFQwen(path)` is `Fuse
 Supported tensor types: Q4_0 for the layer matrices; Q4_0, Q6_K, F16 or F32 for `token_embd` (kept as an fp16 table:
 everything but F16 is rounded to fp16, the reference keeps fp32); `output.weight` absent (tied head), Q4_0 (the Q4_0
 head path), or Q6_K / F16 / F32 (dequantised on the host into an untied fp16 head table, `model["head16"]`).  The
-reference runs a Q6_K head with its own GEMV kernel at 6.5625 bits per weight (scripts/qwen_gguf.py:92-113); here such a
+reference runs a Q6_K head with its own GEMV kernel at 6.5625 bits per weight (scripts/qwen_gguf.py:92-113); so does the
+batch-1 decode step here (`model["head_q6"]`, q4b_head_q6_k_argmax) when hidden is 512 .. 2048; for the other paths such a
 head costs 16 bits per weight and its values carry one fp16 rounding (relative 2^-11), which is the documented
 difference of this loader.
 
@@ -55,7 +56,7 @@ def load_model(path) -> dict:
         embed = g.f32("token_embd.weight").astype(np.float16)
     else:
         raise NotImplementedError(f"token_embd.weight is {_type_name(emb_t.type)}; Q4_0, Q6_K, F16 and F32 are supported")
-    head, head16 = None, None
+    head, head16, head_q6 = None, None, None
     if "output.weight" in g.tensors:
         t = g.tensors["output.weight"]
         if t.type == _Q4_0:
@@ -63,7 +64,12 @@ def load_model(path) -> dict:
             head = (G.pack_nibbles(q), d)
         elif t.type == _F16:
             head16 = np.ascontiguousarray(g.raw("output.weight")[0]).view(np.float16).reshape(vocab, H).copy()
-        elif t.type in (_F32, _Q6_K):
+        elif t.type == _Q6_K:
+            # kept at 6.5625 bits per weight for the batch-1 head kernel (q4b_head_q6_k_argmax); the fp16 table is what
+            # the batched and prefill paths use
+            head_q6 = G.q6_k_planes(g.raw("output.weight")[0], vocab, H)
+            head16 = g.f32("output.weight").astype(np.float16)
+        elif t.type == _F32:
             head16 = g.f32("output.weight").astype(np.float16)
         else:
             raise NotImplementedError(f"output.weight is {_type_name(t.type)}; Q4_0, Q6_K, F16 and F32 are supported")
@@ -93,7 +99,7 @@ def load_model(path) -> dict:
     cfg = ModelConfig(str(m.get("general.name", arch)), nL, H, ffn, nh, nkv, hd, vocab, eps, theta,
                       tied_fp16_head=head is None)            # True also for an untied fp16 table (model["head16"])
     return {"cfg": cfg, "embed": embed, "layers": layers, "norm": g.f32("output_norm.weight").astype(np.float32).copy(),
-            "head": head, "head16": head16}
+            "head": head, "head16": head16, "head_q6": head_q6}
 
 
 def _q4_tensor(W: np.ndarray, S: np.ndarray):

@@ -87,6 +87,14 @@ def head_argmax(E, x, logits, tok, pos, ws) -> None:
               _stream())
 
 
+def head_q6_argmax(planes, x, logits, tok, pos, ws) -> None:
+    """logits = Q6_K(planes) . x at 6.5625 bits per weight, tok = argmax (lowest index), pos += 1 — gemv_q6_source +
+    FINISH_MB in one launch (lab/qwen_kernels.py:608-678, 250-282).  planes = (L, Hb, SC, D) from gguf.q6_k_planes."""
+    L, Hb, SC, D = planes
+    _ffi.call("q4b_head_q6_k_argmax", _p(L), _p(Hb), _p(SC), _p(D), _p(x), _p(logits), L.shape[0], L.shape[1] * 8, _p(tok),
+              _p(pos), _p(ws), ws.numel(), _stream())
+
+
 def finish(logits, tok, pos, ws) -> None:
     """tok = argmax(logits) per row with the lowest-index tie rule, pos += 1 (FINISH, lab/qwen_kernels.py:222-243)."""
     rows = 1 if logits.dim() == 1 else logits.shape[0]

@@ -107,6 +107,16 @@ size_t q4b_head_workspace(int V);
 int q4b_head_f16_argmax(const void* E, const void* x, float* logits, int V, int H, int64_t* tok, int64_t* pos,
                         void* workspace, size_t workspace_bytes, q4b_stream_t stream);
 
+/* LM head stored as Q6_K (the `output.weight` of llama.cpp's Q4_0 exports), 6.5625 bits per weight, greedy pick fused:
+ * logits fp32 [V] = sum over 16-weight sub-blocks of (d * sc) * sum (q - 32) * x, fp32.  Replaces gemv_q6_source + FINISH_MB
+ * (lab/qwen_kernels.py:608-678, 250-282; host scripts/qwen_gguf.py:92-104, 133-144).  Planes as the reference lays them
+ * out: L uint32 [V, K/8] (low nibbles of q + 32, nibble i of word w = weight 8w+i), Hb uint32 [V, K/16] (high two bits of
+ * the 16 weights of a sub-block; weight i at bit 8 ((i % 8) / 2) + 2 ((i % 2) + 2 (i / 8)), the reference uses bit 2 i),
+ * SC int8 [V, K/16], D fp16 [V, K/256].  x fp16 [K].  K in {512, 1024, 1536, 2048}.
+ * tok/pos may be null (logits only).  workspace: q4b_head_workspace(V) bytes, zero-filled once. */
+int q4b_head_q6_k_argmax(const void* L, const void* Hb, const void* SC, const void* D, const void* x, float* logits, int V, int K,
+                         int64_t* tok, int64_t* pos, void* workspace, size_t workspace_bytes, q4b_stream_t stream);
+
 /* The same greedy pick for callers that may not allocate device memory.  (No counterpart in the reference: there the
  * caller always owns a torch-allocated workspace.)  Some hosts give a library nothing but the input and output
  * buffers and keep every allocation to themselves: a serving runtime whose device-memory budget is fixed at start-up,
@@ -326,6 +336,10 @@ typedef struct {
   size_t persistent_ws_bytes;
   const void* head16;     /* untied fp16 LM head [vocab, hidden] (a GGUF `output.weight` kept in fp16), or null: with
                              head.W null the head is then `embed` (tied) */
+  const void* head_q6_L;  /* Q6_K LM head planes (see q4b_head_q6_k_argmax), or all null; taken when head.W is null and */
+  const void* head_q6_H;  /* hidden is 512 .. 2048 in steps of 512 */
+  const void* head_q6_SC;
+  const void* head_q6_D;
 } q4b_decode_desc;
 
 #define Q4B_STEP_TENSOR_CORE 1  /* linears through q4b_gemv_q4_0_tc where K is a multiple of 256 */

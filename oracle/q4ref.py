@@ -225,7 +225,20 @@ class Oracle:
 
     def head_dense(self):
         if "head" not in self._dense:
-            if self.cfg.tied_fp16_head:
+            if self.m.get("head_q6") is not None and self.m.get("head") is None:
+                # Q6_K head: (d * sc) * (q - 32) with the fp32 scale product formed first (lab/gguf.py:95-113)
+                L, Hb, SC, D = (np.asarray(a) for a in self.m["head_q6"])
+                lo, hb = L.view(np.uint32), Hb.view(np.uint32)
+                n, k = lo.shape[0], lo.shape[1] * 8
+                code = np.zeros((n, k), np.int32)
+                for i in range(8):
+                    code[:, i::8] = (lo >> np.uint32(4 * i)) & 15
+                for i in range(16):                            # bit positions of the Hb plane, see the product's gguf._q6_hi_shift
+                    sh = 8 * ((i % 8) // 2) + 2 * ((i % 2) + 2 * (i // 8))
+                    code[:, i::16] |= ((hb >> np.uint32(sh)) & 3).astype(np.int32) << 4
+                scale = np.repeat(D.astype(F32), 16, axis=1) * SC.astype(F32)
+                self._dense["head"] = np.repeat(scale, 16, axis=1).astype(self.dense_dtype) * (code - 32).astype(self.dense_dtype)
+            elif self.cfg.tied_fp16_head:
                 self._dense["head"] = self.m["embed"].astype(self.dense_dtype)
             else:
                 self._dense["head"] = dequant(*self.m["head"], self.dense_dtype)

@@ -92,3 +92,38 @@ def test_q6_k_tensors_load_as_fp16_tables(tmp_path):
     G.write_gguf(tmp_path / "q8.gguf", dict(g.meta), tensors)
     with pytest.raises(NotImplementedError, match="ggml type 8"):
         qg.load_model(tmp_path / "q8.gguf")
+
+
+def test_q6_k_planes_round_trip_against_reference_vectors(golden):
+    """The device planes of the Q6_K head (low-nibble, high-two-bit, scale planes) rebuild exactly the weights that the
+    reference's own Q6_K decode gives for the golden blocks (fixture made by lab.gguf.q6_k_blocks)."""
+    G = pkg("gguf")
+    g = golden["q6_k_codec"]
+    raw = g["raw"]                                              # 40 blocks = 40 x 256 weights
+    L, Hb, SC, D = G.q6_k_planes(raw, 20, 512)
+    assert L.shape == (20, 64) and Hb.shape == (20, 32) and SC.shape == (20, 32) and D.shape == (20, 2)
+    dense = G.q6_k_planes_dense(L, Hb, SC, D, np.float32)
+    assert np.array_equal(dense.reshape(-1), g["f32"])
+    with pytest.raises(ValueError):
+        G.q6_k_planes(raw[:210 * 3], 1, 3 * 256 + 128)          # K not a multiple of the 256-weight block
+
+
+def test_q6_k_head_is_kept_at_six_bits_by_the_loader(tmp_path):
+    synth, qg, G = pkg("synth"), pkg("qwen_gguf"), pkg("gguf")
+    cfg = synth.ModelConfig("q6head", 1, 512, 512, 4, 2, 128, 1024)
+    model = synth.synth_model(cfg, 2)
+    path = tmp_path / "m.gguf"
+    qg.export_model(model, path)
+    g = G.GGUF(path)
+    tensors = {n: (t.type, t.dims, bytes(g.raw(n)[0])) for n, t in g.tensors.items()}
+    rng = np.random.default_rng(4)
+    nblk = cfg.vocab * cfg.hidden // 256
+    raw = rng.integers(0, 256, size=(nblk, 210), dtype=np.uint8)
+    raw[:, 208:210] = rng.uniform(1e-4, 1e-3, nblk).astype(np.float16).view(np.uint8).reshape(-1, 2)
+    tensors["output.weight"] = (14, (cfg.hidden, cfg.vocab), raw.tobytes())
+    G.write_gguf(tmp_path / "q6.gguf", dict(g.meta), tensors)
+    back = qg.load_model(tmp_path / "q6.gguf")
+    assert back["head"] is None and back["head_q6"] is not None
+    dense = G.q6_k_planes_dense(*back["head_q6"], np.float32)
+    assert np.array_equal(dense.reshape(-1), G.q6_k_dequant(raw.reshape(-1)))
+    assert np.array_equal(back["head16"], dense.astype(np.float16))
