@@ -62,6 +62,7 @@ SIGNATURES = {
     "q4b_blockdot_q4_0_q8_1": (_I, [_P, _P, _P, _I, _I, _I, _I, _P, _P]),
     "q4b_gemv_q4_0_tc": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _P, _P]),
     "q4b_gemv_q4_0_mma": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _P, _P]),
+    "q4b_gemv_q4_0_f16mma": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P]),
     "q4b_rmsnorm_gemv_q4_0_mma": (_I, [_P, _P, _P, _P, _F, _P, _P, _I, _I, _I, _P, _P]),
     "q4b_rmsnorm_qkv_rope_kv": (_I, [_P, _P, _P, _P, _F, _P, _P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P, _P]),
     "q4b_debug_gemv_mma_expired_wait": (_I, [_P, _P, _P, _P, _I, _I, _P, _P]),

@@ -65,6 +65,7 @@ int gemv_mma(const void*, const void*, const void*, void*, const void*, int, int
              const int64_t* pos = nullptr, void* kc = nullptr, void* vc = nullptr, int NH = 0, int NKV = 0, int HD = 0,
              int max_len = 0, int withhold_chunk = -1, const GemvLookahead* look = nullptr);
 int gemv_mma_ksplit(int, int);
+int gemv_f16mma(const void*, const void*, const void*, void*, const void*, int, int, int, int, int, uint32_t*, cudaStream_t);
 double peak_i8_launch(int, uint32_t*, cudaStream_t);
 int head_q6_k_argmax(const void*, const void*, const void*, const void*, const void*, float*, int, int, int64_t*, int64_t*, void*, size_t,
                      cudaStream_t);
@@ -205,6 +206,11 @@ int q4b_rmsnorm_qkv_rope_kv(const void* W, const void* Sc, const float* h, const
                             void* vc, int NH, int NKV, int HD, int max_len, uint32_t* status, q4b_stream_t stream) {
   return gemv_mma(W, Sc, h, qkv, bias, (NH + 2 * NKV) * HD, K, 3, Q4B_EPI_BIASF_ROPE_KV, status, S(stream), norm_w, eps, cosT,
                   sinT, pos, kc, vc, NH, NKV, HD, max_len);
+}
+
+int q4b_gemv_q4_0_f16mma(const void* W, const void* Sc, const void* X, void* Y, const void* AUX, int N, int K, int B,
+                         int epilogue, int ldy, uint32_t* status, q4b_stream_t stream) {
+  return gemv_f16mma(W, Sc, X, Y, AUX, N, K, B, epilogue, ldy, status, S(stream));
 }
 
 int q4b_debug_gemv_mma_expired_wait(const void* W, const void* Sc, const void* X, void* Y, int N, int K, uint32_t* status,

@@ -273,14 +273,20 @@ class Batched:
     (scripts/qwen_batched_decode.py:86-187) with the linears routed through Q8_1 activations and the int8
     tensor-core MMQ, as the target configuration asks (the reference's batched path uses fp16 `mma` on dequantised
     weights; its int8 MMQ serves prefill, scripts/qwen_prefill.py:176-246).  Shares the weights of a `FusedQwen`.
-    KV cache [L, B, NKV, max_len, HD] (scripts/qwen_batched_decode.py:99)."""
+    KV cache [L, B, NKV, max_len, HD] (scripts/qwen_batched_decode.py:99).
 
-    def __init__(self, m: FusedQwen, B: int):
+    `linears="f16"` selects the reference's own batched-decode arithmetic instead: fp16 activations against weights
+    dequantised to fp16 on fp16 tensor-core MMAs (gemv_v2_source, lab/qwen_batched.py:467-641), 7 launches per layer
+    (rmsnorm, qkv, attention, o, rmsnorm, gate/up, down: scripts/qwen_batched_decode.py:156-187)."""
+
+    def __init__(self, m: FusedQwen, B: int, linears: str = "q8"):
         if not 1 <= B <= 32:
             raise ValueError("1 <= B <= 32 sequences")
+        if linears not in ("q8", "f16"):
+            raise ValueError("linears: 'q8' (Q8_1 x Q4_0 MMQ) or 'f16' (fp16 MMA on dequantised weights)")
         if not m.tensor_core or m.cfg.hidden % 256 or m.cfg.q_rows % 256 or m.cfg.ffn % 256:
             raise ValueError("the batched path needs tile-packed weights (K multiples of 256)")
-        self.m, self.B = m, B
+        self.m, self.B, self.linears = m, B, linears
         c, dv = m.cfg, m.device
         f16, f32 = torch.float16, torch.float32
         self.h = torch.zeros(B, c.hidden, dtype=f32, device=dv)
@@ -304,14 +310,40 @@ class Batched:
         self.attn_ws = K.attn_workspace(B, c.n_heads, c.head_dim, m.max_len, dv)
         self.head_ws = K.head_workspace(c.vocab, B, dv)
         self.status = QB.Status(dv)
-        self.launches_per_step = 1 + 9 * c.layers + 3
+        self.launches_per_step = 1 + (9 if linears == "q8" else 7) * c.layers + 3
 
     def gemm8(self, pair, N, Kdim, Y, aux, epi, ldy, xq=None, xd=None):
         Wt, St = self.m.packed[id(pair[0])]
         QB.gemm8(Wt, St, self.xq if xq is None else xq, self.xd if xd is None else xd, Y, aux, N, Kdim, self.B, epi, ldy,
                  self.status)
 
+    def gemv16(self, pair, N, Kdim, X, Y, aux, epi, ldy):
+        Wt, St = self.m.packed[id(pair[0])]
+        QB.gemv_f16mma(Wt, St, X, Y, aux, N, Kdim, epi, ldy, self.status)
+
+    def _step_f16(self) -> None:
+        m, c = self.m, self.m.cfg
+        H = c.hidden
+        K.embed(m.embed, self.tok, self.h)
+        for i, L in enumerate(m.L):
+            K.rms(self.h, L["ln1"], self.x, c.eps)
+            self.gemv16(L["qkv"], c.qkv_rows, H, self.x, self.qkv, L["qkv_b"], "biasf", c.qkv_rows)
+            K.attn(self.qkv, m.cos, m.sin, self.pos, self.kc[i], self.vc[i], self.att, c.n_heads, c.n_kv_heads, c.head_dim,
+                   m.max_len, m.scale, self.attn_ws)
+            self.gemv16(L["o"], H, c.q_rows, self.att, self.h, None, "resid", H)
+            K.rms(self.h, L["ln2"], self.x, c.eps)
+            self.gemv16(L["gu"], 2 * c.ffn, H, self.x, self.xm, None, "swiglu", c.ffn)
+            self.gemv16(L["down"], H, c.ffn, self.xm, self.h, None, "resid", H)
+        K.rms(self.h, m.norm, self.x, c.eps)
+        if m.head is None:
+            QB.head_batched(m.head16, self.x, self.logits)
+        else:
+            self.gemv16(m.head, c.vocab, H, self.x, self.logits, None, "logits", c.vocab)
+        K.finish(self.logits, self.tok, self.pos, self.head_ws)
+
     def step(self) -> None:
+        if self.linears == "f16":
+            return self._step_f16()
         m, c, B = self.m, self.m.cfg, self.B
         H = c.hidden
         K.embed(m.embed, self.tok, self.h)

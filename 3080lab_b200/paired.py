@@ -9,6 +9,7 @@ are configurations of this library in ONE process:
 
     python 3080lab_b200/paired.py                      # tensor-core GEMV vs CUDA-core GEMV, + A/A duplicate, 1.5B shape
     python 3080lab_b200/paired.py --arms tc,persistent --rounds 6 --steps 64
+    python 3080lab_b200/paired.py --arms b_q8,b_f16 --batch 32   # batched decode: Q8_1 x Q4_0 MMQ vs fp16 MMA on dequantised weights
 
 The statistics are plain functions (`rotated_rounds`, `ratio_stats`) and are tested without a GPU.
 """
@@ -62,7 +63,69 @@ ARMS = {
     "tc": dict(tensor_core=True),            # tcgen05 exact GEMV (the default path)
     "cuda": dict(tensor_core=False),         # CUDA-core GEMV with the reference's inner-loop arithmetic
     "persistent": dict(tensor_core=True, persistent=True),
+    # batched decode of --batch sequences at a 1024-token context (engine.Batched): the two routes of the linears
+    "b_q8": dict(batched="q8"),
+    "b_f16": dict(batched="f16"),
 }
+
+
+def _batched_main(args, names, torch, synth, engine, model, cfg) -> None:
+    """The paired protocol on `engine.Batched` arms: all arms share one set of weights; every arm holds its own
+    activations and KV cache (filled with the same N(0, 1) context, as scripts/decode_ab.py:56-58 does)."""
+    ctx = 1024
+    m = engine.FusedQwen(model, max_len=ctx + args.steps + 64)
+    gen = torch.Generator(device="cuda").manual_seed(0)
+    kv = None
+    engines, graphs = {}, {}
+    toks = torch.from_numpy(synth.synth_prompt(cfg, args.batch, 5)).cuda()
+    for n in names:
+        bm = engine.Batched(m, args.batch, linears=ARMS[n.replace("_dup", "")]["batched"])
+        if kv is None:
+            kv = (torch.randn(bm.kc.shape, generator=gen, device="cuda", dtype=torch.float16),
+                  torch.randn(bm.vc.shape, generator=gen, device="cuda", dtype=torch.float16))
+        bm.kc.copy_(kv[0])
+        bm.vc.copy_(kv[1])
+        bm.pos.fill_(ctx)
+        bm.tok.copy_(toks)
+        engines[n] = bm
+    for bm in engines.values():                                             # one step each from the same state: the diff
+        bm.step()
+    torch.cuda.synchronize()
+    first = engines[names[0]]
+    diffs = {}
+    for n in names[1:]:
+        e = engines[n]
+        scale = float(first.logits.abs().max())
+        diffs[n] = {"logits_rel": float((e.logits - first.logits).abs().max()) / scale,
+                    "tokens_equal": int((e.tok == first.tok).sum()), "of": args.batch}
+    for n, bm in engines.items():
+        bm.pos.fill_(ctx)
+        bm.tok.copy_(toks)
+        graphs[n] = bm.capture()
+
+    def arm(n):
+        def run() -> float:
+            bm, g = engines[n], graphs[n]
+            bm.pos.fill_(ctx)
+            bm.tok.copy_(toks)
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            s.record()
+            for _ in range(args.steps):
+                g.replay()
+            e.record()
+            torch.cuda.synchronize()
+            bm.status.check("batched decode")
+            return args.batch * args.steps / s.elapsed_time(e) * 1e3        # tok/s over all sequences
+        return run
+
+    res = rotated_rounds({n: arm(n) for n in names}, args.rounds)
+    base = names[0]
+    out = {"batch": args.batch, "context": ctx, "rounds": args.rounds, "steps": args.steps,
+           "tok_per_s_median": {n: statistics.median(v) for n, v in res.items()},
+           "ratio_vs_" + base: {n: ratio_stats(res[n], res[base]) for n in names[1:]},
+           "first_step_vs_" + base: diffs}
+    print(json.dumps(out, indent=1))
 
 
 def main() -> None:
@@ -72,6 +135,7 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--prompt", type=int, default=64)
     ap.add_argument("--layers", type=int, default=28)
+    ap.add_argument("--batch", type=int, default=8, help="sequences of the batched arms (b_q8, b_f16)")
     args = ap.parse_args()
     import torch
     synth = importlib.import_module("3080lab_b200.synth")
@@ -82,6 +146,12 @@ def main() -> None:
     ids = synth.synth_prompt(cfg, args.prompt, 1)
     names = args.arms.split(",")
     names = names + [names[0] + "_dup"]                                   # the A/A control
+    batched = ["batched" in ARMS[n.replace("_dup", "")] for n in names]
+    if any(batched):
+        if not all(batched):
+            raise SystemExit("batched arms (b_q8, b_f16) cannot be mixed with batch-1 arms")
+        args.steps = min(args.steps, 128)
+        return _batched_main(args, names, torch, synth, engine, model, cfg)
     engines, graphs = {}, {}
     for n in names:
         m = engine.FusedQwen(model, max_len=args.prompt + args.steps + 64, **ARMS[n.replace("_dup", "")])

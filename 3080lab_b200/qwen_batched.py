@@ -65,6 +65,16 @@ def gemv_mma(W, S, X, Y, aux, N: int, K: int, epi: str, status: Status) -> None:
     _ffi.call("q4b_gemv_q4_0_mma", _p(W), _p(S), _p(X), _p(Y), _p(aux), N, K, _ffi.EPI[epi], xd, _p(status.word), _stream())
 
 
+def gemv_f16mma(W, S, X, Y, aux, N: int, K: int, epi: str, ldy: int, status: Status) -> None:
+    """Y[b] = epilogue(X[b] . W^T) for up to 32 fp16 activation rows with fp16-dequantised weights on fp16 tensor-core
+    MMAs: the arithmetic of the reference's batched-decode GEMV (gemv_v2_source, lab/qwen_batched.py:467-641).  (W, S)
+    tile-packed by `pack_q4`."""
+    if X.dtype != torch.float16 or X.dim() != 2:
+        raise TypeError("X must be fp16 [B, K]")
+    _ffi.call("q4b_gemv_q4_0_f16mma", _p(W), _p(S), _p(X), _p(Y), _p(aux), N, K, X.shape[0], _ffi.EPI[epi], ldy, _p(status.word),
+              _stream())
+
+
 def rmsnorm_gemv_mma(W, S, h, norm_w, eps: float, Y, aux, N: int, K: int, epi: str, status: Status) -> None:
     """RMSNorm(h) * norm_w -> fp16 -> `gemv_mma`, one launch."""
     _ffi.call("q4b_rmsnorm_gemv_q4_0_mma", _p(W), _p(S), _p(h), _p(norm_w), float(eps), _p(Y), _p(aux), N, K, _ffi.EPI[epi],

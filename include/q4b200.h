@@ -197,6 +197,20 @@ int q4b_rmsnorm_qkv_rope_kv(const void* Wt, const void* St, const float* h, cons
                             const float* bias, int K, const float* cosT, const float* sinT, const int64_t* pos, void* kc,
                             void* vc, int NH, int NKV, int HD, int max_len, uint32_t* status, q4b_stream_t stream);
 
+/* ---- batched-decode GEMV on fp16 tensor-core MMAs (the reference's own batched-decode arithmetic) ---------------------
+ * Y[b, :] = epilogue(X[b, :] . W^T) for B = 1 .. 32 activation rows, with the weights dequantised to fp16 the way the
+ * reference's batched-decode kernel does it (gemv_v2_source, lab/qwen_batched.py:467-641, nibble -> half2 through the
+ * 0x6400 trick, times the fp16 block scale ROUNDED to fp16, `dq` :493-498) and multiplied by the fp16 activations in
+ * mma.sync.m16n8k16 with fp32 accumulation.  It replaces the launch site Batched.step uses for qkv / o / gate_up / down
+ * (scripts/qwen_batched_decode.py:156-187, `self.g[name]`), reading the tile-packed weights of q4b_pack_q4_0 instead
+ * of a fragment-ordered copy (pack_q4_mma, lab/qwen_batched.py:394-436).  The result differs from the exact block-dot
+ * kernels by the fp16 rounding of d * (q - 8): 2e-4 .. 5e-3 relative, as the reference documents for this path.
+ * X fp16 [B, K]; Y [B, ldy]: fp16 for STORE / BIASF / SWIGLU (ldy >= N, or N / 2 for SWIGLU), fp32 for RESID (Y += result)
+ * and LOGITS.  AUX: fp32 bias [N] for BIASF.  K a multiple of 32.
+ * status: one uint32, set non-zero if a bounded device-side wait expired. */
+int q4b_gemv_q4_0_f16mma(const void* Wt, const void* St, const void* X, void* Y, const void* AUX, int N, int K, int B,
+                         int epilogue, int ldy, uint32_t* status, q4b_stream_t stream);
+
 /* Exercise of the failure path of the bounded device-side waits, in a form that always returns: q4b_gemv_q4_0_mma
  * (fp16 x, logits epilogue) with the bulk copies of its first weight chunk withheld and the wait cut to a few thousand
  * polls.  The wait gives up, the kernel sets *status non-zero and finishes normally; Y is meaningless.  The reference's

@@ -56,6 +56,21 @@ def dequant(W, S, dtype=F64):
     return ((q - 8).astype(dtype) * np.repeat(np.asarray(S).astype(dtype), 32, axis=1))
 
 
+def dequant_f16w(W, S, dtype=F64):
+    """Dense weights as the reference's batched-decode GEMV forms them (`dq`, lab/qwen_batched.py:493-498): q - 8 exact
+    in fp16, times the fp16 block scale, rounded ONCE to fp16.  The fp32 product of a 4-bit and an 11-bit significand is
+    exact, so rounding it to fp16 is that single rounding."""
+    q = unpack_words(W)
+    w = (q - 8).astype(F32) * np.repeat(np.asarray(S).astype(F32), 32, axis=1)
+    return w.astype(F16).astype(dtype)
+
+
+def gemv_f16w_ref(W, S, X):
+    """The batched-decode GEMV of gemv_v2_source (lab/qwen_batched.py:467-641) in float64: fp16-rounded weights times
+    fp16 activations X [B, K] -> [B, N] (the kernel accumulates in fp32)."""
+    return np.asarray(X, F16).astype(F64) @ dequant_f16w(W, S, F64).T
+
+
 def gemv_ref(W, S, x):
     """float64 dequantise-and-dot: ref = ((q - 8) * repeat(d, 32)) @ x  (lab/experiments/gemv5.py:49)."""
     return dequant(W, S, F64) @ np.asarray(x, F64)
@@ -195,10 +210,13 @@ class Oracle:
     Q8_1 x Q4_0 as the prefill path does (scripts/qwen_prefill.py:196-246);
     `prefill_q8` = Prefill.chunk (scripts/qwen_prefill.py:196-246)."""
 
-    def __init__(self, model, max_len, cos, sin, batch=1, dense_dtype=F64):
+    def __init__(self, model, max_len, cos, sin, batch=1, dense_dtype=F64, weights="exact"):
         """dense_dtype: storage of the cached dequantised matrices.  float64 by default; float32 halves the memory for
-        the full 1.5B shape (6 GB instead of 12) at ~1e-7 relative error per linear, far below the 1e-3 bar."""
+        the full 1.5B shape (6 GB instead of 12) at ~1e-7 relative error per linear, far below the 1e-3 bar.
+        weights: "exact" = (q - 8) * d; "f16w" = that product rounded to fp16, the layer weights of the reference's
+        batched-decode GEMV (`dequant_f16w`); `step` is then Batched.step of scripts/qwen_batched_decode.py:156-187."""
         self.dense_dtype = dense_dtype
+        self.weights = weights
         self.m, self.cfg = model, model["cfg"]
         self.max_len, self.B = max_len, batch
         c = self.cfg
@@ -216,7 +234,7 @@ class Oracle:
         key = (layer, name)
         if key not in self._dense:
             W, S = self.m["layers"][layer][name] if layer >= 0 else self.m["head"]
-            self._dense[key] = dequant(W, S, self.dense_dtype)
+            self._dense[key] = (dequant_f16w if self.weights == "f16w" and layer >= 0 else dequant)(W, S, self.dense_dtype)
         return self._dense[key]
 
     def _mm(self, x, Wd):
@@ -241,7 +259,7 @@ class Oracle:
             elif self.cfg.tied_fp16_head:
                 self._dense["head"] = self.m["embed"].astype(self.dense_dtype)
             else:
-                self._dense["head"] = dequant(*self.m["head"], self.dense_dtype)
+                self._dense["head"] = (dequant_f16w if self.weights == "f16w" else dequant)(*self.m["head"], self.dense_dtype)
         return self._dense["head"]
 
     def _attend(self, i, qkv):

@@ -17,6 +17,9 @@ Fixtures:
                    (lab/experiments/tensor.py:171-179, which demands exact equality) and its expected A8 @ B8 + C8
   rope_tables.npz  cos / sin rows computed by the reference's own statement (scripts/qwen_gguf.py:111-113, torch double
                    -> float) for head_dim 128, theta 1e6, at a spread of positions
+  pack_q4_mma.npz  a seeded 48 x 192 Q4_0 matrix in the canonical device words and what the reference's own
+                   `pack_q4_mma` (lab/qwen_batched.py:394-436, torch on the CPU) makes of it: the fragment-ordered
+                   operand of its batched-decode GEMV
 """
 from __future__ import annotations
 
@@ -128,6 +131,15 @@ def main(ref_root: str) -> None:
     ang = torch.tensor(positions).double()[:, None] * inv[None]
     np.savez_compressed(HERE / "rope_tables.npz", positions=np.array(positions), head_dim=hd, theta=theta,
                         cos=torch.cos(ang).float().numpy(), sin=torch.sin(ang).float().numpy())
+    # 7. the reference's fragment-order repack for its batched-decode GEMV, run as is on the CPU
+    rb = importlib.import_module("lab.qwen_batched")
+    q, d, _ = gemv_inputs(48, 192, False)
+    words = np.zeros((48, 192 // 8), np.uint32)
+    for i in range(8):                                   # nibble i of word w = weight 8 w + i (scripts/qwen_gguf.py:54-60)
+        words |= q[:, i::8].astype(np.uint32) << np.uint32(4 * i)
+    W = torch.from_numpy(words.view(np.int32).copy())
+    Wp, Sp = rb.pack_q4_mma(W, torch.from_numpy(d.copy()))
+    np.savez_compressed(HERE / "pack_q4_mma.npz", W=W.numpy(), S=d, Wp=Wp.numpy(), Sp=Sp.numpy())
     print("fixtures written to", HERE)
 
 

@@ -1,0 +1,203 @@
+"""The batched-decode GEMV on fp16 tensor-core MMAs (weights dequantised to fp16 with one rounding, the reference's
+gemv_v2 arithmetic) against the oracle that rounds the weights the same way.  What is left between kernel and oracle
+is the fp32 accumulation order: fp32 results within 2e-5 of the largest reference magnitude (the reference itself
+states 2e-4 .. 5e-3 for this path against exact weights); 16-bit outputs within one unit in the last place."""
+import numpy as np
+import pytest
+
+from conftest import oracle, pkg
+
+torch = pytest.importorskip("torch")
+pytestmark = pytest.mark.gpu
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def nerr(got, ref):
+    ref = np.asarray(ref, np.float64)
+    return float(np.max(np.abs(np.asarray(got, np.float64) - ref)) / max(np.max(np.abs(ref)), 1e-30))
+
+
+def rand_q4(rng, n, k):
+    W = rng.integers(0, 2 ** 32, size=(n, k // 8), dtype=np.uint32).view(np.int32)
+    S = rng.uniform(0.002, 0.02, size=(n, k // 32)).astype(np.float16)
+    return W, S
+
+
+def ulps16(a, b):
+    a = np.asarray(a, np.float16).view(np.int16).astype(np.int32)
+    b = np.asarray(b, np.float16).view(np.int16).astype(np.int32)
+    return np.abs(a - b)
+
+
+@pytest.fixture(scope="module")
+def QB():
+    pkg("qwen_kernels").init(0)
+    return pkg("qwen_batched")
+
+
+# ragged and odd N, one k-block, every layer shape of both models, every count of column tiles
+@pytest.mark.parametrize("n,k,b", [(128, 32, 1), (5, 96, 3), (131, 544, 8), (2048, 1536, 32), (1536, 1536, 9), (17920, 1536, 32),
+                                   (1536, 8960, 17), (17920, 1536, 8), (1536, 8960, 32), (260, 18944, 24), (4608, 3584, 32),
+                                   (640, 3584, 16)])
+def test_gemv_f16mma_matches_oracle(QB, n, k, b):
+    o = oracle()
+    rng = np.random.default_rng(n * 7 + k + b)
+    W, S = rand_q4(rng, n, k)
+    X = rng.standard_normal((b, k)).astype(np.float16)
+    X[:, ::97] *= 1e-3
+    ref = o.gemv_f16w_ref(W, S, X)
+    st = QB.Status("cuda")
+    ldy = n + 8
+    y = torch.full((b, ldy), float("nan"), device="cuda")
+    Wd, Sd = QB.pack_q4(dev(W), dev(S))
+    QB.gemv_f16mma(Wd, Sd, dev(X), y, None, n, k, "logits", ldy, st)
+    st.check()
+    got = y.cpu().numpy()
+    assert np.all(np.isnan(got[:, n:]))
+    assert nerr(got[:, :n], ref) < 2e-5
+    # the weight rounding is there: against exact weights the result is off by the documented few 1e-4 .. 1e-3
+    exact = X.astype(np.float64) @ o.dequant(W, S).T
+    assert nerr(got[:, :n], exact) < 1e-2
+    # and twice the same bits
+    y2 = torch.empty_like(y)
+    QB.gemv_f16mma(Wd, Sd, dev(X), y2, None, n, k, "logits", ldy, st)
+    assert torch.equal(y2[:, :n], y[:, :n])
+
+
+def test_gemv_f16mma_rounds_the_weights_like_the_reference(QB):
+    """One activation row that is a unit vector reads single weights back: each must be fp16((q - 8) * d) exactly."""
+    o = oracle()
+    rng = np.random.default_rng(5)
+    n, k = 256, 64
+    W, S = rand_q4(rng, n, k)
+    S = rng.uniform(0.002, 0.02, size=S.shape).astype(np.float16)
+    w16 = o.dequant_f16w(W, S)
+    Wd, Sd = QB.pack_q4(dev(W), dev(S))
+    st = QB.Status("cuda")
+    X = np.zeros((32, k), np.float16)
+    for b in range(32):
+        X[b, (7 * b + 3) % k] = 1.0
+    y = torch.zeros(32, n, device="cuda")
+    QB.gemv_f16mma(Wd, Sd, dev(X), y, None, n, k, "logits", n, st)
+    st.check()
+    got = y.cpu().numpy()
+    for b in range(32):
+        np.testing.assert_array_equal(got[b], w16[:, (7 * b + 3) % k])
+
+
+@pytest.mark.parametrize("b", [2, 8, 32])
+def test_gemv_f16mma_epilogues(QB, b):
+    o = oracle()
+    rng = np.random.default_rng(40 + b)
+    n, k = 1536, 512
+    W, S = rand_q4(rng, n, k)
+    X = rng.standard_normal((b, k)).astype(np.float16)
+    ref = o.gemv_f16w_ref(W, S, X)
+    Wd, Sd = QB.pack_q4(dev(W), dev(S))
+    Xd = dev(X)
+    st = QB.Status("cuda")
+    bias = rng.standard_normal(n).astype(np.float32)
+    y16 = torch.zeros(b, n, dtype=torch.float16, device="cuda")
+    QB.gemv_f16mma(Wd, Sd, Xd, y16, None, n, k, "store", n, st)
+    assert ulps16(y16.cpu().numpy(), ref.astype(np.float16)).max() <= 1
+    QB.gemv_f16mma(Wd, Sd, Xd, y16, dev(bias), n, k, "biasf", n, st)
+    want = (ref + bias).astype(np.float16)
+    big = np.abs(ref + bias) > 0.05 * np.abs(ref).max()
+    assert ulps16(y16.cpu().numpy(), want)[big].max() <= 1 and nerr(y16.float().cpu().numpy(), ref + bias) < 1e-3
+    h = rng.standard_normal((b, n)).astype(np.float32)
+    hd = dev(h)
+    QB.gemv_f16mma(Wd, Sd, Xd, hd, None, n, k, "resid", n, st)
+    assert nerr(hd.cpu().numpy(), h.astype(np.float64) + ref) < 2e-5
+    act = torch.zeros(b, n // 2 + 4, dtype=torch.float16, device="cuda")
+    QB.gemv_f16mma(Wd, Sd, Xd, act, None, n, k, "swiglu", n // 2 + 4, st)
+    want = o.silu_mul(ref[:, 0::2], ref[:, 1::2])
+    assert nerr(act[:, :n // 2].float().cpu().numpy(), want) < 1e-3
+    assert torch.all(act[:, n // 2:] == 0)
+    st.check()
+
+
+def test_gemv_f16mma_bad_arguments(QB):
+    ffi = pkg("_ffi")
+    rng = np.random.default_rng(1)
+    W, S = rand_q4(rng, 128, 64)
+    Wd, Sd = QB.pack_q4(dev(W), dev(S))
+    st = QB.Status("cuda")
+    y = torch.zeros(33, 128, device="cuda")
+    X = torch.zeros(33, 64, dtype=torch.float16, device="cuda")
+    with pytest.raises(ffi.Q4BError):
+        QB.gemv_f16mma(Wd, Sd, X, y, None, 128, 64, "logits", 128, st)            # 33 rows
+    with pytest.raises(ffi.Q4BError):
+        QB.gemv_f16mma(Wd, Sd, X[:4], y, None, 128, 48, "logits", 128, st)        # K not a multiple of 32
+    with pytest.raises(ffi.Q4BError):
+        QB.gemv_f16mma(Wd, Sd, X[:4], y, None, 128, 64, "logits", 64, st)         # ldy shorter than a row
+    with pytest.raises(ffi.Q4BError):
+        QB.gemv_f16mma(Wd, Sd, X[:4], y, None, 128, 64, "biasf", 128, st)         # bias missing
+    with pytest.raises(TypeError):
+        QB.gemv_f16mma(Wd, Sd, X[:4].float(), y, None, 128, 64, "logits", 128, st)
+
+
+@pytest.mark.parametrize("B", [3, 8, 32])
+def test_batched_f16_decode_matches_oracle(B):
+    """`Batched(m, B, linears="f16")`: 24 prompt + 40 greedy steps against the oracle's step with fp16-rounded weights.
+    Per kernel the two agree to fp32 rounding (tests above); along a model a sum that lands within that distance of a
+    fp16 rounding boundary flips one activation by an ulp (5e-4 of it); every step has some, and the two-layer model
+    passes them on to the logits at 2e-4 .. 1e-3, on single tokens more (1.9e-2 seen once in 512 sequence-steps, with
+    every kernel of that step within 1e-3 of the oracle applied to the kernel's own inputs).  So, as for the int8 path:
+    median below 1e-3, nine in ten below 3e-3, none above 5e-2 (the reference's own paths differ by 2e-2,
+    data/night_oct13/ours_pp_r1.txt), and a token may differ from the oracle's only where the oracle's own logit gap is
+    below the error of that step (the oracle's token is then fed)."""
+    synth, engine = pkg("synth"), pkg("engine")
+    o = oracle()
+    cfg = synth.ModelConfig("small-f16", 2, 512, 1536, 4, 2, 128, 4096)
+    model = synth.synth_model(cfg, 11)
+    m = engine.FusedQwen(model, max_len=128)
+    bm = engine.Batched(m, B, linears="f16")
+    cos, sin = synth.rope_tables(cfg, 128)
+    ora = o.Oracle(model, 128, cos, sin, batch=B, weights="f16w")
+    prompts = np.stack([synth.synth_prompt(cfg, 24, 100 + b) for b in range(B)])
+    errs, swaps = [], 0
+    for j in range(64):
+        if j < 24:
+            ora.tok[:] = prompts[:, j]
+            bm.tok.copy_(dev(prompts[:, j]))
+        want = ora.step()
+        bm.step()
+        lg, got = bm.logits.cpu().numpy(), bm.tok.cpu().numpy()
+        for b in range(B):
+            err = np.max(np.abs(lg[b] - ora.logits[b]))
+            errs.append(err / np.max(np.abs(ora.logits[b])))
+            if got[b] != want[b]:
+                gap = ora.logits[b][want[b]] - ora.logits[b][got[b]]
+                assert 0 <= gap <= 2 * err + 1e-6, f"token differs with a logit gap {gap} above the error {err}"
+                swaps += 1
+        bm.tok.copy_(dev(want))
+    errs = np.array(errs)
+    assert np.median(errs) < 1e-3, np.median(errs)
+    assert np.quantile(errs, 0.9) < 3e-3, np.quantile(errs, 0.9)
+    assert errs.max() < 5e-2, errs.max()
+    assert swaps <= 3
+    bm.status.check()
+
+
+def test_batched_f16_and_q8_agree_statistically():
+    """The two batched-decode modes on the same weights and prompts: logits close (int8 activations against fp16-rounded
+    weights: a few 1e-3 each from the exact product), greedy tokens mostly the same."""
+    synth, engine = pkg("synth"), pkg("engine")
+    cfg = synth.ModelConfig("small-ab", 2, 512, 1536, 4, 2, 128, 4096)
+    m = engine.FusedQwen(synth.synth_model(cfg, 12), max_len=64)
+    a, b = engine.Batched(m, 8, linears="f16"), engine.Batched(m, 8, linears="q8")
+    prompts = np.stack([synth.synth_prompt(cfg, 16, 7 + i) for i in range(8)])
+    same = 0
+    for j in range(16):
+        for bm in (a, b):
+            bm.tok.copy_(dev(prompts[:, j]))
+            bm.step()
+        la, lb = a.logits.cpu().numpy(), b.logits.cpu().numpy()
+        assert nerr(la, lb) < 5e-2
+        same += int((a.tok == b.tok).sum().item())
+    assert same >= 0.8 * 16 * 8
+    a.status.check()
+    b.status.check()

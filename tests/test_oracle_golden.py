@@ -158,3 +158,35 @@ def test_blockdot_oracle_on_the_reference_known_answer_inputs(golden):
     W = pkg("gguf").pack_nibbles(nib)                               # canonical words [16, 4]
     got = o.blockdot(W, np.ascontiguousarray(g["B8"].T))            # xq [8 columns, 32] -> [8, 16, 1]
     assert np.array_equal(got[:, :, 0].T, (nib.astype(np.int32) - 8) @ B8)
+
+
+def test_f16_weight_oracle_reads_the_reference_fragment_pack(golden):
+    """`dequant_f16w` against the reference's own repack for its batched-decode GEMV: the fragment-ordered words and
+    scales `pack_q4_mma` made are read the way gemv_v2_source reads them (lane (g, t), word s, A register j =
+    (w >> 4 j) & 0x000F000F, `dq` with the fp16 ops done one by one in numpy float16) and must give, bit for bit, the
+    weights the oracle forms from the canonical words."""
+    o = oracle()
+    g = golden["pack_q4_mma"]
+    W, S, Wp, Sp = g["W"], g["S"], g["Wp"].view(np.uint32), g["Sp"]
+    N, K = W.shape[0], W.shape[1] * 8
+    w16 = np.zeros((N, K), np.float16)
+    for tile in range(N // 16):
+        for ch in range(K // 64):
+            for lane in range(32):
+                gg, t = lane >> 2, lane & 3
+                for s in range(4):                        # k-step of 16 inside the 64-k chunk; Q4_0 block s // 2
+                    word = int(Wp[tile, ch, lane, s])
+                    dA, dB = Sp[tile, ch, gg, 2 * (s // 2)], Sp[tile, ch, gg, 2 * (s // 2) + 1]     # rows g, g + 8
+                    for j in range(4):
+                        h = (word >> (4 * j)) & 0x000F000F
+                        pair = np.array([1024 + (h & 15), 1024 + (h >> 16)], np.float16) - np.float16(1032)
+                        pair = pair * (dA if j % 2 == 0 else dB)                                  # __hmul2, one rounding
+                        row = 16 * tile + gg + (8 if j % 2 else 0)
+                        k = 64 * ch + 16 * s + 2 * t + (8 if j >= 2 else 0)
+                        w16[row, k:k + 2] = pair
+    want = o.dequant_f16w(W, S, np.float64)
+    np.testing.assert_array_equal(w16.astype(np.float64), want)
+    # and the rounding is real: the exact product differs from it in a good share of the weights
+    exact = o.dequant(W, S)
+    assert 0.2 < np.mean(exact != want) < 1.0
+    assert np.max(np.abs(exact - want) / np.abs(exact).max()) < 2 ** -11
