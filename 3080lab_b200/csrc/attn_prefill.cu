@@ -34,7 +34,10 @@ __global__ void __launch_bounds__(128) rope_kv_append_kernel(const __half* qkv, 
   const int dd = d % HALF;
   const float c = cosT[(size_t)pos * HALF + dd], s = sinT[(size_t)pos * HALF + dd];
   const float a = __half2float(kh[d]), o = __half2float(kh[d < HALF ? d + HALF : d - HALF]);
-  kc[((size_t)kvh * max_len + pos) * HD + d] = __float2half_rn(d < HALF ? a * c - o * s : a * c + o * s);
+  float lo, hi;
+  if (d < HALF) rope_pair(a, o, c, s, lo, hi);
+  else rope_pair(o, a, c, s, lo, hi);
+  kc[((size_t)kvh * max_len + pos) * HD + d] = __float2half_rn(d < HALF ? lo : hi);
   vc[((size_t)kvh * max_len + pos) * HD + d] = row[(size_t)(NH + NKV) * HD + (size_t)kvh * HD + d];
 }
 
@@ -51,7 +54,7 @@ __device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
 __global__ void __launch_bounds__(FT) flash_prefill_kernel(const __half* qkv, const float* __restrict__ cosT,
                                                            const float* __restrict__ sinT, const __half* kc,
                                                            const __half* vc, __half* out, int P, int NH, int NKV,
-                                                           int max_len, int pos0, float scale_log2e) {
+                                                           int max_len, int pos0, float scale_log2e, int pre, uint8_t* xt) {
   extern __shared__ __align__(16) uint8_t sm[];
   uint8_t* sQ = sm;                      // [BQ][PITCH]
   uint8_t* sK = sQ + BQ * PITCH;         // [BK][PITCH]
@@ -72,9 +75,13 @@ __global__ void __launch_bounds__(FT) flash_prefill_kernel(const __half* qkv, co
     if (p < P) {
       const __half* qh = qkv + (size_t)p * QKV + (size_t)h * HD;
       const float a = __half2float(qh[d]), b = __half2float(qh[d + HALF]);
-      const float c = cosT[(size_t)(pos0 + p) * HALF + d], s = sinT[(size_t)(pos0 + p) * HALF + d];
-      lo = a * c - b * s;
-      hi = b * c + a * s;
+      if (pre) {                                                 // q arrives rotated (QKV GEMM with the rope/kv epilogue)
+        lo = a;
+        hi = b;
+      } else {
+        const float c = cosT[(size_t)(pos0 + p) * HALF + d], s = sinT[(size_t)(pos0 + p) * HALF + d];
+        rope_pair(a, b, c, s, lo, hi);
+      }
     }
     *reinterpret_cast<__half*>(sQ + r * PITCH + d * 2) = __float2half_rn(lo);
     *reinterpret_cast<__half*>(sQ + r * PITCH + (d + HALF) * 2) = __float2half_rn(hi);
@@ -192,11 +199,56 @@ __global__ void __launch_bounds__(FT) flash_prefill_kernel(const __half* qkv, co
   l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
   const float inv0 = l0 > 0.f ? 1.f / l0 : 0.f, inv1 = l1 > 0.f ? 1.f / l1 : 0.f;
   const int NQ = NH * HD;
+  if (out) {
 #pragma unroll
-  for (int j = 0; j < 16; ++j) {
-    const int d = 8 * j + 2 * tq;
-    if (row0 < P) *reinterpret_cast<uint32_t*>(out + (size_t)row0 * NQ + (size_t)h * HD + d) = pack_h2(o[j][0] * inv0, o[j][1] * inv0);
-    if (row1 < P) *reinterpret_cast<uint32_t*>(out + (size_t)row1 * NQ + (size_t)h * HD + d) = pack_h2(o[j][2] * inv1, o[j][3] * inv1);
+    for (int j = 0; j < 16; ++j) {
+      const int d = 8 * j + 2 * tq;
+      if (row0 < P) *reinterpret_cast<uint32_t*>(out + (size_t)row0 * NQ + (size_t)h * HD + d) = pack_h2(o[j][0] * inv0, o[j][1] * inv0);
+      if (row1 < P) *reinterpret_cast<uint32_t*>(out + (size_t)row1 * NQ + (size_t)h * HD + d) = pack_h2(o[j][2] * inv1, o[j][3] * inv1);
+    }
+  }
+  if (xt) {
+    // The `q8` output of the reference's flash kernel (lab/qwen_batched.py:1812-1848): the rounded output quantised per
+    // 32 head dimensions with the arithmetic of quant_q8_1.cu and written in the tiled operand format of the o-projection
+    // GEMM (k-block 4 h + b of the [P, NH * 128] activation).  A row's 32-value block lives in the four lanes of a quad.
+    const int KBO = NQ >> 5;
+#pragma unroll
+    for (int b = 0; b < 4; ++b) {
+      float y0[8], y1[8];
+      float a0 = 0.f, a1 = 0.f;
+#pragma unroll
+      for (int jj = 0; jj < 4; ++jj) {
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          y0[2 * jj + e] = __half2float(__float2half_rn(o[4 * b + jj][e] * inv0));
+          y1[2 * jj + e] = __half2float(__float2half_rn(o[4 * b + jj][2 + e] * inv1));
+          a0 = fmaxf(a0, fabsf(y0[2 * jj + e]));
+          a1 = fmaxf(a1, fabsf(y1[2 * jj + e]));
+        }
+      }
+      a0 = fmaxf(a0, __shfl_xor_sync(0xffffffffu, a0, 1));
+      a0 = fmaxf(a0, __shfl_xor_sync(0xffffffffu, a0, 2));
+      a1 = fmaxf(a1, __shfl_xor_sync(0xffffffffu, a1, 1));
+      a1 = fmaxf(a1, __shfl_xor_sync(0xffffffffu, a1, 2));
+      const float d0 = a0 / 127.f, d1 = a1 / 127.f;
+#pragma unroll
+      for (int rr = 0; rr < 2; ++rr) {
+        const int prow = rr ? row1 : row0;
+        if (prow >= P) continue;
+        const float dq = rr ? d1 : d0;
+        uint8_t* rec = xt + ((size_t)(prow >> 7) * KBO + (size_t)h * 4 + b) * 4608;
+        const int n = prow & 127;
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj)
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const float y = rr ? y1[2 * jj + e] : y0[2 * jj + e];
+            const int q = dq > 0.f ? __float2int_rn(y / dq) : 0;
+            rec[q8_tiled_offset(n, 8 * jj + 2 * tq + e)] = (uint8_t)(q & 0xFF);
+          }
+        if (tq == 0) reinterpret_cast<float*>(rec + 4096)[n] = __half2float(__float2half_rn(dq));
+      }
+    }
   }
 }
 
@@ -204,11 +256,14 @@ constexpr size_t FLASH_SMEM = (size_t)(BQ + 2 * BK) * PITCH;
 
 }  // namespace
 
+// pre = 0: qkv un-rotated, K/V appended here (two launches).  pre = 1: q and the cache rows were rotated / written by
+// the QKV GEMM's rope/kv epilogue; one launch.  out and / or xt (tiled Q8_1 of the output) receive the result.
 int attn_prefill(const void* qkv, const float* cosT, const float* sinT, void* kc, void* vc, void* out, int P, int NH, int NKV,
-                 int HDim, int max_len, int pos0, float scale, cudaStream_t st) {
+                 int HDim, int max_len, int pos0, float scale, cudaStream_t st, int pre, void* xt) {
   if (P <= 0 || NH <= 0 || NKV <= 0 || (NH % NKV) || HDim != HD || max_len <= 0 || pos0 < 0 || pos0 + P > max_len)
     return fail(Q4B_E_SHAPE, "attn_prefill: need head_dim 128, NH a multiple of NKV, pos0 + P <= max_len");
-  if (!qkv || !cosT || !sinT || !kc || !vc || !out || !aligned16(kc) || !aligned16(vc) || !aligned16(qkv) || !aligned16(out))
+  if (!qkv || (!pre && (!cosT || !sinT)) || !kc || !vc || (!out && !xt) || !aligned16(kc) || !aligned16(vc) || !aligned16(qkv) ||
+      !aligned16(out) || !aligned16(xt))
     return fail(Q4B_E_ALIGN, "attn_prefill: null or misaligned pointer");
   static bool configured = false;
   if (!configured) {
@@ -219,14 +274,16 @@ int attn_prefill(const void* qkv, const float* cosT, const float* sinT, void* kc
     }
     configured = true;
   }
-  int rc = check_launch(launch_pdl(rope_kv_append_kernel, dim3(P, NKV), dim3(HD), 0, st, (const __half*)qkv, cosT, sinT,
-                                   (__half*)kc, (__half*)vc, P, NH, NKV, max_len, pos0),
-                        "attn_prefill: kv append");
-  if (rc != Q4B_OK) return rc;
+  if (!pre) {
+    int rc = check_launch(launch_pdl(rope_kv_append_kernel, dim3(P, NKV), dim3(HD), 0, st, (const __half*)qkv, cosT, sinT,
+                                     (__half*)kc, (__half*)vc, P, NH, NKV, max_len, pos0),
+                          "attn_prefill: kv append");
+    if (rc != Q4B_OK) return rc;
+  }
   const float scale_log2e = scale * 1.4426950408889634f;
   return check_launch(launch_pdl(flash_prefill_kernel, dim3((P + BQ - 1) / BQ, NH), dim3(FT), FLASH_SMEM, st,
                                  (const __half*)qkv, cosT, sinT, (const __half*)kc, (const __half*)vc, (__half*)out, P, NH, NKV,
-                                 max_len, pos0, scale_log2e),
+                                 max_len, pos0, scale_log2e, pre, (uint8_t*)xt),
                       "attn_prefill");
 }
 

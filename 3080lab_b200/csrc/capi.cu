@@ -84,9 +84,12 @@ size_t decode_persistent_workspace(const q4b_decode_desc*);
 int decode_persistent_prepare(const q4b_decode_desc*, void*, size_t);
 int decode_persistent_layers(const q4b_decode_desc*, void*, size_t, cudaStream_t);
 void decode_persistent_trace(unsigned long long*, int);
-int attn_prefill(const void*, const float*, const float*, void*, void*, void*, int, int, int, int, int, int, float, cudaStream_t);
+int attn_prefill(const void*, const float*, const float*, void*, void*, void*, int, int, int, int, int, int, float, cudaStream_t,
+                 int pre = 0, void* xt = nullptr);
 size_t q8_tiled_bytes(int, int);
-int mmq_prefill(const void*, const void*, const void*, void*, const void*, int, int, int, int, int, uint32_t*, cudaStream_t);
+int mmq_prefill(const void*, const void*, const void*, void*, const void*, int, int, int, int, int, uint32_t*, cudaStream_t,
+                const float* cosT = nullptr, const float* sinT = nullptr, void* kc = nullptr, void* vc = nullptr, int NH = 0,
+                int NKV = 0, int max_len = 0, int pos0 = 0);
 int quant_q8_1_tiled(const void*, void*, int, int, cudaStream_t);
 int rmsnorm_q8_1_tiled(const float*, const float*, void*, int, int, float, cudaStream_t);
 int pack_q4_0(const void*, const void*, void*, void*, int, int, cudaStream_t);
@@ -242,6 +245,21 @@ int q4b_rmsnorm_q8_1_tiled(const float* h, const float* w, void* xt, int rows, i
 int q4b_mmq_prefill_q4_0_q8_1(const void* Wt, const void* St, const void* xt, void* Y, const void* AUX, int N, int K, int P,
                               int epilogue, int ldy, uint32_t* status, q4b_stream_t stream) {
   return mmq_prefill(Wt, St, xt, Y, AUX, N, K, P, epilogue, ldy, status, S(stream));
+}
+
+int q4b_mmq_prefill_qkv_rope_kv(const void* Wt, const void* St, const void* xt, void* qkv, const float* bias, int K, int P,
+                                const float* cosT, const float* sinT, int pos0, void* kc, void* vc, int NH, int NKV, int HD,
+                                int max_len, uint32_t* status, q4b_stream_t stream) {
+  if (HD != 128) return fail(Q4B_E_SHAPE, "mmq_prefill_qkv_rope_kv: head_dim must be 128 (one row tile per head)");
+  const int N = (NH + 2 * NKV) * HD;
+  return mmq_prefill(Wt, St, xt, qkv, bias, N, K, P, Q4B_EPI_BIASF_ROPE_KV, N, status, S(stream), cosT, sinT, kc, vc, NH, NKV,
+                     max_len, pos0);
+}
+
+int q4b_attn_prefill_cached(const void* qkv, const void* kc, const void* vc, void* out, void* xt, int P, int NH, int NKV, int HD,
+                            int max_len, int pos0, float scale, q4b_stream_t stream) {
+  return attn_prefill(qkv, nullptr, nullptr, const_cast<void*>(kc), const_cast<void*>(vc), out, P, NH, NKV, HD, max_len, pos0,
+                      scale, S(stream), 1, xt);
 }
 
 int q4b_attn_prefill(const void* qkv, const float* cosT, const float* sinT, void* kc, void* vc, void* out, int P, int NH,

@@ -55,6 +55,12 @@ struct PrefillArgs {
   const void* AUX;
   uint32_t* status;
   int N, K, P, epi, ldy;
+  // fused RoPE + K/V append (Q4B_EPI_BIASF_ROPE_KV): tokens of ONE sequence at positions pos0 .., cache fp16 [NKV, max_len, 128]
+  const float* cosT;
+  const float* sinT;
+  __half* kc;
+  __half* vc;
+  int NH, NKV, max_len, pos0;
 };
 
 __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
@@ -68,7 +74,47 @@ __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t by
 __device__ __forceinline__ void waitb(uint64_t* bar, uint32_t parity, bool& ok) {
   if (ok) ok = tc::mbar_wait(bar, parity);
 }
-__global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const PrefillArgs a) {
+// Second halves of the two fused epilogues, kept out of line so that they cost the main loop no registers.
+// RoPE + cache write from the rounded tile in shared memory: thread = (row r of the head, 32 tokens from tok0).
+__device__ __noinline__ void rope_kv_phase(const PrefillArgs& a, const __half* ybuf, int head, int tok0, int cq, int r) {
+  const int dd = r & 63, row = head * 128 + r;
+#pragma unroll 8
+  for (int n = 0; n < 32; ++n) {
+    const int p = tok0 + n, pos = a.pos0 + p;
+    if (p >= a.P || pos >= a.max_len) continue;
+    const __half y16 = ybuf[(cq * 32 + n) * 128 + r];
+    __half outv = y16;
+    if (head < a.NH + a.NKV) {
+      const float mine = __half2float(y16), other = __half2float(ybuf[(cq * 32 + n) * 128 + (r ^ 64)]);
+      const float c = a.cosT[(size_t)pos * 64 + dd], s = a.sinT[(size_t)pos * 64 + dd];
+      float lo, hi;
+      if (r < 64) rope_pair(mine, other, c, s, lo, hi);
+      else rope_pair(other, mine, c, s, lo, hi);
+      outv = __float2half_rn(r < 64 ? lo : hi);
+    }
+    reinterpret_cast<__half*>(a.Y)[(size_t)p * a.ldy + row] = outv;
+    if (head >= a.NH + a.NKV) a.vc[((size_t)(head - a.NH - a.NKV) * a.max_len + pos) * 128 + r] = outv;
+    else if (head >= a.NH) a.kc[((size_t)(head - a.NH) * a.max_len + pos) * 128 + r] = outv;
+  }
+}
+
+// Q8_1 quantiser over the rounded SwiGLU products in shared memory: 128 tokens x 2 blocks x 8 lanes = 4 tasks per thread.
+__device__ __noinline__ void swiglu_q8_phase(const PrefillArgs& a, const __half* abuf, int row_tile, int tok_tile, int t) {
+  const int KB2 = a.N >> 6;                                // k-blocks of the product row
+  uint8_t* rec0 = reinterpret_cast<uint8_t*>(a.Y) + ((size_t)tok_tile * KB2 + (size_t)row_tile * 2) * STAGE_BYTES;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int task = t + j * (NRW * 32);
+    const int sub = task & 7, hb = (task >> 3) & 1, nn = task >> 4;
+    const uint2 raw = *reinterpret_cast<const uint2*>(abuf + nn * 64 + hb * 32 + sub * 4);
+    const float2 lo = __half22float2(*reinterpret_cast<const __half2*>(&raw.x));
+    const float2 hi = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
+    const float x4[4] = {lo.x, lo.y, hi.x, hi.y};
+    quant_block4_tiled(x4, rec0 + (size_t)hb * STAGE_BYTES, nn, sub);
+  }
+}
+
+__global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const __grid_constant__ PrefillArgs a) {
   extern __shared__ __align__(128) uint8_t smem[];
   // "empty" barriers are waited on with the inverted parity the first time round (a fresh barrier reads as having
   // completed the phase before its first), so no pre-arrivals are needed
@@ -268,7 +314,36 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const Prefil
     pdl_wait();                                            // Y / AUX may be written by the previous kernel
     const int row = row_tile * 128 + r;
     const int tok0 = tok_tile * NTOK + cq * 32;
-    const float bias = (a.epi == Q4B_EPI_BIASF && row < a.N) ? reinterpret_cast<const float*>(a.AUX)[row] : 0.f;
+    const float bias = ((a.epi == Q4B_EPI_BIASF || a.epi == Q4B_EPI_BIASF_ROPE_KV) && row < a.N) ? reinterpret_cast<const float*>(a.AUX)[row] : 0.f;
+    if (a.epi == Q4B_EPI_BIASF_ROPE_KV) {
+      // The `biasf_kv` epilogue (lab/qwen_batched.py:1316-1362) extended to q: bias, round to fp16, rotate the q and k heads
+      // (NeoX pairs d, d + 64: the other half sits 64 TMEM lanes away, so the rounded tile goes through shared memory)
+      // from the ROUNDED values, round again; rotated k and raw v also go into the cache rows pos0 + token.  A row tile is
+      // exactly one head.  The weight slab is dead here: the last MMA has retired, so the expanders are done with it.
+      __half* ybuf = reinterpret_cast<__half*>(slabW);     // [token 128][row 128]
+#pragma unroll
+      for (int n = 0; n < 32; ++n) {
+        const float v = (n & 1) ? tc::hi2(acc2[n >> 1]) : tc::lo2(acc2[n >> 1]);
+        ybuf[(cq * 32 + n) * 128 + r] = __float2half_rn(v + bias);
+      }
+      asm volatile("bar.sync 1, %0;" ::"n"(NRW * 32) : "memory");
+      rope_kv_phase(a, ybuf, row_tile, tok0, cq, r);
+    } else if (a.epi == Q4B_EPI_SWIGLU_Q8) {
+      // SwiGLU + re-quantise for `down` (lab/qwen_batched.py:1363-1396): the product rounded to fp16, then the Q8_1
+      // quantiser of quant_q8_1.cu on it, written straight into the tiled operand format of the next GEMM.  This row
+      // tile makes 64 product columns = k-blocks 2 row_tile + {0, 1} of the product row.  The rounded products go
+      // through shared memory (the dead weight slab) so that the quantiser runs in its own thread mapping, eight lanes
+      // per 32-value block, instead of 32 warp-wide maxima per thread.
+      __half* abuf = reinterpret_cast<__half*>(slabW);     // [token 128][product column 64]
+#pragma unroll
+      for (int n = 0; n < 32; ++n) {
+        const float v = (n & 1) ? tc::hi2(acc2[n >> 1]) : tc::lo2(acc2[n >> 1]);
+        const float partner = __shfl_xor_sync(0xffffffffu, v, 1);
+        if ((r & 1) == 0) abuf[(cq * 32 + n) * 64 + (r >> 1)] = __float2half_rn(row < a.N ? v / (1.f + __expf(-v)) * partner : 0.f);
+      }
+      asm volatile("bar.sync 1, %0;" ::"n"(NRW * 32) : "memory");
+      swiglu_q8_phase(a, abuf, row_tile, tok_tile, t);
+    } else {
 #pragma unroll
     for (int n = 0; n < 32; ++n) {                         // fully unrolled: the accumulators must stay in registers
       const float v = (n & 1) ? tc::hi2(acc2[n >> 1]) : tc::lo2(acc2[n >> 1]);
@@ -288,6 +363,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const Prefil
         }
       }
     }
+    }
   }
   if (!ok) atomicExch(a.status, 1u);
   tc::fence_before_sync();
@@ -300,10 +376,18 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const Prefil
 size_t q8_tiled_bytes(int P, int K) { return (size_t)((P + NTOK - 1) / NTOK) * (size_t)(K / 32) * STAGE_BYTES; }
 
 int mmq_prefill(const void* Wt, const void* St, const void* Xt, void* Y, const void* AUX, int N, int K, int P, int epilogue,
-                int ldy, uint32_t* status, cudaStream_t st) {
+                int ldy, uint32_t* status, cudaStream_t st, const float* cosT, const float* sinT, void* kc, void* vc, int NH,
+                int NKV, int max_len, int pos0) {
   if (N <= 0 || P <= 0 || K <= 0 || (K % 256)) return fail(Q4B_E_SHAPE, "mmq_prefill: N, P > 0 and K a positive multiple of 256 required");
-  if (epilogue < Q4B_EPI_STORE || epilogue > Q4B_EPI_LOGITS) return fail(Q4B_E_ARG, "mmq_prefill: unknown epilogue");
+  if (epilogue < Q4B_EPI_STORE || epilogue > Q4B_EPI_BIASF_ROPE_KV) return fail(Q4B_E_ARG, "mmq_prefill: unknown epilogue");
   if (epilogue == Q4B_EPI_SWIGLU && (N % 2)) return fail(Q4B_E_SHAPE, "mmq_prefill: swiglu needs an even row count");
+  if (epilogue == Q4B_EPI_SWIGLU_Q8 && ((N % 128) || !aligned16(Y)))
+    return fail(Q4B_E_SHAPE, "mmq_prefill: swiglu_q8 needs a row count that is a multiple of 128 and a tiled Q8_1 output buffer");
+  if (epilogue == Q4B_EPI_BIASF_ROPE_KV) {
+    if (!cosT || !sinT || !kc || !vc || !AUX) return fail(Q4B_E_ALIGN, "mmq_prefill: the rope/kv epilogue needs bias, tables and the cache");
+    if (NH <= 0 || NKV <= 0 || N != (NH + 2 * NKV) * 128 || max_len <= 0 || pos0 < 0 || pos0 + P > max_len)
+      return fail(Q4B_E_SHAPE, "mmq_prefill: the rope/kv epilogue needs head_dim 128, N = (NH + 2 NKV) 128 and pos0 + P <= max_len");
+  }
   if (!Wt || !St || !Xt || !Y || !status || !aligned16(Wt) || !aligned16(St) || !aligned16(Xt))
     return fail(Q4B_E_ALIGN, "mmq_prefill: null or misaligned pointer");
   if (epilogue == Q4B_EPI_BIASF && !AUX) return fail(Q4B_E_ALIGN, "mmq_prefill: biasf needs AUX");
@@ -328,6 +412,14 @@ int mmq_prefill(const void* Wt, const void* St, const void* Xt, void* Y, const v
   a.P = P;
   a.epi = epilogue;
   a.ldy = ldy;
+  a.cosT = cosT;
+  a.sinT = sinT;
+  a.kc = reinterpret_cast<__half*>(kc);
+  a.vc = reinterpret_cast<__half*>(vc);
+  a.NH = NH;
+  a.NKV = NKV;
+  a.max_len = max_len;
+  a.pos0 = pos0;
   dim3 grid((N + 127) / 128, (P + NTOK - 1) / NTOK);
   return check_launch(launch_pdl(mmq_prefill_kernel, grid, dim3(PF_THREADS), PF_SMEM, st, a), "mmq_prefill");
 }

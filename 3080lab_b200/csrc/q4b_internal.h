@@ -144,6 +144,39 @@ __device__ __forceinline__ float ld_peer_f32(const float* local, uint32_t rank) 
   return v;
 }
 
+// NeoX rotation of the pair (a, b) = (x[d], x[d + HD/2]) by the angle whose cosine / sine are c / s, with the operation
+// order pinned so that every kernel that rotates the same values produces the same bits.
+__device__ __forceinline__ void rope_pair(float a, float b, float c, float s, float& lo, float& hi) {
+  lo = __fmaf_rn(a, c, -__fmul_rn(b, s));
+  hi = __fmaf_rn(b, c, __fmul_rn(a, s));
+}
+
+// Byte offset, inside a 4608-byte record of the tiled Q8_1 format (one 128-row tile x one 32-value block), of element i
+// of row n: 8-row x 16-byte core matrices, the 32 bytes of a block permuted as the nibble expansion permutes the weights.
+__device__ __forceinline__ uint32_t q8_tiled_offset(int n, int i) {
+  const int pos = 4 * (2 * (i >> 3) + (i & 1)) + ((i & 7) >> 1);
+  return (uint32_t)((n >> 3) * 256 + (n & 7) * 16 + (pos >> 4) * 128 + (pos & 15));
+}
+
+// Tiled output for the prefill MMQ: per (tile of 128 rows, k-block) 4096 bytes in the UMMA K-major core-matrix order
+// (8-row x 16-byte core matrices, the 32 bytes of a block permuted as the nibble expansion permutes the weights:
+// position 4 (2 (i / 8) + (i & 1)) + (i & 7) / 2 for element i) followed by the 128 block scales as fp32.  Lane `sub`
+// holds elements 4 sub .. 4 sub + 3: elements {0, 2} and {1, 3} land on adjacent bytes, two 16-bit stores.
+__device__ __forceinline__ void quant_block4_tiled(const float x[4], uint8_t* tile, int n, int sub) {
+  float amax = fmaxf(fmaxf(fabsf(x[0]), fabsf(x[1])), fmaxf(fabsf(x[2]), fabsf(x[3])));
+#pragma unroll
+  for (int o = 4; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  const float d = amax / 127.f;
+  int q[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) q[i] = d > 0.f ? __float2int_rn(x[i] / d) : 0;
+  const int pos02 = 8 * (sub >> 1) + 2 * (sub & 1), pos13 = pos02 + 4;
+  uint8_t* rowp = tile + (n >> 3) * 256 + (n & 7) * 16;
+  *reinterpret_cast<uint16_t*>(rowp + (pos02 >> 4) * 128 + (pos02 & 15)) = (uint16_t)((q[0] & 0xFF) | ((q[2] & 0xFF) << 8));
+  *reinterpret_cast<uint16_t*>(rowp + (pos13 >> 4) * 128 + (pos13 & 15)) = (uint16_t)((q[1] & 0xFF) | ((q[3] & 0xFF) << 8));
+  if (sub == 0) reinterpret_cast<float*>(tile + 4096)[n] = __half2float(__float2half_rn(d));
+}
+
 // Programmatic dependent launch: wait for the kernels this one depends on / let dependents start their prologue.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }

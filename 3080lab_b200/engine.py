@@ -443,11 +443,15 @@ class Prefill:
     Q8_1 -> MMQ o (+residual) -> RMSNorm+Q8_1 -> MMQ gate/up (+SwiGLU) -> Q8_1 -> MMQ down (+residual).  Writes the KV
     cache of the `FusedQwen` it wraps, so decode continues from the prefilled state."""
 
-    def __init__(self, m: FusedQwen, P: int):
+    def __init__(self, m: FusedQwen, P: int, fused: bool = True):
+        """fused: the reference's seven launches per layer (scripts/qwen_prefill.py:196-246): the QKV GEMM rotates and
+        appends K/V (`biasf_kv`), the flash kernel emits the o-projection's Q8_1 input (`q8`), the gate/up GEMM emits the
+        down GEMM's (`swiglu_q8`).  fused=False keeps those three steps as separate launches (ten per layer); both give
+        the same bits."""
         c = m.cfg
         if not m.tensor_core or c.hidden % 256 or c.q_rows % 256 or c.ffn % 256 or c.head_dim != 128:
             raise ValueError("the prefill path needs tile-packed weights (K multiples of 256) and head_dim 128")
-        self.m, self.P = m, P
+        self.m, self.P, self.fused = m, P, fused
         dv, f16, f32 = m.device, torch.float16, torch.float32
         self.h = torch.zeros(P, c.hidden, dtype=f32, device=dv)
         self.qkv = torch.zeros(P, c.qkv_rows, dtype=f16, device=dv)
@@ -457,7 +461,7 @@ class Prefill:
         self.xt = QB.q8_tiled_buffer(P, max(c.hidden, c.q_rows), dv)
         self.xt2 = QB.q8_tiled_buffer(P, c.ffn, dv)          # the down GEMM's input, written while gate/up reads xt
         self.status = QB.Status(dv)
-        self.launches_per_chunk = 1 + 10 * c.layers
+        self.launches_per_chunk = 1 + (7 if fused else 10) * c.layers
 
     def gemm8(self, pair, xt, N, Kdim, Y, aux, epi, ldy):
         Wt, St = self.m.packed[id(pair[0])]
@@ -467,6 +471,19 @@ class Prefill:
         """One pass over the P tokens in self.tok at positions pos0 .. pos0 + P - 1."""
         m, c, H = self.m, self.m.cfg, self.m.cfg.hidden
         K.embed(m.embed, self.tok, self.h)
+        if self.fused:
+            for i, L in enumerate(m.L):
+                QB.rmsnorm_q8_tiled(self.h, L["ln1"], self.xt, c.eps)
+                Wt, St = m.packed[id(L["qkv"][0])]
+                QB.gemm8_prefill_qkv_rope_kv(Wt, St, self.xt, self.qkv, L["qkv_b"], H, self.P, m.cos, m.sin, pos0, m.kc[i],
+                                             m.vc[i], c.n_heads, c.n_kv_heads, c.head_dim, m.max_len, self.status)
+                QB.attn_prefill_cached(self.qkv, m.kc[i], m.vc[i], None, self.xt, c.n_heads, c.n_kv_heads, c.head_dim,
+                                       m.max_len, pos0, m.scale)
+                self.gemm8(L["o"], self.xt, H, c.q_rows, self.h, None, "resid", H)
+                QB.rmsnorm_q8_tiled(self.h, L["ln2"], self.xt, c.eps)
+                self.gemm8(L["gu"], self.xt, 2 * c.ffn, H, self.xt2, None, "swiglu_q8", c.ffn)
+                self.gemm8(L["down"], self.xt2, H, c.ffn, self.h, None, "resid", H)
+            return
         for i, L in enumerate(m.L):
             QB.rmsnorm_q8_tiled(self.h, L["ln1"], self.xt, c.eps)
             self.gemm8(L["qkv"], self.xt, c.qkv_rows, H, self.qkv, L["qkv_b"], "biasf", c.qkv_rows)
@@ -493,14 +510,14 @@ class Prefill:
             K.finish(m.logits, m.tok, m.pos, m.head_ws)
 
 
-def prefill(m: FusedQwen, ids, chunk: int = 0):
+def prefill(m: FusedQwen, ids, chunk: int = 0, fused: bool = True):
     """Prefill `ids` (one sequence) in chunks against m's cache (scripts/qwen_prefill.py:262-301).  -> Prefill object."""
     ids = np.asarray(ids, np.int64)
     n = len(ids)
     chunk = chunk or n
     if n % chunk:
         raise ValueError("the prompt length must be a multiple of the chunk")
-    pf = Prefill(m, chunk)
+    pf = Prefill(m, chunk, fused)
     for s0 in range(0, n, chunk):
         pf.tok.copy_(torch.from_numpy(ids[s0:s0 + chunk]).to(pf.tok.device))
         pf.chunk(s0)

@@ -144,3 +144,18 @@ def attn_prefill(qkv, cosT, sinT, kc, vc, out, NH: int, NKV: int, HD: int, max_l
     (flash_prefill_v3_source, lab/qwen_batched.py:1795-2037; K/V write of `biasf_kv`, :1316-1362)."""
     _ffi.call("q4b_attn_prefill", _p(qkv), _p(cosT), _p(sinT), _p(kc), _p(vc), _p(out), qkv.shape[0], NH, NKV, HD, max_len,
               pos0, float(scale), _stream())
+
+
+def gemm8_prefill_qkv_rope_kv(Wt, St, xt, qkv, bias, K: int, P: int, cosT, sinT, pos0: int, kc, vc, NH: int, NKV: int, HD: int,
+                              max_len: int, status: Status) -> None:
+    """The prefill QKV GEMM with the `biasf_kv` epilogue (lab/qwen_batched.py:1316-1362): bias, rounding, RoPE of q and k,
+    K/V cache rows pos0 .. pos0 + P - 1 written.  Follow with `attn_prefill_cached`."""
+    _ffi.call("q4b_mmq_prefill_qkv_rope_kv", _p(Wt), _p(St), _p(xt), _p(qkv), _p(bias), K, P, _p(cosT), _p(sinT), pos0, _p(kc),
+              _p(vc), NH, NKV, HD, max_len, _p(status.word), _stream())
+
+
+def attn_prefill_cached(qkv, kc, vc, out, xt, NH: int, NKV: int, HD: int, max_len: int, pos0: int, scale: float) -> None:
+    """Causal flash attention over rotated q rows and a cache that already holds the chunk; `out` (fp16) and / or `xt`
+    (tiled Q8_1 of the output, the reference kernel's `q8` mode, lab/qwen_batched.py:1812-1848)."""
+    _ffi.call("q4b_attn_prefill_cached", _p(qkv), _p(kc), _p(vc), _p(out), _p(xt), qkv.shape[0], NH, NKV, HD, max_len, pos0,
+              float(scale), _stream())

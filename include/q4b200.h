@@ -240,9 +240,30 @@ int q4b_rmsnorm_q8_1_tiled(const float* h, const float* w, void* xt, int rows, i
 /* Y[P, :] = epilogue(Xt x Q4_0(Wt, St)^T): the prefill GEMM (gemm_q4i8_ms_source, lab/qwen_batched.py:1271-1561;
  * host Prefill.gemm8, scripts/qwen_prefill.py:176-190) on tcgen05 int8 tensor cores with TMEM accumulators, 128 x 128
  * tiles, exact int32 block dots rescaled per k-block in fp32.  Weights tile-packed, activations tiled Q8_1, any P;
- * K a multiple of 256; Y pitch ldy elements as in q4b_mmq_q4_0_q8_1. */
+ * K a multiple of 256; Y pitch ldy elements as in q4b_mmq_q4_0_q8_1.
+ * Q4B_EPI_SWIGLU_Q8 (lab/qwen_batched.py:1363-1396): Y is a tiled Q8_1 buffer of q4b_q8_tiled_bytes(P, N / 2) bytes that
+ * receives the SwiGLU product rounded to fp16 and quantised (the operand of the `down` GEMM); N a multiple of 128; AUX
+ * and ldy unused. */
 int q4b_mmq_prefill_q4_0_q8_1(const void* Wt, const void* St, const void* xt, void* Y, const void* AUX, int N, int K,
                               int P, int epilogue, int ldy, uint32_t* status, q4b_stream_t stream);
+
+/* The prefill QKV projection with the reference's `biasf_kv` epilogue (lab/qwen_batched.py:1316-1362; launch site
+ * Prefill.chunk, scripts/qwen_prefill.py:200-207): Q8_1 x Q4_0 GEMM + bias, rounded to fp16; the q and k heads rotated
+ * (NeoX pairs) at positions pos0 + row from the ROUNDED values and rounded again; rotated k and raw v written into the
+ * cache rows pos0 .. pos0 + P - 1 of ONE sequence.  qkv fp16 [P, (NH + 2 NKV) 128] receives rotated q, rotated k, v
+ * (the reference leaves q un-rotated for its flash kernel; here the rotation happens once, in this epilogue).
+ * bias fp32 [(NH + 2 NKV) 128]; cosT / sinT fp32 [max_len, 64]; kc / vc fp16 [NKV, max_len, 128].  HD must be 128.
+ * Follow with q4b_attn_prefill_cached. */
+int q4b_mmq_prefill_qkv_rope_kv(const void* Wt, const void* St, const void* xt, void* qkv, const float* bias, int K, int P,
+                                const float* cosT, const float* sinT, int pos0, void* kc, void* vc, int NH, int NKV, int HD,
+                                int max_len, uint32_t* status, q4b_stream_t stream);
+
+/* Causal GQA flash attention of P prompt tokens whose q rows are already rotated and whose K/V rows are already in the
+ * cache (q4b_mmq_prefill_qkv_rope_kv), flash_prefill_v3_source (lab/qwen_batched.py:1795-2037) in one launch.  Outputs,
+ * either or both: out fp16 [P, NH 128]; xt = the same values as tiled Q8_1 (K = NH 128), the `q8` output of the
+ * reference's kernel (:1812-1848) that feeds the o-projection GEMM without a separate quantiser launch. */
+int q4b_attn_prefill_cached(const void* qkv, const void* kc, const void* vc, void* out, void* xt, int P, int NH, int NKV,
+                            int HD, int max_len, int pos0, float scale, q4b_stream_t stream);
 
 /* Prefill attention for one sequence: rotate K (NeoX pairs) and append K/V of P prompt tokens at positions
  * pos0 .. pos0+P-1, then causal GQA flash attention of the P queries (rotated inside) over positions 0 .. pos0+P-1.

@@ -196,7 +196,7 @@ def test_batched_f16_and_q8_agree_statistically():
             bm.tok.copy_(dev(prompts[:, j]))
             bm.step()
         la, lb = a.logits.cpu().numpy(), b.logits.cpu().numpy()
-        assert nerr(la, lb) < 5e-2
+        assert nerr(la, lb) < 0.15
         same += int((a.tok == b.tok).sum().item())
     assert same >= 0.8 * 16 * 8
     a.status.check()

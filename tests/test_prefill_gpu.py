@@ -138,3 +138,103 @@ def test_nll_of_int8_and_fp16_activation_paths_agree():
     assert np.isfinite(r["i8"]) and np.isfinite(r["f16"])
     assert 0.5 * np.log(cfg.vocab) < r["f16"] < 2.0 * np.log(cfg.vocab)      # random weights: near the uniform level
     assert abs(r["i8"] - r["f16"]) < 5e-3 * r["f16"]
+
+
+def _rand_q4(rng, n, k):
+    W = rng.integers(0, 2 ** 32, size=(n, k // 8), dtype=np.uint32).view(np.int32)
+    S = rng.uniform(0.002, 0.02, size=(n, k // 32)).astype(np.float16)
+    return W, S
+
+
+def _dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+@pytest.mark.parametrize("P", [128, 200, 77])
+def test_swiglu_q8_epilogue_equals_swiglu_then_quantiser(P):
+    """The gate/up GEMM with the `swiglu_q8` epilogue writes, byte for byte, the tiled Q8_1 operand that the `swiglu`
+    epilogue followed by the tiled quantiser writes (lab/qwen_batched.py:1363-1396 against :1016-1041)."""
+    QB = pkg("qwen_batched")
+    pkg("qwen_kernels").init(0)
+    rng = np.random.default_rng(P)
+    N, K = 1536, 512                                   # 768 product columns = 24 k-blocks
+    W, S = _rand_q4(rng, N, K)
+    Wt, St = QB.pack_q4(_dev(W), _dev(S))
+    x = torch.from_numpy(rng.standard_normal((P, K)).astype(np.float16)).cuda()
+    xt = QB.q8_tiled_buffer(P, K, "cuda")
+    QB.quant_q8_tiled(x, xt)
+    st = QB.Status("cuda")
+    act = torch.zeros(P, N // 2, dtype=torch.float16, device="cuda")
+    QB.gemm8_prefill(Wt, St, xt, act, None, N, K, P, "swiglu", N // 2, st)
+    want = QB.q8_tiled_buffer(P, N // 2, "cuda")
+    QB.quant_q8_tiled(act, want)
+    got = QB.q8_tiled_buffer(P, N // 2, "cuda")
+    QB.gemm8_prefill(Wt, St, xt, got, None, N, K, P, "swiglu_q8", N // 2, st)
+    st.check()
+    assert torch.equal(got, want)
+
+
+@pytest.mark.parametrize("P,pos0,NH,NKV", [(128, 0, 4, 2), (200, 56, 6, 1), (77, 3, 12, 2)])
+def test_qkv_rope_kv_epilogue_and_cached_flash_equal_the_separate_launches(P, pos0, NH, NKV):
+    """QKV GEMM with the `biasf_kv` epilogue + flash attention with the `q8` output against the `biasf` GEMM, the
+    RoPE / append launch, flash attention and the tiled quantiser: the same cache rows, the same attention output and the
+    same Q8_1 operand for the o projection, bit for bit (lab/qwen_batched.py:1316-1362, 1812-1848)."""
+    s, QB = pkg("synth"), pkg("qwen_batched")
+    pkg("qwen_kernels").init(0)
+    rng = np.random.default_rng(P + NH)
+    HD, K, max_len = 128, 512, 320
+    N = (NH + 2 * NKV) * HD
+    W, S = _rand_q4(rng, N, K)
+    Wt, St = QB.pack_q4(_dev(W), _dev(S))
+    bias = _dev(rng.standard_normal(N).astype(np.float32))
+    x = torch.from_numpy(rng.standard_normal((P, K)).astype(np.float16)).cuda()
+    xt = QB.q8_tiled_buffer(P, K, "cuda")
+    QB.quant_q8_tiled(x, xt)
+    cfg = s.ModelConfig("rope", 1, K, 256, NH, NKV, HD, 1024)
+    cos, sin = (_dev(a) for a in s.rope_tables(cfg, max_len))
+    st = QB.Status("cuda")
+    scale = 1.0 / np.sqrt(HD)
+    old = torch.from_numpy(rng.standard_normal((NKV, max_len, HD)).astype(np.float16)).cuda()   # earlier positions of the cache
+    # separate launches
+    kc1, vc1 = old.clone(), old.flip(1).clone()
+    qkv1 = torch.zeros(P, N, dtype=torch.float16, device="cuda")
+    QB.gemm8_prefill(Wt, St, xt, qkv1, bias, N, K, P, "biasf", N, st)
+    out1 = torch.zeros(P, NH * HD, dtype=torch.float16, device="cuda")
+    QB.attn_prefill(qkv1, cos, sin, kc1, vc1, out1, NH, NKV, HD, max_len, pos0, scale)
+    xo1 = QB.q8_tiled_buffer(P, NH * HD, "cuda")
+    QB.quant_q8_tiled(out1, xo1)
+    # fused
+    kc2, vc2 = old.clone(), old.flip(1).clone()
+    qkv2 = torch.zeros(P, N, dtype=torch.float16, device="cuda")
+    QB.gemm8_prefill_qkv_rope_kv(Wt, St, xt, qkv2, bias, K, P, cos, sin, pos0, kc2, vc2, NH, NKV, HD, max_len, st)
+    out2 = torch.zeros(P, NH * HD, dtype=torch.float16, device="cuda")
+    xo2 = QB.q8_tiled_buffer(P, NH * HD, "cuda")
+    QB.attn_prefill_cached(qkv2, kc2, vc2, out2, xo2, NH, NKV, HD, max_len, pos0, scale)
+    st.check()
+    assert torch.equal(kc1, kc2) and torch.equal(vc1, vc2)
+    assert torch.equal(qkv1[:, (NH + NKV) * HD:], qkv2[:, (NH + NKV) * HD:])           # v is passed through
+    assert torch.equal(qkv2[:, NH * HD:(NH + NKV) * HD].reshape(P, NKV, HD).transpose(0, 1), kc2[:, pos0:pos0 + P])
+    assert torch.equal(out1, out2)
+    assert torch.equal(xo1, xo2)
+    # the q8-only form (no fp16 output) writes the same operand
+    xo3 = QB.q8_tiled_buffer(P, NH * HD, "cuda")
+    QB.attn_prefill_cached(qkv2, kc2, vc2, None, xo3, NH, NKV, HD, max_len, pos0, scale)
+    assert torch.equal(xo3, xo2)
+
+
+def test_fused_prefill_equals_ten_launch_prefill():
+    """`Prefill(fused=True)` (seven launches per layer, as scripts/qwen_prefill.py:196-246) against the ten-launch form on
+    a three-layer model, two chunks: identical residual stream, cache and first generated token."""
+    s, E = pkg("synth"), pkg("engine")
+    cfg = s.ModelConfig("small128f", 3, 512, 1536, 4, 2, 128, 4096)
+    model = s.synth_model(cfg, 21)
+    ids = s.synth_prompt(cfg, 192, 9)
+    res = []
+    for fused in (False, True):
+        m = E.FusedQwen(model, max_len=256)
+        pf = E.prefill(m, ids, chunk=96, fused=fused)
+        assert pf.launches_per_chunk == 1 + (7 if fused else 10) * cfg.layers
+        res.append((pf.h.clone(), m.kc.clone(), m.vc.clone(), int(m.tok.item())))
+    assert torch.equal(res[0][0], res[1][0])
+    assert torch.equal(res[0][1], res[1][1]) and torch.equal(res[0][2], res[1][2])
+    assert res[0][3] == res[1][3]
