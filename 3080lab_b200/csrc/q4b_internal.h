@@ -158,6 +158,33 @@ __device__ __forceinline__ uint32_t q8_tiled_offset(int n, int i) {
   return (uint32_t)((n >> 3) * 256 + (n & 7) * 16 + (pos >> 4) * 128 + (pos & 15));
 }
 
+// Q8_1 quantiser of one 32-value block (QUANT_Q8, lab/qwen_batched.py:1030-1039), planar output.
+// 8 lanes per block, 4 consecutive values per lane: each lane reads 8 bytes and writes 4.
+__device__ __forceinline__ void quant_block4(const float x[4], int8_t* q_out, __half* d_out, __half* s_out, int lane_in_blk,
+                                             bool live) {
+  float amax = fmaxf(fmaxf(fabsf(x[0]), fabsf(x[1])), fmaxf(fabsf(x[2]), fabsf(x[3])));
+#pragma unroll
+  for (int o = 4; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  const float d = amax / 127.f;
+  int q[4], sq = 0;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    q[i] = d > 0.f ? __float2int_rn(x[i] / d) : 0;
+    sq += q[i];
+  }
+  if (live) {
+    const uint32_t packed = (uint32_t)(q[0] & 0xFF) | ((uint32_t)(q[1] & 0xFF) << 8) | ((uint32_t)(q[2] & 0xFF) << 16) |
+                            ((uint32_t)(q[3] & 0xFF) << 24);
+    *reinterpret_cast<uint32_t*>(q_out) = packed;
+  }
+#pragma unroll
+  for (int o = 4; o; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+  if (live && lane_in_blk == 0) {
+    *d_out = __float2half_rn(d);
+    if (s_out) *s_out = __float2half_rn(d * (float)sq);
+  }
+}
+
 // Tiled output for the prefill MMQ: per (tile of 128 rows, k-block) 4096 bytes in the UMMA K-major core-matrix order
 // (8-row x 16-byte core matrices, the 32 bytes of a block permuted as the nibble expansion permutes the weights:
 // position 4 (2 (i / 8) + (i & 1)) + (i & 7) / 2 for element i) followed by the 128 block scales as fp32.  Lane `sub`

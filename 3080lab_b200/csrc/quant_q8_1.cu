@@ -12,32 +12,6 @@ namespace q4b {
 
 namespace {
 
-// 8 lanes per block, 4 consecutive values per lane: each lane reads 8 bytes and writes 4.
-__device__ __forceinline__ void quant_block4(const float x[4], int8_t* q_out, __half* d_out, __half* s_out, int lane_in_blk,
-                                             bool live) {
-  float amax = fmaxf(fmaxf(fabsf(x[0]), fabsf(x[1])), fmaxf(fabsf(x[2]), fabsf(x[3])));
-#pragma unroll
-  for (int o = 4; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-  const float d = amax / 127.f;
-  int q[4], sq = 0;
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    q[i] = d > 0.f ? __float2int_rn(x[i] / d) : 0;
-    sq += q[i];
-  }
-  if (live) {
-    const uint32_t packed = (uint32_t)(q[0] & 0xFF) | ((uint32_t)(q[1] & 0xFF) << 8) | ((uint32_t)(q[2] & 0xFF) << 16) |
-                            ((uint32_t)(q[3] & 0xFF) << 24);
-    *reinterpret_cast<uint32_t*>(q_out) = packed;
-  }
-#pragma unroll
-  for (int o = 4; o; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
-  if (live && lane_in_blk == 0) {
-    *d_out = __float2half_rn(d);
-    if (s_out) *s_out = __float2half_rn(d * (float)sq);
-  }
-}
-
 __global__ void __launch_bounds__(256) quant_q8_1_tiled_kernel(const __half* x, uint8_t* xt, int P, int KB) {
   pdl_launch_dependents();
   pdl_wait();

@@ -98,14 +98,73 @@ def synth_shard(cfg: ModelConfig, rank: int, tp: int, seed: int = 0) -> dict:
             "rank": rank, "tp": tp}
 
 
+class PeerReduce:
+    """The partial-sum buffers and arrival flags of the fused reduction kernel (`q4b_tp_allreduce_resid_rmsnorm_q8`):
+    two partial buffers [rows, H] fp32 per rank, alternated from call to call, and one flag array per rank, all in
+    symmetric memory so that every rank can address every peer's copy over NVLink.  torch's symmetric-memory allocator
+    does the handle exchange; the data path is the library's own kernel (plain peer loads, no multicast).
+    With group=None the "group" is this process alone (world 1): plain device memory, same kernel."""
+
+    def __init__(self, rows: int, H: int, device, group=None):
+        import ctypes as C
+        self.rows, self.H, self.group = rows, H, group
+        self.epoch = 0
+        if group is None:
+            self.rank, self.world = 0, 1
+            self.parts = torch.zeros(2, rows, H, dtype=torch.float32, device=device)
+            self.flags = torch.zeros(rows, dtype=torch.int32, device=device)
+            part_ptrs, flag_ptrs = [self.parts.data_ptr()], [self.flags.data_ptr()]
+        else:
+            import os
+            import torch.distributed as dist
+            # plain peer mappings only: the kernel uses no multimem instruction, so no NVLink multicast object is bound
+            os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+            import torch.distributed._symmetric_memory as symm
+            self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+            self.parts = symm.empty((2, rows, H), dtype=torch.float32, device=device)
+            self.flags = symm.empty((self.world * rows,), dtype=torch.int32, device=device)
+            self.parts.zero_()
+            self.flags.zero_()
+            hp = symm.rendezvous(self.parts, group)
+            hf = symm.rendezvous(self.flags, group)
+            part_ptrs, flag_ptrs = [int(p) for p in hp.buffer_ptrs], [int(p) for p in hf.buffer_ptrs]
+            self._handles = (hp, hf)
+            torch.cuda.synchronize(device)
+            dist.barrier(group)                                   # every rank's flags are zero before anyone signals
+        nbytes = rows * H * 4
+        self._tables = []
+        for k in range(2):                                        # pointer tables of the two alternating buffer sets
+            pt = (C.c_void_p * self.world)(*[p + k * nbytes for p in part_ptrs])
+            self._tables.append(pt)
+        self._flag_table = (C.c_void_p * self.world)(*flag_ptrs)
+
+    def part(self) -> torch.Tensor:
+        """The buffer this rank's next partial goes into."""
+        return self.parts[self.epoch & 1]
+
+    def reduce_add(self, h, norm_w, eps: float, xq, xd, status) -> None:
+        """h += sum of all ranks' current partials; optionally the RMSNorm + Q8_1 of the result into (xq, xd)."""
+        from . import _ffi
+        from .qwen_kernels import _p, _stream
+        k = self.epoch & 1
+        self.epoch += 1
+        _ffi.call("q4b_tp_allreduce_resid_rmsnorm_q8", self._tables[k], self._flag_table, self.rank, self.world, self.epoch,
+                  _p(h), self.rows, self.H, _p(norm_w), float(eps), _p(xq), _p(xd), _p(status.word), _stream())
+
+
 class TPBatched:
     """B sequences, one decode token each per `step()`, on one rank of a tensor-parallel group.  Same op order as
     `engine.Batched`; the o_proj / down_proj partials are all-reduced (sum) before the residual add.  `group` is a
     torch.distributed process group (NCCL on GPUs); with group=None (tp = 1) it degenerates to the single-GPU path."""
 
-    def __init__(self, shard: dict, B: int, max_len: int, device, group=None):
+    def __init__(self, shard: dict, B: int, max_len: int, device, group=None, reduce: str = "nccl"):
+        """reduce: "nccl" = dist.all_reduce on the partial, then a residual add and the RMSNorm + Q8_1 launch;
+        "peer" = the library's one-shot reduction over peer memory with the residual add and the next RMSNorm + Q8_1
+        fused in (`PeerReduce`), one launch instead of three."""
         import torch.distributed as dist
-        self.dist, self.group = dist, group
+        if reduce not in ("nccl", "peer"):
+            raise ValueError("reduce: 'nccl' or 'peer'")
+        self.dist, self.group, self.reduce = dist, group, reduce
         self.B = B
         self.full: ModelConfig = shard.get("full_cfg", shard["cfg"])
         self.m = FusedQwen(shard, max_len=max_len, device=device)        # local weights, RoPE tables, packing
@@ -118,7 +177,8 @@ class TPBatched:
         self.qkv = torch.zeros(B, c.qkv_rows, dtype=f16, device=dv)
         self.att = torch.zeros(B, self.ko, dtype=f16, device=dv)         # zero beyond the local q rows (K padding)
         self.xm = torch.zeros(B, self.kd, dtype=f16, device=dv)
-        self.part = torch.zeros(B, c.hidden, dtype=f32, device=dv)
+        self.peer = PeerReduce(B, c.hidden, dv, group) if reduce == "peer" else None
+        self._part = None if self.peer else torch.zeros(B, c.hidden, dtype=f32, device=dv)
         kmax = max(c.hidden, self.ko, self.kd)
         self.xq = torch.zeros(B * kmax, dtype=torch.int8, device=dv)
         self.xd = torch.zeros(B * kmax // 32, dtype=f16, device=dv)
@@ -136,6 +196,7 @@ class TPBatched:
         self.allreduces_per_step = 2 * c.layers
         groups = (B + 31) // 32                                          # column groups per linear (<= 32 rows per launch)
         self.launches_per_step = 1 + c.layers * (4 + 4 * groups + 2 + (0 if self.att_view is not None else 1)) + 2 + groups
+        # (the peer path trades the two RMSNorm + Q8_1 launches of a layer for its two reduction launches: same count)
 
     def _gemm8(self, pair, N, Kdim, Y, aux, epi, ldy):
         """One linear over all B sequences; the tensor-core kernel takes up to 32 activation rows per launch."""
@@ -146,17 +207,45 @@ class TPBatched:
             QB.gemm8(Wt, St, self.xq[c0 * Kdim:], self.xd[c0 * (Kdim // 32):], Yf[c0 * ldy:], aux, N, Kdim, n, epi, ldy,
                      self.status)
 
-    def _reduce_add(self):
-        """h += sum over ranks of the partial [B, hidden]."""
+    @property
+    def part(self) -> torch.Tensor:
+        """Where this rank's next partial [B, hidden] goes."""
+        return self.peer.part() if self.peer else self._part
+
+    def _next_norm(self, i: int, which: str):
+        """The RMSNorm weights applied to h right after this reduction (None: the fp16-head path normalises separately)."""
+        m = self.m
+        if which == "o":
+            return m.L[i]["ln2"]
+        if i + 1 < len(m.L):
+            return m.L[i + 1]["ln1"]
+        return m.norm if m.head is not None else None
+
+    def _reduce_add(self, i: int, which: str):
+        """h += sum over ranks of the partial [B, hidden] (+ the next RMSNorm + Q8_1 on the peer path)."""
+        if self.peer:
+            nw = self._next_norm(i, which)
+            self.peer.reduce_add(self.h, nw, self.m.cfg.eps, self.xq if nw is not None else None,
+                                 self.xd if nw is not None else None, self.status)
+            return
         if self.group is not None:
-            self.dist.all_reduce(self.part, op=self.dist.ReduceOp.SUM, group=self.group)
-        self.h.add_(self.part)
+            self.dist.all_reduce(self._part, op=self.dist.ReduceOp.SUM, group=self.group)
+        self.h.add_(self._part)
 
     def step(self) -> None:
+        for i, which in self.phases():
+            self._reduce_add(i, which)
+
+    def phases(self):
+        """The step as a generator that stops wherever a partial [B, hidden] is ready in `self.part` (after o_proj and
+        after down_proj of every layer): the caller reduces it over the ranks, adds it to `self.h` and resumes.  `step()`
+        does that with the process group; `step_together` does it for several ranks living in one process."""
         m, c, H = self.m, self.m.cfg, self.m.cfg.hidden
+        fused = self.peer is not None                                    # the reduction kernel leaves (xq, xd) behind
         K.embed(m.embed, self.tok, self.h)
         for i, L in enumerate(m.L):
-            QB.rmsnorm_q8(self.h, L["ln1"], self.xq, self.xd, c.eps)
+            if not fused or i == 0:
+                QB.rmsnorm_q8(self.h, L["ln1"], self.xq, self.xd, c.eps)
             self._gemm8(L["qkv"], c.qkv_rows, H, self.qkv, L["qkv_b"], "biasf", c.qkv_rows)
             if self.att_view is None:
                 # the attention kernel writes rows of c.q_rows values; with K padding they land in a staging buffer first
@@ -168,20 +257,23 @@ class TPBatched:
                        c.head_dim, m.max_len, m.scale, self.attn_ws)
             QB.quant_q8(self.att, self.xq, self.xd)
             self._gemm8(L["o"], H, self.ko, self.part, None, "logits", H)
-            self._reduce_add()
-            QB.rmsnorm_q8(self.h, L["ln2"], self.xq, self.xd, c.eps)
+            yield i, "o"
+            if not fused:
+                QB.rmsnorm_q8(self.h, L["ln2"], self.xq, self.xd, c.eps)
             if self.kd == c.ffn:
                 self._gemm8(L["gu"], 2 * c.ffn, H, self.xm, None, "swiglu", c.ffn)
             else:
                 self._gemm8(L["gu"], 2 * c.ffn, H, self.xm, None, "swiglu", self.kd)   # pitch = padded K, tail stays zero
             QB.quant_q8(self.xm, self.xq, self.xd)
             self._gemm8(L["down"], H, self.kd, self.part, None, "logits", H)
-            self._reduce_add()
+            yield i, "down"
         if m.head is None:
             K.rms(self.h, m.norm, self.x, c.eps)
-            QB.head_batched(m.head16, self.x, self.logits)
+            for c0 in range(0, self.B, 32):                               # the fp16 head kernel takes up to 32 rows
+                QB.head_batched(m.head16, self.x[c0:c0 + 32], self.logits[c0:c0 + 32])
         else:
-            QB.rmsnorm_q8(self.h, m.norm, self.xq, self.xd, c.eps)
+            if not fused:
+                QB.rmsnorm_q8(self.h, m.norm, self.xq, self.xd, c.eps)
             self._gemm8(m.head, c.vocab, H, self.logits, None, "logits", c.vocab)
         K.finish(self.logits, self.tok, self.pos, self.head_ws)
 
@@ -214,3 +306,21 @@ class TPBatched:
         self.tok.copy_(tok0)
         torch.cuda.synchronize()
         return g
+
+
+def step_together(ranks) -> None:
+    """One decode step of all tensor-parallel ranks held in ONE process (every `TPBatched` built with group=None, each on
+    its own shard): the ranks advance in lock step and their partials are summed in rank order where a process group
+    would all-reduce them.  This is the multi-rank data path without NCCL; it exists for tests on a single GPU."""
+    gens = [r.phases() for r in ranks]
+    while True:
+        alive = [next(g, None) is not None for g in gens]
+        if not any(alive):
+            return
+        if not all(alive):
+            raise RuntimeError("tensor-parallel ranks fell out of step")
+        total = ranks[0].part.clone()
+        for r in ranks[1:]:
+            total.add_(r.part.to(total.device))
+        for r in ranks:
+            r.h.add_(total.to(r.h.device))

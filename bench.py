@@ -696,7 +696,8 @@ def bench_tp7b(args, rank: int, world: int, local_rank: int, torch, dist) -> dic
         cfg = synth.ModelConfig(cfg.name, args.layers, cfg.hidden, cfg.ffn, cfg.n_heads, cfg.n_kv_heads, cfg.head_dim, cfg.vocab,
                                 cfg.eps, cfg.rope_theta, cfg.tied_fp16_head)
     shard = tpm.synth_shard(cfg, rank % tp, tp, seed=0)
-    eng = tpm.TPBatched(shard, B, ctx + 128, f"cuda:{local_rank}", group)
+    reduce = args.tp_reduce if tp > 1 else "nccl"
+    eng = tpm.TPBatched(shard, B, ctx + 128, f"cuda:{local_rank}", group, reduce=reduce)
     eng.kc.normal_()
     eng.vc.normal_()
     eng.pos.fill_(ctx)
@@ -762,8 +763,11 @@ def bench_tp7b(args, rank: int, world: int, local_rank: int, torch, dist) -> dic
         "dtype": "int8 x int4 -> int32, fp32 scaling", "data": "synthetic",
         "config": {"workload": f"qwen2.5-7b-shape batched decode, 64 sequences per replica, 2048-token KV context, "
                                f"{cfg.layers} layers", "parallelism": f"tp{tp} x dp{dp}",
-                   "collective": f"NCCL all-reduce of [64, {cfg.hidden}] fp32 after o_proj and down_proj "
-                                 f"({2 * cfg.layers} per step)" if tp > 1 else "none",
+                   "collective": "none" if tp == 1 else
+                                 (f"own one-shot reduction of [64, {cfg.hidden}] fp32 over peer memory (plain NVLink loads), fused "
+                                  f"with the residual add and the next RMSNorm + Q8_1" if reduce == "peer" else
+                                  f"NCCL all-reduce of [64, {cfg.hidden}] fp32") +
+                                 f" after o_proj and down_proj ({2 * cfg.layers} per step)",
                    "l2": "weights + KV streamed per step are larger than L2"},
         "roofline": {"bound": "hbm", "kernel": "whole step, per GPU", "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                      "frac": ach / peaks["hbm_gbs"], "peak_kind": f"of {peak_kind}", "traffic": None},
@@ -796,6 +800,8 @@ def main() -> None:
                     choices=["decode_b1", "gemv_ffn_up", "batched8", "batched32", "prefill2048", "tp7b"],
                     help="decode_b1 is the benchmark (it carries the others under \"sub\"); the others run one configuration "
                          "alone; tp7b is the tensor-parallel 7B configuration (any --gpus, under torch.distributed.run)")
+    ap.add_argument("--tp-reduce", default="peer", choices=["peer", "nccl"],
+                    help="tp7b: the reduction after o_proj / down_proj: the library's fused peer-memory kernel or NCCL")
     ap.add_argument("--cuda-core", action="store_true", help="linears on the CUDA-core GEMV instead of the tensor-core kernels")
     ap.add_argument("--tcgen05", action="store_true", help="batch-1 linears on the tcgen05 exact-digit GEMV instead of the mma.sync one")
     ap.add_argument("--prompt", type=int, default=PROMPT, help="prompt length (512 = the benchmark configuration)")

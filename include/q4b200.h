@@ -383,6 +383,29 @@ typedef struct {
 #define Q4B_STEP_LOOKAHEAD 8    /* with Q4B_STEP_MMA_GEMV: each GEMV launch also asks for the weights of launches two to three
                                    places down the chain to be brought into L2 (cp.async.bulk.prefetch.L2); off by default */
 
+/* ---- tensor-parallel reduction fused with the residual add and the next RMSNorm + Q8_1 quantiser ---------------------
+ * h[b, :] += sum over ranks r = 0 .. world - 1 (in that order) of parts[r][b, :];  then, when norm_w is given,
+ * (xq, xd) = Q8_1(round16(RMSNorm(h[b, :]) * norm_w)) exactly as q4b_rmsnorm_q8_1 would produce them.  One launch in
+ * place of an NCCL all-reduce, the residual add and the quantiser (the reference is single-GPU: its pieces are the
+ * `resid` epilogue, lab/qwen_kernels.py:21-45, and rmsnorm_q8_source, lab/qwen_batched.py:1044-1091).
+ * parts / flags are HOST arrays of `world` device pointers valid on this GPU: parts[r] = rank r's partial [rows, H] fp32
+ * for THIS call, flags[r] = rank r's flag array of world * rows uint32 (zeroed once, before the first call, on every
+ * rank).  Peer memory is read with plain loads over NVLink (no multicast).  Contract: every rank calls with the same,
+ * strictly increasing `epoch` (1, 2, ...), and alternates between two sets of partial buffers from call to call, so
+ * that a rank's next-but-one GEMM cannot overwrite a partial a peer is still reading.  world = 1 degenerates to
+ * h += parts[0] (flags unused).  H a multiple of 32, at most 4096; one CTA per row.
+ * status: bit 1 is set when the bounded wait for a peer's arrival expired (the kernel then finishes on whatever it
+ * reads; no hang). */
+int q4b_tp_allreduce_resid_rmsnorm_q8(const void* const* parts, void* const* flags, int rank, int world, uint32_t epoch,
+                                      float* h, int rows, int H, const float* norm_w, float eps, void* xq, void* xd,
+                                      uint32_t* status, q4b_stream_t stream);
+
+/* Exercise of that kernel's failure path in a form that always returns: the same call with the wait cut to a few
+ * thousand polls.  With flags nobody raises (a peer that never arrives) the wait gives up, *status gets bit 1, the
+ * kernel finishes. */
+int q4b_debug_tp_allreduce_expired_wait(const void* const* parts, void* const* flags, int rank, int world, uint32_t epoch,
+                                        float* h, int rows, int H, uint32_t* status, q4b_stream_t stream);
+
 int q4b_decode_step(const q4b_decode_desc* desc, q4b_stream_t stream);
 
 /* ---- persistent decode: every layer of one batch-1 token in ONE cooperative kernel, one CTA per SM -------------
