@@ -65,8 +65,9 @@ int gemv_mma(const void*, const void*, const void*, void*, const void*, int, int
              const int64_t* pos = nullptr, void* kc = nullptr, void* vc = nullptr, int NH = 0, int NKV = 0, int HD = 0,
              int max_len = 0, int withhold_chunk = -1, const GemvLookahead* look = nullptr);
 int gemv_mma_ksplit(int, int);
-int tp_allreduce(const void* const*, void* const*, int, int, uint32_t, float*, int, int, const float*, float, void*, void*, uint32_t*,
-                 uint32_t, cudaStream_t);
+int tp_allreduce(const void* const*, void* const*, int, int, uint32_t, const uint32_t*, float*, int, int, const float*, float, void*,
+                 void*, uint32_t*, uint32_t, cudaStream_t);
+int tp_epoch_advance(uint32_t*, uint32_t, cudaStream_t);
 int gemv_f16mma(const void*, const void*, const void*, void*, const void*, int, int, int, int, int, uint32_t*, cudaStream_t);
 double peak_i8_launch(int, uint32_t*, cudaStream_t);
 int head_q6_k_argmax(const void*, const void*, const void*, const void*, const void*, float*, int, int, int64_t*, int64_t*, void*, size_t,
@@ -219,14 +220,16 @@ int q4b_gemv_q4_0_f16mma(const void* W, const void* Sc, const void* X, void* Y, 
 }
 
 int q4b_tp_allreduce_resid_rmsnorm_q8(const void* const* parts, void* const* flags, int rank, int world, uint32_t epoch,
-                                      float* h, int rows, int H, const float* norm_w, float eps, void* xq, void* xd,
-                                      uint32_t* status, q4b_stream_t stream) {
-  return tp_allreduce(parts, flags, rank, world, epoch, h, rows, H, norm_w, eps, xq, xd, status, 0u, S(stream));
+                                      const uint32_t* epoch_base, float* h, int rows, int H, const float* norm_w, float eps,
+                                      void* xq, void* xd, uint32_t* status, q4b_stream_t stream) {
+  return tp_allreduce(parts, flags, rank, world, epoch, epoch_base, h, rows, H, norm_w, eps, xq, xd, status, 0u, S(stream));
 }
+
+int q4b_tp_epoch_advance(uint32_t* epoch_base, uint32_t by, q4b_stream_t stream) { return tp_epoch_advance(epoch_base, by, S(stream)); }
 
 int q4b_debug_tp_allreduce_expired_wait(const void* const* parts, void* const* flags, int rank, int world, uint32_t epoch,
                                         float* h, int rows, int H, uint32_t* status, q4b_stream_t stream) {
-  return tp_allreduce(parts, flags, rank, world, epoch, h, rows, H, nullptr, 0.f, nullptr, nullptr, status, 4096u, S(stream));
+  return tp_allreduce(parts, flags, rank, world, epoch, nullptr, h, rows, H, nullptr, 0.f, nullptr, nullptr, status, 4096u, S(stream));
 }
 
 int q4b_debug_gemv_mma_expired_wait(const void* W, const void* Sc, const void* X, void* Y, int N, int K, uint32_t* status,

@@ -17,7 +17,9 @@
 // with a bound, for slot [r][b] of its own array to reach `epoch` for every peer r (acquire, system scope).  Partials
 // are double-buffered by the caller (consecutive calls alternate buffers) and epochs only grow: a rank can reach call
 // k + 2, whose GEMM overwrites buffer k % 2, only after every peer has arrived at call k + 1, i.e. finished reading
-// call k.  An expired wait sets the status word and the kernel finishes (garbage out, no hang).
+// call k.  An expired wait sets the status word and the kernel finishes (garbage out, no hang).  The epoch is the
+// sum of a launch argument and an optional device word, so a step captured once as a CUDA graph (arguments frozen) can be
+// replayed: the word is advanced by the number of reductions per step at the end of every step.
 #include "q4b_internal.h"
 
 namespace q4b {
@@ -34,6 +36,7 @@ struct ArArgs {
   int8_t* xq;
   __half* xd;
   uint32_t* status;
+  const uint32_t* epoch_base;      // device word added to `epoch` (lets a captured graph replay with growing epochs), or null
   float eps;
   int rank, world, rows, H;
   uint32_t epoch, wait_limit;
@@ -61,13 +64,14 @@ __global__ void __launch_bounds__(1024) tp_allreduce_kernel(const ArArgs a) {
   pdl_launch_dependents();
   pdl_wait();                                             // this rank's partial is complete
   if (t == 0) expired = 0;
+  const uint32_t epoch = a.epoch + (a.epoch_base ? *a.epoch_base : 0u);
   if (t < a.world && t != a.rank) {
     __threadfence_system();
-    st_release_sys(a.flags[t] + (size_t)a.rank * a.rows + row, a.epoch);
+    st_release_sys(a.flags[t] + (size_t)a.rank * a.rows + row, epoch);
     const uint32_t* mine = a.flags[a.rank] + (size_t)t * a.rows + row;
     bool ok = false;
     for (uint32_t i = 0; i < a.wait_limit; ++i) {
-      if ((int32_t)(ld_acquire_sys(mine) - a.epoch) >= 0) {
+      if ((int32_t)(ld_acquire_sys(mine) - epoch) >= 0) {
         ok = true;
         break;
       }
@@ -114,9 +118,21 @@ __global__ void __launch_bounds__(1024) tp_allreduce_kernel(const ArArgs a) {
   quant_block4(v, a.xq + at, a.xd + (at >> 5), nullptr, t & 7, live);   // whole 8-lane groups are live or dead together
 }
 
+__global__ void tp_epoch_advance_kernel(uint32_t* base, uint32_t by) {
+  pdl_launch_dependents();
+  pdl_wait();                                             // every reduction of the step has read the old value
+  if (threadIdx.x == 0) *base += by;
+}
+
 }  // namespace
 
-int tp_allreduce(const void* const* parts, void* const* flags, int rank, int world, uint32_t epoch, float* h, int rows, int H,
+int tp_epoch_advance(uint32_t* base, uint32_t by, cudaStream_t st) {
+  if (!base) return fail(Q4B_E_ALIGN, "tp_epoch_advance: null pointer");
+  return check_launch(launch_pdl(tp_epoch_advance_kernel, dim3(1), dim3(32), 0, st, base, by), "tp_epoch_advance");
+}
+
+int tp_allreduce(const void* const* parts, void* const* flags, int rank, int world, uint32_t epoch, const uint32_t* epoch_base,
+                 float* h, int rows, int H,
                  const float* norm_w, float eps, void* xq, void* xd, uint32_t* status, uint32_t wait_limit, cudaStream_t st) {
   if (world < 1 || world > MAX_RANKS || rank < 0 || rank >= world) return fail(Q4B_E_ARG, "tp_allreduce: 1 <= world <= 8, 0 <= rank < world");
   if (rows <= 0 || H <= 0 || (H % 32) || H > 4096) return fail(Q4B_E_SHAPE, "tp_allreduce: rows > 0, H a multiple of 32, at most 4096");
@@ -134,10 +150,11 @@ int tp_allreduce(const void* const* parts, void* const* flags, int rank, int wor
   a.xq = reinterpret_cast<int8_t*>(xq);
   a.xd = reinterpret_cast<__half*>(xd);
   a.status = status;
+  a.epoch_base = epoch_base;
   a.eps = eps;
   a.rank = rank; a.world = world; a.rows = rows; a.H = H;
   a.epoch = epoch;
-  a.wait_limit = wait_limit ? wait_limit : (1u << 22);   // x 64 ns sleeps: a fraction of a second
+  a.wait_limit = wait_limit ? wait_limit : (1u << 24);   // polls with a 64 ns sleep each: several seconds at most
   const int threads = ((H / 4 + 31) / 32) * 32;
   return check_launch(launch_pdl(tp_allreduce_kernel, dim3(rows), dim3(threads), 0, st, a), "tp_allreduce");
 }

@@ -108,7 +108,8 @@ class PeerReduce:
     def __init__(self, rows: int, H: int, device, group=None):
         import ctypes as C
         self.rows, self.H, self.group = rows, H, group
-        self.epoch = 0
+        self.call = 0                                             # index of the next reduction inside the current step
+        self.base = torch.zeros(1, dtype=torch.int32, device=device)   # reductions made by the steps before (device word)
         if group is None:
             self.rank, self.world = 0, 1
             self.parts = torch.zeros(2, rows, H, dtype=torch.float32, device=device)
@@ -140,16 +141,27 @@ class PeerReduce:
 
     def part(self) -> torch.Tensor:
         """The buffer this rank's next partial goes into."""
-        return self.parts[self.epoch & 1]
+        return self.parts[self.call & 1]
 
     def reduce_add(self, h, norm_w, eps: float, xq, xd, status) -> None:
-        """h += sum of all ranks' current partials; optionally the RMSNorm + Q8_1 of the result into (xq, xd)."""
+        """h += sum of all ranks' current partials; optionally the RMSNorm + Q8_1 of the result into (xq, xd).  The epoch
+        is (calls of the steps before, kept in a device word) + (index of this call in the step + 1)."""
         from . import _ffi
         from .qwen_kernels import _p, _stream
-        k = self.epoch & 1
-        self.epoch += 1
-        _ffi.call("q4b_tp_allreduce_resid_rmsnorm_q8", self._tables[k], self._flag_table, self.rank, self.world, self.epoch,
-                  _p(h), self.rows, self.H, _p(norm_w), float(eps), _p(xq), _p(xd), _p(status.word), _stream())
+        k = self.call
+        self.call += 1
+        _ffi.call("q4b_tp_allreduce_resid_rmsnorm_q8", self._tables[k & 1], self._flag_table, self.rank, self.world, k + 1,
+                  _p(self.base), _p(h), self.rows, self.H, _p(norm_w), float(eps), _p(xq), _p(xd), _p(status.word), _stream())
+
+    def end_step(self) -> None:
+        """Close a step: the device epoch word moves on by the number of reductions the step made (it must be even, so
+        that the buffer alternation repeats), and the call index starts over.  Part of the step when it is captured."""
+        from . import _ffi
+        from .qwen_kernels import _p, _stream
+        if self.call & 1:
+            raise RuntimeError("PeerReduce: a step must make an even number of reductions")
+        _ffi.call("q4b_tp_epoch_advance", _p(self.base), self.call, _stream())
+        self.call = 0
 
 
 class TPBatched:
@@ -235,6 +247,8 @@ class TPBatched:
     def step(self) -> None:
         for i, which in self.phases():
             self._reduce_add(i, which)
+        if self.peer:
+            self.peer.end_step()
 
     def phases(self):
         """The step as a generator that stops wherever a partial [B, hidden] is ready in `self.part` (after o_proj and
@@ -284,11 +298,13 @@ class TPBatched:
         Candidates that reading the capture path leaves open: programmatic-dependent-launch edges on the kernels directly
         in front of and behind a captured NCCL kernel node; NCCL's internal stream joined into the capture through event
         waits after a warm-up that ran on a side stream; two communicators (the world group for barriers, the tensor-
-        parallel group inside the graph) in flight on one GPU.  Until one of them is confirmed the multi-rank step is
-        launched op by op, and this method refuses to record the known-hanging form."""
-        if self.group is not None:
+        parallel group inside the graph) in flight on one GPU.  Until one of them is confirmed this method refuses to
+        record that form.  With reduce="peer" the step holds only this library's kernels (the reduction included, its
+        epochs taken from a device word) and is captured on any number of ranks; every rank must capture and replay in
+        step with the others."""
+        if self.group is not None and not self.peer:
             raise RuntimeError("TPBatched.capture: a CUDA graph holding the NCCL all-reduces did not complete on this "
-                               "platform; run step() op by op when a process group is set")
+                               "platform; run step() op by op, or build the engine with reduce='peer'")
         torch.cuda.synchronize()
         pos0, tok0 = self.pos.clone(), self.tok.clone()
         side = torch.cuda.Stream()

@@ -705,7 +705,7 @@ def bench_tp7b(args, rank: int, world: int, local_rank: int, torch, dist) -> dic
     sampler = ClockSampler(local_rank)
     # One GPU: the step is replayed as a CUDA graph.  With tensor parallelism the step is launched op by op (capturing a
     # graph that holds NCCL all-reduces is refused by TPBatched.capture, see there).
-    run_step = eng.capture().replay if tp == 1 else eng.step
+    run_step = eng.capture().replay if (tp == 1 or reduce == "peer") else eng.step
 
     def barrier():
         if world > 1:

@@ -397,8 +397,10 @@ typedef struct {
  * status: bit 1 is set when the bounded wait for a peer's arrival expired (the kernel then finishes on whatever it
  * reads; no hang). */
 int q4b_tp_allreduce_resid_rmsnorm_q8(const void* const* parts, void* const* flags, int rank, int world, uint32_t epoch,
-                                      float* h, int rows, int H, const float* norm_w, float eps, void* xq, void* xd,
-                                      uint32_t* status, q4b_stream_t stream);
+                                      const uint32_t* epoch_base, float* h, int rows, int H, const float* norm_w, float eps,
+                                      void* xq, void* xd, uint32_t* status, q4b_stream_t stream);
+/* *epoch_base += by, ordered after the launches before it on the stream (see above). */
+int q4b_tp_epoch_advance(uint32_t* epoch_base, uint32_t by, q4b_stream_t stream);
 
 /* Exercise of that kernel's failure path in a form that always returns: the same call with the wait cut to a few
  * thousand polls.  With flags nobody raises (a peer that never arrives) the wait gives up, *status gets bit 1, the

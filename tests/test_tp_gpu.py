@@ -30,10 +30,13 @@ def _worker(rank, world, port, out_dir, reduce="nccl"):
     ref = E.Batched(E.FusedQwen(model, max_len=64, device=f"cuda:{rank}"), B) if rank == 0 else None
     toks = torch.from_numpy(np.stack([synth.synth_prompt(cfg, 1, 100 + b) for b in range(B)])[:, 0]).cuda(rank)
     errs = []
-    for _ in range(steps):
+    run = eng.step
+    for it in range(steps):
         dist.broadcast(toks, 0)                                   # every rank feeds the same (reference) tokens
         eng.tok.copy_(toks)
-        eng.step()
+        if reduce == "peer" and it == steps // 2:                 # second half: the step replayed as a CUDA graph
+            run = eng.capture().replay
+        run()
         if rank == 0:
             ref.tok.copy_(toks)
             ref.step()
@@ -125,14 +128,17 @@ def test_peer_reduce_kernel_single_rank_equals_add_then_quantiser():
     h = torch.randn(rows, H, device="cuda", generator=g)
     w = 1.0 + 0.1 * torch.randn(H, device="cuda", generator=g)
     st = QB.Status("cuda")
-    for it in range(3):
+    for it in range(4):
+        if it == 2:
+            pr.end_step()                                         # two calls make a step; the epoch word moves on
+            assert int(pr.base.item()) == 2
         part = pr.part()
         part.copy_(torch.randn(rows, H, device="cuda", generator=g))
         want_h = h + part
         xq, xd = torch.zeros(rows * H, dtype=torch.int8, device="cuda"), torch.zeros(rows * H // 32, dtype=torch.float16, device="cuda")
         wq, wd = torch.zeros_like(xq), torch.zeros_like(xd)
         QB.rmsnorm_q8(want_h, w, wq, wd, 1e-6)
-        if it == 2:                                               # last call without the fused quantiser
+        if it == 2:                                               # a call without the fused quantiser
             pr.reduce_add(h, None, 1e-6, None, None, st)
         else:
             pr.reduce_add(h, w, 1e-6, xq, xd, st)
