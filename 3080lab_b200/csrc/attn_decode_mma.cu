@@ -1,8 +1,8 @@
 // Decode attention for batches of sequences: one new token per sequence against its fp16 K/V cache, on the fp16
 // tensor cores.  Throughput-oriented sibling of attn_decode.cu (which is built for the latency of a single sequence).
 //
-// Reference arithmetic: ATTN_DECODE_GQA (lab/qwen_kernels.py:116-225) as used per sequence by the batched engine
-// (lab/qwen_batched.py:214-291): q and the new k are rotated (rotate-half pairs d, d + 64) from the fp16 biased QKV
+// Reference arithmetic: ATTN4 (lab/qwen_kernels.py:517-605) as the batched engine launches it per sequence
+// (`batchify`d, scripts/qwen_batched_decode.py:70-83, 116-121): q and the new k are rotated (rotate-half pairs d, d + 64) from the fp16 biased QKV
 // row and rounded to fp16, k/v are appended at posp[b], scores = q.k * scale over positions 0..pos, fp32 soft-max,
 // out = P.V rounded to fp16.
 //
@@ -343,14 +343,9 @@ void attn_decode_mma_trace(unsigned long long* buf) { g_attn_trace = buf; }
 int attn_decode_mma(const void* qkv, const float* cosT, const float* sinT, const int64_t* pos, void* kc, void* vc, void* out, int B,
                     int NH, int NKV, int max_len, float scale, cudaStream_t st, void* xq, void* xd) {
   if (xq && (!xd || ((NH / NKV) * HD) % (NCL * 32) != 0)) return Q4B_E_SHAPE;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attn_decode_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)DYN_SMEM);
-    if (e != cudaSuccess) {
-      set_cuda_error(e, "attn_decode_mma: cudaFuncSetAttribute");
-      return Q4B_E_CUDA;
-    }
-    configured = true;
+  if (cudaError_t e = ensure_dynamic_smem(reinterpret_cast<const void*>(&attn_decode_mma_kernel), DYN_SMEM); e != cudaSuccess) {
+    set_cuda_error(e, "attn_decode_mma: cudaFuncSetAttribute");
+    return Q4B_E_CUDA;
   }
   const int chunk = ((max_len + NCL - 1) / NCL + TILE - 1) / TILE * TILE;
   const float scale_log2e = scale * 1.4426950408889634f;

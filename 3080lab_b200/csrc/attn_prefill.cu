@@ -265,14 +265,9 @@ int attn_prefill(const void* qkv, const float* cosT, const float* sinT, void* kc
   if (!qkv || (!pre && (!cosT || !sinT)) || !kc || !vc || (!out && !xt) || !aligned16(kc) || !aligned16(vc) || !aligned16(qkv) ||
       !aligned16(out) || !aligned16(xt))
     return fail(Q4B_E_ALIGN, "attn_prefill: null or misaligned pointer");
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(flash_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FLASH_SMEM);
-    if (e != cudaSuccess) {
-      set_cuda_error(e, "attn_prefill: cudaFuncSetAttribute");
-      return Q4B_E_CUDA;
-    }
-    configured = true;
+  if (cudaError_t e = ensure_dynamic_smem(reinterpret_cast<const void*>(&flash_prefill_kernel), FLASH_SMEM); e != cudaSuccess) {
+    set_cuda_error(e, "attn_prefill: cudaFuncSetAttribute");
+    return Q4B_E_CUDA;
   }
   if (!pre) {
     int rc = check_launch(launch_pdl(rope_kv_append_kernel, dim3(P, NKV), dim3(HD), 0, st, (const __half*)qkv, cosT, sinT,

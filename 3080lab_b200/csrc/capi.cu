@@ -39,15 +39,17 @@ unsigned long long* trace_slot(int kernel_id, int ctas) {
   return p;
 }
 
+// SM count of the CURRENT device (cached per device ordinal; grids are sized from it)
 int sm_count() {
-  if (g_sm_count <= 0) {
-    int dev = 0, n = 0;
-    if (cudaGetDevice(&dev) == cudaSuccess && cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && n > 0)
-      g_sm_count = n;
-    else
-      return 148;
+  static int per_dev[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return g_sm_count > 0 ? g_sm_count : 148;
+  if (per_dev[dev] <= 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && n > 0) per_dev[dev] = n;
+    else return g_sm_count > 0 ? g_sm_count : 148;
   }
-  return g_sm_count;
+  return per_dev[dev];
 }
 
 // per-op launchers (defined next to their kernels)

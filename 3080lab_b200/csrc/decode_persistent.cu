@@ -17,7 +17,7 @@
 //   * ops are separated by grid barriers (one release-add and an acquire-poll on a global counter, bounded).  Split-K
 //     partial sums go to global scratch and are added, in slice order, by the consumer while it stages its operand, so
 //     the residual add and the RMSNorm (lab/qwen_kernels.py:683-705) cost no extra pass and results are bit-repeatable.
-//   * attention (lab/qwen_kernels.py:116-225 arithmetic: RoPE, fp16 K/V append, soft-max, P.V) runs as (KV head,
+//   * attention (ATTN4 arithmetic, lab/qwen_kernels.py:517-605: RoPE, fp16 K/V append, soft-max, P.V) runs as (KV head,
 //     position chunk) units; its partials (max, sum, unnormalised output) are merged by the o_proj units on read.
 //
 // Measured on B200 (Qwen2.5-1.5B shape, context 512): 1.63 ms per token against 1.00 ms for the chain of per-op
@@ -903,10 +903,8 @@ int decode_persistent_layers(const q4b_decode_desc* d, void* ws, size_t ws_bytes
   a.bkb = p.bkb;
   a.nch_max = p.nch_max;
   auto kern = d->head_dim == 128 ? decode_persistent_kernel<128> : decode_persistent_kernel<64>;
-  static bool configured[2] = {false, false};
-  const int ki = d->head_dim == 128 ? 0 : 1;
-  if (!configured[ki]) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_DYN_SMEM);
+  {
+    cudaError_t e = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), MAX_DYN_SMEM);
     if (e != cudaSuccess) {
       set_cuda_error(e, "decode_persistent: cudaFuncSetAttribute");
       return Q4B_E_CUDA;
@@ -917,7 +915,6 @@ int decode_persistent_layers(const q4b_decode_desc* d, void* ws, size_t ws_bytes
       if (e != cudaSuccess) set_cuda_error(e, "decode_persistent: occupancy query");
       return e != cudaSuccess ? Q4B_E_CUDA : fail(Q4B_E_SHAPE, "decode_persistent: the kernel does not fit one CTA per SM");
     }
-    configured[ki] = true;
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(p.ncta, 1, 1);

@@ -86,16 +86,13 @@ __global__ void __launch_bounds__(HBT, 1) head_f16_batched_kernel(const uint4* _
 
 template <int NB>
 int launch_hb(const void* E, const void* x, float* logits, int V, int H, int B, cudaStream_t st) {
-  static bool configured = false;
   const size_t smem = (size_t)8 * NB * ((size_t)H * 2 + 64);
   auto kern = head_f16_batched_kernel<NB>;
-  if (!configured && smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-    if (e != cudaSuccess) {
+  if (smem > 48 * 1024) {
+    if (cudaError_t e = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), 200 * 1024); e != cudaSuccess) {
       set_cuda_error(e, "head_f16_batched: cudaFuncSetAttribute");
       return Q4B_E_CUDA;
     }
-    configured = true;
   }
   int grid = sm_count();
   const int groups = (V + 15) / 16;

@@ -391,14 +391,9 @@ int mmq_prefill(const void* Wt, const void* St, const void* Xt, void* Y, const v
   if (!Wt || !St || !Xt || !Y || !status || !aligned16(Wt) || !aligned16(St) || !aligned16(Xt))
     return fail(Q4B_E_ALIGN, "mmq_prefill: null or misaligned pointer");
   if (epilogue == Q4B_EPI_BIASF && !AUX) return fail(Q4B_E_ALIGN, "mmq_prefill: biasf needs AUX");
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(mmq_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PF_SMEM);
-    if (e != cudaSuccess) {
-      set_cuda_error(e, "mmq_prefill: cudaFuncSetAttribute");
-      return Q4B_E_CUDA;
-    }
-    configured = true;
+  if (cudaError_t e = ensure_dynamic_smem(reinterpret_cast<const void*>(&mmq_prefill_kernel), PF_SMEM); e != cudaSuccess) {
+    set_cuda_error(e, "mmq_prefill: cudaFuncSetAttribute");
+    return Q4B_E_CUDA;
   }
   PrefillArgs a;
   a.Wt = reinterpret_cast<const uint8_t*>(Wt);

@@ -74,7 +74,6 @@ __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t by
                : "memory");
 }
 // position of element i (0..31) of a k-block inside the 32 operand bytes (see tc::expand_nibbles)
-__device__ __forceinline__ int perm_pos(int i) { return 4 * (2 * (i >> 3) + (i & 1)) + ((i & 7) >> 1); }
 
 template <int NT>
 __device__ __forceinline__ uint32_t b_offset(int kbl, int n, int pos) {
@@ -286,7 +285,7 @@ __global__ void __launch_bounds__(ROWS * ((MODE == MODE_Q8 && NT >= 16) ? 2 : 1)
       int X[4];
 #pragma unroll
       for (int j = 0; j < 4; ++j) X[j] = live ? __float2int_rn(x[j] * inv) : 0;
-      // elements 4 sub + {0, 2} are adjacent operand bytes, and so are 4 sub + {1, 3} (see perm_pos)
+      // elements 4 sub + {0, 2} are adjacent operand bytes, and so are 4 sub + {1, 3} (operand byte of element i: 4 (2 (i / 8) + (i & 1)) + (i & 7) / 2)
       const int pos02 = 8 * (sub >> 1) + 2 * (sub & 1), pos13 = pos02 + 4;
 #pragma unroll
       for (int j = 0; j < NL; ++j) {
@@ -599,15 +598,10 @@ bool plan(int N, int K, int nt, int nacc, Geometry& g) {
 
 template <int MODE, int NT>
 int launch(const StreamArgs& a, const Geometry& g, cudaStream_t st) {
-  static size_t configured = 0;
   auto kern = mmq_stream_kernel<MODE, NT>;
-  if (g.smem > configured) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_DYN_SMEM);
-    if (e != cudaSuccess) {
-      set_cuda_error(e, "mmq_stream: cudaFuncSetAttribute");
-      return Q4B_E_CUDA;
-    }
-    configured = MAX_DYN_SMEM;
+  if (cudaError_t e = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), MAX_DYN_SMEM); e != cudaSuccess) {
+    set_cuda_error(e, "mmq_stream: cudaFuncSetAttribute");
+    return Q4B_E_CUDA;
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((a.N + ROWS - 1) / ROWS, g.ksplit, 1);

@@ -4,6 +4,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <map>
 #include <mutex>
 #include <set>
 #include <utility>
@@ -51,6 +52,22 @@ inline void prefer_max_shared(const void* kern) {
   std::lock_guard<std::mutex> lock(mu);
   if (done.insert({kern, dev}).second)
     cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared);
+}
+
+// cudaFuncSetAttribute(MaxDynamicSharedMemorySize) is per device: raise the limit of `kern` to `bytes` once per (kernel,
+// device), so that a process that drives several GPUs configures each of them.  Returns a cudaError_t.
+inline cudaError_t ensure_dynamic_smem(const void* kern, size_t bytes) {
+  static std::mutex mu;
+  static std::map<std::pair<const void*, int>, size_t> done;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  std::lock_guard<std::mutex> lock(mu);
+  size_t& have = done[{kern, dev}];
+  if (bytes <= have) return cudaSuccess;
+  e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+  if (e == cudaSuccess) have = bytes;
+  return e;
 }
 
 // Ranges a batch-1 GEMV launch asks to be brought into L2 for launches further down the chain (see gemv_mma.cu).

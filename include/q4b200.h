@@ -129,7 +129,9 @@ int q4b_head_q6_k_argmax(const void* L, const void* Hb, const void* SC, const vo
  *     first call before any stream capture begins;
  *   - all calls on a device share the one array: two calls whose kernels can overlap on the GPU (different streams,
  *     no ordering between them) race on it and give wrong results.  Calls ordered on one stream are fine; the counters
- *     are cleared at the start of every call. */
+ *     are cleared at the start of every call;
+ *   - the looked-up address is kept for as long as the device's primary context lives (after a cudaDeviceReset or a
+ *     context teardown it is stale: reload the library), and `stream` must belong to the device that is current. */
 int q4b_argmax_advance_static(const float* logits, int rows, int V, int64_t* tok, int64_t* pos, q4b_stream_t stream);
 
 /* LM head over the tied fp16 table for B = 1..32 sequences: logits fp32 [B, V] = x fp16 [B, H] . E fp16 [V, H]^T.

@@ -1,7 +1,8 @@
 """The allocation-free greedy pick (scratch inside the library image) against the workspace-based entry point.
 
-This file is collected last on purpose: a run that stops at the first failure has then already run every other test.
-It must pass both alone in a fresh process and after the rest of the suite."""
+The file name sorts last on purpose, because the order of first use matters for a scratch array that lives in the
+library image: in a whole-suite run its first call comes after every other kernel of the library has run in the
+process, and run alone it is the first call in a fresh process.  Both orders must pass."""
 import ctypes
 
 import numpy as np
