@@ -633,7 +633,13 @@ size_t attn_decode_workspace(int B, int NH, int HD, int max_len) {
 int attn_decode_mma(const void*, const float*, const float*, const int64_t*, void*, void*, void*, int, int, int, int, float,
                     cudaStream_t, void* xq = nullptr, void* xd = nullptr);
 bool attn_cached_fits(int NH, int NKV, int HD, int max_len);
-int attn_cached(const void*, const int64_t*, const void*, const void*, void*, int, int, int, float, cudaStream_t);
+int attn_cached(const void*, const int64_t*, const void*, const void*, void*, int, int, int, float, cudaStream_t, int B = 1,
+                const float* cosT = nullptr, const float* sinT = nullptr);
+
+// which kernel serves several sequences: 0 = the shared-memory-resident cached form where the context fits it (default),
+// 1 = always the streaming tensor-core kernel of attn_decode_mma.cu
+static int g_batched_kernel = 0;
+void attn_batched_kernel(int which) { g_batched_kernel = which; }
 
 // pre != 0 (one sequence, max_len <= 4096 only): q arrives rotated and position pos is already in the cache (the fused
 // epilogue of the QKV projection did both); cosT / sinT / ws may then be null.
@@ -663,8 +669,11 @@ int attn_decode(const void* qkv, const float* cosT, const float* sinT, const int
   if (ws_bytes < attn_decode_workspace(B, NH, HD, max_len)) return fail(Q4B_E_WORKSPACE, "attn_decode: workspace too small");
   // Several sequences: the tensor-core kernel that reads K/V once per KV group (throughput); one sequence keeps the
   // latency-oriented kernels below.
-  if (B >= 2 && HD == 128 && aligned16(qkv))
+  if (B >= 2 && HD == 128 && aligned16(qkv)) {
+    if (g_batched_kernel == 0 && attn_cached_fits(NH, NKV, HD, max_len))
+      return attn_cached(qkv, pos, kc, vc, out, NH, NKV, max_len, scale, st, B, cosT, sinT);
     return attn_decode_mma(qkv, cosT, sinT, pos, kc, vc, out, B, NH, NKV, max_len, scale, st);
+  }
   if (max_len <= NCL * 128 * 4) {
     // cluster path: 8 chunks of 128 / 256 / 512 positions; a head group is served by 1..4 CTAs
     static const int hsub_for[9] = {1, 1, 2, 3, 2, 3, 2, 4, 4};

@@ -49,10 +49,49 @@ __device__ __forceinline__ void cp_async16(void* dst, const void* src, int bytes
                : "memory");
 }
 
-__global__ void __launch_bounds__(AT, 2) attn_cached_kernel(const __half* qkv, const int64_t* posp, const __half* kc, const __half* vc,
+// 8 fp16 values of a rotated head: `own` holds dimensions 8 cc .. 8 cc + 7, `other` the same offsets in the other half of
+// the head (d +- 64); cs / sn are the 64 cosines / sines of the position.  NeoX pairs (d, d + 64), rounded to fp16.
+__device__ __forceinline__ uint4 rotate8(uint4 own, uint4 other, int cc, const float* cs, const float* sn) {
+  const __half2* a2 = reinterpret_cast<const __half2*>(&own);
+  const __half2* b2 = reinterpret_cast<const __half2*>(&other);
+  uint4 r;
+  uint32_t* rw = reinterpret_cast<uint32_t*>(&r);
+  const int d0 = (cc & 7) * 8;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 a = __half22float2(a2[i]), b = __half22float2(b2[i]);
+    float lo0, hi0, lo1, hi1;
+    if (cc < 8) {                                    // own = first half (d), other = second half (d + 64)
+      rope_pair(a.x, b.x, cs[d0 + 2 * i], sn[d0 + 2 * i], lo0, hi0);
+      rope_pair(a.y, b.y, cs[d0 + 2 * i + 1], sn[d0 + 2 * i + 1], lo1, hi1);
+      rw[i] = pack_h2(lo0, lo1);
+    } else {
+      rope_pair(b.x, a.x, cs[d0 + 2 * i], sn[d0 + 2 * i], lo0, hi0);
+      rope_pair(b.y, a.y, cs[d0 + 2 * i + 1], sn[d0 + 2 * i + 1], lo1, hi1);
+      rw[i] = pack_h2(hi0, hi1);
+    }
+  }
+  return r;
+}
+
+// ROPE = false: q arrives rotated and the cache already holds the current position (batch-1 chain).
+// ROPE = true:  the whole of ATTN4 (lab/qwen_kernels.py:517-605) for gridDim.z sequences: q and the new k are rotated here
+//               from the biased fp16 QKV row, the CTA that owns the current position appends k / v to the cache (single
+//               writer) and uses them from shared memory; the rotation tables' row is fetched ahead of the wait.
+template <bool ROPE>
+__global__ void __launch_bounds__(AT, 2) attn_cached_kernel(const __half* qkv, const int64_t* posp, __half* kc, __half* vc,
                                                             __half* out, int NH, int NKV, int max_len, int cap, float scale_log2e,
-                                                            unsigned long long* trace) {
+                                                            unsigned long long* trace, const float* cosT, const float* sinT) {
   extern __shared__ __align__(16) uint8_t sm[];
+  __shared__ float s_cs[64], s_sn[64];
+  {
+    const size_t b = blockIdx.z;                     // sequence
+    qkv += b * (size_t)(NH + 2 * NKV) * HD;
+    posp += b;
+    kc += b * (size_t)NKV * max_len * HD;
+    vc += b * (size_t)NKV * max_len * HD;
+    out += b * (size_t)NH * HD;
+  }
   uint8_t* sQ = sm;                                  // [16][PITCH]   q heads of the group (rows >= GRP zero)
   uint8_t* sK = sQ + 16 * PITCH;                     // [cap][PITCH]
   uint8_t* sV = sK + (size_t)cap * PITCH;            // [cap][PITCH]
@@ -63,7 +102,7 @@ __global__ void __launch_bounds__(AT, 2) attn_cached_kernel(const __half* qkv, c
 
   const int t = threadIdx.x, warp = t >> 5, lane = t & 31, g = lane >> 2, tq = lane & 3;
   const int c = blockIdx.x, kvh = blockIdx.y;
-  unsigned long long* tr = (trace && t == 0) ? trace + (size_t)(blockIdx.y * gridDim.x + blockIdx.x) * 16 : nullptr;
+  unsigned long long* tr = (trace && t == 0) ? trace + (size_t)((blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * 16 : nullptr;
   int tri = 0;
   auto stamp = [&]() {
     if (tr && tri < 15) {
@@ -101,6 +140,13 @@ __global__ void __launch_bounds__(AT, 2) attn_cached_kernel(const __half* qkv, c
     cp_async16(sV + (size_t)r * PITCH + cc * 16, vbase + off, ld ? 16 : 0);
   }
   asm volatile("cp.async.commit_group;" ::: "memory");
+  if (ROPE) {
+    if (t < 64) {
+      s_cs[t] = cosT[(size_t)p * 64 + t];
+      s_sn[t] = sinT[(size_t)p * 64 + t];
+    }
+    __syncthreads();
+  }
   stamp();                                           // 1: cache rows requested
   pdl_wait();
   stamp();                                           // 2: predecessor complete
@@ -110,8 +156,27 @@ __global__ void __launch_bounds__(AT, 2) attn_cached_kernel(const __half* qkv, c
     uint4 qv = make_uint4(0u, 0u, 0u, 0u), pv = make_uint4(0u, 0u, 0u, 0u);
     {
       const int hl = t >> 4, cc = t & 15;
-      if (hl < GRP) qv = *reinterpret_cast<const uint4*>(qkv + (size_t)(kvh * GRP + hl) * HD + cc * 8);
-      if (mine) pv = *reinterpret_cast<const uint4*>((t < 16 ? kbase : vbase) + (size_t)p * HD + cc * 8);
+      if (!ROPE) {
+        if (hl < GRP) qv = *reinterpret_cast<const uint4*>(qkv + (size_t)(kvh * GRP + hl) * HD + cc * 8);
+        if (mine) pv = *reinterpret_cast<const uint4*>((t < 16 ? kbase : vbase) + (size_t)p * HD + cc * 8);
+      } else {
+        uint4 qo = make_uint4(0u, 0u, 0u, 0u), po = make_uint4(0u, 0u, 0u, 0u);
+        if (hl < GRP) {
+          const __half* qh = qkv + (size_t)(kvh * GRP + hl) * HD;
+          qv = *reinterpret_cast<const uint4*>(qh + cc * 8);
+          qo = *reinterpret_cast<const uint4*>(qh + (cc ^ 8) * 8);
+        }
+        if (mine) {
+          const __half* nh = qkv + (size_t)(t < 16 ? NH + kvh : NH + NKV + kvh) * HD;
+          pv = *reinterpret_cast<const uint4*>(nh + cc * 8);
+          if (t < 16) po = *reinterpret_cast<const uint4*>(nh + (cc ^ 8) * 8);
+        }
+        if (hl < GRP) qv = rotate8(qv, qo, cc, s_cs, s_sn);
+        if (mine) {
+          if (t < 16) pv = rotate8(pv, po, cc, s_cs, s_sn);
+          *reinterpret_cast<uint4*>((t < 16 ? kc : vc) + ((size_t)kvh * max_len + p) * HD + cc * 8) = pv;   // the append
+        }
+      }
       *reinterpret_cast<uint4*>(sQ + hl * PITCH + cc * 16) = qv;
     }
     asm volatile("cp.async.wait_group 0;" ::: "memory");      // this thread's copies have landed (zero-filled slot of row p too)
@@ -269,31 +334,35 @@ bool attn_cached_fits(int NH, int NKV, int HD, int max_len) {
   return HD == 128 && NKV > 0 && NH % NKV == 0 && NH / NKV <= MAXG && max_len > 0 && max_len <= MAX_CTX;
 }
 
+// B = 1 with cosT == nullptr: the cached form (q rotated, row appended by the caller).  cosT / sinT given: RoPE and the
+// append happen inside, for B sequences (qkv [B, (NH + 2 NKV) 128], pos [B], cache [B, NKV, max_len, 128], out [B, NH 128]).
 int attn_cached(const void* qkv, const int64_t* pos, const void* kc, const void* vc, void* out, int NH, int NKV, int max_len,
-                float scale, cudaStream_t st) {
+                float scale, cudaStream_t st, int B, const float* cosT, const float* sinT) {
   if (!attn_cached_fits(NH, NKV, HD, max_len)) return fail(Q4B_E_SHAPE, "attn_decode_cached: needs head_dim 128, NH/NKV <= 8, max_len <= 2048");
-  if (!qkv || !pos || !kc || !vc || !out || !aligned16(qkv) || !aligned16(kc) || !aligned16(vc))
+  if (B < 1 || B > 65535 || (B > 1 && !cosT)) return fail(Q4B_E_SHAPE, "attn_decode_cached: 1 <= B, several sequences need the rotation tables");
+  if (!qkv || !pos || !kc || !vc || !out || !aligned16(qkv) || !aligned16(kc) || !aligned16(vc) || (cosT && !sinT))
     return fail(Q4B_E_ALIGN, "attn_decode_cached: null or misaligned pointer");
   int cap = ((max_len + NCL - 1) / NCL + 15) & ~15;  // positions per CTA at the longest context
   if (cap < 128) cap = 128;                          // the K tile's space later holds the per-warp partials (32 KB)
   const size_t smem = (size_t)(16 + 2 * cap) * PITCH;
-  static size_t configured[64] = {};
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return fail(Q4B_E_CUDA, "attn_decode_cached: no current device");
-  prefer_max_shared(reinterpret_cast<const void*>(&attn_cached_kernel));
-  if (smem > configured[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(attn_cached_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) {
-      set_cuda_error(e, "attn_decode_cached");
-      return Q4B_E_CUDA;
-    }
-    configured[dev] = smem;
+  const void* kern = cosT ? reinterpret_cast<const void*>(&attn_cached_kernel<true>) : reinterpret_cast<const void*>(&attn_cached_kernel<false>);
+  if (!cosT) prefer_max_shared(kern);                // the batch-1 chain shares one carve-out (see q4b_internal.h)
+  if (cudaError_t e = ensure_dynamic_smem(kern, smem); e != cudaSuccess) {
+    set_cuda_error(e, "attn_decode_cached");
+    return Q4B_E_CUDA;
   }
-  unsigned long long* trace = trace_slot(2, NCL * NKV);
+  unsigned long long* trace = trace_slot(2, NCL * NKV * B);
   const float scale_log2e = scale * 1.4426950408889634f;
-  return check_launch(launch_pdl_cluster(attn_cached_kernel, dim3(NCL, NKV), dim3(AT), smem, st, NCL, 1, (const __half*)qkv, pos,
-                                         (const __half*)kc, (const __half*)vc, (__half*)out, NH, NKV, max_len, cap, scale_log2e, trace),
-                      "attn_decode_cached");
+  __half* kcw = reinterpret_cast<__half*>(const_cast<void*>(kc));
+  __half* vcw = reinterpret_cast<__half*>(const_cast<void*>(vc));
+  cudaError_t e;
+  if (cosT)
+    e = launch_pdl_cluster(attn_cached_kernel<true>, dim3(NCL, NKV, B), dim3(AT), smem, st, NCL, 1, (const __half*)qkv, pos, kcw, vcw,
+                           (__half*)out, NH, NKV, max_len, cap, scale_log2e, trace, cosT, sinT);
+  else
+    e = launch_pdl_cluster(attn_cached_kernel<false>, dim3(NCL, NKV, B), dim3(AT), smem, st, NCL, 1, (const __half*)qkv, pos, kcw, vcw,
+                           (__half*)out, NH, NKV, max_len, cap, scale_log2e, trace, cosT, sinT);
+  return check_launch(e, "attn_decode_cached");
 }
 
 }  // namespace q4b

@@ -67,6 +67,7 @@ int gemv_mma(const void*, const void*, const void*, void*, const void*, int, int
              const int64_t* pos = nullptr, void* kc = nullptr, void* vc = nullptr, int NH = 0, int NKV = 0, int HD = 0,
              int max_len = 0, int withhold_chunk = -1, const GemvLookahead* look = nullptr);
 int gemv_mma_ksplit(int, int);
+void attn_batched_kernel(int);
 int tp_allreduce(const void* const*, void* const*, int, int, uint32_t, const uint32_t*, float*, int, int, const float*, float, void*,
                  void*, uint32_t*, uint32_t, cudaStream_t);
 int tp_epoch_advance(uint32_t*, uint32_t, cudaStream_t);
@@ -232,6 +233,12 @@ int q4b_tp_epoch_advance(uint32_t* epoch_base, uint32_t by, q4b_stream_t stream)
 int q4b_debug_tp_allreduce_expired_wait(const void* const* parts, void* const* flags, int rank, int world, uint32_t epoch,
                                         float* h, int rows, int H, uint32_t* status, q4b_stream_t stream) {
   return tp_allreduce(parts, flags, rank, world, epoch, nullptr, h, rows, H, nullptr, 0.f, nullptr, nullptr, status, 4096u, S(stream));
+}
+
+int q4b_attn_batched_kernel(int which) {
+  if (which != 0 && which != 1) return fail(Q4B_E_ARG, "attn_batched_kernel: 0 (cached form where it fits) or 1 (streaming kernel)");
+  attn_batched_kernel(which);
+  return Q4B_OK;
 }
 
 int q4b_debug_gemv_mma_expired_wait(const void* W, const void* Sc, const void* X, void* Y, int N, int K, uint32_t* status,

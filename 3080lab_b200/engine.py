@@ -310,6 +310,9 @@ class Batched:
         self.attn_ws = K.attn_workspace(B, c.n_heads, c.head_dim, m.max_len, dv)
         self.head_ws = K.head_workspace(c.vocab, B, dv)
         self.status = QB.Status(dv)
+        # contexts up to 2048: attention through the shared-memory-resident kernel (K / V requested ahead of the dependency
+        # wait) + the quantiser, instead of the streaming kernel with the quantiser fused in
+        self.attn_cached = c.head_dim == 128 and c.n_heads // c.n_kv_heads <= 8 and m.max_len <= 2048
         self.launches_per_step = 1 + (9 if linears == "q8" else 7) * c.layers + 3
 
     def gemm8(self, pair, N, Kdim, Y, aux, epi, ldy, xq=None, xd=None):
@@ -350,8 +353,8 @@ class Batched:
         for i, L in enumerate(m.L):
             QB.rmsnorm_q8(self.h, L["ln1"], self.xq, self.xd, c.eps)
             self.gemm8(L["qkv"], c.qkv_rows, H, self.qkv, L["qkv_b"], "biasf", c.qkv_rows)
-            if not K.attn_q8(self.qkv, m.cos, m.sin, self.pos, self.kc[i], self.vc[i], self.att, self.xq, self.xd, c.n_heads,
-                             c.n_kv_heads, c.head_dim, m.max_len, m.scale):
+            if self.attn_cached or not K.attn_q8(self.qkv, m.cos, m.sin, self.pos, self.kc[i], self.vc[i], self.att, self.xq,
+                                                  self.xd, c.n_heads, c.n_kv_heads, c.head_dim, m.max_len, m.scale):
                 K.attn(self.qkv, m.cos, m.sin, self.pos, self.kc[i], self.vc[i], self.att, c.n_heads, c.n_kv_heads,
                        c.head_dim, m.max_len, m.scale, self.attn_ws)
                 QB.quant_q8(self.att, self.xq, self.xd)

@@ -187,6 +187,11 @@ int q4b_gemv_q4_0_mma(const void* Wt, const void* St, const void* X, void* Y, co
 int q4b_rmsnorm_gemv_q4_0_mma(const void* Wt, const void* St, const float* h, const float* norm_w, float eps, void* Y,
                               const void* AUX, int N, int K, int epilogue, uint32_t* status, q4b_stream_t stream);
 
+/* Which kernel q4b_attn_decode uses for B >= 2 sequences (head_dim 128): 0 (default) = the shared-memory-resident form
+ * (whole chunk of K / V requested ahead of the dependency wait, RoPE and append inside) where max_len <= 2048, else the
+ * streaming tensor-core kernel; 1 = always the streaming kernel.  Process-wide; meant for A/B measurements. */
+int q4b_attn_batched_kernel(int which);
+
 /* The QKV projection of one decode token with everything up to the cache write fused in: RMSNorm(h) -> Q4_0 GEMV ->
  * + bias, round to fp16 -> NeoX rotation of the q and k heads at position pos[0] from the ROUNDED values, rounded
  * again -> rotated k and raw v stored into the cache row pos[0].  This is the `biasf_kv` epilogue of the reference's

@@ -209,23 +209,33 @@ def _attn_case(K, B, NH, NKV, HD, max_len, positions, seed):
     return got
 
 
+@pytest.fixture(params=["cached", "streaming"])
+def batched_kernel(request):
+    """Both kernels that serve several sequences: the shared-memory-resident form (default where max_len <= 2048) and the
+    streaming tensor-core kernel."""
+    ffi = pkg("_ffi")
+    ffi.call("q4b_attn_batched_kernel", 1 if request.param == "streaming" else 0)
+    yield request.param
+    ffi.call("q4b_attn_batched_kernel", 0)
+
+
 @pytest.mark.parametrize("pos", [0, 1, 127, 128, 129, 511, 767, 1023])
 def test_attn_decode_qwen_shape(K, pos):
     _attn_case(K, 1, 12, 2, 128, 1024, [pos], pos)
 
 
 @pytest.mark.parametrize("NH,NKV,HD", [(4, 2, 64), (7, 1, 128), (14, 2, 128), (8, 8, 64), (8, 1, 128), (6, 2, 64)])
-def test_attn_decode_head_groups(K, NH, NKV, HD):
+def test_attn_decode_head_groups(K, NH, NKV, HD, batched_kernel):
     _attn_case(K, 3, NH, NKV, HD, 300, [0, 130, 299], NH * HD)
 
 
-def test_attn_decode_repeatable(K):
+def test_attn_decode_repeatable(K, batched_kernel):
     a = _attn_case(K, 2, 12, 2, 128, 2048, [2047, 1000], 11)
     b = _attn_case(K, 2, 12, 2, 128, 2048, [2047, 1000], 11)
     assert np.array_equal(a, b)
 
 
-def test_attn_decode_batched_ragged_positions(K):
+def test_attn_decode_batched_ragged_positions(K, batched_kernel):
     """32 sequences at different positions (tile and chunk boundaries of the tensor-core kernel: 64-position tiles,
     chunks of max_len / 8 rounded to tiles), Qwen2.5-1.5B head shape."""
     positions = [0, 1, 62, 63, 64, 65, 127, 128, 159, 160, 161, 191, 192, 319, 320, 321, 479, 480, 639, 640, 641, 799, 800, 959,
@@ -267,7 +277,9 @@ def test_attn_decode_fused_q8_equals_attention_then_quantiser(K, B, NH, NKV, pos
                 return
             assert ok
         else:
+            pkg("_ffi").call("q4b_attn_batched_kernel", 1)          # the fused quantiser lives in the streaming kernel
             K.attn(qkv, dev(cos), dev(sin), pos, kcd, vcd, out, NH, NKV, HD, max_len, scale, K.attn_workspace(B, NH, HD, max_len, "cuda"))
+            pkg("_ffi").call("q4b_attn_batched_kernel", 0)
             QB.quant_q8(out, xq, xd)
         torch.cuda.synchronize()
         outs.append((out.clone(), xq.clone(), xd.clone(), kcd, vcd))

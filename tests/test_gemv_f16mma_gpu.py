@@ -183,21 +183,23 @@ def test_batched_f16_decode_matches_oracle(B):
 
 
 def test_batched_f16_and_q8_agree_statistically():
-    """The two batched-decode modes on the same weights and prompts: logits close (int8 activations against fp16-rounded
-    weights: a few 1e-3 each from the exact product), greedy tokens mostly the same."""
+    """The two batched-decode modes on the same weights and prompts, each with its own cache: one rounds the weights to
+    fp16, the other the activations to int8, so single logits may sit far apart (a flipped int8 value stays in that
+    arm's cache), but the typical distance is a few 1e-3 and the greedy tokens mostly agree."""
     synth, engine = pkg("synth"), pkg("engine")
     cfg = synth.ModelConfig("small-ab", 2, 512, 1536, 4, 2, 128, 4096)
     m = engine.FusedQwen(synth.synth_model(cfg, 12), max_len=64)
     a, b = engine.Batched(m, 8, linears="f16"), engine.Batched(m, 8, linears="q8")
     prompts = np.stack([synth.synth_prompt(cfg, 16, 7 + i) for i in range(8)])
-    same = 0
+    same, errs = 0, []
     for j in range(16):
         for bm in (a, b):
             bm.tok.copy_(dev(prompts[:, j]))
             bm.step()
         la, lb = a.logits.cpu().numpy(), b.logits.cpu().numpy()
-        assert nerr(la, lb) < 0.15
+        errs.extend(np.max(np.abs(la - lb), axis=1) / np.max(np.abs(lb), axis=1))
         same += int((a.tok == b.tok).sum().item())
+    assert np.median(errs) < 2e-2, np.median(errs)
     assert same >= 0.8 * 16 * 8
     a.status.check()
     b.status.check()
