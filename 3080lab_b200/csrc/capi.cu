@@ -72,6 +72,7 @@ int tp_allreduce(const void* const*, void* const*, int, int, uint32_t, const uin
                  void*, uint32_t*, uint32_t, cudaStream_t);
 int tp_epoch_advance(uint32_t*, uint32_t, cudaStream_t);
 int gemv_f16mma(const void*, const void*, const void*, void*, const void*, int, int, int, int, int, uint32_t*, cudaStream_t);
+int gemv_q8mma(const void*, const void*, const void*, const void*, void*, const void*, int, int, int, int, int, uint32_t*, cudaStream_t);
 double peak_i8_launch(int, uint32_t*, cudaStream_t);
 int head_q6_k_argmax(const void*, const void*, const void*, const void*, const void*, float*, int, int, int64_t*, int64_t*, void*, size_t,
                      cudaStream_t);
@@ -239,6 +240,11 @@ int q4b_attn_batched_kernel(int which) {
   if (which != 0 && which != 1) return fail(Q4B_E_ARG, "attn_batched_kernel: 0 (cached form where it fits) or 1 (streaming kernel)");
   attn_batched_kernel(which);
   return Q4B_OK;
+}
+
+int q4b_mmq_q4_0_q8_1_mma(const void* W, const void* Sc, const void* xq, const void* xd, void* Y, const void* AUX, int N, int K,
+                          int P, int epilogue, int ldy, uint32_t* status, q4b_stream_t stream) {
+  return gemv_q8mma(W, Sc, xq, xd, Y, AUX, N, K, P, epilogue, ldy, status, S(stream));
 }
 
 int q4b_debug_gemv_mma_expired_wait(const void* W, const void* Sc, const void* X, void* Y, int N, int K, uint32_t* status,

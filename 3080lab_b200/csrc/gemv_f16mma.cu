@@ -16,9 +16,11 @@
 //     and keeps that natural byte order: logical k slots of the MMA are a permutation of the block's 32 weights, and the
 //     activation fragment is permuted to match with two byte-permutes, so no repacked weight copy is needed;
 //   * the k groups are added in a fixed order through shared memory, K slices through the thread-block cluster
-//     (every CTA pulls the partial sums of its share of the rows from its peers in rank order): bit-repeatable.
+//     (every CTA pushes the partial sums of the rows it does not finish to their owner, one cluster barrier, the owner
+//     adds in rank order): bit-repeatable.
 // Every wait is bounded (status word + fall through).
 #include <algorithm>
+#include <cstdio>
 #include <map>
 #include <mutex>
 #include <tuple>
@@ -40,7 +42,9 @@ constexpr size_t MAX_DYN_SMEM = 226 * 1024;
 struct F16Args {
   const uint8_t* W;      // tile-packed nibbles [T, K/32, 128, 16 bytes]
   const __half* S;       // tile-packed scales [T, K/32, 128]
-  const __half* X;       // [B, K]
+  const __half* X;       // fp16 [B, K]                      (MODE_F16)
+  const int8_t* XQ;      // Q8_1 values int8 [B, K]           (MODE_Q8)
+  const __half* XD;      // Q8_1 block scales fp16 [B, K/32]  (MODE_Q8)
   void* Y;               // [B, ldy]
   const void* AUX;
   uint32_t* status;
@@ -60,6 +64,16 @@ __device__ __forceinline__ void mma_f16(float (&c)[4], uint32_t a0, uint32_t a1,
       "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
       : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// int8 MMA whose accumulator starts from the constant 0x4B400000 in every lane: read as a float the result is
+// 2^23 + 2^22 + dot, so one subtraction gives float(dot) exactly (|dot| < 2^22); the reference plants the same constant in
+// the C operand of its int8 MMQ (lab/qwen_batched.py:1237-1243).
+__device__ __forceinline__ void mma_s8_magic(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%10, %10, %10, %10};"
+      : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0x4B400000));
 }
 
 __device__ __forceinline__ uint32_t h2_as_u32(__half2 v) { return *reinterpret_cast<uint32_t*>(&v); }
@@ -84,20 +98,21 @@ __device__ __forceinline__ bool mbar_wait_n(uint64_t* bar, uint32_t parity, uint
   return false;
 }
 
-// 8-byte read of a peer CTA's shared memory at the address `local` has in this CTA
-__device__ __forceinline__ float2 ld_peer_f32x2(const float* local, uint32_t rank) {
-  uint32_t addr;
-  float2 v;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(addr) : "r"(tc::smem_u32(local)), "r"(rank));
-  asm volatile("ld.shared::cluster.v2.f32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(addr) : "memory");
-  return v;
-}
-
 // bytes per staged activation row: an odd multiple of 64, so that the 16-byte fragment reads of a quarter warp (two
 // rows x 64 bytes) fall into distinct banks
 __host__ __device__ __forceinline__ size_t x_pitch(int cap) { return (size_t)(cap | 1) * 64; }
 
-template <int NT>
+// bytes per staged row of int8 activations (MODE_Q8): 32 mod 128, so that the 8-byte fragment reads of a half warp (four
+// rows x 32 bytes) fall into distinct banks
+__host__ __device__ __forceinline__ size_t xq_pitch(int cap) { return ((size_t)cap * 32 + 127) / 128 * 128 + 32; }
+
+constexpr int MODE_F16 = 0, MODE_Q8 = 1;
+
+// MODE_F16: fp16 activations, weights dequantised to fp16 (the reference's batched-decode GEMV).
+// MODE_Q8:  Q8_1 activations (int8 values + fp16 block scales), exact int32 block dots by mma.sync.m16n8k32.s8 with register
+//           accumulators, rescaled per block in fp32: acc += (d_w / 16 * d_x) * float(dot), the block arithmetic of the
+//           reference's MMQ (lab/qwen_batched.py:1237-1243) for up to 32 activation rows.
+template <int NT, int MODE>
 __global__ void __launch_bounds__(GT, NT <= 2 ? 2 : 1) gemv_f16mma_kernel(const F16Args a) {
   extern __shared__ __align__(128) uint8_t smem[];
   __shared__ __align__(8) uint64_t bar_load[MAX_CHUNKS];
@@ -108,14 +123,16 @@ __global__ void __launch_bounds__(GT, NT <= 2 ? 2 : 1) gemv_f16mma_kernel(const 
   const int g = lane >> 2, tq = lane & 3;
   const int tile = blockIdx.x, ks = blockIdx.y;
   pdl_launch_dependents();
+  if (a.ksplit > 1) asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");   // "this CTA exists"
   const int kb0 = (int)(((long long)a.KB * ks) / a.ksplit), kb1 = (int)(((long long)a.KB * (ks + 1)) / a.ksplit);
   const int nkb = kb1 - kb0;
   const int cap = a.cap;                                  // k-blocks per window of the slab (nkb <= cap except for very long K)
-  const size_t xp = x_pitch(cap);
+  const size_t xp = MODE == MODE_F16 ? x_pitch(cap) : xq_pitch(cap);
   uint8_t* slabW = smem;                                  // [k-block][128 rows][16 bytes]
   uint8_t* slabS = slabW + (size_t)cap * 2048;            // [k-block][128 rows] fp16
-  uint8_t* xs = slabS + (size_t)cap * 256;                // [8 NT rows][pitch] fp16: the K window of X
-  float* P = reinterpret_cast<float*>(xs + (size_t)NT * 8 * xp);   // [8 NT columns][PSTR]: this CTA's partial sums
+  uint8_t* xs = slabS + (size_t)cap * 256;                // [8 NT rows][pitch]: the K window of X (fp16, or int8 permuted)
+  float* dxs = reinterpret_cast<float*>(xs + (size_t)NT * 8 * xp);   // MODE_Q8: [k-block][8 NT] block scales / 16 as fp32
+  float* P = dxs + (MODE == MODE_Q8 ? (size_t)cap * NT * 8 : 0);   // [8 NT columns][PSTR]: this CTA's partial sums
 
   // window `win` covers k-blocks kb0 + win cap .. of this CTA's slice; lane c of warp 0 owns weight chunk c
   auto issue_weights = [&](int win) {
@@ -148,9 +165,29 @@ __global__ void __launch_bounds__(GT, NT <= 2 ? 2 : 1) gemv_f16mma_kernel(const 
   // activation rows B .. 8 NT - 1 do not exist: their MMA columns read zeros
   for (int i = t; i < (NT * 8 - a.B) * (int)(xp / 16); i += GT)
     reinterpret_cast<uint4*>(xs + (size_t)a.B * xp)[i] = make_uint4(0u, 0u, 0u, 0u);
+  if (MODE == MODE_Q8)
+    for (int i = t; i < cap * NT * 8; i += GT) dxs[i] = 0.f;
   __syncthreads();
   pdl_wait();                                             // X comes from the previous kernel
-  if (warp == 1) issue_x(0);
+  if (MODE == MODE_F16 && warp == 1) issue_x(0);
+  // MODE_Q8: int8 values by plain 8-byte loads, the bytes of each group of eight reordered to (k0, k2, k4, k6 | k1, k3, k5, k7)
+  // to match the nibble expansion of the weights; block scales converted to fp32 with the factor 1/16 of the expansion
+  auto stage_q8 = [&](int win) {
+    const int wkb = min(cap, nkb - win * cap);
+    const size_t kbase = (size_t)kb0 + (size_t)win * cap;
+    for (int i = t; i < a.B * wkb * 4; i += GT) {
+      const int col = i / (wkb * 4), r = i - col * (wkb * 4);
+      const uint2 v = *reinterpret_cast<const uint2*>(a.XQ + (size_t)col * a.K + kbase * 32 + (size_t)r * 8);
+      uint2 o;
+      tc::permute_bytes(v.x, v.y, o.x, o.y);
+      *reinterpret_cast<uint2*>(xs + (size_t)col * xp + (size_t)r * 8) = o;
+    }
+    for (int i = t; i < a.B * wkb; i += GT) {
+      const int col = i / wkb, kb = i - col * wkb;
+      dxs[kb * NT * 8 + col] = __half2float(a.XD[(size_t)col * a.KB + kbase + kb]) * 0.0625f;
+    }
+  };
+  if (MODE == MODE_Q8) stage_q8(0);
 
   // ---- main loop: rows rg * 32 + {g, g + 8, g + 16, g + 24}, k-blocks kg, kg + 4, ... of each window
   // A lane holds word tq of each row's 16 bytes (nibble i = weight 8 tq + i).  Logical k slot -> weight of the block:
@@ -174,16 +211,54 @@ __global__ void __launch_bounds__(GT, NT <= 2 ? 2 : 1) gemv_f16mma_kernel(const 
       // reads before the bulk copies that overwrite the slab
       tc::fence_async_smem();
       if (t < MAX_CHUNKS) issue_weights(win);
-      if (warp == 1) issue_x(win);
+      if (MODE == MODE_F16 && warp == 1) issue_x(win);
+      if (MODE == MODE_Q8) stage_q8(win);
     }
     // warp w polls weight chunk w, the last warp the activations; the block barrier publishes the bulk-copied bytes to
     // everyone.  (Polling each chunk inside the loop instead, to start the MMAs while later chunks are in flight, was
     // measured slower: gate/up at 8 rows 7.9 us against 7.0.)
     if (lane == 0) {
       for (int ch = warp; ch * CHK < wkb; ch += GT / 32) ok = mbar_wait_n(&bar_load[ch], parity, a.wait_limit) && ok;
-      if (warp == GT / 32 - 1) ok = mbar_wait_n(&bar_x, parity, a.wait_limit) && ok;
+      if (MODE == MODE_F16 && warp == GT / 32 - 1) ok = mbar_wait_n(&bar_x, parity, a.wait_limit) && ok;
     }
     __syncthreads();
+    if (MODE == MODE_Q8) {
+      // A fragment of an m16 tile: a0 / a2 = even / odd weights of row g's word tq, a1 / a3 the same of row g + 8; the
+      // activation bytes were staged in the matching order, so lane tq reads its 8 bytes of column g in one load.
+      const uint8_t* xq0 = xs + (size_t)g * xp + tq * 8;
+#pragma unroll 1
+      for (int kb = kg; kb < wkb; kb += 4) {
+        uint32_t w[4];
+        float dw[4];
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+          w[r] = *reinterpret_cast<const uint32_t*>(wp0 + (size_t)kb * 2048 + r * 8 * 16);
+          dw[r] = __half2float(sp0[kb * 128 + r * 8]);
+        }
+        uint2 xb[NT];
+        float2 dx[NT];
+#pragma unroll
+        for (int n = 0; n < NT; ++n) {
+          xb[n] = *reinterpret_cast<const uint2*>(xq0 + (size_t)n * 8 * xp + (size_t)kb * 32);
+          dx[n] = *reinterpret_cast<const float2*>(dxs + kb * NT * 8 + n * 8 + 2 * tq);
+        }
+#pragma unroll
+        for (int m = 0; m < 2; ++m) {
+          uint32_t eA, oA, eB, oB;
+          tc::expand_nibbles(w[2 * m], eA, oA);
+          tc::expand_nibbles(w[2 * m + 1], eB, oB);
+#pragma unroll
+          for (int n = 0; n < NT; ++n) {
+            int d[4];
+            mma_s8_magic(d, eA, eB, oA, oB, xb[n].x, xb[n].y);
+            c[m][n][0] = fmaf(dw[2 * m] * dx[n].x, __int_as_float(d[0]) - 12582912.f, c[m][n][0]);
+            c[m][n][1] = fmaf(dw[2 * m] * dx[n].y, __int_as_float(d[1]) - 12582912.f, c[m][n][1]);
+            c[m][n][2] = fmaf(dw[2 * m + 1] * dx[n].x, __int_as_float(d[2]) - 12582912.f, c[m][n][2]);
+            c[m][n][3] = fmaf(dw[2 * m + 1] * dx[n].y, __int_as_float(d[3]) - 12582912.f, c[m][n][3]);
+          }
+        }
+      }
+    } else
 #pragma unroll 1
     for (int kb = kg; kb < wkb; kb += 4) {
       uint32_t w[4];
@@ -223,46 +298,90 @@ __global__ void __launch_bounds__(GT, NT <= 2 ? 2 : 1) gemv_f16mma_kernel(const 
     __syncthreads();
   }
 
-  // ---- k groups added in order 0, 1, 2, 3 into P[column][row]
-#pragma unroll 1
-  for (int s = 0; s < 4; ++s) {
-    if (kg == s) {
+  // ---- k groups: with up to 8 columns every k group writes its own tile and the sums are formed on reading (one block
+  // barrier); with more columns the groups add into one tile in turn (four barriers, a quarter of the shared memory).
+  // Either way the order is k group 0, 1, 2, 3.
+  constexpr int NPB = NT == 1 ? 4 : 1;
+  constexpr size_t PB = (size_t)NT * 8 * PSTR;            // floats per partial tile
+  if (NPB == 4) {
 #pragma unroll
-      for (int m = 0; m < 2; ++m)
+    for (int m = 0; m < 2; ++m)
 #pragma unroll
-        for (int n = 0; n < NT; ++n) {
-          float* p0 = P + (size_t)(n * 8 + 2 * tq) * PSTR + rg * 32 + 16 * m + g;
-          if (s == 0) {
-            p0[0] = c[m][n][0]; p0[PSTR] = c[m][n][1]; p0[8] = c[m][n][2]; p0[PSTR + 8] = c[m][n][3];
-          } else {
-            p0[0] += c[m][n][0]; p0[PSTR] += c[m][n][1]; p0[8] += c[m][n][2]; p0[PSTR + 8] += c[m][n][3];
-          }
-        }
-    }
+      for (int n = 0; n < NT; ++n) {
+        float* p0 = P + kg * PB + (size_t)(n * 8 + 2 * tq) * PSTR + rg * 32 + 16 * m + g;
+        p0[0] = c[m][n][0]; p0[PSTR] = c[m][n][1]; p0[8] = c[m][n][2]; p0[PSTR + 8] = c[m][n][3];
+      }
     __syncthreads();
+  } else {
+#pragma unroll 1
+    for (int s = 0; s < 4; ++s) {
+      if (kg == s) {
+#pragma unroll
+        for (int m = 0; m < 2; ++m)
+#pragma unroll
+          for (int n = 0; n < NT; ++n) {
+            float* p0 = P + (size_t)(n * 8 + 2 * tq) * PSTR + rg * 32 + 16 * m + g;
+            if (s == 0) {
+              p0[0] = c[m][n][0]; p0[PSTR] = c[m][n][1]; p0[8] = c[m][n][2]; p0[PSTR + 8] = c[m][n][3];
+            } else {
+              p0[0] += c[m][n][0]; p0[PSTR] += c[m][n][1]; p0[8] += c[m][n][2]; p0[PSTR + 8] += c[m][n][3];
+            }
+          }
+      }
+      __syncthreads();
+    }
   }
+  auto partial2 = [&](int col, int pr) {                  // this CTA's sums of rows 2 pr, 2 pr + 1 of column col
+    const float* src = P + (size_t)col * PSTR + 2 * pr;
+    float2 v = *reinterpret_cast<const float2*>(src);
+    if (NPB == 4) {
+#pragma unroll
+      for (int q = 1; q < 4; ++q) {
+        const float2 u = *reinterpret_cast<const float2*>(src + q * PB);
+        v.x += u.x;
+        v.y += u.y;
+      }
+    }
+    return v;
+  };
 
-  // ---- K slices: CTA `ks` of the cluster finishes row pairs [64 ks / ksplit, 64 (ks + 1) / ksplit) of the tile
+  // ---- K slices: CTA r of the cluster finishes row pairs [64 r / ksplit, 64 (r + 1) / ksplit) of the tile.  Every CTA
+  // PUSHES the pairs it does not own into their owner's receive buffer (remote stores, nothing to wait for), one cluster
+  // barrier publishes them, and the owner adds the ksplit contributions in rank order.
   int pr0 = 0, pr1 = ROWS / 2;
+  const int maxp = (ROWS / 2 + a.ksplit - 1) / a.ksplit;  // pairs per slice, at most
+  float* recv = P + NPB * PB;                             // [rank][column][maxp] float2
   if (a.ksplit > 1) {
-    cluster_sync_all();                                                     // every peer's P is complete and visible
     pr0 = (ROWS / 2 * ks) / a.ksplit;
     pr1 = (ROWS / 2 * (ks + 1)) / a.ksplit;
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");    // pairs with the arrive at the top: every peer runs
+    for (int i = t; i < (ROWS / 2) * a.B; i += GT) {
+      const int col = i >> 6, pr = i & 63;
+      int r = (pr * a.ksplit) >> 6;
+      if (((ROWS / 2) * (r + 1)) / a.ksplit <= pr) ++r;
+      const float2 v = partial2(col, pr);
+      const int local = pr - ((ROWS / 2) * r) / a.ksplit;
+      const float* slot = recv + (((size_t)ks * NT * 8 + col) * maxp + local) * 2;
+      uint32_t addr;
+      asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(addr) : "r"(tc::smem_u32(slot)), "r"(r));
+      asm volatile("st.shared::cluster.v2.f32 [%0], {%1, %2};" ::"r"(addr), "f"(v.x), "f"(v.y) : "memory");
+    }
+    cluster_sync_all();
   }
   const int npr = pr1 - pr0;
   for (int i = t; i < npr * a.B; i += GT) {
-    const int col = i / npr, pr = pr0 + (i - col * npr);
-    const float* src = P + (size_t)col * PSTR + 2 * pr;
+    const int col = i / npr, pl = i - col * npr, pr = pr0 + pl;
     float v0 = 0.f, v1 = 0.f;
     if (a.ksplit > 1) {
-      for (int r = 0; r < a.ksplit; ++r) {                                  // rank order, whoever does the adding
-        const float2 pv = ld_peer_f32x2(src, (uint32_t)r);
+      for (int r = 0; r < a.ksplit; ++r) {                                  // rank order
+        const float2 pv = *reinterpret_cast<const float2*>(recv + (((size_t)r * NT * 8 + col) * maxp + pl) * 2);
         v0 += pv.x;
         v1 += pv.y;
       }
     } else {
-      v0 = src[0];
-      v1 = src[1];
+      const float2 pv = partial2(col, pr);
+      v0 = pv.x;
+      v1 = pv.y;
     }
     const int row = tile * ROWS + 2 * pr;
     if (row >= a.N) continue;
@@ -301,32 +420,19 @@ __global__ void __launch_bounds__(GT, NT <= 2 ? 2 : 1) gemv_f16mma_kernel(const 
     }
   }
   if (!ok) atomicOr(a.status, 1u);
-  if (a.ksplit > 1) cluster_sync_all();                   // nobody leaves while a peer may still read its partial sums
 }
 
-size_t smem_for(int cap, int nt) {
-  return (size_t)cap * (2048 + 256) + (size_t)nt * 8 * x_pitch(cap) + (size_t)nt * 8 * PSTR * sizeof(float);
-}
-
-template <int NT>
-int prepare(size_t smem) {
-  static size_t configured[64] = {};
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return fail(Q4B_E_CUDA, "gemv_q4_0_f16mma: no current device");
-  if (smem > configured[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(gemv_f16mma_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_DYN_SMEM);
-    if (e != cudaSuccess) {
-      set_cuda_error(e, "gemv_q4_0_f16mma");
-      return Q4B_E_CUDA;
-    }
-    configured[dev] = MAX_DYN_SMEM;
-  }
-  return Q4B_OK;
+size_t smem_for(int cap, int nt, int mode, int ks) {
+  const size_t x = mode == MODE_F16 ? (size_t)nt * 8 * x_pitch(cap) : (size_t)nt * 8 * xq_pitch(cap) + (size_t)cap * nt * 8 * sizeof(float);
+  // partial tiles (four with up to 8 columns, else one) + with K slices the receive buffer of their reduction (< 64 + 8 pairs)
+  size_t red = (size_t)(nt == 1 ? 4 : 1) * nt * 8 * PSTR * sizeof(float);
+  if (ks > 1) red += (size_t)nt * 8 * (ROWS / 2 + 8) * 2 * sizeof(float);
+  return (size_t)cap * (2048 + 256) + x + red;
 }
 
 // How many clusters of `ks` CTAs with `smem` bytes each can be resident at once (cached per device and configuration):
 // a grid of T clusters that does not fit runs in two waves, which a smaller split avoids.
-template <int NT>
+template <int NT, int MODE>
 int resident_clusters(int ks, size_t smem) {
   static std::mutex mu;
   static std::map<std::tuple<int, int, size_t>, int> cache;
@@ -348,7 +454,7 @@ int resident_clusters(int ks, size_t smem) {
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   int n = 0;
-  if (cudaOccupancyMaxActiveClusters(&n, gemv_f16mma_kernel<NT>, &cfg) != cudaSuccess) {
+  if (cudaOccupancyMaxActiveClusters(&n, gemv_f16mma_kernel<NT, MODE>, &cfg) != cudaSuccess) {
     cudaGetLastError();
     n = 1 << 30;                                          // unknown: do not constrain the split
   }
@@ -356,40 +462,64 @@ int resident_clusters(int ks, size_t smem) {
   return n;
 }
 
-template <int NT>
-int launch(F16Args& a, int T, cudaStream_t st) {
+template <int NT, int MODE>
+int launch(F16Args& a, int T, cudaStream_t st, const char* where) {
   // K slices: fill the SMs when there are fewer row tiles than SMs; the slab holds `cap` k-blocks of one slice (longer
   // slices run as several windows); prefer a split whose clusters are all resident at once
-  int cap_max = CHK * MAX_CHUNKS;
-  while (cap_max > 1 && smem_for(cap_max, NT) > MAX_DYN_SMEM) --cap_max;
-  int rc = prepare<NT>(MAX_DYN_SMEM);
-  if (rc != Q4B_OK) return rc;
+  auto cap_for = [&](int ks) {
+    int cap = std::min(CHK * MAX_CHUNKS, (a.KB + ks - 1) / ks);
+    while (cap > 1 && smem_for(cap, NT, MODE, ks) > MAX_DYN_SMEM) --cap;
+    return cap;
+  };
+  if (cudaError_t e = ensure_dynamic_smem(reinterpret_cast<const void*>(&gemv_f16mma_kernel<NT, MODE>), MAX_DYN_SMEM); e != cudaSuccess) {
+    set_cuda_error(e, where);
+    return Q4B_E_CUDA;
+  }
   int ks = sm_count() / T;
   ks = ks < 1 ? 1 : (ks > 8 ? 8 : ks);
   if (ks > a.KB) ks = a.KB;
-  for (; ks > 1; --ks) {
-    const int cap = std::min(cap_max, (a.KB + ks - 1) / ks);
-    if (resident_clusters<NT>(ks, smem_for(cap, NT)) >= T) break;
-  }
+  for (; ks > 1; --ks)
+    if (resident_clusters<NT, MODE>(ks, smem_for(cap_for(ks), NT, MODE, ks)) >= T) break;
   a.ksplit = ks;
-  a.cap = std::min(cap_max, (a.KB + ks - 1) / ks);
+  a.cap = cap_for(ks);
   dim3 grid(T, ks), block(GT);
-  return check_launch(launch_pdl_cluster(gemv_f16mma_kernel<NT>, grid, block, smem_for(a.cap, NT), st, 1, ks, a), "gemv_q4_0_f16mma");
+  return check_launch(launch_pdl_cluster(gemv_f16mma_kernel<NT, MODE>, grid, block, smem_for(a.cap, NT, MODE, ks), st, 1, ks, a), where);
+}
+
+int check_common(const char* where, const void* W, const void* S, const void* Y, const void* AUX, int N, int K, int B, int epi, int ldy,
+                 const uint32_t* status) {
+  static thread_local char msg[160];
+  auto say = [&](int code, const char* what) {
+    snprintf(msg, sizeof msg, "%s: %s", where, what);
+    return fail(code, msg);
+  };
+  if (N <= 0 || K <= 0 || (K % 32)) return say(Q4B_E_SHAPE, "N > 0 and K a positive multiple of 32 required");
+  if (B < 1 || B > 32) return say(Q4B_E_SHAPE, "1 <= B <= 32 activation rows");
+  if (!W || !S || !Y || !status || !aligned16(W) || !aligned16(S)) return say(Q4B_E_ALIGN, "null or misaligned pointer");
+  if (epi < Q4B_EPI_STORE || epi > Q4B_EPI_LOGITS) return say(Q4B_E_ARG, "unknown epilogue");
+  if (epi == Q4B_EPI_BIASF && !AUX) return say(Q4B_E_ALIGN, "biasf needs AUX");
+  if (epi == Q4B_EPI_SWIGLU && (N % 2)) return say(Q4B_E_SHAPE, "swiglu needs an even row count");
+  if (ldy < (epi == Q4B_EPI_SWIGLU ? N / 2 : N)) return say(Q4B_E_SHAPE, "ldy shorter than an output row");
+  return Q4B_OK;
+}
+
+template <int MODE>
+int dispatch(F16Args& a, int T, int nt, cudaStream_t st, const char* where) {
+  switch (nt) {
+    case 1: return launch<1, MODE>(a, T, st, where);
+    case 2: return launch<2, MODE>(a, T, st, where);
+    case 3: return launch<3, MODE>(a, T, st, where);
+    default: return launch<4, MODE>(a, T, st, where);
+  }
 }
 
 }  // namespace
 
 int gemv_f16mma(const void* W, const void* S, const void* X, void* Y, const void* AUX, int N, int K, int B, int epi, int ldy,
                 uint32_t* status, cudaStream_t st) {
-  if (N <= 0 || K <= 0 || (K % 32)) return fail(Q4B_E_SHAPE, "gemv_q4_0_f16mma: N > 0 and K a positive multiple of 32 required");
-  if (B < 1 || B > 32) return fail(Q4B_E_SHAPE, "gemv_q4_0_f16mma: 1 <= B <= 32 activation rows");
-  if (!W || !S || !X || !Y || !status || !aligned16(W) || !aligned16(S) || !aligned16(X))
-    return fail(Q4B_E_ALIGN, "gemv_q4_0_f16mma: null or misaligned pointer");
-  if (epi < Q4B_EPI_STORE || epi > Q4B_EPI_LOGITS) return fail(Q4B_E_ARG, "gemv_q4_0_f16mma: unknown epilogue");
-  if (epi == Q4B_EPI_BIASF && !AUX) return fail(Q4B_E_ALIGN, "gemv_q4_0_f16mma: biasf needs AUX");
-  if (epi == Q4B_EPI_SWIGLU && (N % 2)) return fail(Q4B_E_SHAPE, "gemv_q4_0_f16mma: swiglu needs an even row count");
-  if (ldy < (epi == Q4B_EPI_SWIGLU ? N / 2 : N)) return fail(Q4B_E_SHAPE, "gemv_q4_0_f16mma: ldy shorter than an output row");
-  const int T = (N + ROWS - 1) / ROWS, KB = K / 32, nt = (B + 7) / 8;
+  const char* where = "gemv_q4_0_f16mma";
+  if (int rc = check_common(where, W, S, Y, AUX, N, K, B, epi, ldy, status); rc != Q4B_OK) return rc;
+  if (!X || !aligned16(X)) return fail(Q4B_E_ALIGN, "gemv_q4_0_f16mma: null or misaligned pointer");
   F16Args a{};
   a.W = reinterpret_cast<const uint8_t*>(W);
   a.S = reinterpret_cast<const __half*>(S);
@@ -397,14 +527,29 @@ int gemv_f16mma(const void* W, const void* S, const void* X, void* Y, const void
   a.Y = Y;
   a.AUX = AUX;
   a.status = status;
-  a.N = N; a.K = K; a.KB = KB; a.B = B; a.epi = epi; a.ldy = ldy;
+  a.N = N; a.K = K; a.KB = K / 32; a.B = B; a.epi = epi; a.ldy = ldy;
   a.wait_limit = tc::WAIT_LIMIT;
-  switch (nt) {
-    case 1: return launch<1>(a, T, st);
-    case 2: return launch<2>(a, T, st);
-    case 3: return launch<3>(a, T, st);
-    default: return launch<4>(a, T, st);
-  }
+  return dispatch<MODE_F16>(a, (N + ROWS - 1) / ROWS, (B + 7) / 8, st, where);
+}
+
+// The same kernel skeleton with Q8_1 activations and exact int8 block dots in registers (MODE_Q8).
+int gemv_q8mma(const void* W, const void* S, const void* XQ, const void* XD, void* Y, const void* AUX, int N, int K, int B, int epi,
+               int ldy, uint32_t* status, cudaStream_t st) {
+  const char* where = "mmq_q4_0_q8_1_mma";
+  if (int rc = check_common(where, W, S, Y, AUX, N, K, B, epi, ldy, status); rc != Q4B_OK) return rc;
+  if (!XQ || !XD || (reinterpret_cast<uintptr_t>(XQ) & 7u) || (reinterpret_cast<uintptr_t>(XD) & 1u))
+    return fail(Q4B_E_ALIGN, "mmq_q4_0_q8_1_mma: null or misaligned pointer");
+  F16Args a{};
+  a.W = reinterpret_cast<const uint8_t*>(W);
+  a.S = reinterpret_cast<const __half*>(S);
+  a.XQ = reinterpret_cast<const int8_t*>(XQ);
+  a.XD = reinterpret_cast<const __half*>(XD);
+  a.Y = Y;
+  a.AUX = AUX;
+  a.status = status;
+  a.N = N; a.K = K; a.KB = K / 32; a.B = B; a.epi = epi; a.ldy = ldy;
+  a.wait_limit = tc::WAIT_LIMIT;
+  return dispatch<MODE_Q8>(a, (N + ROWS - 1) / ROWS, (B + 7) / 8, st, where);
 }
 
 }  // namespace q4b

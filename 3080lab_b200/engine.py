@@ -268,6 +268,9 @@ def run_fused(m: FusedQwen, ids, gen: int):
     return toks, s.elapsed_time(e) / gen
 
 
+MMQ_MMA_MAX_ROWS = 32
+
+
 class Batched:
     """B concurrent sequences, one decode token each per `step()` — the reference's `Batched(m, B)`
     (scripts/qwen_batched_decode.py:86-187) with the linears routed through Q8_1 activations and the int8
@@ -279,7 +282,7 @@ class Batched:
     dequantised to fp16 on fp16 tensor-core MMAs (gemv_v2_source, lab/qwen_batched.py:467-641), 7 launches per layer
     (rmsnorm, qkv, attention, o, rmsnorm, gate/up, down: scripts/qwen_batched_decode.py:156-187)."""
 
-    def __init__(self, m: FusedQwen, B: int, linears: str = "q8"):
+    def __init__(self, m: FusedQwen, B: int, linears: str = "q8", mmq: str = "auto"):
         if not 1 <= B <= 32:
             raise ValueError("1 <= B <= 32 sequences")
         if linears not in ("q8", "f16"):
@@ -313,12 +316,18 @@ class Batched:
         # contexts up to 2048: attention through the shared-memory-resident kernel (K / V requested ahead of the dependency
         # wait) + the quantiser, instead of the streaming kernel with the quantiser fused in
         self.attn_cached = c.head_dim == 128 and c.n_heads // c.n_kv_heads <= 8 and m.max_len <= 2048
+        # Q8_1 x Q4_0 with register accumulators (mma.sync) instead of tcgen05 tiles: the rescale costs three fp32
+        # operations per output and k-block on the CUDA cores either way, but register accumulators have no per-tile
+        # retirement latency; measured faster up to MMQ_MMA_MAX_ROWS sequences
+        self.mmq_mma = mmq == "mma" or (mmq == "auto" and B <= MMQ_MMA_MAX_ROWS)
+        if self.mmq_mma:
+            self._fuse_gu = False
         self.launches_per_step = 1 + (9 if linears == "q8" else 7) * c.layers + 3
 
     def gemm8(self, pair, N, Kdim, Y, aux, epi, ldy, xq=None, xd=None):
         Wt, St = self.m.packed[id(pair[0])]
-        QB.gemm8(Wt, St, self.xq if xq is None else xq, self.xd if xd is None else xd, Y, aux, N, Kdim, self.B, epi, ldy,
-                 self.status)
+        fn = QB.gemm8_mma if self.mmq_mma and epi != "swiglu_q8" else QB.gemm8
+        fn(Wt, St, self.xq if xq is None else xq, self.xd if xd is None else xd, Y, aux, N, Kdim, self.B, epi, ldy, self.status)
 
     def gemv16(self, pair, N, Kdim, X, Y, aux, epi, ldy):
         Wt, St = self.m.packed[id(pair[0])]

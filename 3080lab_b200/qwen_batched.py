@@ -113,6 +113,13 @@ def gemm8(W, S, xq, xd, Y, aux, N: int, K: int, P: int, epi: str, ldy: int, stat
               _p(status.word), _stream())
 
 
+def gemm8_mma(W, S, xq, xd, Y, aux, N: int, K: int, P: int, epi: str, ldy: int, status: Status) -> None:
+    """`gemm8` for up to 32 rows with register accumulators (mma.sync.m16n8k32.s8, bulk-copied weight slab): same block
+    arithmetic, no swiglu_q8 epilogue."""
+    _ffi.call("q4b_mmq_q4_0_q8_1_mma", _p(W), _p(S), _p(xq), _p(xd), _p(Y), _p(aux), N, K, P, _ffi.EPI[epi], ldy,
+              _p(status.word), _stream())
+
+
 def head_batched(E, x, logits) -> None:
     """logits fp32 [B, V] = x fp16 [B, H] . E^T for the tied fp16 table (head_v2_source, lab/qwen_batched.py:681-833)."""
     _ffi.call("q4b_head_f16_batched", _p(E), _p(x), _p(logits), E.shape[0], E.shape[1], x.shape[0], _stream())

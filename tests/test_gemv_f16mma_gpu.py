@@ -203,3 +203,59 @@ def test_batched_f16_and_q8_agree_statistically():
     assert same >= 0.8 * 16 * 8
     a.status.check()
     b.status.check()
+
+
+# ---- the same kernel skeleton with Q8_1 activations (exact int8 block dots in registers)
+@pytest.mark.parametrize("P", [1, 3, 8, 9, 17, 32])
+@pytest.mark.parametrize("n,k", [(2048, 1536), (1536, 8960), (17920, 1536), (200, 544), (131, 96), (260, 18944)])
+def test_mmq_q8_mma_matches_oracle_and_the_tcgen05_kernel(QB, P, n, k):
+    o = oracle()
+    rng = np.random.default_rng(P * 1000 + n + k)
+    W, S = rand_q4(rng, n, k)
+    x = rng.standard_normal((P, k)).astype(np.float16)
+    x[:, ::53] *= 1e-3
+    xq, xd, _ = o.quant_q8_1(x)
+    ref = o.mmq(W, S, xq, xd)
+    st = QB.Status("cuda")
+    Wd, Sd = QB.pack_q4(dev(W), dev(S))
+    y = torch.full((P, n + 4), float("nan"), device="cuda")
+    QB.gemm8_mma(Wd, Sd, dev(xq), dev(xd), y, None, n, k, P, "logits", n + 4, st)
+    st.check()
+    got = y.cpu().numpy()
+    assert np.all(np.isnan(got[:, n:]))
+    assert nerr(got[:, :n], ref) < 2e-6
+    y2 = torch.empty_like(y)
+    QB.gemm8_mma(Wd, Sd, dev(xq), dev(xd), y2, None, n, k, P, "logits", n + 4, st)
+    assert torch.equal(y2[:, :n], y[:, :n]), "not bit-repeatable"
+    if k % 256 == 0 and k <= 8960:                      # the tcgen05 streaming kernel on the same operands
+        y3 = torch.empty(P, n, device="cuda")
+        QB.gemm8(Wd, Sd, dev(xq), dev(xd), y3, None, n, k, P, "logits", n, st)
+        st.check()
+        assert nerr(y3.cpu().numpy(), got[:, :n]) < 2e-6
+
+
+def test_mmq_q8_mma_epilogues(QB):
+    o = oracle()
+    rng = np.random.default_rng(6)
+    P, n, k = 8, 512, 1536
+    W, S = rand_q4(rng, n, k)
+    x = rng.standard_normal((P, k)).astype(np.float16)
+    xq, xd, _ = o.quant_q8_1(x)
+    acc = o.mmq(W, S, xq, xd)
+    Wd, Sd = QB.pack_q4(dev(W), dev(S))
+    xqd, xdd = dev(xq), dev(xd)
+    st = QB.Status("cuda")
+    bias = (0.1 * rng.standard_normal(n)).astype(np.float32)
+    y = torch.empty(P, n, dtype=torch.float16, device="cuda")
+    QB.gemm8_mma(Wd, Sd, xqd, xdd, y, dev(bias), n, k, P, "biasf", n, st)
+    assert nerr(y.float().cpu().numpy(), o.f16(acc + bias)) < 1e-3
+    h0 = rng.standard_normal((P, n)).astype(np.float32)
+    h = dev(h0)
+    QB.gemm8_mma(Wd, Sd, xqd, xdd, h, None, n, k, P, "resid", n, st)
+    assert nerr(h.cpu().numpy(), h0 + acc) < 1e-5
+    ys = torch.empty(P, n // 2, dtype=torch.float16, device="cuda")
+    QB.gemm8_mma(Wd, Sd, xqd, xdd, ys, None, n, k, P, "swiglu", n // 2, st)
+    assert nerr(ys.float().cpu().numpy(), o.silu_mul(acc[:, 0::2], acc[:, 1::2])) < 1e-3
+    st.check()
+    with pytest.raises(pkg("_ffi").Q4BError):
+        QB.gemm8_mma(Wd, Sd, xqd, xdd, ys, None, n, k, 33, "swiglu", n // 2, st)
