@@ -68,6 +68,7 @@ SIGNATURES = {
     "q4b_debug_tp_allreduce_expired_wait": (_I, [_P, _P, _I, _I, C.c_uint32, _P, _I, _I, _P, _P]),
     "q4b_attn_batched_kernel": (_I, [_I]),
     "q4b_mmq_q4_0_q8_1_mma": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P]),
+    "q4b_quant_mmq_q4_0_q8_1_mma": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P]),
     "q4b_rmsnorm_gemv_q4_0_mma": (_I, [_P, _P, _P, _P, _F, _P, _P, _I, _I, _I, _P, _P]),
     "q4b_rmsnorm_qkv_rope_kv": (_I, [_P, _P, _P, _P, _F, _P, _P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P, _P]),
     "q4b_debug_gemv_mma_expired_wait": (_I, [_P, _P, _P, _P, _I, _I, _P, _P]),

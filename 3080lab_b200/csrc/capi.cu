@@ -247,6 +247,11 @@ int q4b_mmq_q4_0_q8_1_mma(const void* W, const void* Sc, const void* xq, const v
   return gemv_q8mma(W, Sc, xq, xd, Y, AUX, N, K, P, epilogue, ldy, status, S(stream));
 }
 
+int q4b_quant_mmq_q4_0_q8_1_mma(const void* W, const void* Sc, const void* x16, void* Y, const void* AUX, int N, int K, int P,
+                                int epilogue, int ldy, uint32_t* status, q4b_stream_t stream) {
+  return gemv_q8mma(W, Sc, nullptr, x16, Y, AUX, N, K, P, epilogue, ldy, status, S(stream));
+}
+
 int q4b_debug_gemv_mma_expired_wait(const void* W, const void* Sc, const void* X, void* Y, int N, int K, uint32_t* status,
                                     q4b_stream_t stream) {
   return gemv_mma(W, Sc, X, Y, nullptr, N, K, 0, Q4B_EPI_LOGITS, status, S(stream), nullptr, 0.f, nullptr, nullptr, nullptr,

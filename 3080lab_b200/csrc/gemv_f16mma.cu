@@ -187,7 +187,44 @@ __global__ void __launch_bounds__(GT, NT <= 2 ? 2 : 1) gemv_f16mma_kernel(const 
       dxs[kb * NT * 8 + col] = __half2float(a.XD[(size_t)col * a.KB + kbase + kb]) * 0.0625f;
     }
   };
-  if (MODE == MODE_Q8) stage_q8(0);
+  // MODE_Q8 with fp16 activations given: the Q8_1 quantiser of quant_q8_1.cu (QUANT_Q8, lab/qwen_batched.py:1030-1039) runs
+  // here on this CTA's K window, eight lanes per 32-value block, so no separate quantiser launch is needed; values and
+  // scales are the ones that launch would have written (the scale goes through fp16 as it does there).
+  auto stage_q8_from_f16 = [&](int win) {
+    const int wkb = min(cap, nkb - win * cap);
+    const size_t kbase = (size_t)kb0 + (size_t)win * cap;
+    const int total = a.B * wkb * 8;
+    for (int i0 = 0; i0 < total; i0 += GT) {              // whole warps stay in the loop: the shuffles need every lane
+      const int i = i0 + t;
+      const bool live = i < total;
+      const int blk = (live ? i : 0) >> 3, sub = i & 7;
+      const int col = blk / wkb, kb = blk - col * wkb;
+      float x[4] = {0.f, 0.f, 0.f, 0.f};
+      if (live) {
+        const uint2 raw = *reinterpret_cast<const uint2*>(a.X + (size_t)col * a.K + (kbase + kb) * 32 + sub * 4);
+        const float2 lo = __half22float2(*reinterpret_cast<const __half2*>(&raw.x));
+        const float2 hi = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
+        x[0] = lo.x; x[1] = lo.y; x[2] = hi.x; x[3] = hi.y;
+      }
+      float amax = fmaxf(fmaxf(fabsf(x[0]), fabsf(x[1])), fmaxf(fabsf(x[2]), fabsf(x[3])));
+#pragma unroll
+      for (int o = 4; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+      const float d = amax / 127.f;
+      int q[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) q[j] = d > 0.f ? __float2int_rn(x[j] / d) : 0;
+      if (live) {
+        uint8_t* dst = xs + (size_t)col * xp + (size_t)kb * 32 + (sub >> 1) * 8 + (sub & 1) * 2;
+        *reinterpret_cast<uint16_t*>(dst) = (uint16_t)((q[0] & 0xFF) | ((q[2] & 0xFF) << 8));
+        *reinterpret_cast<uint16_t*>(dst + 4) = (uint16_t)((q[1] & 0xFF) | ((q[3] & 0xFF) << 8));
+        if (sub == 0) dxs[kb * NT * 8 + col] = __half2float(__float2half_rn(d)) * 0.0625f;
+      }
+    }
+  };
+  if (MODE == MODE_Q8) {
+    if (a.XQ) stage_q8(0);
+    else stage_q8_from_f16(0);
+  }
 
   // ---- main loop: rows rg * 32 + {g, g + 8, g + 16, g + 24}, k-blocks kg, kg + 4, ... of each window
   // A lane holds word tq of each row's 16 bytes (nibble i = weight 8 tq + i).  Logical k slot -> weight of the block:
@@ -212,7 +249,10 @@ __global__ void __launch_bounds__(GT, NT <= 2 ? 2 : 1) gemv_f16mma_kernel(const 
       tc::fence_async_smem();
       if (t < MAX_CHUNKS) issue_weights(win);
       if (MODE == MODE_F16 && warp == 1) issue_x(win);
-      if (MODE == MODE_Q8) stage_q8(win);
+      if (MODE == MODE_Q8) {
+        if (a.XQ) stage_q8(win);
+        else stage_q8_from_f16(win);
+      }
     }
     // warp w polls weight chunk w, the last warp the activations; the block barrier publishes the bulk-copied bytes to
     // everyone.  (Polling each chunk inside the loop instead, to start the MMAs while later chunks are in flight, was
@@ -537,13 +577,15 @@ int gemv_q8mma(const void* W, const void* S, const void* XQ, const void* XD, voi
                int ldy, uint32_t* status, cudaStream_t st) {
   const char* where = "mmq_q4_0_q8_1_mma";
   if (int rc = check_common(where, W, S, Y, AUX, N, K, B, epi, ldy, status); rc != Q4B_OK) return rc;
-  if (!XQ || !XD || (reinterpret_cast<uintptr_t>(XQ) & 7u) || (reinterpret_cast<uintptr_t>(XD) & 1u))
+  // XQ == nullptr: XD is the fp16 activation matrix [B, K] and the quantiser runs inside the kernel
+  if (!XD || (XQ && ((reinterpret_cast<uintptr_t>(XQ) & 7u) || (reinterpret_cast<uintptr_t>(XD) & 1u))) || (!XQ && (reinterpret_cast<uintptr_t>(XD) & 7u)))
     return fail(Q4B_E_ALIGN, "mmq_q4_0_q8_1_mma: null or misaligned pointer");
   F16Args a{};
   a.W = reinterpret_cast<const uint8_t*>(W);
   a.S = reinterpret_cast<const __half*>(S);
   a.XQ = reinterpret_cast<const int8_t*>(XQ);
-  a.XD = reinterpret_cast<const __half*>(XD);
+  a.XD = XQ ? reinterpret_cast<const __half*>(XD) : nullptr;
+  a.X = XQ ? nullptr : reinterpret_cast<const __half*>(XD);
   a.Y = Y;
   a.AUX = AUX;
   a.status = status;

@@ -120,6 +120,14 @@ def gemm8_mma(W, S, xq, xd, Y, aux, N: int, K: int, P: int, epi: str, ldy: int, 
               _p(status.word), _stream())
 
 
+def quant_gemm8_mma(W, S, x16, Y, aux, N: int, K: int, epi: str, ldy: int, status: Status) -> None:
+    """`quant_q8` followed by `gemm8_mma` in one launch: x16 fp16 [P, K] is quantised inside the kernel (same bits).
+    Saves a launch, but every CTA requantises its K window after its dependency wait; in the batched decode step the two
+    separate launches measured faster, so the engine does not use this form."""
+    _ffi.call("q4b_quant_mmq_q4_0_q8_1_mma", _p(W), _p(S), _p(x16), _p(Y), _p(aux), N, K, x16.shape[0], _ffi.EPI[epi], ldy,
+              _p(status.word), _stream())
+
+
 def head_batched(E, x, logits) -> None:
     """logits fp32 [B, V] = x fp16 [B, H] . E^T for the tied fp16 table (head_v2_source, lab/qwen_batched.py:681-833)."""
     _ffi.call("q4b_head_f16_batched", _p(E), _p(x), _p(logits), E.shape[0], E.shape[1], x.shape[0], _stream())

@@ -227,6 +227,12 @@ int q4b_gemv_q4_0_f16mma(const void* Wt, const void* St, const void* X, void* Y,
 int q4b_mmq_q4_0_q8_1_mma(const void* Wt, const void* St, const void* xq, const void* xd, void* Y, const void* AUX, int N, int K,
                           int P, int epilogue, int ldy, uint32_t* status, q4b_stream_t stream);
 
+/* q4b_quant_q8_1 + q4b_mmq_q4_0_q8_1_mma in one launch: x16 fp16 [P, K] is quantised to Q8_1 inside the kernel (each CTA its
+ * own K window; QUANT_Q8 arithmetic, lab/qwen_batched.py:1030-1039) and multiplied as above.  Same results, bit for bit,
+ * as the two launches.  Replaces the reference's `QUANT_Q8` + `gemm8` pair (scripts/qwen_prefill.py:208-246) for <= 32 rows. */
+int q4b_quant_mmq_q4_0_q8_1_mma(const void* Wt, const void* St, const void* x16, void* Y, const void* AUX, int N, int K, int P,
+                                int epilogue, int ldy, uint32_t* status, q4b_stream_t stream);
+
 /* Exercise of the failure path of the bounded device-side waits, in a form that always returns: q4b_gemv_q4_0_mma
  * (fp16 x, logits epilogue) with the bulk copies of its first weight chunk withheld and the wait cut to a few thousand
  * polls.  The wait gives up, the kernel sets *status non-zero and finishes normally; Y is meaningless.  The reference's

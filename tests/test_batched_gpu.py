@@ -27,14 +27,16 @@ def test_head_f16_batched(B, V, H):
     assert np.max(np.abs(got - ref)) / np.max(np.abs(ref)) < 1e-5
 
 
+@pytest.mark.parametrize("mmq", ["auto", "tc"])
 @pytest.mark.parametrize("cfg_name,B,seed", [("tiny", 3, 0), ("small", 8, 1), ("small", 32, 4)])
-def test_batched_greedy_matches_oracle(cfg_name, B, seed):
-    """Graph-replayed greedy decode of B different sequences: identical tokens over 64 steps."""
+def test_batched_greedy_matches_oracle(cfg_name, B, seed, mmq):
+    """Graph-replayed greedy decode of B different sequences: identical tokens over 64 steps, through the register-
+    accumulator MMQ with the quantisers fused in (the default) and through the tcgen05 MMQ."""
     s, E = pkg("synth"), pkg("engine")
     cfg = s.CONFIGS[cfg_name]
     model = s.synth_model(cfg, seed)
     m = E.FusedQwen(model, max_len=128)
-    bm = E.Batched(m, B)
+    bm = E.Batched(m, B, mmq=mmq)
     prompts = np.stack([s.synth_prompt(cfg, 12, seed * 100 + b) for b in range(B)])
     got, _ = E.run_batched(bm, prompts, 64)
     cos, sin = s.rope_tables(cfg, 128)
@@ -49,7 +51,8 @@ def test_batched_greedy_matches_oracle(cfg_name, B, seed):
 
 
 @pytest.mark.parametrize("cfg_name,B,seed", [("tiny", 32, 2), ("small", 16, 3)])
-def test_batched_teacher_forced_logits(cfg_name, B, seed):
+@pytest.mark.parametrize("mmq", ["auto", "tc"])
+def test_batched_teacher_forced_logits(cfg_name, B, seed, mmq):
     """Every sequence is fed the oracle's tokens, so the two never drift apart, and the logits are compared at every
     step.  The int8 activation path is discontinuous: an activation that differs from the oracle's by one fp16 ulp
     (allowed) can move an int8 value by one unit, which shifts logits by a few 1e-3.  So: the typical (median) error
@@ -60,7 +63,7 @@ def test_batched_teacher_forced_logits(cfg_name, B, seed):
     cfg = s.CONFIGS[cfg_name]
     model = s.synth_model(cfg, seed)
     m = E.FusedQwen(model, max_len=64)
-    bm = E.Batched(m, B)
+    bm = E.Batched(m, B, mmq=mmq)
     cos, sin = s.rope_tables(cfg, 64)
     orc = oracle().Oracle(model, 64, cos, sin, batch=B)
     toks = np.stack([s.synth_prompt(cfg, 1, seed * 100 + b) for b in range(B)])[:, 0]

@@ -259,3 +259,22 @@ def test_mmq_q8_mma_epilogues(QB):
     st.check()
     with pytest.raises(pkg("_ffi").Q4BError):
         QB.gemm8_mma(Wd, Sd, xqd, xdd, ys, None, n, k, 33, "swiglu", n // 2, st)
+
+
+@pytest.mark.parametrize("P,n,k", [(8, 1536, 1536), (5, 1536, 8960), (32, 1536, 8960), (17, 200, 544), (8, 260, 18944)])
+def test_quantiser_fused_into_the_mmq_equals_two_launches(QB, P, n, k):
+    """fp16 activations quantised inside the GEMM launch: the same bits as the quantiser launch followed by the GEMM."""
+    rng = np.random.default_rng(P + n + k)
+    W, S = rand_q4(rng, n, k)
+    Wd, Sd = QB.pack_q4(dev(W), dev(S))
+    x = torch.from_numpy(rng.standard_normal((P, k)).astype(np.float16)).cuda()
+    x[:, 64:96] = 0                                          # an all-zero block: scale 0, values 0
+    st = QB.Status("cuda")
+    xq, xd = torch.zeros(P * k, dtype=torch.int8, device="cuda"), torch.zeros(P * k // 32, dtype=torch.float16, device="cuda")
+    QB.quant_q8(x, xq, xd)
+    h0 = torch.from_numpy(rng.standard_normal((P, n)).astype(np.float32)).cuda()
+    a, b = h0.clone(), h0.clone()
+    QB.gemm8_mma(Wd, Sd, xq, xd, a, None, n, k, P, "resid", n, st)
+    QB.quant_gemm8_mma(Wd, Sd, x, b, None, n, k, "resid", n, st)
+    st.check()
+    assert torch.equal(a, b)
