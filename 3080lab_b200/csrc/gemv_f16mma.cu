@@ -106,7 +106,7 @@ __host__ __device__ __forceinline__ size_t x_pitch(int cap) { return (size_t)(ca
 // rows x 32 bytes) fall into distinct banks
 __host__ __device__ __forceinline__ size_t xq_pitch(int cap) { return ((size_t)cap * 32 + 127) / 128 * 128 + 32; }
 
-constexpr int MODE_F16 = 0, MODE_Q8 = 1;
+constexpr int MODE_F16 = 0, MODE_Q8 = 1, MODE_Q8F = 2;   // Q8F: Q8 arithmetic, fp16 activations quantised inside
 
 // MODE_F16: fp16 activations, weights dequantised to fp16 (the reference's batched-decode GEMV).
 // MODE_Q8:  Q8_1 activations (int8 values + fp16 block scales), exact int32 block dots by mma.sync.m16n8k32.s8 with register
@@ -127,12 +127,13 @@ __global__ void __launch_bounds__(GT, NT <= 2 ? 2 : 1) gemv_f16mma_kernel(const 
   const int kb0 = (int)(((long long)a.KB * ks) / a.ksplit), kb1 = (int)(((long long)a.KB * (ks + 1)) / a.ksplit);
   const int nkb = kb1 - kb0;
   const int cap = a.cap;                                  // k-blocks per window of the slab (nkb <= cap except for very long K)
-  const size_t xp = MODE == MODE_F16 ? x_pitch(cap) : xq_pitch(cap);
+  constexpr bool Q8 = MODE != MODE_F16;                   // int8 block-dot arithmetic (activations given as Q8_1, or quantised here)
+  const size_t xp = Q8 ? xq_pitch(cap) : x_pitch(cap);
   uint8_t* slabW = smem;                                  // [k-block][128 rows][16 bytes]
   uint8_t* slabS = slabW + (size_t)cap * 2048;            // [k-block][128 rows] fp16
   uint8_t* xs = slabS + (size_t)cap * 256;                // [8 NT rows][pitch]: the K window of X (fp16, or int8 permuted)
   float* dxs = reinterpret_cast<float*>(xs + (size_t)NT * 8 * xp);   // MODE_Q8: [k-block][8 NT] block scales / 16 as fp32
-  float* P = dxs + (MODE == MODE_Q8 ? (size_t)cap * NT * 8 : 0);   // [8 NT columns][PSTR]: this CTA's partial sums
+  float* P = dxs + (Q8 ? (size_t)cap * NT * 8 : 0);   // [8 NT columns][PSTR]: this CTA's partial sums
 
   // window `win` covers k-blocks kb0 + win cap .. of this CTA's slice; lane c of warp 0 owns weight chunk c
   auto issue_weights = [&](int win) {
@@ -165,7 +166,7 @@ __global__ void __launch_bounds__(GT, NT <= 2 ? 2 : 1) gemv_f16mma_kernel(const 
   // activation rows B .. 8 NT - 1 do not exist: their MMA columns read zeros
   for (int i = t; i < (NT * 8 - a.B) * (int)(xp / 16); i += GT)
     reinterpret_cast<uint4*>(xs + (size_t)a.B * xp)[i] = make_uint4(0u, 0u, 0u, 0u);
-  if (MODE == MODE_Q8)
+  if (Q8)
     for (int i = t; i < cap * NT * 8; i += GT) dxs[i] = 0.f;
   __syncthreads();
   pdl_wait();                                             // X comes from the previous kernel
@@ -221,10 +222,10 @@ __global__ void __launch_bounds__(GT, NT <= 2 ? 2 : 1) gemv_f16mma_kernel(const 
       }
     }
   };
-  if (MODE == MODE_Q8) {
-    if (a.XQ) stage_q8(0);
-    else stage_q8_from_f16(0);
-  }
+  // (the quantising form is a template instance of its own: with both stagings in one kernel the plain Q8_1 form ran
+  // 0.9 us per launch slower inside the decode step, though not in isolation)
+  if (MODE == MODE_Q8) stage_q8(0);
+  if (MODE == MODE_Q8F) stage_q8_from_f16(0);
 
   // ---- main loop: rows rg * 32 + {g, g + 8, g + 16, g + 24}, k-blocks kg, kg + 4, ... of each window
   // A lane holds word tq of each row's 16 bytes (nibble i = weight 8 tq + i).  Logical k slot -> weight of the block:
@@ -249,10 +250,8 @@ __global__ void __launch_bounds__(GT, NT <= 2 ? 2 : 1) gemv_f16mma_kernel(const 
       tc::fence_async_smem();
       if (t < MAX_CHUNKS) issue_weights(win);
       if (MODE == MODE_F16 && warp == 1) issue_x(win);
-      if (MODE == MODE_Q8) {
-        if (a.XQ) stage_q8(win);
-        else stage_q8_from_f16(win);
-      }
+      if (MODE == MODE_Q8) stage_q8(win);
+      if (MODE == MODE_Q8F) stage_q8_from_f16(win);
     }
     // warp w polls weight chunk w, the last warp the activations; the block barrier publishes the bulk-copied bytes to
     // everyone.  (Polling each chunk inside the loop instead, to start the MMAs while later chunks are in flight, was
@@ -262,7 +261,7 @@ __global__ void __launch_bounds__(GT, NT <= 2 ? 2 : 1) gemv_f16mma_kernel(const 
       if (MODE == MODE_F16 && warp == GT / 32 - 1) ok = mbar_wait_n(&bar_x, parity, a.wait_limit) && ok;
     }
     __syncthreads();
-    if (MODE == MODE_Q8) {
+    if (Q8) {
       // A fragment of an m16 tile: a0 / a2 = even / odd weights of row g's word tq, a1 / a3 the same of row g + 8; the
       // activation bytes were staged in the matching order, so lane tq reads its 8 bytes of column g in one load.
       const uint8_t* xq0 = xs + (size_t)g * xp + tq * 8;
@@ -463,7 +462,7 @@ __global__ void __launch_bounds__(GT, NT <= 2 ? 2 : 1) gemv_f16mma_kernel(const 
 }
 
 size_t smem_for(int cap, int nt, int mode, int ks) {
-  const size_t x = mode == MODE_F16 ? (size_t)nt * 8 * x_pitch(cap) : (size_t)nt * 8 * xq_pitch(cap) + (size_t)cap * nt * 8 * sizeof(float);
+  const size_t x = mode == MODE_F16 ? (size_t)nt * 8 * x_pitch(cap) : (size_t)nt * 8 * xq_pitch(cap) + (size_t)cap * nt * 8 * sizeof(float);   // Q8 and Q8F alike
   // partial tiles (four with up to 8 columns, else one) + with K slices the receive buffer of their reduction (< 64 + 8 pairs)
   size_t red = (size_t)(nt == 1 ? 4 : 1) * nt * 8 * PSTR * sizeof(float);
   if (ks > 1) red += (size_t)nt * 8 * (ROWS / 2 + 8) * 2 * sizeof(float);
@@ -591,6 +590,7 @@ int gemv_q8mma(const void* W, const void* S, const void* XQ, const void* XD, voi
   a.status = status;
   a.N = N; a.K = K; a.KB = K / 32; a.B = B; a.epi = epi; a.ldy = ldy;
   a.wait_limit = tc::WAIT_LIMIT;
+  if (!XQ) return dispatch<MODE_Q8F>(a, (N + ROWS - 1) / ROWS, (B + 7) / 8, st, where);
   return dispatch<MODE_Q8>(a, (N + ROWS - 1) / ROWS, (B + 7) / 8, st, where);
 }
 

@@ -14,7 +14,6 @@ namespace q4b {
 
 namespace {
 
-constexpr int HBT = 256, HBW = HBT / 32;
 
 __device__ __forceinline__ void mma16816(float* c, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
   asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
@@ -22,10 +21,15 @@ __device__ __forceinline__ void mma16816(float* c, uint32_t a0, uint32_t a1, uin
                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-template <int NB>   // n-tiles of 8 sequences
+// NB n-tiles of 8 sequences; HBT threads.  A warp keeps 4 spans x 2 rows x 16 bytes per lane in flight: 16 warps = 64 KB per SM,
+// what the HBM latency asks for (8 warps: 114 us for the 1.5B table at 8 sequences, 179 us at 32; 16 warps: 82 and 94 us).
+// Up to 8 sequences keep 8 warps all the same: inside the Q8_1 decode step the 16-warp form made the STEP 39 us slower
+// although the kernel itself was 31 us faster (measured repeatedly; the cause was not isolated).
+template <int NB, int HBT>
 __global__ void __launch_bounds__(HBT, 1) head_f16_batched_kernel(const uint4* __restrict__ E, const __half* x,
                                                                   float* logits, int V, int H, int B) {
   extern __shared__ __align__(16) uint8_t xs[];         // [8 NB][pitch] fp16, pitch = 2 H + 64 bytes (conflict-free)
+  constexpr int HBW = HBT / 32;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   const int HC = H >> 3;                                 // 16-byte chunks per row
   const uint32_t pitch = (uint32_t)H * 2 + 64;
@@ -48,7 +52,7 @@ __global__ void __launch_bounds__(HBT, 1) head_f16_batched_kernel(const uint4* _
     float acc[NB][4];
 #pragma unroll
     for (int j = 0; j < NB; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
-    constexpr int UN = 4;                                // spans in flight
+    constexpr int UN = HBT == 256 ? 8 : 4;               // spans in flight: 64 KB per SM either way
     for (int s0 = 0; s0 < spans; s0 += UN) {
       uint4 wa[UN], wb[UN];
 #pragma unroll
@@ -84,10 +88,11 @@ __global__ void __launch_bounds__(HBT, 1) head_f16_batched_kernel(const uint4* _
   }
 }
 
-template <int NB>
+template <int NB, int HBT>
 int launch_hb(const void* E, const void* x, float* logits, int V, int H, int B, cudaStream_t st) {
+  constexpr int HBW = HBT / 32;
   const size_t smem = (size_t)8 * NB * ((size_t)H * 2 + 64);
-  auto kern = head_f16_batched_kernel<NB>;
+  auto kern = head_f16_batched_kernel<NB, HBT>;
   if (smem > 48 * 1024) {
     if (cudaError_t e = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), 200 * 1024); e != cudaSuccess) {
       set_cuda_error(e, "head_f16_batched: cudaFuncSetAttribute");
@@ -108,9 +113,9 @@ int head_f16_batched(const void* E, const void* x, float* logits, int V, int H, 
   if (V <= 0 || H <= 0 || (H % 32) || B < 1 || B > 32) return fail(Q4B_E_SHAPE, "head_f16_batched: need V > 0, H a multiple of 32, 1 <= B <= 32");
   if ((size_t)32 * ((size_t)H * 2 + 64) > 200 * 1024 && B > 16) return fail(Q4B_E_SHAPE, "head_f16_batched: H too large for 32 sequences");
   if (!E || !x || !logits || !aligned16(E) || !aligned16(x)) return fail(Q4B_E_ALIGN, "head_f16_batched: null or misaligned pointer");
-  if (B <= 8) return launch_hb<1>(E, x, logits, V, H, B, st);
-  if (B <= 16) return launch_hb<2>(E, x, logits, V, H, B, st);
-  return launch_hb<4>(E, x, logits, V, H, B, st);
+  if (B <= 8) return launch_hb<1, 256>(E, x, logits, V, H, B, st);
+  if (B <= 16) return launch_hb<2, 512>(E, x, logits, V, H, B, st);
+  return launch_hb<4, 512>(E, x, logits, V, H, B, st);
 }
 
 }  // namespace q4b

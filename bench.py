@@ -358,12 +358,36 @@ def bench_batched(model, cfg, B: int, steps: int, warmup: int, local_rank: int, 
     e2e_ms = s.elapsed_time(e) / gen
     step_bytes = cfg.q4_bytes_per_layer() * cfg.layers + cfg.head_bytes() + B * cfg.kv_bytes_per_position() * (ctx + gen / 2.0)
     ach = step_bytes / (ms * 1e-3) / 1e9
+    # the other two routes of the linears, device-timed the same way: the tcgen05 MMQ (TMEM accumulators, one tile per
+    # k-block) and the reference's own fp16-weight arithmetic; reported beside the default, not as the value
+    others = {}
+    for name, kw in (("q8_tcgen05_mmq", dict(linears="q8", mmq="tc")), ("f16_weights_fp16_mma", dict(linears="f16"))):
+        b2 = engine.Batched(m, B, **kw)
+        b2.kc.copy_(bm.kc)
+        b2.vc.copy_(bm.vc)
+        b2.pos.fill_(ctx)
+        b2.tok.copy_(bm.tok)
+        g2 = b2.capture()
+        for _ in range(3):
+            g2.replay()
+        b2.pos.fill_(ctx)
+        torch.cuda.synchronize()
+        s.record()
+        for _ in range(gen):
+            g2.replay()
+        e.record()
+        torch.cuda.synchronize()
+        b2.status.check("batched decode")
+        others[name] = {"tok_per_s": B / (s.elapsed_time(e) / gen) * 1e3, "launches_per_step": b2.launches_per_step}
+        del b2, g2
     out = {
         "metric": f"decode_tok_per_s_batch{B}", "value": B / ms * 1e3, "unit": "tok/s", "n_gpus": 1, "steps": gen,
         "warmup": warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "int8 x int4 -> int32, fp32 scaling", "data": "synthetic",
         "config": {"workload": f"qwen2.5-1.5b-shape batched decode, {B} sequences, 1024-token KV context, Q8_1 x Q4_0 MMQ",
+                   "linears": "Q8_1 activations, exact int32 block dots by mma.sync.m16n8k32.s8 with register accumulators",
                    "l2": "1.2 GB of weights + KV streamed per step, larger than L2"},
+        "other_routes": others,
         "roofline": {"bound": "hbm", "kernel": "whole step", "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                      "frac": ach / peaks["hbm_gbs"], "peak_kind": f"of {peak_kind}", "traffic": None},
         "e2e": {"value": B / e2e_ms * 1e3, "unit": "tok/s", "h2d_bytes_per_step": 8 * B, "d2h_bytes_per_step": 8 * B},
