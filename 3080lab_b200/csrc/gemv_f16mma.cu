@@ -407,6 +407,25 @@ __global__ void __launch_bounds__(GT, NT <= 2 ? 2 : 1) gemv_f16mma_kernel(const 
     }
     cluster_sync_all();
   }
+  if (a.epi == Q4B_EPI_SWIGLU_Q8) {
+    // SwiGLU + re-quantise for `down` (lab/qwen_batched.py:1363-1396; unsplit launches, whole tiles only): the product
+    // rounded to fp16, then the Q8_1 quantiser on it.  A 32-value block of the product is 32 row pairs of one column = one
+    // warp of this loop (64 B is a multiple of 32, so warps are whole).
+    int8_t* qo = reinterpret_cast<int8_t*>(a.Y);
+    __half* dout = reinterpret_cast<__half*>(const_cast<void*>(a.AUX));
+    for (int i = t; i < (ROWS / 2) * a.B; i += GT) {
+      const int col = i >> 6, pr = i & 63;
+      const float2 pv = partial2(col, pr);
+      const float act = __half2float(__float2half_rn(pv.x / (1.f + __expf(-pv.x)) * pv.y));
+      const float d = warp_max(fabsf(act)) / 127.f;
+      const int q = d > 0.f ? __float2int_rn(act / d) : 0;
+      const size_t f = (size_t)tile * (ROWS / 2) + pr;
+      qo[(size_t)col * a.ldy + f] = (int8_t)q;
+      if (lane == 0) dout[(size_t)col * (a.ldy >> 5) + (f >> 5)] = __float2half_rn(d);
+    }
+    if (!ok) atomicOr(a.status, 1u);
+    return;
+  }
   const int npr = pr1 - pr0;
   for (int i = t; i < npr * a.B; i += GT) {
     const int col = i / npr, pl = i - col * npr, pr = pr0 + pl;
@@ -519,6 +538,7 @@ int launch(F16Args& a, int T, cudaStream_t st, const char* where) {
   if (ks > a.KB) ks = a.KB;
   for (; ks > 1; --ks)
     if (resident_clusters<NT, MODE>(ks, smem_for(cap_for(ks), NT, MODE, ks)) >= T) break;
+  if (a.epi == Q4B_EPI_SWIGLU_Q8 && ks > 1) return fail(Q4B_E_SHAPE, "mmq_q4_0_q8_1_mma: swiglu_q8 only where the launch is not split along K");
   a.ksplit = ks;
   a.cap = cap_for(ks);
   dim3 grid(T, ks), block(GT);
@@ -535,10 +555,11 @@ int check_common(const char* where, const void* W, const void* S, const void* Y,
   if (N <= 0 || K <= 0 || (K % 32)) return say(Q4B_E_SHAPE, "N > 0 and K a positive multiple of 32 required");
   if (B < 1 || B > 32) return say(Q4B_E_SHAPE, "1 <= B <= 32 activation rows");
   if (!W || !S || !Y || !status || !aligned16(W) || !aligned16(S)) return say(Q4B_E_ALIGN, "null or misaligned pointer");
-  if (epi < Q4B_EPI_STORE || epi > Q4B_EPI_LOGITS) return say(Q4B_E_ARG, "unknown epilogue");
+  if (epi < Q4B_EPI_STORE || epi > Q4B_EPI_SWIGLU_Q8) return say(Q4B_E_ARG, "unknown epilogue");
+  if (epi == Q4B_EPI_SWIGLU_Q8 && ((N % 128) || !AUX || (ldy % 32))) return say(Q4B_E_SHAPE, "swiglu_q8 needs N a multiple of 128, AUX (scales out) and ldy a multiple of 32");
   if (epi == Q4B_EPI_BIASF && !AUX) return say(Q4B_E_ALIGN, "biasf needs AUX");
   if (epi == Q4B_EPI_SWIGLU && (N % 2)) return say(Q4B_E_SHAPE, "swiglu needs an even row count");
-  if (ldy < (epi == Q4B_EPI_SWIGLU ? N / 2 : N)) return say(Q4B_E_SHAPE, "ldy shorter than an output row");
+  if (ldy < (epi == Q4B_EPI_SWIGLU || epi == Q4B_EPI_SWIGLU_Q8 ? N / 2 : N)) return say(Q4B_E_SHAPE, "ldy shorter than an output row");
   return Q4B_OK;
 }
 
@@ -559,6 +580,7 @@ int gemv_f16mma(const void* W, const void* S, const void* X, void* Y, const void
   const char* where = "gemv_q4_0_f16mma";
   if (int rc = check_common(where, W, S, Y, AUX, N, K, B, epi, ldy, status); rc != Q4B_OK) return rc;
   if (!X || !aligned16(X)) return fail(Q4B_E_ALIGN, "gemv_q4_0_f16mma: null or misaligned pointer");
+  if (epi == Q4B_EPI_SWIGLU_Q8) return fail(Q4B_E_ARG, "gemv_q4_0_f16mma: unknown epilogue");
   F16Args a{};
   a.W = reinterpret_cast<const uint8_t*>(W);
   a.S = reinterpret_cast<const __half*>(S);

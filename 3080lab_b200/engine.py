@@ -324,12 +324,12 @@ class Batched:
             # (the quantisers stay separate launches: run inside the o_proj / down_proj launches instead, through
             # QB.quant_gemm8_mma, every CTA requantises its K window after the dependency wait, and the step was slower:
             # 1230 against 1188 us at 8 sequences, 2346 against 2094 us at 32)
-            self._fuse_gu = False
+            self._fuse_gu = None                          # SwiGLU + quantiser in the gate/up epilogue where it is unsplit
         self.launches_per_step = 1 + (9 if linears == "q8" else 7) * c.layers + 3
 
     def gemm8(self, pair, N, Kdim, Y, aux, epi, ldy, xq=None, xd=None):
         Wt, St = self.m.packed[id(pair[0])]
-        fn = QB.gemm8_mma if self.mmq_mma and epi != "swiglu_q8" else QB.gemm8
+        fn = QB.gemm8_mma if self.mmq_mma else QB.gemm8
         fn(Wt, St, self.xq if xq is None else xq, self.xd if xd is None else xd, Y, aux, N, Kdim, self.B, epi, ldy, self.status)
 
     def gemv16(self, pair, N, Kdim, X, Y, aux, epi, ldy):

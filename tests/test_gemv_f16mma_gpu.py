@@ -278,3 +278,30 @@ def test_quantiser_fused_into_the_mmq_equals_two_launches(QB, P, n, k):
     QB.quant_gemm8_mma(Wd, Sd, x, b, None, n, k, "resid", n, st)
     st.check()
     assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("P", [3, 8, 32])
+def test_mmq_q8_mma_swiglu_q8_equals_swiglu_then_quantiser(QB, P):
+    """Unsplit gate/up launch (as many row tiles as SMs): SwiGLU product quantised in the epilogue = `swiglu` + quantiser."""
+    o = oracle()
+    rng = np.random.default_rng(P)
+    n, k = 128 * 160, 512
+    W, S = rand_q4(rng, n, k)
+    Wd, Sd = QB.pack_q4(dev(W), dev(S))
+    x = rng.standard_normal((P, k)).astype(np.float16)
+    xq, xd, _ = o.quant_q8_1(x)
+    xqd, xdd = dev(xq), dev(xd)
+    st = QB.Status("cuda")
+    act = torch.zeros(P, n // 2, dtype=torch.float16, device="cuda")
+    QB.gemm8_mma(Wd, Sd, xqd, xdd, act, None, n, k, P, "swiglu", n // 2, st)
+    wq, wd = torch.zeros(P * n // 2, dtype=torch.int8, device="cuda"), torch.zeros(P * n // 64, dtype=torch.float16, device="cuda")
+    QB.quant_q8(act, wq, wd)
+    gq, gd = torch.zeros_like(wq), torch.zeros_like(wd)
+    QB.gemm8_mma(Wd, Sd, xqd, xdd, gq, gd, n, k, P, "swiglu_q8", n // 2, st)
+    st.check()
+    assert torch.equal(gq, wq) and torch.equal(gd, wd)
+    # a launch that is split along K has no fused form: the caller falls back
+    W2, S2 = rand_q4(rng, 1024, k)
+    with pytest.raises(pkg("_ffi").Q4BError) as e:
+        QB.gemm8_mma(*QB.pack_q4(dev(W2), dev(S2)), xqd, xdd, gq, gd, 1024, k, P, "swiglu_q8", 512, st)
+    assert e.value.code == pkg("_ffi").E_SHAPE
