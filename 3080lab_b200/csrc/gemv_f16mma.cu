@@ -171,21 +171,31 @@ __global__ void __launch_bounds__(GT, NT <= 2 ? 2 : 1) gemv_f16mma_kernel(const 
   __syncthreads();
   pdl_wait();                                             // X comes from the previous kernel
   if (MODE == MODE_F16 && warp == 1) issue_x(0);
-  // MODE_Q8: int8 values by plain 8-byte loads, the bytes of each group of eight reordered to (k0, k2, k4, k6 | k1, k3, k5, k7)
-  // to match the nibble expansion of the weights; block scales converted to fp32 with the factor 1/16 of the expansion
+  // MODE_Q8: the int8 rows arrive by bulk copy like the fp16 ones (one round trip; as plain loads in a loop they were three
+  // dependent ones), the block scales by plain loads that are in flight meanwhile (converted to fp32 with the factor 1/16
+  // of the nibble expansion).  `permute_q8`, after the copies have landed, reorders the bytes of each group of eight in
+  // place to (k0, k2, k4, k6 | k1, k3, k5, k7), the order the expansion gives the weights.
   auto stage_q8 = [&](int win) {
     const int wkb = min(cap, nkb - win * cap);
     const size_t kbase = (size_t)kb0 + (size_t)win * cap;
-    for (int i = t; i < a.B * wkb * 4; i += GT) {
-      const int col = i / (wkb * 4), r = i - col * (wkb * 4);
-      const uint2 v = *reinterpret_cast<const uint2*>(a.XQ + (size_t)col * a.K + kbase * 32 + (size_t)r * 8);
-      uint2 o;
-      tc::permute_bytes(v.x, v.y, o.x, o.y);
-      *reinterpret_cast<uint2*>(xs + (size_t)col * xp + (size_t)r * 8) = o;
+    if (warp == 1) {
+      if (lane == 0) tc::mbar_expect_tx(&bar_x, (uint32_t)a.B * (uint32_t)wkb * 32u);
+      __syncwarp();
+      if (lane < a.B) bulk_g2s(xs + (size_t)lane * xp, a.XQ + (size_t)lane * a.K + kbase * 32, (uint32_t)wkb * 32u, &bar_x);
     }
     for (int i = t; i < a.B * wkb; i += GT) {
       const int col = i / wkb, kb = i - col * wkb;
       dxs[kb * NT * 8 + col] = __half2float(a.XD[(size_t)col * a.KB + kbase + kb]) * 0.0625f;
+    }
+  };
+  auto permute_q8 = [&](int wkb) {
+    for (int i = t; i < a.B * wkb * 4; i += GT) {
+      const int col = i / (wkb * 4), r = i - col * (wkb * 4);
+      uint2* p8 = reinterpret_cast<uint2*>(xs + (size_t)col * xp + (size_t)r * 8);
+      const uint2 v = *p8;
+      uint2 o;
+      tc::permute_bytes(v.x, v.y, o.x, o.y);
+      *p8 = o;
     }
   };
   // MODE_Q8 with fp16 activations given: the Q8_1 quantiser of quant_q8_1.cu (QUANT_Q8, lab/qwen_batched.py:1030-1039) runs
@@ -258,9 +268,13 @@ __global__ void __launch_bounds__(GT, NT <= 2 ? 2 : 1) gemv_f16mma_kernel(const 
     // measured slower: gate/up at 8 rows 7.9 us against 7.0.)
     if (lane == 0) {
       for (int ch = warp; ch * CHK < wkb; ch += GT / 32) ok = mbar_wait_n(&bar_load[ch], parity, a.wait_limit) && ok;
-      if (MODE == MODE_F16 && warp == GT / 32 - 1) ok = mbar_wait_n(&bar_x, parity, a.wait_limit) && ok;
+      if (MODE != MODE_Q8F && warp == GT / 32 - 1) ok = mbar_wait_n(&bar_x, parity, a.wait_limit) && ok;
     }
     __syncthreads();
+    if (MODE == MODE_Q8) {
+      permute_q8(wkb);
+      __syncthreads();
+    }
     if (Q8) {
       // A fragment of an m16 tile: a0 / a2 = even / odd weights of row g's word tq, a1 / a3 the same of row g + 8; the
       // activation bytes were staged in the matching order, so lane tq reads its 8 bytes of column g in one load.
@@ -599,7 +613,7 @@ int gemv_q8mma(const void* W, const void* S, const void* XQ, const void* XD, voi
   const char* where = "mmq_q4_0_q8_1_mma";
   if (int rc = check_common(where, W, S, Y, AUX, N, K, B, epi, ldy, status); rc != Q4B_OK) return rc;
   // XQ == nullptr: XD is the fp16 activation matrix [B, K] and the quantiser runs inside the kernel
-  if (!XD || (XQ && ((reinterpret_cast<uintptr_t>(XQ) & 7u) || (reinterpret_cast<uintptr_t>(XD) & 1u))) || (!XQ && (reinterpret_cast<uintptr_t>(XD) & 7u)))
+  if (!XD || (XQ && ((reinterpret_cast<uintptr_t>(XQ) & 15u) || (reinterpret_cast<uintptr_t>(XD) & 1u))) || (!XQ && (reinterpret_cast<uintptr_t>(XD) & 7u)))
     return fail(Q4B_E_ALIGN, "mmq_q4_0_q8_1_mma: null or misaligned pointer");
   F16Args a{};
   a.W = reinterpret_cast<const uint8_t*>(W);

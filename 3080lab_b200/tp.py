@@ -211,13 +211,14 @@ class TPBatched:
         # (the peer path trades the two RMSNorm + Q8_1 launches of a layer for its two reduction launches: same count)
 
     def _gemm8(self, pair, N, Kdim, Y, aux, epi, ldy):
-        """One linear over all B sequences; the tensor-core kernel takes up to 32 activation rows per launch."""
+        """One linear over all B sequences; the MMQ (register accumulators, as engine.Batched uses it) takes up to 32
+        activation rows per launch."""
         Wt, St = self.m.packed[id(pair[0])]
         Yf = Y.view(-1)
         for c0 in range(0, self.B, 32):
             n = min(32, self.B - c0)
-            QB.gemm8(Wt, St, self.xq[c0 * Kdim:], self.xd[c0 * (Kdim // 32):], Yf[c0 * ldy:], aux, N, Kdim, n, epi, ldy,
-                     self.status)
+            QB.gemm8_mma(Wt, St, self.xq[c0 * Kdim:], self.xd[c0 * (Kdim // 32):], Yf[c0 * ldy:], aux, N, Kdim, n, epi, ldy,
+                         self.status)
 
     @property
     def part(self) -> torch.Tensor:

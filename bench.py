@@ -315,7 +315,7 @@ def bench_gemv_config1(torch, peaks, peak_kind) -> dict:
             "e2e": {"value": b / e2e_us / 1e3, "unit": "GB/s", "us_per_call": e2e_us, "h2d_bytes_per_step": k * 4, "d2h_bytes_per_step": n * 4}}
 
 
-def bench_batched(model, cfg, B: int, steps: int, warmup: int, local_rank: int, torch, peaks, peak_kind) -> dict:
+def bench_batched(model, cfg, B: int, steps: int, warmup: int, local_rank: int, torch, peaks, peak_kind, routes: bool = True) -> dict:
     """Batched decode at B concurrent sequences, each with a 1024-token KV context (Q8_1 activations, int8 MMQ)."""
     synth = importlib.import_module("3080lab_b200.synth")
     engine = importlib.import_module("3080lab_b200.engine")
@@ -361,7 +361,7 @@ def bench_batched(model, cfg, B: int, steps: int, warmup: int, local_rank: int, 
     # the other two routes of the linears, device-timed the same way: the tcgen05 MMQ (TMEM accumulators, one tile per
     # k-block) and the reference's own fp16-weight arithmetic; reported beside the default, not as the value
     others = {}
-    for name, kw in (("q8_tcgen05_mmq", dict(linears="q8", mmq="tc")), ("f16_weights_fp16_mma", dict(linears="f16"))):
+    for name, kw in ((("q8_tcgen05_mmq", dict(linears="q8", mmq="tc")), ("f16_weights_fp16_mma", dict(linears="f16"))) if routes else ()):
         b2 = engine.Batched(m, B, **kw)
         b2.kc.copy_(bm.kc)
         b2.vc.copy_(bm.vc)
@@ -692,7 +692,8 @@ def run_other_workload(args, local_rank: int) -> None:
         print(json.dumps(bench_prefill(model, cfg, args.steps, args.warmup, local_rank, torch, measure_i8_peak(torch))), flush=True)
         return
     B = 8 if args.workload == "batched8" else 32
-    print(json.dumps(bench_batched(model, cfg, B, args.steps, args.warmup, local_rank, torch, peaks, peak_kind)), flush=True)
+    print(json.dumps(bench_batched(model, cfg, B, args.steps, args.warmup, local_rank, torch, peaks, peak_kind,
+                                   routes=not args.profile)), flush=True)
 
 
 def bench_tp7b(args, rank: int, world: int, local_rank: int, torch, dist) -> dict:

@@ -222,7 +222,7 @@ int q4b_gemv_q4_0_f16mma(const void* Wt, const void* St, const void* X, void* Y,
  * site: the linears of Batched.step, scripts/qwen_batched_decode.py:156-187, with the block arithmetic of the
  * reference's int8 MMQ, lab/qwen_batched.py:1237-1243: exact int32 dot per 32-weight block by mma.sync.m16n8k32.s8 with
  * the magic constant planted in the accumulator, then acc += d_w * d_x * float(dot) in fp32, blocks in ascending k
- * within a k group).  Epilogues STORE / BIASF / RESID / SWIGLU / LOGITS; K a multiple of 32; xq int8 [P, K] 8-byte
+ * within a k group).  Epilogues STORE / BIASF / RESID / SWIGLU / SWIGLU_Q8 (unsplit launches) / LOGITS; K a multiple of 32; xq int8 [P, K] 16-byte
  * aligned, xd fp16 [P, K / 32].  Results equal q4b_mmq_q4_0_q8_1 up to the fp32 summation order over k groups. */
 int q4b_mmq_q4_0_q8_1_mma(const void* Wt, const void* St, const void* xq, const void* xd, void* Y, const void* AUX, int N, int K,
                           int P, int epilogue, int ldy, uint32_t* status, q4b_stream_t stream);

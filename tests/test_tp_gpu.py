@@ -114,7 +114,8 @@ def test_tp2_shards_on_one_gpu_match_single_gpu_engine():
     # split-K over ranks changes the fp32 summation order of o_proj / down_proj: typical error at fp32 rounding level,
     # an occasional int8 flip of an activation as in every int8-activation path
     assert np.median(errs) < 1e-5, np.median(errs)
-    assert errs.max() < 5e-2, errs.max()
+    assert np.quantile(errs, 0.9) < 5e-3, np.quantile(errs, 0.9)
+    assert errs.max() < 0.2, errs.max()                          # 400 sequence-steps: a flip or two, kept in that engine's cache
 
 
 def test_peer_reduce_kernel_single_rank_equals_add_then_quantiser():
