@@ -320,6 +320,7 @@ class Batched:
         # operations per output and k-block on the CUDA cores either way, but register accumulators have no per-tile
         # retirement latency; measured faster up to MMQ_MMA_MAX_ROWS sequences
         self.mmq_mma = mmq == "mma" or (mmq == "auto" and B <= MMQ_MMA_MAX_ROWS)
+        self.attn_cached = self.attn_cached and self.mmq_mma   # mmq="tc" keeps the whole earlier route (for A/B): fused-quantiser attention
         if self.mmq_mma:
             # (the quantisers stay separate launches: run inside the o_proj / down_proj launches instead, through
             # QB.quant_gemm8_mma, every CTA requantises its K window after the dependency wait, and the step was slower:

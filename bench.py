@@ -315,13 +315,14 @@ def bench_gemv_config1(torch, peaks, peak_kind) -> dict:
             "e2e": {"value": b / e2e_us / 1e3, "unit": "GB/s", "us_per_call": e2e_us, "h2d_bytes_per_step": k * 4, "d2h_bytes_per_step": n * 4}}
 
 
-def bench_batched(model, cfg, B: int, steps: int, warmup: int, local_rank: int, torch, peaks, peak_kind, routes: bool = True) -> dict:
+def bench_batched(model, cfg, B: int, steps: int, warmup: int, local_rank: int, torch, peaks, peak_kind, routes: bool = True,
+                  mmq: str = "auto") -> dict:
     """Batched decode at B concurrent sequences, each with a 1024-token KV context (Q8_1 activations, int8 MMQ)."""
     synth = importlib.import_module("3080lab_b200.synth")
     engine = importlib.import_module("3080lab_b200.engine")
     ctx, gen = 1024, min(steps, 128)
     m = engine.FusedQwen(model, max_len=ctx + 256, device=f"cuda:{local_rank}")
-    bm = engine.Batched(m, B)
+    bm = engine.Batched(m, B, mmq=mmq)
     bm.kc.normal_()                                   # a 1024-token KV context per sequence (N(0,1) fp16, as the
     bm.vc.normal_()                                   # reference's decode A/B harness fills it, scripts/decode_ab.py:56-58)
     bm.pos.fill_(ctx)
@@ -385,7 +386,8 @@ def bench_batched(model, cfg, B: int, steps: int, warmup: int, local_rank: int, 
         "warmup": warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "int8 x int4 -> int32, fp32 scaling", "data": "synthetic",
         "config": {"workload": f"qwen2.5-1.5b-shape batched decode, {B} sequences, 1024-token KV context, Q8_1 x Q4_0 MMQ",
-                   "linears": "Q8_1 activations, exact int32 block dots by mma.sync.m16n8k32.s8 with register accumulators",
+                   "linears": "Q8_1 activations, exact int32 block dots by " + ("tcgen05.mma.kind::i8 with TMEM accumulators" if mmq == "tc"
+                                                                                 else "mma.sync.m16n8k32.s8 with register accumulators"),
                    "l2": "1.2 GB of weights + KV streamed per step, larger than L2"},
         "other_routes": others,
         "roofline": {"bound": "hbm", "kernel": "whole step", "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s",
@@ -696,7 +698,7 @@ def run_other_workload(args, local_rank: int) -> None:
         return
     B = 8 if args.workload == "batched8" else 32
     print(json.dumps(bench_batched(model, cfg, B, args.steps, args.warmup, local_rank, torch, peaks, peak_kind,
-                                   routes=not args.profile)), flush=True)
+                                   routes=not args.profile and args.mmq == "auto", mmq=args.mmq)), flush=True)
 
 
 def bench_tp7b(args, rank: int, world: int, local_rank: int, torch, dist) -> dict:
@@ -828,6 +830,9 @@ def main() -> None:
                     choices=["decode_b1", "gemv_ffn_up", "batched8", "batched32", "prefill2048", "tp7b"],
                     help="decode_b1 is the benchmark (it carries the others under \"sub\"); the others run one configuration "
                          "alone; tp7b is the tensor-parallel 7B configuration (any --gpus, under torch.distributed.run)")
+    ap.add_argument("--mmq", default="auto", choices=["auto", "tc"],
+                    help="batched8 / batched32 alone: the int8 MMQ of the linears; tc = the tcgen05 kernel with TMEM accumulators "
+                         "(and the streaming attention with the quantiser fused in) instead of the default register-accumulator one")
     ap.add_argument("--tp-reduce", default="peer", choices=["peer", "nccl"],
                     help="tp7b: the reduction after o_proj / down_proj: the library's fused peer-memory kernel or NCCL")
     ap.add_argument("--cuda-core", action="store_true", help="linears on the CUDA-core GEMV instead of the tensor-core kernels")
