@@ -106,6 +106,12 @@ __host__ __device__ __forceinline__ size_t x_pitch(int cap) { return (size_t)(ca
 // rows x 32 bytes) fall into distinct banks
 __host__ __device__ __forceinline__ size_t xq_pitch(int cap) { return ((size_t)cap * 32 + 127) / 128 * 128 + 32; }
 
+// bytes of the region that holds the weight slab during the main loop and the partial-sum tiles after it
+__host__ __device__ __forceinline__ size_t slab_region(int cap, int nt) {
+  const size_t slab = (size_t)cap * (2048 + 256), part = (size_t)(nt == 1 ? 4 : 1) * nt * 8 * PSTR * sizeof(float);
+  return ((slab > part ? slab : part) + 127) / 128 * 128;
+}
+
 constexpr int MODE_F16 = 0, MODE_Q8 = 1, MODE_Q8F = 2;   // Q8F: Q8 arithmetic, fp16 activations quantised inside
 
 // MODE_F16: fp16 activations, weights dequantised to fp16 (the reference's batched-decode GEMV).
@@ -131,9 +137,18 @@ __global__ void __launch_bounds__(GT, NT <= 2 ? 2 : 1) gemv_f16mma_kernel(const 
   const size_t xp = Q8 ? xq_pitch(cap) : x_pitch(cap);
   uint8_t* slabW = smem;                                  // [k-block][128 rows][16 bytes]
   uint8_t* slabS = slabW + (size_t)cap * 2048;            // [k-block][128 rows] fp16
-  uint8_t* xs = slabS + (size_t)cap * 256;                // [8 NT rows][pitch]: the K window of X (fp16, or int8 permuted)
+  uint8_t* xs = smem + slab_region(cap, NT);              // [8 NT rows][pitch]: the K window of X (fp16, or int8 permuted)
   float* dxs = reinterpret_cast<float*>(xs + (size_t)NT * 8 * xp);   // MODE_Q8: [k-block][8 NT] block scales / 16 as fp32
-  float* P = dxs + (Q8 ? (size_t)cap * NT * 8 : 0);   // [8 NT columns][PSTR]: this CTA's partial sums
+  // The partial-sum tiles [8 NT columns][PSTR] live over the weight slab, which is dead once the main loop is done (the
+  // slab region is sized for whichever is larger): 17 KB less per CTA at 8 rows, which is what lets gate/up (124 KB) and
+  // down (95 KB) share an SM, so that down's weight copies run under gate/up.  The receive buffer of the K-slice reduction
+  // is written by PEERS while this CTA may still be in its loop, so it keeps a region of its own.
+  // Measured per mode at 8 rows: the int8 step gains 5 % from it (1192 -> 1130 us); the fp16-weight step LOSES 18 % (1040 ->
+  // 1230 us: its down launch, then two CTAs per SM, takes 9.8 instead of 7.1 us), so that mode keeps tiles of its own.
+  // (The maximum shared-memory carve-out on these kernels was measured too: slower in both modes.)
+  float* recv = dxs + (Q8 ? (size_t)cap * NT * 8 : 0);    // [rank][column][maxp] float2
+  float* P = Q8 ? reinterpret_cast<float*>(smem)
+                : recv + (a.ksplit > 1 ? (size_t)NT * 8 * (ROWS / 2 + 8) * 2 : 0);
 
   // window `win` covers k-blocks kb0 + win cap .. of this CTA's slice; lane c of warp 0 owns weight chunk c
   auto issue_weights = [&](int win) {
@@ -403,7 +418,6 @@ __global__ void __launch_bounds__(GT, NT <= 2 ? 2 : 1) gemv_f16mma_kernel(const 
   // barrier publishes them, and the owner adds the ksplit contributions in rank order.
   int pr0 = 0, pr1 = ROWS / 2;
   const int maxp = (ROWS / 2 + a.ksplit - 1) / a.ksplit;  // pairs per slice, at most
-  float* recv = P + NPB * PB;                             // [rank][column][maxp] float2
   if (a.ksplit > 1) {
     pr0 = (ROWS / 2 * ks) / a.ksplit;
     pr1 = (ROWS / 2 * (ks + 1)) / a.ksplit;
@@ -496,10 +510,10 @@ __global__ void __launch_bounds__(GT, NT <= 2 ? 2 : 1) gemv_f16mma_kernel(const 
 
 size_t smem_for(int cap, int nt, int mode, int ks) {
   const size_t x = mode == MODE_F16 ? (size_t)nt * 8 * x_pitch(cap) : (size_t)nt * 8 * xq_pitch(cap) + (size_t)cap * nt * 8 * sizeof(float);   // Q8 and Q8F alike
-  // partial tiles (four with up to 8 columns, else one) + with K slices the receive buffer of their reduction (< 64 + 8 pairs)
-  size_t red = (size_t)(nt == 1 ? 4 : 1) * nt * 8 * PSTR * sizeof(float);
-  if (ks > 1) red += (size_t)nt * 8 * (ROWS / 2 + 8) * 2 * sizeof(float);
-  return (size_t)cap * (2048 + 256) + x + red;
+  // with K slices: the receive buffer of their reduction (< 64 + 8 pairs per column)
+  const size_t recv = ks > 1 ? (size_t)nt * 8 * (ROWS / 2 + 8) * 2 * sizeof(float) : 0;
+  const size_t own_tiles = mode == MODE_F16 ? (size_t)(nt == 1 ? 4 : 1) * nt * 8 * PSTR * sizeof(float) : 0;   // see the kernel
+  return slab_region(cap, nt) + x + recv + own_tiles;
 }
 
 // How many clusters of `ks` CTAs with `smem` bytes each can be resident at once (cached per device and configuration):

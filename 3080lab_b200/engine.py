@@ -282,7 +282,7 @@ class Batched:
     dequantised to fp16 on fp16 tensor-core MMAs (gemv_v2_source, lab/qwen_batched.py:467-641), 7 launches per layer
     (rmsnorm, qkv, attention, o, rmsnorm, gate/up, down: scripts/qwen_batched_decode.py:156-187)."""
 
-    def __init__(self, m: FusedQwen, B: int, linears: str = "q8", mmq: str = "auto"):
+    def __init__(self, m: FusedQwen, B: int, linears: str = "q8", mmq: str = "auto", attention: str = "auto"):
         if not 1 <= B <= 32:
             raise ValueError("1 <= B <= 32 sequences")
         if linears not in ("q8", "f16"):
@@ -320,7 +320,8 @@ class Batched:
         # operations per output and k-block on the CUDA cores either way, but register accumulators have no per-tile
         # retirement latency; measured faster up to MMQ_MMA_MAX_ROWS sequences
         self.mmq_mma = mmq == "mma" or (mmq == "auto" and B <= MMQ_MMA_MAX_ROWS)
-        self.attn_cached = self.attn_cached and self.mmq_mma   # mmq="tc" keeps the whole earlier route (for A/B): fused-quantiser attention
+        if attention == "streaming":                      # the earlier route: streaming kernel with the quantiser fused in
+            self.attn_cached = False
         if self.mmq_mma:
             # (the quantisers stay separate launches: run inside the o_proj / down_proj launches instead, through
             # QB.quant_gemm8_mma, every CTA requantises its K window after the dependency wait, and the step was slower:

@@ -322,7 +322,7 @@ def bench_batched(model, cfg, B: int, steps: int, warmup: int, local_rank: int, 
     engine = importlib.import_module("3080lab_b200.engine")
     ctx, gen = 1024, min(steps, 128)
     m = engine.FusedQwen(model, max_len=ctx + 256, device=f"cuda:{local_rank}")
-    bm = engine.Batched(m, B, mmq=mmq)
+    bm = engine.Batched(m, B, mmq=mmq, attention="streaming" if mmq == "tc" else "auto")   # --mmq tc: the whole earlier route
     bm.kc.normal_()                                   # a 1024-token KV context per sequence (N(0,1) fp16, as the
     bm.vc.normal_()                                   # reference's decode A/B harness fills it, scripts/decode_ab.py:56-58)
     bm.pos.fill_(ctx)
