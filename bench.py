@@ -727,7 +727,21 @@ def bench_tp7b(args, rank: int, world: int, local_rank: int, torch, dist) -> dic
                                 cfg.eps, cfg.rope_theta, cfg.tied_fp16_head)
     shard = tpm.synth_shard(cfg, rank % tp, tp, seed=0)
     reduce = args.tp_reduce if tp > 1 else "nccl"
-    eng = tpm.TPBatched(shard, B, ctx + 128, f"cuda:{local_rank}", group, reduce=reduce)
+    eng, why = None, ""
+    if reduce == "peer":
+        # the peer-memory reduction needs symmetric memory across the group; if any rank cannot set it up, every rank
+        # falls back to NCCL together (the choice is reported in config.collective)
+        try:
+            eng = tpm.TPBatched(shard, B, ctx + 128, f"cuda:{local_rank}", group, reduce="peer")
+        except Exception as ex:                              # noqa: BLE001 - reported, then the NCCL form is used
+            why = f"{type(ex).__name__}: {ex}"[:200]
+        flag = torch.tensor([1 if eng is not None else 0], device="cuda")
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        if int(flag.item()) == 0:
+            eng, reduce = None, "nccl"
+            torch.cuda.empty_cache()
+    if eng is None:
+        eng = tpm.TPBatched(shard, B, ctx + 128, f"cuda:{local_rank}", group, reduce=reduce)
     eng.kc.normal_()
     eng.vc.normal_()
     eng.pos.fill_(ctx)
@@ -796,7 +810,7 @@ def bench_tp7b(args, rank: int, world: int, local_rank: int, torch, dist) -> dic
                    "collective": "none" if tp == 1 else
                                  (f"own one-shot reduction of [64, {cfg.hidden}] fp32 over peer memory (plain NVLink loads), fused "
                                   f"with the residual add and the next RMSNorm + Q8_1" if reduce == "peer" else
-                                  f"NCCL all-reduce of [64, {cfg.hidden}] fp32") +
+                                  f"NCCL all-reduce of [64, {cfg.hidden}] fp32" + (f" (peer-memory reduction unavailable: {why})" if why else "")) +
                                  f" after o_proj and down_proj ({2 * cfg.layers} per step)",
                    "l2": "weights + KV streamed per step are larger than L2"},
         "roofline": {"bound": "hbm", "kernel": "whole step, per GPU", "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s",
