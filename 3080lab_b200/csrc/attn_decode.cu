@@ -634,7 +634,7 @@ int attn_decode_mma(const void*, const float*, const float*, const int64_t*, voi
                     cudaStream_t, void* xq = nullptr, void* xd = nullptr);
 bool attn_cached_fits(int NH, int NKV, int HD, int max_len);
 int attn_cached(const void*, const int64_t*, const void*, const void*, void*, int, int, int, float, cudaStream_t, int B = 1,
-                const float* cosT = nullptr, const float* sinT = nullptr);
+                const float* cosT = nullptr, const float* sinT = nullptr, void* xq = nullptr, void* xd = nullptr);
 
 // which kernel serves several sequences: 0 = the shared-memory-resident cached form where the context fits it (default),
 // 1 = always the streaming tensor-core kernel of attn_decode_mma.cu
@@ -710,6 +710,11 @@ int attn_decode_q8(const void* qkv, const float* cosT, const float* sinT, const 
   if (B < 2 || HD != 128 || NKV <= 0 || (NH % NKV) || NH / NKV > 8 || max_len <= 0) return Q4B_E_SHAPE;
   if (!qkv || !cosT || !sinT || !pos || !kc || !vc || !out || !xq || !xd || !aligned16(kc) || !aligned16(vc) || !aligned16(qkv))
     return fail(Q4B_E_ALIGN, "attn_decode_q8: null or misaligned pointer");
+  // the shared-memory-resident kernel where the context fits it (its combine step quantises 32-dimension slices), else the
+  // streaming kernel
+  if (g_batched_kernel == 0 && attn_cached_fits(NH, NKV, HD, max_len))
+    return attn_cached(qkv, pos, kc, vc, out, NH, NKV, max_len, scale, st, B, cosT, sinT, xq, xd);
+  if (((NH / NKV) * HD) % 256) return Q4B_E_SHAPE;
   return attn_decode_mma(qkv, cosT, sinT, pos, kc, vc, out, B, NH, NKV, max_len, scale, st, xq, xd);
 }
 

@@ -81,7 +81,8 @@ __device__ __forceinline__ uint4 rotate8(uint4 own, uint4 other, int cc, const f
 template <bool ROPE>
 __global__ void __launch_bounds__(AT, 2) attn_cached_kernel(const __half* qkv, const int64_t* posp, __half* kc, __half* vc,
                                                             __half* out, int NH, int NKV, int max_len, int cap, float scale_log2e,
-                                                            unsigned long long* trace, const float* cosT, const float* sinT) {
+                                                            unsigned long long* trace, const float* cosT, const float* sinT,
+                                                            int8_t* xq, __half* xd) {
   extern __shared__ __align__(16) uint8_t sm[];
   __shared__ float s_cs[64], s_sn[64];
   {
@@ -90,14 +91,19 @@ __global__ void __launch_bounds__(AT, 2) attn_cached_kernel(const __half* qkv, c
     posp += b;
     kc += b * (size_t)NKV * max_len * HD;
     vc += b * (size_t)NKV * max_len * HD;
-    out += b * (size_t)NH * HD;
+    if (out) out += b * (size_t)NH * HD;
+    if (xq) {
+      xq += b * (size_t)NH * HD;
+      xd += b * (size_t)NH * (HD / 32);
+    }
   }
+  const bool q8out = xq != nullptr;                  // combine in 32-dimension slices (CTAs 0..3) and quantise them
   uint8_t* sQ = sm;                                  // [16][PITCH]   q heads of the group (rows >= GRP zero)
   uint8_t* sK = sQ + 16 * PITCH;                     // [cap][PITCH]
   uint8_t* sV = sK + (size_t)cap * PITCH;            // [cap][PITCH]
   __shared__ float wmax[NW][MAXG], wsum[NW][MAXG];   // per warp and head: maximum score, sum of probabilities (base 2)
   // combiner: this CTA owns output dimensions 16 c .. 16 c + 15; every chunk pushes its share and its (max, sum) here
-  __shared__ __align__(16) float comb_o[NCL][MAXG][16];
+  __shared__ __align__(16) float comb_o[NCL][MAXG][32];   // [chunk][head][16 dims; 32 with the quantiser fused in]
   __shared__ float comb_ml[NCL][MAXG][2];
 
   const int t = threadIdx.x, warp = t >> 5, lane = t & 31, g = lane >> 2, tq = lane & 3;
@@ -274,7 +280,9 @@ __global__ void __launch_bounds__(AT, 2) attn_cached_kernel(const __half* qkv, c
     asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");   // pairs with the arrive at the top
     if (g < GRP) {
       uint32_t r_o;
-      asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r_o) : "r"((uint32_t)__cvta_generic_to_shared(&comb_o[c][g][0])), "r"(warp));
+      // owner of this warp's 16 dimensions: CTA `warp`, or with the quantiser fused in CTA warp / 2 (a Q8_1 block is 32)
+      asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r_o)
+                   : "r"((uint32_t)__cvta_generic_to_shared(&comb_o[c][g][q8out ? 16 * (warp & 1) : 0])), "r"(q8out ? warp >> 1 : warp));
 #pragma unroll
       for (int nt = 0; nt < 2; ++nt) {
         asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(r_o + (uint32_t)((8 * nt + 2 * tq) * 4)), "f"(o[nt][0]) : "memory");
@@ -299,6 +307,36 @@ __global__ void __launch_bounds__(AT, 2) attn_cached_kernel(const __half* qkv, c
   }
   cluster_sync_all();                                // every active chunk's partials are in the combiners
   stamp();                                           // 5: cluster barrier passed
+  if (q8out) {
+    // CTAs 0..3 own dimensions 32 c .. 32 c + 31 of every head: warp = head, lane = dimension = one Q8_1 block.  Same sums in
+    // the same chunk order as below, then the quantiser of quant_q8_1.cu on the rounded output.
+    if (c < 4) {
+      const int hl = t >> 5, dd = t & 31;
+      if (hl < GRP) {
+        float Mx = -INFINITY;
+#pragma unroll
+        for (int cc = 0; cc < NCL; ++cc) Mx = fmaxf(Mx, cc < nact ? comb_ml[cc][hl][0] : -INFINITY);
+        float ov = 0.f, L = 0.f;
+#pragma unroll
+        for (int cc = 0; cc < NCL; ++cc) {
+          const bool on = cc < nact;
+          const float w = exp2f((on ? comb_ml[cc][hl][0] : -INFINITY) - Mx);
+          L += (on ? comb_ml[cc][hl][1] : 0.f) * w;
+          ov += (on ? comb_o[cc][hl][dd] : 0.f) * w;
+        }
+        const __half y16 = __float2half_rn(ov / L);
+        const float y = __half2float(y16);
+        const float d = warp_max(fabsf(y)) / 127.f;
+        const int q = d > 0.f ? __float2int_rn(y / d) : 0;
+        const size_t at = (size_t)(kvh * GRP + hl) * HD + 32 * c + dd;
+        xq[at] = (int8_t)q;
+        if (dd == 0) xd[at >> 5] = __float2half_rn(d);
+        if (out) out[at] = y16;
+      }
+    }
+    stamp();
+    return;
+  }
   // chunk order, so the result does not depend on timing; thread (head, dimension) of this CTA's 16 dimensions
   if (t < MAXG * 16) {
     const int hl = t >> 4, dd = t & 15;
@@ -337,10 +375,10 @@ bool attn_cached_fits(int NH, int NKV, int HD, int max_len) {
 // B = 1 with cosT == nullptr: the cached form (q rotated, row appended by the caller).  cosT / sinT given: RoPE and the
 // append happen inside, for B sequences (qkv [B, (NH + 2 NKV) 128], pos [B], cache [B, NKV, max_len, 128], out [B, NH 128]).
 int attn_cached(const void* qkv, const int64_t* pos, const void* kc, const void* vc, void* out, int NH, int NKV, int max_len,
-                float scale, cudaStream_t st, int B, const float* cosT, const float* sinT) {
+                float scale, cudaStream_t st, int B, const float* cosT, const float* sinT, void* xq, void* xd) {
   if (!attn_cached_fits(NH, NKV, HD, max_len)) return fail(Q4B_E_SHAPE, "attn_decode_cached: needs head_dim 128, NH/NKV <= 8, max_len <= 2048");
   if (B < 1 || B > 65535 || (B > 1 && !cosT)) return fail(Q4B_E_SHAPE, "attn_decode_cached: 1 <= B, several sequences need the rotation tables");
-  if (!qkv || !pos || !kc || !vc || !out || !aligned16(qkv) || !aligned16(kc) || !aligned16(vc) || (cosT && !sinT))
+  if (!qkv || !pos || !kc || !vc || (!out && !xq) || (xq && !xd) || !aligned16(qkv) || !aligned16(kc) || !aligned16(vc) || (cosT && !sinT))
     return fail(Q4B_E_ALIGN, "attn_decode_cached: null or misaligned pointer");
   int cap = ((max_len + NCL - 1) / NCL + 15) & ~15;  // positions per CTA at the longest context
   if (cap < 128) cap = 128;                          // the K tile's space later holds the per-warp partials (32 KB)
@@ -358,10 +396,10 @@ int attn_cached(const void* qkv, const int64_t* pos, const void* kc, const void*
   cudaError_t e;
   if (cosT)
     e = launch_pdl_cluster(attn_cached_kernel<true>, dim3(NCL, NKV, B), dim3(AT), smem, st, NCL, 1, (const __half*)qkv, pos, kcw, vcw,
-                           (__half*)out, NH, NKV, max_len, cap, scale_log2e, trace, cosT, sinT);
+                           (__half*)out, NH, NKV, max_len, cap, scale_log2e, trace, cosT, sinT, (int8_t*)xq, (__half*)xd);
   else
     e = launch_pdl_cluster(attn_cached_kernel<false>, dim3(NCL, NKV, B), dim3(AT), smem, st, NCL, 1, (const __half*)qkv, pos, kcw, vcw,
-                           (__half*)out, NH, NKV, max_len, cap, scale_log2e, trace, cosT, sinT);
+                           (__half*)out, NH, NKV, max_len, cap, scale_log2e, trace, cosT, sinT, (int8_t*)xq, (__half*)xd);
   return check_launch(e, "attn_decode_cached");
 }
 

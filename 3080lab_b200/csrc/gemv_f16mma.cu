@@ -319,6 +319,8 @@ __global__ void __launch_bounds__(GT, NT <= 2 ? 2 : 1) gemv_f16mma_kernel(const 
           for (int n = 0; n < NT; ++n) {
             int d[4];
             mma_s8_magic(d, eA, eB, oA, oB, xb[n].x, xb[n].y);
+            // (two-wide fp32 instructions for these - half the issue slots at the same lane throughput - were measured:
+            // gate/up at 32 rows 15.0 against 14.5 us, at 8 rows 6.6 against 6.8; not kept)
             c[m][n][0] = fmaf(dw[2 * m] * dx[n].x, __int_as_float(d[0]) - 12582912.f, c[m][n][0]);
             c[m][n][1] = fmaf(dw[2 * m] * dx[n].y, __int_as_float(d[1]) - 12582912.f, c[m][n][1]);
             c[m][n][2] = fmaf(dw[2 * m + 1] * dx[n].x, __int_as_float(d[2]) - 12582912.f, c[m][n][2]);

@@ -320,14 +320,26 @@ class Batched:
         # operations per output and k-block on the CUDA cores either way, but register accumulators have no per-tile
         # retirement latency; measured faster up to MMQ_MMA_MAX_ROWS sequences
         self.mmq_mma = mmq == "mma" or (mmq == "auto" and B <= MMQ_MMA_MAX_ROWS)
-        if attention == "streaming":                      # the earlier route: streaming kernel with the quantiser fused in
+        if attention not in ("auto", "streaming"):
+            raise ValueError("attention: 'auto' (shared-memory-resident kernel where the context fits) or 'streaming'")
+        self.attention = attention
+        if attention == "streaming":
             self.attn_cached = False
         if self.mmq_mma:
             # (the quantisers stay separate launches: run inside the o_proj / down_proj launches instead, through
             # QB.quant_gemm8_mma, every CTA requantises its K window after the dependency wait, and the step was slower:
             # 1230 against 1188 us at 8 sequences, 2346 against 2094 us at 32)
             self._fuse_gu = None                          # SwiGLU + quantiser in the gate/up epilogue where it is unsplit
-        self.launches_per_step = 1 + (9 if linears == "q8" else 7) * c.layers + 3
+        self._attn_fused = True                           # settled by the first step, like _fuse_gu
+
+    @property
+    def launches_per_step(self) -> int:
+        """Kernel launches of one step: embed + per layer 7 (both quantisers of the int8 route fused into their producers;
+        one more for each that is a launch of its own) + final norm, head, argmax."""
+        per_layer = 7
+        if self.linears == "q8":
+            per_layer += (0 if self._fuse_gu else 1) + (0 if self._attn_fused else 1)
+        return 1 + per_layer * self.m.cfg.layers + 3
 
     def gemm8(self, pair, N, Kdim, Y, aux, epi, ldy, xq=None, xd=None):
         Wt, St = self.m.packed[id(pair[0])]
@@ -359,6 +371,16 @@ class Batched:
         K.finish(self.logits, self.tok, self.pos, self.head_ws)
 
     def step(self) -> None:
+        if self.attention == "streaming":                 # process-wide selector: set for the launches of this step only
+            _ffi.call("q4b_attn_batched_kernel", 1)
+            try:
+                self._step()
+            finally:
+                _ffi.call("q4b_attn_batched_kernel", 0)
+        else:
+            self._step()
+
+    def _step(self) -> None:
         if self.linears == "f16":
             return self._step_f16()
         m, c, B = self.m, self.m.cfg, self.B
@@ -367,8 +389,13 @@ class Batched:
         for i, L in enumerate(m.L):
             QB.rmsnorm_q8(self.h, L["ln1"], self.xq, self.xd, c.eps)
             self.gemm8(L["qkv"], c.qkv_rows, H, self.qkv, L["qkv_b"], "biasf", c.qkv_rows)
-            if self.attn_cached or not K.attn_q8(self.qkv, m.cos, m.sin, self.pos, self.kc[i], self.vc[i], self.att, self.xq,
-                                                  self.xd, c.n_heads, c.n_kv_heads, c.head_dim, m.max_len, m.scale):
+            # attention with the Q8_1 quantiser of its output fused in (either kernel has one); False = no fused form here
+            # With the shared-memory-resident kernel the fused quantiser pays only for few sequences (8: 1139 -> 1130 us
+            # per step; 32, two waves of CTAs: 1849 -> 1920 us), so beyond 8 the quantiser stays a launch of its own there.
+            self._attn_fused = (not self.attn_cached or B <= 8) and K.attn_q8(
+                self.qkv, m.cos, m.sin, self.pos, self.kc[i], self.vc[i], self.att, self.xq, self.xd, c.n_heads, c.n_kv_heads,
+                c.head_dim, m.max_len, m.scale)
+            if not self._attn_fused:
                 K.attn(self.qkv, m.cos, m.sin, self.pos, self.kc[i], self.vc[i], self.att, c.n_heads, c.n_kv_heads,
                        c.head_dim, m.max_len, m.scale, self.attn_ws)
                 QB.quant_q8(self.att, self.xq, self.xd)
