@@ -10,7 +10,8 @@ device, maximum over ranks.  Prints ONE JSON line on rank 0.
 The headline is batch 1; the same line carries, under "sub", the other configurations of the metric: at one GPU the
 single ffn_up GEMV (34 distinct weight buffers rotated inside one graph), batched decode at 8 and 32 sequences and the
 2048-token prefill; at N > 1 GPUs the tensor-parallel 7B configuration on the same ranks (TP = min(N, 4), replicas
-beyond).  `--workload X` runs one of them alone and prints its object as the line.
+beyond).  `--workload X` runs one of them alone and prints its object as the line.  The batched objects also carry, under
+"other_routes", the same step with the linears through the tcgen05 MMQ and through the reference's fp16-weight arithmetic.
 
 `--impl reference` times the reference's CPU implementation of the same step (its numpy dequantise-and-dot, restated
 in oracle/q4ref.py) on the host cores; each of its steps is a bounded sample of the workload (see `cpu_baseline`).
