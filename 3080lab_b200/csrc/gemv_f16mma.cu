@@ -1,12 +1,21 @@
-// Batched-decode Q4_0 GEMV on fp16 tensor-core MMAs: up to 32 activation rows against weights dequantised to fp16.
+// Batched-decode Q4_0 linear for 1 .. 32 activation rows on mma.sync tensor-core instructions, in two arithmetics:
 //
-//   Y[b, m] = epilogue( sum_k w16[m, k] * X[b, k] ),    w16[m, k] = round_fp16( (q4[m, k] - 8) * d[m, k / 32] )
+// MODE_Q8 (the int8 route of the batched decode step): Q8_1 activations, the block arithmetic of the reference's MMQ
+//   (gemm_q4i8_ms_source, lab/qwen_batched.py:1237-1243):
+//     Y[b, m] = epilogue( sum_blocks (d_w[m, blk] * d_x[b, blk]) * dot[m, b, blk] ),   dot = exact int32 over 32 weights
+//   mma.sync.m16n8k32.s8 with the accumulator started from 0x4B400000, so that float(dot) is one subtraction; the scale
+//   product and the fused multiply-add per output and block run on the CUDA cores, accumulators stay in registers.
+//   (The tcgen05 form of the same arithmetic, mmq_stream.cu, needs one accumulator tile per block and those retire one per
+//   177 clocks; at these row counts the register form is faster.)
 //
-// This is the arithmetic of the reference's batched-decode linears (gemv_v2_source, lab/qwen_batched.py:467-641):
-// nibbles become exact fp16 integers through the 0x6400 exponent trick, are multiplied by the fp16 block scale with ONE
-// rounding to fp16, and meet the fp16 activations in mma.sync.m16n8k16 with fp32 accumulation; epilogues as
-// lab/qwen_batched.py:251-267.  The rounding of d * (q - 8) to fp16 is what separates this mode from the exact block-dot
-// kernels; tests compare against an oracle that rounds the weights the same way.
+// MODE_F16: fp16 activations against weights dequantised to fp16, the reference's own batched-decode GEMV
+//   (gemv_v2_source, lab/qwen_batched.py:467-641):
+//     Y[b, m] = epilogue( sum_k w16[m, k] * X[b, k] ),    w16[m, k] = round_fp16( (q4[m, k] - 8) * d[m, k / 32] )
+//   nibbles become exact fp16 integers through the 0x6400 exponent trick, are multiplied by the fp16 block scale with ONE
+//   rounding to fp16, and meet the fp16 activations in mma.sync.m16n8k16 with fp32 accumulation.  That rounding is what
+//   separates this mode from the exact block-dot kernels; tests compare against an oracle that rounds the same way.
+//
+// Epilogues as lab/qwen_batched.py:251-267 (+ swiglu_q8, :1363-1396, in MODE_Q8).
 //
 // Shape of the kernel (B200), shared with the batch-1 GEMV of gemv_mma.cu:
 //   * one CTA = one 128-row tile x one K slice of the tile-packed layout (pack.cu): its weights are ONE contiguous range,
