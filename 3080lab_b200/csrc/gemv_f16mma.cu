@@ -195,17 +195,29 @@ __global__ void __launch_bounds__(GT, NT <= 2 ? 2 : 1) gemv_f16mma_kernel(const 
   __syncthreads();
   pdl_wait();                                             // X comes from the previous kernel
   if (MODE == MODE_F16 && warp == 1) issue_x(0);
-  // MODE_Q8: the int8 rows arrive by bulk copy like the fp16 ones (one round trip; as plain loads in a loop they were three
-  // dependent ones), the block scales by plain loads that are in flight meanwhile (converted to fp32 with the factor 1/16
-  // of the nibble expansion).  `permute_q8`, after the copies have landed, reorders the bytes of each group of eight in
-  // place to (k0, k2, k4, k6 | k1, k3, k5, k7), the order the expansion gives the weights.
+  // MODE_Q8: up to 16 rows the int8 rows arrive by bulk copy like the fp16 ones (one round trip; as plain loads in a loop
+  // they were three dependent ones) and `permute_q8`, after the copies have landed, reorders the bytes of each group of
+  // eight in place to (k0, k2, k4, k6 | k1, k3, k5, k7), the order the expansion gives the weights.  With more rows the
+  // in-place pass costs more than it saves (down at 32 rows 12.9 against 12.2 us), so they keep plain loads that reorder on
+  // the way.  The block scales come by plain loads either way (fp32, with the factor 1/16 of the nibble expansion).
+  constexpr bool XQ_BULK = NT <= 2;
   auto stage_q8 = [&](int win) {
     const int wkb = min(cap, nkb - win * cap);
     const size_t kbase = (size_t)kb0 + (size_t)win * cap;
-    if (warp == 1) {
-      if (lane == 0) tc::mbar_expect_tx(&bar_x, (uint32_t)a.B * (uint32_t)wkb * 32u);
-      __syncwarp();
-      if (lane < a.B) bulk_g2s(xs + (size_t)lane * xp, a.XQ + (size_t)lane * a.K + kbase * 32, (uint32_t)wkb * 32u, &bar_x);
+    if (XQ_BULK) {
+      if (warp == 1) {
+        if (lane == 0) tc::mbar_expect_tx(&bar_x, (uint32_t)a.B * (uint32_t)wkb * 32u);
+        __syncwarp();
+        if (lane < a.B) bulk_g2s(xs + (size_t)lane * xp, a.XQ + (size_t)lane * a.K + kbase * 32, (uint32_t)wkb * 32u, &bar_x);
+      }
+    } else {
+      for (int i = t; i < a.B * wkb * 4; i += GT) {         // plain 8-byte loads, reordered on the way
+        const int col = i / (wkb * 4), r = i - col * (wkb * 4);
+        const uint2 v = *reinterpret_cast<const uint2*>(a.XQ + (size_t)col * a.K + kbase * 32 + (size_t)r * 8);
+        uint2 o;
+        tc::permute_bytes(v.x, v.y, o.x, o.y);
+        *reinterpret_cast<uint2*>(xs + (size_t)col * xp + (size_t)r * 8) = o;
+      }
     }
     for (int i = t; i < a.B * wkb; i += GT) {
       const int col = i / wkb, kb = i - col * wkb;
@@ -292,10 +304,10 @@ __global__ void __launch_bounds__(GT, NT <= 2 ? 2 : 1) gemv_f16mma_kernel(const 
     // measured slower: gate/up at 8 rows 7.9 us against 7.0.)
     if (lane == 0) {
       for (int ch = warp; ch * CHK < wkb; ch += GT / 32) ok = mbar_wait_n(&bar_load[ch], parity, a.wait_limit) && ok;
-      if (MODE != MODE_Q8F && warp == GT / 32 - 1) ok = mbar_wait_n(&bar_x, parity, a.wait_limit) && ok;
+      if ((MODE == MODE_F16 || (MODE == MODE_Q8 && XQ_BULK)) && warp == GT / 32 - 1) ok = mbar_wait_n(&bar_x, parity, a.wait_limit) && ok;
     }
     __syncthreads();
-    if (MODE == MODE_Q8) {
+    if (MODE == MODE_Q8 && XQ_BULK) {
       permute_q8(wkb);
       __syncthreads();
     }
