@@ -55,6 +55,8 @@ struct PrefillArgs {
   const void* AUX;
   uint32_t* status;
   int N, K, P, epi, ldy;
+  float* Y2;           // split launch: where the second K half stores its sums, fp32 [P, ldy]
+  int kb_split;        // split launch: first k-block of the second half (a multiple of 8)
   // fused RoPE + K/V append (Q4B_EPI_BIASF_ROPE_KV): tokens of ONE sequence at positions pos0 .., cache fp16 [NKV, max_len, 128]
   const float* cosT;
   const float* sinT;
@@ -130,10 +132,14 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const __grid
   uint8_t* stage = slabS + (size_t)WB * WBATCH_S;          // [SB][4608]
 
   const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
-  const int KB = a.K >> 5, NBATCH = KB >> 3;
+  // K range of this CTA: all of K, or with a split launch (gridDim.z = 2) the k-blocks below / from a.kb_split.  The second
+  // half stores its sums as fp32 into Y2 instead of adding them to Y; whoever reads Y next adds Y2 (in that fixed order).
+  const int KBT = a.K >> 5;
+  const int kb_lo = blockIdx.z ? a.kb_split : 0;
+  const int KB = (gridDim.z == 2 ? (blockIdx.z ? KBT - a.kb_split : a.kb_split) : KBT), NBATCH = KB >> 3;
   const int row_tile = blockIdx.x, tok_tile = blockIdx.y;
-  const size_t wbase = (size_t)row_tile * KB;              // k-block index of this row tile in the packed arrays
-  const uint8_t* xbase = a.Xt + (size_t)tok_tile * KB * STAGE_BYTES;
+  const size_t wbase = (size_t)row_tile * KBT + kb_lo;     // k-block index of this row tile in the packed arrays
+  const uint8_t* xbase = a.Xt + ((size_t)tok_tile * KBT + kb_lo) * STAGE_BYTES;
 
   if (warp == 0) {
     tc::tmem_alloc(&tmem_base_s, 512);
@@ -354,7 +360,10 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const __grid
         switch (a.epi) {
           case Q4B_EPI_STORE: reinterpret_cast<__half*>(a.Y)[base + row] = __float2half_rn(v); break;
           case Q4B_EPI_BIASF: reinterpret_cast<__half*>(a.Y)[base + row] = __float2half_rn(v + bias); break;
-          case Q4B_EPI_RESID: reinterpret_cast<float*>(a.Y)[base + row] += v; break;
+          case Q4B_EPI_RESID:
+            if (blockIdx.z) a.Y2[base + row] = v;
+            else reinterpret_cast<float*>(a.Y)[base + row] += v;
+            break;
           case Q4B_EPI_LOGITS: reinterpret_cast<float*>(a.Y)[base + row] = v; break;
           case Q4B_EPI_SWIGLU:
             if ((r & 1) == 0) reinterpret_cast<__half*>(a.Y)[base + (row >> 1)] = __float2half_rn(v / (1.f + __expf(-v)) * partner);
@@ -375,9 +384,10 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const __grid
 
 size_t q8_tiled_bytes(int P, int K) { return (size_t)((P + NTOK - 1) / NTOK) * (size_t)(K / 32) * STAGE_BYTES; }
 
+// Y2 != nullptr (RESID only): the launch is split along K over gridDim.z = 2; Y += first half, Y2 = second half.
 int mmq_prefill(const void* Wt, const void* St, const void* Xt, void* Y, const void* AUX, int N, int K, int P, int epilogue,
                 int ldy, uint32_t* status, cudaStream_t st, const float* cosT, const float* sinT, void* kc, void* vc, int NH,
-                int NKV, int max_len, int pos0) {
+                int NKV, int max_len, int pos0, float* Y2) {
   if (N <= 0 || P <= 0 || K <= 0 || (K % 256)) return fail(Q4B_E_SHAPE, "mmq_prefill: N, P > 0 and K a positive multiple of 256 required");
   if (epilogue < Q4B_EPI_STORE || epilogue > Q4B_EPI_BIASF_ROPE_KV) return fail(Q4B_E_ARG, "mmq_prefill: unknown epilogue");
   if (epilogue == Q4B_EPI_SWIGLU && (N % 2)) return fail(Q4B_E_SHAPE, "mmq_prefill: swiglu needs an even row count");
@@ -415,7 +425,14 @@ int mmq_prefill(const void* Wt, const void* St, const void* Xt, void* Y, const v
   a.NKV = NKV;
   a.max_len = max_len;
   a.pos0 = pos0;
+  a.Y2 = Y2;
+  a.kb_split = 0;
   dim3 grid((N + 127) / 128, (P + NTOK - 1) / NTOK);
+  if (Y2) {
+    if (epilogue != Q4B_EPI_RESID || K < 512 || !aligned16(Y2)) return fail(Q4B_E_SHAPE, "mmq_prefill: a K-split launch needs the resid epilogue and K >= 512");
+    a.kb_split = ((K / 32 / 2 + 7) / 8) * 8;             // halves in whole batches of 8 k-blocks
+    grid.z = 2;
+  }
   return check_launch(launch_pdl(mmq_prefill_kernel, grid, dim3(PF_THREADS), PF_SMEM, st, a), "mmq_prefill");
 }
 

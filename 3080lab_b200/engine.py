@@ -487,11 +487,14 @@ class Prefill:
     Q8_1 -> MMQ o (+residual) -> RMSNorm+Q8_1 -> MMQ gate/up (+SwiGLU) -> Q8_1 -> MMQ down (+residual).  Writes the KV
     cache of the `FusedQwen` it wraps, so decode continues from the prefilled state."""
 
-    def __init__(self, m: FusedQwen, P: int, fused: bool = True):
+    def __init__(self, m: FusedQwen, P: int, fused: bool = True, split_k=None):
         """fused: the reference's seven launches per layer (scripts/qwen_prefill.py:196-246): the QKV GEMM rotates and
         appends K/V (`biasf_kv`), the flash kernel emits the o-projection's Q8_1 input (`q8`), the gate/up GEMM emits the
         down GEMM's (`swiglu_q8`).  fused=False keeps those three steps as separate launches (ten per layer); both give
-        the same bits."""
+        the same bits.
+        split_k: launch o_proj and down_proj as two half-K CTAs per output tile (the second half lands in `h2` and is added
+        by the next RMSNorm + Q8_1 launch).  Default: on where their grid would otherwise fill the SMs in a ragged second
+        round (12 row tiles x P / 128 token tiles between one and two times the SM count)."""
         c = m.cfg
         if not m.tensor_core or c.hidden % 256 or c.q_rows % 256 or c.ffn % 256 or c.head_dim != 128:
             raise ValueError("the prefill path needs tile-packed weights (K multiples of 256) and head_dim 128")
@@ -505,40 +508,64 @@ class Prefill:
         self.xt = QB.q8_tiled_buffer(P, max(c.hidden, c.q_rows), dv)
         self.xt2 = QB.q8_tiled_buffer(P, c.ffn, dv)          # the down GEMM's input, written while gate/up reads xt
         self.status = QB.Status(dv)
-        self.launches_per_chunk = 1 + (7 if fused else 10) * c.layers
+        tiles = ((c.hidden + 127) // 128) * ((P + 127) // 128)
+        sms = torch.cuda.get_device_properties(dv).multi_processor_count
+        self.split_k = (sms < tiles < 2 * sms) if split_k is None else bool(split_k)
+        self.h2 = torch.zeros(P, c.hidden, dtype=f32, device=dv) if self.split_k else None
+        self.launches_per_chunk = 1 + (7 if fused else 10) * c.layers + (1 if self.split_k else 0)
 
     def gemm8(self, pair, xt, N, Kdim, Y, aux, epi, ldy):
         Wt, St = self.m.packed[id(pair[0])]
         QB.gemm8_prefill(Wt, St, xt, Y, aux, N, Kdim, self.P, epi, ldy, self.status)
 
+    def resid(self, pair, xt, Kdim):
+        """h += linear(xt): one launch; with split_k the second K half goes to h2 and `self._pending` records that h2
+        still has to be added (the next `norm_q8` does it)."""
+        Wt, St = self.m.packed[id(pair[0])]
+        H = self.m.cfg.hidden
+        if self.split_k and Kdim >= 512:
+            QB.gemm8_prefill_resid_ksplit(Wt, St, xt, self.h, self.h2, H, Kdim, self.P, H, self.status)
+            self._pending = True
+        else:
+            QB.gemm8_prefill(Wt, St, xt, self.h, None, H, Kdim, self.P, "resid", H, self.status)
+
+    def norm_q8(self, w):
+        """RMSNorm + tiled Q8_1 of h into xt, completing h with a pending second K half first."""
+        if self._pending:
+            QB.rmsnorm_q8_tiled_add(self.h, self.h2, w, self.xt, self.m.cfg.eps)
+            self._pending = False
+        else:
+            QB.rmsnorm_q8_tiled(self.h, w, self.xt, self.m.cfg.eps)
+
     def chunk(self, pos0: int = 0) -> None:
         """One pass over the P tokens in self.tok at positions pos0 .. pos0 + P - 1."""
         m, c, H = self.m, self.m.cfg, self.m.cfg.hidden
         K.embed(m.embed, self.tok, self.h)
-        if self.fused:
-            for i, L in enumerate(m.L):
-                QB.rmsnorm_q8_tiled(self.h, L["ln1"], self.xt, c.eps)
+        self._pending = False
+        for i, L in enumerate(m.L):
+            self.norm_q8(L["ln1"])
+            if self.fused:
                 Wt, St = m.packed[id(L["qkv"][0])]
                 QB.gemm8_prefill_qkv_rope_kv(Wt, St, self.xt, self.qkv, L["qkv_b"], H, self.P, m.cos, m.sin, pos0, m.kc[i],
                                              m.vc[i], c.n_heads, c.n_kv_heads, c.head_dim, m.max_len, self.status)
                 QB.attn_prefill_cached(self.qkv, m.kc[i], m.vc[i], None, self.xt, c.n_heads, c.n_kv_heads, c.head_dim,
                                        m.max_len, pos0, m.scale)
-                self.gemm8(L["o"], self.xt, H, c.q_rows, self.h, None, "resid", H)
-                QB.rmsnorm_q8_tiled(self.h, L["ln2"], self.xt, c.eps)
+            else:
+                self.gemm8(L["qkv"], self.xt, c.qkv_rows, H, self.qkv, L["qkv_b"], "biasf", c.qkv_rows)
+                QB.attn_prefill(self.qkv, m.cos, m.sin, m.kc[i], m.vc[i], self.att, c.n_heads, c.n_kv_heads, c.head_dim,
+                                m.max_len, pos0, m.scale)
+                QB.quant_q8_tiled(self.att, self.xt)
+            self.resid(L["o"], self.xt, c.q_rows)
+            self.norm_q8(L["ln2"])
+            if self.fused:
                 self.gemm8(L["gu"], self.xt, 2 * c.ffn, H, self.xt2, None, "swiglu_q8", c.ffn)
-                self.gemm8(L["down"], self.xt2, H, c.ffn, self.h, None, "resid", H)
-            return
-        for i, L in enumerate(m.L):
-            QB.rmsnorm_q8_tiled(self.h, L["ln1"], self.xt, c.eps)
-            self.gemm8(L["qkv"], self.xt, c.qkv_rows, H, self.qkv, L["qkv_b"], "biasf", c.qkv_rows)
-            QB.attn_prefill(self.qkv, m.cos, m.sin, m.kc[i], m.vc[i], self.att, c.n_heads, c.n_kv_heads, c.head_dim,
-                            m.max_len, pos0, m.scale)
-            QB.quant_q8_tiled(self.att, self.xt)
-            self.gemm8(L["o"], self.xt, H, c.q_rows, self.h, None, "resid", H)
-            QB.rmsnorm_q8_tiled(self.h, L["ln2"], self.xt, c.eps)
-            self.gemm8(L["gu"], self.xt, 2 * c.ffn, H, self.xm, None, "swiglu", c.ffn)
-            QB.quant_q8_tiled(self.xm, self.xt2)
-            self.gemm8(L["down"], self.xt2, H, c.ffn, self.h, None, "resid", H)
+            else:
+                self.gemm8(L["gu"], self.xt, 2 * c.ffn, H, self.xm, None, "swiglu", c.ffn)
+                QB.quant_q8_tiled(self.xm, self.xt2)
+            self.resid(L["down"], self.xt2, c.ffn)
+        if self._pending:                                       # the last down_proj's second half
+            QB.add_rows(self.h, self.h2)
+            self._pending = False
 
     def finish(self, pos0: int = 0) -> None:
         """Greedy token after the last prompt token: final norm + LM head on the last row; leaves the wrapped engine

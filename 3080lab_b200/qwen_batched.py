@@ -174,3 +174,17 @@ def attn_prefill_cached(qkv, kc, vc, out, xt, NH: int, NKV: int, HD: int, max_le
     (tiled Q8_1 of the output, the reference kernel's `q8` mode, lab/qwen_batched.py:1812-1848)."""
     _ffi.call("q4b_attn_prefill_cached", _p(qkv), _p(kc), _p(vc), _p(out), _p(xt), qkv.shape[0], NH, NKV, HD, max_len, pos0,
               float(scale), _stream())
+
+
+def gemm8_prefill_resid_ksplit(Wt, St, xt, Y, Y2, N: int, K: int, P: int, ldy: int, status: Status) -> None:
+    """The residual-adding prefill GEMM with its launch split along K: Y += first half, Y2 = second half (see the header)."""
+    _ffi.call("q4b_mmq_prefill_resid_ksplit", _p(Wt), _p(St), _p(xt), _p(Y), _p(Y2), N, K, P, ldy, _p(status.word), _stream())
+
+
+def rmsnorm_q8_tiled_add(h, h_add, w, xt, eps: float) -> None:
+    """h += h_add (written back), then `rmsnorm_q8_tiled`."""
+    _ffi.call("q4b_rmsnorm_q8_1_tiled_add", _p(h), _p(h_add), _p(w), _p(xt), h.shape[0], h.shape[1], float(eps), _stream())
+
+
+def add_rows(h, h_add) -> None:
+    _ffi.call("q4b_add_rows", _p(h), _p(h_add), h.numel(), _stream())
