@@ -96,10 +96,10 @@ int attn_prefill(const void*, const float*, const float*, void*, void*, void*, i
 size_t q8_tiled_bytes(int, int);
 int mmq_prefill(const void*, const void*, const void*, void*, const void*, int, int, int, int, int, uint32_t*, cudaStream_t,
                 const float* cosT = nullptr, const float* sinT = nullptr, void* kc = nullptr, void* vc = nullptr, int NH = 0,
-                int NKV = 0, int max_len = 0, int pos0 = 0, float* Y2 = nullptr);
-int add_rows(float*, const float*, size_t, cudaStream_t);
+                int NKV = 0, int max_len = 0, int pos0 = 0, float* Y2 = nullptr, int parts = 1);
+int add_rows(float*, const float*, size_t, int, cudaStream_t);
 int quant_q8_1_tiled(const void*, void*, int, int, cudaStream_t);
-int rmsnorm_q8_1_tiled(const float*, const float*, void*, int, int, float, cudaStream_t, float* h_add = nullptr);
+int rmsnorm_q8_1_tiled(const float*, const float*, void*, int, int, float, cudaStream_t, float* h_add = nullptr, int n_add = 1);
 int pack_q4_0(const void*, const void*, void*, void*, int, int, cudaStream_t);
 int quant_q8_1(const void*, void*, void*, void*, int, int, cudaStream_t);
 int rmsnorm_q8_1(const float*, const float*, void*, void*, void*, void*, int, int, float, cudaStream_t);
@@ -299,18 +299,19 @@ int q4b_attn_prefill_cached(const void* qkv, const void* kc, const void* vc, voi
                       scale, S(stream), 1, xt);
 }
 
-int q4b_mmq_prefill_resid_ksplit(const void* Wt, const void* St, const void* xt, float* Y, float* Y2, int N, int K, int P, int ldy,
-                                 uint32_t* status, q4b_stream_t stream) {
+int q4b_mmq_prefill_resid_ksplit(const void* Wt, const void* St, const void* xt, float* Y, float* Y2, int parts, int N, int K, int P,
+                                 int ldy, uint32_t* status, q4b_stream_t stream) {
   if (!Y2) return fail(Q4B_E_ALIGN, "mmq_prefill_resid_ksplit: Y2 missing");
   return mmq_prefill(Wt, St, xt, Y, nullptr, N, K, P, Q4B_EPI_RESID, ldy, status, S(stream), nullptr, nullptr, nullptr, nullptr, 0, 0,
-                     0, 0, Y2);
+                     0, 0, Y2, parts);
 }
 
-int q4b_rmsnorm_q8_1_tiled_add(float* h, const float* h_add, const float* w, void* xt, int rows, int H, float eps, q4b_stream_t stream) {
-  return rmsnorm_q8_1_tiled(h, w, xt, rows, H, eps, S(stream), const_cast<float*>(h_add));
+int q4b_rmsnorm_q8_1_tiled_add(float* h, const float* h_add, int n_add, const float* w, void* xt, int rows, int H, float eps,
+                               q4b_stream_t stream) {
+  return rmsnorm_q8_1_tiled(h, w, xt, rows, H, eps, S(stream), const_cast<float*>(h_add), n_add);
 }
 
-int q4b_add_rows(float* h, const float* h_add, size_t n, q4b_stream_t stream) { return add_rows(h, h_add, n, S(stream)); }
+int q4b_add_rows(float* h, const float* h_add, int n_add, size_t n, q4b_stream_t stream) { return add_rows(h, h_add, n, n_add, S(stream)); }
 
 int q4b_attn_prefill(const void* qkv, const float* cosT, const float* sinT, void* kc, void* vc, void* out, int P, int NH,
                      int NKV, int HD, int max_len, int pos0, float scale, q4b_stream_t stream) {

@@ -55,8 +55,8 @@ struct PrefillArgs {
   const void* AUX;
   uint32_t* status;
   int N, K, P, epi, ldy;
-  float* Y2;           // split launch: where the second K half stores its sums, fp32 [P, ldy]
-  int kb_split;        // split launch: first k-block of the second half (a multiple of 8)
+  float* Y2;           // split launch: where parts 1 .. of K store their sums, fp32 [parts - 1][P, ldy]
+  int kb_bound[5];     // k-block bounds of the parts (multiples of 8); unsplit: {0, K / 32}
   // fused RoPE + K/V append (Q4B_EPI_BIASF_ROPE_KV): tokens of ONE sequence at positions pos0 .., cache fp16 [NKV, max_len, 128]
   const float* cosT;
   const float* sinT;
@@ -132,11 +132,12 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const __grid
   uint8_t* stage = slabS + (size_t)WB * WBATCH_S;          // [SB][4608]
 
   const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
-  // K range of this CTA: all of K, or with a split launch (gridDim.z = 2) the k-blocks below / from a.kb_split.  The second
-  // half stores its sums as fp32 into Y2 instead of adding them to Y; whoever reads Y next adds Y2 (in that fixed order).
+  // K range of this CTA: all of K, or with a split launch (gridDim.z = 2 .. 4) part blockIdx.z of it (bounds in whole
+  // batches of 8 k-blocks).  Part 0 adds its sums to Y; part z > 0 stores them as fp32 into Y2[z - 1]; whoever reads Y next
+  // adds the parts in that fixed order.
   const int KBT = a.K >> 5;
-  const int kb_lo = blockIdx.z ? a.kb_split : 0;
-  const int KB = (gridDim.z == 2 ? (blockIdx.z ? KBT - a.kb_split : a.kb_split) : KBT), NBATCH = KB >> 3;
+  const int kb_lo = a.kb_bound[blockIdx.z];
+  const int KB = a.kb_bound[blockIdx.z + 1] - kb_lo, NBATCH = KB >> 3;
   const int row_tile = blockIdx.x, tok_tile = blockIdx.y;
   const size_t wbase = (size_t)row_tile * KBT + kb_lo;     // k-block index of this row tile in the packed arrays
   const uint8_t* xbase = a.Xt + ((size_t)tok_tile * KBT + kb_lo) * STAGE_BYTES;
@@ -361,7 +362,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const __grid
           case Q4B_EPI_STORE: reinterpret_cast<__half*>(a.Y)[base + row] = __float2half_rn(v); break;
           case Q4B_EPI_BIASF: reinterpret_cast<__half*>(a.Y)[base + row] = __float2half_rn(v + bias); break;
           case Q4B_EPI_RESID:
-            if (blockIdx.z) a.Y2[base + row] = v;
+            if (blockIdx.z) a.Y2[(size_t)(blockIdx.z - 1) * a.P * a.ldy + base + row] = v;
             else reinterpret_cast<float*>(a.Y)[base + row] += v;
             break;
           case Q4B_EPI_LOGITS: reinterpret_cast<float*>(a.Y)[base + row] = v; break;
@@ -384,10 +385,10 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const __grid
 
 size_t q8_tiled_bytes(int P, int K) { return (size_t)((P + NTOK - 1) / NTOK) * (size_t)(K / 32) * STAGE_BYTES; }
 
-// Y2 != nullptr (RESID only): the launch is split along K over gridDim.z = 2; Y += first half, Y2 = second half.
+// Y2 != nullptr (RESID only): the launch is split along K over gridDim.z = parts; Y += part 0, Y2[z - 1] = part z.
 int mmq_prefill(const void* Wt, const void* St, const void* Xt, void* Y, const void* AUX, int N, int K, int P, int epilogue,
                 int ldy, uint32_t* status, cudaStream_t st, const float* cosT, const float* sinT, void* kc, void* vc, int NH,
-                int NKV, int max_len, int pos0, float* Y2) {
+                int NKV, int max_len, int pos0, float* Y2, int parts) {
   if (N <= 0 || P <= 0 || K <= 0 || (K % 256)) return fail(Q4B_E_SHAPE, "mmq_prefill: N, P > 0 and K a positive multiple of 256 required");
   if (epilogue < Q4B_EPI_STORE || epilogue > Q4B_EPI_BIASF_ROPE_KV) return fail(Q4B_E_ARG, "mmq_prefill: unknown epilogue");
   if (epilogue == Q4B_EPI_SWIGLU && (N % 2)) return fail(Q4B_E_SHAPE, "mmq_prefill: swiglu needs an even row count");
@@ -426,12 +427,15 @@ int mmq_prefill(const void* Wt, const void* St, const void* Xt, void* Y, const v
   a.max_len = max_len;
   a.pos0 = pos0;
   a.Y2 = Y2;
-  a.kb_split = 0;
+  a.kb_bound[0] = 0;
+  a.kb_bound[1] = a.kb_bound[2] = a.kb_bound[3] = a.kb_bound[4] = K / 32;
   dim3 grid((N + 127) / 128, (P + NTOK - 1) / NTOK);
   if (Y2) {
-    if (epilogue != Q4B_EPI_RESID || K < 512 || !aligned16(Y2)) return fail(Q4B_E_SHAPE, "mmq_prefill: a K-split launch needs the resid epilogue and K >= 512");
-    a.kb_split = ((K / 32 / 2 + 7) / 8) * 8;             // halves in whole batches of 8 k-blocks
-    grid.z = 2;
+    if (epilogue != Q4B_EPI_RESID || parts < 2 || parts > 4 || K / 256 < parts || !aligned16(Y2))
+      return fail(Q4B_E_SHAPE, "mmq_prefill: a K-split launch needs the resid epilogue, 2 .. 4 parts and K >= 256 per part");
+    const int batches = K / 256;                         // whole batches of 8 k-blocks, spread as evenly as they go
+    for (int z = 1; z < parts; ++z) a.kb_bound[z] = (int)(((long long)batches * z + parts - 1) / parts) * 8;
+    grid.z = parts;
   }
   return check_launch(launch_pdl(mmq_prefill_kernel, grid, dim3(PF_THREADS), PF_SMEM, st, a), "mmq_prefill");
 }

@@ -27,18 +27,20 @@ __global__ void __launch_bounds__(256) quant_q8_1_tiled_kernel(const __half* x, 
   quant_block4_tiled(v, xt + ((size_t)(p >> 7) * KB + kb) * 4608, p & 127, sub);
 }
 
-// h_add != nullptr: the row is first completed, h[row] += h_add[row] (written back), e.g. with the second half of a linear
-// whose launch was split along K; then normalised and quantised as usual.
+// h_add != nullptr: the row is first completed, h[row] += h_add[0][row] + .. (written back), e.g. with the further parts of a
+// linear whose launch was split along K; then normalised and quantised as usual.
 __global__ void __launch_bounds__(1024) rmsnorm_q8_1_tiled_kernel(const float* h, const float* __restrict__ w, uint8_t* xt,
-                                                                  int H, float eps, float* h_add) {
+                                                                  int H, float eps, float* h_add, int n_add) {
   __shared__ float part[32];
   pdl_launch_dependents();
   pdl_wait();
   const int row = blockIdx.x, t = threadIdx.x, i0 = 4 * t;
   float4 hv = *reinterpret_cast<const float4*>(h + (size_t)row * H + i0);
   if (h_add) {
-    const float4 av = *reinterpret_cast<const float4*>(h_add + (size_t)row * H + i0);
-    hv.x += av.x; hv.y += av.y; hv.z += av.z; hv.w += av.w;
+    for (int j = 0; j < n_add; ++j) {                    // the addends [n_add][rows, H], in order
+      const float4 av = *reinterpret_cast<const float4*>(h_add + ((size_t)j * gridDim.x + row) * H + i0);
+      hv.x += av.x; hv.y += av.y; hv.z += av.z; hv.w += av.w;
+    }
     *reinterpret_cast<float4*>(const_cast<float*>(h) + (size_t)row * H + i0) = hv;
   }
   const float4 wv = *reinterpret_cast<const float4*>(w + i0);
@@ -120,31 +122,33 @@ int quant_q8_1_tiled(const void* x, void* xt, int rows, int K, cudaStream_t st) 
                                  (const __half*)x, (uint8_t*)xt, rows, K / 32), "quant_q8_1_tiled");
 }
 
-int rmsnorm_q8_1_tiled(const float* h, const float* w, void* xt, int rows, int H, float eps, cudaStream_t st, float* h_add) {
+int rmsnorm_q8_1_tiled(const float* h, const float* w, void* xt, int rows, int H, float eps, cudaStream_t st, float* h_add, int n_add) {
   if (rows <= 0 || H <= 0 || (H % 128) || H > 4096) return fail(Q4B_E_SHAPE, "rmsnorm_q8_1_tiled: H must be a multiple of 128, at most 4096");
   if (!h || !w || !xt || !aligned16(h) || !aligned16(w) || !aligned16(xt) || !aligned16(h_add))
     return fail(Q4B_E_ALIGN, "rmsnorm_q8_1_tiled: null or misaligned pointer");
-  return check_launch(launch_pdl(rmsnorm_q8_1_tiled_kernel, dim3(rows), dim3(H / 4), 0, st, h, w, (uint8_t*)xt, H, eps, h_add),
+  return check_launch(launch_pdl(rmsnorm_q8_1_tiled_kernel, dim3(rows), dim3(H / 4), 0, st, h, w, (uint8_t*)xt, H, eps, h_add, n_add),
                       "rmsnorm_q8_1_tiled");
 }
 
 namespace {
-__global__ void __launch_bounds__(256) add_rows_kernel(float* h, const float* h_add, size_t n4) {
+__global__ void __launch_bounds__(256) add_rows_kernel(float* h, const float* h_add, size_t n4, int n_add) {
   pdl_launch_dependents();
   pdl_wait();
   const size_t i = (size_t)blockIdx.x * 256 + threadIdx.x;
   if (i >= n4) return;
   float4 a = reinterpret_cast<float4*>(h)[i];
-  const float4 b = reinterpret_cast<const float4*>(h_add)[i];
-  a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+  for (int j = 0; j < n_add; ++j) {
+    const float4 b = reinterpret_cast<const float4*>(h_add)[(size_t)j * n4 + i];
+    a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+  }
   reinterpret_cast<float4*>(h)[i] = a;
 }
 }  // namespace
 
-// h[0 .. n) += h_add[0 .. n), n a multiple of 4 (completes rows whose second K half was stored apart)
-int add_rows(float* h, const float* h_add, size_t n, cudaStream_t st) {
-  if (!h || !h_add || !aligned16(h) || !aligned16(h_add) || (n % 4) || n == 0) return fail(Q4B_E_ALIGN, "add_rows: null, misaligned or ragged");
-  return check_launch(launch_pdl(add_rows_kernel, dim3((unsigned)((n / 4 + 255) / 256)), dim3(256), 0, st, h, h_add, n / 4), "add_rows");
+// h[0 .. n) += h_add[0][0 .. n) + h_add[1][0 .. n) + .., n a multiple of 4 (completes rows whose further K parts were stored apart)
+int add_rows(float* h, const float* h_add, size_t n, int n_add, cudaStream_t st) {
+  if (!h || !h_add || !aligned16(h) || !aligned16(h_add) || (n % 4) || n == 0 || n_add < 1) return fail(Q4B_E_ALIGN, "add_rows: null, misaligned or ragged");
+  return check_launch(launch_pdl(add_rows_kernel, dim3((unsigned)((n / 4 + 255) / 256)), dim3(256), 0, st, h, h_add, n / 4, n_add), "add_rows");
 }
 
 int rmsnorm_q8_1(const float* h, const float* w, void* xq, void* xd, void* xsum, void* x16, int rows, int H, float eps,

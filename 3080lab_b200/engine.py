@@ -492,8 +492,8 @@ class Prefill:
         appends K/V (`biasf_kv`), the flash kernel emits the o-projection's Q8_1 input (`q8`), the gate/up GEMM emits the
         down GEMM's (`swiglu_q8`).  fused=False keeps those three steps as separate launches (ten per layer); both give
         the same bits.
-        split_k: launch o_proj and down_proj as two half-K CTAs per output tile (the second half lands in `h2` and is added
-        by the next RMSNorm + Q8_1 launch).  Default: on where their grid would otherwise fill the SMs in a ragged second
+        split_k: launch o_proj and down_proj as two to four CTAs per output tile, each over a part of K (the further parts
+        land in `h2` and are added by the next RMSNorm + Q8_1 launch).  Default: on where their grid would otherwise fill the SMs in a ragged second
         round (12 row tiles x P / 128 token tiles between one and two times the SM count)."""
         c = m.cfg
         if not m.tensor_core or c.hidden % 256 or c.q_rows % 256 or c.ffn % 256 or c.head_dim != 128:
@@ -511,7 +511,23 @@ class Prefill:
         tiles = ((c.hidden + 127) // 128) * ((P + 127) // 128)
         sms = torch.cuda.get_device_properties(dv).multi_processor_count
         self.split_k = (sms < tiles < 2 * sms) if split_k is None else bool(split_k)
-        self.h2 = torch.zeros(P, c.hidden, dtype=f32, device=dv) if self.split_k else None
+
+        def parts_for(Kdim: int) -> int:
+            """Parts that leave the fewest rounds of CTAs per unit of work (ceil(tiles * n / SMs) / n), with at least 64
+            k-blocks per part so that a CTA's fixed costs stay small."""
+            best, cost = 1, -(-tiles // sms)
+            for n in (2, 3, 4):
+                if Kdim // 32 // n < 64 and n > 2:
+                    break
+                if Kdim < 512:
+                    break
+                cn = -(-tiles * n // sms) / n
+                if cn < cost - 1e-9:
+                    best, cost = n, cn
+            return best
+        self.parts = {Kd: (parts_for(Kd) if self.split_k else 1) for Kd in (c.q_rows, c.ffn)}
+        nbuf = max(self.parts.values()) - 1
+        self.h2 = torch.zeros(nbuf, P, c.hidden, dtype=f32, device=dv) if nbuf > 0 else None
         self.launches_per_chunk = 1 + (7 if fused else 10) * c.layers + (1 if self.split_k else 0)
 
     def gemm8(self, pair, xt, N, Kdim, Y, aux, epi, ldy):
@@ -519,21 +535,22 @@ class Prefill:
         QB.gemm8_prefill(Wt, St, xt, Y, aux, N, Kdim, self.P, epi, ldy, self.status)
 
     def resid(self, pair, xt, Kdim):
-        """h += linear(xt): one launch; with split_k the second K half goes to h2 and `self._pending` records that h2
-        still has to be added (the next `norm_q8` does it)."""
+        """h += linear(xt): one launch; with split_k the further K parts go to h2[0 ..] and `self._pending` records how many
+        still have to be added (the next `norm_q8` does it)."""
         Wt, St = self.m.packed[id(pair[0])]
         H = self.m.cfg.hidden
-        if self.split_k and Kdim >= 512:
-            QB.gemm8_prefill_resid_ksplit(Wt, St, xt, self.h, self.h2, H, Kdim, self.P, H, self.status)
-            self._pending = True
+        n = self.parts.get(Kdim, 1)
+        if n > 1:
+            QB.gemm8_prefill_resid_ksplit(Wt, St, xt, self.h, self.h2[:n - 1], H, Kdim, self.P, H, self.status)
+            self._pending = n - 1
         else:
             QB.gemm8_prefill(Wt, St, xt, self.h, None, H, Kdim, self.P, "resid", H, self.status)
 
     def norm_q8(self, w):
         """RMSNorm + tiled Q8_1 of h into xt, completing h with a pending second K half first."""
         if self._pending:
-            QB.rmsnorm_q8_tiled_add(self.h, self.h2, w, self.xt, self.m.cfg.eps)
-            self._pending = False
+            QB.rmsnorm_q8_tiled_add(self.h, self.h2[:self._pending], w, self.xt, self.m.cfg.eps)
+            self._pending = 0
         else:
             QB.rmsnorm_q8_tiled(self.h, w, self.xt, self.m.cfg.eps)
 
@@ -541,7 +558,7 @@ class Prefill:
         """One pass over the P tokens in self.tok at positions pos0 .. pos0 + P - 1."""
         m, c, H = self.m, self.m.cfg, self.m.cfg.hidden
         K.embed(m.embed, self.tok, self.h)
-        self._pending = False
+        self._pending = 0
         for i, L in enumerate(m.L):
             self.norm_q8(L["ln1"])
             if self.fused:
@@ -563,9 +580,9 @@ class Prefill:
                 self.gemm8(L["gu"], self.xt, 2 * c.ffn, H, self.xm, None, "swiglu", c.ffn)
                 QB.quant_q8_tiled(self.xm, self.xt2)
             self.resid(L["down"], self.xt2, c.ffn)
-        if self._pending:                                       # the last down_proj's second half
-            QB.add_rows(self.h, self.h2)
-            self._pending = False
+        if self._pending:                                       # the last down_proj's further parts
+            QB.add_rows(self.h, self.h2[:self._pending])
+            self._pending = 0
 
     def finish(self, pos0: int = 0) -> None:
         """Greedy token after the last prompt token: final norm + LM head on the last row; leaves the wrapped engine

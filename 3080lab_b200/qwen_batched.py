@@ -177,14 +177,18 @@ def attn_prefill_cached(qkv, kc, vc, out, xt, NH: int, NKV: int, HD: int, max_le
 
 
 def gemm8_prefill_resid_ksplit(Wt, St, xt, Y, Y2, N: int, K: int, P: int, ldy: int, status: Status) -> None:
-    """The residual-adding prefill GEMM with its launch split along K: Y += first half, Y2 = second half (see the header)."""
-    _ffi.call("q4b_mmq_prefill_resid_ksplit", _p(Wt), _p(St), _p(xt), _p(Y), _p(Y2), N, K, P, ldy, _p(status.word), _stream())
+    """The residual-adding prefill GEMM with its launch split along K into 1 + Y2.shape[0] parts: Y += part 0, Y2[z - 1] =
+    part z (see the header)."""
+    _ffi.call("q4b_mmq_prefill_resid_ksplit", _p(Wt), _p(St), _p(xt), _p(Y), _p(Y2), 1 + Y2.shape[0], N, K, P, ldy, _p(status.word),
+              _stream())
 
 
 def rmsnorm_q8_tiled_add(h, h_add, w, xt, eps: float) -> None:
-    """h += h_add (written back), then `rmsnorm_q8_tiled`."""
-    _ffi.call("q4b_rmsnorm_q8_1_tiled_add", _p(h), _p(h_add), _p(w), _p(xt), h.shape[0], h.shape[1], float(eps), _stream())
+    """h += h_add[0] + h_add[1] + .. (written back), then `rmsnorm_q8_tiled`.  h_add fp32 [n, rows, H]."""
+    _ffi.call("q4b_rmsnorm_q8_1_tiled_add", _p(h), _p(h_add), h_add.shape[0], _p(w), _p(xt), h.shape[0], h.shape[1], float(eps),
+              _stream())
 
 
 def add_rows(h, h_add) -> None:
-    _ffi.call("q4b_add_rows", _p(h), _p(h_add), h.numel(), _stream())
+    """h += h_add[0] + h_add[1] + ..; h_add fp32 [n, *h.shape]."""
+    _ffi.call("q4b_add_rows", _p(h), _p(h_add), h_add.shape[0], h.numel(), _stream())

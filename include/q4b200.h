@@ -287,15 +287,17 @@ int q4b_mmq_prefill_qkv_rope_kv(const void* Wt, const void* St, const void* xt, 
 int q4b_attn_prefill_cached(const void* qkv, const void* kc, const void* vc, void* out, void* xt, int P, int NH, int NKV,
                             int HD, int max_len, int pos0, float scale, q4b_stream_t stream);
 
-/* The residual-adding prefill GEMM with its launch split along K (two CTAs per output tile, each half of K): Y += first
- * half, Y2 = second half (fp32 [P, ldy], overwritten).  o_proj and down_proj have 12 row tiles x P / 128 token tiles =
- * 192 CTAs on 148 SMs at P = 2048; as 384 half-length CTAs they fill the machine in 1.5 instead of 2 rounds.  The next
- * reader of Y must add Y2: q4b_rmsnorm_q8_1_tiled_add does (h += h_add, written back, then RMSNorm + tiled Q8_1), and
- * q4b_add_rows after the last layer.  The order h + first + second is fixed, so results are bit-repeatable. */
-int q4b_mmq_prefill_resid_ksplit(const void* Wt, const void* St, const void* xt, float* Y, float* Y2, int N, int K, int P, int ldy,
-                                 uint32_t* status, q4b_stream_t stream);
-int q4b_rmsnorm_q8_1_tiled_add(float* h, const float* h_add, const float* w, void* xt, int rows, int H, float eps, q4b_stream_t stream);
-int q4b_add_rows(float* h, const float* h_add, size_t n, q4b_stream_t stream);
+/* The residual-adding prefill GEMM with its launch split along K into `parts` (2 .. 4) CTAs per output tile: Y += part 0,
+ * Y2[z - 1] = part z (fp32 [parts - 1][P, ldy], overwritten).  o_proj and down_proj have 12 row tiles x P / 128 token
+ * tiles = 192 CTAs on 148 SMs at P = 2048; as 384 half-length CTAs they fill the machine in 1.5 instead of 2 rounds, as 576
+ * third-length ones in 1.33.  The next reader of Y must add the parts: q4b_rmsnorm_q8_1_tiled_add does (h += h_add[0] + ..,
+ * written back, then RMSNorm + tiled Q8_1), and q4b_add_rows after the last layer.  The order of the additions is fixed,
+ * so results are bit-repeatable. */
+int q4b_mmq_prefill_resid_ksplit(const void* Wt, const void* St, const void* xt, float* Y, float* Y2, int parts, int N, int K, int P,
+                                 int ldy, uint32_t* status, q4b_stream_t stream);
+int q4b_rmsnorm_q8_1_tiled_add(float* h, const float* h_add, int n_add, const float* w, void* xt, int rows, int H, float eps,
+                               q4b_stream_t stream);
+int q4b_add_rows(float* h, const float* h_add, int n_add, size_t n, q4b_stream_t stream);
 
 /* Prefill attention for one sequence: rotate K (NeoX pairs) and append K/V of P prompt tokens at positions
  * pos0 .. pos0+P-1, then causal GQA flash attention of the P queries (rotated inside) over positions 0 .. pos0+P-1.

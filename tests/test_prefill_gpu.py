@@ -256,10 +256,10 @@ def test_resid_gemm_split_along_k_equals_the_two_halves(P, n, k):
     QB.quant_q8_tiled(_dev(x), xt)
     st = QB.Status("cuda")
     h0 = torch.from_numpy(rng.standard_normal((P, n)).astype(np.float32)).cuda()
-    y, y2 = h0.clone(), torch.full((P, n), float("nan"), device="cuda")
+    y, y2 = h0.clone(), torch.full((1, P, n), float("nan"), device="cuda")
     QB.gemm8_prefill_resid_ksplit(Wt, St, xt, y, y2, n, k, P, n, st)
     st.check()
-    got = (y.double() + y2.double()).cpu().numpy()
+    got = (y.double() + y2[0].double()).cpu().numpy()
     want = h0.double().cpu().numpy() + ref
     assert np.max(np.abs(got - want)) / np.max(np.abs(want)) < 2e-6
     # the halves against the oracle restricted to their k-blocks
@@ -267,7 +267,13 @@ def test_resid_gemm_split_along_k_equals_the_two_halves(P, n, k):
     lo = o.mmq(W[:, :split // 8], S[:, :split // 32], xq[:, :split], xd[:, :split // 32])
     hi = o.mmq(W[:, split // 8:], S[:, split // 32:], xq[:, split:], xd[:, split // 32:])
     assert np.max(np.abs((y - h0).double().cpu().numpy() - lo)) / np.max(np.abs(lo)) < 2e-6
-    assert np.max(np.abs(y2.double().cpu().numpy() - hi)) / np.max(np.abs(hi)) < 2e-6
+    assert np.max(np.abs(y2[0].double().cpu().numpy() - hi)) / np.max(np.abs(hi)) < 2e-6
+    if k >= 768:                                             # three parts: their sum is the whole product again
+        y3, p3 = h0.clone(), torch.full((2, P, n), float("nan"), device="cuda")
+        QB.gemm8_prefill_resid_ksplit(Wt, St, xt, y3, p3, n, k, P, n, st)
+        st.check()
+        got3 = (y3.double() + p3[0].double() + p3[1].double()).cpu().numpy()
+        assert np.max(np.abs(got3 - want)) / np.max(np.abs(want)) < 2e-6
     # twice the same bits
     ya, yb = h0.clone(), torch.zeros_like(y2)
     QB.gemm8_prefill_resid_ksplit(Wt, St, xt, ya, yb, n, k, P, n, st)
@@ -280,9 +286,9 @@ def test_rmsnorm_q8_tiled_add_equals_add_then_quantiser():
     g = torch.Generator(device="cuda").manual_seed(1)
     P, H = 200, 1536
     h = torch.randn(P, H, device="cuda", generator=g)
-    h2 = torch.randn(P, H, device="cuda", generator=g)
+    h2 = torch.randn(2, P, H, device="cuda", generator=g)
     w = 1.0 + 0.1 * torch.randn(H, device="cuda", generator=g)
-    want_h = h + h2
+    want_h = (h + h2[0]) + h2[1]
     want = QB.q8_tiled_buffer(P, H, "cuda")
     QB.rmsnorm_q8_tiled(want_h, w, want, 1e-6)
     got = QB.q8_tiled_buffer(P, H, "cuda")
@@ -291,7 +297,7 @@ def test_rmsnorm_q8_tiled_add_equals_add_then_quantiser():
     a = torch.randn(P, H, device="cuda", generator=g)
     b = a.clone()
     QB.add_rows(b, h2)
-    assert torch.equal(b, a + h2)
+    assert torch.equal(b, (a + h2[0]) + h2[1])
 
 
 def test_prefill_with_split_k_matches_the_unsplit_pass():
