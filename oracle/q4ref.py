@@ -9,7 +9,9 @@ operation by operation in float32.
 
 Pinning: `q4_0_blocks`, `dequant` and `gemv_ref` are checked against the reference's own `lab/gguf.py` code and the
 generator/oracle of `lab/experiments/gemv5.py` through fixtures under tests/golden (made by tests/golden/make_golden.py
-with the reference imported).  The remaining functions restate CUDA source that cannot execute without the
+with the reference imported); the RoPE tables against the reference's statement run with torch on the CPU; `blockdot`
+against the reference's s8 known-answer operands and against its own `pack_q4_i8` repack with the planted offset term;
+`dequant_f16w` against its `pack_q4_mma` repack read the way its kernel reads it.  The remaining functions restate CUDA source that cannot execute without the
 reference's NVRTC toolchain and model files: parity for those is unpinned against a running reference and is
 cross-checked against an independent formulation in the tests instead.
 

@@ -17,6 +17,8 @@ Fixtures:
                    (lab/experiments/tensor.py:171-179, which demands exact equality) and its expected A8 @ B8 + C8
   rope_tables.npz  cos / sin rows computed by the reference's own statement (scripts/qwen_gguf.py:111-113, torch double
                    -> float) for head_dim 128, theta 1e6, at a spread of positions
+  pack_q4_i8.npz   the same matrix through the reference's `pack_q4_i8` (lab/qwen_batched.py:987-1013): the operand of its
+                   int8 MMQ (unsigned nibbles, offset corrected through the planted -8 sum(x) term)
   pack_q4_mma.npz  a seeded 48 x 192 Q4_0 matrix in the canonical device words and what the reference's own
                    `pack_q4_mma` (lab/qwen_batched.py:394-436, torch on the CPU) makes of it: the fragment-ordered
                    operand of its batched-decode GEMV
@@ -140,6 +142,9 @@ def main(ref_root: str) -> None:
     W = torch.from_numpy(words.view(np.int32).copy())
     Wp, Sp = rb.pack_q4_mma(W, torch.from_numpy(d.copy()))
     np.savez_compressed(HERE / "pack_q4_mma.npz", W=W.numpy(), S=d, Wp=Wp.numpy(), Sp=Sp.numpy())
+    # 8. ... and its repack for the int8 MMQ (unsigned nibbles as the A operand), on the same matrix
+    Wi, Si = rb.pack_q4_i8(W, torch.from_numpy(d.copy()))
+    np.savez_compressed(HERE / "pack_q4_i8.npz", W=W.numpy(), S=d, Wp=Wi.numpy(), Sp=Si.numpy())
     print("fixtures written to", HERE)
 
 

@@ -190,3 +190,44 @@ def test_f16_weight_oracle_reads_the_reference_fragment_pack(golden):
     exact = o.dequant(W, S)
     assert 0.2 < np.mean(exact != want) < 1.0
     assert np.max(np.abs(exact - want) / np.abs(exact).max()) < 2 ** -11
+
+
+def test_block_dot_oracle_against_the_reference_int8_repack(golden):
+    """The reference's int8 MMQ multiplies UNSIGNED nibbles (its `pack_q4_i8` operand) with the int8 activations and plants
+    0x4B400000 - 8 sum(x) in the accumulator (QUANT_Q8, lab/qwen_batched.py:1016-1041), so that the result is the bit
+    pattern of 2^23 + 2^22 + sum((q - 8) x).  Reading the reference-made operand the way its kernel does (lane (g, t), word
+    2 b + h, byte i = row g | row g + 8 << 4 at k = 32 b + 16 h + 4 t + i) and applying that correction must give the
+    oracle's signed block dots, and the planted constant must turn them into exact floats."""
+    o = oracle()
+    g = golden["pack_q4_i8"]
+    W, Wp, Sp, S = g["W"], g["Wp"].view(np.uint32), g["Sp"], g["S"]
+    N, K = W.shape[0], W.shape[1] * 8
+    q = np.zeros((N, K), np.int64)
+    for tile in range(N // 16):
+        for ch in range(K // 64):
+            for lane in range(32):
+                gg, t = lane >> 2, lane & 3
+                for b in range(2):
+                    for h in range(2):
+                        word = int(Wp[tile, ch, lane, 2 * b + h])
+                        for i in range(4):
+                            k = 64 * ch + 32 * b + 16 * h + 4 * t + i
+                            byte = (word >> (8 * i)) & 0xFF
+                            q[16 * tile + gg, k] = byte & 15
+                            q[16 * tile + gg + 8, k] = byte >> 4
+    np.testing.assert_array_equal(q, o.unpack_words(W))
+    # scales: [tile][chunk][g][4] = (row g blk 0, row g + 8 blk 0, row g blk 1, row g + 8 blk 1)
+    Sv = S.reshape(N // 16, 16, K // 64, 2)
+    np.testing.assert_array_equal(Sp[:, :, :, 0], Sv[:, :8, :, 0].transpose(0, 2, 1))
+    np.testing.assert_array_equal(Sp[:, :, :, 3], Sv[:, 8:, :, 1].transpose(0, 2, 1))
+    rng = np.random.default_rng(3)
+    xq = rng.integers(-127, 128, size=(5, K)).astype(np.int8)
+    want = o.blockdot(W, xq)                                   # [P, N, K / 32] signed dots
+    qb = q.reshape(N, K // 32, 32)
+    xb = xq.astype(np.int64).reshape(5, K // 32, 32)
+    unsigned = np.einsum("nbk,pbk->pnb", qb, xb)
+    planted = 0x4B400000 - 8 * xb.sum(axis=2)                  # per (token, block), as QUANT_Q8 writes it
+    acc = (unsigned + planted[:, None, :]).astype(np.int64)
+    np.testing.assert_array_equal(acc - 0x4B400000, want)
+    as_float = acc.astype(np.uint32).view(np.float32).astype(np.float64) - 12582912.0
+    np.testing.assert_array_equal(as_float, want.astype(np.float64))
