@@ -83,6 +83,7 @@ SIGNATURES = {
     "q4b_mmq_prefill_resid_ksplit": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P]),
     "q4b_rmsnorm_q8_1_tiled_add": (_I, [_P, _P, _I, _P, _P, _I, _I, _F, _P]),
     "q4b_add_rows": (_I, [_P, _P, _I, _Z, _P]),
+    "q4b_mmq_prefill_trace": (_I, [_P, _Z]),
     "q4b_attn_prefill": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P]),
     "q4b_trace_buffer": (_I, [_P, _Z]),
     "q4b_peak_i8_launch": (C.c_double, [_I, _P, _P]),

@@ -67,6 +67,7 @@ int gemv_mma(const void*, const void*, const void*, void*, const void*, int, int
              const int64_t* pos = nullptr, void* kc = nullptr, void* vc = nullptr, int NH = 0, int NKV = 0, int HD = 0,
              int max_len = 0, int withhold_chunk = -1, const GemvLookahead* look = nullptr);
 int gemv_mma_ksplit(int, int);
+void mmq_prefill_trace(long long*);
 void attn_batched_kernel(int);
 int tp_allreduce(const void* const*, void* const*, int, int, uint32_t, const uint32_t*, float*, int, int, const float*, float, void*,
                  void*, uint32_t*, uint32_t, cudaStream_t);
@@ -251,6 +252,12 @@ int q4b_mmq_q4_0_q8_1_mma(const void* W, const void* Sc, const void* xq, const v
 int q4b_quant_mmq_q4_0_q8_1_mma(const void* W, const void* Sc, const void* x16, void* Y, const void* AUX, int N, int K, int P,
                                 int epilogue, int ldy, uint32_t* status, q4b_stream_t stream) {
   return gemv_q8mma(W, Sc, nullptr, x16, Y, AUX, N, K, P, epilogue, ldy, status, S(stream));
+}
+
+int q4b_mmq_prefill_trace(int64_t* device_buffer, size_t entries) {
+  if (device_buffer && entries < 11 * 64) return fail(Q4B_E_WORKSPACE, "mmq_prefill_trace: need 11 x 64 entries");
+  mmq_prefill_trace(reinterpret_cast<long long*>(device_buffer));
+  return Q4B_OK;
 }
 
 int q4b_debug_gemv_mma_expired_wait(const void* W, const void* Sc, const void* X, void* Y, int N, int K, uint32_t* status,

@@ -30,6 +30,22 @@
 #include "q4b_internal.h"
 #include "tc05.cuh"
 
+#ifndef PF_ABLATE
+#define PF_ABLATE 0
+#endif
+#if PF_ABLATE == 12
+#define PF_NOEXP 1
+#define PF_NOCOPY 1
+#define PF_NOMMA 1
+#endif
+#if PF_ABLATE == 11
+#define PF_NOEXP 1
+#endif
+#if PF_ABLATE == 2 || PF_ABLATE == 3 || PF_ABLATE == 12
+#define PF_LD(addr, regs) do { _Pragma("unroll") for (int i_ = 0; i_ < 16; ++i_) asm volatile("" : "+r"(regs[i_])); } while (0)
+#else
+#define PF_LD(addr, regs) tc::tmem_ld16(addr, regs)
+#endif
 namespace q4b {
 
 namespace {
@@ -55,6 +71,7 @@ struct PrefillArgs {
   const void* AUX;
   uint32_t* status;
   int N, K, P, epi, ldy;
+  long long* trace;    // per-role clock stamps of CTA (0, 0, 0), [11][64] (see q4b_mmq_prefill_trace); null = off
   float* Y2;           // split launch: where parts 1 .. of K store their sums, fp32 [parts - 1][P, ldy]
   int kb_bound[5];     // k-block bounds of the parts (multiples of 8); unsplit: {0, K / 32}
   // fused RoPE + K/V append (Q4B_EPI_BIASF_ROPE_KV): tokens of ONE sequence at positions pos0 .., cache fp16 [NKV, max_len, 128]
@@ -74,7 +91,44 @@ __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t by
 
 // wait unless an earlier wait of this thread already expired
 __device__ __forceinline__ void waitb(uint64_t* bar, uint32_t parity, bool& ok) {
+#if PF_ABLATE == 10
   if (ok) ok = tc::mbar_wait(bar, parity);
+#else
+  if (ok) ok = tc::mbar_wait_parked(bar, parity);
+#endif
+}
+__device__ __forceinline__ void waitm(uint64_t* bar, uint32_t parity, bool& ok) {
+#if PF_ABLATE == 6
+  if (ok) {
+    ok = false;
+    for (uint32_t i = 0; i < (1u << 24); ++i)
+      if (tc::mbar_test(bar, parity)) { ok = true; break; }
+  }
+#else
+  waitb(bar, parity, ok);
+#endif
+}
+// Warp-wide wait with ONE polling lane: the others park at the warp barrier, which also orders their later reads after the
+// phase completion lane 0 observed.  (With all 32 lanes of 20 warps polling, every mbarrier operation of the CTA - the MMA
+// issuer's included - queued behind the polls in the shared-memory pipe.)  Only lane 0's `ok` can turn false.
+__device__ __forceinline__ void waitw(uint64_t* bar, uint32_t parity, bool& ok, int lane) {
+#if PF_ABLATE == 5
+  waitb(bar, parity, ok);
+#else
+  if (lane == 0) waitb(bar, parity, ok);
+  __syncwarp();
+#endif
+}
+// SwiGLU of one gate/up row pair (adjacent TMEM lanes = adjacent threads) for the token pair (2 j, 2 j + 1) held in `acc`:
+// the even lane takes token 2 j, the odd lane token 2 j + 1, so each lane evaluates 16 of the 32 products (one exchange
+// and one division per token pair instead of two of each).  Returns the product and the token n it belongs to.
+__device__ __forceinline__ float swiglu_pair(uint64_t acc, int r, int j, int& n) {
+  const bool odd = r & 1;
+  const float v0 = tc::lo2(acc), v1 = tc::hi2(acc);
+  const float got = __shfl_xor_sync(0xffffffffu, odd ? v0 : v1, 1);
+  const float g = odd ? got : v0, u = odd ? v1 : got;
+  n = 2 * j + (odd ? 1 : 0);
+  return g / (1.f + __expf(-g)) * u;
 }
 // Second halves of the two fused epilogues, kept out of line so that they cost the main loop no registers.
 // RoPE + cache write from the rounded tile in shared memory: thread = (row r of the head, 32 tokens from tok0).
@@ -116,6 +170,7 @@ __device__ __noinline__ void swiglu_q8_phase(const PrefillArgs& a, const __half*
   }
 }
 
+template <bool TRACE>
 __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const __grid_constant__ PrefillArgs a) {
   extern __shared__ __align__(128) uint8_t smem[];
   // "empty" barriers are waited on with the inverted parity the first time round (a fresh barrier reads as having
@@ -142,6 +197,8 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const __grid
   const size_t wbase = (size_t)row_tile * KBT + kb_lo;     // k-block index of this row tile in the packed arrays
   const uint8_t* xbase = a.Xt + ((size_t)tok_tile * KBT + kb_lo) * STAGE_BYTES;
 
+  [[maybe_unused]] long long t_entry = 0;
+  if constexpr (TRACE) t_entry = clock64();
   if (warp == 0) {
     tc::tmem_alloc(&tmem_base_s, 512);
     tc::tmem_relinquish();
@@ -173,20 +230,39 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const __grid
   const uint32_t tmem_a = tmem, tmem_d = tmem + NA * 8;    // A: NA x 8 columns; D: NSLOT x 128 columns
   constexpr uint32_t IDESC = tc::idesc_i8(128, NTOK);
   bool ok = true;
+  // TRACE instance only: timeline of the first 64 k-blocks of one CTA, one row per pipeline role (SM clock).  The stamps
+  // cost ~10 % of the kernel's time even when switched off at run time, hence a separate instance.
+  auto stamp = [&](int role, int b) {
+    if constexpr (TRACE) {
+      if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && b < 64) a.trace[role * 64 + b] = clock64();
+    }
+  };
+
+  if constexpr (TRACE) {
+    if (t == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) a.trace[10 * 64 + 0] = t_entry;
+  }
+  if (t == 0) stamp(10, 1);                                // set-up done (tensor memory, barriers)
 
   if (warp == W_COPY) {
     // ===================== bulk-copy producer (one thread) =====================
     if (lane == 0) {
       auto load_w = [&](int j) {                           // weight batch j -> slot j % WB
         const int s = j % WB;
+#if PF_ABLATE == 8 || PF_ABLATE == 9 || defined(PF_NOCOPY)
+        if (j >= WB) { tc::mbar_arrive(&w_full[s]); return; }
+#endif
         tc::mbar_expect_tx(&w_full[s], WBATCH_W + WBATCH_S);
         bulk_g2s(slabW + (size_t)s * WBATCH_W, a.Wt + (wbase + (size_t)j * 8) * 2048, WBATCH_W, &w_full[s]);
         bulk_g2s(slabS + (size_t)s * WBATCH_S, a.St + (wbase + (size_t)j * 8) * 128, WBATCH_S, &w_full[s]);
       };
       auto load_b = [&](int b) {                           // activation k-block b -> stage b % SB
         const int s = b % SB;
+#if PF_ABLATE == 7 || PF_ABLATE == 9 || defined(PF_NOCOPY)
+        if (b >= SB) { tc::mbar_arrive(&b_full[s]); stamp(0, b); return; }
+#endif
         tc::mbar_expect_tx(&b_full[s], STAGE_BYTES);
         bulk_g2s(stage + (size_t)s * STAGE_BYTES, xbase + (size_t)b * STAGE_BYTES, STAGE_BYTES, &b_full[s]);
+        stamp(0, b);
       };
       for (int j = 0; j < WB && j < NBATCH; ++j) load_w(j);   // weights do not depend on the previous kernel
       pdl_wait();                                             // activations do
@@ -211,15 +287,20 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const __grid
       const uint32_t stage0 = tc::smem_u32(stage);
       for (int b = 0; b < KB; ++b) {
         const int slot = b % NSLOT, s = b % SB, as = b % NA;
-        waitb(&a_full[as], (uint32_t)(b / NA) & 1u, ok);
-        waitb(&b_full[s], (uint32_t)(b / SB) & 1u, ok);
-        waitb(&d_empty[slot], ((uint32_t)(b / NSLOT) & 1u) ^ 1u, ok);   // the slot has been read out (k-block b - NSLOT)
+        stamp(6, b);
+        waitm(&a_full[as], (uint32_t)(b / NA) & 1u, ok);
+        stamp(7, b);
+        waitm(&b_full[s], (uint32_t)(b / SB) & 1u, ok);
+        stamp(8, b);
+        waitm(&d_empty[slot], ((uint32_t)(b / NSLOT) & 1u) ^ 1u, ok);   // the slot has been read out (k-block b - NSLOT)
+        stamp(9, b);
         tc::fence_after_sync();
         const uint64_t bdesc = tc::smem_desc_kmajor(stage0 + (uint32_t)s * STAGE_BYTES, 128, 256);
-        tc::mma_i8_ts(tmem_d + (uint32_t)slot * 128, tmem_a + (uint32_t)as * 8, bdesc, IDESC, 0u);
+        if (PF_ABLATE != 4 && PF_ABLATE != 12) tc::mma_i8_ts(tmem_d + (uint32_t)slot * 128, tmem_a + (uint32_t)as * 8, bdesc, IDESC, 0u);
         tc::mma_commit(&d_full[slot]);
         tc::mma_commit(&a_empty[as]);
         tc::mma_commit(&b_empty[s]);
+        stamp(2, b);
       }
     }
   } else if (warp >= NRW) {
@@ -228,21 +309,30 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const __grid
     const uint32_t lane_off = (uint32_t)(32 * (warp & 3)) << 16;
     for (int b = 0; b < KB; ++b) {
       const int ws = (b >> 3) % WB, as = b % NA;
-      if ((b & 7) == 0) waitb(&w_full[ws], (uint32_t)((b >> 3) / WB) & 1u, ok);
+      if ((b & 7) == 0) waitw(&w_full[ws], (uint32_t)((b >> 3) / WB) & 1u, ok, lane);
+#ifdef PF_NOEXP
+      uint32_t ex[8] = {};
+#else
       const uint4 w = *reinterpret_cast<const uint4*>(slabW + (size_t)ws * WBATCH_W + (size_t)(b & 7) * 2048 + r * 16);
       uint32_t ex[8];
       tc::expand_nibbles(w.x, ex[0], ex[1]);
       tc::expand_nibbles(w.y, ex[2], ex[3]);
       tc::expand_nibbles(w.z, ex[4], ex[5]);
       tc::expand_nibbles(w.w, ex[6], ex[7]);
-      waitb(&a_empty[as], ((uint32_t)(b / NA) & 1u) ^ 1u, ok);   // the MMA of k-block b - NA has read this operand
+#endif
+      waitw(&a_empty[as], ((uint32_t)(b / NA) & 1u) ^ 1u, ok, lane);   // the MMA of k-block b - NA has read this operand
       tc::fence_after_sync();
+#ifndef PF_NOEXP
       tc::tmem_st8(tmem_a + lane_off + (uint32_t)as * 8, ex);
       tc::tmem_wait_st();                                  // warp-wide
+#else
+      asm volatile("" ::"r"(ex[0]));
+#endif
       tc::fence_before_sync();
       if (lane == 0) {
         tc::mbar_arrive(&a_full[as]);
         if ((b & 7) == 7) tc::mbar_arrive(&w_empty[ws]);   // this warp is done with the batch's nibbles
+        if (warp == NRW) stamp(1, b);
       }
     }
 
@@ -259,6 +349,11 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const __grid
     // 16 columns of one k-block: exact int -> float through the magic constant (two integer adds per pair), then three
     // two-wide fp32 ops per pair: subtract the bias, scale product dw * dx, fused multiply-add
     auto fold16 = [&](const uint32_t* d, const ulonglong2* sx, uint64_t dw2, int half) {
+#if PF_ABLATE == 1 || PF_ABLATE == 3 || PF_ABLATE == 12
+#pragma unroll
+      for (int q = 0; q < 8; ++q) acc2[8 * half + q] ^= tc::pack2u(d[2 * q], d[2 * q + 1]);
+      return;
+#endif
 #pragma unroll
       for (int q = 0; q < 4; ++q) {
         const ulonglong2 x4 = sx[4 * half + q];            // four block scales = two packed pairs
@@ -273,16 +368,16 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const __grid
     // slower, the exposed read latency costs more than the earlier release gains.)
     uint32_t dA[16], dB[16];
     if (KB > 0) {
-      waitb(&w_full[0], 0u, ok);
-      waitb(&d_full[0], 0u, ok);
+      waitw(&w_full[0], 0u, ok, lane);
+      waitw(&d_full[0], 0u, ok, lane);
       tc::fence_after_sync();
-      tc::tmem_ld16(dbase, dA);
+      PF_LD(dbase, dA);
       tc::tmem_wait_ld();
     }
     int slot = 0, s = 0;                                   // b % NSLOT, b % SB, kept incrementally
     for (int b = 0; b < KB; ++b) {
       const int ws = (b >> 3) & (WB - 1);
-      tc::tmem_ld16(dbase + (uint32_t)slot * 128 + 16, dB);      // second half of k-block b
+      PF_LD(dbase + (uint32_t)slot * 128 + 16, dB);      // second half of k-block b
       const float dw = __half2float(reinterpret_cast<const __half*>(slabS + (size_t)ws * WBATCH_S)[(b & 7) * 128 + r]) * 0.0625f;
       const ulonglong2* sx = reinterpret_cast<const ulonglong2*>(stage + (size_t)s * STAGE_BYTES + 4096) + cq * 8;
       const uint64_t dw2 = tc::pack2(dw, dw);
@@ -290,27 +385,32 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const __grid
       tc::tmem_wait_ld();                                  // warp-wide: the slot is now entirely in registers
       tc::fence_before_sync();
       if (lane == 0) tc::mbar_arrive(&d_empty[slot]);      // one arrival per warp: the MMA of k-block b + NSLOT may overwrite it
+      if (warp == 0 && lane == 0) stamp(4, b);
       const int nb = b + 1, nslot = slot + 1 == NSLOT ? 0 : slot + 1;
       const uint32_t npar = (uint32_t)(nb / NSLOT) & 1u;
       bool requested = false;
       if (nb < KB) {
-        if ((nb & 7) == 0) waitb(&w_full[(nb >> 3) & (WB - 1)], (uint32_t)((nb >> 3) / WB) & 1u, ok);   // next batch's weight scales
-        if (tc::mbar_try(&d_full[nslot], npar)) {
+        if ((nb & 7) == 0) waitw(&w_full[(nb >> 3) & (WB - 1)], (uint32_t)((nb >> 3) / WB) & 1u, ok, lane);   // next batch's weight scales
+        // a look only (non-blocking), by one lane so that the warp-wide read-back below is entered uniformly
+        if (__shfl_sync(0xffffffffu, lane == 0 && tc::mbar_test(&d_full[nslot], npar) ? 1 : 0, 0)) {
           tc::fence_after_sync();
-          tc::tmem_ld16(dbase + (uint32_t)nslot * 128, dA);
+          PF_LD(dbase + (uint32_t)nslot * 128, dA);
           requested = true;
+          if (warp == 0 && lane == 0) stamp(3, nb);
         }
       }
       fold16(dB, sx, dw2, 1);
       __syncwarp();
+      if (warp == 0 && lane == 0) stamp(5, b);
       if (lane == 0) {
         tc::mbar_arrive(&b_empty[s]);                      // this warp is done with the stage's block scales
         if ((b & 7) == 7) tc::mbar_arrive(&w_empty[ws]);   // ... and with the weight batch's scales
       }
       if (nb < KB && !requested) {
-        waitb(&d_full[nslot], npar, ok);
+        waitw(&d_full[nslot], npar, ok, lane);
         tc::fence_after_sync();
-        tc::tmem_ld16(dbase + (uint32_t)nslot * 128, dA);
+        PF_LD(dbase + (uint32_t)nslot * 128, dA);
+        if (warp == 0 && lane == 0) stamp(3, nb);
       }
       tc::tmem_wait_ld();
       slot = nslot;
@@ -318,7 +418,9 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const __grid
     }
 
     // ---- epilogue: thread (row r, 32 activation rows)
+    if (t == 0) stamp(10, 2);                              // main loop left
     pdl_wait();                                            // Y / AUX may be written by the previous kernel
+    if (t == 0) stamp(10, 5);                              // previous grid seen complete
     const int row = row_tile * 128 + r;
     const int tok0 = tok_tile * NTOK + cq * 32;
     const float bias = ((a.epi == Q4B_EPI_BIASF || a.epi == Q4B_EPI_BIASF_ROPE_KV) && row < a.N) ? reinterpret_cast<const float*>(a.AUX)[row] : 0.f;
@@ -334,6 +436,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const __grid
         ybuf[(cq * 32 + n) * 128 + r] = __float2half_rn(v + bias);
       }
       asm volatile("bar.sync 1, %0;" ::"n"(NRW * 32) : "memory");
+      if (t == 0) stamp(10, 6);                            // rounded tile in shared memory
       rope_kv_phase(a, ybuf, row_tile, tok0, cq, r);
     } else if (a.epi == Q4B_EPI_SWIGLU_Q8) {
       // SwiGLU + re-quantise for `down` (lab/qwen_batched.py:1363-1396): the product rounded to fp16, then the Q8_1
@@ -343,45 +446,65 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const __grid
       // per 32-value block, instead of 32 warp-wide maxima per thread.
       __half* abuf = reinterpret_cast<__half*>(slabW);     // [token 128][product column 64]
 #pragma unroll
-      for (int n = 0; n < 32; ++n) {
-        const float v = (n & 1) ? tc::hi2(acc2[n >> 1]) : tc::lo2(acc2[n >> 1]);
-        const float partner = __shfl_xor_sync(0xffffffffu, v, 1);
-        if ((r & 1) == 0) abuf[(cq * 32 + n) * 64 + (r >> 1)] = __float2half_rn(row < a.N ? v / (1.f + __expf(-v)) * partner : 0.f);
+      for (int j = 0; j < 16; ++j) {
+        int n;
+        const float prod = swiglu_pair(acc2[j], r, j, n);
+        abuf[(cq * 32 + n) * 64 + (r >> 1)] = __float2half_rn(row < a.N ? prod : 0.f);
       }
       asm volatile("bar.sync 1, %0;" ::"n"(NRW * 32) : "memory");
+      if (t == 0) stamp(10, 6);                            // rounded tile in shared memory
       swiglu_q8_phase(a, abuf, row_tile, tok_tile, t);
+    } else if (a.epi == Q4B_EPI_SWIGLU) {
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        int n;
+        const float prod = swiglu_pair(acc2[j], r, j, n);
+        const int p = tok0 + n;
+        if (p < a.P && row < a.N) reinterpret_cast<__half*>(a.Y)[(size_t)p * a.ldy + (row >> 1)] = __float2half_rn(prod);
+      }
+    } else if (a.epi == Q4B_EPI_RESID && blockIdx.z == 0) {
+      // h += sum: all 32 loads first (issued back to back), then the adds and stores; one load-add-store per token in turn
+      // would pay the global-memory latency 32 times over, the loads being ordered behind the stores to the same array
+      float* y = reinterpret_cast<float*>(a.Y) + (size_t)tok0 * a.ldy + row;
+      float old[32];
+#pragma unroll
+      for (int n = 0; n < 32; ++n) old[n] = (tok0 + n < a.P && row < a.N) ? y[(size_t)n * a.ldy] : 0.f;
+#pragma unroll
+      for (int n = 0; n < 32; ++n) {
+        const float v = (n & 1) ? tc::hi2(acc2[n >> 1]) : tc::lo2(acc2[n >> 1]);
+        if (tok0 + n < a.P && row < a.N) y[(size_t)n * a.ldy] = old[n] + v;
+      }
     } else {
 #pragma unroll
     for (int n = 0; n < 32; ++n) {                         // fully unrolled: the accumulators must stay in registers
       const float v = (n & 1) ? tc::hi2(acc2[n >> 1]) : tc::lo2(acc2[n >> 1]);
-      const float partner = __shfl_xor_sync(0xffffffffu, v, 1);
       const int p = tok0 + n;
       if (p < a.P && row < a.N) {
         const size_t base = (size_t)p * a.ldy;
         switch (a.epi) {
           case Q4B_EPI_STORE: reinterpret_cast<__half*>(a.Y)[base + row] = __float2half_rn(v); break;
           case Q4B_EPI_BIASF: reinterpret_cast<__half*>(a.Y)[base + row] = __float2half_rn(v + bias); break;
-          case Q4B_EPI_RESID:
-            if (blockIdx.z) a.Y2[(size_t)(blockIdx.z - 1) * a.P * a.ldy + base + row] = v;
-            else reinterpret_cast<float*>(a.Y)[base + row] += v;
-            break;
+          case Q4B_EPI_RESID: a.Y2[(size_t)(blockIdx.z - 1) * a.P * a.ldy + base + row] = v; break;   // part z > 0 of a split launch
           case Q4B_EPI_LOGITS: reinterpret_cast<float*>(a.Y)[base + row] = v; break;
-          case Q4B_EPI_SWIGLU:
-            if ((r & 1) == 0) reinterpret_cast<__half*>(a.Y)[base + (row >> 1)] = __float2half_rn(v / (1.f + __expf(-v)) * partner);
-            break;
           default: break;
         }
       }
     }
     }
   }
+  if (t == 0) stamp(10, 3);                                // epilogue written
   if (!ok) atomicExch(a.status, 1u);
   tc::fence_before_sync();
   __syncthreads();
   if (warp == 0) tc::tmem_dealloc(tmem, 512);
+  if (t == 0) stamp(10, 4);                                // tensor memory released
 }
 
+long long* g_prefill_trace = nullptr;
+
 }  // namespace
+
+void mmq_prefill_trace(long long* buf) { g_prefill_trace = buf; }
 
 size_t q8_tiled_bytes(int P, int K) { return (size_t)((P + NTOK - 1) / NTOK) * (size_t)(K / 32) * STAGE_BYTES; }
 
@@ -402,7 +525,8 @@ int mmq_prefill(const void* Wt, const void* St, const void* Xt, void* Y, const v
   if (!Wt || !St || !Xt || !Y || !status || !aligned16(Wt) || !aligned16(St) || !aligned16(Xt))
     return fail(Q4B_E_ALIGN, "mmq_prefill: null or misaligned pointer");
   if (epilogue == Q4B_EPI_BIASF && !AUX) return fail(Q4B_E_ALIGN, "mmq_prefill: biasf needs AUX");
-  if (cudaError_t e = ensure_dynamic_smem(reinterpret_cast<const void*>(&mmq_prefill_kernel), PF_SMEM); e != cudaSuccess) {
+  auto kern = g_prefill_trace ? mmq_prefill_kernel<true> : mmq_prefill_kernel<false>;
+  if (cudaError_t e = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), PF_SMEM); e != cudaSuccess) {
     set_cuda_error(e, "mmq_prefill: cudaFuncSetAttribute");
     return Q4B_E_CUDA;
   }
@@ -426,6 +550,7 @@ int mmq_prefill(const void* Wt, const void* St, const void* Xt, void* Y, const v
   a.NKV = NKV;
   a.max_len = max_len;
   a.pos0 = pos0;
+  a.trace = g_prefill_trace;
   a.Y2 = Y2;
   a.kb_bound[0] = 0;
   a.kb_bound[1] = a.kb_bound[2] = a.kb_bound[3] = a.kb_bound[4] = K / 32;
@@ -437,7 +562,7 @@ int mmq_prefill(const void* Wt, const void* St, const void* Xt, void* Y, const v
     for (int z = 1; z < parts; ++z) a.kb_bound[z] = (int)(((long long)batches * z + parts - 1) / parts) * 8;
     grid.z = parts;
   }
-  return check_launch(launch_pdl(mmq_prefill_kernel, grid, dim3(PF_THREADS), PF_SMEM, st, a), "mmq_prefill");
+  return check_launch(launch_pdl(kern, grid, dim3(PF_THREADS), PF_SMEM, st, a), "mmq_prefill");
 }
 
 }  // namespace q4b

@@ -39,6 +39,17 @@ __device__ __forceinline__ bool mbar_try(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// Non-blocking test of a phase: returns at once either way (try_wait may suspend the thread for a hardware-chosen slice
+// when the phase is not complete, which is wrong for an opportunistic look).
+__device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred P;\n\tmbarrier.test_wait.parity.shared::cta.b64 P, [%1], %2;\n\tselp.b32 %0, 1, 0, P;\n\t}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
 // try_wait with a suspend-time hint: the thread may sleep up to `ns` nanoseconds and is woken when the phase completes.
 // Waiting warps then stay out of the issue slots of the working warps on their scheduler.
 __device__ __forceinline__ bool mbar_try_hint(uint64_t* bar, uint32_t parity, uint32_t ns) {
@@ -55,6 +66,17 @@ constexpr uint32_t WAIT_LIMIT = 1u << 22;
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
   for (uint32_t i = 0; i < WAIT_LIMIT; ++i)
     if (mbar_try(bar, parity)) return true;
+  return false;
+}
+// The same bound (about a second, by the SM clock) for waits whose failed tries suspend for up to `ns` nanoseconds each: a
+// try_wait without the hint comes back within ~100 clocks and the retry loop around it then fills the issue slots of the
+// warps that have work; with it a waiting thread costs a handful of instructions per wait and is woken by the completion.
+__device__ __forceinline__ bool mbar_wait_parked(uint64_t* bar, uint32_t parity, uint32_t ns = 200000u) {
+  if (mbar_try_hint(bar, parity, ns)) return true;
+  const long long t0 = clock64();
+  do {
+    if (mbar_try_hint(bar, parity, ns)) return true;
+  } while (clock64() - t0 < (1ll << 31));
   return false;
 }
 

@@ -12,6 +12,7 @@ launch has no programmatic overlap with its neighbours and its weights sit in L2
     python 3080lab_b200/timeline.py attn --batch 32   # batched decode attention, 1024-token context
     python 3080lab_b200/timeline.py persistent        # one token through the persistent all-layers kernel (8 layers)
     python 3080lab_b200/timeline.py chain             # one captured batch-1 decode step of the full 1.5B shape, launch by launch
+    python 3080lab_b200/timeline.py prefill           # pipeline roles of one CTA of the prefill GEMM (gate/up shape), per k-block
 
 `chain` uses `q4b_trace_chain`: every GEMV / attention launch of the captured step keeps its own stamp region, so the
 replayed graph shows when each launch's CTAs start (how far ahead of their dependency wait they move in), when the wait
@@ -121,9 +122,82 @@ def _chain(torch, synth, engine, ffi) -> None:
               f" {(last - t00) / 1e3:20.2f}   {np.round(np.median(rel, axis=0), 2).tolist()}")
 
 
+def _prefill(torch, ffi) -> None:
+    """SM-clock stamps of CTA (0, 0, 0) of one gate/up-shaped prefill GEMM (`q4b_mmq_prefill_trace`): per k-block, when each
+    pipeline role got to it.  Printed as clocks since the first stamp, and the steady-state period of every role."""
+    QB = importlib.import_module("3080lab_b200.qwen_batched")
+    rng = np.random.default_rng(0)
+    n, k, P = 17920, 1536, 2048
+    W = torch.from_numpy(rng.integers(0, 2 ** 32, size=(n, k // 8), dtype=np.uint32).view(np.int32)).cuda()
+    S = torch.from_numpy(rng.uniform(0.002, 0.02, size=(n, k // 32)).astype(np.float16)).cuda()
+    Wt, St = QB.pack_q4(W, S)
+    x = torch.randn(P, k, device="cuda").half()
+    xt = QB.q8_tiled_buffer(P, k, "cuda")
+    QB.quant_q8_tiled(x, xt)
+    y = torch.zeros(P, n // 2, dtype=torch.float16, device="cuda")
+    st = QB.Status("cuda")
+    for _ in range(2):
+        QB.gemm8_prefill(Wt, St, xt, y, None, n, k, P, "swiglu", n // 2, st)
+    buf = torch.zeros(11 * 64, dtype=torch.int64, device="cuda")
+    torch.cuda.synchronize()
+    ffi.call("q4b_mmq_prefill_trace", buf.data_ptr(), buf.numel())
+    QB.gemm8_prefill(Wt, St, xt, y, None, n, k, P, "swiglu", n // 2, st)
+    torch.cuda.synchronize()
+    ffi.call("q4b_mmq_prefill_trace", None, 0)
+    st.check()
+    full = buf.cpu().numpy().reshape(11, 64).astype(np.int64)
+    t = full[:, :k // 32]
+    t0 = t[t > 0].min()
+    names = ["stage requested", "A operand written", "MMA issued", "accumulator seen", "slot handed back", "folded"]
+    print("clocks since the first stamp; k-blocks 0..47 of CTA (0,0,0), gate/up shape 2048 x 17920 x 1536")
+    for r, nm in enumerate(names):
+        row = t[r] - t0
+        per = np.diff(row[16:44])
+        print(f"{nm:20s} period median {np.median(per):7.0f} (min {per.min():.0f}, max {per.max():.0f})   first 12: {row[:12].tolist()}")
+    w = lambda a, b: (float(np.median((t[b] - t[a])[16:44])), (t[b] - t[a])[:6].tolist())
+    print("MMA issuer, clocks spent per k-block (median over k-blocks 16..43; first six k-blocks):")
+    print(f"  waiting for the A operand {w(6, 7)}; for the activation stage {w(7, 8)}; for a free accumulator slot {w(8, 9)}; "
+          f"issue + commits {w(9, 2)}")
+    def phases(name, full, kb):
+        ph = full[10, :7]
+        mid = f"(of which: wait for the previous grid {ph[5] - ph[2]}, tile through shared memory {ph[6] - ph[5]}) " if ph[6] else f"(of which: wait for the previous grid {ph[5] - ph[2]}) "
+        print(f"phases of the CTA [{name}], clocks: entry -> set-up done {ph[1] - ph[0]}; -> first activation stage requested {full[0, 0] - ph[1]}; "
+              f"-> first MMA issued {full[2, 0] - full[0, 0]}; -> first k-block folded {full[5, 0] - full[2, 0]}; "
+              f"k-block {min(kb, 64) - 1} folded at {full[5, min(kb, 64) - 1] - ph[0]}; main loop left at {ph[2] - ph[0]}; -> epilogue written {ph[3] - ph[2]} {mid}"
+              f"-> tensor memory released {ph[4] - ph[3]}; whole CTA {ph[4] - ph[0]}")
+
+    phases("gate/up, swiglu", full, k // 32)
+    # the other launches of a prefill layer: phases only
+    def traced(fn):
+        for _ in range(2):
+            fn()
+        buf.zero_()
+        torch.cuda.synchronize()
+        ffi.call("q4b_mmq_prefill_trace", buf.data_ptr(), buf.numel())
+        fn()
+        torch.cuda.synchronize()
+        ffi.call("q4b_mmq_prefill_trace", None, 0)
+        return buf.cpu().numpy().reshape(11, 64).astype(np.int64)
+
+    xt2 = QB.q8_tiled_buffer(P, n // 2, "cuda")
+    phases("gate/up, swiglu_q8", traced(lambda: QB.gemm8_prefill(Wt, St, xt, xt2, None, n, k, P, "swiglu_q8", n // 2, st)), k // 32)
+    Wo, So = QB.pack_q4(W[:1536].contiguous(), S[:1536].contiguous())
+    h = torch.zeros(P, 1536, device="cuda")
+    phases("o_proj, resid", traced(lambda: QB.gemm8_prefill(Wo, So, xt, h, None, 1536, k, P, "resid", 1536, st)), k // 32)
+    Wq, Sq = QB.pack_q4(W[:2048].contiguous(), S[:2048].contiguous())
+    qkv = torch.zeros(P, 2048, dtype=torch.float16, device="cuda")
+    bias = torch.zeros(2048, device="cuda")
+    phases("qkv, biasf", traced(lambda: QB.gemm8_prefill(Wq, Sq, xt, qkv, bias, 2048, k, P, "biasf", 2048, st)), k // 32)
+    st.check()
+    print("lags per k-block (median over k-blocks 16..43), clocks:")
+    lag = lambda a, b: float(np.median((t[b] - t[a])[16:44]))
+    print(f"  A written -> MMA issued {lag(1, 2):.0f}; MMA issued -> accumulator seen {lag(2, 3):.0f}; seen -> slot handed back {lag(3, 4):.0f}; "
+          f"handed back -> folded {lag(4, 5):.0f}; stage requested -> MMA issued {lag(0, 2):.0f}")
+
+
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("what", choices=["gemv", "mmq", "attn", "persistent", "chain"])
+    ap.add_argument("what", choices=["gemv", "mmq", "attn", "persistent", "chain", "prefill"])
     ap.add_argument("--batch", type=int, default=32)
     ap.add_argument("--tcgen05", action="store_true", help="gemv: the tcgen05 exact-digit kernel instead of the mma.sync one")
     args = ap.parse_args()
@@ -131,6 +205,10 @@ def main() -> None:
     synth, engine, ffi, K = _mods()
     if args.what == "chain":
         _chain(torch, synth, engine, ffi)
+        return
+    if args.what == "prefill":
+        K.init(0)
+        _prefill(torch, ffi)
         return
     layers = 8 if args.what == "persistent" else 2
     cfg = synth.ModelConfig("qwen2.5-1.5b-cut", layers, 1536, 8960, 12, 2, 128, 8192)

@@ -287,6 +287,15 @@ int q4b_mmq_prefill_qkv_rope_kv(const void* Wt, const void* St, const void* xt, 
 int q4b_attn_prefill_cached(const void* qkv, const void* kc, const void* vc, void* out, void* xt, int P, int NH, int NKV,
                             int HD, int max_len, int pos0, float scale, q4b_stream_t stream);
 
+/* Pipeline timeline of the prefill GEMM: while a device buffer of 11 x 64 int64 is set, every q4b_mmq_prefill_* launch
+ * runs a second instance of the kernel whose CTA (0, 0, 0) writes SM-clock stamps for its first 64 k-blocks, one row per
+ * event: 0 activation stage requested, 1 A operand written (first expander warp), 2 MMA issued and committed, 3 accumulator
+ * seen complete by the first rescale warp, 4 that warp has read it out (slot handed back), 5 that warp has folded it,
+ * 6 .. 9 the MMA issuer before its waits for the A operand, the activation stage, a free accumulator slot, and after them;
+ * row 10 holds the CTA's phases: entry, set-up done, main loop left, epilogue written, tensor memory released.
+ * Null switches back to the plain instance (the default).  Used by `3080lab_b200/timeline.py prefill`. */
+int q4b_mmq_prefill_trace(int64_t* device_buffer, size_t entries);
+
 /* The residual-adding prefill GEMM with its launch split along K into `parts` (2 .. 4) CTAs per output tile: Y += part 0,
  * Y2[z - 1] = part z (fp32 [parts - 1][P, ldy], overwritten).  o_proj and down_proj have 12 row tiles x P / 128 token
  * tiles = 192 CTAs on 148 SMs at P = 2048; as 384 half-length CTAs they fill the machine in 1.5 instead of 2 rounds, as 576
