@@ -30,22 +30,6 @@
 #include "q4b_internal.h"
 #include "tc05.cuh"
 
-#ifndef PF_ABLATE
-#define PF_ABLATE 0
-#endif
-#if PF_ABLATE == 12
-#define PF_NOEXP 1
-#define PF_NOCOPY 1
-#define PF_NOMMA 1
-#endif
-#if PF_ABLATE == 11
-#define PF_NOEXP 1
-#endif
-#if PF_ABLATE == 2 || PF_ABLATE == 3 || PF_ABLATE == 12
-#define PF_LD(addr, regs) do { _Pragma("unroll") for (int i_ = 0; i_ < 16; ++i_) asm volatile("" : "+r"(regs[i_])); } while (0)
-#else
-#define PF_LD(addr, regs) tc::tmem_ld16(addr, regs)
-#endif
 namespace q4b {
 
 namespace {
@@ -71,6 +55,7 @@ struct PrefillArgs {
   const void* AUX;
   uint32_t* status;
   int N, K, P, epi, ldy;
+  int pair16;          // fp16 outputs may go out two rows at a time (N, ldy even, Y 4-byte aligned)
   long long* trace;    // per-role clock stamps of CTA (0, 0, 0), [11][64] (see q4b_mmq_prefill_trace); null = off
   float* Y2;           // split launch: where parts 1 .. of K store their sums, fp32 [parts - 1][P, ldy]
   int kb_bound[5];     // k-block bounds of the parts (multiples of 8); unsplit: {0, K / 32}
@@ -89,35 +74,18 @@ __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t by
                : "memory");
 }
 
-// wait unless an earlier wait of this thread already expired
+// Wait unless an earlier wait of this thread already expired.  Worker warps call it with all 32 lanes (one polling lane
+// plus a warp barrier was measured 4 % slower); the tries park the thread (suspend hint) instead of spinning, which was
+// worth little by itself but keeps waiting warps out of the issue slots.
 __device__ __forceinline__ void waitb(uint64_t* bar, uint32_t parity, bool& ok) {
-#if PF_ABLATE == 10
-  if (ok) ok = tc::mbar_wait(bar, parity);
-#else
   if (ok) ok = tc::mbar_wait_parked(bar, parity);
-#endif
 }
-__device__ __forceinline__ void waitm(uint64_t* bar, uint32_t parity, bool& ok) {
-#if PF_ABLATE == 6
-  if (ok) {
-    ok = false;
-    for (uint32_t i = 0; i < (1u << 24); ++i)
-      if (tc::mbar_test(bar, parity)) { ok = true; break; }
-  }
-#else
-  waitb(bar, parity, ok);
-#endif
-}
-// Warp-wide wait with ONE polling lane: the others park at the warp barrier, which also orders their later reads after the
-// phase completion lane 0 observed.  (With all 32 lanes of 20 warps polling, every mbarrier operation of the CTA - the MMA
-// issuer's included - queued behind the polls in the shared-memory pipe.)  Only lane 0's `ok` can turn false.
-__device__ __forceinline__ void waitw(uint64_t* bar, uint32_t parity, bool& ok, int lane) {
-#if PF_ABLATE == 5
-  waitb(bar, parity, ok);
-#else
-  if (lane == 0) waitb(bar, parity, ok);
-  __syncwarp();
-#endif
+// Bits of float(12582912 + d) for -2^22 <= d < 2^22 without an addition: the low 22 bits of d, bit 22 inverted, 0x4B0 on
+// top.  One LOP3 with two constant operands that select, per bit, (b, c) = (0,0) d, (0,1) ~d, (1,0) 0, (1,1) 1.
+__device__ __forceinline__ uint32_t magic_lop(uint32_t d) {
+  uint32_t r;
+  asm("lop3.b32 %0, %1, %2, %3, 0x9A;" : "=r"(r) : "r"(d), "r"(0xFF800000u), "r"(0x4B400000u));
+  return r;
 }
 // SwiGLU of one gate/up row pair (adjacent TMEM lanes = adjacent threads) for the token pair (2 j, 2 j + 1) held in `acc`:
 // the even lane takes token 2 j, the odd lane token 2 j + 1, so each lane evaluates 16 of the 32 products (one exchange
@@ -131,33 +99,45 @@ __device__ __forceinline__ float swiglu_pair(uint64_t acc, int r, int j, int& n)
   return g / (1.f + __expf(-g)) * u;
 }
 // Second halves of the two fused epilogues, kept out of line so that they cost the main loop no registers.
-// RoPE + cache write from the rounded tile in shared memory: thread = (row r of the head, 32 tokens from tok0).
-__device__ __noinline__ void rope_kv_phase(const PrefillArgs& a, const __half* ybuf, int head, int tok0, int cq, int r) {
-  const int dd = r & 63, row = head * 128 + r;
-#pragma unroll 8
-  for (int n = 0; n < 32; ++n) {
-    const int p = tok0 + n, pos = a.pos0 + p;
+// RoPE + cache write from the rounded tile in shared memory: thread = (row pair 2 pr, 2 pr + 1 of the head, 16 tokens), so
+// that every access is a 4-byte one and a warp's stores cover 128 contiguous bytes (2-byte stores, one row per thread,
+// were measured at ~20 clocks per warp store).
+__device__ __noinline__ void rope_kv_phase(const PrefillArgs& a, const __half* ybuf, int head, int tok_base, int t) {
+  const int r = 2 * (t & 63), dd = r & 63, row = head * 128 + r;
+  const bool rotate = head < a.NH + a.NKV, upper = r >= 64;
+#pragma unroll 4
+  for (int n = 0; n < 16; ++n) {
+    const int tl = (t >> 6) * 16 + n, p = tok_base + tl, pos = a.pos0 + p;
     if (p >= a.P || pos >= a.max_len) continue;
-    const __half y16 = ybuf[(cq * 32 + n) * 128 + r];
-    __half outv = y16;
-    if (head < a.NH + a.NKV) {
-      const float mine = __half2float(y16), other = __half2float(ybuf[(cq * 32 + n) * 128 + (r ^ 64)]);
-      const float c = a.cosT[(size_t)pos * 64 + dd], s = a.sinT[(size_t)pos * 64 + dd];
-      float lo, hi;
-      if (r < 64) rope_pair(mine, other, c, s, lo, hi);
-      else rope_pair(other, mine, c, s, lo, hi);
-      outv = __float2half_rn(r < 64 ? lo : hi);
+    __half2 outv = *reinterpret_cast<const __half2*>(ybuf + tl * 128 + r);
+    if (rotate) {
+      const float2 mine = __half22float2(outv);
+      const float2 other = __half22float2(*reinterpret_cast<const __half2*>(ybuf + tl * 128 + (r ^ 64)));
+      const float2 c = __ldg(reinterpret_cast<const float2*>(a.cosT + (size_t)pos * 64 + dd));   // read-only path: free to move above the stores
+      const float2 s = __ldg(reinterpret_cast<const float2*>(a.sinT + (size_t)pos * 64 + dd));
+      float lo0, hi0, lo1, hi1;
+      if (!upper) {
+        rope_pair(mine.x, other.x, c.x, s.x, lo0, hi0);
+        rope_pair(mine.y, other.y, c.y, s.y, lo1, hi1);
+        outv = __floats2half2_rn(lo0, lo1);
+      } else {
+        rope_pair(other.x, mine.x, c.x, s.x, lo0, hi0);
+        rope_pair(other.y, mine.y, c.y, s.y, lo1, hi1);
+        outv = __floats2half2_rn(hi0, hi1);
+      }
     }
-    reinterpret_cast<__half*>(a.Y)[(size_t)p * a.ldy + row] = outv;
-    if (head >= a.NH + a.NKV) a.vc[((size_t)(head - a.NH - a.NKV) * a.max_len + pos) * 128 + r] = outv;
-    else if (head >= a.NH) a.kc[((size_t)(head - a.NH) * a.max_len + pos) * 128 + r] = outv;
+    *reinterpret_cast<__half2*>(reinterpret_cast<__half*>(a.Y) + (size_t)p * a.ldy + row) = outv;
+    if (head >= a.NH + a.NKV) *reinterpret_cast<__half2*>(a.vc + ((size_t)(head - a.NH - a.NKV) * a.max_len + pos) * 128 + r) = outv;
+    else if (head >= a.NH) *reinterpret_cast<__half2*>(a.kc + ((size_t)(head - a.NH) * a.max_len + pos) * 128 + r) = outv;
   }
 }
 
 // Q8_1 quantiser over the rounded SwiGLU products in shared memory: 128 tokens x 2 blocks x 8 lanes = 4 tasks per thread.
+// The two records (k-blocks 2 row_tile, 2 row_tile + 1 of this token tile; adjacent in the operand) are put together in
+// shared memory behind the products and leave as 16-byte stores: the quantiser's own stores are 2 bytes wide and scattered.
 __device__ __noinline__ void swiglu_q8_phase(const PrefillArgs& a, const __half* abuf, int row_tile, int tok_tile, int t) {
   const int KB2 = a.N >> 6;                                // k-blocks of the product row
-  uint8_t* rec0 = reinterpret_cast<uint8_t*>(a.Y) + ((size_t)tok_tile * KB2 + (size_t)row_tile * 2) * STAGE_BYTES;
+  uint8_t* rec = reinterpret_cast<uint8_t*>(const_cast<__half*>(abuf)) + 128 * 64 * 2;   // [2][STAGE_BYTES]
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
     const int task = t + j * (NRW * 32);
@@ -166,8 +146,12 @@ __device__ __noinline__ void swiglu_q8_phase(const PrefillArgs& a, const __half*
     const float2 lo = __half22float2(*reinterpret_cast<const __half2*>(&raw.x));
     const float2 hi = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
     const float x4[4] = {lo.x, lo.y, hi.x, hi.y};
-    quant_block4_tiled(x4, rec0 + (size_t)hb * STAGE_BYTES, nn, sub);
+    quant_block4_tiled(x4, rec + (size_t)hb * STAGE_BYTES, nn, sub);
   }
+  asm volatile("bar.sync 1, %0;" ::"n"(NRW * 32) : "memory");
+  uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(a.Y) + ((size_t)tok_tile * KB2 + (size_t)row_tile * 2) * STAGE_BYTES);
+  const uint4* src = reinterpret_cast<const uint4*>(rec);
+  for (int i = t; i < 2 * (int)STAGE_BYTES / 16; i += NRW * 32) dst[i] = src[i];
 }
 
 template <bool TRACE>
@@ -248,18 +232,12 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const __grid
     if (lane == 0) {
       auto load_w = [&](int j) {                           // weight batch j -> slot j % WB
         const int s = j % WB;
-#if PF_ABLATE == 8 || PF_ABLATE == 9 || defined(PF_NOCOPY)
-        if (j >= WB) { tc::mbar_arrive(&w_full[s]); return; }
-#endif
         tc::mbar_expect_tx(&w_full[s], WBATCH_W + WBATCH_S);
         bulk_g2s(slabW + (size_t)s * WBATCH_W, a.Wt + (wbase + (size_t)j * 8) * 2048, WBATCH_W, &w_full[s]);
         bulk_g2s(slabS + (size_t)s * WBATCH_S, a.St + (wbase + (size_t)j * 8) * 128, WBATCH_S, &w_full[s]);
       };
       auto load_b = [&](int b) {                           // activation k-block b -> stage b % SB
         const int s = b % SB;
-#if PF_ABLATE == 7 || PF_ABLATE == 9 || defined(PF_NOCOPY)
-        if (b >= SB) { tc::mbar_arrive(&b_full[s]); stamp(0, b); return; }
-#endif
         tc::mbar_expect_tx(&b_full[s], STAGE_BYTES);
         bulk_g2s(stage + (size_t)s * STAGE_BYTES, xbase + (size_t)b * STAGE_BYTES, STAGE_BYTES, &b_full[s]);
         stamp(0, b);
@@ -288,15 +266,15 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const __grid
       for (int b = 0; b < KB; ++b) {
         const int slot = b % NSLOT, s = b % SB, as = b % NA;
         stamp(6, b);
-        waitm(&a_full[as], (uint32_t)(b / NA) & 1u, ok);
+        waitb(&a_full[as], (uint32_t)(b / NA) & 1u, ok);
         stamp(7, b);
-        waitm(&b_full[s], (uint32_t)(b / SB) & 1u, ok);
+        waitb(&b_full[s], (uint32_t)(b / SB) & 1u, ok);
         stamp(8, b);
-        waitm(&d_empty[slot], ((uint32_t)(b / NSLOT) & 1u) ^ 1u, ok);   // the slot has been read out (k-block b - NSLOT)
+        waitb(&d_empty[slot], ((uint32_t)(b / NSLOT) & 1u) ^ 1u, ok);   // the slot has been read out (k-block b - NSLOT)
         stamp(9, b);
         tc::fence_after_sync();
         const uint64_t bdesc = tc::smem_desc_kmajor(stage0 + (uint32_t)s * STAGE_BYTES, 128, 256);
-        if (PF_ABLATE != 4 && PF_ABLATE != 12) tc::mma_i8_ts(tmem_d + (uint32_t)slot * 128, tmem_a + (uint32_t)as * 8, bdesc, IDESC, 0u);
+        tc::mma_i8_ts(tmem_d + (uint32_t)slot * 128, tmem_a + (uint32_t)as * 8, bdesc, IDESC, 0u);
         tc::mma_commit(&d_full[slot]);
         tc::mma_commit(&a_empty[as]);
         tc::mma_commit(&b_empty[s]);
@@ -309,25 +287,17 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const __grid
     const uint32_t lane_off = (uint32_t)(32 * (warp & 3)) << 16;
     for (int b = 0; b < KB; ++b) {
       const int ws = (b >> 3) % WB, as = b % NA;
-      if ((b & 7) == 0) waitw(&w_full[ws], (uint32_t)((b >> 3) / WB) & 1u, ok, lane);
-#ifdef PF_NOEXP
-      uint32_t ex[8] = {};
-#else
+      if ((b & 7) == 0) waitb(&w_full[ws], (uint32_t)((b >> 3) / WB) & 1u, ok);
       const uint4 w = *reinterpret_cast<const uint4*>(slabW + (size_t)ws * WBATCH_W + (size_t)(b & 7) * 2048 + r * 16);
       uint32_t ex[8];
       tc::expand_nibbles(w.x, ex[0], ex[1]);
       tc::expand_nibbles(w.y, ex[2], ex[3]);
       tc::expand_nibbles(w.z, ex[4], ex[5]);
       tc::expand_nibbles(w.w, ex[6], ex[7]);
-#endif
-      waitw(&a_empty[as], ((uint32_t)(b / NA) & 1u) ^ 1u, ok, lane);   // the MMA of k-block b - NA has read this operand
+      waitb(&a_empty[as], ((uint32_t)(b / NA) & 1u) ^ 1u, ok);   // the MMA of k-block b - NA has read this operand
       tc::fence_after_sync();
-#ifndef PF_NOEXP
       tc::tmem_st8(tmem_a + lane_off + (uint32_t)as * 8, ex);
       tc::tmem_wait_st();                                  // warp-wide
-#else
-      asm volatile("" ::"r"(ex[0]));
-#endif
       tc::fence_before_sync();
       if (lane == 0) {
         tc::mbar_arrive(&a_full[as]);
@@ -349,15 +319,12 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const __grid
     // 16 columns of one k-block: exact int -> float through the magic constant (two integer adds per pair), then three
     // two-wide fp32 ops per pair: subtract the bias, scale product dw * dx, fused multiply-add
     auto fold16 = [&](const uint32_t* d, const ulonglong2* sx, uint64_t dw2, int half) {
-#if PF_ABLATE == 1 || PF_ABLATE == 3 || PF_ABLATE == 12
-#pragma unroll
-      for (int q = 0; q < 8; ++q) acc2[8 * half + q] ^= tc::pack2u(d[2 * q], d[2 * q + 1]);
-      return;
-#endif
 #pragma unroll
       for (int q = 0; q < 4; ++q) {
         const ulonglong2 x4 = sx[4 * half + q];            // four block scales = two packed pairs
-        const uint64_t f0 = tc::add2(tc::pack2u(d[4 * q + 0] + tc::I2F_MAGIC, d[4 * q + 1] + tc::I2F_MAGIC), neg_bias);
+        // the first pair through one LOP3 each (logic pipe), the second through an integer add (which the compiler puts on
+        // the fp32 pipe as IMAD): splitting them evens out the two pipes, measured 1.5 % over adds only (all-LOP3: 0.7 %)
+        const uint64_t f0 = tc::add2(tc::pack2u(magic_lop(d[4 * q + 0]), magic_lop(d[4 * q + 1])), neg_bias);
         const uint64_t f1 = tc::add2(tc::pack2u(d[4 * q + 2] + tc::I2F_MAGIC, d[4 * q + 3] + tc::I2F_MAGIC), neg_bias);
         acc2[8 * half + 2 * q + 0] = tc::fma2(tc::mul2(dw2, x4.x), f0, acc2[8 * half + 2 * q + 0]);
         acc2[8 * half + 2 * q + 1] = tc::fma2(tc::mul2(dw2, x4.y), f1, acc2[8 * half + 2 * q + 1]);
@@ -368,16 +335,16 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const __grid
     // slower, the exposed read latency costs more than the earlier release gains.)
     uint32_t dA[16], dB[16];
     if (KB > 0) {
-      waitw(&w_full[0], 0u, ok, lane);
-      waitw(&d_full[0], 0u, ok, lane);
+      waitb(&w_full[0], 0u, ok);
+      waitb(&d_full[0], 0u, ok);
       tc::fence_after_sync();
-      PF_LD(dbase, dA);
+      tc::tmem_ld16(dbase, dA);
       tc::tmem_wait_ld();
     }
     int slot = 0, s = 0;                                   // b % NSLOT, b % SB, kept incrementally
     for (int b = 0; b < KB; ++b) {
       const int ws = (b >> 3) & (WB - 1);
-      PF_LD(dbase + (uint32_t)slot * 128 + 16, dB);      // second half of k-block b
+      tc::tmem_ld16(dbase + (uint32_t)slot * 128 + 16, dB);      // second half of k-block b
       const float dw = __half2float(reinterpret_cast<const __half*>(slabS + (size_t)ws * WBATCH_S)[(b & 7) * 128 + r]) * 0.0625f;
       const ulonglong2* sx = reinterpret_cast<const ulonglong2*>(stage + (size_t)s * STAGE_BYTES + 4096) + cq * 8;
       const uint64_t dw2 = tc::pack2(dw, dw);
@@ -390,11 +357,13 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const __grid
       const uint32_t npar = (uint32_t)(nb / NSLOT) & 1u;
       bool requested = false;
       if (nb < KB) {
-        if ((nb & 7) == 0) waitw(&w_full[(nb >> 3) & (WB - 1)], (uint32_t)((nb >> 3) / WB) & 1u, ok, lane);   // next batch's weight scales
-        // a look only (non-blocking), by one lane so that the warp-wide read-back below is entered uniformly
+        if ((nb & 7) == 0) waitb(&w_full[(nb >> 3) & (WB - 1)], (uint32_t)((nb >> 3) / WB) & 1u, ok);   // next batch's weight scales
+        // A look only (non-blocking), by one lane so that the warp-wide read-back below is entered uniformly.  Measured
+        // alternatives: all lanes looking + a vote (7 % slower); looking before the first fold (the accumulator is usually
+        // not there yet, and the blocking path costs more); a blocking try (suspends the warp for hundreds of clocks).
         if (__shfl_sync(0xffffffffu, lane == 0 && tc::mbar_test(&d_full[nslot], npar) ? 1 : 0, 0)) {
           tc::fence_after_sync();
-          PF_LD(dbase + (uint32_t)nslot * 128, dA);
+          tc::tmem_ld16(dbase + (uint32_t)nslot * 128, dA);
           requested = true;
           if (warp == 0 && lane == 0) stamp(3, nb);
         }
@@ -407,9 +376,9 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const __grid
         if ((b & 7) == 7) tc::mbar_arrive(&w_empty[ws]);   // ... and with the weight batch's scales
       }
       if (nb < KB && !requested) {
-        waitw(&d_full[nslot], npar, ok, lane);
+        waitb(&d_full[nslot], npar, ok);
         tc::fence_after_sync();
-        PF_LD(dbase + (uint32_t)nslot * 128, dA);
+        tc::tmem_ld16(dbase + (uint32_t)nslot * 128, dA);
         if (warp == 0 && lane == 0) stamp(3, nb);
       }
       tc::tmem_wait_ld();
@@ -437,7 +406,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const __grid
       }
       asm volatile("bar.sync 1, %0;" ::"n"(NRW * 32) : "memory");
       if (t == 0) stamp(10, 6);                            // rounded tile in shared memory
-      rope_kv_phase(a, ybuf, row_tile, tok0, cq, r);
+      rope_kv_phase(a, ybuf, row_tile, tok_tile * NTOK, t);
     } else if (a.epi == Q4B_EPI_SWIGLU_Q8) {
       // SwiGLU + re-quantise for `down` (lab/qwen_batched.py:1363-1396): the product rounded to fp16, then the Q8_1
       // quantiser of quant_q8_1.cu on it, written straight into the tiled operand format of the next GEMM.  This row
@@ -461,6 +430,19 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const __grid
         const float prod = swiglu_pair(acc2[j], r, j, n);
         const int p = tok0 + n;
         if (p < a.P && row < a.N) reinterpret_cast<__half*>(a.Y)[(size_t)p * a.ldy + (row >> 1)] = __float2half_rn(prod);
+      }
+    } else if ((a.epi == Q4B_EPI_STORE || a.epi == Q4B_EPI_BIASF) && a.pair16) {
+      // fp16 outputs as 4-byte stores: the even lane of a row pair writes (row, row + 1) of token 2 j, the odd lane of
+      // token 2 j + 1 (one exchange per token pair); a warp store then covers two runs of 64 bytes
+      const bool odd = r & 1;
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        const float v0 = tc::lo2(acc2[j]) + bias, v1 = tc::hi2(acc2[j]) + bias;
+        const float got = __shfl_xor_sync(0xffffffffu, odd ? v0 : v1, 1);
+        const int p = tok0 + 2 * j + (odd ? 1 : 0);
+        if (p < a.P && row < a.N)
+          *reinterpret_cast<__half2*>(reinterpret_cast<__half*>(a.Y) + (size_t)p * a.ldy + (row & ~1)) =
+              odd ? __floats2half2_rn(got, v1) : __floats2half2_rn(v0, got);
       }
     } else if (a.epi == Q4B_EPI_RESID && blockIdx.z == 0) {
       // h += sum: all 32 loads first (issued back to back), then the adds and stores; one load-add-store per token in turn
@@ -519,6 +501,9 @@ int mmq_prefill(const void* Wt, const void* St, const void* Xt, void* Y, const v
     return fail(Q4B_E_SHAPE, "mmq_prefill: swiglu_q8 needs a row count that is a multiple of 128 and a tiled Q8_1 output buffer");
   if (epilogue == Q4B_EPI_BIASF_ROPE_KV) {
     if (!cosT || !sinT || !kc || !vc || !AUX) return fail(Q4B_E_ALIGN, "mmq_prefill: the rope/kv epilogue needs bias, tables and the cache");
+    if (reinterpret_cast<uintptr_t>(cosT) % 8 || reinterpret_cast<uintptr_t>(sinT) % 8 || reinterpret_cast<uintptr_t>(kc) % 4 ||
+        reinterpret_cast<uintptr_t>(vc) % 4 || reinterpret_cast<uintptr_t>(Y) % 4 || (ldy % 2))
+      return fail(Q4B_E_ALIGN, "mmq_prefill: the rope/kv epilogue needs 8-byte aligned tables, 4-byte aligned outputs and an even ldy");
     if (NH <= 0 || NKV <= 0 || N != (NH + 2 * NKV) * 128 || max_len <= 0 || pos0 < 0 || pos0 + P > max_len)
       return fail(Q4B_E_SHAPE, "mmq_prefill: the rope/kv epilogue needs head_dim 128, N = (NH + 2 NKV) 128 and pos0 + P <= max_len");
   }
@@ -542,6 +527,7 @@ int mmq_prefill(const void* Wt, const void* St, const void* Xt, void* Y, const v
   a.P = P;
   a.epi = epilogue;
   a.ldy = ldy;
+  a.pair16 = (N % 2 == 0 && ldy % 2 == 0 && reinterpret_cast<uintptr_t>(Y) % 4 == 0) ? 1 : 0;
   a.cosT = cosT;
   a.sinT = sinT;
   a.kc = reinterpret_cast<__half*>(kc);
