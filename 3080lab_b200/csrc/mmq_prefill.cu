@@ -26,6 +26,12 @@
 // fp32 pipe busy.  (A variant that pre-loaded the accumulator slot with the magic constant through tcgen05.st, so
 // that the words came back as floats, was measured: the extra 64 KB of tensor-memory writes per k-block cost more than
 // the integer adds they saved.)
+// What sets the pace (clock trace of every role, launch time against K, launches with parts removed): no single stage;
+// barriers, waits and commits alone take half of a k-block's time.  A dependent mbarrier wait on a completed phase costs
+// 86 clocks on an idle SM and ~180 in this kernel, a k-block costs each rescale warp two of them plus two tensor-memory
+// read latencies, and the four rescale warps of a scheduler run in step.  Waits therefore park (suspend-time hint) with
+// all lanes polling.  The epilogues are written for latency, not instruction count: loads hoisted above the stores of
+// the same array, one SwiGLU product per lane pair and token, fp16 outputs as 4-byte row-pair stores.
 // All waits are bounded; after the first expired wait a thread stops waiting (status word, garbage out, no hang).
 #include "q4b_internal.h"
 #include "tc05.cuh"
@@ -138,7 +144,7 @@ __device__ __noinline__ void rope_kv_phase(const PrefillArgs& a, const __half* y
 __device__ __noinline__ void swiglu_q8_phase(const PrefillArgs& a, const __half* abuf, int row_tile, int tok_tile, int t) {
   const int KB2 = a.N >> 6;                                // k-blocks of the product row
   uint8_t* rec = reinterpret_cast<uint8_t*>(const_cast<__half*>(abuf)) + 128 * 64 * 2;   // [2][STAGE_BYTES]
-#pragma unroll
+#pragma unroll 1
   for (int j = 0; j < 4; ++j) {
     const int task = t + j * (NRW * 32);
     const int sub = task & 7, hb = (task >> 3) & 1, nn = task >> 4;

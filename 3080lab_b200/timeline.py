@@ -122,6 +122,40 @@ def _chain(torch, synth, engine, ffi) -> None:
               f" {(last - t00) / 1e3:20.2f}   {np.round(np.median(rel, axis=0), 2).tolist()}")
 
 
+def _prefill_sweep(torch, QB, rng, st, P) -> None:
+    """Whole-launch time of the gate/up shape against K (replayed graph): the slope is the cost of a k-block, the
+    intercept the fixed cost of a tile (set-up, pipeline fill, epilogue, CTA turnover), both per round of CTAs."""
+    n = 17920
+    ks, ts = (256, 512, 1024, 1536, 3072), []
+    for k in ks:
+        W = torch.from_numpy(rng.integers(0, 2 ** 32, size=(n, k // 8), dtype=np.uint32).view(np.int32)).cuda()
+        S = torch.from_numpy(rng.uniform(0.002, 0.02, size=(n, k // 32)).astype(np.float16)).cuda()
+        Wt, St = QB.pack_q4(W, S)
+        xt = QB.q8_tiled_buffer(P, k, "cuda")
+        QB.quant_q8_tiled(torch.randn(P, k, device="cuda").half(), xt)
+        y = torch.zeros(P, n // 2, dtype=torch.float16, device="cuda")
+        fn = lambda: QB.gemm8_prefill(Wt, St, xt, y, None, n, k, P, "swiglu", n // 2, st)
+        fn()
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            fn()
+        for _ in range(3):
+            g.replay()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(10):
+            g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        ts.append(1e3 * e0.elapsed_time(e1) / 10)
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    rounds = -(-(n // 128) * (P // 128) // sms)
+    slope, icpt = np.polyfit(np.array(ks) / 32, np.array(ts), 1)
+    print(f"gate/up launch time against K (us): {dict(zip(ks, [round(t, 1) for t in ts]))}; {rounds} rounds of CTAs: "
+          f"{slope / rounds:.3f} us per k-block, {icpt / rounds:.2f} us fixed per tile")
+
+
 def _prefill(torch, ffi) -> None:
     """SM-clock stamps of CTA (0, 0, 0) of one gate/up-shaped prefill GEMM (`q4b_mmq_prefill_trace`): per k-block, when each
     pipeline role got to it.  Printed as clocks since the first stamp, and the steady-state period of every role."""
@@ -146,6 +180,7 @@ def _prefill(torch, ffi) -> None:
     ffi.call("q4b_mmq_prefill_trace", None, 0)
     st.check()
     full = buf.cpu().numpy().reshape(11, 64).astype(np.int64)
+    _prefill_sweep(torch, QB, rng, st, P)
     t = full[:, :k // 32]
     t0 = t[t > 0].min()
     names = ["stage requested", "A operand written", "MMA issued", "accumulator seen", "slot handed back", "folded"]
