@@ -97,7 +97,9 @@ int attn_prefill(const void*, const float*, const float*, void*, void*, void*, i
 size_t q8_tiled_bytes(int, int);
 int mmq_prefill(const void*, const void*, const void*, void*, const void*, int, int, int, int, int, uint32_t*, cudaStream_t,
                 const float* cosT = nullptr, const float* sinT = nullptr, void* kc = nullptr, void* vc = nullptr, int NH = 0,
-                int NKV = 0, int max_len = 0, int pos0 = 0, float* Y2 = nullptr, int parts = 1);
+                int NKV = 0, int max_len = 0, int pos0 = 0, float* Y2 = nullptr, int parts = 1, int f16 = 0);
+size_t f16_tiled_bytes(int, int);
+int f16_tiled(const void*, void*, int, int, cudaStream_t);
 int add_rows(float*, const float*, size_t, int, cudaStream_t);
 int quant_q8_1_tiled(const void*, void*, int, int, cudaStream_t);
 int rmsnorm_q8_1_tiled(const float*, const float*, void*, int, int, float, cudaStream_t, float* h_add = nullptr, int n_add = 1);
@@ -252,6 +254,16 @@ int q4b_mmq_q4_0_q8_1_mma(const void* W, const void* Sc, const void* xq, const v
 int q4b_quant_mmq_q4_0_q8_1_mma(const void* W, const void* Sc, const void* x16, void* Y, const void* AUX, int N, int K, int P,
                                 int epilogue, int ldy, uint32_t* status, q4b_stream_t stream) {
   return gemv_q8mma(W, Sc, nullptr, x16, Y, AUX, N, K, P, epilogue, ldy, status, S(stream));
+}
+
+size_t q4b_f16_tiled_bytes(int rows, int K) { return (rows > 0 && K > 0) ? f16_tiled_bytes(rows, K) : 0; }
+
+int q4b_f16_tiled(const void* x, void* xt, int rows, int K, q4b_stream_t stream) { return f16_tiled(x, xt, rows, K, S(stream)); }
+
+int q4b_mm_prefill_q4_0_f16(const void* Wt, const void* St, const void* xt, void* Y, const void* AUX, int N, int K, int P,
+                            int epilogue, int ldy, uint32_t* status, q4b_stream_t stream) {
+  return mmq_prefill(Wt, St, xt, Y, AUX, N, K, P, epilogue, ldy, status, S(stream), nullptr, nullptr, nullptr, nullptr, 0, 0, 0, 0,
+                     nullptr, 1, 1);
 }
 
 int q4b_mmq_prefill_trace(int64_t* device_buffer, size_t entries) {

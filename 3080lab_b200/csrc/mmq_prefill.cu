@@ -52,6 +52,15 @@ constexpr int WB = 4;                     // weight batches in flight (8 k-block
 constexpr uint32_t STAGE_BYTES = 4096 + 512;
 constexpr uint32_t WBATCH_W = 8 * 2048, WBATCH_S = 8 * 256;
 constexpr size_t PF_SMEM = (size_t)WB * (WBATCH_W + WBATCH_S) + (size_t)SB * STAGE_BYTES + 128;
+// fp16 mode (weights dequantised to fp16 by the expanders, fp16 activations, one fp32 accumulator over all of K): the
+// pipeline moves UNITS of G k-blocks so that the one MMA-issuing thread pays its waits and commits once per 2 G MMAs
+constexpr int G16 = 4;                    // k-blocks per unit
+constexpr int NAU = 4;                    // A units in tensor memory (G16 x 16 columns each)
+constexpr int SBU = 3;                    // activation units in shared memory
+constexpr int NXG = (NRW + NEW) / 4;      // expander groups of four warps (one per TMEM lane quarter): every warp expands
+constexpr uint32_t REC16 = 128 * 32 * 2;  // one k-block of fp16 activations for 128 tokens
+constexpr uint32_t UNIT16 = G16 * REC16;
+constexpr size_t PF_SMEM16 = (size_t)WB * (WBATCH_W + WBATCH_S) + (size_t)SBU * UNIT16 + 128;
 
 struct PrefillArgs {
   const uint8_t* Wt;   // tile-packed nibbles
@@ -80,6 +89,8 @@ __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t by
                : "memory");
 }
 
+__device__ __forceinline__ uint32_t h2_as_u32(__half2 v) { return *reinterpret_cast<uint32_t*>(&v); }
+__device__ __forceinline__ __half2 u32_as_h2(uint32_t v) { return *reinterpret_cast<__half2*>(&v); }
 // Wait unless an earlier wait of this thread already expired.  Worker warps call it with all 32 lanes (one polling lane
 // plus a warp barrier was measured 4 % slower); the tries park the thread (suspend hint) instead of spinning, which was
 // worth little by itself but keeps waiting warps out of the issue slots.
@@ -160,7 +171,7 @@ __device__ __noinline__ void swiglu_q8_phase(const PrefillArgs& a, const __half*
   for (int i = t; i < 2 * (int)STAGE_BYTES / 16; i += NRW * 32) dst[i] = src[i];
 }
 
-template <bool TRACE>
+template <bool TRACE, bool F16>
 __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const __grid_constant__ PrefillArgs a) {
   extern __shared__ __align__(128) uint8_t smem[];
   // "empty" barriers are waited on with the inverted parity the first time round (a fresh barrier reads as having
@@ -185,7 +196,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const __grid
   const int KB = a.kb_bound[blockIdx.z + 1] - kb_lo, NBATCH = KB >> 3;
   const int row_tile = blockIdx.x, tok_tile = blockIdx.y;
   const size_t wbase = (size_t)row_tile * KBT + kb_lo;     // k-block index of this row tile in the packed arrays
-  const uint8_t* xbase = a.Xt + ((size_t)tok_tile * KBT + kb_lo) * STAGE_BYTES;
+  const uint8_t* xbase = a.Xt + ((size_t)tok_tile * KBT + kb_lo) * (F16 ? REC16 : STAGE_BYTES);
 
   [[maybe_unused]] long long t_entry = 0;
   if constexpr (TRACE) t_entry = clock64();
@@ -200,7 +211,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const __grid
     }
     for (int i = 0; i < SB; ++i) {
       tc::mbar_init(&b_full[i], 1);
-      tc::mbar_init(&b_empty[i], 1 + NRW);                 // operand read by the MMA (commit), block scales by the rescale warps
+      tc::mbar_init(&b_empty[i], F16 ? 1 : 1 + NRW);       // operand read by the MMA (commit), block scales by the rescale warps
     }
     for (int i = 0; i < NA; ++i) {
       tc::mbar_init(&a_full[i], NEW);
@@ -217,7 +228,8 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const __grid
   tc::fence_after_sync();
   pdl_launch_dependents();
   const uint32_t tmem = tmem_base_s;
-  const uint32_t tmem_a = tmem, tmem_d = tmem + NA * 8;    // A: NA x 8 columns; D: NSLOT x 128 columns
+  // int8 mode: A NA x 8 columns, D NSLOT x 128 columns; fp16 mode: A NAU x G16 x 16 columns, D 128 columns
+  const uint32_t tmem_a = tmem, tmem_d = tmem + (F16 ? NAU * G16 * 16 : NA * 8);
   constexpr uint32_t IDESC = tc::idesc_i8(128, NTOK);
   bool ok = true;
   // TRACE instance only: timeline of the first 64 k-blocks of one CTA, one row per pipeline role (SM clock).  The stamps
@@ -233,7 +245,113 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const __grid
   }
   if (t == 0) stamp(10, 1);                                // set-up done (tensor memory, barriers)
 
-  if (warp == W_COPY) {
+  // ===================== fp16 mode: every role's main loop =====================
+  [[maybe_unused]] const int NU = KB / G16;                // units of this CTA (KB is a multiple of 8)
+  [[maybe_unused]] auto expand16 = [&]() {
+    // Warps 0 .. 19 in five groups of four (one warp per TMEM lane quarter); group g expands units u = g (mod 5):
+    // nibbles -> (q - 8) exactly in fp16 -> times the block scale, rounded once (gemv_v2_source's `dq`,
+    // lab/qwen_batched.py:493-498) -> 16 columns of tensor memory per k-block.  A word's 8 weights come out as the pairs
+    // (0,4) (1,5) (2,6) (3,7); the activation operand carries the same order within every 8 values.
+    const int grp = warp >> 2;
+    const int r = (warp & 3) * 32 + lane;
+    const uint32_t lane_off = (uint32_t)(32 * (warp & 3)) << 16;
+    const __half2 c1032 = __float2half2_rn(1032.f), c16th = __float2half2_rn(0.0625f), c72 = __float2half2_rn(-72.f);
+    for (int u = 0; u < NU; ++u) {
+      const int b0 = u * G16, ws = (b0 >> 3) % WB;
+      if ((b0 & 7) == 0) waitb(&w_full[ws], (uint32_t)((b0 >> 3) / WB) & 1u, ok);
+      if (u % NXG == grp) {
+        const int as = u % NAU;
+        waitb(&a_empty[as], ((uint32_t)(u / NAU) & 1u) ^ 1u, ok);   // the MMAs of unit u - NAU have read this operand
+        tc::fence_after_sync();
+#pragma unroll
+        for (int g = 0; g < G16; ++g) {
+          const int bb = (b0 + g) & 7;
+          const uint4 w = *reinterpret_cast<const uint4*>(slabW + (size_t)ws * WBATCH_W + (size_t)bb * 2048 + r * 16);
+          const __half2 d2 = __half2half2(reinterpret_cast<const __half*>(slabS + (size_t)ws * WBATCH_S)[bb * 128 + r]);
+          const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+          uint32_t ex[16];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const uint32_t w0 = ww[i], w8 = ww[i] >> 8;
+            const __half2 l0 = __hsub2(u32_as_h2((w0 & 0x000F000Fu) | 0x64006400u), c1032);
+            const __half2 h0 = __hfma2(u32_as_h2((w0 & 0x00F000F0u) | 0x64006400u), c16th, c72);
+            const __half2 l1 = __hsub2(u32_as_h2((w8 & 0x000F000Fu) | 0x64006400u), c1032);
+            const __half2 h1 = __hfma2(u32_as_h2((w8 & 0x00F000F0u) | 0x64006400u), c16th, c72);
+            ex[4 * i + 0] = h2_as_u32(__hmul2(l0, d2));
+            ex[4 * i + 1] = h2_as_u32(__hmul2(h0, d2));
+            ex[4 * i + 2] = h2_as_u32(__hmul2(l1, d2));
+            ex[4 * i + 3] = h2_as_u32(__hmul2(h1, d2));
+          }
+          tc::tmem_st16(tmem_a + lane_off + (uint32_t)(as * G16 + g) * 16, ex);
+        }
+        tc::tmem_wait_st();                                // warp-wide
+        tc::fence_before_sync();
+        if (lane == 0) tc::mbar_arrive(&a_full[as]);
+      }
+      if (((b0 + G16 - 1) & 7) == 7) {
+        __syncwarp();
+        if (lane == 0) tc::mbar_arrive(&w_empty[ws]);      // this warp is done with the batch (whether it expanded any of it or not)
+      }
+    }
+  };
+  if constexpr (F16) {
+    if (warp == W_COPY) {
+      if (lane == 0) {
+        auto load_w = [&](int j) {
+          const int s = j % WB;
+          tc::mbar_expect_tx(&w_full[s], WBATCH_W + WBATCH_S);
+          bulk_g2s(slabW + (size_t)s * WBATCH_W, a.Wt + (wbase + (size_t)j * 8) * 2048, WBATCH_W, &w_full[s]);
+          bulk_g2s(slabS + (size_t)s * WBATCH_S, a.St + (wbase + (size_t)j * 8) * 128, WBATCH_S, &w_full[s]);
+        };
+        auto load_u = [&](int u) {                         // G16 consecutive records = one contiguous piece
+          const int s = u % SBU;
+          tc::mbar_expect_tx(&b_full[s], UNIT16);
+          bulk_g2s(stage + (size_t)s * UNIT16, xbase + (size_t)u * UNIT16, UNIT16, &b_full[s]);
+        };
+        for (int j = 0; j < WB && j < NBATCH; ++j) load_w(j);
+        pdl_wait();
+        for (int u = 0; u < SBU && u < NU; ++u) load_u(u);
+        for (int ou = 0; ou < NU; ++ou) {
+          if (ou + SBU < NU) {
+            waitb(&b_empty[ou % SBU], (uint32_t)(ou / SBU) & 1u, ok);
+            load_u(ou + SBU);
+          }
+          if (((ou * G16 + G16 - 1) & 7) == 7) {
+            const int oj = (ou * G16) >> 3;
+            if (oj + WB < NBATCH) {
+              waitb(&w_empty[oj % WB], (uint32_t)(oj / WB) & 1u, ok);
+              load_w(oj + WB);
+            }
+          }
+        }
+      }
+    } else if (warp == W_MMA) {
+      if (lane == 0) {
+        constexpr uint32_t IDESC16 = tc::idesc_f16(128, NTOK);
+        const uint32_t stage0 = tc::smem_u32(stage);
+        for (int u = 0; u < NU; ++u) {
+          const int s = u % SBU, as = u % NAU;
+          waitb(&a_full[as], (uint32_t)(u / NAU) & 1u, ok);
+          waitb(&b_full[s], (uint32_t)(u / SBU) & 1u, ok);
+          tc::fence_after_sync();
+#pragma unroll
+          for (int g = 0; g < G16; ++g) {
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {                  // 16 of the k-block's 32 values per instruction
+              // per 8-token group: four 8-value chunks of 128 bytes; chunks 2 j, 2 j + 1 belong to this instruction
+              const uint64_t bdesc = tc::smem_desc_kmajor(stage0 + (uint32_t)s * UNIT16 + (uint32_t)g * REC16 + (uint32_t)j * 256, 128, 512);
+              tc::mma_f16_ts(tmem_d, tmem_a + (uint32_t)(as * G16 + g) * 16 + (uint32_t)j * 8, bdesc, IDESC16, (u | g | j) ? 1u : 0u);
+            }
+          }
+          tc::mma_commit(&a_empty[as]);
+          tc::mma_commit(&b_empty[s]);
+        }
+        tc::mma_commit(&d_full[0]);
+      }
+    } else if (warp >= NRW) {
+      expand16();
+    }
+  } else if (warp == W_COPY) {
     // ===================== bulk-copy producer (one thread) =====================
     if (lane == 0) {
       auto load_w = [&](int j) {                           // weight batch j -> slot j % WB
@@ -311,8 +429,8 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const __grid
         if (warp == NRW) stamp(1, b);
       }
     }
-
-  } else {
+  }
+  if (warp < NRW) {
     // ===================== rescale warps: TMEM lane quarter lq (rows), column quarter cq (32 activation rows) ==========
     const int lq = warp & 3, cq = warp >> 2;
     const int r = lq * 32 + lane;
@@ -336,6 +454,21 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const __grid
         acc2[8 * half + 2 * q + 1] = tc::fma2(tc::mul2(dw2, x4.y), f1, acc2[8 * half + 2 * q + 1]);
       }
     };
+    if constexpr (F16) {
+      // fp16 mode: these warps expand too; then the one accumulator (complete sums over K) is read out once
+      expand16();
+      uint32_t dA[16], dB[16];
+      waitb(&d_full[0], 0u, ok);
+      tc::fence_after_sync();
+      tc::tmem_ld16(dbase, dA);
+      tc::tmem_ld16(dbase + 16, dB);
+      tc::tmem_wait_ld();
+#pragma unroll
+      for (int n = 0; n < 8; ++n) {
+        acc2[n] = tc::pack2u(dA[2 * n], dA[2 * n + 1]);
+        acc2[8 + n] = tc::pack2u(dB[2 * n], dB[2 * n + 1]);
+      }
+    } else {
     // Rolling schedule: the read-back of the next 16 columns is always in flight while the previous 16 are folded, so a
     // warp does not sit idle on tensor-memory latency.  (Handing the slot back before folding anything was measured:
     // slower, the exposed read latency costs more than the earlier release gains.)
@@ -392,6 +525,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const __grid
       s = s + 1 == SB ? 0 : s + 1;
     }
 
+    }
     // ---- epilogue: thread (row r, 32 activation rows)
     if (t == 0) stamp(10, 2);                              // main loop left
     pdl_wait();                                            // Y / AUX may be written by the previous kernel
@@ -494,12 +628,49 @@ long long* g_prefill_trace = nullptr;
 
 void mmq_prefill_trace(long long* buf) { g_prefill_trace = buf; }
 
+size_t f16_tiled_bytes(int P, int K) { return (size_t)((P + NTOK - 1) / NTOK) * (size_t)(K / 32) * REC16; }
+
+// fp16 activations [P, K] -> the fp16 mode's B operand: per (128-token tile, k-block) 8192 bytes in the tensor core's
+// K-major core-matrix order ([8-token group 16][8-value chunk 4][token 8][16 bytes]); within a chunk the values sit as
+// (0,4,1,5,2,6,3,7), the order in which the expanders' nibble masks deliver a word's weights.  A warp writes 512
+// contiguous bytes and reads 64 contiguous bytes of 8 tokens.
+__global__ void __launch_bounds__(256) f16_tiled_kernel(const __half* __restrict__ x, uint8_t* __restrict__ xt, int P, int K) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int KB = K >> 5;
+  const size_t i = (size_t)blockIdx.x * 256 + threadIdx.x;
+  const int r = (int)(i & 7), c = (int)(i >> 3) & 3;
+  const size_t grp = i >> 5;
+  const int g = (int)(grp & 15);
+  const size_t rec = grp >> 4;                              // (token tile, k-block)
+  const int kb = (int)(rec % KB), tt = (int)(rec / KB);
+  const int p = tt * NTOK + g * 8 + r;
+  if (p >= P) return;                                       // rows past P stay zero (the buffer is zero-filled once)
+  const uint4 v = *reinterpret_cast<const uint4*>(x + (size_t)p * K + kb * 32 + c * 8);
+  uint4 o;                                                  // halves (0..7) -> (0,4,1,5,2,6,3,7)
+  o.x = __byte_perm(v.x, v.z, 0x5410);
+  o.y = __byte_perm(v.x, v.z, 0x7632);
+  o.z = __byte_perm(v.y, v.w, 0x5410);
+  o.w = __byte_perm(v.y, v.w, 0x7632);
+  *reinterpret_cast<uint4*>(xt + rec * REC16 + (size_t)g * 512 + c * 128 + r * 16) = o;
+}
+
+int f16_tiled(const void* x, void* xt, int P, int K, cudaStream_t st) {
+  if (P <= 0 || K <= 0 || (K % 32)) return fail(Q4B_E_SHAPE, "f16_tiled: P > 0 and K a positive multiple of 32 required");
+  if (!x || !xt || !aligned16(x) || !aligned16(xt)) return fail(Q4B_E_ALIGN, "f16_tiled: null or misaligned pointer");
+  const size_t threads = (size_t)((P + NTOK - 1) / NTOK) * (size_t)(K / 32) * 16 * 32;
+  return check_launch(launch_pdl(f16_tiled_kernel, dim3((unsigned)((threads + 255) / 256)), dim3(256), 0, st,
+                                 reinterpret_cast<const __half*>(x), reinterpret_cast<uint8_t*>(xt), P, K),
+                      "f16_tiled");
+}
+
 size_t q8_tiled_bytes(int P, int K) { return (size_t)((P + NTOK - 1) / NTOK) * (size_t)(K / 32) * STAGE_BYTES; }
 
 // Y2 != nullptr (RESID only): the launch is split along K over gridDim.z = parts; Y += part 0, Y2[z - 1] = part z.
 int mmq_prefill(const void* Wt, const void* St, const void* Xt, void* Y, const void* AUX, int N, int K, int P, int epilogue,
                 int ldy, uint32_t* status, cudaStream_t st, const float* cosT, const float* sinT, void* kc, void* vc, int NH,
-                int NKV, int max_len, int pos0, float* Y2, int parts) {
+                int NKV, int max_len, int pos0, float* Y2, int parts, int f16) {
+  if (f16 && epilogue == Q4B_EPI_SWIGLU_Q8) return fail(Q4B_E_ARG, "mmq_prefill: no swiglu_q8 epilogue in fp16 mode");
   if (N <= 0 || P <= 0 || K <= 0 || (K % 256)) return fail(Q4B_E_SHAPE, "mmq_prefill: N, P > 0 and K a positive multiple of 256 required");
   if (epilogue < Q4B_EPI_STORE || epilogue > Q4B_EPI_BIASF_ROPE_KV) return fail(Q4B_E_ARG, "mmq_prefill: unknown epilogue");
   if (epilogue == Q4B_EPI_SWIGLU && (N % 2)) return fail(Q4B_E_SHAPE, "mmq_prefill: swiglu needs an even row count");
@@ -516,8 +687,9 @@ int mmq_prefill(const void* Wt, const void* St, const void* Xt, void* Y, const v
   if (!Wt || !St || !Xt || !Y || !status || !aligned16(Wt) || !aligned16(St) || !aligned16(Xt))
     return fail(Q4B_E_ALIGN, "mmq_prefill: null or misaligned pointer");
   if (epilogue == Q4B_EPI_BIASF && !AUX) return fail(Q4B_E_ALIGN, "mmq_prefill: biasf needs AUX");
-  auto kern = g_prefill_trace ? mmq_prefill_kernel<true> : mmq_prefill_kernel<false>;
-  if (cudaError_t e = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), PF_SMEM); e != cudaSuccess) {
+  auto kern = f16 ? mmq_prefill_kernel<false, true> : g_prefill_trace ? mmq_prefill_kernel<true, false> : mmq_prefill_kernel<false, false>;
+  const size_t smem_bytes = f16 ? PF_SMEM16 : PF_SMEM;
+  if (cudaError_t e = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), smem_bytes); e != cudaSuccess) {
     set_cuda_error(e, "mmq_prefill: cudaFuncSetAttribute");
     return Q4B_E_CUDA;
   }
@@ -554,7 +726,7 @@ int mmq_prefill(const void* Wt, const void* St, const void* Xt, void* Y, const v
     for (int z = 1; z < parts; ++z) a.kb_bound[z] = (int)(((long long)batches * z + parts - 1) / parts) * 8;
     grid.z = parts;
   }
-  return check_launch(launch_pdl(kern, grid, dim3(PF_THREADS), PF_SMEM, st, a), "mmq_prefill");
+  return check_launch(launch_pdl(kern, grid, dim3(PF_THREADS), smem_bytes, st, a), "mmq_prefill");
 }
 
 }  // namespace q4b

@@ -138,6 +138,22 @@ def q8_tiled_buffer(rows: int, K: int, device) -> torch.Tensor:
     return torch.zeros(_ffi.lib().q4b_q8_tiled_bytes(rows, K), dtype=torch.uint8, device=device)
 
 
+def f16_tiled_buffer(rows: int, K: int, device) -> torch.Tensor:
+    """Zero-filled buffer for the fp16-mode prefill GEMM's activation operand (up to `rows` rows of K values)."""
+    return torch.zeros(_ffi.lib().q4b_f16_tiled_bytes(rows, K), dtype=torch.uint8, device=device)
+
+
+def f16_tile(x, xt) -> None:
+    """x fp16 [rows, K] -> the tensor-core operand order of `gemm16_prefill`."""
+    _ffi.call("q4b_f16_tiled", _p(x), _p(xt), x.shape[0], x.shape[1], _stream())
+
+
+def gemm16_prefill(Wt, St, xt, Y, aux, N: int, K: int, P: int, epi: str, ldy: int, status: Status) -> None:
+    """The prefill GEMM in fp16 arithmetic: weights dequantised to fp16 as gemv_v2_source does (lab/qwen_batched.py:493-498),
+    fp16 activations (tiled by `f16_tile`), fp32 accumulation over all of K on tcgen05."""
+    _ffi.call("q4b_mm_prefill_q4_0_f16", _p(Wt), _p(St), _p(xt), _p(Y), _p(aux), N, K, P, _ffi.EPI[epi], ldy, _p(status.word), _stream())
+
+
 def quant_q8_tiled(x, xt) -> None:
     """x fp16 [rows, K] -> tiled Q8_1 (the prefill MMQ's activation operand)."""
     _ffi.call("q4b_quant_q8_1_tiled", _p(x), _p(xt), x.shape[0], x.shape[1], _stream())

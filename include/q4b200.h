@@ -287,6 +287,17 @@ int q4b_mmq_prefill_qkv_rope_kv(const void* Wt, const void* St, const void* xt, 
 int q4b_attn_prefill_cached(const void* qkv, const void* kc, const void* vc, void* out, void* xt, int P, int NH, int NKV,
                             int HD, int max_len, int pos0, float scale, q4b_stream_t stream);
 
+/* The prefill GEMM in the arithmetic of the reference's fp16-weight batched GEMV (gemv_v2_source,
+ * lab/qwen_batched.py:467-641; `dq` :493-498) at prefill width: weights dequantised to fp16 ((q - 8) exact, times the block
+ * scale, rounded once) by the kernel's expander warps, fp16 activations, one fp32 tensor-memory accumulator over all of K
+ * (tcgen05.mma.kind::f16), no per-block rescale.  Not the reference's prefill arithmetic (that is the int8 MMQ above); the
+ * faster route when fp16 activations are wanted.  xt = q4b_f16_tiled(x): q4b_f16_tiled_bytes(rows, K) = ceil(rows/128) *
+ * K/32 * 8192 bytes, zero-filled once by the caller.  Epilogues store, biasf, resid, swiglu, logits. */
+size_t q4b_f16_tiled_bytes(int rows, int K);
+int q4b_f16_tiled(const void* x, void* xt, int rows, int K, q4b_stream_t stream);
+int q4b_mm_prefill_q4_0_f16(const void* Wt, const void* St, const void* xt, void* Y, const void* AUX, int N, int K, int P,
+                            int epilogue, int ldy, uint32_t* status, q4b_stream_t stream);
+
 /* Pipeline timeline of the prefill GEMM: while a device buffer of 11 x 64 int64 is set, every q4b_mmq_prefill_* launch
  * runs a second instance of the kernel whose CTA (0, 0, 0) writes SM-clock stamps for its first 64 k-blocks, one row per
  * event: 0 activation stage requested, 1 A operand written (first expander warp), 2 MMA issued and committed, 3 accumulator
