@@ -487,8 +487,13 @@ class Prefill:
     Q8_1 -> MMQ o (+residual) -> RMSNorm+Q8_1 -> MMQ gate/up (+SwiGLU) -> Q8_1 -> MMQ down (+residual).  Writes the KV
     cache of the `FusedQwen` it wraps, so decode continues from the prefilled state."""
 
-    def __init__(self, m: FusedQwen, P: int, fused: bool = True, split_k=None):
-        """fused: the reference's seven launches per layer (scripts/qwen_prefill.py:196-246): the QKV GEMM rotates and
+    def __init__(self, m: FusedQwen, P: int, fused: bool = True, split_k=None, linears: str = "q8"):
+        """linears: "q8" = the reference's prefill arithmetic (Q8_1 activations, int8 MMQ, described above); "f16" = the
+        arithmetic of its fp16-weight batched GEMV (lab/qwen_batched.py:467-641) at prefill width: fp16 activations, weights
+        dequantised to fp16 inside the GEMM, fp32 accumulation over all of K on the tensor cores - about three times
+        faster per pass and without the int8 rounding of the activations, eleven launches per layer (RMSNorm, operand
+        tiling, GEMM ...).
+        fused: the reference's seven launches per layer (scripts/qwen_prefill.py:196-246): the QKV GEMM rotates and
         appends K/V (`biasf_kv`), the flash kernel emits the o-projection's Q8_1 input (`q8`), the gate/up GEMM emits the
         down GEMM's (`swiglu_q8`).  fused=False keeps those three steps as separate launches (ten per layer); both give
         the same bits.
@@ -498,7 +503,9 @@ class Prefill:
         c = m.cfg
         if not m.tensor_core or c.hidden % 256 or c.q_rows % 256 or c.ffn % 256 or c.head_dim != 128:
             raise ValueError("the prefill path needs tile-packed weights (K multiples of 256) and head_dim 128")
-        self.m, self.P, self.fused = m, P, fused
+        if linears not in ("q8", "f16"):
+            raise ValueError("linears is 'q8' or 'f16'")
+        self.m, self.P, self.fused, self.linears = m, P, fused, linears
         dv, f16, f32 = m.device, torch.float16, torch.float32
         self.h = torch.zeros(P, c.hidden, dtype=f32, device=dv)
         self.qkv = torch.zeros(P, c.qkv_rows, dtype=f16, device=dv)
@@ -529,6 +536,11 @@ class Prefill:
         nbuf = max(self.parts.values()) - 1
         self.h2 = torch.zeros(nbuf, P, c.hidden, dtype=f32, device=dv) if nbuf > 0 else None
         self.launches_per_chunk = 1 + (7 if fused else 10) * c.layers + (1 if self.split_k else 0)
+        if linears == "f16":
+            self.x16 = torch.zeros(P, c.hidden, dtype=f16, device=dv)
+            self.xt16 = QB.f16_tiled_buffer(P, max(c.hidden, c.q_rows), dv)
+            self.xt16b = QB.f16_tiled_buffer(P, c.ffn, dv)
+            self.launches_per_chunk = 1 + 11 * c.layers
 
     def gemm8(self, pair, xt, N, Kdim, Y, aux, epi, ldy):
         Wt, St = self.m.packed[id(pair[0])]
@@ -554,8 +566,30 @@ class Prefill:
         else:
             QB.rmsnorm_q8_tiled(self.h, w, self.xt, self.m.cfg.eps)
 
+    def gemm16(self, pair, x, N, Kdim, Y, aux, epi, ldy):
+        """fp16 route: tile x [P, Kdim] into the tensor-core operand order, then the GEMM."""
+        Wt, St = self.m.packed[id(pair[0])]
+        xt = self.xt16b if Kdim == self.m.cfg.ffn else self.xt16
+        QB.f16_tile(x, xt)
+        QB.gemm16_prefill(Wt, St, xt, Y, aux, N, Kdim, self.P, epi, ldy, self.status)
+
+    def _chunk_f16(self, pos0: int) -> None:
+        m, c, H = self.m, self.m.cfg, self.m.cfg.hidden
+        K.embed(m.embed, self.tok, self.h)
+        for i, L in enumerate(m.L):
+            K.rms(self.h, L["ln1"], self.x16, c.eps)
+            self.gemm16(L["qkv"], self.x16, c.qkv_rows, H, self.qkv, L["qkv_b"], "biasf", c.qkv_rows)
+            QB.attn_prefill(self.qkv, m.cos, m.sin, m.kc[i], m.vc[i], self.att, c.n_heads, c.n_kv_heads, c.head_dim,
+                            m.max_len, pos0, m.scale)
+            self.gemm16(L["o"], self.att, H, c.q_rows, self.h, None, "resid", H)
+            K.rms(self.h, L["ln2"], self.x16, c.eps)
+            self.gemm16(L["gu"], self.x16, 2 * c.ffn, H, self.xm, None, "swiglu", c.ffn)
+            self.gemm16(L["down"], self.xm, H, c.ffn, self.h, None, "resid", H)
+
     def chunk(self, pos0: int = 0) -> None:
         """One pass over the P tokens in self.tok at positions pos0 .. pos0 + P - 1."""
+        if self.linears == "f16":
+            return self._chunk_f16(pos0)
         m, c, H = self.m, self.m.cfg, self.m.cfg.hidden
         K.embed(m.embed, self.tok, self.h)
         self._pending = 0
@@ -598,14 +632,14 @@ class Prefill:
             K.finish(m.logits, m.tok, m.pos, m.head_ws)
 
 
-def prefill(m: FusedQwen, ids, chunk: int = 0, fused: bool = True):
+def prefill(m: FusedQwen, ids, chunk: int = 0, fused: bool = True, linears: str = "q8"):
     """Prefill `ids` (one sequence) in chunks against m's cache (scripts/qwen_prefill.py:262-301).  -> Prefill object."""
     ids = np.asarray(ids, np.int64)
     n = len(ids)
     chunk = chunk or n
     if n % chunk:
         raise ValueError("the prompt length must be a multiple of the chunk")
-    pf = Prefill(m, chunk, fused)
+    pf = Prefill(m, chunk, fused, linears=linears)
     for s0 in range(0, n, chunk):
         pf.tok.copy_(torch.from_numpy(ids[s0:s0 + chunk]).to(pf.tok.device))
         pf.chunk(s0)

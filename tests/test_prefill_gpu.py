@@ -324,3 +324,108 @@ def test_prefill_with_split_k_matches_the_unsplit_pass():
     # an int8 flip downstream of a last-bit difference is possible, as everywhere on this path: typical rows agree to fp32 level
     err = ((a - b).abs().max(dim=1).values / a.abs().max()).cpu().numpy()
     assert np.median(err) < 1e-5 and err.max() < 5e-2
+
+
+# ---- fp16 route: weights dequantised to fp16 inside the GEMM, fp16 activations, fp32 accumulation over all of K ----------
+
+def test_f16_tile_layout():
+    """The fp16 operand: per (128-token tile, k-block) [8-token group][8-value chunk][token][16 bytes], values of a chunk
+    in the order (0,4,1,5,2,6,3,7); rows past P stay zero."""
+    QB = pkg("qwen_batched")
+    rng = np.random.default_rng(3)
+    P, K = 200, 96
+    x = rng.standard_normal((P, K)).astype(np.float16)
+    xt = QB.f16_tiled_buffer(P, K, "cuda")
+    QB.f16_tile(dev(x), xt)
+    got = xt.cpu().numpy().view(np.float16).reshape(2, K // 32, 16, 4, 8, 8)      # tile, k-block, group, chunk, token, value
+    xp = np.zeros((256, K), np.float16)
+    xp[:P] = x
+    want = xp.reshape(2, 16, 8, K // 32, 4, 8)[..., [0, 4, 1, 5, 2, 6, 3, 7]].transpose(0, 3, 1, 4, 2, 5)
+    assert np.array_equal(got.view(np.uint16), np.ascontiguousarray(want).view(np.uint16))
+
+
+@pytest.mark.parametrize("P,n,k,epi", [(128, 128, 256, "logits"), (200, 256, 512, "store"), (130, 384, 1536, "biasf"),
+                                       (256, 1536, 8960, "resid"), (300, 512, 768, "swiglu"), (1, 128, 256, "logits")])
+def test_gemm16_prefill_matches_f16w_oracle(P, n, k, epi):
+    """Against the float64 product of the fp16-rounded weights (the reference's `dq`) and the fp16 activations; the kernel
+    accumulates in fp32 on the tensor cores, so the bar is north_star's 1e-3 of the output scale, and in practice 1e-5."""
+    QB, o = pkg("qwen_batched"), oracle()
+    rng = np.random.default_rng(P + n)
+    W = rng.integers(0, 2 ** 32, size=(n, k // 8), dtype=np.uint32).view(np.int32)
+    S = rng.uniform(0.002, 0.02, size=(n, k // 32)).astype(np.float16)
+    x = rng.standard_normal((P, k)).astype(np.float16)
+    Wt, St = QB.pack_q4(dev(W), dev(S))
+    xt = QB.f16_tiled_buffer(P, k, "cuda")
+    QB.f16_tile(dev(x), xt)
+    st = QB.Status("cuda")
+    ref = o.gemv_f16w_ref(W, S, x)
+    scale = np.abs(ref).max()
+    if epi == "resid":
+        h0 = rng.standard_normal((P, n)).astype(np.float32)
+        y = dev(h0)
+        QB.gemm16_prefill(Wt, St, xt, y, None, n, k, P, epi, n, st)
+        got, want = y.cpu().numpy(), h0 + ref
+    elif epi == "swiglu":
+        y = torch.full((P, n // 2), float("nan"), dtype=torch.float16, device="cuda")
+        QB.gemm16_prefill(Wt, St, xt, y, None, n, k, P, epi, n // 2, st)
+        g, u = ref[:, 0::2], ref[:, 1::2]
+        got, want = y.float().cpu().numpy(), g / (1 + np.exp(-g)) * u
+        scale = np.abs(want).max()
+    elif epi == "biasf":
+        b = rng.standard_normal(n).astype(np.float32)
+        y = torch.full((P, n), float("nan"), dtype=torch.float16, device="cuda")
+        QB.gemm16_prefill(Wt, St, xt, y, dev(b), n, k, P, epi, n, st)
+        got, want = y.float().cpu().numpy(), ref + b
+    else:
+        y = torch.full((P, n), float("nan"), dtype=torch.float16 if epi == "store" else torch.float32, device="cuda")
+        QB.gemm16_prefill(Wt, St, xt, y, None, n, k, P, epi, n, st)
+        got, want = y.float().cpu().numpy(), ref
+    st.check()
+    assert not np.isnan(got).any()
+    tol = 1e-3 if y.dtype == torch.float16 else 1e-4          # fp16 outputs: half an ulp of the largest value is 5e-4 of it
+    assert np.abs(got - want).max() / scale < tol
+
+
+def test_prefill_f16_route_matches_f16w_oracle_and_decode_continues():
+    """Three layers through `Prefill(linears="f16")` against the oracle's token-by-token forward with the same fp16-rounded
+    weights (statistical: fp16 activations are rounded at every storage point on both sides, the accumulation orders
+    differ)."""
+    s, E = pkg("synth"), pkg("engine")
+    cfg = s.ModelConfig("small128", 3, 512, 1536, 4, 2, 128, 4096)
+    model = s.synth_model(cfg, 5)
+    m = E.FusedQwen(model, max_len=256)
+    ids = s.synth_prompt(cfg, 160, 5)
+    pf = E.prefill(m, ids, linears="f16")
+    cos, sin = s.rope_tables(cfg, 256)
+    orc = oracle().Oracle(model, 256, cos, sin, weights="f16w")
+    rows = []
+    for t in ids:
+        orc.tok[:] = t
+        orc.step()
+        rows.append(orc.h_last[0])
+    h_ref = np.stack(rows)
+    h = pf.h.cpu().numpy()
+    err = np.abs(h - h_ref) / np.max(np.abs(h_ref))
+    assert np.median(err) < 1e-3 and np.quantile(err, 0.9) < 3e-3 and err.max() < 5e-2, (np.median(err), err.max())
+    lg_ref = orc.logits_of(h_ref[-1:])[0]
+    lg = m.logits.cpu().numpy()
+    lerr = np.max(np.abs(lg - lg_ref))
+    assert lerr / np.max(np.abs(lg_ref)) < 2e-2
+    assert lg_ref.max() - lg_ref[int(m.tok.item())] <= 2 * lerr + 1e-6
+    assert int(m.pos.item()) == len(ids)
+    m.step()
+    m.check_status()
+    assert 0 <= int(m.tok.item()) < cfg.vocab and int(m.pos.item()) == len(ids) + 1
+
+
+def test_prefill_f16_and_q8_routes_agree_statistically():
+    s, E = pkg("synth"), pkg("engine")
+    cfg = s.ModelConfig("small128", 2, 512, 1536, 4, 2, 128, 4096)
+    model = s.synth_model(cfg, 6)
+    ids = s.synth_prompt(cfg, 256, 6)
+    hs = []
+    for lin in ("q8", "f16"):
+        m = E.FusedQwen(model, max_len=256)
+        hs.append(E.prefill(m, ids, linears=lin).h.cpu().numpy())
+    err = np.abs(hs[0] - hs[1]) / np.max(np.abs(hs[1]))
+    assert np.median(err) < 5e-3 and err.max() < 0.2, (np.median(err), err.max())
