@@ -294,8 +294,9 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const __grid
       }
     }
   };
-  if constexpr (F16) {
-    if (warp == W_COPY) {
+  if (warp == W_COPY) {
+    // ===================== bulk-copy producer (one thread) =====================
+    if constexpr (F16) {
       if (lane == 0) {
         auto load_w = [&](int j) {
           const int s = j % WB;
@@ -325,34 +326,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const __grid
           }
         }
       }
-    } else if (warp == W_MMA) {
-      if (lane == 0) {
-        constexpr uint32_t IDESC16 = tc::idesc_f16(128, NTOK);
-        const uint32_t stage0 = tc::smem_u32(stage);
-        for (int u = 0; u < NU; ++u) {
-          const int s = u % SBU, as = u % NAU;
-          waitb(&a_full[as], (uint32_t)(u / NAU) & 1u, ok);
-          waitb(&b_full[s], (uint32_t)(u / SBU) & 1u, ok);
-          tc::fence_after_sync();
-#pragma unroll
-          for (int g = 0; g < G16; ++g) {
-#pragma unroll
-            for (int j = 0; j < 2; ++j) {                  // 16 of the k-block's 32 values per instruction
-              // per 8-token group: four 8-value chunks of 128 bytes; chunks 2 j, 2 j + 1 belong to this instruction
-              const uint64_t bdesc = tc::smem_desc_kmajor(stage0 + (uint32_t)s * UNIT16 + (uint32_t)g * REC16 + (uint32_t)j * 256, 128, 512);
-              tc::mma_f16_ts(tmem_d, tmem_a + (uint32_t)(as * G16 + g) * 16 + (uint32_t)j * 8, bdesc, IDESC16, (u | g | j) ? 1u : 0u);
-            }
-          }
-          tc::mma_commit(&a_empty[as]);
-          tc::mma_commit(&b_empty[s]);
-        }
-        tc::mma_commit(&d_full[0]);
-      }
-    } else if (warp >= NRW) {
-      expand16();
-    }
-  } else if (warp == W_COPY) {
-    // ===================== bulk-copy producer (one thread) =====================
+    } else
     if (lane == 0) {
       auto load_w = [&](int j) {                           // weight batch j -> slot j % WB
         const int s = j % WB;
@@ -385,6 +359,30 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const __grid
     }
   } else if (warp == W_MMA) {
     // ===================== MMA issuer (one thread) =====================
+    if constexpr (F16) {
+      if (lane == 0) {
+        constexpr uint32_t IDESC16 = tc::idesc_f16(128, NTOK);
+        const uint32_t stage0 = tc::smem_u32(stage);
+        for (int u = 0; u < NU; ++u) {
+          const int s = u % SBU, as = u % NAU;
+          waitb(&a_full[as], (uint32_t)(u / NAU) & 1u, ok);
+          waitb(&b_full[s], (uint32_t)(u / SBU) & 1u, ok);
+          tc::fence_after_sync();
+#pragma unroll
+          for (int g = 0; g < G16; ++g) {
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {                  // 16 of the k-block's 32 values per instruction
+              // per 8-token group: four 8-value chunks of 128 bytes; chunks 2 j, 2 j + 1 belong to this instruction
+              const uint64_t bdesc = tc::smem_desc_kmajor(stage0 + (uint32_t)s * UNIT16 + (uint32_t)g * REC16 + (uint32_t)j * 256, 128, 512);
+              tc::mma_f16_ts(tmem_d, tmem_a + (uint32_t)(as * G16 + g) * 16 + (uint32_t)j * 8, bdesc, IDESC16, (u | g | j) ? 1u : 0u);
+            }
+          }
+          tc::mma_commit(&a_empty[as]);
+          tc::mma_commit(&b_empty[s]);
+        }
+        tc::mma_commit(&d_full[0]);
+      }
+    } else
     if (lane == 0) {
       const uint32_t stage0 = tc::smem_u32(stage);
       for (int b = 0; b < KB; ++b) {
@@ -407,6 +405,9 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const __grid
     }
   } else if (warp >= NRW) {
     // ===================== expanders: thread = weight row, nibbles -> signed bytes -> A operand in tensor memory ==========
+    if constexpr (F16) {
+      expand16();
+    } else {
     const int r = (warp - NRW) * 32 + lane;                // row of the tile = TMEM lane
     const uint32_t lane_off = (uint32_t)(32 * (warp & 3)) << 16;
     for (int b = 0; b < KB; ++b) {
@@ -429,8 +430,8 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const __grid
         if (warp == NRW) stamp(1, b);
       }
     }
-  }
-  if (warp < NRW) {
+    }
+  } else {
     // ===================== rescale warps: TMEM lane quarter lq (rows), column quarter cq (32 activation rows) ==========
     const int lq = warp & 3, cq = warp >> 2;
     const int r = lq * 32 + lane;
