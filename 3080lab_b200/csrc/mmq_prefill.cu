@@ -55,7 +55,10 @@ constexpr size_t PF_SMEM = (size_t)WB * (WBATCH_W + WBATCH_S) + (size_t)SB * STA
 // fp16 mode (weights dequantised to fp16 by the expanders, fp16 activations, one fp32 accumulator over all of K): the
 // pipeline moves UNITS of G k-blocks so that the one MMA-issuing thread pays its waits and commits once per 2 G MMAs
 constexpr int G16 = 4;                    // k-blocks per unit
-constexpr int NAU = 4;                    // A units in tensor memory (G16 x 16 columns each)
+constexpr int MH16 = 2;                   // row halves: a CTA makes 256 weight rows x 128 tokens, two accumulators, so that
+                                          // an activation record fetched from L2 feeds two MMAs (the copies set the pace)
+constexpr int WB16 = 2;                   // weight batches in flight (8 k-blocks x 2 row halves each)
+constexpr int NAU = 2;                    // A units in tensor memory (G16 x MH16 x 16 columns each)
 constexpr int SBU = 3;                    // activation units in shared memory
 constexpr int NXG = (NRW + NEW) / 4;      // expander groups of four warps (one per TMEM lane quarter): every warp expands
 constexpr uint32_t REC16 = 128 * 32 * 2;  // one k-block of fp16 activations for 128 tokens
@@ -194,7 +197,8 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const __grid
   const int KBT = a.K >> 5;
   const int kb_lo = a.kb_bound[blockIdx.z];
   const int KB = a.kb_bound[blockIdx.z + 1] - kb_lo, NBATCH = KB >> 3;
-  const int row_tile = blockIdx.x, tok_tile = blockIdx.y;
+  const int row_tile = F16 ? 2 * (int)blockIdx.x : (int)blockIdx.x, tok_tile = blockIdx.y;   // fp16 mode: row tiles 2 x, 2 x + 1
+  [[maybe_unused]] const bool have1 = F16 && (row_tile + 1) * 128 < a.N;
   const size_t wbase = (size_t)row_tile * KBT + kb_lo;     // k-block index of this row tile in the packed arrays
   const uint8_t* xbase = a.Xt + ((size_t)tok_tile * KBT + kb_lo) * (F16 ? REC16 : STAGE_BYTES);
 
@@ -228,8 +232,8 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const __grid
   tc::fence_after_sync();
   pdl_launch_dependents();
   const uint32_t tmem = tmem_base_s;
-  // int8 mode: A NA x 8 columns, D NSLOT x 128 columns; fp16 mode: A NAU x G16 x 16 columns, D 128 columns
-  const uint32_t tmem_a = tmem, tmem_d = tmem + (F16 ? NAU * G16 * 16 : NA * 8);
+  // int8 mode: A NA x 8 columns, D NSLOT x 128 columns; fp16 mode: A NAU x G16 x MH16 x 16 columns, D MH16 x 128 columns
+  const uint32_t tmem_a = tmem, tmem_d = tmem + (F16 ? NAU * G16 * MH16 * 16 : NA * 8);
   constexpr uint32_t IDESC = tc::idesc_i8(128, NTOK);
   bool ok = true;
   // TRACE instance only: timeline of the first 64 k-blocks of one CTA, one row per pipeline role (SM clock).  The stamps
@@ -257,17 +261,19 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const __grid
     const uint32_t lane_off = (uint32_t)(32 * (warp & 3)) << 16;
     const __half2 c1032 = __float2half2_rn(1032.f), c16th = __float2half2_rn(0.0625f), c72 = __float2half2_rn(-72.f);
     for (int u = 0; u < NU; ++u) {
-      const int b0 = u * G16, ws = (b0 >> 3) % WB;
-      if ((b0 & 7) == 0) waitb(&w_full[ws], (uint32_t)((b0 >> 3) / WB) & 1u, ok);
+      const int b0 = u * G16, ws = (b0 >> 3) % WB16;
+      if ((b0 & 7) == 0) waitb(&w_full[ws], (uint32_t)((b0 >> 3) / WB16) & 1u, ok);
       if (u % NXG == grp) {
         const int as = u % NAU;
         waitb(&a_empty[as], ((uint32_t)(u / NAU) & 1u) ^ 1u, ok);   // the MMAs of unit u - NAU have read this operand
         tc::fence_after_sync();
 #pragma unroll
-        for (int g = 0; g < G16; ++g) {
+        for (int gh = 0; gh < G16 * MH16; ++gh) {
+          const int g = gh >> 1, hf = gh & 1;
+          if (hf && !have1) continue;
           const int bb = (b0 + g) & 7;
-          const uint4 w = *reinterpret_cast<const uint4*>(slabW + (size_t)ws * WBATCH_W + (size_t)bb * 2048 + r * 16);
-          const __half2 d2 = __half2half2(reinterpret_cast<const __half*>(slabS + (size_t)ws * WBATCH_S)[bb * 128 + r]);
+          const uint4 w = *reinterpret_cast<const uint4*>(slabW + (size_t)(ws * MH16 + hf) * WBATCH_W + (size_t)bb * 2048 + r * 16);
+          const __half2 d2 = __half2half2(reinterpret_cast<const __half*>(slabS + (size_t)(ws * MH16 + hf) * WBATCH_S)[bb * 128 + r]);
           const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
           uint32_t ex[16];
 #pragma unroll
@@ -282,7 +288,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const __grid
             ex[4 * i + 2] = h2_as_u32(__hmul2(l1, d2));
             ex[4 * i + 3] = h2_as_u32(__hmul2(h1, d2));
           }
-          tc::tmem_st16(tmem_a + lane_off + (uint32_t)(as * G16 + g) * 16, ex);
+          tc::tmem_st16(tmem_a + lane_off + (uint32_t)((as * G16 + g) * MH16 + hf) * 16, ex);
         }
         tc::tmem_wait_st();                                // warp-wide
         tc::fence_before_sync();
@@ -298,18 +304,21 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const __grid
     // ===================== bulk-copy producer (one thread) =====================
     if constexpr (F16) {
       if (lane == 0) {
-        auto load_w = [&](int j) {
-          const int s = j % WB;
-          tc::mbar_expect_tx(&w_full[s], WBATCH_W + WBATCH_S);
-          bulk_g2s(slabW + (size_t)s * WBATCH_W, a.Wt + (wbase + (size_t)j * 8) * 2048, WBATCH_W, &w_full[s]);
-          bulk_g2s(slabS + (size_t)s * WBATCH_S, a.St + (wbase + (size_t)j * 8) * 128, WBATCH_S, &w_full[s]);
+        auto load_w = [&](int j) {                         // batch j of both row halves -> slot j % WB16
+          const int s = j % WB16;
+          tc::mbar_expect_tx(&w_full[s], (have1 ? 2u : 1u) * (WBATCH_W + WBATCH_S));
+          for (int hf = 0; hf < (have1 ? 2 : 1); ++hf) {
+            const size_t wb = wbase + (size_t)hf * KBT + (size_t)j * 8;
+            bulk_g2s(slabW + (size_t)(s * MH16 + hf) * WBATCH_W, a.Wt + wb * 2048, WBATCH_W, &w_full[s]);
+            bulk_g2s(slabS + (size_t)(s * MH16 + hf) * WBATCH_S, a.St + wb * 128, WBATCH_S, &w_full[s]);
+          }
         };
         auto load_u = [&](int u) {                         // G16 consecutive records = one contiguous piece
           const int s = u % SBU;
           tc::mbar_expect_tx(&b_full[s], UNIT16);
           bulk_g2s(stage + (size_t)s * UNIT16, xbase + (size_t)u * UNIT16, UNIT16, &b_full[s]);
         };
-        for (int j = 0; j < WB && j < NBATCH; ++j) load_w(j);
+        for (int j = 0; j < WB16 && j < NBATCH; ++j) load_w(j);
         pdl_wait();
         for (int u = 0; u < SBU && u < NU; ++u) load_u(u);
         for (int ou = 0; ou < NU; ++ou) {
@@ -319,9 +328,9 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const __grid
           }
           if (((ou * G16 + G16 - 1) & 7) == 7) {
             const int oj = (ou * G16) >> 3;
-            if (oj + WB < NBATCH) {
-              waitb(&w_empty[oj % WB], (uint32_t)(oj / WB) & 1u, ok);
-              load_w(oj + WB);
+            if (oj + WB16 < NBATCH) {
+              waitb(&w_empty[oj % WB16], (uint32_t)(oj / WB16) & 1u, ok);
+              load_w(oj + WB16);
             }
           }
         }
@@ -374,7 +383,11 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const __grid
             for (int j = 0; j < 2; ++j) {                  // 16 of the k-block's 32 values per instruction
               // per 8-token group: four 8-value chunks of 128 bytes; chunks 2 j, 2 j + 1 belong to this instruction
               const uint64_t bdesc = tc::smem_desc_kmajor(stage0 + (uint32_t)s * UNIT16 + (uint32_t)g * REC16 + (uint32_t)j * 256, 128, 512);
-              tc::mma_f16_ts(tmem_d, tmem_a + (uint32_t)(as * G16 + g) * 16 + (uint32_t)j * 8, bdesc, IDESC16, (u | g | j) ? 1u : 0u);
+#pragma unroll
+              for (int hf = 0; hf < MH16; ++hf)            // the same activations against both row halves
+                if (hf == 0 || have1)
+                  tc::mma_f16_ts(tmem_d + (uint32_t)hf * 128, tmem_a + (uint32_t)((as * G16 + g) * MH16 + hf) * 16 + (uint32_t)j * 8, bdesc,
+                                 IDESC16, (u | g | j) ? 1u : 0u);
             }
           }
           tc::mma_commit(&a_empty[as]);
@@ -458,17 +471,8 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const __grid
     if constexpr (F16) {
       // fp16 mode: these warps expand too; then the one accumulator (complete sums over K) is read out once
       expand16();
-      uint32_t dA[16], dB[16];
       waitb(&d_full[0], 0u, ok);
       tc::fence_after_sync();
-      tc::tmem_ld16(dbase, dA);
-      tc::tmem_ld16(dbase + 16, dB);
-      tc::tmem_wait_ld();
-#pragma unroll
-      for (int n = 0; n < 8; ++n) {
-        acc2[n] = tc::pack2u(dA[2 * n], dA[2 * n + 1]);
-        acc2[8 + n] = tc::pack2u(dB[2 * n], dB[2 * n + 1]);
-      }
     } else {
     // Rolling schedule: the read-back of the next 16 columns is always in flight while the previous 16 are folded, so a
     // warp does not sit idle on tensor-memory latency.  (Handing the slot back before folding anything was measured:
@@ -527,11 +531,25 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const __grid
     }
 
     }
-    // ---- epilogue: thread (row r, 32 activation rows)
+    // ---- epilogue: thread (row r, 32 activation rows); fp16 mode: once per row half, from that half's accumulator
     if (t == 0) stamp(10, 2);                              // main loop left
     pdl_wait();                                            // Y / AUX may be written by the previous kernel
     if (t == 0) stamp(10, 5);                              // previous grid seen complete
-    const int row = row_tile * 128 + r;
+    for (int hh = 0; hh < (F16 ? MH16 : 1); ++hh) {
+    const int rt = row_tile + hh;
+    if constexpr (F16) {
+      if (hh && !have1) break;
+      uint32_t dA[16], dB[16];
+      tc::tmem_ld16(dbase + (uint32_t)hh * 128, dA);
+      tc::tmem_ld16(dbase + (uint32_t)hh * 128 + 16, dB);
+      tc::tmem_wait_ld();
+#pragma unroll
+      for (int n = 0; n < 8; ++n) {
+        acc2[n] = tc::pack2u(dA[2 * n], dA[2 * n + 1]);
+        acc2[8 + n] = tc::pack2u(dB[2 * n], dB[2 * n + 1]);
+      }
+    }
+    const int row = rt * 128 + r;
     const int tok0 = tok_tile * NTOK + cq * 32;
     const float bias = ((a.epi == Q4B_EPI_BIASF || a.epi == Q4B_EPI_BIASF_ROPE_KV) && row < a.N) ? reinterpret_cast<const float*>(a.AUX)[row] : 0.f;
     if (a.epi == Q4B_EPI_BIASF_ROPE_KV) {
@@ -547,7 +565,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const __grid
       }
       asm volatile("bar.sync 1, %0;" ::"n"(NRW * 32) : "memory");
       if (t == 0) stamp(10, 6);                            // rounded tile in shared memory
-      rope_kv_phase(a, ybuf, row_tile, tok_tile * NTOK, t);
+      rope_kv_phase(a, ybuf, rt, tok_tile * NTOK, t);
     } else if (a.epi == Q4B_EPI_SWIGLU_Q8) {
       // SwiGLU + re-quantise for `down` (lab/qwen_batched.py:1363-1396): the product rounded to fp16, then the Q8_1
       // quantiser of quant_q8_1.cu on it, written straight into the tiled operand format of the next GEMM.  This row
@@ -563,7 +581,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const __grid
       }
       asm volatile("bar.sync 1, %0;" ::"n"(NRW * 32) : "memory");
       if (t == 0) stamp(10, 6);                            // rounded tile in shared memory
-      swiglu_q8_phase(a, abuf, row_tile, tok_tile, t);
+      swiglu_q8_phase(a, abuf, rt, tok_tile, t);
     } else if (a.epi == Q4B_EPI_SWIGLU) {
 #pragma unroll
       for (int j = 0; j < 16; ++j) {
@@ -612,6 +630,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const __grid
           default: break;
         }
       }
+    }
     }
     }
   }
@@ -719,7 +738,7 @@ int mmq_prefill(const void* Wt, const void* St, const void* Xt, void* Y, const v
   a.Y2 = Y2;
   a.kb_bound[0] = 0;
   a.kb_bound[1] = a.kb_bound[2] = a.kb_bound[3] = a.kb_bound[4] = K / 32;
-  dim3 grid((N + 127) / 128, (P + NTOK - 1) / NTOK);
+  dim3 grid(f16 ? (N + 255) / 256 : (N + 127) / 128, (P + NTOK - 1) / NTOK);
   if (Y2) {
     if (epilogue != Q4B_EPI_RESID || parts < 2 || parts > 4 || K / 256 < parts || !aligned16(Y2))
       return fail(Q4B_E_SHAPE, "mmq_prefill: a K-split launch needs the resid epilogue, 2 .. 4 parts and K >= 256 per part");

@@ -454,6 +454,36 @@ def bench_prefill(model, cfg, steps: int, warmup: int, local_rank: int, torch, i
     # quality of int8 activations: mean next-token NLL of the first 512 prompt tokens under the prefill path and under
     # the fp16-activation decode path (the reference's perplexity check, scripts/qwen_prefill.py:315-333)
     nll = engine.perplexity(m, ids[:512], chunk=512)
+    # the other route: fp16 activations, weights dequantised to fp16 inside the GEMM, fp32 tensor-core accumulation over
+    # all of K (the arithmetic of the reference's `cublas` prefill mode, scripts/qwen_prefill.py:37-53, 156-160)
+    pf16 = engine.Prefill(m, P, linears="f16")
+    pf16.tok.copy_(host_ids)
+    g16 = graph_of(lambda: pf16.chunk(0), torch)
+    for _ in range(3):
+        g16.replay()
+    torch.cuda.synchronize()
+    s.record()
+    for _ in range(steps):
+        g16.replay()
+    e.record()
+    torch.cuda.synchronize()
+    ms16 = s.elapsed_time(e) / steps
+    def gu16_all():
+        for L in L0:
+            Wt, St = m.packed[id(L["gu"][0])]
+            QB_.gemm16_prefill(Wt, St, pf16.xt16, pf16.xm, None, 2 * cfg.ffn, cfg.hidden, P, "swiglu", cfg.ffn, pf16.status)
+    QB_ = importlib.import_module("3080lab_b200.qwen_batched")
+    us_gu16 = time_kernel(gu16_all, cfg.layers, 3, torch)
+    pf16.status.check("prefill, fp16 route")
+    peaks, peak_kind = measured_peaks()
+    f16_peak = peaks.get("bf16_tflops")
+    other = {"f16": {"tok_per_s": P / ms16 * 1e3, "ms_per_step": ms16, "launches_per_step": pf16.launches_per_chunk,
+                     "what": "Prefill(linears='f16'): fp16 activations x Q4_0 weights dequantised to fp16 in the GEMM, tcgen05.mma.kind::f16",
+                     "gate_up_us": us_gu16, "gate_up_tflops": ops_gu / us_gu16 / 1e6,
+                     "gate_up_frac_of_bf16_peak": (ops_gu / us_gu16 / 1e6 / f16_peak) if f16_peak else None,
+                     "bf16_peak_tflops": f16_peak, "peak_kind": "of " + peak_kind + " (cuBLAS bf16 GEMM, burst)",
+                     "whole_pass_tflops": ops / (ms16 * 1e-3) / 1e12}}
+    del g16, pf16
     out = {
         "metric": "prefill_tok_per_s", "value": P / ms * 1e3, "unit": "tok/s", "n_gpus": 1, "steps": steps,
         "warmup": warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
@@ -470,6 +500,7 @@ def bench_prefill(model, cfg, steps: int, warmup: int, local_rank: int, torch, i
         "e2e": {"value": P / e2e_ms * 1e3, "unit": "tok/s", "h2d_bytes_per_step": P * 8, "d2h_bytes_per_step": 8},
         "nll": {"int8_activations": nll["i8"], "fp16_activations": nll["f16"], "tokens": nll["tokens"],
                 "what": "mean next-token NLL over the first 512 prompt tokens (uniform random tokens), prefill path vs decode path"},
+        "other_routes": other,
         "gpu_launches": pf.launches_per_chunk * steps, "clocks": clocks}
     del pf, m, g
     torch.cuda.empty_cache()
