@@ -78,6 +78,8 @@ SIGNATURES = {
     "q4b_f16_tiled_bytes": (_Z, [_I, _I]),
     "q4b_f16_tiled": (_I, [_P, _P, _I, _I, _P]),
     "q4b_mm_prefill_q4_0_f16": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P]),
+    "q4b_mm_prefill_f16_resid_ksplit": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P]),
+    "q4b_rmsnorm_f16_tiled_add": (_I, [_P, _P, _I, _P, _P, _I, _I, _F, _P]),
     "q4b_quant_q8_1_tiled": (_I, [_P, _P, _I, _I, _P]),
     "q4b_rmsnorm_q8_1_tiled": (_I, [_P, _P, _P, _I, _I, _F, _P]),
     "q4b_mmq_prefill_q4_0_q8_1": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P]),

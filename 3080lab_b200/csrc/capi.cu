@@ -99,6 +99,7 @@ int mmq_prefill(const void*, const void*, const void*, void*, const void*, int, 
                 const float* cosT = nullptr, const float* sinT = nullptr, void* kc = nullptr, void* vc = nullptr, int NH = 0,
                 int NKV = 0, int max_len = 0, int pos0 = 0, float* Y2 = nullptr, int parts = 1, int f16 = 0);
 size_t f16_tiled_bytes(int, int);
+int rmsnorm_f16_tiled(const float*, const float*, void*, int, int, float, cudaStream_t, float* h_add = nullptr, int n_add = 0);
 int f16_tiled(const void*, void*, int, int, cudaStream_t);
 int add_rows(float*, const float*, size_t, int, cudaStream_t);
 int quant_q8_1_tiled(const void*, void*, int, int, cudaStream_t);
@@ -264,6 +265,19 @@ int q4b_mm_prefill_q4_0_f16(const void* Wt, const void* St, const void* xt, void
                             int epilogue, int ldy, uint32_t* status, q4b_stream_t stream) {
   return mmq_prefill(Wt, St, xt, Y, AUX, N, K, P, epilogue, ldy, status, S(stream), nullptr, nullptr, nullptr, nullptr, 0, 0, 0, 0,
                      nullptr, 1, 1);
+}
+
+int q4b_mm_prefill_f16_resid_ksplit(const void* Wt, const void* St, const void* xt, float* Y, float* Y2, int parts, int N, int K, int P,
+                                    int ldy, uint32_t* status, q4b_stream_t stream) {
+  if (parts < 2 || !Y2) return fail(Q4B_E_ARG, "mm_prefill_f16_resid_ksplit: parts >= 2 and Y2 required");
+  return mmq_prefill(Wt, St, xt, Y, nullptr, N, K, P, Q4B_EPI_RESID, ldy, status, S(stream), nullptr, nullptr, nullptr, nullptr, 0, 0,
+                     0, 0, Y2, parts, 1);
+}
+
+int q4b_rmsnorm_f16_tiled_add(float* h, const float* h_add, int n_add, const float* w, void* xt, int rows, int H, float eps,
+                              q4b_stream_t stream) {
+  if (n_add < 0 || n_add > 3 || (n_add > 0 && !h_add)) return fail(Q4B_E_ARG, "rmsnorm_f16_tiled_add: 0 .. 3 addends");
+  return rmsnorm_f16_tiled(h, w, xt, rows, H, eps, S(stream), n_add ? const_cast<float*>(h_add) : nullptr, n_add);
 }
 
 int q4b_mmq_prefill_trace(int64_t* device_buffer, size_t entries) {

@@ -57,6 +57,43 @@ __global__ void __launch_bounds__(1024) rmsnorm_q8_1_tiled_kernel(const float* h
   quant_block4_tiled(v, xt + ((size_t)(row >> 7) * KB + (i0 >> 5)) * 4608, row & 127, t & 7);
 }
 
+// The same row pass with fp16 output in the operand order of the fp16-mode prefill GEMM (per 128-token tile and k-block
+// 8192 bytes, [8-token group][8-value chunk][token][16 bytes], a chunk's values as (0,4,1,5,2,6,3,7)).  Two neighbouring
+// threads hold the two halves of a chunk and trade one pair of values.
+__global__ void __launch_bounds__(1024) rmsnorm_f16_tiled_kernel(const float* h, const float* __restrict__ w, uint8_t* xt, int H,
+                                                                 float eps, float* h_add, int n_add) {
+  __shared__ float part[32];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int row = blockIdx.x, t = threadIdx.x, i0 = 4 * t;
+  float4 hv = *reinterpret_cast<const float4*>(h + (size_t)row * H + i0);
+  if (h_add) {
+    for (int j = 0; j < n_add; ++j) {                    // the addends [n_add][rows, H], in order
+      const float4 av = *reinterpret_cast<const float4*>(h_add + ((size_t)j * gridDim.x + row) * H + i0);
+      hv.x += av.x; hv.y += av.y; hv.z += av.z; hv.w += av.w;
+    }
+    *reinterpret_cast<float4*>(const_cast<float*>(h) + (size_t)row * H + i0) = hv;
+  }
+  const float4 wv = *reinterpret_cast<const float4*>(w + i0);
+  float ss = hv.x * hv.x + hv.y * hv.y + hv.z * hv.z + hv.w * hv.w;
+  ss = warp_sum(ss);
+  if ((t & 31) == 0) part[t >> 5] = ss;
+  __syncthreads();
+  float tot = 0.f;
+  for (int j = 0; j < (int)(blockDim.x >> 5); ++j) tot += part[j];
+  const float r = rsqrtf(tot / (float)H + eps);
+  const __half2 a2 = __floats2half2_rn(hv.x * r * wv.x, hv.y * r * wv.y), b2 = __floats2half2_rn(hv.z * r * wv.z, hv.w * r * wv.w);
+  const uint32_t A = *reinterpret_cast<const uint32_t*>(&a2), B = *reinterpret_cast<const uint32_t*>(&b2);
+  const bool upper = t & 1;                                // values 4 .. 7 of the chunk
+  const uint32_t R = __shfl_xor_sync(0xffffffffu, upper ? A : B, 1);
+  uint2 o;                                                 // lower: (0,4,1,5) from A = (0,1), R = (4,5); upper: (2,6,3,7) from R = (2,3), B = (6,7)
+  o.x = upper ? __byte_perm(R, B, 0x5410) : __byte_perm(A, R, 0x5410);
+  o.y = upper ? __byte_perm(R, B, 0x7632) : __byte_perm(A, R, 0x7632);
+  const int wi = i0 >> 3, KB = H >> 5, tk = row & 127;
+  uint8_t* rec = xt + ((size_t)(row >> 7) * KB + (wi >> 2)) * 8192;
+  *reinterpret_cast<uint2*>(rec + (tk >> 3) * 512 + (wi & 3) * 128 + (tk & 7) * 16 + (upper ? 8 : 0)) = o;
+}
+
 __global__ void __launch_bounds__(256) quant_q8_1_kernel(const __half* x, int8_t* xq, __half* xd, __half* xsum, size_t nblk) {
   pdl_launch_dependents();
   pdl_wait();
@@ -128,6 +165,14 @@ int rmsnorm_q8_1_tiled(const float* h, const float* w, void* xt, int rows, int H
     return fail(Q4B_E_ALIGN, "rmsnorm_q8_1_tiled: null or misaligned pointer");
   return check_launch(launch_pdl(rmsnorm_q8_1_tiled_kernel, dim3(rows), dim3(H / 4), 0, st, h, w, (uint8_t*)xt, H, eps, h_add, n_add),
                       "rmsnorm_q8_1_tiled");
+}
+
+int rmsnorm_f16_tiled(const float* h, const float* w, void* xt, int rows, int H, float eps, cudaStream_t st, float* h_add, int n_add) {
+  if (rows <= 0 || H <= 0 || (H % 128) || H > 4096) return fail(Q4B_E_SHAPE, "rmsnorm_f16_tiled: H must be a multiple of 128, at most 4096");
+  if (!h || !w || !xt || !aligned16(h) || !aligned16(w) || !aligned16(xt) || !aligned16(h_add))
+    return fail(Q4B_E_ALIGN, "rmsnorm_f16_tiled: null or misaligned pointer");
+  return check_launch(launch_pdl(rmsnorm_f16_tiled_kernel, dim3(rows), dim3(H / 4), 0, st, h, w, (uint8_t*)xt, H, eps, h_add, n_add),
+                      "rmsnorm_f16_tiled");
 }
 
 namespace {

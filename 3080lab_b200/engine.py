@@ -491,8 +491,8 @@ class Prefill:
         """linears: "q8" = the reference's prefill arithmetic (Q8_1 activations, int8 MMQ, described above); "f16" = the
         arithmetic of its fp16-weight batched GEMV (lab/qwen_batched.py:467-641) at prefill width: fp16 activations, weights
         dequantised to fp16 inside the GEMM, fp32 accumulation over all of K on the tensor cores - about three times
-        faster per pass and without the int8 rounding of the activations, eleven launches per layer (RMSNorm, operand
-        tiling, GEMM ...).
+        faster per pass and without the int8 rounding of the activations, nine launches per layer (RMSNorm into the operand
+        order, GEMM, attention, operand tiling, GEMM ...).
         fused: the reference's seven launches per layer (scripts/qwen_prefill.py:196-246): the QKV GEMM rotates and
         appends K/V (`biasf_kv`), the flash kernel emits the o-projection's Q8_1 input (`q8`), the gate/up GEMM emits the
         down GEMM's (`swiglu_q8`).  fused=False keeps those three steps as separate launches (ten per layer); both give
@@ -537,10 +537,25 @@ class Prefill:
         self.h2 = torch.zeros(nbuf, P, c.hidden, dtype=f32, device=dv) if nbuf > 0 else None
         self.launches_per_chunk = 1 + (7 if fused else 10) * c.layers + (1 if self.split_k else 0)
         if linears == "f16":
-            self.x16 = torch.zeros(P, c.hidden, dtype=f16, device=dv)
+            # 256 weight rows per CTA: half as many tiles; split along K where that leaves SMs idle (down_proj)
+            tiles16 = ((c.hidden + 255) // 256) * ((P + 127) // 128)
+
+            def parts16(Kdim: int) -> int:
+                best, cost = 1, -(-tiles16 // sms)
+                for n in (2, 3, 4):
+                    if Kdim // 32 // n < 64:
+                        break
+                    cn = -(-tiles16 * n // sms) / n
+                    if cn < cost - 1e-9:
+                        best, cost = n, cn
+                return best
+            on = (tiles16 < sms) if split_k is None else bool(split_k)
+            self.parts = {Kd: (parts16(Kd) if on else 1) for Kd in (c.q_rows, c.ffn)}
+            nbuf = max(self.parts.values()) - 1
+            self.h2 = torch.zeros(nbuf, P, c.hidden, dtype=f32, device=dv) if nbuf > 0 else None
             self.xt16 = QB.f16_tiled_buffer(P, max(c.hidden, c.q_rows), dv)
             self.xt16b = QB.f16_tiled_buffer(P, c.ffn, dv)
-            self.launches_per_chunk = 1 + 11 * c.layers
+            self.launches_per_chunk = 1 + 9 * c.layers + (1 if nbuf > 0 else 0)
 
     def gemm8(self, pair, xt, N, Kdim, Y, aux, epi, ldy):
         Wt, St = self.m.packed[id(pair[0])]
@@ -567,24 +582,40 @@ class Prefill:
             QB.rmsnorm_q8_tiled(self.h, w, self.xt, self.m.cfg.eps)
 
     def gemm16(self, pair, x, N, Kdim, Y, aux, epi, ldy):
-        """fp16 route: tile x [P, Kdim] into the tensor-core operand order, then the GEMM."""
+        """fp16 route: x [P, Kdim] fp16 (None: already in the operand buffer) -> operand order -> the GEMM; a `resid` GEMM
+        may be split along K like the int8 one (`self._pending` parts left for the next norm to add)."""
         Wt, St = self.m.packed[id(pair[0])]
         xt = self.xt16b if Kdim == self.m.cfg.ffn else self.xt16
-        QB.f16_tile(x, xt)
-        QB.gemm16_prefill(Wt, St, xt, Y, aux, N, Kdim, self.P, epi, ldy, self.status)
+        if x is not None:
+            QB.f16_tile(x, xt)
+        n = self.parts.get(Kdim, 1) if epi == "resid" else 1
+        if n > 1:
+            QB.gemm16_prefill_resid_ksplit(Wt, St, xt, Y, self.h2[:n - 1], N, Kdim, self.P, ldy, self.status)
+            self._pending = n - 1
+        else:
+            QB.gemm16_prefill(Wt, St, xt, Y, aux, N, Kdim, self.P, epi, ldy, self.status)
+
+    def norm16(self, w):
+        """RMSNorm of h straight into the operand buffer, completing h with pending K parts first."""
+        QB.rmsnorm_f16_tiled(self.h, w, self.xt16, self.m.cfg.eps, self.h2[:self._pending] if self._pending else None)
+        self._pending = 0
 
     def _chunk_f16(self, pos0: int) -> None:
         m, c, H = self.m, self.m.cfg, self.m.cfg.hidden
         K.embed(m.embed, self.tok, self.h)
+        self._pending = 0
         for i, L in enumerate(m.L):
-            K.rms(self.h, L["ln1"], self.x16, c.eps)
-            self.gemm16(L["qkv"], self.x16, c.qkv_rows, H, self.qkv, L["qkv_b"], "biasf", c.qkv_rows)
+            self.norm16(L["ln1"])
+            self.gemm16(L["qkv"], None, c.qkv_rows, H, self.qkv, L["qkv_b"], "biasf", c.qkv_rows)
             QB.attn_prefill(self.qkv, m.cos, m.sin, m.kc[i], m.vc[i], self.att, c.n_heads, c.n_kv_heads, c.head_dim,
                             m.max_len, pos0, m.scale)
             self.gemm16(L["o"], self.att, H, c.q_rows, self.h, None, "resid", H)
-            K.rms(self.h, L["ln2"], self.x16, c.eps)
-            self.gemm16(L["gu"], self.x16, 2 * c.ffn, H, self.xm, None, "swiglu", c.ffn)
+            self.norm16(L["ln2"])
+            self.gemm16(L["gu"], None, 2 * c.ffn, H, self.xm, None, "swiglu", c.ffn)
             self.gemm16(L["down"], self.xm, H, c.ffn, self.h, None, "resid", H)
+        if self._pending:
+            QB.add_rows(self.h, self.h2[:self._pending])
+            self._pending = 0
 
     def chunk(self, pos0: int = 0) -> None:
         """One pass over the P tokens in self.tok at positions pos0 .. pos0 + P - 1."""

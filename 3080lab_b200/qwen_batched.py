@@ -154,6 +154,20 @@ def gemm16_prefill(Wt, St, xt, Y, aux, N: int, K: int, P: int, epi: str, ldy: in
     _ffi.call("q4b_mm_prefill_q4_0_f16", _p(Wt), _p(St), _p(xt), _p(Y), _p(aux), N, K, P, _ffi.EPI[epi], ldy, _p(status.word), _stream())
 
 
+def gemm16_prefill_resid_ksplit(Wt, St, xt, Y, Y2, N: int, K: int, P: int, ldy: int, status: Status) -> None:
+    """`gemm16_prefill` with the resid epilogue, its launch split along K into 1 + Y2.shape[0] parts (Y += part 0, Y2[z - 1] =
+    part z)."""
+    _ffi.call("q4b_mm_prefill_f16_resid_ksplit", _p(Wt), _p(St), _p(xt), _p(Y), _p(Y2), 1 + Y2.shape[0], N, K, P, ldy,
+              _p(status.word), _stream())
+
+
+def rmsnorm_f16_tiled(h, w, xt, eps: float, h_add=None) -> None:
+    """RMSNorm of every row of h (fp32) as fp16 in the operand order of `gemm16_prefill`; with h_add [n, rows, H] first
+    h += h_add[0] + h_add[1] + .. (written back)."""
+    n = 0 if h_add is None else h_add.shape[0]
+    _ffi.call("q4b_rmsnorm_f16_tiled_add", _p(h), _p(h_add), n, _p(w), _p(xt), h.shape[0], h.shape[1], float(eps), _stream())
+
+
 def quant_q8_tiled(x, xt) -> None:
     """x fp16 [rows, K] -> tiled Q8_1 (the prefill MMQ's activation operand)."""
     _ffi.call("q4b_quant_q8_1_tiled", _p(x), _p(xt), x.shape[0], x.shape[1], _stream())

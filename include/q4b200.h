@@ -298,6 +298,13 @@ int q4b_f16_tiled(const void* x, void* xt, int rows, int K, q4b_stream_t stream)
 int q4b_mm_prefill_q4_0_f16(const void* Wt, const void* St, const void* xt, void* Y, const void* AUX, int N, int K, int P,
                             int epilogue, int ldy, uint32_t* status, q4b_stream_t stream);
 
+/* fp16 mode of q4b_mmq_prefill_resid_ksplit (same contract: Y += part 0, Y2[z - 1] = part z), and the RMSNorm that completes
+ * h with n_add (0 .. 3) such parts and writes its fp16 result straight into the fp16 operand order (q4b_f16_tiled's). */
+int q4b_mm_prefill_f16_resid_ksplit(const void* Wt, const void* St, const void* xt, float* Y, float* Y2, int parts, int N, int K, int P,
+                                    int ldy, uint32_t* status, q4b_stream_t stream);
+int q4b_rmsnorm_f16_tiled_add(float* h, const float* h_add, int n_add, const float* w, void* xt, int rows, int H, float eps,
+                              q4b_stream_t stream);
+
 /* Pipeline timeline of the prefill GEMM: while a device buffer of 11 x 64 int64 is set, every q4b_mmq_prefill_* launch
  * runs a second instance of the kernel whose CTA (0, 0, 0) writes SM-clock stamps for its first 64 k-blocks, one row per
  * event: 0 activation stage requested, 1 A operand written (first expander warp), 2 MMA issued and committed, 3 accumulator

@@ -429,3 +429,53 @@ def test_prefill_f16_and_q8_routes_agree_statistically():
         hs.append(E.prefill(m, ids, linears=lin).h.cpu().numpy())
     err = np.abs(hs[0] - hs[1]) / np.max(np.abs(hs[1]))
     assert np.median(err) < 5e-3 and err.max() < 0.2, (np.median(err), err.max())
+
+
+def test_rmsnorm_f16_tiled_equals_rmsnorm_then_tiling_and_adds_parts():
+    """Layout exactly that of `f16_tile`, values those of the fp16 RMSNorm kernel to one fp16 ulp (the two kernels sum the
+    squares in different orders); with addends: h completed exactly, and the same bits as the plain call on the completed h."""
+    QB, K = pkg("qwen_batched"), pkg("qwen_kernels")
+    rng = np.random.default_rng(11)
+    P, H = 200, 512
+    h = rng.standard_normal((P, H)).astype(np.float32)
+    add = rng.standard_normal((2, P, H)).astype(np.float32)
+    w = rng.uniform(0.5, 1.5, H).astype(np.float32)
+    x16 = torch.zeros(P, H, dtype=torch.float16, device="cuda")
+    K.rms(dev(h), dev(w), x16, 1e-6)
+    want = QB.f16_tiled_buffer(P, H, "cuda")
+    QB.f16_tile(x16, want)
+    got = QB.f16_tiled_buffer(P, H, "cuda")
+    QB.rmsnorm_f16_tiled(dev(h), dev(w), got, 1e-6)
+    a = got.cpu().numpy().view(np.int16).astype(np.int32)
+    b = want.cpu().numpy().view(np.int16).astype(np.int32)
+    assert np.abs(a - b).max() <= 1 and np.mean(a != b) < 0.01
+    total = (h + add[0]) + add[1]
+    plain = QB.f16_tiled_buffer(P, H, "cuda")
+    QB.rmsnorm_f16_tiled(dev(total), dev(w), plain, 1e-6)
+    hd = dev(h)
+    summed = QB.f16_tiled_buffer(P, H, "cuda")
+    QB.rmsnorm_f16_tiled(hd, dev(w), summed, 1e-6, dev(add))
+    assert torch.equal(summed, plain)
+    assert np.array_equal(hd.cpu().numpy(), total)
+
+
+@pytest.mark.parametrize("P,n,k,parts", [(256, 1536, 8960, 3), (130, 512, 1536, 2), (2048, 1536, 8960, 3)])
+def test_gemm16_resid_split_along_k_matches_the_unsplit_launch(P, n, k, parts):
+    QB = pkg("qwen_batched")
+    rng = np.random.default_rng(P + parts)
+    W = rng.integers(0, 2 ** 32, size=(n, k // 8), dtype=np.uint32).view(np.int32)
+    S = rng.uniform(0.002, 0.02, size=(n, k // 32)).astype(np.float16)
+    Wt, St = QB.pack_q4(dev(W), dev(S))
+    xt = QB.f16_tiled_buffer(P, k, "cuda")
+    QB.f16_tile(dev(rng.standard_normal((P, k)).astype(np.float16)), xt)
+    st = QB.Status("cuda")
+    h0 = rng.standard_normal((P, n)).astype(np.float32)
+    y1, y2 = dev(h0), dev(h0)
+    y2b = torch.full((parts - 1, P, n), float("nan"), device="cuda")
+    QB.gemm16_prefill(Wt, St, xt, y1, None, n, k, P, "resid", n, st)
+    QB.gemm16_prefill_resid_ksplit(Wt, St, xt, y2, y2b, n, k, P, n, st)
+    QB.add_rows(y2, y2b)
+    st.check()
+    a, b = y1.cpu().numpy(), y2.cpu().numpy()
+    assert not np.isnan(b).any()
+    assert np.abs(a - b).max() / np.abs(a).max() < 1e-5        # the same products, summed in parts
