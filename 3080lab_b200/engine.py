@@ -488,10 +488,10 @@ class Prefill:
     cache of the `FusedQwen` it wraps, so decode continues from the prefilled state."""
 
     def __init__(self, m: FusedQwen, P: int, fused: bool = True, split_k=None, linears: str = "q8"):
-        """linears: "q8" = the reference's prefill arithmetic (Q8_1 activations, int8 MMQ, described above); "f16" = the
-        arithmetic of its fp16-weight batched GEMV (lab/qwen_batched.py:467-641) at prefill width: fp16 activations, weights
-        dequantised to fp16 inside the GEMM, fp32 accumulation over all of K on the tensor cores - about three times
-        faster per pass and without the int8 rounding of the activations, nine launches per layer (RMSNorm into the operand
+        """linears: "q8" = the reference's `i8` prefill mode (Q8_1 activations, int8 MMQ, described above); "f16" = the
+        arithmetic of its `cublas` mode (scripts/qwen_prefill.py:37-53, 156-160: weights dequantised to fp16, fp16
+        activations, fp32 accumulation), with the dequantisation inside the GEMM kernel - about three times
+        faster per pass and without the int8 rounding of the activations, ten launches per layer (RMSNorm into the operand
         order, GEMM, attention, operand tiling, GEMM ...).
         fused: the reference's seven launches per layer (scripts/qwen_prefill.py:196-246): the QKV GEMM rotates and
         appends K/V (`biasf_kv`), the flash kernel emits the o-projection's Q8_1 input (`q8`), the gate/up GEMM emits the
@@ -555,7 +555,7 @@ class Prefill:
             self.h2 = torch.zeros(nbuf, P, c.hidden, dtype=f32, device=dv) if nbuf > 0 else None
             self.xt16 = QB.f16_tiled_buffer(P, max(c.hidden, c.q_rows), dv)
             self.xt16b = QB.f16_tiled_buffer(P, c.ffn, dv)
-            self.launches_per_chunk = 1 + 9 * c.layers + (1 if nbuf > 0 else 0)
+            self.launches_per_chunk = 1 + 10 * c.layers + (1 if nbuf > 0 else 0)
 
     def gemm8(self, pair, xt, N, Kdim, Y, aux, epi, ldy):
         Wt, St = self.m.packed[id(pair[0])]

@@ -149,8 +149,9 @@ def f16_tile(x, xt) -> None:
 
 
 def gemm16_prefill(Wt, St, xt, Y, aux, N: int, K: int, P: int, epi: str, ldy: int, status: Status) -> None:
-    """The prefill GEMM in fp16 arithmetic: weights dequantised to fp16 as gemv_v2_source does (lab/qwen_batched.py:493-498),
-    fp16 activations (tiled by `f16_tile`), fp32 accumulation over all of K on tcgen05."""
+    """The prefill GEMM in the arithmetic of the reference's `cublas` mode (scripts/qwen_prefill.py:37-53, 156-160): weights
+    dequantised to fp16 (`dq`, lab/qwen_batched.py:493-498) inside the kernel, fp16 activations (tiled by `f16_tile` or
+    `rmsnorm_f16_tiled`), fp32 accumulation over all of K on tcgen05."""
     _ffi.call("q4b_mm_prefill_q4_0_f16", _p(Wt), _p(St), _p(xt), _p(Y), _p(aux), N, K, P, _ffi.EPI[epi], ldy, _p(status.word), _stream())
 
 

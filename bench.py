@@ -400,13 +400,14 @@ def bench_batched(model, cfg, B: int, steps: int, warmup: int, local_rank: int, 
     return out
 
 
-def bench_prefill(model, cfg, steps: int, warmup: int, local_rank: int, torch, i8_peak: dict, profile: bool = False) -> dict:
+def bench_prefill(model, cfg, steps: int, warmup: int, local_rank: int, torch, i8_peak: dict, profile: bool = False,
+                  profile_linears: str = "q8") -> dict:
     """One 2048-token prompt through the prefill path (tiled Q8_1 quantisers, tcgen05 int8 MMQ, causal flash attention)."""
     synth = importlib.import_module("3080lab_b200.synth")
     engine = importlib.import_module("3080lab_b200.engine")
     P = 2048
     m = engine.FusedQwen(model, max_len=P, device=f"cuda:{local_rank}")
-    pf = engine.Prefill(m, P)
+    pf = engine.Prefill(m, P, linears=profile_linears if profile else "q8")   # a profiler run may look at the fp16 route alone
     ids = synth.synth_prompt(cfg, P, 0)
     host_ids = torch.from_numpy(ids).pin_memory()
     pf.tok.copy_(host_ids)
@@ -726,7 +727,7 @@ def run_other_workload(args, local_rank: int) -> None:
     model = synth.synth_model(cfg, 0)
     if args.workload == "prefill2048":
         print(json.dumps(bench_prefill(model, cfg, args.steps, args.warmup, local_rank, torch,
-                                       {} if args.profile else measure_i8_peak(torch), args.profile)), flush=True)
+                                       {} if args.profile else measure_i8_peak(torch), args.profile, args.prefill_linears)), flush=True)
         return
     B = 8 if args.workload == "batched8" else 32
     print(json.dumps(bench_batched(model, cfg, B, args.steps, args.warmup, local_rank, torch, peaks, peak_kind,
@@ -885,6 +886,8 @@ def main() -> None:
     ap.add_argument("--tcgen05", action="store_true", help="batch-1 linears on the tcgen05 exact-digit GEMV instead of the mma.sync one")
     ap.add_argument("--prompt", type=int, default=PROMPT, help="prompt length (512 = the benchmark configuration)")
     ap.add_argument("--layers", type=int, default=0, help="profile runs only: cut the model to this many layers")
+    ap.add_argument("--prefill-linears", choices=["q8", "f16"], default="q8",
+                    help="prefill2048 with --profile: which route's graph to replay (the benchmark itself times both)")
     ap.add_argument("--profile", action="store_true",
                     help="short run for a profiler: only the warm-up and timed graph replays, no e2e / roofline / CPU legs")
     args = ap.parse_args()
