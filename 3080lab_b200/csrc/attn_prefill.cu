@@ -57,8 +57,7 @@ __global__ void __launch_bounds__(FT) flash_prefill_kernel(const __half* qkv, co
                                                            int max_len, int pos0, float scale_log2e, int pre, uint8_t* xt) {
   extern __shared__ __align__(16) uint8_t sm[];
   uint8_t* sQ = sm;                      // [BQ][PITCH]
-  uint8_t* sK = sQ + BQ * PITCH;         // [BK][PITCH]
-  uint8_t* sV = sK + BK * PITCH;         // [BK][PITCH]
+  uint8_t* sKV = sQ + BQ * PITCH;        // [2 stages][K, V][BK][PITCH]: the next key tile lands while this one is used
   const int t = threadIdx.x, warp = t >> 5, lane = t & 31, g = lane >> 2, tq = lane & 3;
   const int h = blockIdx.y, kvh = h / (NH / NKV);
   const int qt = (int)gridDim.x - 1 - (int)blockIdx.x;           // longest key ranges first
@@ -109,19 +108,31 @@ __global__ void __launch_bounds__(FT) flash_prefill_kernel(const __half* qkv, co
   const __half* kbase = kc + (size_t)kvh * max_len * HD;
   const __half* vbase = vc + (size_t)kvh * max_len * HD;
 
-  for (int k0 = 0; k0 <= last_key; k0 += BK) {
-    __syncthreads();                                             // previous tile fully consumed
-    for (int i = t; i < BK * (HD / 8); i += FT) {                // 16-byte chunks
+  // key tile -> stage: 16-byte asynchronous copies, rows past the last visible key zero-filled (source size 0)
+  auto issue = [&](int k0, int stg) {
+    uint8_t* dK = sKV + (size_t)stg * 2 * BK * PITCH;
+    uint8_t* dV = dK + BK * PITCH;
+    for (int i = t; i < BK * (HD / 8); i += FT) {
       const int r = i / (HD / 8), c = i - r * (HD / 8);
-      uint4 kv = make_uint4(0u, 0u, 0u, 0u), vv = kv;
-      if (k0 + r <= last_key) {
-        kv = *reinterpret_cast<const uint4*>(kbase + (size_t)(k0 + r) * HD + c * 8);
-        vv = *reinterpret_cast<const uint4*>(vbase + (size_t)(k0 + r) * HD + c * 8);
-      }
-      *reinterpret_cast<uint4*>(sK + r * PITCH + c * 16) = kv;
-      *reinterpret_cast<uint4*>(sV + r * PITCH + c * 16) = vv;
+      const bool live = k0 + r <= last_key;
+      const size_t src = (size_t)(live ? k0 + r : 0) * HD + c * 8;
+      const uint32_t n = live ? 16u : 0u;
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"((uint32_t)__cvta_generic_to_shared(dK + r * PITCH + c * 16)),
+                   "l"(kbase + src), "r"(n)
+                   : "memory");
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"((uint32_t)__cvta_generic_to_shared(dV + r * PITCH + c * 16)),
+                   "l"(vbase + src), "r"(n)
+                   : "memory");
     }
-    __syncthreads();
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  issue(0, 0);
+  for (int k0 = 0, it = 0; k0 <= last_key; k0 += BK, ++it) {
+    asm volatile("cp.async.wait_group 0;" ::: "memory");          // this thread's part of tile `it` has landed
+    __syncthreads();                                             // ... everyone's; and tile it - 1 is fully consumed
+    if (k0 + BK <= last_key) issue(k0 + BK, (it + 1) & 1);
+    const uint8_t* sK = sKV + (size_t)(it & 1) * 2 * BK * PITCH;
+    const uint8_t* sV = sK + BK * PITCH;
 
     // ---- S = Q K^T for 16 rows x 64 keys
     float sacc[8][4];
@@ -252,7 +263,7 @@ __global__ void __launch_bounds__(FT) flash_prefill_kernel(const __half* qkv, co
   }
 }
 
-constexpr size_t FLASH_SMEM = (size_t)(BQ + 2 * BK) * PITCH;
+constexpr size_t FLASH_SMEM = (size_t)(BQ + 4 * BK) * PITCH;
 
 }  // namespace
 
