@@ -478,7 +478,25 @@ __global__ void __launch_bounds__(GT, NT <= 2 ? 2 : 1) gemv_f16mma_kernel(const 
     return;
   }
   const int npr = pr1 - pr0;
+  // resid: the old values of every item of this thread are loaded first, as 8-byte pairs (at most NT items: npr <= 64,
+  // B <= 8 NT).  A load per item in the loop below would wait behind the previous item's store to the same array and pay
+  // the global-memory latency once per item.
+  const bool resid2 = a.epi == Q4B_EPI_RESID && ((a.ldy | a.N) & 1) == 0 && (reinterpret_cast<uintptr_t>(a.Y) & 7) == 0;
+  float2 oldv[NT];
+  if (resid2) {
+#pragma unroll
+    for (int it = 0; it < NT; ++it) {
+      const int i = t + it * GT;
+      oldv[it] = make_float2(0.f, 0.f);
+      if (i < npr * a.B) {
+        const int col = i / npr, row = tile * ROWS + 2 * (pr0 + i - col * npr);
+        if (row < a.N) oldv[it] = *reinterpret_cast<const float2*>(reinterpret_cast<const float*>(a.Y) + (size_t)col * a.ldy + row);
+      }
+    }
+  }
+  int it = -1;
   for (int i = t; i < npr * a.B; i += GT) {
+    ++it;
     const int col = i / npr, pl = i - col * npr, pr = pr0 + pl;
     float v0 = 0.f, v1 = 0.f;
     if (a.ksplit > 1) {
@@ -512,8 +530,16 @@ __global__ void __launch_bounds__(GT, NT <= 2 ? 2 : 1) gemv_f16mma_kernel(const 
       }
       case Q4B_EPI_RESID: {
         float* Y = reinterpret_cast<float*>(a.Y);
-        Y[o] += v0;
-        if (two) Y[o + 1] += v1;
+        if (resid2) {
+          float2 ov = make_float2(0.f, 0.f);
+#pragma unroll
+          for (int q = 0; q < NT; ++q)                                       // static indexing keeps oldv in registers
+            if (q == it) ov = oldv[q];
+          *reinterpret_cast<float2*>(Y + o) = make_float2(ov.x + v0, ov.y + v1);
+        } else {
+          Y[o] += v0;
+          if (two) Y[o + 1] += v1;
+        }
         break;
       }
       case Q4B_EPI_LOGITS: {
