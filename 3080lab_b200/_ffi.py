@@ -11,7 +11,7 @@ from pathlib import Path
 LIB_PATH = Path(__file__).resolve().parent / "libq4b200.so"
 
 OK, E_SHAPE, E_ALIGN, E_WORKSPACE, E_CUDA, E_ARG, E_TIMEOUT = 0, -1, -2, -3, -4, -5, -6
-EPI = {"store": 0, "biasf": 1, "resid": 2, "swiglu": 3, "logits": 4, "swiglu_q8": 5, "biasf_rope_kv": 6}
+EPI = {"store": 0, "biasf": 1, "resid": 2, "swiglu": 3, "logits": 4, "swiglu_q8": 5, "biasf_rope_kv": 6, "swiglu_f16t": 7}
 X_F16, X_F32 = 0, 1
 
 _P, _I, _F, _Z = C.c_void_p, C.c_int, C.c_float, C.c_size_t

@@ -302,6 +302,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const __grid
         tc::tmem_wait_st();                                // warp-wide
         tc::fence_before_sync();
         if (lane == 0) tc::mbar_arrive(&a_full[as]);
+        if ((warp & 3) == 0 && lane == 0) stamp(1, u);
       }
       if (((b0 + G16 - 1) & 7) == 7) {
         __syncwarp();
@@ -326,6 +327,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const __grid
           const int s = u % SBU;
           tc::mbar_expect_tx(&b_full[s], UNIT16);
           bulk_g2s(stage + (size_t)s * UNIT16, xbase + (size_t)u * UNIT16, UNIT16, &b_full[s]);
+          stamp(0, u);
         };
         for (int j = 0; j < WB16 && j < NBATCH; ++j) load_w(j);
         pdl_wait();
@@ -401,6 +403,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const __grid
           }
           tc::mma_commit(&a_empty[as]);
           tc::mma_commit(&b_empty[s]);
+          stamp(2, u);
         }
         tc::mma_commit(&d_full[0]);
       }
@@ -591,6 +594,37 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const __grid
       asm volatile("bar.sync 1, %0;" ::"n"(NRW * 32) : "memory");
       if (t == 0) stamp(10, 6);                            // rounded tile in shared memory
       swiglu_q8_phase(a, abuf, rt, tok_tile, t);
+    } else if (F16 && a.epi == Q4B_EPI_SWIGLU_F16T) {       // compiled into the fp16 instance only
+      // fp16 mode: the rounded products in the operand order of the next fp16 GEMM (see f16_tiled_kernel).  This row tile
+      // makes product columns 64 rt .. 64 rt + 63 = k-blocks 2 rt, 2 rt + 1 of the product row.  Through shared memory (the
+      // dead weight slab; rows padded to 144 bytes so that eight tokens' 16-byte reads fall into distinct banks), then
+      // 16-byte stores, eight tokens = 128 contiguous bytes.
+      constexpr int AP = 72;                               // halves per staged token row
+      __half* abuf = reinterpret_cast<__half*>(slabW);
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        int n;
+        const float prod = swiglu_pair(acc2[j], r, j, n);
+        abuf[(cq * 32 + n) * AP + (r >> 1)] = __float2half_rn(row < a.N ? prod : 0.f);
+      }
+      asm volatile("bar.sync 1, %0;" ::"n"(NRW * 32) : "memory");
+      const int KB2 = a.N >> 6;
+#pragma unroll
+      for (int itx = 0; itx < 2; ++itx) {
+        const int item = t + itx * (NRW * 32);
+        const int r8 = item & 7, wd = (item >> 3) & 7, gq = item >> 6, tk = gq * 8 + r8;
+        if (tok_tile * NTOK + tk < a.P) {
+          const uint4 v = *reinterpret_cast<const uint4*>(abuf + tk * AP + wd * 8);
+          uint4 o;                                           // halves (0..7) -> (0,4,1,5,2,6,3,7)
+          o.x = __byte_perm(v.x, v.z, 0x5410);
+          o.y = __byte_perm(v.x, v.z, 0x7632);
+          o.z = __byte_perm(v.y, v.w, 0x5410);
+          o.w = __byte_perm(v.y, v.w, 0x7632);
+          uint8_t* rec = reinterpret_cast<uint8_t*>(a.Y) + ((size_t)tok_tile * KB2 + (size_t)(2 * rt + (wd >> 2))) * REC16;
+          *reinterpret_cast<uint4*>(rec + gq * 512 + (wd & 3) * 128 + r8 * 16) = o;
+        }
+      }
+      asm volatile("bar.sync 1, %0;" ::"n"(NRW * 32) : "memory");   // the other row half reuses the buffer
     } else if (a.epi == Q4B_EPI_SWIGLU) {
 #pragma unroll
       for (int j = 0; j < 16; ++j) {
@@ -700,8 +734,10 @@ int mmq_prefill(const void* Wt, const void* St, const void* Xt, void* Y, const v
                 int ldy, uint32_t* status, cudaStream_t st, const float* cosT, const float* sinT, void* kc, void* vc, int NH,
                 int NKV, int max_len, int pos0, float* Y2, int parts, int f16) {
   if (f16 && epilogue == Q4B_EPI_SWIGLU_Q8) return fail(Q4B_E_ARG, "mmq_prefill: no swiglu_q8 epilogue in fp16 mode");
+  if (epilogue == Q4B_EPI_SWIGLU_F16T && (!f16 || (N % 128) || !aligned16(Y)))
+    return fail(Q4B_E_ARG, "mmq_prefill: swiglu_f16t is an fp16-mode epilogue, needs N a multiple of 128 and a tiled fp16 output buffer");
   if (N <= 0 || P <= 0 || K <= 0 || (K % 256)) return fail(Q4B_E_SHAPE, "mmq_prefill: N, P > 0 and K a positive multiple of 256 required");
-  if (epilogue < Q4B_EPI_STORE || epilogue > Q4B_EPI_BIASF_ROPE_KV) return fail(Q4B_E_ARG, "mmq_prefill: unknown epilogue");
+  if (epilogue < Q4B_EPI_STORE || epilogue > Q4B_EPI_SWIGLU_F16T) return fail(Q4B_E_ARG, "mmq_prefill: unknown epilogue");
   if (epilogue == Q4B_EPI_SWIGLU && (N % 2)) return fail(Q4B_E_SHAPE, "mmq_prefill: swiglu needs an even row count");
   if (epilogue == Q4B_EPI_SWIGLU_Q8 && ((N % 128) || !aligned16(Y)))
     return fail(Q4B_E_SHAPE, "mmq_prefill: swiglu_q8 needs a row count that is a multiple of 128 and a tiled Q8_1 output buffer");
@@ -716,7 +752,8 @@ int mmq_prefill(const void* Wt, const void* St, const void* Xt, void* Y, const v
   if (!Wt || !St || !Xt || !Y || !status || !aligned16(Wt) || !aligned16(St) || !aligned16(Xt))
     return fail(Q4B_E_ALIGN, "mmq_prefill: null or misaligned pointer");
   if (epilogue == Q4B_EPI_BIASF && !AUX) return fail(Q4B_E_ALIGN, "mmq_prefill: biasf needs AUX");
-  auto kern = f16 ? mmq_prefill_kernel<false, true> : g_prefill_trace ? mmq_prefill_kernel<true, false> : mmq_prefill_kernel<false, false>;
+  auto kern = f16 ? (g_prefill_trace ? mmq_prefill_kernel<true, true> : mmq_prefill_kernel<false, true>)
+                  : (g_prefill_trace ? mmq_prefill_kernel<true, false> : mmq_prefill_kernel<false, false>);
   const size_t smem_bytes = f16 ? PF_SMEM16 : PF_SMEM;
   if (cudaError_t e = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), smem_bytes); e != cudaSuccess) {
     set_cuda_error(e, "mmq_prefill: cudaFuncSetAttribute");

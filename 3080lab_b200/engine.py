@@ -491,7 +491,7 @@ class Prefill:
         """linears: "q8" = the reference's `i8` prefill mode (Q8_1 activations, int8 MMQ, described above); "f16" = the
         arithmetic of its `cublas` mode (scripts/qwen_prefill.py:37-53, 156-160: weights dequantised to fp16, fp16
         activations, fp32 accumulation), with the dequantisation inside the GEMM kernel - about three times
-        faster per pass and without the int8 rounding of the activations, ten launches per layer (RMSNorm into the operand
+        faster per pass and without the int8 rounding of the activations, nine launches per layer (RMSNorm into the operand
         order, GEMM, attention, operand tiling, GEMM ...).
         fused: the reference's seven launches per layer (scripts/qwen_prefill.py:196-246): the QKV GEMM rotates and
         appends K/V (`biasf_kv`), the flash kernel emits the o-projection's Q8_1 input (`q8`), the gate/up GEMM emits the
@@ -555,7 +555,7 @@ class Prefill:
             self.h2 = torch.zeros(nbuf, P, c.hidden, dtype=f32, device=dv) if nbuf > 0 else None
             self.xt16 = QB.f16_tiled_buffer(P, max(c.hidden, c.q_rows), dv)
             self.xt16b = QB.f16_tiled_buffer(P, c.ffn, dv)
-            self.launches_per_chunk = 1 + 10 * c.layers + (1 if nbuf > 0 else 0)
+            self.launches_per_chunk = 1 + 9 * c.layers + (1 if nbuf > 0 else 0)
 
     def gemm8(self, pair, xt, N, Kdim, Y, aux, epi, ldy):
         Wt, St = self.m.packed[id(pair[0])]
@@ -585,7 +585,7 @@ class Prefill:
         """fp16 route: x [P, Kdim] fp16 (None: already in the operand buffer) -> operand order -> the GEMM; a `resid` GEMM
         may be split along K like the int8 one (`self._pending` parts left for the next norm to add)."""
         Wt, St = self.m.packed[id(pair[0])]
-        xt = self.xt16b if Kdim == self.m.cfg.ffn else self.xt16
+        xt = self.xt16b if Kdim == self.m.cfg.ffn and N != 2 * self.m.cfg.ffn else self.xt16
         if x is not None:
             QB.f16_tile(x, xt)
         n = self.parts.get(Kdim, 1) if epi == "resid" else 1
@@ -611,8 +611,8 @@ class Prefill:
                             m.max_len, pos0, m.scale)
             self.gemm16(L["o"], self.att, H, c.q_rows, self.h, None, "resid", H)
             self.norm16(L["ln2"])
-            self.gemm16(L["gu"], None, 2 * c.ffn, H, self.xm, None, "swiglu", c.ffn)
-            self.gemm16(L["down"], self.xm, H, c.ffn, self.h, None, "resid", H)
+            self.gemm16(L["gu"], None, 2 * c.ffn, H, self.xt16b, None, "swiglu_f16t", c.ffn)   # products land in down's operand order
+            self.gemm16(L["down"], None, H, c.ffn, self.h, None, "resid", H)
         if self._pending:
             QB.add_rows(self.h, self.h2[:self._pending])
             self._pending = 0

@@ -472,7 +472,7 @@ def bench_prefill(model, cfg, steps: int, warmup: int, local_rank: int, torch, i
     def gu16_all():
         for L in L0:
             Wt, St = m.packed[id(L["gu"][0])]
-            QB_.gemm16_prefill(Wt, St, pf16.xt16, pf16.xm, None, 2 * cfg.ffn, cfg.hidden, P, "swiglu", cfg.ffn, pf16.status)
+            QB_.gemm16_prefill(Wt, St, pf16.xt16, pf16.xt16b, None, 2 * cfg.ffn, cfg.hidden, P, "swiglu_f16t", cfg.ffn, pf16.status)   # as the pass runs it
     QB_ = importlib.import_module("3080lab_b200.qwen_batched")
     us_gu16 = time_kernel(gu16_all, cfg.layers, 3, torch)
     pf16.status.check("prefill, fp16 route")

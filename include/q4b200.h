@@ -51,6 +51,8 @@ extern "C" {
 #define Q4B_EPI_SWIGLU_Q8 5 /* Q8_1 MMQ only: the SwiGLU product rounded to fp16 and quantised in the epilogue:
                                Y int8 [cols, N/2], AUX (written) fp16 [cols, N/64]; N a multiple of 64 */
 
+#define Q4B_EPI_SWIGLU_F16T 7 /* q4b_mm_prefill_q4_0_f16 only: the SwiGLU product rounded to fp16 and written in the operand
+                               order of the next fp16 GEMM (Y = a q4b_f16_tiled_bytes(P, N / 2) buffer; N a multiple of 128) */
 #define Q4B_EPI_BIASF_ROPE_KV 6 /* q4b_rmsnorm_qkv_rope_kv only: bias, round, RoPE of q and k, K/V append (see there) */
 
 #define Q4B_X_F16 0
@@ -293,7 +295,7 @@ int q4b_attn_prefill_cached(const void* qkv, const void* kc, const void* vc, voi
  * kernel: the expander warps write the fp16 A operand into tensor memory, tcgen05.mma.kind::f16 accumulates, no dense fp16
  * copy of the matrix and no per-block rescale; the epilogue works on the fp32 sums (the reference's matmul rounds them to
  * fp16 first).  About 3.7 times the speed of the int8 MMQ above on B200 and free of the activations' int8 rounding.  xt = q4b_f16_tiled(x): q4b_f16_tiled_bytes(rows, K) = ceil(rows/128) *
- * K/32 * 8192 bytes, zero-filled once by the caller.  Epilogues store, biasf, resid, swiglu, logits. */
+ * K/32 * 8192 bytes, zero-filled once by the caller.  Epilogues store, biasf, resid, swiglu, swiglu_f16t, logits. */
 size_t q4b_f16_tiled_bytes(int rows, int K);
 int q4b_f16_tiled(const void* x, void* xt, int rows, int K, q4b_stream_t stream);
 int q4b_mm_prefill_q4_0_f16(const void* Wt, const void* St, const void* xt, void* Y, const void* AUX, int N, int K, int P,

@@ -479,3 +479,25 @@ def test_gemm16_resid_split_along_k_matches_the_unsplit_launch(P, n, k, parts):
     a, b = y1.cpu().numpy(), y2.cpu().numpy()
     assert not np.isnan(b).any()
     assert np.abs(a - b).max() / np.abs(a).max() < 1e-5        # the same products, summed in parts
+
+
+@pytest.mark.parametrize("P,n,k", [(200, 256, 512), (2048, 1024, 256), (130, 384, 768)])
+def test_swiglu_f16t_epilogue_equals_swiglu_then_tiling(P, n, k):
+    """The fused epilogue of the fp16 gate/up GEMM writes the same bits into the next GEMM's operand as the plain swiglu
+    epilogue followed by `f16_tile` (also with a last row pair that has only one row tile, n = 384)."""
+    QB = pkg("qwen_batched")
+    rng = np.random.default_rng(P + k)
+    W = rng.integers(0, 2 ** 32, size=(n, k // 8), dtype=np.uint32).view(np.int32)
+    S = rng.uniform(0.002, 0.02, size=(n, k // 32)).astype(np.float16)
+    Wt, St = QB.pack_q4(dev(W), dev(S))
+    xt = QB.f16_tiled_buffer(P, k, "cuda")
+    QB.f16_tile(dev(rng.standard_normal((P, k)).astype(np.float16)), xt)
+    st = QB.Status("cuda")
+    y = torch.zeros(P, n // 2, dtype=torch.float16, device="cuda")
+    QB.gemm16_prefill(Wt, St, xt, y, None, n, k, P, "swiglu", n // 2, st)
+    want = QB.f16_tiled_buffer(P, n // 2, "cuda")
+    QB.f16_tile(y, want)
+    got = QB.f16_tiled_buffer(P, n // 2, "cuda")
+    QB.gemm16_prefill(Wt, St, xt, got, None, n, k, P, "swiglu_f16t", n // 2, st)
+    st.check()
+    assert torch.equal(got, want)
