@@ -226,10 +226,11 @@ def _prefill(torch, ffi) -> None:
     # fp16 mode of the same kernel (256 rows x 128 tokens per CTA, units of four k-blocks): phases and unit pace
     xt16 = QB.f16_tiled_buffer(P, k, "cuda")
     QB.f16_tile(x, xt16)
-    f16 = traced(lambda: QB.gemm16_prefill(Wt, St, xt16, y, None, n, k, P, "swiglu", n // 2, st))
+    xt16b = QB.f16_tiled_buffer(P, n // 2, "cuda")
+    f16 = traced(lambda: QB.gemm16_prefill(Wt, St, xt16, xt16b, None, n, k, P, "swiglu_f16t", n // 2, st))
     nu = k // 32 // 4
     ph = f16[10, :6]
-    print(f"fp16 mode [gate/up, swiglu], clocks from entry: set-up done {ph[1] - ph[0]}; units requested {(f16[0, :nu] - ph[0]).tolist()}; "
+    print(f"fp16 mode [gate/up, swiglu_f16t], clocks from entry: set-up done {ph[1] - ph[0]}; units requested {(f16[0, :nu] - ph[0]).tolist()}; "
           f"expanded (first warp of each group) {(f16[1, :nu] - ph[0]).tolist()}; MMAs issued {(f16[2, :nu] - ph[0]).tolist()}; "
           f"main loop left {ph[2] - ph[0]}; both epilogue passes written {ph[3] - ph[0]}; tensor memory released {ph[4] - ph[0]}")
     st.check()
