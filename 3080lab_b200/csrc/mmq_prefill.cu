@@ -329,9 +329,12 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const __grid
           bulk_g2s(stage + (size_t)s * UNIT16, xbase + (size_t)u * UNIT16, UNIT16, &b_full[s]);
           stamp(0, u);
         };
-        for (int j = 0; j < WB16 && j < NBATCH; ++j) load_w(j);
+        // what the first MMA needs goes first (every CTA of a round fills its rings at the same moment, ~25 MB from L2)
+        load_w(0);
         pdl_wait();
-        for (int u = 0; u < SBU && u < NU; ++u) load_u(u);
+        load_u(0);
+        for (int j = 1; j < WB16 && j < NBATCH; ++j) load_w(j);
+        for (int u = 1; u < SBU && u < NU; ++u) load_u(u);
         for (int ou = 0; ou < NU; ++ou) {
           if (ou + SBU < NU) {
             waitb(&b_empty[ou % SBU], (uint32_t)(ou / SBU) & 1u, ok);
