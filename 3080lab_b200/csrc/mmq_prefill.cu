@@ -119,12 +119,15 @@ __device__ __forceinline__ uint32_t magic_lop(uint32_t d) {
 // SwiGLU of one gate/up row pair (adjacent TMEM lanes = adjacent threads) for the token pair (2 j, 2 j + 1) held in `acc`:
 // the even lane takes token 2 j, the odd lane token 2 j + 1, so each lane evaluates 16 of the 32 products (one exchange
 // and one division per token pair instead of two of each).  Returns the product and the token n it belongs to.
+// FAST (fp16 mode, whose results are held to a tolerance, not to bits): the quotient through the approximate reciprocal.
+template <bool FAST>
 __device__ __forceinline__ float swiglu_pair(uint64_t acc, int r, int j, int& n) {
   const bool odd = r & 1;
   const float v0 = tc::lo2(acc), v1 = tc::hi2(acc);
   const float got = __shfl_xor_sync(0xffffffffu, odd ? v0 : v1, 1);
   const float g = odd ? got : v0, u = odd ? v1 : got;
   n = 2 * j + (odd ? 1 : 0);
+  if constexpr (FAST) return __fdividef(g, 1.f + __expf(-g)) * u;
   return g / (1.f + __expf(-g)) * u;
 }
 // Second halves of the two fused epilogues, kept out of line so that they cost the main loop no registers.
@@ -591,7 +594,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const __grid
 #pragma unroll
       for (int j = 0; j < 16; ++j) {
         int n;
-        const float prod = swiglu_pair(acc2[j], r, j, n);
+        const float prod = swiglu_pair<F16>(acc2[j], r, j, n);
         abuf[(cq * 32 + n) * 64 + (r >> 1)] = __float2half_rn(row < a.N ? prod : 0.f);
       }
       asm volatile("bar.sync 1, %0;" ::"n"(NRW * 32) : "memory");
@@ -607,7 +610,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const __grid
 #pragma unroll
       for (int j = 0; j < 16; ++j) {
         int n;
-        const float prod = swiglu_pair(acc2[j], r, j, n);
+        const float prod = swiglu_pair<F16>(acc2[j], r, j, n);
         abuf[(cq * 32 + n) * AP + (r >> 1)] = __float2half_rn(row < a.N ? prod : 0.f);
       }
       asm volatile("bar.sync 1, %0;" ::"n"(NRW * 32) : "memory");
@@ -632,7 +635,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const __grid
 #pragma unroll
       for (int j = 0; j < 16; ++j) {
         int n;
-        const float prod = swiglu_pair(acc2[j], r, j, n);
+        const float prod = swiglu_pair<F16>(acc2[j], r, j, n);
         const int p = tok0 + n;
         if (p < a.P && row < a.N) reinterpret_cast<__half*>(a.Y)[(size_t)p * a.ldy + (row >> 1)] = __float2half_rn(prod);
       }

@@ -294,7 +294,8 @@ int q4b_attn_prefill_cached(const void* qkv, const void* kc, const void* vc, voi
  * ((q - 8) exact, times the block scale, rounded once), fp16 activations, fp32 accumulation over all of K - here inside one
  * kernel: the expander warps write the fp16 A operand into tensor memory, tcgen05.mma.kind::f16 accumulates, no dense fp16
  * copy of the matrix and no per-block rescale; the epilogue works on the fp32 sums (the reference's matmul rounds them to
- * fp16 first).  About 3.7 times the speed of the int8 MMQ above on B200 and free of the activations' int8 rounding.  xt = q4b_f16_tiled(x): q4b_f16_tiled_bytes(rows, K) = ceil(rows/128) *
+ * fp16 first), and its SwiGLU forms the quotient with the approximate reciprocal (2 ulp of fp32, below the fp16 rounding of
+ * the product).  About 3.7 times the speed of the int8 MMQ above on B200 and free of the activations' int8 rounding.  xt = q4b_f16_tiled(x): q4b_f16_tiled_bytes(rows, K) = ceil(rows/128) *
  * K/32 * 8192 bytes, zero-filled once by the caller.  Epilogues store, biasf, resid, swiglu, swiglu_f16t, logits. */
 size_t q4b_f16_tiled_bytes(int rows, int K);
 int q4b_f16_tiled(const void* x, void* xt, int rows, int K, q4b_stream_t stream);
