@@ -139,12 +139,18 @@ __global__ void __launch_bounds__(FT) flash_prefill_kernel(const __half* qkv, co
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       sacc[j][0] = sacc[j][1] = sacc[j][2] = sacc[j][3] = 0.f;
-      const uint8_t* kr = sK + (8 * j + g) * PITCH;
+      // K fragments of two 16-dimension steps per ldmatrix.x4 (8 keys x 8 dims each: step 2 sp low / high, step 2 sp + 1
+      // low / high) instead of eight 4-byte loads
+      const int mi = lane >> 3;
+      const uint8_t* kr = sK + (8 * j + (lane & 7)) * PITCH + (16 * (mi >> 1) + 8 * (mi & 1)) * 2;
 #pragma unroll
-      for (int s = 0; s < 8; ++s) {
-        const uint32_t b0 = *reinterpret_cast<const uint32_t*>(kr + (16 * s + 2 * tq) * 2);
-        const uint32_t b1 = *reinterpret_cast<const uint32_t*>(kr + (16 * s + 2 * tq + 8) * 2);
-        mma16816(sacc[j], qa[s][0], qa[s][1], qa[s][2], qa[s][3], b0, b1);
+      for (int sp = 0; sp < 4; ++sp) {
+        uint32_t b0, b1, b2, b3;
+        asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(b0), "=r"(b1), "=r"(b2), "=r"(b3)
+                     : "r"((uint32_t)__cvta_generic_to_shared(kr + 64 * sp)));
+        mma16816(sacc[j], qa[2 * sp][0], qa[2 * sp][1], qa[2 * sp][2], qa[2 * sp][3], b0, b1);
+        mma16816(sacc[j], qa[2 * sp + 1][0], qa[2 * sp + 1][1], qa[2 * sp + 1][2], qa[2 * sp + 1][3], b2, b3);
       }
     }
     // ---- scale, causal mask, online softmax (base 2)
