@@ -683,9 +683,10 @@ def perplexity(m: FusedQwen, ids, chunk: int = 0):
     """Mean next-token negative log-likelihood of the sequence `ids` under the two activation paths, the reference's
     quality check of int8 activations (scripts/qwen_prefill.py:315-333: all positions through the final norm and the
     head, NLL of the actual next tokens):
-      "i8"   the prefill path (Q8_1 activations, int8 MMQ), in chunks of `chunk` tokens (0 = one chunk);
-      "f16"  the decode path token by token (fp16 activations, exact block dots).
-    -> {"i8": nll, "f16": nll, "tokens": n - 1}.  Log-softmax and the gather are host-side torch: this is a check, not a
+      "i8"     the prefill path (Q8_1 activations, int8 MMQ), in chunks of `chunk` tokens (0 = one chunk);
+      "cublas" the fp16 prefill path (`Prefill(linears="f16")`), the reference's yardstick in this check;
+      "f16"    the decode path token by token (fp16 activations, exact block dots).
+    -> {"i8": nll, "cublas": nll, "f16": nll, "tokens": n - 1}.  Log-softmax and the gather are host-side torch: this is a check, not a
     hot path.  The reference runs it on real text; without a model file any token sequence serves, and what is reported
     is the DIFFERENCE between the two paths."""
     ids = np.asarray(ids, np.int64)
@@ -708,31 +709,38 @@ def perplexity(m: FusedQwen, ids, chunk: int = 0):
     chunk = chunk or n
     if n % chunk:
         raise ValueError("the sequence length must be a multiple of the chunk")
-    pf = Prefill(m, chunk)
-    nll8 = torch.zeros((), dtype=torch.float64, device=m.device)
     x = torch.empty(chunk, c.hidden, dtype=torch.float16, device=m.device)
     lg = torch.empty(32, c.vocab, dtype=torch.float32, device=m.device)
     st = QB.Status(m.device)
-    for s0 in range(0, n, chunk):
-        pf.tok.copy_(torch.from_numpy(ids[s0:s0 + chunk]).to(m.device))
-        pf.chunk(s0)
-        K.rms(pf.h, m.norm, x, c.eps)
-        for r0 in range(0, chunk, 32):
-            rows = min(32, chunk - r0)
-            if m.head is None:
-                QB.head_batched(m.head16, x[r0:r0 + rows], lg[:rows])
-            else:
-                Wt, St = m.packed[id(m.head[0])]
-                xq = torch.empty(rows, c.hidden, dtype=torch.int8, device=m.device)
-                xd = torch.empty(rows, c.hidden // 32, dtype=torch.float16, device=m.device)
-                QB.quant_q8(x[r0:r0 + rows], xq, xd)
-                QB.gemm8(Wt, St, xq, xd, lg, None, c.vocab, c.hidden, rows, "logits", c.vocab, st)
-            pos = torch.arange(s0 + r0, s0 + r0 + rows, device=m.device)
-            keep = pos < n - 1
-            if bool(keep.any()):
-                lp = torch.log_softmax(lg[:rows].double(), -1)
-                picked = lp[torch.arange(rows, device=m.device)[keep], tgt[pos[keep]]]
-                nll8 -= picked.sum()
-    pf.status.check("prefill")
+
+    def prefill_nll(linears: str) -> float:
+        m.reset()
+        pf = Prefill(m, chunk, linears=linears)
+        nll = torch.zeros((), dtype=torch.float64, device=m.device)
+        for s0 in range(0, n, chunk):
+            pf.tok.copy_(torch.from_numpy(ids[s0:s0 + chunk]).to(m.device))
+            pf.chunk(s0)
+            K.rms(pf.h, m.norm, x, c.eps)
+            for r0 in range(0, chunk, 32):
+                rows = min(32, chunk - r0)
+                if m.head is None:
+                    QB.head_batched(m.head16, x[r0:r0 + rows], lg[:rows])
+                else:
+                    Wt, St = m.packed[id(m.head[0])]
+                    xq = torch.empty(rows, c.hidden, dtype=torch.int8, device=m.device)
+                    xd = torch.empty(rows, c.hidden // 32, dtype=torch.float16, device=m.device)
+                    QB.quant_q8(x[r0:r0 + rows], xq, xd)
+                    QB.gemm8(Wt, St, xq, xd, lg, None, c.vocab, c.hidden, rows, "logits", c.vocab, st)
+                pos = torch.arange(s0 + r0, s0 + r0 + rows, device=m.device)
+                keep = pos < n - 1
+                if bool(keep.any()):
+                    lp = torch.log_softmax(lg[:rows].double(), -1)
+                    picked = lp[torch.arange(rows, device=m.device)[keep], tgt[pos[keep]]]
+                    nll -= picked.sum()
+        pf.status.check("prefill")
+        return float(nll / (n - 1))
+
+    out = {"i8": prefill_nll("q8"), "cublas": prefill_nll("f16")}   # the two prefill modes the reference's check compares
     st.check("head")
-    return {"i8": float(nll8 / (n - 1)), "f16": float(nll16 / (n - 1)), "tokens": n - 1}
+    out.update({"f16": float(nll16 / (n - 1)), "tokens": n - 1})
+    return out

@@ -126,7 +126,8 @@ def test_chunked_prefill_equals_single_chunk():
 
 def test_nll_of_int8_and_fp16_activation_paths_agree():
     """The reference's quality check of int8 activations (scripts/qwen_prefill.py:315-333): mean next-token NLL over all
-    positions, prefill path (Q8_1 activations) against the token-by-token decode path (fp16 activations).  On a small
+    positions, prefill path (Q8_1 activations; and the fp16 prefill mode the reference compares it with) against the
+    token-by-token decode path (fp16 activations).  On a small
     random-weight model the two must agree to well under one percent of the NLL itself."""
     s, E = pkg("synth"), pkg("engine")
     cfg = s.CONFIGS["small"]
@@ -138,6 +139,7 @@ def test_nll_of_int8_and_fp16_activation_paths_agree():
     assert np.isfinite(r["i8"]) and np.isfinite(r["f16"])
     assert 0.5 * np.log(cfg.vocab) < r["f16"] < 2.0 * np.log(cfg.vocab)      # random weights: near the uniform level
     assert abs(r["i8"] - r["f16"]) < 5e-3 * r["f16"]
+    assert abs(r["cublas"] - r["f16"]) < 2e-3 * r["f16"]                      # the fp16 prefill mode: no int8 rounding
 
 
 def _rand_q4(rng, n, k):
