@@ -497,7 +497,8 @@ def bench_prefill(model, cfg, steps: int, warmup: int, local_rank: int, torch, i
                      "achieved": ach_gu, "peak": i8_peak.get("tops") or nominal_int8, "unit": "TOP/s (int8)",
                      "frac": ach_gu / (i8_peak.get("tops") or nominal_int8),
                      "peak_kind": "of measured (tcgen05.mma.kind::i8 micro-benchmark in this run)" if i8_peak.get("tops") else "of nominal dense int8",
-                     "frac_of_nominal_4500": ach_gu / nominal_int8, "measured_i8_peak": i8_peak, "us_per_launch": us_gu, "traffic": None},
+                     "frac_of_nominal_4500": ach_gu / nominal_int8, "measured_i8_peak": i8_peak, "us_per_launch": us_gu,
+                     "traffic": ncu_traffic_table().get("prefill_gate_up")},
         "e2e": {"value": P / e2e_ms * 1e3, "unit": "tok/s", "h2d_bytes_per_step": P * 8, "d2h_bytes_per_step": 8},
         "nll": {"int8_activations": nll["i8"], "fp16_prefill": nll["cublas"], "fp16_activations": nll["f16"], "tokens": nll["tokens"],
                 "what": "mean next-token NLL over the first 512 prompt tokens (uniform random tokens): int8 prefill, fp16 prefill (the reference's cublas mode), token-by-token decode"},
