@@ -581,11 +581,10 @@ class Prefill:
         else:
             QB.rmsnorm_q8_tiled(self.h, w, self.xt, self.m.cfg.eps)
 
-    def gemm16(self, pair, x, N, Kdim, Y, aux, epi, ldy):
-        """fp16 route: x [P, Kdim] fp16 (None: already in the operand buffer) -> operand order -> the GEMM; a `resid` GEMM
-        may be split along K like the int8 one (`self._pending` parts left for the next norm to add)."""
+    def gemm16(self, pair, xt, x, N, Kdim, Y, aux, epi, ldy):
+        """fp16 route: x [P, Kdim] fp16 (None: already there) -> operand buffer xt -> the GEMM; a `resid` GEMM may be split
+        along K like the int8 one (`self._pending` parts left for the next norm to add)."""
         Wt, St = self.m.packed[id(pair[0])]
-        xt = self.xt16b if Kdim == self.m.cfg.ffn and N != 2 * self.m.cfg.ffn else self.xt16
         if x is not None:
             QB.f16_tile(x, xt)
         n = self.parts.get(Kdim, 1) if epi == "resid" else 1
@@ -606,13 +605,13 @@ class Prefill:
         self._pending = 0
         for i, L in enumerate(m.L):
             self.norm16(L["ln1"])
-            self.gemm16(L["qkv"], None, c.qkv_rows, H, self.qkv, L["qkv_b"], "biasf", c.qkv_rows)
+            self.gemm16(L["qkv"], self.xt16, None, c.qkv_rows, H, self.qkv, L["qkv_b"], "biasf", c.qkv_rows)
             QB.attn_prefill(self.qkv, m.cos, m.sin, m.kc[i], m.vc[i], self.att, c.n_heads, c.n_kv_heads, c.head_dim,
                             m.max_len, pos0, m.scale)
-            self.gemm16(L["o"], self.att, H, c.q_rows, self.h, None, "resid", H)
+            self.gemm16(L["o"], self.xt16, self.att, H, c.q_rows, self.h, None, "resid", H)
             self.norm16(L["ln2"])
-            self.gemm16(L["gu"], None, 2 * c.ffn, H, self.xt16b, None, "swiglu_f16t", c.ffn)   # products land in down's operand order
-            self.gemm16(L["down"], None, H, c.ffn, self.h, None, "resid", H)
+            self.gemm16(L["gu"], self.xt16, None, 2 * c.ffn, H, self.xt16b, None, "swiglu_f16t", c.ffn)   # products land in down's operand order
+            self.gemm16(L["down"], self.xt16b, None, H, c.ffn, self.h, None, "resid", H)
         if self._pending:
             QB.add_rows(self.h, self.h2[:self._pending])
             self._pending = 0

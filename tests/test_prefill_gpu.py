@@ -124,6 +124,23 @@ def test_chunked_prefill_equals_single_chunk():
     assert float(rel) < 2e-2
 
 
+def test_chunked_prefill_equals_single_chunk_on_the_fp16_route():
+    """The same for `linears="f16"`: no int8 rounding, so the two agree to the fp16 level (the attention sums differ in
+    order between one key range and two)."""
+    s, E = pkg("synth"), pkg("engine")
+    cfg = s.ModelConfig("small128", 2, 512, 1536, 4, 2, 128, 4096)
+    model = s.synth_model(cfg, 3)
+    ids = s.synth_prompt(cfg, 128, 3)
+    m1 = E.FusedQwen(model, max_len=128)
+    E.prefill(m1, ids, linears="f16")
+    m2 = E.FusedQwen(model, max_len=128)
+    E.prefill(m2, ids, chunk=64, linears="f16")
+    assert torch.equal(m1.vc[0], m2.vc[0])
+    rel = (m1.logits - m2.logits).abs().max() / m1.logits.abs().max()
+    assert float(rel) < 5e-3
+    assert int(m1.tok.item()) == int(m2.tok.item())
+
+
 def test_nll_of_int8_and_fp16_activation_paths_agree():
     """The reference's quality check of int8 activations (scripts/qwen_prefill.py:315-333): mean next-token NLL over all
     positions, prefill path (Q8_1 activations; and the fp16 prefill mode the reference compares it with) against the
