@@ -75,6 +75,7 @@ SIGNATURES = {
     "q4b_attn_decode_cached": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _F, _P]),
     "q4b_pack_q4_0": (_I, [_P, _P, _P, _P, _I, _I, _P]),
     "q4b_q8_tiled_bytes": (_Z, [_I, _I]),
+    "q4b_debug_mmq_prefill_expired_wait": (_I, [_P, _P, _P, _P, _I, _I, _I, _P, _P]),
     "q4b_f16_tiled_bytes": (_Z, [_I, _I]),
     "q4b_f16_tiled": (_I, [_P, _P, _I, _I, _P]),
     "q4b_mm_prefill_q4_0_f16": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P]),

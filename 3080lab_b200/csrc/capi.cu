@@ -68,6 +68,7 @@ int gemv_mma(const void*, const void*, const void*, void*, const void*, int, int
              int max_len = 0, int withhold_chunk = -1, const GemvLookahead* look = nullptr);
 int gemv_mma_ksplit(int, int);
 void mmq_prefill_trace(long long*);
+void mmq_prefill_debug_no_copy(bool);
 void attn_batched_kernel(int);
 int tp_allreduce(const void* const*, void* const*, int, int, uint32_t, const uint32_t*, float*, int, int, const float*, float, void*,
                  void*, uint32_t*, uint32_t, cudaStream_t);
@@ -278,6 +279,14 @@ int q4b_rmsnorm_f16_tiled_add(float* h, const float* h_add, int n_add, const flo
                               q4b_stream_t stream) {
   if (n_add < 0 || n_add > 3 || (n_add > 0 && !h_add)) return fail(Q4B_E_ARG, "rmsnorm_f16_tiled_add: 0 .. 3 addends");
   return rmsnorm_f16_tiled(h, w, xt, rows, H, eps, S(stream), n_add ? const_cast<float*>(h_add) : nullptr, n_add);
+}
+
+int q4b_debug_mmq_prefill_expired_wait(const void* Wt, const void* St, const void* xt, void* Y, int N, int K, int P, uint32_t* status,
+                                       q4b_stream_t stream) {
+  mmq_prefill_debug_no_copy(true);
+  const int rc = mmq_prefill(Wt, St, xt, Y, nullptr, N, K, P, Q4B_EPI_LOGITS, N, status, S(stream));
+  mmq_prefill_debug_no_copy(false);
+  return rc;
 }
 
 int q4b_mmq_prefill_trace(int64_t* device_buffer, size_t entries) {

@@ -84,6 +84,8 @@ struct PrefillArgs {
   int N, K, P, epi, ldy;
   int pair16;          // fp16 outputs may go out two rows at a time (N, ldy even, Y 4-byte aligned)
   long long* trace;    // per-role clock stamps of CTA (0, 0, 0), [11][64] (see q4b_mmq_prefill_trace); null = off
+  int debug_no_copy;   // TRACE instance only: the copy thread issues nothing, every wait of the pipeline runs out (see
+                       // q4b_debug_mmq_prefill_expired_wait)
   float* Y2;           // split launch: where parts 1 .. of K store their sums, fp32 [parts - 1][P, ldy]
   int kb_bound[5];     // k-block bounds of the parts (multiples of 8); unsplit: {0, K / 32}
   // fused RoPE + K/V append (Q4B_EPI_BIASF_ROPE_KV): tokens of ONE sequence at positions pos0 .., cache fp16 [NKV, max_len, 128]
@@ -196,6 +198,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const __grid
   // issuer - operand written, stage landed, slot free - was measured: 8 % slower than these separate ones.)
   __shared__ __align__(8) uint64_t w_full[WB], w_empty[WB], b_full[SB], b_empty[SB], a_full[NA], a_empty[NA], d_full[NSLOT],
       d_empty[NSLOT];
+  __shared__ __align__(8) uint64_t drain;                  // failure path only: the MMA issuer waits here for its MMAs to retire
   __shared__ uint32_t tmem_base_s;
 
   uint8_t* slabW = smem;                                   // [WB][8][128 rows][16]
@@ -233,6 +236,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const __grid
       tc::mbar_init(&a_full[i], NEW);
       tc::mbar_init(&a_empty[i], 1);                       // commit of the MMA that read it
     }
+    tc::mbar_init(&drain, 1);
     for (int i = 0; i < NSLOT; ++i) {
       tc::mbar_init(&d_full[i], 1);                        // commit of the MMA that wrote it
       tc::mbar_init(&d_empty[i], NRW);                     // read out by every rescale warp
@@ -252,12 +256,12 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const __grid
   // cost ~10 % of the kernel's time even when switched off at run time, hence a separate instance.
   auto stamp = [&](int role, int b) {
     if constexpr (TRACE) {
-      if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && b < 64) a.trace[role * 64 + b] = clock64();
+      if (a.trace && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && b < 64) a.trace[role * 64 + b] = clock64();
     }
   };
 
   if constexpr (TRACE) {
-    if (t == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) a.trace[10 * 64 + 0] = t_entry;
+    if (a.trace && t == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) a.trace[10 * 64 + 0] = t_entry;
   }
   if (t == 0) stamp(10, 1);                                // set-up done (tensor memory, barriers)
 
@@ -353,7 +357,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const __grid
         }
       }
     } else
-    if (lane == 0) {
+    if (lane == 0 && !(TRACE && a.debug_no_copy)) {
       auto load_w = [&](int j) {                           // weight batch j -> slot j % WB
         const int s = j % WB;
         tc::mbar_expect_tx(&w_full[s], WBATCH_W + WBATCH_S);
@@ -412,6 +416,10 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const __grid
           stamp(2, u);
         }
         tc::mma_commit(&d_full[0]);
+        if (!ok) {                                         // as in the int8 mode below
+          tc::mma_commit(&drain);
+          tc::mbar_wait_parked(&drain, 0u);
+        }
       }
     } else
     if (lane == 0) {
@@ -432,6 +440,10 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const __grid
         tc::mma_commit(&a_empty[as]);
         tc::mma_commit(&b_empty[s]);
         stamp(2, b);
+      }
+      if (!ok) {                                           // a wait ran out: nobody may be waiting for the accumulators, so
+        tc::mma_commit(&drain);                            // see the MMAs retire here before tensor memory is freed
+        tc::mbar_wait_parked(&drain, 0u);
       }
     }
   } else if (warp >= NRW) {
@@ -692,10 +704,12 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const __grid
 }
 
 long long* g_prefill_trace = nullptr;
+bool g_prefill_no_copy = false;
 
 }  // namespace
 
 void mmq_prefill_trace(long long* buf) { g_prefill_trace = buf; }
+void mmq_prefill_debug_no_copy(bool on) { g_prefill_no_copy = on; }
 
 size_t f16_tiled_bytes(int P, int K) { return (size_t)((P + NTOK - 1) / NTOK) * (size_t)(K / 32) * REC16; }
 
@@ -758,8 +772,9 @@ int mmq_prefill(const void* Wt, const void* St, const void* Xt, void* Y, const v
   if (!Wt || !St || !Xt || !Y || !status || !aligned16(Wt) || !aligned16(St) || !aligned16(Xt))
     return fail(Q4B_E_ALIGN, "mmq_prefill: null or misaligned pointer");
   if (epilogue == Q4B_EPI_BIASF && !AUX) return fail(Q4B_E_ALIGN, "mmq_prefill: biasf needs AUX");
-  auto kern = f16 ? (g_prefill_trace ? mmq_prefill_kernel<true, true> : mmq_prefill_kernel<false, true>)
-                  : (g_prefill_trace ? mmq_prefill_kernel<true, false> : mmq_prefill_kernel<false, false>);
+  const bool traced = g_prefill_trace || g_prefill_no_copy;
+  auto kern = f16 ? (traced ? mmq_prefill_kernel<true, true> : mmq_prefill_kernel<false, true>)
+                  : (traced ? mmq_prefill_kernel<true, false> : mmq_prefill_kernel<false, false>);
   const size_t smem_bytes = f16 ? PF_SMEM16 : PF_SMEM;
   if (cudaError_t e = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), smem_bytes); e != cudaSuccess) {
     set_cuda_error(e, "mmq_prefill: cudaFuncSetAttribute");
@@ -787,6 +802,7 @@ int mmq_prefill(const void* Wt, const void* St, const void* Xt, void* Y, const v
   a.max_len = max_len;
   a.pos0 = pos0;
   a.trace = g_prefill_trace;
+  a.debug_no_copy = g_prefill_no_copy ? 1 : 0;
   a.Y2 = Y2;
   a.kb_bound[0] = 0;
   a.kb_bound[1] = a.kb_bound[2] = a.kb_bound[3] = a.kb_bound[4] = K / 32;

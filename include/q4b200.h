@@ -309,6 +309,13 @@ int q4b_mm_prefill_f16_resid_ksplit(const void* Wt, const void* St, const void* 
 int q4b_rmsnorm_f16_tiled_add(float* h, const float* h_add, int n_add, const float* w, void* xt, int rows, int H, float eps,
                               q4b_stream_t stream);
 
+/* The failure path of the prefill GEMM's bounded waits, in a form that always returns: q4b_mmq_prefill_q4_0_q8_1 (logits
+ * epilogue, ldy = N) with its copy thread issuing nothing, so that every wait of the pipeline runs into its limit (about a
+ * second by the SM clock).  The threads stop waiting, the kernel sets *status non-zero, frees its tensor memory and ends;
+ * Y is meaningless. */
+int q4b_debug_mmq_prefill_expired_wait(const void* Wt, const void* St, const void* xt, void* Y, int N, int K, int P, uint32_t* status,
+                                       q4b_stream_t stream);
+
 /* Pipeline timeline of the prefill GEMM: while a device buffer of 11 x 64 int64 is set, every q4b_mmq_prefill_* launch
  * runs a second instance of the kernel whose CTA (0, 0, 0) writes SM-clock stamps for its first 64 k-blocks, one row per
  * event: 0 activation stage requested, 1 A operand written (first expander warp), 2 MMA issued and committed, 3 accumulator

@@ -520,3 +520,33 @@ def test_swiglu_f16t_epilogue_equals_swiglu_then_tiling(P, n, k):
     QB.gemm16_prefill(Wt, St, xt, got, None, n, k, P, "swiglu_f16t", n // 2, st)
     st.check()
     assert torch.equal(got, want)
+
+
+def test_prefill_gemm_expired_waits_set_the_status_word_and_return():
+    """The bounded waits of the tcgen05 pipeline: with the copy thread issuing nothing every role runs into its limit
+    (about a second), the kernel sets the status word, lets its MMAs retire, frees its tensor memory and returns; the
+    next launch on the same context computes correctly."""
+    QB, ffi, o = pkg("qwen_batched"), pkg("_ffi"), oracle()
+    rng = np.random.default_rng(5)
+    P, n, k = 128, 128, 256
+    W = rng.integers(0, 2 ** 32, size=(n, k // 8), dtype=np.uint32).view(np.int32)
+    S = rng.uniform(0.002, 0.02, size=(n, k // 32)).astype(np.float16)
+    Wt, St = QB.pack_q4(dev(W), dev(S))
+    x = rng.standard_normal((P, k)).astype(np.float16)
+    xt = QB.q8_tiled_buffer(P, k, "cuda")
+    QB.quant_q8_tiled(dev(x), xt)
+    y = torch.zeros(P, n, dtype=torch.float32, device="cuda")
+    st = QB.Status("cuda")
+    ffi.call("q4b_debug_mmq_prefill_expired_wait", Wt.data_ptr(), St.data_ptr(), xt.data_ptr(), y.data_ptr(), n, k, P,
+             st.word.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()                                  # the kernel came back
+    assert int(st.word.item()) != 0
+    with pytest.raises(ffi.Q4BError) as e:
+        st.check("prefill")
+    assert e.value.code == ffi.E_TIMEOUT
+    QB.gemm8_prefill(Wt, St, xt, y, None, n, k, P, "logits", n, st)
+    torch.cuda.synchronize()
+    st.check("prefill")
+    xq, xd, _ = o.quant_q8_1(x)
+    ref = o.mmq(W, S, xq, xd)
+    assert np.abs(y.cpu().numpy() - ref).max() / np.abs(ref).max() < 1e-5
