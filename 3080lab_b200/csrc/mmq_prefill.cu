@@ -342,7 +342,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const __grid
         load_u(0);
         for (int j = 1; j < WB16 && j < NBATCH; ++j) load_w(j);
         for (int u = 1; u < SBU && u < NU; ++u) load_u(u);
-        for (int ou = 0; ou < NU; ++ou) {
+        for (int ou = 0; ou < NU && ok; ++ou) {            // (after an expired wait: no further copies)
           if (ou + SBU < NU) {
             waitb(&b_empty[ou % SBU], (uint32_t)(ou / SBU) & 1u, ok);
             load_u(ou + SBU);
@@ -373,8 +373,8 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const __grid
       for (int j = 0; j < WB && j < NBATCH; ++j) load_w(j);   // weights do not depend on the previous kernel
       pdl_wait();                                             // activations do
       for (int b = 0; b < SB && b < KB; ++b) load_b(b);
-      for (int ob = 0; ob < KB; ++ob) {                       // refill each ring slot as soon as its k-block is done with
-        if (ob + SB < KB) {
+      for (int ob = 0; ob < KB && ok; ++ob) {                 // refill each ring slot as soon as its k-block is done with
+        if (ob + SB < KB) {                                   // (after an expired wait: no further copies into a ring in use)
           waitb(&b_empty[ob % SB], (uint32_t)(ob / SB) & 1u, ok);
           load_b(ob + SB);
         }
