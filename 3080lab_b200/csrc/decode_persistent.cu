@@ -153,7 +153,7 @@ template <int HD>
 __global__ void __launch_bounds__(PT, 1) decode_persistent_kernel(const __grid_constant__ PArgs a) {
   extern __shared__ __align__(128) uint8_t smem[];
   __shared__ __align__(8) uint64_t full[MAX_STAGES], empty[MAX_STAGES];
-  __shared__ __align__(8) uint64_t aready[NSLOT], dfull[NSLOT], dempty[NSLOT];
+  __shared__ __align__(8) uint64_t aready[NSLOT], dfull[NSLOT], dempty[NSLOT], bar_drain;
   __shared__ uint32_t tmem_base_s;
   __shared__ volatile uint32_t abort_s;                 // a bounded wait expired somewhere in this CTA: stop waiting
   __shared__ float red[8];
@@ -181,6 +181,7 @@ __global__ void __launch_bounds__(PT, 1) decode_persistent_kernel(const __grid_c
       tc::mbar_init(&dfull[s], 1);
       tc::mbar_init(&dempty[s], 4);
     }
+    tc::mbar_init(&bar_drain, 1);            // failure path: the MMA-issuing lane (tc::drain_mmas_on_failure)
     tc::mbar_fence_init();
   }
   for (int i = t; i < a.bkb * 64; i += PT) reinterpret_cast<uint32_t*>(sB)[i] = 0u;   // digit columns 3..7 stay zero
@@ -717,6 +718,7 @@ __global__ void __launch_bounds__(PT, 1) decode_persistent_kernel(const __grid_c
 
   if (!ok) atomicExch(a.status, 1u);
   tc::fence_before_sync();
+  tc::drain_mmas_on_failure(ok, warp == WARP_MMA && lane == 0, &bar_drain);
   __syncthreads();
   if (warp == 0) tc::tmem_dealloc(tmem, 512);
   if (t == 0) {

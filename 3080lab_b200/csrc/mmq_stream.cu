@@ -100,6 +100,7 @@ __global__ void __launch_bounds__(ROWS * ((MODE == MODE_Q8 && NT >= 16) ? 2 : 1)
   __shared__ __align__(8) uint64_t bar_load[MAX_BATCH];
   __shared__ __align__(8) uint64_t bar_mma[2];
   __shared__ __align__(8) uint64_t bar_free[2];          // warpgroup 1 has read an accumulator slot
+  __shared__ __align__(8) uint64_t bar_drain;            // see tc::drain_mmas_on_failure
   __shared__ uint32_t tmem_base_s;
 
   const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
@@ -138,6 +139,7 @@ __global__ void __launch_bounds__(ROWS * ((MODE == MODE_Q8 && NT >= 16) ? 2 : 1)
     tc::mbar_init(&bar_mma[1], 4);
     tc::mbar_init(&bar_free[0], 4);
     tc::mbar_init(&bar_free[1], 4);
+    tc::mbar_init(&bar_drain, 4);                        // failure path: the four issuing lanes
     tc::mbar_fence_init();
   }
   stamp();                                              // TMEM allocated, barriers initialised
@@ -544,8 +546,8 @@ __global__ void __launch_bounds__(ROWS * ((MODE == MODE_Q8 && NT >= 16) ? 2 : 1)
       }
     }
   }
-  if (!ok && t == 0) atomicExch(a.status, 1u);
   tc::fence_before_sync();
+  if (tc::drain_mmas_on_failure(ok, wg == 0 && lane == 0, &bar_drain) && t == 0) atomicExch(a.status, 1u);   // any thread's expired wait
   __syncthreads();
   if (warp == 0) tc::tmem_dealloc(tmem, TCOLS);
   stamp();                                              // end

@@ -189,6 +189,22 @@ __device__ __forceinline__ void mma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
+// Failure path of a kernel that holds tensor memory, called by EVERY thread of the CTA just before the memory is freed.  A
+// thread whose bounded wait has expired stops waiting, so the CTA can get here with MMAs still in flight; freeing tensor
+// memory under them must not happen.  If any thread reports !ok, the issuing threads (`issuer`; `bar` was initialised with
+// their number) commit once more and everybody waits, again bounded, for those MMAs to retire.  One barrier-with-vote per
+// kernel when nothing went wrong.
+// Returns whether any thread had failed.
+__device__ __forceinline__ bool drain_mmas_on_failure(bool ok, bool issuer, uint64_t* bar) {
+  const bool failed = __syncthreads_or(ok ? 0 : 1) != 0;
+  if (failed) {
+    if (issuer) mma_commit(bar);
+    mbar_wait_parked(bar, 0u);
+    __syncthreads();
+  }
+  return failed;
+}
+
 // ---- packed fp32 pairs (sm_100 has two-wide fp32 add / mul / fma on 64-bit registers) ---------------------------------
 __device__ __forceinline__ uint64_t pack2(float lo, float hi) {
   return (uint64_t)__float_as_uint(lo) | ((uint64_t)__float_as_uint(hi) << 32);
