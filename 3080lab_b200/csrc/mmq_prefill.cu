@@ -279,9 +279,12 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const __grid
     for (int u = 0; u < NU; ++u) {
       const int b0 = u * G16, ws = (b0 >> 3) % WB16;
       if ((b0 & 7) == 0) waitb(&w_full[ws], (uint32_t)((b0 >> 3) / WB16) & 1u, ok);
+      // EVERY warp waits for the slot of EVERY unit, not only of the units it expands: a parity wait is only sound if the
+      // waiter has seen the phase before, and a group that skipped four units could otherwise meet a slot barrier two
+      // phases behind (unit u - 4 written but not yet consumed), which reads as "free" and lets it overwrite live data.
+      const int as = u % NAU;
+      waitb(&a_empty[as], ((uint32_t)(u / NAU) & 1u) ^ 1u, ok);     // the MMAs of unit u - NAU have read this operand
       if (u % NXG == grp) {
-        const int as = u % NAU;
-        waitb(&a_empty[as], ((uint32_t)(u / NAU) & 1u) ^ 1u, ok);   // the MMAs of unit u - NAU have read this operand
         tc::fence_after_sync();
 #pragma unroll
         for (int gh = 0; gh < G16 * MH16; ++gh) {
