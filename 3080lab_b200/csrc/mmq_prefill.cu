@@ -198,7 +198,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const __grid
   // issuer - operand written, stage landed, slot free - was measured: 8 % slower than these separate ones.)
   __shared__ __align__(8) uint64_t w_full[WB], w_empty[WB], b_full[SB], b_empty[SB], a_full[NA], a_empty[NA], d_full[NSLOT],
       d_empty[NSLOT];
-  __shared__ __align__(8) uint64_t drain;                  // failure path only: the MMA issuer waits here for its MMAs to retire
+  __shared__ __align__(8) uint64_t drain;                  // failure path only (tc::drain_mmas_on_failure)
   __shared__ uint32_t tmem_base_s;
 
   uint8_t* slabW = smem;                                   // [WB][8][128 rows][16]
@@ -419,10 +419,6 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const __grid
           stamp(2, u);
         }
         tc::mma_commit(&d_full[0]);
-        if (!ok) {                                         // as in the int8 mode below
-          tc::mma_commit(&drain);
-          tc::mbar_wait_parked(&drain, 0u);
-        }
       }
     } else
     if (lane == 0) {
@@ -443,10 +439,6 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const __grid
         tc::mma_commit(&a_empty[as]);
         tc::mma_commit(&b_empty[s]);
         stamp(2, b);
-      }
-      if (!ok) {                                           // a wait ran out: nobody may be waiting for the accumulators, so
-        tc::mma_commit(&drain);                            // see the MMAs retire here before tensor memory is freed
-        tc::mbar_wait_parked(&drain, 0u);
       }
     }
   } else if (warp >= NRW) {
@@ -701,6 +693,9 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const __grid
   if (t == 0) stamp(10, 3);                                // epilogue written
   if (!ok) atomicExch(a.status, 1u);
   tc::fence_before_sync();
+  // any thread's expired wait: the MMA issuer sees its MMAs retire before tensor memory is freed (it may itself have met
+  // no expired wait: the others' late arrivals satisfy its barriers)
+  tc::drain_mmas_on_failure(ok, warp == W_MMA && lane == 0, &drain);
   __syncthreads();
   if (warp == 0) tc::tmem_dealloc(tmem, 512);
   if (t == 0) stamp(10, 4);                                // tensor memory released
