@@ -33,6 +33,8 @@
 // all lanes polling.  The epilogues are written for latency, not instruction count: loads hoisted above the stores of
 // the same array, one SwiGLU product per lane pair and token, fp16 outputs as 4-byte row-pair stores.
 // All waits are bounded; after the first expired wait a thread stops waiting (status word, garbage out, no hang).
+#include <algorithm>
+
 #include "q4b_internal.h"
 #include "tc05.cuh"
 
@@ -60,19 +62,22 @@ constexpr size_t PF_SMEM = (size_t)WB * (WBATCH_W + WBATCH_S) + (size_t)SB * STA
 // tensor-memory tile per 128 rows, and the per-block rescale - the int8 mode's bottleneck - does not exist.  A CTA makes
 // 256 weight rows x 128 tokens (two accumulators), so every activation record fetched from L2 feeds two MMAs.  The
 // pipeline moves UNITS of G k-blocks so that the one MMA-issuing thread pays its waits and commits once per 4 G MMAs.
-// Measured on B200, gate/up 2048 x 17920 x 1536: 156 us = 722 TFLOP/s (0.44 of the measured cuBLAS bf16 peak) against
-// 586 us for the int8 mode; 0.237 us per k-block and 8.1 us fixed per tile (removing the copies changes nothing, half of
-// the MMAs -16 %, the expansion -14 %: again no single stage, and the fixed part is 40 % of a tile).
+// CTAs are persistent (one per SM, tiles c, c + #CTAs, ..): rings and parities run on across tiles, so the next tile's
+// copies, its first expansion and - once the accumulators are in registers - its first MMAs proceed under the epilogue.
+// Measured on B200, gate/up 2048 x 17920 x 1536: 134 - 145 us = 780 - 840 TFLOP/s (about half of the measured cuBLAS bf16
+// peak) against 586 us for the int8 mode; ~0.25 us per k-block and 5.6 us fixed per tile (8.1 before the CTAs were
+// persistent; removing the copies changes nothing, half of the MMAs -16 %, the expansion -14 %: again no single stage).
 constexpr int G16 = 4;                    // k-blocks per unit
 constexpr int MH16 = 2;                   // row halves: a CTA makes 256 weight rows x 128 tokens, two accumulators, so that
                                           // an activation record fetched from L2 feeds two MMAs (the copies set the pace)
 constexpr int WB16 = 2;                   // weight batches in flight (8 k-blocks x 2 row halves each)
 constexpr int NAU = 2;                    // A units in tensor memory (G16 x MH16 x 16 columns each)
 constexpr int SBU = 3;                    // activation units in shared memory
-constexpr int NXG = (NRW + NEW) / 4;      // expander groups of four warps (one per TMEM lane quarter): every warp expands
+constexpr int NXG = (NRW + NEW) / 4;      // groups of four worker warps (one warp per TMEM lane quarter)
 constexpr uint32_t REC16 = 128 * 32 * 2;  // one k-block of fp16 activations for 128 tokens
 constexpr uint32_t UNIT16 = G16 * REC16;
-constexpr size_t PF_SMEM16 = (size_t)WB * (WBATCH_W + WBATCH_S) + (size_t)SBU * UNIT16 + 128;
+constexpr uint32_t SCR16 = 128 * 72 * 2;  // fp16 mode's epilogue staging (the weight ring is live then: the next tile's weights)
+constexpr size_t PF_SMEM16 = (size_t)WB * (WBATCH_W + WBATCH_S) + (size_t)SBU * UNIT16 + SCR16 + 128;
 
 struct PrefillArgs {
   const uint8_t* Wt;   // tile-packed nibbles
@@ -83,6 +88,7 @@ struct PrefillArgs {
   uint32_t* status;
   int N, K, P, epi, ldy;
   int pair16;          // fp16 outputs may go out two rows at a time (N, ldy even, Y 4-byte aligned)
+  int tx, ty, ntiles;  // fp16 mode (persistent CTAs): row pairs, token tiles, tiles in all = tx * ty * K parts
   long long* trace;    // per-role clock stamps of CTA (0, 0, 0), [11][64] (see q4b_mmq_prefill_trace); null = off
   int debug_no_copy;   // TRACE instance only: the copy thread issues nothing, every wait of the pipeline runs out (see
                        // q4b_debug_mmq_prefill_expired_wait)
@@ -266,9 +272,43 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const __grid
   if (t == 0) stamp(10, 1);                                // set-up done (tensor memory, barriers)
 
   // ===================== fp16 mode: every role's main loop =====================
-  [[maybe_unused]] const int NU = KB / G16;                // units of this CTA (KB is a multiple of 8)
-  [[maybe_unused]] auto expand16 = [&]() {
-    // Warps 0 .. 19 in five groups of four (one warp per TMEM lane quarter); group g expands units u = g (mod 5):
+  // Persistent CTAs: CTA c works on tiles c, c + gridDim.x, ..  (tile = row pair fastest, then token tile, then K part).
+  // Rings and their parities run on across tiles, so the copies, the first expansions and (once the accumulators have
+  // been read out) the MMAs of the next tile proceed under the epilogue of this one.
+  struct Tile16 {
+    int row_tile, tok_tile, z, KB, NB, NU;
+    bool have1;
+    size_t wbase;
+    const uint8_t* xbase;
+  };
+  [[maybe_unused]] auto tile16 = [&](int idx) {
+    Tile16 q;
+    const int rx = idx % a.tx, rest = idx / a.tx;
+    q.row_tile = 2 * rx;
+    q.tok_tile = rest % a.ty;
+    q.z = rest / a.ty;
+    const int lo = a.kb_bound[q.z];
+    q.KB = a.kb_bound[q.z + 1] - lo;
+    q.NB = q.KB >> 3;
+    q.NU = q.KB / G16;
+    q.have1 = (q.row_tile + 1) * 128 < a.N;
+    q.wbase = (size_t)q.row_tile * KBT + lo;
+    q.xbase = a.Xt + ((size_t)q.tok_tile * KBT + lo) * REC16;
+    return q;
+  };
+  [[maybe_unused]] int ug0 = 0, wg0 = 0;                   // units / weight batches of this CTA's earlier tiles (expander warps)
+  // fp16 mode's waits say where they gave up: the first expired wait leaves (info << 12 | id << 8 | 1) in the status word,
+  // id 1 weights landed, 2 A slot free, 3 weight slot free, 4 activation slot free, 5 accumulators read out, 6 A operand
+  // written, 7 activations landed, 8 accumulators complete; info = warp and unit, or tile count
+  [[maybe_unused]] auto waitf = [&](uint64_t* bar, uint32_t parity, uint32_t id, uint32_t info) {
+    if (ok && !tc::mbar_wait_parked(bar, parity)) {
+      ok = false;
+      atomicCAS(a.status, 0u, (info << 12) | (id << 8) | 1u);
+    }
+  };
+  [[maybe_unused]] auto expand16 = [&](const Tile16& q) {
+    // Every worker warp runs this loop (the weight ring counts all twenty), two groups of four warps (one warp per TMEM
+    // lane quarter) expand, see below:
     // nibbles -> (q - 8) exactly in fp16 -> times the block scale, rounded once (gemv_v2_source's `dq`,
     // lab/qwen_batched.py:493-498) -> 16 columns of tensor memory per k-block.  A word's 8 weights come out as the pairs
     // (0,4) (1,5) (2,6) (3,7); the activation operand carries the same order within every 8 values.
@@ -276,15 +316,25 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const __grid
     const int r = (warp & 3) * 32 + lane;
     const uint32_t lane_off = (uint32_t)(32 * (warp & 3)) << 16;
     const __half2 c1032 = __float2half2_rn(1032.f), c16th = __float2half2_rn(0.0625f), c72 = __float2half2_rn(-72.f);
-    for (int u = 0; u < NU; ++u) {
-      const int b0 = u * G16, ws = (b0 >> 3) % WB16;
-      if ((b0 & 7) == 0) waitb(&w_full[ws], (uint32_t)((b0 >> 3) / WB16) & 1u, ok);
+    const bool have1 = q.have1;
+    for (int u = 0; u < q.NU; ++u) {
+      const int b0 = u * G16, wg = wg0 + (b0 >> 3), ws = wg % WB16, ug = ug0 + u;
+      if ((b0 & 7) == 0) waitb(&w_full[ws], (uint32_t)(wg / WB16) & 1u, ok);
       // EVERY warp waits for the slot of EVERY unit, not only of the units it expands: a parity wait is only sound if the
       // waiter has seen the phase before, and a group that skipped four units could otherwise meet a slot barrier two
       // phases behind (unit u - 4 written but not yet consumed), which reads as "free" and lets it overwrite live data.
-      const int as = u % NAU;
-      waitb(&a_empty[as], ((uint32_t)(u / NAU) & 1u) ^ 1u, ok);     // the MMAs of unit u - NAU have read this operand
-      if (u % NXG == grp) {
+      // Each tensor-memory slot belongs to ONE group of four warps: the even units (slot 0) to warps 16 .. 19, which have
+      // no epilogue to do and so expand the next tile's first unit while the others still write this tile out, the odd
+      // units (slot 1) to warps 0 .. 3.  A group therefore waits for consecutive phases of its own slot's barrier and for
+      // nothing else - a parity wait is only sound for a waiter that is neither a phase early (a group that skipped units
+      // met a barrier two phases behind and overwrote a live operand) nor a phase late (warps coming out of the epilogue
+      // after the MMAs had moved on blocked for good); the other twelve warps do not touch the slots at all.
+      static_assert(NAU == 2, "slot = unit parity");
+      const int as = ug & 1;
+      const int owner = as ? 0 : NXG - 1;
+      if (owner == grp)
+        waitf(&a_empty[as], ((uint32_t)(ug / NAU) & 1u) ^ 1u, 2u, (uint32_t)(warp << 8) | (uint32_t)(u & 255));
+      if (owner == grp) {
         tc::fence_after_sync();
 #pragma unroll
         for (int gh = 0; gh < G16 * MH16; ++gh) {
@@ -312,49 +362,43 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const __grid
         tc::tmem_wait_st();                                // warp-wide
         tc::fence_before_sync();
         if (lane == 0) tc::mbar_arrive(&a_full[as]);
-        if ((warp & 3) == 0 && lane == 0) stamp(1, u);
+        if ((warp & 3) == 0 && lane == 0) stamp(1, ug);
       }
       if (((b0 + G16 - 1) & 7) == 7) {
         __syncwarp();
         if (lane == 0) tc::mbar_arrive(&w_empty[ws]);      // this warp is done with the batch (whether it expanded any of it or not)
       }
     }
+    ug0 += q.NU;
+    wg0 += q.NB;
   };
   if (warp == W_COPY) {
     // ===================== bulk-copy producer (one thread) =====================
     if constexpr (F16) {
       if (lane == 0) {
-        auto load_w = [&](int j) {                         // batch j of both row halves -> slot j % WB16
-          const int s = j % WB16;
-          tc::mbar_expect_tx(&w_full[s], (have1 ? 2u : 1u) * (WBATCH_W + WBATCH_S));
-          for (int hf = 0; hf < (have1 ? 2 : 1); ++hf) {
-            const size_t wb = wbase + (size_t)hf * KBT + (size_t)j * 8;
-            bulk_g2s(slabW + (size_t)(s * MH16 + hf) * WBATCH_W, a.Wt + wb * 2048, WBATCH_W, &w_full[s]);
-            bulk_g2s(slabS + (size_t)(s * MH16 + hf) * WBATCH_S, a.St + wb * 128, WBATCH_S, &w_full[s]);
-          }
-        };
-        auto load_u = [&](int u) {                         // G16 consecutive records = one contiguous piece
-          const int s = u % SBU;
-          tc::mbar_expect_tx(&b_full[s], UNIT16);
-          bulk_g2s(stage + (size_t)s * UNIT16, xbase + (size_t)u * UNIT16, UNIT16, &b_full[s]);
-          stamp(0, u);
-        };
-        // what the first MMA needs goes first (every CTA of a round fills its rings at the same moment, ~25 MB from L2)
-        load_w(0);
-        pdl_wait();
-        load_u(0);
-        for (int j = 1; j < WB16 && j < NBATCH; ++j) load_w(j);
-        for (int u = 1; u < SBU && u < NU; ++u) load_u(u);
-        for (int ou = 0; ou < NU && ok; ++ou) {            // (after an expired wait: no further copies)
-          if (ou + SBU < NU) {
-            waitb(&b_empty[ou % SBU], (uint32_t)(ou / SBU) & 1u, ok);
-            load_u(ou + SBU);
-          }
-          if (((ou * G16 + G16 - 1) & 7) == 7) {
-            const int oj = (ou * G16) >> 3;
-            if (oj + WB16 < NBATCH) {
-              waitb(&w_empty[oj % WB16], (uint32_t)(oj / WB16) & 1u, ok);
-              load_w(oj + WB16);
+        int ug = 0, wg = 0;                                // units / weight batches requested so far, over all tiles
+        bool first = true;
+        for (int tile = blockIdx.x; tile < a.ntiles && ok; tile += gridDim.x) {
+          const Tile16 q = tile16(tile);
+          for (int j = 0; j < q.NB && ok; ++j, ++wg) {     // a weight batch (both row halves), then its units
+            const int s = wg % WB16;                       // (after an expired wait: no further copies)
+            if (wg >= WB16) waitf(&w_empty[s], (uint32_t)(wg / WB16 - 1) & 1u, 3u, (uint32_t)(j & 255));
+            tc::mbar_expect_tx(&w_full[s], (q.have1 ? 2u : 1u) * (WBATCH_W + WBATCH_S));
+            for (int hf = 0; hf < (q.have1 ? 2 : 1); ++hf) {
+              const size_t wb = q.wbase + (size_t)hf * KBT + (size_t)j * 8;
+              bulk_g2s(slabW + (size_t)(s * MH16 + hf) * WBATCH_W, a.Wt + wb * 2048, WBATCH_W, &w_full[s]);
+              bulk_g2s(slabS + (size_t)(s * MH16 + hf) * WBATCH_S, a.St + wb * 128, WBATCH_S, &w_full[s]);
+            }
+            if (first) {                                   // weights do not depend on the previous kernel, activations do
+              pdl_wait();
+              first = false;
+            }
+            for (int k = 0; k < 8 / G16; ++k, ++ug) {      // G16 consecutive records = one contiguous piece
+              const int sb = ug % SBU;
+              if (ug >= SBU) waitf(&b_empty[sb], (uint32_t)(ug / SBU - 1) & 1u, 4u, (uint32_t)(j & 255));
+              tc::mbar_expect_tx(&b_full[sb], UNIT16);
+              bulk_g2s(stage + (size_t)sb * UNIT16, q.xbase + (size_t)(j * (8 / G16) + k) * UNIT16, UNIT16, &b_full[sb]);
+              stamp(0, ug);
             }
           }
         }
@@ -396,29 +440,34 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const __grid
       if (lane == 0) {
         constexpr uint32_t IDESC16 = tc::idesc_f16(128, NTOK);
         const uint32_t stage0 = tc::smem_u32(stage);
-        for (int u = 0; u < NU; ++u) {
-          const int s = u % SBU, as = u % NAU;
-          waitb(&a_full[as], (uint32_t)(u / NAU) & 1u, ok);
-          waitb(&b_full[s], (uint32_t)(u / SBU) & 1u, ok);
-          tc::fence_after_sync();
+        int ug = 0, it = 0;
+        for (int tile = blockIdx.x; tile < a.ntiles; tile += gridDim.x, ++it) {
+          const Tile16 q = tile16(tile);
+          if (it > 0) waitf(&d_empty[0], (uint32_t)(it - 1) & 1u, 5u, (uint32_t)it);
+          for (int u = 0; u < q.NU; ++u, ++ug) {
+            const int s = ug % SBU, as = ug % NAU;
+            waitf(&a_full[as], (uint32_t)(ug / NAU) & 1u, 6u, (uint32_t)(it << 8) | (uint32_t)(u & 255));
+            waitf(&b_full[s], (uint32_t)(ug / SBU) & 1u, 7u, (uint32_t)(it << 8) | (uint32_t)(u & 255));
+            tc::fence_after_sync();
 #pragma unroll
-          for (int g = 0; g < G16; ++g) {
+            for (int g = 0; g < G16; ++g) {
 #pragma unroll
-            for (int j = 0; j < 2; ++j) {                  // 16 of the k-block's 32 values per instruction
-              // per 8-token group: four 8-value chunks of 128 bytes; chunks 2 j, 2 j + 1 belong to this instruction
-              const uint64_t bdesc = tc::smem_desc_kmajor(stage0 + (uint32_t)s * UNIT16 + (uint32_t)g * REC16 + (uint32_t)j * 256, 128, 512);
+              for (int j = 0; j < 2; ++j) {                // 16 of the k-block's 32 values per instruction
+                // per 8-token group: four 8-value chunks of 128 bytes; chunks 2 j, 2 j + 1 belong to this instruction
+                const uint64_t bdesc = tc::smem_desc_kmajor(stage0 + (uint32_t)s * UNIT16 + (uint32_t)g * REC16 + (uint32_t)j * 256, 128, 512);
 #pragma unroll
-              for (int hf = 0; hf < MH16; ++hf)            // the same activations against both row halves
-                if (hf == 0 || have1)
-                  tc::mma_f16_ts(tmem_d + (uint32_t)hf * 128, tmem_a + (uint32_t)((as * G16 + g) * MH16 + hf) * 16 + (uint32_t)j * 8, bdesc,
-                                 IDESC16, (u | g | j) ? 1u : 0u);
+                for (int hf = 0; hf < MH16; ++hf)          // the same activations against both row halves
+                  if (hf == 0 || q.have1)
+                    tc::mma_f16_ts(tmem_d + (uint32_t)hf * 128, tmem_a + (uint32_t)((as * G16 + g) * MH16 + hf) * 16 + (uint32_t)j * 8, bdesc,
+                                   IDESC16, (u | g | j) ? 1u : 0u);
+              }
             }
+            tc::mma_commit(&a_empty[as]);
+            tc::mma_commit(&b_empty[s]);
+            stamp(2, ug);
           }
-          tc::mma_commit(&a_empty[as]);
-          tc::mma_commit(&b_empty[s]);
-          stamp(2, u);
+          tc::mma_commit(&d_full[0]);
         }
-        tc::mma_commit(&d_full[0]);
       }
     } else
     if (lane == 0) {
@@ -444,7 +493,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const __grid
   } else if (warp >= NRW) {
     // ===================== expanders: thread = weight row, nibbles -> signed bytes -> A operand in tensor memory ==========
     if constexpr (F16) {
-      expand16();
+      for (int tile = blockIdx.x; tile < a.ntiles; tile += gridDim.x) expand16(tile16(tile));
     } else {
     const int r = (warp - NRW) * 32 + lane;                // row of the tile = TMEM lane
     const uint32_t lane_off = (uint32_t)(32 * (warp & 3)) << 16;
@@ -493,10 +542,19 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const __grid
         acc2[8 * half + 2 * q + 1] = tc::fma2(tc::mul2(dw2, x4.y), f1, acc2[8 * half + 2 * q + 1]);
       }
     };
+    // fp16 mode: one pass of this loop per tile of the CTA; int8 mode: exactly one pass
+    for (int it16 = 0, tile = blockIdx.x; F16 ? tile < a.ntiles : it16 < 1; ++it16, tile += gridDim.x) {
+    int e_row = row_tile, e_tok = tok_tile, e_z = blockIdx.z;        // what the epilogue below works on
+    [[maybe_unused]] bool e_have1 = false;
     if constexpr (F16) {
-      // fp16 mode: these warps expand too; then the one accumulator (complete sums over K) is read out once
-      expand16();
-      waitb(&d_full[0], 0u, ok);
+      // fp16 mode: these warps expand too; then the accumulators (complete sums over K) are read out once
+      const Tile16 q = tile16(tile);
+      e_row = q.row_tile;
+      e_tok = q.tok_tile;
+      e_z = q.z;
+      e_have1 = q.have1;
+      expand16(q);
+      waitf(&d_full[0], (uint32_t)it16 & 1u, 8u, (uint32_t)(warp << 8) | (uint32_t)it16);
       tc::fence_after_sync();
     } else {
     // Rolling schedule: the read-back of the next 16 columns is always in flight while the previous 16 are folded, so a
@@ -561,13 +619,17 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const __grid
     pdl_wait();                                            // Y / AUX may be written by the previous kernel
     if (t == 0) stamp(10, 5);                              // previous grid seen complete
     for (int hh = 0; hh < (F16 ? MH16 : 1); ++hh) {
-    const int rt = row_tile + hh;
+    const int rt = e_row + hh;
     if constexpr (F16) {
-      if (hh && !have1) break;
+      if (hh && !e_have1) break;
       uint32_t dA[16], dB[16];
       tc::tmem_ld16(dbase + (uint32_t)hh * 128, dA);
       tc::tmem_ld16(dbase + (uint32_t)hh * 128 + 16, dB);
       tc::tmem_wait_ld();
+      if (hh == (e_have1 ? 1 : 0)) {                       // both accumulators are in registers: the next tile's MMAs may start
+        tc::fence_before_sync();
+        if (lane == 0) tc::mbar_arrive(&d_empty[0]);
+      }
 #pragma unroll
       for (int n = 0; n < 8; ++n) {
         acc2[n] = tc::pack2u(dA[2 * n], dA[2 * n + 1]);
@@ -575,7 +637,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const __grid
       }
     }
     const int row = rt * 128 + r;
-    const int tok0 = tok_tile * NTOK + cq * 32;
+    const int tok0 = e_tok * NTOK + cq * 32;
     const float bias = ((a.epi == Q4B_EPI_BIASF || a.epi == Q4B_EPI_BIASF_ROPE_KV) && row < a.N) ? reinterpret_cast<const float*>(a.AUX)[row] : 0.f;
     if (a.epi == Q4B_EPI_BIASF_ROPE_KV) {
       // The `biasf_kv` epilogue (lab/qwen_batched.py:1316-1362) extended to q: bias, round to fp16, rotate the q and k heads
@@ -590,7 +652,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const __grid
       }
       asm volatile("bar.sync 1, %0;" ::"n"(NRW * 32) : "memory");
       if (t == 0) stamp(10, 6);                            // rounded tile in shared memory
-      rope_kv_phase(a, ybuf, rt, tok_tile * NTOK, t);
+      rope_kv_phase(a, ybuf, rt, e_tok * NTOK, t);
     } else if (a.epi == Q4B_EPI_SWIGLU_Q8) {
       // SwiGLU + re-quantise for `down` (lab/qwen_batched.py:1363-1396): the product rounded to fp16, then the Q8_1
       // quantiser of quant_q8_1.cu on it, written straight into the tiled operand format of the next GEMM.  This row
@@ -606,14 +668,14 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const __grid
       }
       asm volatile("bar.sync 1, %0;" ::"n"(NRW * 32) : "memory");
       if (t == 0) stamp(10, 6);                            // rounded tile in shared memory
-      swiglu_q8_phase(a, abuf, rt, tok_tile, t);
+      swiglu_q8_phase(a, abuf, rt, e_tok, t);
     } else if (F16 && a.epi == Q4B_EPI_SWIGLU_F16T) {       // compiled into the fp16 instance only
       // fp16 mode: the rounded products in the operand order of the next fp16 GEMM (see f16_tiled_kernel).  This row tile
       // makes product columns 64 rt .. 64 rt + 63 = k-blocks 2 rt, 2 rt + 1 of the product row.  Through shared memory (the
       // dead weight slab; rows padded to 144 bytes so that eight tokens' 16-byte reads fall into distinct banks), then
       // 16-byte stores, eight tokens = 128 contiguous bytes.
       constexpr int AP = 72;                               // halves per staged token row
-      __half* abuf = reinterpret_cast<__half*>(slabW);
+      __half* abuf = reinterpret_cast<__half*>(stage + (size_t)SBU * UNIT16);   // its own buffer: the weight ring is live
 #pragma unroll
       for (int j = 0; j < 16; ++j) {
         int n;
@@ -626,14 +688,14 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const __grid
       for (int itx = 0; itx < 2; ++itx) {
         const int item = t + itx * (NRW * 32);
         const int r8 = item & 7, wd = (item >> 3) & 7, gq = item >> 6, tk = gq * 8 + r8;
-        if (tok_tile * NTOK + tk < a.P) {
+        if (e_tok * NTOK + tk < a.P) {
           const uint4 v = *reinterpret_cast<const uint4*>(abuf + tk * AP + wd * 8);
           uint4 o;                                           // halves (0..7) -> (0,4,1,5,2,6,3,7)
           o.x = __byte_perm(v.x, v.z, 0x5410);
           o.y = __byte_perm(v.x, v.z, 0x7632);
           o.z = __byte_perm(v.y, v.w, 0x5410);
           o.w = __byte_perm(v.y, v.w, 0x7632);
-          uint8_t* rec = reinterpret_cast<uint8_t*>(a.Y) + ((size_t)tok_tile * KB2 + (size_t)(2 * rt + (wd >> 2))) * REC16;
+          uint8_t* rec = reinterpret_cast<uint8_t*>(a.Y) + ((size_t)e_tok * KB2 + (size_t)(2 * rt + (wd >> 2))) * REC16;
           *reinterpret_cast<uint4*>(rec + gq * 512 + (wd & 3) * 128 + r8 * 16) = o;
         }
       }
@@ -659,7 +721,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const __grid
           *reinterpret_cast<__half2*>(reinterpret_cast<__half*>(a.Y) + (size_t)p * a.ldy + (row & ~1)) =
               odd ? __floats2half2_rn(got, v1) : __floats2half2_rn(v0, got);
       }
-    } else if (a.epi == Q4B_EPI_RESID && blockIdx.z == 0) {
+    } else if (a.epi == Q4B_EPI_RESID && e_z == 0) {
       // h += sum: all 32 loads first (issued back to back), then the adds and stores; one load-add-store per token in turn
       // would pay the global-memory latency 32 times over, the loads being ordered behind the stores to the same array
       float* y = reinterpret_cast<float*>(a.Y) + (size_t)tok0 * a.ldy + row;
@@ -681,7 +743,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const __grid
         switch (a.epi) {
           case Q4B_EPI_STORE: reinterpret_cast<__half*>(a.Y)[base + row] = __float2half_rn(v); break;
           case Q4B_EPI_BIASF: reinterpret_cast<__half*>(a.Y)[base + row] = __float2half_rn(v + bias); break;
-          case Q4B_EPI_RESID: a.Y2[(size_t)(blockIdx.z - 1) * a.P * a.ldy + base + row] = v; break;   // part z > 0 of a split launch
+          case Q4B_EPI_RESID: a.Y2[(size_t)(e_z - 1) * a.P * a.ldy + base + row] = v; break;   // part z > 0 of a split launch
           case Q4B_EPI_LOGITS: reinterpret_cast<float*>(a.Y)[base + row] = v; break;
           default: break;
         }
@@ -689,9 +751,10 @@ __global__ void __launch_bounds__(PF_THREADS, 1) mmq_prefill_kernel(const __grid
     }
     }
     }
+    }
   }
   if (t == 0) stamp(10, 3);                                // epilogue written
-  if (!ok) atomicExch(a.status, 1u);
+  if (!ok) atomicCAS(a.status, 0u, 1u);
   tc::fence_before_sync();
   // any thread's expired wait: the MMA issuer sees its MMAs retire before tensor memory is freed (it may itself have met
   // no expired wait: the others' late arrivals satisfy its barriers)
@@ -811,6 +874,13 @@ int mmq_prefill(const void* Wt, const void* St, const void* Xt, void* Y, const v
     const int batches = K / 256;                         // whole batches of 8 k-blocks, spread as evenly as they go
     for (int z = 1; z < parts; ++z) a.kb_bound[z] = (int)(((long long)batches * z + parts - 1) / parts) * 8;
     grid.z = parts;
+  }
+  a.tx = a.ty = a.ntiles = 0;
+  if (f16) {                                             // persistent CTAs over (row pair, token tile, K part)
+    a.tx = (int)grid.x;
+    a.ty = (int)grid.y;
+    a.ntiles = a.tx * a.ty * (int)grid.z;
+    grid = dim3((unsigned)std::min(a.ntiles, sm_count()));
   }
   return check_launch(launch_pdl(kern, grid, dim3(PF_THREADS), smem_bytes, st, a), "mmq_prefill");
 }
