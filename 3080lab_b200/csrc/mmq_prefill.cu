@@ -57,8 +57,8 @@ constexpr size_t PF_SMEM = (size_t)WB * (WBATCH_W + WBATCH_S) + (size_t)SB * STA
 // ---- fp16 mode (the second instance of the kernel; q4b_mm_prefill_q4_0_f16) ------------------------------------------
 // The arithmetic of the reference's `cublas` prefill mode (scripts/qwen_prefill.py:37-53 DEQ, :156-160): weights
 // dequantised to fp16 ((q - 8) exact, times the block scale, one rounding), fp16 activations, fp32 accumulation - but
-// with the dequantisation inside the GEMM instead of through a dense fp16 copy of the matrix: the expander warps (all
-// twenty here) write fp16 A operands into tensor memory, tcgen05.mma.kind::f16 accumulates over ALL of K into one
+// with the dequantisation inside the GEMM instead of through a dense fp16 copy of the matrix: expander warps (two groups
+// of four here, each owning one operand slot) write fp16 A operands into tensor memory, tcgen05.mma.kind::f16 accumulates over ALL of K into one
 // tensor-memory tile per 128 rows, and the per-block rescale - the int8 mode's bottleneck - does not exist.  A CTA makes
 // 256 weight rows x 128 tokens (two accumulators), so every activation record fetched from L2 feeds two MMAs.  The
 // pipeline moves UNITS of G k-blocks so that the one MMA-issuing thread pays its waits and commits once per 4 G MMAs.
